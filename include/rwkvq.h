@@ -1,0 +1,151 @@
+/*
+ * rwkvq.h -- C ABI of librwkvq.so: the quantized projection path of the RWKV-7
+ * quantization toolkit AUXStar/rwkv7-quantization, written for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (every entry point):
+ *   - returns 0 (RWKVQ_OK) or a negative RWKVQ_E_* code; never throws, never allocates,
+ *     never synchronizes the host with the device; rwkvq_last_error_string() describes the
+ *     last failure on the calling thread;
+ *   - pointers are DEVICE pointers unless the name says `host`; matrices are row-major with
+ *     an explicit leading dimension in ELEMENTS (ld*); weights are [N, K] with K contiguous,
+ *     exactly the layouts schemes.py / int4/quantize_int4.py / int8/quantize_int8.py of the
+ *     reference write;
+ *   - `stream` is a cudaStream_t passed as void* (0 = the legacy default stream); work is
+ *     only enqueued;
+ *   - `x_dtype` is RWKVQ_F16 or RWKVQ_BF16;
+ *   - `div_mode` selects how the fp32 scale divisions (448/amax, amax/448, 127/amax, amax/127,
+ *     x/awq) are evaluated: RWKVQ_DIV_FULL = PTX div.full.f32, which is what the reference's
+ *     Triton kernels execute on a GPU; RWKVQ_DIV_IEEE = round-to-nearest, which is what
+ *     torch (and the Triton CPU interpreter) compute.
+ *
+ * Each declaration names the reference function it replaces (file:line in the reference tree).
+ */
+#ifndef RWKVQ_H_
+#define RWKVQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RWKVQ_OK 0
+#define RWKVQ_E_BADARG (-1)    /* null pointer, unknown enum value                         */
+#define RWKVQ_E_ALIGN (-2)     /* pointer or leading dimension not 16-byte aligned          */
+#define RWKVQ_E_SHAPE (-3)     /* size outside what the entry point supports                */
+#define RWKVQ_E_ARCH (-4)      /* device is not compute capability 10.x                     */
+#define RWKVQ_E_LAUNCH (-5)    /* CUDA reported a launch / runtime error                    */
+#define RWKVQ_E_TIMEOUT (-6)   /* a bounded device-side wait gave up                        */
+#define RWKVQ_E_WORKSPACE (-7) /* caller-provided scratch is missing or too small           */
+
+#define RWKVQ_F16 0
+#define RWKVQ_BF16 1
+
+#define RWKVQ_DIV_IEEE 0
+#define RWKVQ_DIV_FULL 1
+
+/* flags of the W8A8 entry points */
+#define RWKVQ_FLAG_AMAX_AFTER_BF16 1u /* amax over bf16-rounded x (reference M==1 kernel, fused_fp8_gemm.py:662) */
+#define RWKVQ_FLAG_INT8_SHARED_WSCALE 2u /* k and v use r's weight scale (reference defect, fused_fp8_gemm.py:855-857) */
+#define RWKVQ_FLAG_OUT_VIA_BF16 4u    /* round the result to bf16 before fp16 (fp8_ops.py:77-86)        */
+#define RWKVQ_FLAG_QUANT_FROM_BF16 8u /* quantize bf16(x) instead of x (the GEMM kernels read prep_x's bf16 copy, fused_fp8_gemm.py:248-250) */
+
+int32_t rwkvq_version(void);
+const char* rwkvq_last_error_string(void);
+/* 0 when the current device can run this library (compute capability 10.x). */
+int32_t rwkvq_device_ok(void);
+/* number of this library's kernel launches enqueued by the calling process so far */
+int64_t rwkvq_launch_count(void);
+
+/* out[i] = a[i] / b[i] evaluated with div.full.f32 (div_mode FULL) or IEEE (test hook that lets a CPU
+ * checker reproduce the hardware-defined division of the reference's Triton kernels). */
+int32_t rwkvq_div_f32(const float* a, const float* b, float* out, int64_t n, int32_t div_mode, void* stream);
+
+/* ---------------------------------------------------------------- activation preparation */
+
+/* prep_x / prep_x_kernel (fused_fp8_gemm.py:30-79): out_bf16 = bf16(fp32(x) [/ awq]); amax[0] = max over the
+ * whole call of |fp32(x) [/ awq]| (zeroed by this call first).  awq may be NULL.  out_bf16 may be NULL. */
+int32_t rwkvq_prep_x(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, const float* awq,
+                     void* out_bf16, int64_t ldo, float* amax, int32_t div_mode, void* stream);
+
+/* prep3_x / prep3_x_kernel (fused_fp8_gemm.py:86-150): the same for xr, xk, xv in one launch; amax[0..2]. */
+int32_t rwkvq_prep3_x(const void* xr, const void* xk, const void* xv, int32_t x_dtype, int64_t M, int64_t K,
+                      int64_t ldx, const float* awq_r, const float* awq_k, void* out_r, void* out_k, void* out_v,
+                      int64_t ldo, float* amax3, int32_t div_mode, void* stream);
+
+/* prep_x_fp8 (fused_fp8_gemm.py:341-390): per-call amax, inv = 448 / max(amax, 1e-12) (IEEE, as torch),
+ * codes = e4m3_rn(clamp(x * inv, +-448)), scale[0] = amax / 448.  amax_scratch: one fp32 owned by the caller. */
+int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes,
+                         int64_t ldc, float* scale, float* amax_scratch, void* stream);
+
+/* The activation half of linear_fp8_fused for M above the decode kernel's range (prep_x + the in-loop
+ * quantization of fused_fp8_hwdot_gemm_kernel, fused_fp8_gemm.py:240-250) and of linear_fp8 (fp8_ops.py:71-75):
+ * amax[0] = per-call amax (of bf16(x) with RWKVQ_FLAG_AMAX_AFTER_BF16), codes = e4m3_rn(clamp(v * inv, +-448)) with
+ * inv = 448 / max(amax, 1e-12) under div_mode and v = bf16(x) with RWKVQ_FLAG_QUANT_FROM_BF16, else x;
+ * scale (optional) = amax / 448 under div_mode. */
+int32_t rwkvq_actq_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                       float* amax, float* scale, int32_t div_mode, uint32_t flags, void* stream);
+
+/* prep_x_int8 / _prep_x_int8_kernel (fused_fp8_gemm.py:687-731): per-ROW amax (floor 1e-12), s = 127/amax,
+ * codes = trunc(clamp(x*s, -128, 127)), scales[m] = amax/127. */
+int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes,
+                          int64_t ldc, float* scales, int32_t div_mode, void* stream);
+
+/* ---------------------------------------------------------------- W8A8 decode GEMV (M <= 32) */
+
+/* linear_fp8_m1_fused / linear_fp8_fused (fused_fp8_gemm.py:600-679, 1020-1077, 219-257) for small M:
+ * ONE launch that derives the per-call amax, quantizes x to e4m3 in the prologue and streams W once.
+ * out[M,N] fp16 = fp16( (q(x) . W^T) * (amax/448 * w_scale[0]) ).  awq may be NULL. */
+int32_t rwkvq_gemv_fp8(const void* x, int32_t x_dtype, const float* awq, const uint8_t* w, int64_t ldw,
+                       const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                       int64_t ldx, int32_t div_mode, uint32_t flags, void* stream);
+
+/* linear_rkv_fused / fused_rkv_fp8_kernel (fused_fp8_gemm.py:944-1017, 264-334): r, k, v in ONE launch;
+ * three activations, three amax, three weight scales.  awq_r / awq_k may be NULL. */
+int32_t rwkvq_gemv_fp8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const float* awq_r,
+                           const float* awq_k, const uint8_t* wr, const uint8_t* wk, const uint8_t* wv, int64_t ldw,
+                           const float* sr, const float* sk, const float* sv, void* out_r, void* out_k, void* out_v,
+                           int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                           uint32_t flags, void* stream);
+
+/* linear_int8_fused / fused_int8_gemm_kernel (fused_fp8_gemm.py:734-818) for small M: per-row activation
+ * quantization in the prologue, exact int32 accumulation, out = fp16(float(acc) * (x_scale[m] * w_scale[0])).
+ * acc_out (optional, int32 [M, ldacc]) receives the raw accumulators. */
+int32_t rwkvq_gemv_int8(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale,
+                        void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M, int64_t N, int64_t K,
+                        int64_t ldx, int32_t div_mode, uint32_t flags, void* stream);
+
+/* linear_rkv_int8_fused / fused_rkv_int8_kernel (fused_fp8_gemm.py:825-934). */
+int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const int8_t* wr,
+                            const int8_t* wk, const int8_t* wv, int64_t ldw, const float* sr, const float* sk,
+                            const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N,
+                            int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags, void* stream);
+
+/* ---------------------------------------------------------------- W8A8 GEMM on pre-quantized codes (any M) */
+
+/* The GEMM half of linear_fp8_fused / linear_fp8 (fused_fp8_gemm.py:219-257, fp8_ops.py:77-80):
+ * out = fp16( (a_codes . W^T) * (a_scale * w_scale[0]) ), where a_scale = amax[0]/448 if amax_is_amax != 0
+ * (div_mode applies) or a_scale = amax[0] taken as the scale itself otherwise. */
+int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
+                       const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M,
+                       int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
+
+/* The GEMM half of linear_int8_fused (fused_fp8_gemm.py:734-782): codes int8 [M,K], a_scales fp32 [M]. */
+int32_t rwkvq_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                        const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M,
+                        int64_t N, int64_t K, uint32_t flags, void* stream);
+
+/* The same two GEMMs forced onto the register-streaming mma.sync kernel (any M; the dispatchers above use it
+ * below the tensor-memory kernel's range).  Same reference lines. */
+int32_t rwkvq_gemm_fp8_mma(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
+                           const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M,
+                           int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
+int32_t rwkvq_gemm_int8_mma(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                            const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc,
+                            int64_t M, int64_t N, int64_t K, uint32_t flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RWKVQ_H_ */

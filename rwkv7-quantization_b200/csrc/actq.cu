@@ -1,0 +1,317 @@
+// Activation preparation kernels: bf16 copy + per-call amax (FP8 path), per-call e4m3 codes
+// (large-M FP8 path) and per-row int8 codes (INT8 path).  All HBM/L2-bound elementwise work:
+// 128-bit loads and stores, one row segment per CTA, block reduction + one atomic per CTA.
+#include "common.cuh"
+
+namespace rwkvq {
+
+thread_local char g_err[512] = "";
+std::atomic<int64_t> g_launches{0};
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int32_t check_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+    return RWKVQ_OK;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev != cached_dev) {
+        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+        cached_dev = dev;
+    }
+    return cached > 0 ? cached : 148;
+}
+
+constexpr int kThreads = 256;
+constexpr int kSegElems = kThreads * 8 * 4;   // elements of one row handled by one CTA (vector path)
+
+__device__ __forceinline__ float block_max(float v, float* sh) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = sh[0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) r = fmaxf(r, sh[i]);
+    __syncthreads();
+    return r;
+}
+
+template <int DT>
+__device__ __forceinline__ float load1(const void* x, int64_t i) {
+    const uint16_t v = reinterpret_cast<const uint16_t*>(x)[i];
+    if (DT == RWKVQ_F16) return __half2float(__ushort_as_half(v));
+    return __uint_as_float((uint32_t)v << 16);
+}
+
+// ----------------------------------------------------------------------------------------
+// prep_x for up to three tensors: bf16 copy (optional), amax per tensor.
+struct Prep3Args {
+    const void* x[3];
+    const float* awq[3];
+    void* out[3];
+    float* amax;      // [ntensors]
+};
+
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(kThreads) prep_x_kernel(Prep3Args a, int64_t K, int64_t ldx, int64_t ldo, int div_mode, int after_bf16) {
+    __shared__ float sh[kThreads / 32];
+    const int t = blockIdx.z;
+    const int64_t row = blockIdx.x;
+    const int64_t k0 = (int64_t)blockIdx.y * kSegElems;
+    const char* xrow = reinterpret_cast<const char*>(a.x[t]) + row * ldx * 2;
+    uint16_t* orow = a.out[t] ? reinterpret_cast<uint16_t*>(a.out[t]) + row * ldo : nullptr;
+    const float* awq = a.awq[t];
+    float m = 0.f;
+    if (VEC) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + ((int64_t)j * kThreads + threadIdx.x) * 8;
+            if (k < K) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xrow + k * 2);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float2 f = cvt2<DT>(w[q]);
+                    if (awq) {
+                        f.x = div_mode_f32(f.x, awq[k + 2 * q], div_mode);
+                        f.y = div_mode_f32(f.y, awq[k + 2 * q + 1], div_mode);
+                    }
+                    o[q] = pack_bf16x2(f.x, f.y);
+                    if (after_bf16) f = cvt2<RWKVQ_BF16>(o[q]);
+                    m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+                }
+                if (orow) *reinterpret_cast<uint4*>(orow + k) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+    } else {
+        const int64_t kend = (k0 + kSegElems < K) ? k0 + kSegElems : K;
+        for (int64_t k = k0 + threadIdx.x; k < kend; k += kThreads) {
+            float f = load1<DT>(xrow, k);
+            if (awq) f = div_mode_f32(f, awq[k], div_mode);
+            m = fmaxf(m, fabsf(after_bf16 ? bf16_round(f) : f));
+            if (orow) {
+                __nv_bfloat16 b = __float2bfloat16_rn(f);
+                orow[k] = *reinterpret_cast<uint16_t*>(&b);
+            }
+        }
+    }
+    m = block_max(m, sh);
+    if (threadIdx.x == 0) atomic_max_nonneg(a.amax + t, m);
+}
+
+static int32_t launch_prep(const Prep3Args& a, int nt, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int64_t ldo,
+                           int32_t div_mode, cudaStream_t st, int after_bf16 = 0) {
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "prep_x: x_dtype %d", x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "prep_x: div_mode %d", div_mode);
+    RWKVQ_REQUIRE(M >= 0 && K >= 0 && ldx >= K, RWKVQ_E_SHAPE, "prep_x: M=%lld K=%lld ldx=%lld", (long long)M, (long long)K, (long long)ldx);
+    RWKVQ_REQUIRE(a.amax != nullptr, RWKVQ_E_BADARG, "prep_x: amax is null");
+    if (cudaMemsetAsync(a.amax, 0, sizeof(float) * nt, st) != cudaSuccess) return check_launch("prep_x memset");
+    if (M == 0 || K == 0) return RWKVQ_OK;
+    bool vec = (K % 8 == 0) && (ldx % 8 == 0);
+    for (int t = 0; t < nt; ++t) {
+        RWKVQ_REQUIRE(a.x[t] != nullptr, RWKVQ_E_BADARG, "prep_x: x[%d] is null", t);
+        vec = vec && aligned16(a.x[t]) && (a.out[t] == nullptr || (aligned16(a.out[t]) && ldo % 8 == 0));
+        RWKVQ_REQUIRE(a.out[t] == nullptr || ldo >= K, RWKVQ_E_SHAPE, "prep_x: ldo=%lld < K", (long long)ldo);
+    }
+    const int64_t segs = (K + kSegElems - 1) / kSegElems;
+    RWKVQ_REQUIRE(segs <= 65535, RWKVQ_E_SHAPE, "prep_x: K=%lld too large", (long long)K);
+    dim3 grid((unsigned)M, (unsigned)segs, nt);
+#define RWKVQ_PREP(DT, V) prep_x_kernel<DT, V><<<grid, kThreads, 0, st>>>(a, K, ldx, ldo, div_mode, after_bf16)
+    if (x_dtype == RWKVQ_F16) { if (vec) RWKVQ_PREP(RWKVQ_F16, true); else RWKVQ_PREP(RWKVQ_F16, false); }
+    else                      { if (vec) RWKVQ_PREP(RWKVQ_BF16, true); else RWKVQ_PREP(RWKVQ_BF16, false); }
+#undef RWKVQ_PREP
+    return check_launch("prep_x");
+}
+
+// ----------------------------------------------------------------------------------------
+// prep_x_fp8, second pass: e4m3 codes from the per-call amax (IEEE divisions, as torch computes them).
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(kThreads) quant_fp8_kernel(const void* x, uint8_t* codes, float* scale, const float* amax_p,
+                                                             int64_t K, int64_t ldx, int64_t ldc, int div_mode, int from_bf16) {
+    const int64_t row = blockIdx.x;
+    const int64_t k0 = (int64_t)blockIdx.y * kSegElems;
+    const float amax = *amax_p;
+    const float inv = div_mode_f32(448.f, fmaxf(amax, 1e-12f), div_mode);
+    if (scale && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale = div_mode_f32(amax, 448.f, div_mode);
+    const char* xrow = reinterpret_cast<const char*>(x) + row * ldx * 2;
+    uint8_t* crow = codes + row * ldc;
+    if (VEC) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + ((int64_t)j * kThreads + threadIdx.x) * 8;
+            if (k < K) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xrow + k * 2);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                uint32_t c[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float2 f = cvt2<DT>(w[q]);
+                    if (from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                    c[q] = e4m3x2(clamp448(f.x * inv), clamp448(f.y * inv));
+                }
+                *reinterpret_cast<uint2*>(crow + k) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+            }
+        }
+    } else {
+        const int64_t kend = (k0 + kSegElems < K) ? k0 + kSegElems : K;
+        for (int64_t k = k0 + threadIdx.x; k < kend; k += kThreads) {
+            float f = load1<DT>(xrow, k);
+            if (from_bf16) f = bf16_round(f);
+            crow[k] = (uint8_t)(e4m3x2(clamp448(f * inv), 0.f) & 0xff);
+        }
+    }
+}
+
+// ----------------------------------------------------------------------------------------
+// prep_x_int8: one CTA per row; the row is read twice (second read hits L1/L2).
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(kThreads) quant_int8_kernel(const void* x, int8_t* codes, float* scales, int64_t K, int64_t ldx,
+                                                              int64_t ldc, int div_mode) {
+    __shared__ float sh[kThreads / 32];
+    const int64_t row = blockIdx.x;
+    const char* xrow = reinterpret_cast<const char*>(x) + row * ldx * 2;
+    int8_t* crow = codes + row * ldc;
+    float m = 0.f;
+    if (VEC) {
+        for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += kThreads * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xrow + k * 2);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
+        }
+    } else {
+        for (int64_t k = threadIdx.x; k < K; k += kThreads) m = fmaxf(m, fabsf(load1<DT>(xrow, k)));
+    }
+    m = fmaxf(block_max(m, sh), 1e-12f);
+    const float s = div_mode_f32(127.f, m, div_mode);
+    if (threadIdx.x == 0) scales[row] = div_mode_f32(m, 127.f, div_mode);
+    auto q8 = [s](float f) -> uint32_t {
+        return (uint32_t)(__float2int_rz(fminf(fmaxf(f * s, -128.f), 127.f))) & 0xffu;
+    };
+    if (VEC) {
+        for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += kThreads * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xrow + k * 2);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                c[q] = q8(f.x) | (q8(f.y) << 8);
+            }
+            *reinterpret_cast<uint2*>(crow + k) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+        }
+    } else {
+        for (int64_t k = threadIdx.x; k < K; k += kThreads) crow[k] = (int8_t)q8(load1<DT>(xrow, k));
+    }
+}
+
+__global__ void div_kernel(const float* a, const float* b, float* o, int64_t n, int mode) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) o[i] = div_mode_f32(a[i], b[i], mode);
+}
+
+}  // namespace rwkvq
+
+using namespace rwkvq;
+
+extern "C" {
+
+int32_t rwkvq_version(void) { return 100; }
+const char* rwkvq_last_error_string(void) { return g_err; }
+int64_t rwkvq_launch_count(void) { return g_launches.load(); }
+
+int32_t rwkvq_device_ok(void) {
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fail(RWKVQ_E_ARCH, "no CUDA device");
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (major != 10) return fail(RWKVQ_E_ARCH, "device compute capability major %d, need 10 (sm_100a)", major);
+    return RWKVQ_OK;
+}
+
+int32_t rwkvq_div_f32(const float* a, const float* b, float* out, int64_t n, int32_t div_mode, void* stream) {
+    RWKVQ_REQUIRE(a && b && out, RWKVQ_E_BADARG, "div_f32: null pointer");
+    if (n <= 0) return RWKVQ_OK;
+    div_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, b, out, n, div_mode);
+    return check_launch("div_f32");
+}
+
+int32_t rwkvq_prep_x(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, const float* awq, void* out_bf16,
+                     int64_t ldo, float* amax, int32_t div_mode, void* stream) {
+    Prep3Args a{};
+    a.x[0] = x; a.awq[0] = awq; a.out[0] = out_bf16; a.amax = amax;
+    return launch_prep(a, 1, x_dtype, M, K, ldx, ldo, div_mode, (cudaStream_t)stream);
+}
+
+int32_t rwkvq_prep3_x(const void* xr, const void* xk, const void* xv, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx,
+                      const float* awq_r, const float* awq_k, void* out_r, void* out_k, void* out_v, int64_t ldo,
+                      float* amax3, int32_t div_mode, void* stream) {
+    Prep3Args a{};
+    a.x[0] = xr; a.x[1] = xk; a.x[2] = xv;
+    a.awq[0] = awq_r; a.awq[1] = awq_k; a.awq[2] = nullptr;
+    a.out[0] = out_r; a.out[1] = out_k; a.out[2] = out_v;
+    a.amax = amax3;
+    return launch_prep(a, 3, x_dtype, M, K, ldx, ldo, div_mode, (cudaStream_t)stream);
+}
+
+int32_t rwkvq_actq_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                       float* amax, float* scale, int32_t div_mode, uint32_t flags, void* stream) {
+    RWKVQ_REQUIRE(codes && amax, RWKVQ_E_BADARG, "actq_fp8: null output");
+    RWKVQ_REQUIRE(ldc >= K, RWKVQ_E_SHAPE, "actq_fp8: ldc=%lld < K", (long long)ldc);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int after = (flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? 1 : 0, from_bf16 = (flags & RWKVQ_FLAG_QUANT_FROM_BF16) ? 1 : 0;
+    Prep3Args a{};
+    a.x[0] = x; a.amax = amax;
+    int32_t rc = launch_prep(a, 1, x_dtype, M, K, ldx, K, div_mode, st, after);
+    if (rc != RWKVQ_OK) return rc;
+    if (M == 0 || K == 0) {   // scale = 0/448
+        if (scale && cudaMemsetAsync(scale, 0, sizeof(float), st) != cudaSuccess) return check_launch("actq_fp8 memset");
+        return RWKVQ_OK;
+    }
+    const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && aligned16(x) && (ldc % 8 == 0) && ((uintptr_t)codes % 8 == 0);
+    dim3 grid((unsigned)M, (unsigned)((K + kSegElems - 1) / kSegElems));
+#define RWKVQ_Q(DT, V) quant_fp8_kernel<DT, V><<<grid, kThreads, 0, st>>>(x, codes, scale, amax, K, ldx, ldc, div_mode, from_bf16)
+    if (x_dtype == RWKVQ_F16) { if (vec) RWKVQ_Q(RWKVQ_F16, true); else RWKVQ_Q(RWKVQ_F16, false); }
+    else                      { if (vec) RWKVQ_Q(RWKVQ_BF16, true); else RWKVQ_Q(RWKVQ_BF16, false); }
+#undef RWKVQ_Q
+    return check_launch("actq_fp8");
+}
+
+int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                         float* scale, float* amax_scratch, void* stream) {
+    RWKVQ_REQUIRE(scale != nullptr, RWKVQ_E_BADARG, "prep_x_fp8: scale is null");
+    return rwkvq_actq_fp8(x, x_dtype, M, K, ldx, codes, ldc, amax_scratch, scale, RWKVQ_DIV_IEEE, 0u, stream);
+}
+
+int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes, int64_t ldc,
+                          float* scales, int32_t div_mode, void* stream) {
+    RWKVQ_REQUIRE(x && codes && scales, RWKVQ_E_BADARG, "prep_x_int8: null pointer");
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "prep_x_int8: x_dtype %d", x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "prep_x_int8: div_mode %d", div_mode);
+    RWKVQ_REQUIRE(M >= 0 && K >= 0 && ldx >= K && ldc >= K, RWKVQ_E_SHAPE, "prep_x_int8: M=%lld K=%lld", (long long)M, (long long)K);
+    if (M == 0) return RWKVQ_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && aligned16(x) && (ldc % 8 == 0) && ((uintptr_t)codes % 8 == 0);
+#define RWKVQ_Q(DT, V) quant_int8_kernel<DT, V><<<(unsigned)M, kThreads, 0, st>>>(x, codes, scales, K, ldx, ldc, div_mode)
+    if (x_dtype == RWKVQ_F16) { if (vec) RWKVQ_Q(RWKVQ_F16, true); else RWKVQ_Q(RWKVQ_F16, false); }
+    else                      { if (vec) RWKVQ_Q(RWKVQ_BF16, true); else RWKVQ_Q(RWKVQ_BF16, false); }
+#undef RWKVQ_Q
+    return check_launch("prep_x_int8");
+}
+
+}  // extern "C"

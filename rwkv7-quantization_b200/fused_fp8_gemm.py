@@ -1,0 +1,288 @@
+"""Drop-in for the reference module `fused_fp8_gemm.py`: same public names, argument meaning and return
+shapes, with every device kernel replaced by librwkvq.so (hand-written CUDA for sm_100a, see include/rwkvq.h).
+
+    prep_x / prep3_x / prep_x_fp8 / prep_x_int8 / prep3_x_int8     activation preparation
+    linear_fp8_m1_fused / linear_fp8_fused / linear_rkv_fused       FP8 W8A8 projections
+    linear_int8_fused / linear_rkv_int8_fused                       INT8 W8A8 projections
+    linear_quantized_fused                                          dispatcher used by the engine
+
+Outputs are freshly allocated tensors owned by the caller; weights are borrowed; launches go to torch's current
+CUDA stream without host synchronisation -- the conventions of the reference wrappers
+(fused_fp8_gemm.py:55-79, 645-679, 785-818, 944-1098).
+
+Routing by M = rows of the flattened activation:
+    M <= 32 (and the code tile fits shared memory)  one fused launch: activation quantization in the GEMV prologue
+    larger M                                        activation-quantization kernels + GEMM on the codes
+"""
+from __future__ import annotations
+
+import torch
+
+import rwkvq_abi as abi
+
+F8E4M3_MAX = 448.0
+FUSED_M_MAX = 512      # kept for importers (fused_fp8_gemm.py:1101); this build has no cuBLASLt route to switch to
+USE_CUDA_GRAPH = False  # kept for importers (fused_fp8_gemm.py:941); graphs are the caller's business here
+
+GEMV_M_MAX = 32
+_GEMV_SMEM_BUDGET = 200 * 1024 - 5 * 1024
+
+
+# --------------------------------------------------------------------------- helpers
+def _rows16(x: torch.Tensor) -> torch.Tensor:
+    """[..., K] -> contiguous [M, K] in fp16/bf16 (other dtypes become bf16), as the reference wrappers do."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.dtype not in (torch.float16, torch.bfloat16):
+        x2 = x2.to(torch.bfloat16)
+    if x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) != x2.shape[1]) or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+        if x2.data_ptr() % 16:
+            x2 = x2.clone()
+    return x2
+
+
+def _unpack(weight_info_or_w, res_scale=None):
+    if isinstance(weight_info_or_w, dict):
+        return weight_info_or_w["weight"], weight_info_or_w["tensor_scale"]
+    return weight_info_or_w, res_scale
+
+
+def _gemv_fits(m: int, k: int) -> bool:
+    pitch = (k + 127) // 128 * 128 + 64
+    return 0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0
+
+
+def _finish(out2d: torch.Tensor, lead, n: int, out_dtype):
+    out = out2d.reshape(*lead, n)
+    return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
+
+
+def _u8(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype in (torch.uint8, torch.int8) else t.view(torch.uint8)
+
+
+# --------------------------------------------------------------------------- activation preparation
+def prep_x(x, awq_scale=None, out=None):
+    """bf16(AWQ(x)) and the per-call amax as a GPU scalar, one launch (fused_fp8_gemm.py:55-79)."""
+    x2 = _rows16(x)
+    m, k = x2.shape
+    if out is None or out.shape != x2.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        out = torch.empty((m, k), dtype=torch.bfloat16, device=x2.device)
+    amax = torch.empty(1, dtype=torch.float32, device=x2.device)
+    awq = None if awq_scale is None else awq_scale.to(device=x2.device, dtype=torch.float32).contiguous()
+    abi.call("rwkvq_prep_x", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k, abi.ptr(awq),
+             out.data_ptr(), k, amax.data_ptr(), abi.DEFAULT_DIV, abi.stream_ptr())
+    return out, amax
+
+
+def prep3_x(xr, xk, xv, awq_r=None, awq_k=None):
+    """prep_x for the three attention inputs in one launch (fused_fp8_gemm.py:121-150)."""
+    xs = [_rows16(t) for t in (xr, xk, xv)]
+    if len({t.dtype for t in xs}) != 1:
+        xs = [t.to(torch.bfloat16) for t in xs]
+    xs = [t.contiguous() for t in xs]
+    m, k = xs[0].shape
+    outs = [torch.empty((m, k), dtype=torch.bfloat16, device=xs[0].device) for _ in range(3)]
+    amax = torch.empty(3, dtype=torch.float32, device=xs[0].device)
+    f32 = lambda a: None if a is None else a.to(device=xs[0].device, dtype=torch.float32).contiguous()
+    awq_r, awq_k = f32(awq_r), f32(awq_k)
+    abi.call("rwkvq_prep3_x", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]), m, k, k,
+             abi.ptr(awq_r), abi.ptr(awq_k), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), k,
+             amax.data_ptr(), abi.DEFAULT_DIV, abi.stream_ptr())
+    return outs[0], outs[1], outs[2], amax[0:1], amax[1:2], amax[2:3]
+
+
+def prep_x_fp8(x):
+    """e4m3 codes and the GPU-resident scale amax/448 for a scaled matmul (fused_fp8_gemm.py:363-390)."""
+    x2 = _rows16(x).contiguous()
+    m, k = x2.shape
+    codes = torch.empty((m, k), dtype=torch.float8_e4m3fn, device=x2.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x2.device)
+    amax = torch.empty(1, dtype=torch.float32, device=x2.device)
+    abi.call("rwkvq_prep_x_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k, scale.data_ptr(),
+             amax.data_ptr(), abi.stream_ptr())
+    return codes, scale
+
+
+def prep_x_int8(x):
+    """int8 codes with one scale per row (fused_fp8_gemm.py:712-731)."""
+    x2 = _rows16(x).contiguous()
+    m, k = x2.shape
+    codes = torch.empty((m, k), dtype=torch.int8, device=x2.device)
+    scale = torch.empty(m, dtype=torch.float32, device=x2.device)
+    abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k, scale.data_ptr(),
+             abi.DEFAULT_DIV, abi.stream_ptr())
+    return codes, scale
+
+
+def prep3_x_int8(xr, xk, xv):
+    """Three prep_x_int8 calls; returns (codes_r, codes_k, codes_v, scale_r, scale_k, scale_v) (fused_fp8_gemm.py:889-894)."""
+    (cr, sr), (ck, sk), (cv, sv) = prep_x_int8(xr), prep_x_int8(xk), prep_x_int8(xv)
+    return cr, ck, cv, sr, sk, sv
+
+
+# --------------------------------------------------------------------------- tile configuration (informational)
+def _cfg_for(M, N=None, K=None):
+    """(rows of activations, weight rows, K bytes per step, warps) of the kernel a shape is routed to."""
+    if K is not None and _gemv_fits(M, K):
+        return (16 if M <= 16 else 32, 8, 64, 8)
+    return (32, 8, 64, 8)
+
+
+def _cfg_for_rkv(M, N=None, K=None):
+    """The r/k/v launch uses the single-matrix tile; the three matrices share the CTA schedule, not a tile."""
+    return _cfg_for(M, N, K)
+
+
+def _best_method(M, N, K):
+    return "gemv_fused" if _gemv_fits(M, K) else "actq+gemm"
+
+
+# --------------------------------------------------------------------------- FP8
+def _fp8_gemv(x2, w, w_ts, awq, flags):
+    m, k = x2.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    abi.call("rwkvq_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
+             w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
+             abi.stream_ptr())
+    return out
+
+
+def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
+    """Activation quantization kernels, then the GEMM on codes (any M)."""
+    m, k = x2.shape
+    n = w.shape[0]
+    codes = torch.empty((m, k), dtype=torch.uint8, device=x2.device)
+    amax = torch.empty(1, dtype=torch.float32, device=x2.device)
+    out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    st = abi.stream_ptr()
+    abi.call("rwkvq_actq_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
+             codes.data_ptr(), k, amax.data_ptr(), None, abi.DEFAULT_DIV, act_flags, st)
+    abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
+             out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, st)
+    return out
+
+
+def linear_fp8_m1_fused(x, weight_info, out_dtype=torch.float16):
+    """M == 1 FP8 projection in a single launch (fused_fp8_gemm.py:645-679).  fp16 input is rounded to bf16
+    before the amax, as there (:662)."""
+    w, w_ts = _unpack(weight_info)
+    x2 = _rows16(x.reshape(1, -1))
+    out = _fp8_gemv(x2, _u8(w), w_ts, None, abi.FLAG_AMAX_AFTER_BF16)
+    return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
+
+
+def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float16):
+    """FP8 W8A8 projection with on-the-fly activation quantization (fused_fp8_gemm.py:1020-1077)."""
+    w, w_ts = _unpack(weight_info_or_w, res_scale)
+    k = x.shape[-1]
+    m = x.numel() // k if k else 0
+    if m == 1:
+        return linear_fp8_m1_fused(x, {"weight": w, "tensor_scale": w_ts}, out_dtype)
+    x2 = _rows16(x)
+    if _gemv_fits(m, k):
+        out = _fp8_gemv(x2, _u8(w), w_ts, None, 0)
+    else:
+        out = _fp8_codes_gemm(x2, _u8(w), w_ts, abi.FLAG_QUANT_FROM_BF16)
+    return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
+
+
+def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.float16):
+    """r, k, v projections (fused_fp8_gemm.py:944-1017): one launch for decode-sized M."""
+    lead = xr.shape[:-1]
+    xs = [_rows16(t) for t in (xr, xk, xv)]
+    if len({t.dtype for t in xs}) != 1:
+        xs = [t.to(torch.bfloat16) for t in xs]
+    m, k = xs[0].shape
+    ws = [_u8(i["weight"]) for i in (wr_info, wk_info, wv_info)]
+    n = ws[0].shape[0]
+    dev = xs[0].device
+    awq_r, awq_k = wr_info.get("awq_scale"), wk_info.get("awq_scale")
+    same_ld = len({w.stride(0) for w in ws}) == 1 and all(w.shape == ws[0].shape for w in ws)
+    if _gemv_fits(m, k) and same_ld:
+        xs = [t.contiguous() for t in xs]
+        outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
+        f32 = lambda a: None if a is None else a.to(device=dev, dtype=torch.float32).contiguous()
+        awq_r, awq_k = f32(awq_r), f32(awq_k)
+        abi.call("rwkvq_gemv_fp8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),
+                 abi.ptr(awq_r), abi.ptr(awq_k), ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0),
+                 wr_info["tensor_scale"].data_ptr(), wk_info["tensor_scale"].data_ptr(),
+                 wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
+                 m, n, k, k, abi.DEFAULT_DIV, 0, abi.stream_ptr())
+    else:
+        outs = []
+        for x2, w, info, awq in zip(xs, ws, (wr_info, wk_info, wv_info), (awq_r, awq_k, None)):
+            if awq is not None:                      # AWQ division, then the plain route on the bf16 copy
+                x2, _ = prep_x(x2, awq)
+            outs.append(_fp8_codes_gemm(x2, w, info["tensor_scale"], abi.FLAG_QUANT_FROM_BF16))
+    return tuple(_finish(o, lead, n, out_dtype) for o in outs)
+
+
+# --------------------------------------------------------------------------- INT8
+def _int8_any(x2, w, w_scale, acc_out=None):
+    m, k = x2.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    st = abi.stream_ptr()
+    if _gemv_fits(m, k):
+        abi.call("rwkvq_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
+                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0, st)
+    else:
+        codes = torch.empty((m, k), dtype=torch.int8, device=x2.device)
+        xs = torch.empty(m, dtype=torch.float32, device=x2.device)
+        abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
+                 codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
+        abi.call("rwkvq_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
+                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, st)
+    return out
+
+
+def linear_int8_fused(x, weight_info, out_dtype=torch.float16, acc_out=None):
+    """INT8 W8A8 projection, exact int32 accumulation (fused_fp8_gemm.py:785-818).  `acc_out` (optional int32
+    [M, N]) receives the raw accumulators."""
+    w, w_scale = weight_info["weight"], weight_info["tensor_scale"]
+    out = _int8_any(_rows16(x), w, w_scale, acc_out)
+    return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
+
+
+def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.float16, compat_shared_scale=True):
+    """r, k, v INT8 projections (fused_fp8_gemm.py:897-934).  The reference scales all three results by r's
+    weight scale (:855-857, :906); `compat_shared_scale=False` uses each matrix's own scale instead."""
+    lead = xr.shape[:-1]
+    xs = [_rows16(t) for t in (xr, xk, xv)]
+    if len({t.dtype for t in xs}) != 1:
+        xs = [t.to(torch.bfloat16) for t in xs]
+    m, k = xs[0].shape
+    infos = (wr_info, wk_info, wv_info)
+    ws = [i["weight"] for i in infos]
+    n = ws[0].shape[0]
+    scales = [wr_info["tensor_scale"]] * 3 if compat_shared_scale else [i["tensor_scale"] for i in infos]
+    same_ld = len({w.stride(0) for w in ws}) == 1 and all(w.shape == ws[0].shape for w in ws)
+    if _gemv_fits(m, k) and same_ld:
+        xs = [t.contiguous() for t in xs]
+        outs = [torch.empty((m, n), dtype=torch.float16, device=xs[0].device) for _ in range(3)]
+        abi.call("rwkvq_gemv_int8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),
+                 ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0), scales[0].data_ptr(),
+                 scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(),
+                 outs[2].data_ptr(), n, m, n, k, k, abi.DEFAULT_DIV, 0, abi.stream_ptr())
+    else:
+        outs = [_int8_any(x2, w, s) for x2, w, s in zip(xs, ws, scales)]
+    return tuple(_finish(o, lead, n, out_dtype) for o in outs)
+
+
+# --------------------------------------------------------------------------- dispatcher
+def linear_quantized_fused(x, weight_info, out_dtype=torch.float16):
+    """Engine-facing dispatcher (fused_fp8_gemm.py:1080-1098): qtype "int8" -> INT8 path; otherwise FP8, with the
+    fused semantics up to FUSED_M_MAX rows and the linear_fp8 semantics (bf16 first, result through bf16) above."""
+    qtype = weight_info.get("qtype", "fp8")
+    m = x.numel() // x.size(-1)
+    if qtype == "int8":
+        return linear_int8_fused(x, weight_info, out_dtype)
+    if qtype == "nvfp4":
+        from nvfp4_ops import linear_nvfp4
+        return linear_nvfp4(x, weight_info, out_dtype)
+    if m <= FUSED_M_MAX:
+        return linear_fp8_fused(x, weight_info, out_dtype=out_dtype)
+    from fp8_ops import linear_fp8
+    return linear_fp8(x, weight_info, out_dtype)

@@ -1,0 +1,126 @@
+"""ctypes binding of librwkvq.so (C ABI declared in include/rwkvq.h).
+
+There is no fallback: if the library is missing, was built for another architecture, or the device is not
+compute capability 10.x, the first call raises.  Tensors cross the boundary as raw device pointers
+(`tensor.data_ptr()`), sizes and leading dimensions; the stream is torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librwkvq.so")
+
+OK = 0
+F16, BF16 = 0, 1
+DIV_IEEE, DIV_FULL = 0, 1
+FLAG_AMAX_AFTER_BF16 = 1
+FLAG_INT8_SHARED_WSCALE = 2
+FLAG_OUT_VIA_BF16 = 4
+FLAG_QUANT_FROM_BF16 = 8
+
+# The reference's Triton kernels divide with div.full.f32 on a GPU; RWKVQ_DIV=ieee switches every wrapper
+# to IEEE division (what torch and the Triton CPU interpreter compute).
+DEFAULT_DIV = DIV_IEEE if os.environ.get("RWKVQ_DIV", "full").lower() == "ieee" else DIV_FULL
+
+_p, _i32, _i64, _u32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_uint32
+
+# name -> argtypes (restype is int32 unless listed in _RESTYPES)
+SIGNATURES = {
+    "rwkvq_version": [],
+    "rwkvq_last_error_string": [],
+    "rwkvq_device_ok": [],
+    "rwkvq_launch_count": [],
+    "rwkvq_div_f32": [_p, _p, _p, _i64, _i32, _p],
+    "rwkvq_prep_x": [_p, _i32, _i64, _i64, _i64, _p, _p, _i64, _p, _i32, _p],
+    "rwkvq_prep3_x": [_p, _p, _p, _i32, _i64, _i64, _i64, _p, _p, _p, _p, _p, _i64, _p, _i32, _p],
+    "rwkvq_prep_x_fp8": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _p],
+    "rwkvq_actq_fp8": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _i32, _u32, _p],
+    "rwkvq_prep_x_int8": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _i32, _p],
+    "rwkvq_gemv_fp8": [_p, _i32, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p],
+    "rwkvq_gemv_fp8_rkv": [_p, _p, _p, _i32, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
+                           _i64, _i32, _u32, _p],
+    "rwkvq_gemv_int8": [_p, _i32, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p],
+    "rwkvq_gemv_int8_rkv": [_p, _p, _p, _i32, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
+                            _i32, _u32, _p],
+    "rwkvq_gemm_fp8": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
+    "rwkvq_gemm_int8": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p],
+    "rwkvq_gemm_fp8_mma": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
+    "rwkvq_gemm_int8_mma": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p],
+}
+_RESTYPES = {"rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64}
+
+_lib = None
+_device_checked = False
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises if it has not been built (python build_ext.py)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python build_ext.py` (nvcc, sm_100a). "
+                               "There is no CPU or Triton fallback.")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(L, name)          # AttributeError here = header and library out of step
+            fn.argtypes = args
+            fn.restype = _RESTYPES.get(name, _i32)
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().rwkvq_last_error_string().decode("utf-8", "replace")
+
+
+def require_device() -> None:
+    global _device_checked
+    if _device_checked:
+        return
+    if not torch.cuda.is_available():
+        raise RuntimeError("rwkvq: no CUDA device; this library runs on sm_100a only and has no CPU path")
+    rc = lib().rwkvq_device_ok()
+    if rc != OK:
+        raise RuntimeError(f"rwkvq: {last_error()}")
+    _device_checked = True
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def call(name: str, *args) -> None:
+    """Invoke an entry point; a non-zero status becomes RuntimeError carrying the library's message."""
+    require_device()
+    rc = getattr(lib(), name)(*args)
+    if rc != OK:
+        raise RuntimeError(f"{name} failed with status {rc}: {last_error()}")
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return F16
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"rwkvq: activations must be float16 or bfloat16, got {t.dtype}")
+
+
+def launch_count() -> int:
+    return int(lib().rwkvq_launch_count())
+
+
+def div_on_device(a: torch.Tensor, b: torch.Tensor, mode: int = DIV_FULL) -> torch.Tensor:
+    """Element-wise a / b evaluated by the GPU with the chosen division mode (for checkers)."""
+    a32 = a.to(device="cuda", dtype=torch.float32).contiguous()
+    b32 = torch.broadcast_to(torch.as_tensor(b, dtype=torch.float32).to("cuda"), a32.shape).contiguous()
+    out = torch.empty_like(a32)
+    call("rwkvq_div_f32", a32.data_ptr(), b32.data_ptr(), out.data_ptr(), a32.numel(), mode, stream_ptr())
+    return out
