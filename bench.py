@@ -1,0 +1,321 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized projection path on B200.
+
+Workload (N = 1 and per rank for N > 1): one decode step (B = 1) through the quantized projections of all
+32 layers of RWKV-7 7.2B with FP8 W8A8 weights -- per layer the fused r/k/v launch (3 x [4096,4096]), the
+attention output [4096,4096], the FFN key [16384,4096] and the FFN value [4096,16384] -- 128 launches that
+stream 6.44 GB of distinct weights (>> the 126 MB L2, so every byte comes from HBM).  The metric is the HBM
+rate of that step: algorithmic bytes (weights + scales + activations in + fp16 results out) per second.
+Data is synthetic: seeded N(0,1/K) weights quantized like schemes._q_fp8, N(0,1) bf16 activations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--extra]
+
+For N > 1 launch with torch.distributed.run; ranks hold replicas and independent token streams (sequence
+sharding, no collective on the data path).  `--impl reference` times the reference's CPU route (dequantize with
+the stored scale, then a torch CPU matmul) on the host cores on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "rwkv7-quantization_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+C, F, LAYERS = 4096, 16384, 32
+METRIC = "B=1 quantized GEMV HBM GB/s + prefill GEMM TFLOPS, RWKV-7 7.2B shapes, 1-8 GPU"
+WORKLOAD = "rwkv7-7.2B fp8 w8a8 decode B=1: 32 layers x (rkv-fused 3x[4096,4096] + att_out [4096,4096] + ffn_key [16384,4096] + ffn_value [4096,16384])"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def gemv_bytes(m, n, k, in_bytes=2):
+    """Algorithmic bytes of one W8A8 projection: weights + scale + activations in + fp16 out."""
+    return n * k + 4 + m * k * in_bytes + m * n * 2
+
+
+def step_bytes(m=1):
+    per_layer = 3 * gemv_bytes(m, C, C) + gemv_bytes(m, C, C) + gemv_bytes(m, F, C) + gemv_bytes(m, C, F)
+    return per_layer * LAYERS
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------ model data
+def make_fp8_weight(n, k, gen, dev):
+    """N(0,1/K) weights quantized per tensor to e4m3 the way schemes._q_fp8 does, on the device."""
+    w = torch.randn((n, k), generator=gen, device=dev, dtype=torch.float32) * (1.0 / k) ** 0.5
+    amax = w.abs().max().clamp(min=1e-12)
+    scale = (amax / 448.0).float()
+    q = (w / scale).clamp(-448.0, 448.0).round().to(torch.float8_e4m3fn)
+    return {"weight": q, "tensor_scale": scale, "qtype": "fp8"}
+
+
+def make_model(dev, seed):
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    layers = []
+    for _ in range(LAYERS):
+        layers.append({
+            "r": make_fp8_weight(C, C, gen, dev), "k": make_fp8_weight(C, C, gen, dev), "v": make_fp8_weight(C, C, gen, dev),
+            "o": make_fp8_weight(C, C, gen, dev), "ffn_k": make_fp8_weight(F, C, gen, dev),
+            "ffn_v": make_fp8_weight(C, F, gen, dev),
+        })
+    return layers
+
+
+def make_inputs(dev, seed, m=1, pinned_host=False):
+    """Six activation tensors of one decode step: xr, xk, xv, the WKV result, the FFN input, the FFN hidden."""
+    gen = torch.Generator().manual_seed(seed)
+    host = {name: torch.randn((m, k), generator=gen).to(torch.bfloat16)
+            for name, k in (("xr", C), ("xk", C), ("xv", C), ("xo", C), ("xf", C), ("xg", F))}
+    if pinned_host:
+        host = {k: v.pin_memory() for k, v in host.items()}
+    return host, {k: v.to(dev) for k, v in host.items()}
+
+
+def decode_step(layers, x):
+    """One token through the six quantized projections of every layer, by the public drop-in calls."""
+    import fused_fp8_gemm as f
+    y = None
+    for L in layers:
+        f.linear_rkv_fused(x["xr"], x["xk"], x["xv"], L["r"], L["k"], L["v"])
+        f.linear_quantized_fused(x["xo"], L["o"])
+        f.linear_quantized_fused(x["xf"], L["ffn_k"])
+        y = f.linear_quantized_fused(x["xg"], L["ffn_v"])
+    return y
+
+
+LAUNCHES_PER_STEP = 4 * LAYERS
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+_CPU_LAYER = []   # one layer of (weight-info, activation) pairs, built once
+
+def cpu_reference_sample(threads, repeats=3):
+    """The reference's CPU route on ONE layer of the workload (1/32 of a step): weights quantized like
+    schemes._q_fp8, then per projection w.float()*scale and a torch CPU matmul.  Returns (GB/s, seconds/sample)."""
+    from oracle import rwkvq_oracle as O
+    torch.set_num_threads(threads)
+    if not _CPU_LAYER:
+        gen = torch.Generator().manual_seed(1)
+        for n, k in [(C, C)] * 4 + [(F, C), (C, F)]:
+            q, s = O.q_fp8(torch.randn((n, k), generator=gen) * (1.0 / k) ** 0.5)
+            _CPU_LAYER.append(({"weight": q, "tensor_scale": s}, torch.randn((1, k), generator=gen).to(torch.bfloat16)))
+    infos, xs = [p[0] for p in _CPU_LAYER], [p[1] for p in _CPU_LAYER]
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for info, x in zip(infos, xs):
+            O.cpu_dequant_matmul_fp8(x, info)
+        best = min(best, time.perf_counter() - t0)
+    layer_bytes = step_bytes(1) / LAYERS
+    return layer_bytes / best / 1e9, best
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    cpu_reference_sample(threads, repeats=max(1, args.warmup))
+    t = []
+    for _ in range(args.steps):
+        gbs, sec = cpu_reference_sample(threads, repeats=1)
+        t.append(sec)
+    sec = sum(t) / len(t)
+    gbs = step_bytes(1) / LAYERS / sec / 1e9
+    sample = "one of the 32 layers (6 projections, 201 MB of e4m3 weights) per step; GB/s needs no scaling"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3 * LAYERS, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "timed": "CPU; ms_per_step is the one-layer sample x 32"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def timed(fn, steps, dist_on):
+    """Time `steps` calls of fn with CUDA events on the current stream; barrier + synchronize on both sides."""
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    if dist_on:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist_on:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = t.item()
+    return ms
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    import rwkvq_abi as abi
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    abi.require_device()
+    dist_on = world > 1
+    if dist_on:
+        dist.init_process_group("nccl", device_id=dev)
+
+    layers = make_model(dev, seed=100 + rank)
+    host, x = make_inputs(dev, seed=7 + rank, pinned_host=True)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            y = decode_step(layers, x)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            y = decode_step(layers, x)
+        y_host = torch.empty(y.shape, dtype=y.dtype).pin_memory()
+
+        def step_resident():
+            graph.replay()
+
+        def step_e2e():
+            for k in x:
+                x[k].copy_(host[k], non_blocking=True)
+            graph.replay()
+            y_host.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        def step_eager():
+            for k in x:
+                x[k].copy_(host[k], non_blocking=True)
+            out = decode_step(layers, x)
+            y_host.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(max(3, args.warmup)):
+            step_resident()
+        l0 = abi.launch_count()
+        with ClockSampler(local_rank) as clocks:
+            ms = timed(step_resident, args.steps, dist_on)
+        for _ in range(3):
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps, dist_on)
+        for _ in range(3):
+            step_eager()
+        ms_eager = timed(step_eager, max(1, args.steps // 4), dist_on) / max(1, args.steps // 4) * args.steps
+        eager_launches = abi.launch_count() - l0
+
+    nbytes = step_bytes(1)
+    per_step = ms / args.steps
+    gbs = nbytes * world / (per_step * 1e-3) / 1e9
+    gbs_e2e = nbytes * world / (ms_e2e / args.steps * 1e-3) / 1e9
+    gbs_eager = nbytes * world / (ms_eager / args.steps * 1e-3) / 1e9
+    pk = peaks()
+    per_gpu = gbs / world
+    line = {
+        "metric": METRIC, "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": round(per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens_per_step_per_gpu": 1, "parallelism": f"sequence-sharded x{world}",
+                   "l2": "6.44 GB of distinct weights per step (inputs larger than L2)",
+                   "launch": "CUDA graph of the 128 public-API calls"},
+        "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(per_gpu / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                     "kernel": "gemv_w8a8_kernel<fp8>", "bytes_per_launch": nbytes // LAUNCHES_PER_STEP,
+                     "us_per_launch": round(per_step * 1e3 / LAUNCHES_PER_STEP, 3)},
+        "e2e": {"value": round(gbs_e2e, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()),
+                "d2h_bytes_per_step": y_host.numel() * y_host.element_size(),
+                "mode": "pinned host -> device copies, graph replay of the public API calls, device -> host result",
+                "eager_python_calls_gbs": round(gbs_eager, 2)},
+        "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+        "launches_counted_eager": int(eager_launches),
+        "clocks": clocks.summary(),
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu:
+            threads = os.cpu_count() or 1
+            gbs_cpu, sec = cpu_reference_sample(threads, repeats=3)
+            line["cpu_baseline"] = {"value": round(gbs_cpu, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": "one of the 32 layers (6 projections, 201 MB of e4m3 weights), best of 3"}
+        print(json.dumps(line))
+    if dist_on:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
