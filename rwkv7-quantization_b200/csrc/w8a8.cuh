@@ -1,0 +1,202 @@
+// Shared pieces of the W8A8 (FP8 e4m3 / INT8) kernels: argument block, mma.sync wrappers and the activation
+// quantization prologues that fill the shared-memory code tile.
+#pragma once
+#include "common.cuh"
+
+namespace rwkvq {
+
+constexpr int kWarps = 8;
+constexpr int kThr = kWarps * 32;
+constexpr int kUnroll = 4;   // any-M kernel: 64-byte units in flight per lane
+
+enum { QT_FP8 = 0, QT_INT8 = 1 };
+
+// Programmatic dependent launch: a kernel may start while its predecessor in the stream drains.  Everything
+// before griddep_wait() may only touch data no earlier kernel writes (here: the weights).
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+struct W8Args {
+    const void* x[3];         // fused: activations (x_dtype)
+    const float* awq[3];      // fused FP8: optional per-channel divisor
+    const uint8_t* w[3];
+    const float* ws[3];       // weight scale (one fp32 each)
+    __half* out[3];
+    int32_t* acc[3];          // INT8: optional raw accumulators
+    const uint8_t* a_codes;   // pre-quantized mode
+    const float* a_scale;     // pre-quantized: FP8 amax-or-scale [1], INT8 per-row scales [M]
+    int64_t ldx, ldw, ldo, ldacc, lda;
+    int M, N, K, nmat;
+    int div_mode, amax_is_amax;
+    uint32_t flags;
+    int pitch;                // fused: bytes between rows of the code tile in shared memory
+};
+
+template <int QT>
+struct Acc { using T = float; };
+template <>
+struct Acc<QT_INT8> { using T = int32_t; };
+
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_s8(int32_t (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <int QT, typename T>
+__device__ __forceinline__ void mma8(T (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    if constexpr (QT == QT_FP8) mma_e4m3(c, a0, a1, a2, a3, b0, b1);
+    else mma_s8(c, a0, a1, a2, a3, b0, b1);
+}
+
+__device__ __forceinline__ float cta_max(float v, float* sh) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = sh[0];
+#pragma unroll
+    for (int i = 1; i < kWarps; ++i) r = fmaxf(r, sh[i]);
+    __syncthreads();
+    return r;
+}
+
+// ---- fused prologue, FP8: per-call amax then e4m3 codes into shared memory; returns max(amax, 1e-12).
+// Up to 4 vectors of 8 activations per thread stay in registers between the two phases (M*K <= 8192, i.e. the
+// M = 1 and M = 2 decode cases at K = 4096); larger calls read x a second time (L1/L2 hits).
+template <int DT>
+__device__ __forceinline__ void fp8_vec_amax(const uint4& v, const float* awq, int k, int div_mode, bool after, float& m) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float2 f = cvt2<DT>(w[q]);
+        if (awq) {
+            f.x = div_mode_f32(f.x, awq[k + 2 * q], div_mode);
+            f.y = div_mode_f32(f.y, awq[k + 2 * q + 1], div_mode);
+        }
+        if (after) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+        m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+}
+template <int DT>
+__device__ __forceinline__ uint2 fp8_vec_codes(const uint4& v, const float* awq, int k, int div_mode, float inv) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t c[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float2 f = cvt2<DT>(w[q]);
+        if (awq) {
+            f.x = div_mode_f32(f.x, awq[k + 2 * q], div_mode);
+            f.y = div_mode_f32(f.y, awq[k + 2 * q + 1], div_mode);
+        }
+        c[q] = e4m3x2(clamp448(bf16_round(f.x) * inv), clamp448(bf16_round(f.y) * inv));
+    }
+    return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+}
+
+template <int DT>
+__device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh) {
+    const char* x = reinterpret_cast<const char*>(a.x[mat]);
+    const float* awq = a.awq[mat];
+    const int kv = a.K >> 3;                  // 8-element vectors per row
+    const int nvec = a.M * kv;
+    const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
+    float m = 0.f;
+    if (nvec <= 4 * kThr) {
+        uint4 v[4];
+        int rr[4], kk[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * kThr;
+            rr[j] = -1;
+            if (i < nvec) {
+                rr[j] = i / kv;
+                kk[j] = (i - rr[j] * kv) << 3;
+                v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)rr[j] * a.ldx + kk[j]) * 2);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (rr[j] >= 0) fp8_vec_amax<DT>(v[j], awq, kk[j], a.div_mode, after, m);
+        const float amax = fmaxf(cta_max(m, sh), 1e-12f);
+        const float inv = div_mode_f32(448.f, amax, a.div_mode);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (rr[j] >= 0)
+                *reinterpret_cast<uint2*>(xq + (size_t)rr[j] * a.pitch + kk[j]) = fp8_vec_codes<DT>(v[j], awq, kk[j], a.div_mode, inv);
+        return amax;
+    }
+    for (int i = threadIdx.x; i < nvec; i += kThr) {
+        const int r = i / kv, k = (i - r * kv) << 3;
+        const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
+        fp8_vec_amax<DT>(v, awq, k, a.div_mode, after, m);
+    }
+    const float amax = fmaxf(cta_max(m, sh), 1e-12f);
+    const float inv = div_mode_f32(448.f, amax, a.div_mode);
+    for (int i = threadIdx.x; i < nvec; i += kThr) {
+        const int r = i / kv, k = (i - r * kv) << 3;
+        const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
+        *reinterpret_cast<uint2*>(xq + (size_t)r * a.pitch + k) = fp8_vec_codes<DT>(v, awq, k, a.div_mode, inv);
+    }
+    return amax;
+}
+
+// ---- fused prologue, INT8: per-row amax / codes; row scales amax/127 into xs[].
+// Few rows (M <= 4): the whole CTA works on one row at a time; more rows: one warp per row.
+template <int DT>
+__device__ __forceinline__ float int8_vec_amax(const uint4& v, float m) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 f = cvt2<DT>(w[q]);
+        m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+    return m;
+}
+template <int DT>
+__device__ __forceinline__ uint2 int8_vec_codes(const uint4& v, float s) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t c[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 f = cvt2<DT>(w[q]);
+        const uint32_t lo = (uint32_t)__float2int_rz(fminf(fmaxf(f.x * s, -128.f), 127.f)) & 0xffu;
+        const uint32_t hi = (uint32_t)__float2int_rz(fminf(fmaxf(f.y * s, -128.f), 127.f)) & 0xffu;
+        c[q] = lo | (hi << 8);
+    }
+    return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+}
+
+template <int DT>
+__device__ void quantize_int8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* xs, float* sh) {
+    const char* x = reinterpret_cast<const char*>(a.x[mat]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (a.M <= 4) {
+        for (int r = 0; r < a.M; ++r) {
+            const char* xr = x + (int64_t)r * a.ldx * 2;
+            float m = 0.f;
+            for (int k = threadIdx.x * 8; k < a.K; k += kThr * 8) m = int8_vec_amax<DT>(*reinterpret_cast<const uint4*>(xr + k * 2), m);
+            m = fmaxf(cta_max(m, sh), 1e-12f);
+            const float s = div_mode_f32(127.f, m, a.div_mode);
+            if (threadIdx.x == 0) xs[r] = div_mode_f32(m, 127.f, a.div_mode);
+            for (int k = threadIdx.x * 8; k < a.K; k += kThr * 8)
+                *reinterpret_cast<uint2*>(xq + (size_t)r * a.pitch + k) = int8_vec_codes<DT>(*reinterpret_cast<const uint4*>(xr + k * 2), s);
+        }
+        return;
+    }
+    for (int r = warp; r < a.M; r += kWarps) {
+        const char* xr = x + (int64_t)r * a.ldx * 2;
+        float m = 0.f;
+        for (int k = lane * 8; k < a.K; k += 256) m = int8_vec_amax<DT>(*reinterpret_cast<const uint4*>(xr + k * 2), m);
+        m = fmaxf(warp_max(m), 1e-12f);
+        const float s = div_mode_f32(127.f, m, a.div_mode);
+        if (lane == 0) xs[r] = div_mode_f32(m, 127.f, a.div_mode);
+        for (int k = lane * 8; k < a.K; k += 256)
+            *reinterpret_cast<uint2*>(xq + (size_t)r * a.pitch + k) = int8_vec_codes<DT>(*reinterpret_cast<const uint4*>(xr + k * 2), s);
+    }
+}
+
+}  // namespace rwkvq
