@@ -145,6 +145,53 @@ int32_t rwkvq_gemm_int8_mma(const int8_t* a_codes, int64_t lda, const float* a_s
                             const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc,
                             int64_t M, int64_t N, int64_t K, uint32_t flags, void* stream);
 
+/* ---------------------------------------------------------------- tensor-memory kernels (tcgen05 + TMA)
+ *
+ * The same projections on the 5th-generation tensor cores.  `workspace` is caller-owned device scratch:
+ * rwkvq_workspace_bytes() bytes (16-byte aligned), ZEROED ONCE before its first use; every launch leaves its
+ * counters zero again, so one workspace serves any number of launches that are ordered on one stream.  Launches
+ * that may overlap on the device (different streams) need separate workspaces.  The workspace also holds a status
+ * word that a kernel sets to RWKVQ_E_TIMEOUT if one of its bounded waits gave up; rwkvq_workspace_status() reads
+ * it (this one call synchronizes the device). */
+int64_t rwkvq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t nmat);
+int32_t rwkvq_workspace_status(const void* workspace, int32_t* host_status);
+
+/* linear_fp8_m1_fused / linear_fp8_fused (fused_fp8_gemm.py:600-679, 1020-1077) for M <= 16: one launch, activation
+ * quantization by dedicated warps of the kernel, weights streamed by TMA into tcgen05.mma. */
+int32_t rwkvq_tc_gemv_fp8(const void* x, int32_t x_dtype, const float* awq, const uint8_t* w, int64_t ldw,
+                          const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                          int64_t ldx, int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes,
+                          void* stream);
+/* linear_rkv_fused (fused_fp8_gemm.py:944-1017) for M <= 16. */
+int32_t rwkvq_tc_gemv_fp8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const float* awq_r,
+                              const float* awq_k, const uint8_t* wr, const uint8_t* wk, const uint8_t* wv, int64_t ldw,
+                              const float* sr, const float* sk, const float* sv, void* out_r, void* out_k, void* out_v,
+                              int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                              uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream);
+/* linear_int8_fused (fused_fp8_gemm.py:785-818) for M <= 16. */
+int32_t rwkvq_tc_gemv_int8(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale,
+                           void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M, int64_t N, int64_t K,
+                           int64_t ldx, int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes,
+                           void* stream);
+/* linear_rkv_int8_fused (fused_fp8_gemm.py:897-934) for M <= 16. */
+int32_t rwkvq_tc_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const int8_t* wr,
+                               const int8_t* wk, const int8_t* wv, int64_t ldw, const float* sr, const float* sk,
+                               const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M,
+                               int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags, void* workspace,
+                               int64_t workspace_bytes, void* stream);
+/* GEMM on pre-quantized codes, any M (fused_fp8_hwdot_gemm_kernel fused_fp8_gemm.py:219-257, torch._scaled_mm
+ * fp8_ops.py:77-80): M <= 128 streams the weights once (needs the workspace); larger M runs the 128 x 256 tile
+ * prefill kernel (workspace optional, used for the status word only). */
+int32_t rwkvq_tc_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
+                          const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M,
+                          int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* workspace,
+                          int64_t workspace_bytes, void* stream);
+/* fused_int8_gemm_kernel (fused_fp8_gemm.py:734-782) on codes, any M. */
+int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                           const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc,
+                           int64_t M, int64_t N, int64_t K, uint32_t flags, void* workspace, int64_t workspace_bytes,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,739 @@
+// W8A8 projections on the 5th-generation tensor cores: TMA -> shared memory -> tcgen05.mma -> tensor memory.
+//
+// One persistent, warp-specialised kernel (one CTA per SM) serves both regimes:
+//
+//   SWAP (decode, M <= 128 tokens, HBM-bound): the WEIGHTS are the 128-row "A" operand of the MMA, the
+//     quantized activations the narrow "B" operand (N = 16..128 tokens), so D^T[weight row, token] accumulates in
+//     128 TMEM lanes x N columns.  Weight tiles [128 rows x 128 B] stream through a deep TMA ring straight into
+//     the tensor core: no register staging, no LDS.  The (matrix, row tile, 128-byte K chunk) space is cut into
+//     one contiguous range per CTA (stream-K), so every SM streams the same number of bytes; a row tile that is
+//     shared by several CTAs is finished by the last one to arrive, which adds the partial sums in CTA order
+//     (fixed order: results are run-to-run identical).
+//     FUSED variant: four extra warps derive the amax / row scales and write the e4m3 / int8 codes of every
+//     K chunk directly into the swizzled B tile of its ring stage (activation quantization in the prologue of
+//     the GEMV, one launch per projection).
+//
+//   GEMM (prefill, compute-bound): tokens are the 128-row A operand, a block of NB = 256 weight rows the B
+//     operand; both come by TMA; 128 x 256 fp32 (or int32) accumulators, double-buffered in tensor memory so the
+//     epilogue of one tile overlaps the MMAs of the next.
+//
+// Roles: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and owner of the TMEM allocation,
+// warps 2-5 = epilogue (one TMEM lane quarter each), warps 6-9 = activation quantizer (SWAP+FUSED only).
+// Every mbarrier wait is bounded; a timeout is reported through the status word and the CTA drains and exits.
+#include <algorithm>
+#include <cstdlib>
+#include <mutex>
+
+#include "tc_common.cuh"
+#include "w8a8.cuh"
+
+namespace rwkvq {
+using namespace tc;
+
+constexpr int kTcThreads = 320;
+constexpr int kMaxStages = 12;
+constexpr int kChunk = 128;          // bytes of K per ring stage (one swizzle row)
+constexpr int kTileP = 128;          // rows of the A operand (UMMA M)
+constexpr uint32_t kABytes = kTileP * kChunk;
+
+struct TcMaps {
+    CUtensorMap w[3];   // weights  [N, K] uint8
+    CUtensorMap a[3];   // activation codes [M, K] uint8 (unused in the FUSED variant)
+};
+
+struct TcArgs {
+    const void* x[3];          // FUSED: activations (x_dtype), rows ldx apart
+    const float* awq[3];       // FUSED FP8: optional per-channel divisor
+    const float* a_scale[3];   // codes route: FP8 amax-or-scale [1]; INT8 row scales [M]
+    const float* ws[3];        // weight scale (one fp32 per matrix)
+    __half* out[3];
+    int32_t* acc[3];           // INT8: optional raw accumulators
+    float* scratch;            // SWAP: partial sums [row tile][slot][M][128] (fp32 or int32 bits)
+    int* counters;             // SWAP: arrivals per row tile, zero before the first use, left zero by every launch
+    int* status;               // set to RWKVQ_E_TIMEOUT if a bounded wait gave up
+    int64_t ldx, ldo, ldacc;
+    int M, N, K, nmat;
+    int NB;                    // rows of the B operand (UMMA N)
+    int kchunks, ptiles, qtiles, max_slots, stages, acc_stride;
+    int x_dtype, div_mode, amax_is_amax;
+    uint32_t flags;
+};
+
+struct Part {
+    int mat, prow, qrow, kc0, kc1, tile, slot, nslots;
+};
+
+// Enumerates the parts of this CTA: SWAP = contiguous range of (tile, chunk) units; GEMM = whole tiles, strided.
+template <bool SWAP>
+struct PartIter {
+    const TcArgs& a;
+    int64_t pos, end, total;
+    __device__ explicit PartIter(const TcArgs& args) : a(args) {
+        if constexpr (SWAP) {
+            total = (int64_t)a.nmat * a.ptiles * a.kchunks;
+            pos = begin_of(blockIdx.x);
+            end = begin_of(blockIdx.x + 1);
+        } else {
+            total = (int64_t)a.nmat * a.ptiles * a.qtiles;
+            pos = blockIdx.x;
+            end = total;
+        }
+    }
+    __device__ int64_t begin_of(int64_t c) const { return total * c / gridDim.x; }
+    __device__ int owner(int64_t u) const {     // CTA whose range holds unit u
+        int64_t c = u * gridDim.x / total;
+        while (begin_of(c + 1) <= u) ++c;
+        while (c > 0 && begin_of(c) > u) --c;
+        return (int)c;
+    }
+    __device__ bool next(Part& p) {
+        if (pos >= end) return false;
+        if constexpr (SWAP) {
+            const int64_t tile = pos / a.kchunks;
+            p.tile = (int)tile;
+            p.kc0 = (int)(pos - tile * a.kchunks);
+            p.kc1 = (int)min((int64_t)a.kchunks, p.kc0 + (end - pos));
+            p.mat = (int)(tile / a.ptiles);
+            p.prow = (int)(tile - (int64_t)p.mat * a.ptiles) * kTileP;
+            p.qrow = 0;
+            if (p.kc0 == 0 && p.kc1 == a.kchunks) {
+                p.slot = 0;
+                p.nslots = 1;
+            } else {
+                const int first = owner(tile * a.kchunks), last = owner((tile + 1) * a.kchunks - 1);
+                p.slot = (int)blockIdx.x - first;
+                p.nslots = last - first + 1;
+            }
+            pos += p.kc1 - p.kc0;
+        } else {
+            const int per_mat = a.ptiles * a.qtiles;
+            p.tile = (int)pos;
+            p.mat = (int)(pos / per_mat);
+            const int r = (int)(pos - (int64_t)p.mat * per_mat);
+            p.prow = (r / a.qtiles) * kTileP;
+            p.qrow = (r % a.qtiles) * a.NB;
+            p.kc0 = 0;
+            p.kc1 = a.kchunks;
+            p.slot = 0;
+            p.nslots = 1;
+            pos += gridDim.x;
+        }
+        return true;
+    }
+};
+
+struct TcShared {
+    uint64_t full[kMaxStages], empty[kMaxStages], tfull[2], tempty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int last_flag;
+    float amax[3];             // FUSED FP8: max(amax, 1e-12) per matrix
+    float xs[3][16];           // FUSED INT8: row scales per matrix
+    float red[4];
+};
+
+__device__ __forceinline__ void tc_abort(TcShared& s, const TcArgs& a) {
+    s.abort_flag = 1;
+    if (a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
+}
+
+// ---- FUSED quantizer helpers (128 threads = warps 6..9); qt = thread index within the group
+__device__ __forceinline__ float group_max(float v, float* red, int qt) {   // max over the 128 quantizer threads
+    v = warp_max(v);
+    named_bar_sync(2, 128);
+    if ((qt & 31) == 0) red[qt >> 5] = v;
+    named_bar_sync(2, 128);
+    return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+}
+
+template <int KIND, int DT>
+__device__ void quantizer_scales(const TcArgs& a, TcShared& s, int qt) {
+    for (int mat = 0; mat < a.nmat; ++mat) {
+        const char* x = reinterpret_cast<const char*>(a.x[mat]);
+        const float* awq = KIND == KIND_F8 ? a.awq[mat] : nullptr;
+        if constexpr (KIND == KIND_F8) {
+            const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
+            float m = 0.f;
+            const int kv = a.K >> 3, nvec = a.M * kv;
+            for (int i = qt; i < nvec; i += 128) {
+                const int r = i / kv, k = (i - r * kv) << 3;
+                const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
+                fp8_vec_amax<DT>(v, awq, k, a.div_mode, after, m);
+            }
+            m = group_max(m, s.red, qt);
+            if (qt == 0) s.amax[mat] = fmaxf(m, 1e-12f);
+        } else {
+            for (int r = 0; r < a.M; ++r) {
+                float m = 0.f;
+                for (int k = qt * 8; k < a.K; k += 128 * 8)
+                    m = int8_vec_amax<DT>(*reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2), m);
+                m = fmaxf(group_max(m, s.red, qt), 1e-12f);
+                if (qt == 0) s.xs[mat][r] = m;      // the row amax; scale amax/127 is formed where it is used
+            }
+        }
+    }
+    named_bar_sync(2, 128);
+}
+
+// Quantizes all of x (every matrix) into the compact code cache [mat][row][Kpad] in shared memory.
+template <int KIND, int DT>
+__device__ void quantize_all(const TcArgs& a, const TcShared& s, uint8_t* cache, int kpad, int qt) {
+    const int kv = a.K >> 3;
+    for (int mat = 0; mat < a.nmat; ++mat) {
+        const char* x = reinterpret_cast<const char*>(a.x[mat]);
+        for (int i = qt; i < a.M * kv; i += 128) {
+            const int r = i / kv, k = (i - r * kv) << 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
+            uint2 c;
+            if constexpr (KIND == KIND_F8) {
+                c = fp8_vec_codes<DT>(v, a.awq[mat], k, a.div_mode, div_mode_f32(448.f, s.amax[mat], a.div_mode));
+            } else {
+                c = int8_vec_codes<DT>(v, div_mode_f32(127.f, s.xs[mat][r], a.div_mode));
+            }
+            *reinterpret_cast<uint2*>(cache + ((size_t)mat * a.M + r) * kpad + k) = c;
+        }
+    }
+}
+
+// Copies the codes of K chunk kc from the cache into a swizzled B tile; one warp: lane -> (row = lane/8 + 4*pass,
+// 16-byte chunk = lane%8).  Rows >= M of the tile stay zero.
+__device__ __forceinline__ void copy_chunk(const TcArgs& a, const uint8_t* cache, int kpad, int mat, int kc, uint8_t* btile, int lane) {
+    const int c = lane & 7;
+    for (int r = lane >> 3; r < a.M; r += 4) {
+        const uint4 v = *reinterpret_cast<const uint4*>(cache + ((size_t)mat * a.M + r) * kpad + kc * kChunk + c * 16);
+        *reinterpret_cast<uint4*>(btile + (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4)) = v;
+    }
+}
+
+template <int KIND, bool SWAP, bool FUSED, int DT>
+__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcArgs a) {
+    using T = typename Acc<KIND == KIND_F8 ? QT_FP8 : QT_INT8>::T;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ TcShared s;
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t stage_bytes = kABytes + (uint32_t)a.NB * kChunk;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = a.acc_stride * 2 <= 32 ? 32u : (a.acc_stride * 2 <= 64 ? 64u : (a.acc_stride * 2 <= 128 ? 128u : (a.acc_stride * 2 <= 256 ? 256u : 512u)));
+
+    griddep_launch_dependents();
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < a.stages; ++i) {
+            mbar_init(&s.full[i], FUSED ? 2 : 1);
+            mbar_init(&s.empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s.tfull[i], 1);
+            mbar_init(&s.tempty[i], 4);
+        }
+        s.abort_flag = 0;
+        s.last_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        for (int i = 0; i < a.nmat; ++i) {
+            prefetch_tmap(&maps.w[i]);
+            if (!FUSED) prefetch_tmap(&maps.a[i]);
+        }
+    }
+    if (warp == 1) tmem_alloc(&s.tmem_base, tmem_cols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = s.tmem_base;
+    const volatile int* abort_flag = &s.abort_flag;
+
+    if (warp == 0) {
+        // ============================== TMA producer ==============================
+        if (lane == 0) {
+            if (!(SWAP && FUSED)) griddep_wait();       // activation codes are written by the previous kernel
+            PartIter<SWAP> it(a);
+            Part p;
+            uint32_t n = 0;
+            bool ok = true;
+            while (ok && it.next(p)) {
+                for (int kc = p.kc0; kc < p.kc1 && ok; ++kc, ++n) {
+                    const int st = n % a.stages;
+                    const uint32_t ph = (n / a.stages) & 1;
+                    if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
+                    uint8_t* dst = ring + (size_t)st * stage_bytes;
+                    mbar_expect_tx(&s.full[st], FUSED ? kABytes : stage_bytes);
+                    tma_load_2d(dst, SWAP ? &maps.w[p.mat] : &maps.a[p.mat], kc * kChunk, p.prow, &s.full[st]);
+                    if (!FUSED) tma_load_2d(dst + kABytes, SWAP ? &maps.a[p.mat] : &maps.w[p.mat], kc * kChunk, p.qrow, &s.full[st]);
+                }
+            }
+            if (!ok) {   // give copies already in flight a bounded time to land before the CTA's memory is released
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 2000000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ============================== MMA issuer ==============================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(KIND, kTileP, a.NB);
+            PartIter<SWAP> it(a);
+            Part p;
+            uint32_t n = 0, pc = 0;
+            bool ok = true;
+            while (ok && it.next(p)) {
+                const int buf = pc & 1;
+                if (!mbar_wait(&s.tempty[buf], ((pc >> 1) & 1) ^ 1, abort_flag)) { tc_abort(s, a); break; }
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + (uint32_t)(buf * a.acc_stride);
+                for (int kc = p.kc0; kc < p.kc1; ++kc, ++n) {
+                    const int st = n % a.stages;
+                    if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(ring + (size_t)st * stage_bytes);
+                    const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
+#pragma unroll
+                    for (int k = 0; k < kChunk / 32; ++k)
+                        tc_mma<KIND>(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kc > p.kc0 || k > 0) ? 1u : 0u);
+                    tc_commit(&s.empty[st]);            // the stage may be refilled once these MMAs have read it
+                }
+                if (ok) tc_commit(&s.tfull[buf]);
+                ++pc;
+            }
+        }
+    } else if (warp < 6) {
+        // ============================== epilogue ==============================
+        griddep_wait();
+        const int q = warp & 3;                         // TMEM lane quarter this warp may read
+        const int et = (warp - 2) * 32 + lane;          // thread index inside the epilogue group
+        const int prow_l = q * 32 + lane;               // row of the A operand held by this thread
+        PartIter<SWAP> it(a);
+        Part p;
+        uint32_t pc = 0;
+        while (it.next(p)) {
+            const int buf = pc & 1;
+            if (!mbar_wait(&s.tfull[buf], (pc >> 1) & 1, abort_flag)) { tc_abort(s, a); break; }
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + (uint32_t)(buf * a.acc_stride) + ((uint32_t)(q * 32) << 16);
+            const float wsc = a.ws[p.mat][0];
+            if constexpr (SWAP) {
+                const int n = p.prow + prow_l;          // weight row
+                const bool partial = p.nslots > 1;
+                float out_scale = 0.f;
+                if constexpr (KIND == KIND_F8) {
+                    float am;
+                    if constexpr (FUSED) am = s.amax[p.mat];
+                    else am = a.amax_is_amax ? fmaxf(a.a_scale[p.mat][0], 1e-12f) : a.a_scale[p.mat][0];
+                    out_scale = ((FUSED || a.amax_is_amax) ? div_mode_f32(am, 448.f, a.div_mode) : am) * wsc;
+                }
+                auto finish = [&](T v, int m) {
+                    float f;
+                    if constexpr (KIND == KIND_F8) {
+                        f = v * out_scale;
+                    } else {
+                        if (a.acc[p.mat]) a.acc[p.mat][(int64_t)m * a.ldacc + n] = v;
+                        float rs;
+                        if constexpr (FUSED) rs = div_mode_f32(s.xs[p.mat][m], 127.f, a.div_mode);
+                        else rs = a.a_scale[p.mat][m];
+                        f = (float)v * (rs * wsc);
+                    }
+                    if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
+                    a.out[p.mat][(int64_t)m * a.ldo + n] = __float2half_rn(f);
+                };
+                T* part = reinterpret_cast<T*>(a.scratch) + ((int64_t)p.tile * a.max_slots + p.slot) * a.M * kTileP;
+                for (int c0 = 0; c0 < a.M; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(taddr + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int m = c0 + j;
+                        if (m < a.M) {
+                            T v;
+                            if constexpr (KIND == KIND_F8) v = __uint_as_float(r[j]); else v = (int32_t)r[j];
+                            if (partial) __stcg(part + (int64_t)m * kTileP + prow_l, v);
+                            else if (n < a.N) finish(v, m);
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.tempty[buf]);
+                if (partial) {
+                    __threadfence();
+                    named_bar_sync(1, 128);
+                    if (et == 0) {
+                        const int old = atomicAdd(a.counters + p.tile, 1);
+                        s.last_flag = old == p.nslots - 1;
+                        if (s.last_flag) a.counters[p.tile] = 0;
+                    }
+                    named_bar_sync(1, 128);
+                    if (s.last_flag) {
+                        __threadfence();
+                        const T* base = reinterpret_cast<const T*>(a.scratch) + (int64_t)p.tile * a.max_slots * a.M * kTileP;
+                        if (n < a.N)
+                            for (int m = 0; m < a.M; ++m) {
+                                T sum = 0;
+                                for (int sl = 0; sl < p.nslots; ++sl)
+                                    sum += __ldcg(base + ((int64_t)sl * a.M + m) * kTileP + prow_l);
+                                finish(sum, m);
+                            }
+                    }
+                }
+            } else {
+                const int m = p.prow + prow_l;          // token row
+                float rowscale;
+                if constexpr (KIND == KIND_F8) {
+                    const float am = a.a_scale[p.mat][0];
+                    rowscale = (a.amax_is_amax ? div_mode_f32(fmaxf(am, 1e-12f), 448.f, a.div_mode) : am) * wsc;
+                } else {
+                    rowscale = (m < a.M ? a.a_scale[p.mat][m] : 0.f) * wsc;
+                }
+                const bool vec_ok = (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out[p.mat]) & 15) == 0);
+                for (int c0 = 0; c0 < a.NB; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(taddr + c0, r);
+                    tmem_ld_wait();
+                    const int n0 = p.qrow + c0;
+                    if (m < a.M && n0 < a.N) {
+                        uint32_t h[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float f0, f1;
+                            if constexpr (KIND == KIND_F8) {
+                                f0 = __uint_as_float(r[2 * j]) * rowscale;
+                                f1 = __uint_as_float(r[2 * j + 1]) * rowscale;
+                            } else {
+                                f0 = (float)(int32_t)r[2 * j] * rowscale;
+                                f1 = (float)(int32_t)r[2 * j + 1] * rowscale;
+                            }
+                            if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
+                            const __half2 hh = __floats2half2_rn(f0, f1);
+                            h[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                        }
+                        __half* o = a.out[p.mat] + (int64_t)m * a.ldo + n0;
+                        if (vec_ok && n0 + 16 <= a.N) {
+                            reinterpret_cast<uint4*>(o)[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                            reinterpret_cast<uint4*>(o)[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (n0 + j < a.N) o[j] = __ushort_as_half((unsigned short)((h[j >> 1] >> ((j & 1) * 16)) & 0xffff));
+                        }
+                        if constexpr (KIND == KIND_I8) {
+                            if (a.acc[p.mat]) {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    if (n0 + j < a.N) a.acc[p.mat][(int64_t)m * a.ldacc + n0 + j] = (int32_t)r[j];
+                            }
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.tempty[buf]);
+            }
+            ++pc;
+        }
+    } else if (SWAP && FUSED) {
+        // ============================== activation quantizer ==============================
+        griddep_wait();
+        const int qt = threadIdx.x - 6 * 32, qw = warp - 6;
+        const int kpad = a.kchunks * kChunk;
+        uint8_t* cache = ring + (size_t)a.stages * stage_bytes;          // [nmat][M][kpad] codes, zero beyond K
+        // rows >= M of every B tile are zero for the whole kernel; so is the cache tail beyond K
+        for (int st = 0; st < a.stages; ++st) {
+            uint4* b = reinterpret_cast<uint4*>(ring + (size_t)st * stage_bytes + kABytes);
+            for (int i = qt; i < a.NB * kChunk / 16; i += 128) b[i] = make_uint4(0, 0, 0, 0);
+        }
+        if (kpad != a.K)
+            for (int i = qt; i < a.nmat * a.M * kpad / 16; i += 128) reinterpret_cast<uint4*>(cache)[i] = make_uint4(0, 0, 0, 0);
+        quantizer_scales<KIND, DT>(a, s, qt);
+        quantize_all<KIND, DT>(a, s, cache, kpad, qt);
+        named_bar_sync(2, 128);
+        // each of the four warps feeds every fourth ring slot
+        PartIter<SWAP> it(a);
+        Part p;
+        uint32_t n = 0;
+        bool ok = true;
+        while (ok && it.next(p)) {
+            for (int kc = p.kc0; kc < p.kc1; ++kc, ++n) {
+                if ((int)(n & 3) != qw) continue;
+                const int st = n % a.stages;
+                if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
+                copy_chunk(a, cache, kpad, p.mat, kc, ring + (size_t)st * stage_bytes + kABytes, lane);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.full[st]);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// uint8 matrix [rows, K] with `ld` bytes between rows, tiles of box_rows x 128 bytes, 128-byte swizzle, zero fill
+static int32_t make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows, const char* who) {
+    EncodeTiledFn fn = encode_fn();
+    RWKVQ_REQUIRE(fn != nullptr, RWKVQ_E_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+    RWKVQ_REQUIRE(aligned16(ptr) && ld % 16 == 0 && ld >= K, RWKVQ_E_ALIGN, "%s: TMA needs a 16-byte aligned base and row pitch", who);
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld};
+    const cuuint32_t box[2] = {(cuuint32_t)kChunk, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RWKVQ_REQUIRE(r == CUDA_SUCCESS, RWKVQ_E_LAUNCH, "%s: cuTensorMapEncodeTiled failed (%d)", who, (int)r);
+    return RWKVQ_OK;
+}
+
+constexpr int64_t kWsCounterInts = 1024;                       // arrival counters (row tiles of all matrices)
+constexpr int64_t kWsHeaderBytes = (kWsCounterInts + 16) * 4;  // counters + status word, then the partial sums
+constexpr size_t kTcSmemBudget = 225 * 1024;
+constexpr size_t kTcCacheMax = 96 * 1024;       // FUSED: all activation codes of a call live in shared memory
+
+static int tc_grid() {
+    static const int forced = [] {
+        const char* e = std::getenv("RWKVQ_TC_GRID");
+        return e ? std::atoi(e) : 0;
+    }();
+    return forced > 0 ? forced : sm_count();
+}
+
+// upper bound of the CTAs that share one row tile under the stream-K split
+static int max_slots_for(int64_t total_units, int kchunks, int grid) {
+    const int64_t per = std::max<int64_t>(1, total_units / grid);
+    return (int)((kchunks + per - 1) / per) + 1;
+}
+
+template <int KIND, bool SWAP, bool FUSED, int DT>
+static int32_t launch_tc(const TcMaps& maps, const TcArgs& a, int grid, cudaStream_t st, const char* who) {
+    auto kern = gemm_tc_kernel<KIND, SWAP, FUSED, DT>;
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget); });
+    RWKVQ_REQUIRE(attr_err == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(attr_err));
+    const size_t cache = FUSED ? (size_t)a.nmat * a.M * a.kchunks * kChunk : 0;
+    const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.NB * kChunk) + cache + 1024;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    const char* e = std::getenv("RWKVQ_PDL");
+    cfg.numAttrs = (e && e[0] == '0') ? 0 : 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, maps, a);
+    if (err != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(err));
+    }
+    return check_launch(who);
+}
+
+struct TcCall {
+    int kind;                 // KIND_F8 / KIND_I8
+    bool fused;               // SWAP only: quantize activations in the kernel
+    int x_dtype;
+    const void* w[3];
+    int64_t ldw;
+    const void* codes[3];     // codes route
+    int64_t lda;
+    void* workspace;
+    int64_t workspace_bytes;
+};
+
+static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
+    RWKVQ_REQUIRE(a.M >= 0 && a.N >= 0 && a.K >= 0, RWKVQ_E_SHAPE, "%s: negative size", who);
+    RWKVQ_REQUIRE(a.K % 16 == 0, RWKVQ_E_SHAPE, "%s: K=%d must be a multiple of 16", who, a.K);
+    RWKVQ_REQUIRE(a.ldo >= a.N, RWKVQ_E_SHAPE, "%s: ldo=%lld < N", who, (long long)a.ldo);
+    RWKVQ_REQUIRE(a.div_mode == RWKVQ_DIV_IEEE || a.div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, a.div_mode);
+    for (int i = 0; i < a.nmat; ++i) {
+        RWKVQ_REQUIRE(c.w[i] && a.ws[i] && a.out[i], RWKVQ_E_BADARG, "%s: null weight / scale / out pointer (matrix %d)", who, i);
+        if (c.fused) {
+            RWKVQ_REQUIRE(a.x[i] != nullptr, RWKVQ_E_BADARG, "%s: null activation pointer", who);
+            RWKVQ_REQUIRE(aligned16(a.x[i]) && a.ldx % 8 == 0 && a.ldx >= a.K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+        } else {
+            RWKVQ_REQUIRE(c.codes[i] && a.a_scale[i], RWKVQ_E_BADARG, "%s: null activation codes / scale", who);
+        }
+    }
+    if (c.fused) RWKVQ_REQUIRE(c.x_dtype == RWKVQ_F16 || c.x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, c.x_dtype);
+    if (a.M == 0 || a.N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(a.K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
+
+    const bool swap = c.fused || a.M <= 128;
+    if (c.fused) RWKVQ_REQUIRE(a.M <= 16, RWKVQ_E_SHAPE, "%s: the fused kernel takes M <= 16, got %d", who, a.M);
+    a.kchunks = (a.K + kChunk - 1) / kChunk;
+    TcMaps maps;
+    int grid;
+    if (swap) {
+        a.NB = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : (a.M <= 64 ? 64 : 128));
+        a.ptiles = (a.N + kTileP - 1) / kTileP;
+        a.qtiles = 1;
+        const int64_t total = (int64_t)a.nmat * a.ptiles * a.kchunks;
+        grid = (int)std::min<int64_t>(tc_grid(), total);
+        a.max_slots = max_slots_for(total, a.kchunks, grid);
+        const int64_t tiles = (int64_t)a.nmat * a.ptiles;
+        RWKVQ_REQUIRE(tiles <= kWsCounterInts, RWKVQ_E_SHAPE, "%s: N=%d has too many row tiles for the workspace counters", who, a.N);
+        const int64_t need = kWsHeaderBytes + tiles * a.max_slots * (int64_t)a.M * kTileP * 4;
+        RWKVQ_REQUIRE(c.workspace != nullptr && c.workspace_bytes >= need, RWKVQ_E_WORKSPACE,
+                      "%s: workspace of %lld bytes needed, %lld given", who, (long long)need, (long long)c.workspace_bytes);
+        RWKVQ_REQUIRE(aligned16(c.workspace), RWKVQ_E_ALIGN, "%s: workspace must be 16-byte aligned", who);
+        a.counters = reinterpret_cast<int*>(c.workspace);
+        a.status = a.counters + kWsCounterInts;
+        a.scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(c.workspace) + kWsHeaderBytes);
+    } else {
+        a.NB = 256;
+        a.ptiles = (a.M + kTileP - 1) / kTileP;
+        a.qtiles = (a.N + a.NB - 1) / a.NB;
+        grid = (int)std::min<int64_t>(tc_grid(), (int64_t)a.nmat * a.ptiles * a.qtiles);
+        a.max_slots = 1;
+        a.status = c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : nullptr;
+    }
+    a.acc_stride = std::max(a.NB, 32);
+    const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk;
+    const size_t cache_bytes = c.fused ? (size_t)a.nmat * a.M * a.kchunks * kChunk : 0;
+    RWKVQ_REQUIRE(cache_bytes <= kTcCacheMax, RWKVQ_E_SHAPE, "%s: %d x %d x %d activation codes do not fit the fused kernel's shared memory",
+                  who, a.nmat, a.M, a.K);
+    a.stages = (int)std::min<size_t>(kMaxStages, (kTcSmemBudget - 1024 - cache_bytes) / stage_bytes);
+    for (int i = 0; i < a.nmat; ++i) {
+        int32_t rc = make_map(&maps.w[i], c.w[i], a.N, a.K, c.ldw, swap ? kTileP : a.NB, who);
+        if (rc) return rc;
+        if (!c.fused) {
+            rc = make_map(&maps.a[i], c.codes[i], a.M, a.K, c.lda, swap ? a.NB : kTileP, who);
+            if (rc) return rc;
+        }
+    }
+#define RWKVQ_TC(KIND, SWAP, FUSED, DT) launch_tc<KIND, SWAP, FUSED, DT>(maps, a, grid, st, who)
+    if (c.kind == KIND_F8) {
+        if (c.fused) return c.x_dtype == RWKVQ_F16 ? RWKVQ_TC(KIND_F8, true, true, RWKVQ_F16) : RWKVQ_TC(KIND_F8, true, true, RWKVQ_BF16);
+        return swap ? RWKVQ_TC(KIND_F8, true, false, RWKVQ_BF16) : RWKVQ_TC(KIND_F8, false, false, RWKVQ_BF16);
+    }
+    if (c.fused) return c.x_dtype == RWKVQ_F16 ? RWKVQ_TC(KIND_I8, true, true, RWKVQ_F16) : RWKVQ_TC(KIND_I8, true, true, RWKVQ_BF16);
+    return swap ? RWKVQ_TC(KIND_I8, true, false, RWKVQ_BF16) : RWKVQ_TC(KIND_I8, false, false, RWKVQ_BF16);
+#undef RWKVQ_TC
+}
+
+}  // namespace rwkvq
+
+using namespace rwkvq;
+
+extern "C" {
+
+int64_t rwkvq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t nmat) {
+    if (M <= 0 || N <= 0 || K <= 0 || nmat <= 0) return kWsHeaderBytes;
+    const int kchunks = (int)((K + kChunk - 1) / kChunk);
+    const int64_t tiles = nmat * ((N + kTileP - 1) / kTileP);
+    const int64_t total = tiles * kchunks;
+    const int grid = (int)std::min<int64_t>(tc_grid(), total);
+    return kWsHeaderBytes + tiles * max_slots_for(total, kchunks, grid) * M * kTileP * 4;
+}
+
+int32_t rwkvq_workspace_status(const void* workspace, int32_t* host_status) {
+    RWKVQ_REQUIRE(workspace && host_status, RWKVQ_E_BADARG, "workspace_status: null pointer");
+    const cudaError_t e = cudaMemcpy(host_status, reinterpret_cast<const int*>(workspace) + kWsCounterInts, sizeof(int32_t), cudaMemcpyDeviceToHost);
+    RWKVQ_REQUIRE(e == cudaSuccess, RWKVQ_E_LAUNCH, "workspace_status: %s", cudaGetErrorString(e));
+    return RWKVQ_OK;
+}
+
+static void fill_common(TcArgs& a, int nmat, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldo, int32_t div_mode, uint32_t flags) {
+    a.nmat = nmat; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldo = ldo; a.div_mode = div_mode; a.flags = flags;
+}
+
+int32_t rwkvq_tc_gemv_fp8(const void* x, int32_t x_dtype, const float* awq, const uint8_t* w, int64_t ldw, const float* w_scale,
+                          void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                          uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream) {
+    TcArgs a{};
+    a.x[0] = x; a.awq[0] = awq; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    fill_common(a, 1, M, N, K, ldx, ldo, div_mode, flags);
+    TcCall c{};
+    c.kind = KIND_F8; c.fused = true; c.x_dtype = x_dtype; c.w[0] = w; c.ldw = ldw; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemv_fp8");
+}
+
+int32_t rwkvq_tc_gemv_fp8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const float* awq_r,
+                              const float* awq_k, const uint8_t* wr, const uint8_t* wk, const uint8_t* wv, int64_t ldw,
+                              const float* sr, const float* sk, const float* sv, void* out_r, void* out_k, void* out_v,
+                              int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags,
+                              void* workspace, int64_t workspace_bytes, void* stream) {
+    TcArgs a{};
+    a.x[0] = xr; a.x[1] = xk; a.x[2] = xv; a.awq[0] = awq_r; a.awq[1] = awq_k;
+    a.ws[0] = sr; a.ws[1] = sk; a.ws[2] = sv;
+    a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
+    fill_common(a, 3, M, N, K, ldx, ldo, div_mode, flags);
+    TcCall c{};
+    c.kind = KIND_F8; c.fused = true; c.x_dtype = x_dtype; c.w[0] = wr; c.w[1] = wk; c.w[2] = wv; c.ldw = ldw;
+    c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemv_fp8_rkv");
+}
+
+int32_t rwkvq_tc_gemv_int8(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale, void* out_f16,
+                           int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                           int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream) {
+    TcArgs a{};
+    a.x[0] = x; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16; a.acc[0] = acc_out; a.ldacc = ldacc;
+    fill_common(a, 1, M, N, K, ldx, ldo, div_mode, flags);
+    RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "tc_gemv_int8: ldacc < N");
+    TcCall c{};
+    c.kind = KIND_I8; c.fused = true; c.x_dtype = x_dtype; c.w[0] = w; c.ldw = ldw; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemv_int8");
+}
+
+int32_t rwkvq_tc_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const int8_t* wr,
+                               const int8_t* wk, const int8_t* wv, int64_t ldw, const float* sr, const float* sk,
+                               const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N,
+                               int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags, void* workspace,
+                               int64_t workspace_bytes, void* stream) {
+    TcArgs a{};
+    a.x[0] = xr; a.x[1] = xk; a.x[2] = xv;
+    const bool shared = (flags & RWKVQ_FLAG_INT8_SHARED_WSCALE) != 0;
+    a.ws[0] = sr; a.ws[1] = shared ? sr : sk; a.ws[2] = shared ? sr : sv;
+    a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
+    fill_common(a, 3, M, N, K, ldx, ldo, div_mode, flags);
+    TcCall c{};
+    c.kind = KIND_I8; c.fused = true; c.x_dtype = x_dtype; c.w[0] = wr; c.w[1] = wk; c.w[2] = wv; c.ldw = ldw;
+    c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemv_int8_rkv");
+}
+
+int32_t rwkvq_tc_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
+                          int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                          int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream) {
+    TcArgs a{};
+    a.a_scale[0] = amax; a.amax_is_amax = amax_is_amax; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    fill_common(a, 1, M, N, K, 0, ldo, div_mode, flags);
+    TcCall c{};
+    c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_fp8");
+}
+
+int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                           const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M,
+                           int64_t N, int64_t K, uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream) {
+    TcArgs a{};
+    a.a_scale[0] = a_scales; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16; a.acc[0] = acc_out; a.ldacc = ldacc;
+    fill_common(a, 1, M, N, K, 0, ldo, RWKVQ_DIV_IEEE, flags);
+    RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "tc_gemm_int8: ldacc < N");
+    TcCall c{};
+    c.kind = KIND_I8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8");
+}
+
+}  // extern "C"

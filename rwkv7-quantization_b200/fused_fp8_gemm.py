@@ -10,11 +10,16 @@ Outputs are freshly allocated tensors owned by the caller; weights are borrowed;
 CUDA stream without host synchronisation -- the conventions of the reference wrappers
 (fused_fp8_gemm.py:55-79, 645-679, 785-818, 944-1098).
 
-Routing by M = rows of the flattened activation:
-    M <= 32 (and the code tile fits shared memory)  one fused launch: activation quantization in the GEMV prologue
-    larger M                                        activation-quantization kernels + GEMM on the codes
+Routing by M = rows of the flattened activation (tensor-memory kernels: TMA -> tcgen05.mma):
+    M <= 4      one fused launch: activation quantization by dedicated warps of the weight-streaming kernel
+    M <= 128    activation-quantization kernels, then the weight-streaming kernel on the codes
+    larger M    activation-quantization kernels, then the 128 x 256 tile prefill GEMM
+RWKVQ_ROUTE=mma selects the register-streaming mma.sync kernels instead (M <= 32 fused, codes GEMM above);
+they compute the same results and serve as the cross-check of the tensor-memory path.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -26,6 +31,9 @@ USE_CUDA_GRAPH = False  # kept for importers (fused_fp8_gemm.py:941); graphs are
 
 GEMV_M_MAX = 32
 _GEMV_SMEM_BUDGET = 200 * 1024 - 5 * 1024
+TC_FUSED_M_MAX = 4                 # rows up to which the activation quantization rides inside the streaming kernel
+_TC_CACHE_MAX = 96 * 1024
+ROUTE = os.environ.get("RWKVQ_ROUTE", "tc").lower()
 
 
 # --------------------------------------------------------------------------- helpers
@@ -50,6 +58,10 @@ def _unpack(weight_info_or_w, res_scale=None):
 def _gemv_fits(m: int, k: int) -> bool:
     pitch = (k + 127) // 128 * 128 + 64
     return 0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0
+
+
+def _tc_fused_fits(m: int, k: int, nmat: int = 1) -> bool:
+    return ROUTE == "tc" and 0 < m <= TC_FUSED_M_MAX and k % 16 == 0 and nmat * m * ((k + 127) // 128 * 128) <= _TC_CACHE_MAX
 
 
 def _finish(out2d: torch.Tensor, lead, n: int, out_dtype):
@@ -143,6 +155,12 @@ def _fp8_gemv(x2, w, w_ts, awq, flags):
     m, k = x2.shape
     n = w.shape[0]
     out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    if _tc_fused_fits(m, k):
+        ws = abi.workspace(m, n, k, 1, x2.device)
+        abi.call("rwkvq_tc_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
+                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
+                 ws.data_ptr(), ws.numel(), abi.stream_ptr())
+        return out
     abi.call("rwkvq_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
              w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
              abi.stream_ptr())
@@ -159,8 +177,13 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     st = abi.stream_ptr()
     abi.call("rwkvq_actq_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
              codes.data_ptr(), k, amax.data_ptr(), None, abi.DEFAULT_DIV, act_flags, st)
-    abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
-             out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, st)
+    if ROUTE == "tc":
+        ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
+        abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
+                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(), st)
+    else:
+        abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
+                 out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, st)
     return out
 
 
@@ -181,7 +204,7 @@ def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float1
     if m == 1:
         return linear_fp8_m1_fused(x, {"weight": w, "tensor_scale": w_ts}, out_dtype)
     x2 = _rows16(x)
-    if _gemv_fits(m, k):
+    if _tc_fused_fits(m, k) or (ROUTE != "tc" and _gemv_fits(m, k)):
         out = _fp8_gemv(x2, _u8(w), w_ts, None, 0)
     else:
         out = _fp8_codes_gemm(x2, _u8(w), w_ts, abi.FLAG_QUANT_FROM_BF16)
@@ -195,24 +218,34 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     if len({t.dtype for t in xs}) != 1:
         xs = [t.to(torch.bfloat16) for t in xs]
     m, k = xs[0].shape
-    ws = [_u8(i["weight"]) for i in (wr_info, wk_info, wv_info)]
-    n = ws[0].shape[0]
+    ws_ = [_u8(i["weight"]) for i in (wr_info, wk_info, wv_info)]
+    n = ws_[0].shape[0]
     dev = xs[0].device
     awq_r, awq_k = wr_info.get("awq_scale"), wk_info.get("awq_scale")
-    same_ld = len({w.stride(0) for w in ws}) == 1 and all(w.shape == ws[0].shape for w in ws)
-    if _gemv_fits(m, k) and same_ld:
+    same_ld = len({w.stride(0) for w in ws_}) == 1 and all(w.shape == ws_[0].shape for w in ws_)
+    f32 = lambda a: None if a is None else a.to(device=dev, dtype=torch.float32).contiguous()
+    if _tc_fused_fits(m, k, 3) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
-        f32 = lambda a: None if a is None else a.to(device=dev, dtype=torch.float32).contiguous()
+        awq_r, awq_k = f32(awq_r), f32(awq_k)
+        ws = abi.workspace(m, n, k, 3, dev)
+        abi.call("rwkvq_tc_gemv_fp8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),
+                 abi.ptr(awq_r), abi.ptr(awq_k), ws_[0].data_ptr(), ws_[1].data_ptr(), ws_[2].data_ptr(), ws_[0].stride(0),
+                 wr_info["tensor_scale"].data_ptr(), wk_info["tensor_scale"].data_ptr(),
+                 wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
+                 m, n, k, k, abi.DEFAULT_DIV, 0, ws.data_ptr(), ws.numel(), abi.stream_ptr())
+    elif ROUTE != "tc" and _gemv_fits(m, k) and same_ld:
+        xs = [t.contiguous() for t in xs]
+        outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
         awq_r, awq_k = f32(awq_r), f32(awq_k)
         abi.call("rwkvq_gemv_fp8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),
-                 abi.ptr(awq_r), abi.ptr(awq_k), ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0),
+                 abi.ptr(awq_r), abi.ptr(awq_k), ws_[0].data_ptr(), ws_[1].data_ptr(), ws_[2].data_ptr(), ws_[0].stride(0),
                  wr_info["tensor_scale"].data_ptr(), wk_info["tensor_scale"].data_ptr(),
                  wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
                  m, n, k, k, abi.DEFAULT_DIV, 0, abi.stream_ptr())
     else:
         outs = []
-        for x2, w, info, awq in zip(xs, ws, (wr_info, wk_info, wv_info), (awq_r, awq_k, None)):
+        for x2, w, info, awq in zip(xs, ws_, (wr_info, wk_info, wv_info), (awq_r, awq_k, None)):
             if awq is not None:                      # AWQ division, then the plain route on the bf16 copy
                 x2, _ = prep_x(x2, awq)
             outs.append(_fp8_codes_gemm(x2, w, info["tensor_scale"], abi.FLAG_QUANT_FROM_BF16))
@@ -225,7 +258,12 @@ def _int8_any(x2, w, w_scale, acc_out=None):
     n = w.shape[0]
     out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
     st = abi.stream_ptr()
-    if _gemv_fits(m, k):
+    if _tc_fused_fits(m, k):
+        ws = abi.workspace(m, n, k, 1, x2.device)
+        abi.call("rwkvq_tc_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
+                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0,
+                 ws.data_ptr(), ws.numel(), st)
+    elif ROUTE != "tc" and _gemv_fits(m, k):
         abi.call("rwkvq_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
                  out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0, st)
     else:
@@ -233,8 +271,13 @@ def _int8_any(x2, w, w_scale, acc_out=None):
         xs = torch.empty(m, dtype=torch.float32, device=x2.device)
         abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
                  codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
-        abi.call("rwkvq_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
-                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, st)
+        if ROUTE == "tc":
+            ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
+            abi.call("rwkvq_tc_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0),
+                     w_scale.data_ptr(), out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, ws.data_ptr(), ws.numel(), st)
+        else:
+            abi.call("rwkvq_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
+                     out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, st)
     return out
 
 
@@ -259,7 +302,15 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
     n = ws[0].shape[0]
     scales = [wr_info["tensor_scale"]] * 3 if compat_shared_scale else [i["tensor_scale"] for i in infos]
     same_ld = len({w.stride(0) for w in ws}) == 1 and all(w.shape == ws[0].shape for w in ws)
-    if _gemv_fits(m, k) and same_ld:
+    if _tc_fused_fits(m, k, 3) and same_ld:
+        xs = [t.contiguous() for t in xs]
+        outs = [torch.empty((m, n), dtype=torch.float16, device=xs[0].device) for _ in range(3)]
+        wsp = abi.workspace(m, n, k, 3, xs[0].device)
+        abi.call("rwkvq_tc_gemv_int8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),
+                 ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0), scales[0].data_ptr(),
+                 scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(),
+                 outs[2].data_ptr(), n, m, n, k, k, abi.DEFAULT_DIV, 0, wsp.data_ptr(), wsp.numel(), abi.stream_ptr())
+    elif ROUTE != "tc" and _gemv_fits(m, k) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=xs[0].device) for _ in range(3)]
         abi.call("rwkvq_gemv_int8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),

@@ -50,8 +50,18 @@ SIGNATURES = {
     "rwkvq_gemm_int8": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p],
     "rwkvq_gemm_fp8_mma": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
     "rwkvq_gemm_int8_mma": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p],
+    "rwkvq_workspace_bytes": [_i64, _i64, _i64, _i32],
+    "rwkvq_workspace_status": [_p, _p],
+    "rwkvq_tc_gemv_fp8": [_p, _i32, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _i64, _p],
+    "rwkvq_tc_gemv_fp8_rkv": [_p, _p, _p, _i32, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64,
+                              _i64, _i64, _i32, _u32, _p, _i64, _p],
+    "rwkvq_tc_gemv_int8": [_p, _i32, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _i64, _p],
+    "rwkvq_tc_gemv_int8_rkv": [_p, _p, _p, _i32, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
+                               _i64, _i32, _u32, _p, _i64, _p],
+    "rwkvq_tc_gemm_fp8": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p, _i64, _p],
+    "rwkvq_tc_gemm_int8": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p, _i64, _p],
 }
-_RESTYPES = {"rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64}
+_RESTYPES = {"rwkvq_workspace_bytes": ctypes.c_int64, "rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64}
 
 _lib = None
 _device_checked = False
@@ -124,3 +134,25 @@ def div_on_device(a: torch.Tensor, b: torch.Tensor, mode: int = DIV_FULL) -> tor
     out = torch.empty_like(a32)
     call("rwkvq_div_f32", a32.data_ptr(), b32.data_ptr(), out.data_ptr(), a32.numel(), mode, stream_ptr())
     return out
+
+
+# ---------------------------------------------------------------------------- workspace of the tensor-memory kernels
+_workspaces: dict = {}
+
+
+def workspace(m: int, n: int, k: int, nmat: int, device) -> torch.Tensor:
+    """Zero-initialised scratch for the tcgen05 kernels, one per (device, stream), grown on demand.
+    Launches on one stream are ordered, so they can share it; the kernels leave its counters zero."""
+    need = int(lib().rwkvq_workspace_bytes(m, n, k, nmat))
+    key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_status(ws: torch.Tensor) -> int:
+    out = ctypes.c_int32(0)
+    call("rwkvq_workspace_status", ws.data_ptr(), ctypes.addressof(out))
+    return out.value
