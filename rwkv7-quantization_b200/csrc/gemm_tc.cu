@@ -51,6 +51,7 @@ struct TcArgs {
     float* scratch;            // SWAP: partial sums [row tile][slot][M][128] (fp32 or int32 bits)
     int* counters;             // SWAP: arrivals per row tile, zero before the first use, left zero by every launch
     int* status;               // set to RWKVQ_E_TIMEOUT if a bounded wait gave up
+    unsigned long long* trace; // optional [grid][16] timestamps of role milestones (profiling aid), else null
     int64_t ldx, ldo, ldacc;
     int M, N, K, nmat;
     int NB;                    // rows of the B operand (UMMA N)
@@ -66,22 +67,23 @@ struct Part {
 // Enumerates the parts of this CTA: SWAP = contiguous range of (tile, chunk) units; GEMM = whole tiles, strided.
 template <bool SWAP>
 struct PartIter {
+    // all counts fit 32 bits: the host checks total * grid < 2^31
     const TcArgs& a;
-    int64_t pos, end, total;
+    uint32_t pos, end, total;
     __device__ explicit PartIter(const TcArgs& args) : a(args) {
         if constexpr (SWAP) {
-            total = (int64_t)a.nmat * a.ptiles * a.kchunks;
+            total = (uint32_t)(a.nmat * a.ptiles * a.kchunks);
             pos = begin_of(blockIdx.x);
             end = begin_of(blockIdx.x + 1);
         } else {
-            total = (int64_t)a.nmat * a.ptiles * a.qtiles;
+            total = (uint32_t)(a.nmat * a.ptiles * a.qtiles);
             pos = blockIdx.x;
             end = total;
         }
     }
-    __device__ int64_t begin_of(int64_t c) const { return total * c / gridDim.x; }
-    __device__ int owner(int64_t u) const {     // CTA whose range holds unit u
-        int64_t c = u * gridDim.x / total;
+    __device__ uint32_t begin_of(uint32_t c) const { return total * c / gridDim.x; }
+    __device__ int owner(uint32_t u) const {     // CTA whose range holds unit u
+        uint32_t c = u * gridDim.x / total;
         while (begin_of(c + 1) <= u) ++c;
         while (c > 0 && begin_of(c) > u) --c;
         return (int)c;
@@ -89,12 +91,12 @@ struct PartIter {
     __device__ bool next(Part& p) {
         if (pos >= end) return false;
         if constexpr (SWAP) {
-            const int64_t tile = pos / a.kchunks;
+            const uint32_t tile = pos / (uint32_t)a.kchunks;
             p.tile = (int)tile;
             p.kc0 = (int)(pos - tile * a.kchunks);
-            p.kc1 = (int)min((int64_t)a.kchunks, p.kc0 + (end - pos));
-            p.mat = (int)(tile / a.ptiles);
-            p.prow = (int)(tile - (int64_t)p.mat * a.ptiles) * kTileP;
+            p.kc1 = (int)min((uint32_t)a.kchunks, p.kc0 + (end - pos));
+            p.mat = (int)(tile / (uint32_t)a.ptiles);
+            p.prow = (int)(tile - (uint32_t)p.mat * a.ptiles) * kTileP;
             p.qrow = 0;
             if (p.kc0 == 0 && p.kc1 == a.kchunks) {
                 p.slot = 0;
@@ -108,8 +110,8 @@ struct PartIter {
         } else {
             const int per_mat = a.ptiles * a.qtiles;
             p.tile = (int)pos;
-            p.mat = (int)(pos / per_mat);
-            const int r = (int)(pos - (int64_t)p.mat * per_mat);
+            p.mat = (int)(pos / (uint32_t)per_mat);
+            const int r = (int)(pos - (uint32_t)p.mat * per_mat);
             p.prow = (r / a.qtiles) * kTileP;
             p.qrow = (r % a.qtiles) * a.NB;
             p.kc0 = 0;
@@ -129,8 +131,14 @@ struct TcShared {
     int last_flag;
     float amax[3];             // FUSED FP8: max(amax, 1e-12) per matrix
     float xs[3][16];           // FUSED INT8: row scales per matrix
-    float red[4];
+    float red[8];
+    uint64_t done;             // epilogue warps have read their last accumulator
+    uint64_t xbar;             // FUSED: the activation block has landed in shared memory
 };
+
+__device__ __forceinline__ void tc_mark(const TcArgs& a, int slot) {
+    if (a.trace) a.trace[(size_t)blockIdx.x * 16 + slot] = global_ns();
+}
 
 __device__ __forceinline__ void tc_abort(TcShared& s, const TcArgs& a) {
     s.abort_flag = 1;
@@ -138,61 +146,77 @@ __device__ __forceinline__ void tc_abort(TcShared& s, const TcArgs& a) {
 }
 
 // ---- FUSED quantizer helpers (128 threads = warps 6..9); qt = thread index within the group
-__device__ __forceinline__ float group_max(float v, float* red, int qt) {   // max over the 128 quantizer threads
+constexpr int kQThreads = 256;   // warps 2..9 share the FUSED prologue
+
+__device__ __forceinline__ float group_max(float v, float* red, int qt) {   // max over the 256 prologue threads
     v = warp_max(v);
-    named_bar_sync(2, 128);
+    named_bar_sync(2, kQThreads);
     if ((qt & 31) == 0) red[qt >> 5] = v;
-    named_bar_sync(2, 128);
-    return fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    named_bar_sync(2, kQThreads);
+    return fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
 }
 
-template <int KIND, int DT>
-__device__ void quantizer_scales(const TcArgs& a, TcShared& s, int qt) {
-    for (int mat = 0; mat < a.nmat; ++mat) {
-        const char* x = reinterpret_cast<const char*>(a.x[mat]);
-        const float* awq = KIND == KIND_F8 ? a.awq[mat] : nullptr;
-        if constexpr (KIND == KIND_F8) {
-            const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
-            float m = 0.f;
-            const int kv = a.K >> 3, nvec = a.M * kv;
-            for (int i = qt; i < nvec; i += 128) {
-                const int r = i / kv, k = (i - r * kv) << 3;
-                const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
-                fp8_vec_amax<DT>(v, awq, k, a.div_mode, after, m);
-            }
-            m = group_max(m, s.red, qt);
-            if (qt == 0) s.amax[mat] = fmaxf(m, 1e-12f);
-        } else {
-            for (int r = 0; r < a.M; ++r) {
-                float m = 0.f;
-                for (int k = qt * 8; k < a.K; k += 128 * 8)
-                    m = int8_vec_amax<DT>(*reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2), m);
-                m = fmaxf(group_max(m, s.red, qt), 1e-12f);
-                if (qt == 0) s.xs[mat][r] = m;      // the row amax; scale amax/127 is formed where it is used
-            }
-        }
-    }
-    named_bar_sync(2, 128);
-}
+// FUSED prologue of the quantizer warps: scales (per-call amax for FP8, per-row amax for INT8) and the codes of
+// the whole activation block into the compact cache [mat][row][kpad].  Two short loops (amax, then codes) with
+// kQB loads in flight per thread; the second read of x hits L1/L2.  The code is kept small on purpose: it runs
+// once per CTA, and straight-line code that is executed once is paced by instruction fetch, not by the ALUs.
+constexpr int kQB = 4;
 
-// Quantizes all of x (every matrix) into the compact code cache [mat][row][Kpad] in shared memory.
 template <int KIND, int DT>
-__device__ void quantize_all(const TcArgs& a, const TcShared& s, uint8_t* cache, int kpad, int qt) {
+__device__ __noinline__ void quantizer_prologue(const TcArgs& a, TcShared& s, uint8_t* cache, const uint8_t* xstage, int kpad, int qt) {
     const int kv = a.K >> 3;
+    const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
+    const int rstep = KIND == KIND_F8 ? a.M : 1;      // rows sharing one scale
+    const int nvec = rstep * kv;
     for (int mat = 0; mat < a.nmat; ++mat) {
-        const char* x = reinterpret_cast<const char*>(a.x[mat]);
-        for (int i = qt; i < a.M * kv; i += 128) {
-            const int r = i / kv, k = (i - r * kv) << 3;
-            const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
-            uint2 c;
-            if constexpr (KIND == KIND_F8) {
-                c = fp8_vec_codes<DT>(v, a.awq[mat], k, a.div_mode, div_mode_f32(448.f, s.amax[mat], a.div_mode));
-            } else {
-                c = int8_vec_codes<DT>(v, div_mode_f32(127.f, s.xs[mat][r], a.div_mode));
+        const float* awq = KIND == KIND_F8 ? a.awq[mat] : nullptr;
+        for (int r0 = 0; r0 < a.M; r0 += rstep) {
+            const char* xb = reinterpret_cast<const char*>(xstage) + ((size_t)mat * a.M + r0) * a.K * 2;   // staged rows are K apart
+            uint8_t* cb = cache + ((size_t)mat * a.M + r0) * kpad;
+            float m = 0.f;
+#pragma unroll 1
+            for (int b = qt; b < nvec; b += kQThreads * kQB) {
+                uint4 v[kQB];
+                int kk[kQB];
+#pragma unroll
+                for (int j = 0; j < kQB; ++j) {
+                    const int i = min(b + j * kQThreads, nvec - 1), r = i / kv;
+                    kk[j] = (i - r * kv) << 3;
+                    v[j] = *reinterpret_cast<const uint4*>(xb + ((size_t)r * a.K + kk[j]) * 2);
+                }
+#pragma unroll
+                for (int j = 0; j < kQB; ++j) {
+                    if constexpr (KIND == KIND_F8) fp8_vec_amax<DT>(v[j], awq, kk[j], a.div_mode, after, m);
+                    else m = int8_vec_amax<DT>(v[j], m);
+                }
             }
-            *reinterpret_cast<uint2*>(cache + ((size_t)mat * a.M + r) * kpad + k) = c;
+            m = fmaxf(group_max(m, s.red, qt), 1e-12f);
+            if (qt == 0) {
+                if constexpr (KIND == KIND_F8) s.amax[mat] = m; else s.xs[mat][r0] = m;
+            }
+            const float sc = div_mode_f32(KIND == KIND_F8 ? 448.f : 127.f, m, a.div_mode);
+#pragma unroll 1
+            for (int b = qt; b < nvec; b += kQThreads * kQB) {
+                uint4 v[kQB];
+                int kk[kQB], rr[kQB];
+#pragma unroll
+                for (int j = 0; j < kQB; ++j) {
+                    const int i = min(b + j * kQThreads, nvec - 1);
+                    rr[j] = i / kv;
+                    kk[j] = (i - rr[j] * kv) << 3;
+                    v[j] = *reinterpret_cast<const uint4*>(xb + ((size_t)rr[j] * a.K + kk[j]) * 2);
+                }
+#pragma unroll
+                for (int j = 0; j < kQB; ++j) {
+                    uint2 c;
+                    if constexpr (KIND == KIND_F8) c = fp8_vec_codes<DT>(v[j], awq, kk[j], a.div_mode, sc);
+                    else c = int8_vec_codes<DT>(v[j], sc);
+                    if (b + j * kQThreads < nvec) *reinterpret_cast<uint2*>(cb + (size_t)rr[j] * kpad + kk[j]) = c;
+                }
+            }
         }
     }
+    named_bar_sync(2, kQThreads);
 }
 
 // Copies the codes of K chunk kc from the cache into a swizzled B tile; one warp: lane -> (row = lane/8 + 4*pass,
@@ -205,8 +229,36 @@ __device__ __forceinline__ void copy_chunk(const TcArgs& a, const uint8_t* cache
     }
 }
 
+// FUSED: bring the activation block into shared memory with bulk copies (one memory latency for all of it), zero the
+// B tiles (rows >= M stay zero for the whole kernel) and the cache tail meanwhile, then quantize from shared memory.
+template <int KIND, int DT>
+__device__ __noinline__ bool fused_prologue(const TcArgs& a, TcShared& s, uint8_t* ring, uint32_t stage_bytes, int qt,
+                                            const volatile int* abort_flag) {
+    const int kpad = a.kchunks * kChunk;
+    uint8_t* cache = ring + (size_t)a.stages * stage_bytes;          // [nmat][M][kpad] codes, zero beyond K
+    uint8_t* xstage = cache + (size_t)a.nmat * a.M * kpad;           // [nmat][M][K] activations as given
+    if (qt == 0) {
+        const uint32_t row_bytes = (uint32_t)a.K * 2;
+        mbar_expect_tx(&s.xbar, row_bytes * a.M * a.nmat);
+        for (int mat = 0; mat < a.nmat; ++mat)
+            for (int r = 0; r < a.M; ++r)
+                bulk_load_1d(xstage + ((size_t)mat * a.M + r) * row_bytes,
+                             reinterpret_cast<const char*>(a.x[mat]) + (int64_t)r * a.ldx * 2, row_bytes, &s.xbar);
+    }
+    for (int st = 0; st < a.stages; ++st) {
+        uint4* b = reinterpret_cast<uint4*>(ring + (size_t)st * stage_bytes + kABytes);
+        for (int i = qt; i < a.NB * kChunk / 16; i += kQThreads) b[i] = make_uint4(0, 0, 0, 0);
+    }
+    if (kpad != a.K)
+        for (int i = qt; i < a.nmat * a.M * kpad / 16; i += kQThreads) reinterpret_cast<uint4*>(cache)[i] = make_uint4(0, 0, 0, 0);
+    const bool ok = mbar_wait(&s.xbar, 0, abort_flag);
+    named_bar_sync(2, kQThreads);
+    if (ok) quantizer_prologue<KIND, DT>(a, s, cache, xstage, kpad, qt);
+    return ok;
+}
+
 template <int KIND, bool SWAP, bool FUSED, int DT>
-__global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcArgs a) {
+__global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const __grid_constant__ TcMaps maps, const TcArgs a) {
     using T = typename Acc<KIND == KIND_F8 ? QT_FP8 : QT_INT8>::T;
     extern __shared__ uint8_t smem_raw[];
     __shared__ TcShared s;
@@ -216,6 +268,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     const uint32_t tmem_cols = a.acc_stride * 2 <= 32 ? 32u : (a.acc_stride * 2 <= 64 ? 64u : (a.acc_stride * 2 <= 128 ? 128u : (a.acc_stride * 2 <= 256 ? 256u : 512u)));
 
     griddep_launch_dependents();
+    if (threadIdx.x == 0) tc_mark(a, 0);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < a.stages; ++i) {
@@ -226,6 +279,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             mbar_init(&s.tfull[i], 1);
             mbar_init(&s.tempty[i], 4);
         }
+        mbar_init(&s.done, 4);
+        mbar_init(&s.xbar, 1);
         s.abort_flag = 0;
         s.last_flag = 0;
         fence_barrier_init();
@@ -240,6 +295,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = s.tmem_base;
+    if (threadIdx.x == 0) tc_mark(a, 1);
     const volatile int* abort_flag = &s.abort_flag;
 
     if (warp == 0) {
@@ -259,8 +315,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     mbar_expect_tx(&s.full[st], FUSED ? kABytes : stage_bytes);
                     tma_load_2d(dst, SWAP ? &maps.w[p.mat] : &maps.a[p.mat], kc * kChunk, p.prow, &s.full[st]);
                     if (!FUSED) tma_load_2d(dst + kABytes, SWAP ? &maps.a[p.mat] : &maps.w[p.mat], kc * kChunk, p.qrow, &s.full[st]);
+                    if (n == 0) tc_mark(a, 2);
                 }
             }
+            tc_mark(a, 10);
             if (!ok) {   // give copies already in flight a bounded time to land before the CTA's memory is released
                 const unsigned long long t0 = global_ns();
                 while (global_ns() - t0 < 2000000ull) {}
@@ -283,6 +341,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                     const int st = n % a.stages;
                     if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
                     tc_fence_after_sync();
+                    if (n == 0) tc_mark(a, 5);
                     const uint32_t sa = smem_u32(ring + (size_t)st * stage_bytes);
                     const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
 #pragma unroll
@@ -293,10 +352,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                 if (ok) tc_commit(&s.tfull[buf]);
                 ++pc;
             }
+            tc_mark(a, 6);
         }
     } else if (warp < 6) {
         // ============================== epilogue ==============================
         griddep_wait();
+        if constexpr (SWAP && FUSED) {
+            if (!fused_prologue<KIND, DT>(a, s, ring, stage_bytes, threadIdx.x - 64, abort_flag)) tc_abort(s, a);
+        }
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
         const int et = (warp - 2) * 32 + lane;          // thread index inside the epilogue group
         const int prow_l = q * 32 + lane;               // row of the A operand held by this thread
@@ -307,6 +370,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             const int buf = pc & 1;
             if (!mbar_wait(&s.tfull[buf], (pc >> 1) & 1, abort_flag)) { tc_abort(s, a); break; }
             tc_fence_after_sync();
+            if (pc == 0 && et == 0) tc_mark(a, 7);
             const uint32_t taddr = tmem_base + (uint32_t)(buf * a.acc_stride) + ((uint32_t)(q * 32) << 16);
             const float wsc = a.ws[p.mat][0];
             if constexpr (SWAP) {
@@ -367,8 +431,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
                         if (n < a.N)
                             for (int m = 0; m < a.M; ++m) {
                                 T sum = 0;
-                                for (int sl = 0; sl < p.nslots; ++sl)
-                                    sum += __ldcg(base + ((int64_t)sl * a.M + m) * kTileP + prow_l);
+                                for (int s0 = 0; s0 < p.nslots; s0 += 8) {       // 8 independent loads in flight
+                                    T v[8];
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j)
+                                        v[j] = s0 + j < p.nslots ? __ldcg(base + ((int64_t)(s0 + j) * a.M + m) * kTileP + prow_l) : T(0);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) sum += v[j];     // CTA order: run-to-run identical
+                                }
                                 finish(sum, m);
                             }
                     }
@@ -428,22 +498,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
             }
             ++pc;
         }
+        if (et == 0) tc_mark(a, 8);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.done);
     } else if (SWAP && FUSED) {
         // ============================== activation quantizer ==============================
         griddep_wait();
-        const int qt = threadIdx.x - 6 * 32, qw = warp - 6;
+        const int qw = warp - 6;
         const int kpad = a.kchunks * kChunk;
-        uint8_t* cache = ring + (size_t)a.stages * stage_bytes;          // [nmat][M][kpad] codes, zero beyond K
-        // rows >= M of every B tile are zero for the whole kernel; so is the cache tail beyond K
-        for (int st = 0; st < a.stages; ++st) {
-            uint4* b = reinterpret_cast<uint4*>(ring + (size_t)st * stage_bytes + kABytes);
-            for (int i = qt; i < a.NB * kChunk / 16; i += 128) b[i] = make_uint4(0, 0, 0, 0);
-        }
-        if (kpad != a.K)
-            for (int i = qt; i < a.nmat * a.M * kpad / 16; i += 128) reinterpret_cast<uint4*>(cache)[i] = make_uint4(0, 0, 0, 0);
-        quantizer_scales<KIND, DT>(a, s, qt);
-        quantize_all<KIND, DT>(a, s, cache, kpad, qt);
-        named_bar_sync(2, 128);
+        const uint8_t* cache = ring + (size_t)a.stages * stage_bytes;
+        if (threadIdx.x == 6 * 32) tc_mark(a, 3);
+        if (!fused_prologue<KIND, DT>(a, s, ring, stage_bytes, threadIdx.x - 64, abort_flag)) tc_abort(s, a);
+        if (threadIdx.x == 6 * 32) tc_mark(a, 4);
         // each of the four warps feeds every fourth ring slot
         PartIter<SWAP> it(a);
         Part p;
@@ -462,9 +529,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemm_tc_kernel(const __grid_con
         }
     }
 
+    __syncwarp();            // single-lane roles: the other lanes wait here for their lane 0
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
+        // the accumulators are released only after every epilogue warp has read its last one
+        if (!mbar_wait(&s.done, 0, abort_flag)) tc_abort(s, a);
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, tmem_cols);
     }
@@ -504,7 +574,8 @@ static int32_t make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t K
 constexpr int64_t kWsCounterInts = 1024;                       // arrival counters (row tiles of all matrices)
 constexpr int64_t kWsHeaderBytes = (kWsCounterInts + 16) * 4;  // counters + status word, then the partial sums
 constexpr size_t kTcSmemBudget = 225 * 1024;
-constexpr size_t kTcCacheMax = 96 * 1024;       // FUSED: all activation codes of a call live in shared memory
+constexpr size_t kTcSmemBudgetHalf = 110 * 1024;   // SWAP: two CTAs per SM, so the next launch can set up early
+constexpr size_t kTcCacheMax = 100 * 1024;      // FUSED: the activations of a call and their codes live in shared memory
 
 static int tc_grid() {
     static const int forced = [] {
@@ -527,7 +598,7 @@ static int32_t launch_tc(const TcMaps& maps, const TcArgs& a, int grid, cudaStre
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget); });
     RWKVQ_REQUIRE(attr_err == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(attr_err));
-    const size_t cache = FUSED ? (size_t)a.nmat * a.M * a.kchunks * kChunk : 0;
+    const size_t cache = FUSED ? (size_t)a.nmat * a.M * ((size_t)a.kchunks * kChunk + (size_t)a.K * 2) : 0;
     const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.NB * kChunk) + cache + 1024;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
@@ -560,7 +631,10 @@ struct TcCall {
     int64_t workspace_bytes;
 };
 
+static unsigned long long* g_trace = nullptr;
+
 static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
+    a.trace = g_trace;
     RWKVQ_REQUIRE(a.M >= 0 && a.N >= 0 && a.K >= 0, RWKVQ_E_SHAPE, "%s: negative size", who);
     RWKVQ_REQUIRE(a.K % 16 == 0, RWKVQ_E_SHAPE, "%s: K=%d must be a multiple of 16", who, a.K);
     RWKVQ_REQUIRE(a.ldo >= a.N, RWKVQ_E_SHAPE, "%s: ldo=%lld < N", who, (long long)a.ldo);
@@ -589,6 +663,7 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
         a.qtiles = 1;
         const int64_t total = (int64_t)a.nmat * a.ptiles * a.kchunks;
         grid = (int)std::min<int64_t>(tc_grid(), total);
+        RWKVQ_REQUIRE(total * grid < (int64_t(1) << 31), RWKVQ_E_SHAPE, "%s: problem too large for the 32-bit tile schedule", who);
         a.max_slots = max_slots_for(total, a.kchunks, grid);
         const int64_t tiles = (int64_t)a.nmat * a.ptiles;
         RWKVQ_REQUIRE(tiles <= kWsCounterInts, RWKVQ_E_SHAPE, "%s: N=%d has too many row tiles for the workspace counters", who, a.N);
@@ -609,10 +684,13 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
     }
     a.acc_stride = std::max(a.NB, 32);
     const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk;
-    const size_t cache_bytes = c.fused ? (size_t)a.nmat * a.M * a.kchunks * kChunk : 0;
+    const size_t cache_bytes = c.fused ? (size_t)a.nmat * a.M * ((size_t)a.kchunks * kChunk + (size_t)a.K * 2) : 0;
     RWKVQ_REQUIRE(cache_bytes <= kTcCacheMax, RWKVQ_E_SHAPE, "%s: %d x %d x %d activation codes do not fit the fused kernel's shared memory",
                   who, a.nmat, a.M, a.K);
-    a.stages = (int)std::min<size_t>(kMaxStages, (kTcSmemBudget - 1024 - cache_bytes) / stage_bytes);
+    const size_t budget = (swap && cache_bytes + 5 * stage_bytes + 1024 <= kTcSmemBudgetHalf && !std::getenv("RWKVQ_TC_ONE_PER_SM"))
+                              ? kTcSmemBudgetHalf : kTcSmemBudget;
+    a.stages = (int)std::min<size_t>(kMaxStages, (budget - 1024 - cache_bytes) / stage_bytes);
+    RWKVQ_REQUIRE(a.stages >= 2, RWKVQ_E_SHAPE, "%s: shared memory leaves fewer than two ring stages", who);
     for (int i = 0; i < a.nmat; ++i) {
         int32_t rc = make_map(&maps.w[i], c.w[i], a.N, a.K, c.ldw, swap ? kTileP : a.NB, who);
         if (rc) return rc;
@@ -636,6 +714,9 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
 using namespace rwkvq;
 
 extern "C" {
+
+/* profiling aid: device buffer of [grid][16] uint64 that every tensor-memory launch stamps with role milestones */
+void rwkvq_tc_set_trace(void* device_buffer) { g_trace = reinterpret_cast<unsigned long long*>(device_buffer); }
 
 int64_t rwkvq_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t nmat) {
     if (M <= 0 || N <= 0 || K <= 0 || nmat <= 0) return kWsHeaderBytes;

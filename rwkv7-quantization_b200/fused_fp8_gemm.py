@@ -32,7 +32,7 @@ USE_CUDA_GRAPH = False  # kept for importers (fused_fp8_gemm.py:941); graphs are
 GEMV_M_MAX = 32
 _GEMV_SMEM_BUDGET = 200 * 1024 - 5 * 1024
 TC_FUSED_M_MAX = 4                 # rows up to which the activation quantization rides inside the streaming kernel
-_TC_CACHE_MAX = 96 * 1024
+_TC_CACHE_MAX = 100 * 1024        # shared memory for the activations (2 B) and their codes (1 B) in the fused kernel
 ROUTE = os.environ.get("RWKVQ_ROUTE", "tc").lower()
 
 
@@ -61,7 +61,7 @@ def _gemv_fits(m: int, k: int) -> bool:
 
 
 def _tc_fused_fits(m: int, k: int, nmat: int = 1) -> bool:
-    return ROUTE == "tc" and 0 < m <= TC_FUSED_M_MAX and k % 16 == 0 and nmat * m * ((k + 127) // 128 * 128) <= _TC_CACHE_MAX
+    return ROUTE == "tc" and 0 < m <= TC_FUSED_M_MAX and k % 16 == 0 and nmat * m * ((k + 127) // 128 * 128 + 2 * k) <= _TC_CACHE_MAX
 
 
 def _finish(out2d: torch.Tensor, lead, n: int, out_dtype):
@@ -246,6 +246,9 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     else:
         outs = []
         for x2, w, info, awq in zip(xs, ws_, (wr_info, wk_info, wv_info), (awq_r, awq_k, None)):
+            if _tc_fused_fits(m, k):                 # three fused launches when one for all three does not fit
+                outs.append(_fp8_gemv(x2.contiguous(), w, info["tensor_scale"], f32(awq), 0))
+                continue
             if awq is not None:                      # AWQ division, then the plain route on the bf16 copy
                 x2, _ = prep_x(x2, awq)
             outs.append(_fp8_codes_gemm(x2, w, info["tensor_scale"], abi.FLAG_QUANT_FROM_BF16))
