@@ -55,9 +55,19 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&p);
 }
-// two fp32 -> two e4m3 bytes (lo in bits 0-7), round-to-nearest-even, saturating
+// two fp32 -> two e4m3 bytes (lo in bits 0-7), round-to-nearest-even, saturating.  One hardware instruction
+// (written as PTX: the cuda_fp8.h helper may pick its software path, hundreds of instructions per pair).
 __device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
-    return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+    unsigned short r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t)r;
+}
+// two e4m3 bytes (bits 0-15) -> two f16 (exact), low byte in the low half
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_codes) {
+    uint32_t r;
+    const unsigned short c = (unsigned short)two_codes;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(c));
+    return r;
 }
 __device__ __forceinline__ float clamp448(float v) { return fminf(fmaxf(v, -448.f), 448.f); }
 

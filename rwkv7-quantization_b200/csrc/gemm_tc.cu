@@ -131,7 +131,7 @@ struct TcShared {
     int last_flag;
     float amax[3];             // FUSED FP8: max(amax, 1e-12) per matrix
     float xs[3][16];           // FUSED INT8: row scales per matrix
-    float red[8];
+    float red[16];             // [0..7] group_max scratch, [8..15] per-warp running maxima
     uint64_t done;             // epilogue warps have read their last accumulator
     uint64_t xbar;             // FUSED: the activation block has landed in shared memory
 };
@@ -160,60 +160,56 @@ __device__ __forceinline__ float group_max(float v, float* red, int qt) {   // m
 // the whole activation block into the compact cache [mat][row][kpad].  Two short loops (amax, then codes) with
 // kQB loads in flight per thread; the second read of x hits L1/L2.  The code is kept small on purpose: it runs
 // once per CTA, and straight-line code that is executed once is paced by instruction fetch, not by the ALUs.
-constexpr int kQB = 4;
 
 template <int KIND, int DT>
 __device__ __noinline__ void quantizer_prologue(const TcArgs& a, TcShared& s, uint8_t* cache, const uint8_t* xstage, int kpad, int qt) {
-    const int kv = a.K >> 3;
+    const int kv = a.K >> 3;                          // 8-element vectors per row
     const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
-    const int rstep = KIND == KIND_F8 ? a.M : 1;      // rows sharing one scale
-    const int nvec = rstep * kv;
     for (int mat = 0; mat < a.nmat; ++mat) {
         const float* awq = KIND == KIND_F8 ? a.awq[mat] : nullptr;
-        for (int r0 = 0; r0 < a.M; r0 += rstep) {
-            const char* xb = reinterpret_cast<const char*>(xstage) + ((size_t)mat * a.M + r0) * a.K * 2;   // staged rows are K apart
-            uint8_t* cb = cache + ((size_t)mat * a.M + r0) * kpad;
-            float m = 0.f;
-#pragma unroll 1
-            for (int b = qt; b < nvec; b += kQThreads * kQB) {
-                uint4 v[kQB];
-                int kk[kQB];
+        const char* xb = reinterpret_cast<const char*>(xstage) + (size_t)mat * a.M * a.K * 2;     // staged rows are K apart
+        uint8_t* cb = cache + (size_t)mat * a.M * kpad;
+        float sc = 0.f;
+        // FP8: one scale for all rows (amax pass over the block, then the code pass); INT8: both passes row by row
+        for (int pass = 0; pass < 2; ++pass) {
+            for (int r = 0; r < a.M; ++r) {
+                const char* xr = xb + (size_t)r * a.K * 2;
+                if (KIND == KIND_F8 ? pass == 0 : true) {
+                    float m = 0.f;
+                    if (KIND == KIND_I8 && pass == 1) continue;
+                    for (int b = qt; b < kv; b += kQThreads) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)b * 16);
+                        if constexpr (KIND == KIND_F8) fp8_vec_amax<DT>(v, awq, b << 3, a.div_mode, after, m);
+                        else m = int8_vec_amax<DT>(v, m);
+                    }
+                    if constexpr (KIND == KIND_F8) {
+                        s.red[8 + (qt >> 5)] = fmaxf(r == 0 ? 0.f : s.red[8 + (qt >> 5)], warp_max(m));   // per-warp running max
+                        if (r + 1 < a.M) continue;
+                        named_bar_sync(2, kQThreads);
+                        m = 0.f;
 #pragma unroll
-                for (int j = 0; j < kQB; ++j) {
-                    const int i = min(b + j * kQThreads, nvec - 1), r = i / kv;
-                    kk[j] = (i - r * kv) << 3;
-                    v[j] = *reinterpret_cast<const uint4*>(xb + ((size_t)r * a.K + kk[j]) * 2);
+                        for (int w = 0; w < 8; ++w) m = fmaxf(m, s.red[8 + w]);
+                        m = fmaxf(m, 1e-12f);
+                        if (qt == 0) s.amax[mat] = m;
+                        sc = div_mode_f32(448.f, m, a.div_mode);
+                        named_bar_sync(2, kQThreads);
+                        continue;
+                    } else {
+                        m = fmaxf(group_max(m, s.red, qt), 1e-12f);
+                        if (qt == 0) s.xs[mat][r] = m;
+                        sc = div_mode_f32(127.f, m, a.div_mode);
+                    }
                 }
-#pragma unroll
-                for (int j = 0; j < kQB; ++j) {
-                    if constexpr (KIND == KIND_F8) fp8_vec_amax<DT>(v[j], awq, kk[j], a.div_mode, after, m);
-                    else m = int8_vec_amax<DT>(v[j], m);
-                }
-            }
-            m = fmaxf(group_max(m, s.red, qt), 1e-12f);
-            if (qt == 0) {
-                if constexpr (KIND == KIND_F8) s.amax[mat] = m; else s.xs[mat][r0] = m;
-            }
-            const float sc = div_mode_f32(KIND == KIND_F8 ? 448.f : 127.f, m, a.div_mode);
-#pragma unroll 1
-            for (int b = qt; b < nvec; b += kQThreads * kQB) {
-                uint4 v[kQB];
-                int kk[kQB], rr[kQB];
-#pragma unroll
-                for (int j = 0; j < kQB; ++j) {
-                    const int i = min(b + j * kQThreads, nvec - 1);
-                    rr[j] = i / kv;
-                    kk[j] = (i - rr[j] * kv) << 3;
-                    v[j] = *reinterpret_cast<const uint4*>(xb + ((size_t)rr[j] * a.K + kk[j]) * 2);
-                }
-#pragma unroll
-                for (int j = 0; j < kQB; ++j) {
+                uint8_t* cr = cb + (size_t)r * kpad;
+                for (int b = qt; b < kv; b += kQThreads) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)b * 16);
                     uint2 c;
-                    if constexpr (KIND == KIND_F8) c = fp8_vec_codes<DT>(v[j], awq, kk[j], a.div_mode, sc);
-                    else c = int8_vec_codes<DT>(v[j], sc);
-                    if (b + j * kQThreads < nvec) *reinterpret_cast<uint2*>(cb + (size_t)rr[j] * kpad + kk[j]) = c;
+                    if constexpr (KIND == KIND_F8) c = fp8_vec_codes<DT>(v, awq, b << 3, a.div_mode, sc);
+                    else c = int8_vec_codes<DT>(v, sc);
+                    *reinterpret_cast<uint2*>(cr + (size_t)b * 8) = c;
                 }
             }
+            if (KIND == KIND_I8) break;
         }
     }
     named_bar_sync(2, kQThreads);

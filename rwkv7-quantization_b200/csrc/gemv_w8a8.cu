@@ -27,7 +27,9 @@
 
 namespace rwkvq {
 
-template <int QT, int DT, int MT, int D>
+// WIDE (FP8 only): activations kept as f16 values and weights widened in registers (m16n8k16.f16) instead of
+// e4m3 codes multiplied by mma.sync.m16n8k32.e4m3.
+template <int QT, int DT, int MT, int D, bool WIDE>
 __global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
     extern __shared__ __align__(16) uint8_t smem[];
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W
             cur_mat = mat;
             __syncthreads();   // nobody still reads the previous matrix's codes
             if constexpr (QT == QT_FP8) {
-                const float amax = quantize_fp8_to_smem<DT>(a, mat, xq, sh);
+                const float amax = quantize_fp8_to_smem<DT, WIDE>(a, mat, xq, sh);
                 out_scale = div_mode_f32(amax, 448.f, a.div_mode) * a.ws[mat][0];
             } else {
                 quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
@@ -102,14 +104,36 @@ __global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W
                 ring[j] = fetch(pf, pfc, j);
                 const int k = koff + (ch * D + j) * (kWarps << 6);
                 const bool kin = k < a.K;
+                if constexpr (QT == QT_FP8 && WIDE) {
+                    // widen the 16 weight bytes to f16 pairs; four m16n8k16 MMAs per 16 bytes
+                    const uint4 w01 = e4m3x8_to_f16x8(make_uint2(wv.x, wv.y)), w23 = e4m3x8_to_f16x8(make_uint2(wv.z, wv.w));
 #pragma unroll
-                for (int i = 0; i < MT; ++i) {
-                    const int r0 = i * 16 + g, r1 = r0 + 8;
-                    uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
-                    if (kin && r0 < a.M) a0 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k);
-                    if (kin && r1 < a.M) a1 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k);
-                    mma8<QT>(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
-                    mma8<QT>(c[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+                    for (int i = 0; i < MT; ++i) {
+                        const int r0 = i * 16 + g, r1 = r0 + 8;
+                        uint4 a00 = make_uint4(0, 0, 0, 0), a01 = a00, a10 = a00, a11 = a00;
+                        if (kin && r0 < a.M) {
+                            a00 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k * 2);
+                            a01 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k * 2 + 16);
+                        }
+                        if (kin && r1 < a.M) {
+                            a10 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k * 2);
+                            a11 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k * 2 + 16);
+                        }
+                        mma_f16(c[i], a00.x, a10.x, a00.y, a10.y, w01.x, w01.y);
+                        mma_f16(c[i], a00.z, a10.z, a00.w, a10.w, w01.z, w01.w);
+                        mma_f16(c[i], a01.x, a11.x, a01.y, a11.y, w23.x, w23.y);
+                        mma_f16(c[i], a01.z, a11.z, a01.w, a11.w, w23.z, w23.w);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < MT; ++i) {
+                        const int r0 = i * 16 + g, r1 = r0 + 8;
+                        uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+                        if (kin && r0 < a.M) a0 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k);
+                        if (kin && r1 < a.M) a1 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k);
+                        mma8<QT>(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
+                        mma8<QT>(c[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+                    }
                 }
             }
         }
@@ -151,6 +175,16 @@ static size_t smem_bytes(int MT, int M, int pitch) {
 
 constexpr size_t kFusedSmemMax = 200 * 1024;
 
+// FP8 weights are widened to f16 in registers by default: measured on B200, mma.sync.m16n8k32.e4m3 is slower than
+// cvt.f16x2.e4m3x2 + m16n8k16.f16 for this HBM-bound loop.  RWKVQ_F8_MMA=native selects the e4m3 instruction.
+static bool fp8_wide() {
+    static const bool on = [] {
+        const char* e = std::getenv("RWKVQ_F8_MMA");
+        return !(e && e[0] == 'n');
+    }();
+    return on;
+}
+
 static bool use_pdl() {
     static const bool on = [] {
         const char* e = std::getenv("RWKVQ_PDL");
@@ -159,9 +193,9 @@ static bool use_pdl() {
     return on;
 }
 
-template <int QT, int DT, int MT, int D>
+template <int QT, int DT, int MT, int D, bool WIDE>
 static int32_t launch_one(const W8Args& a, int64_t tiles, size_t smem, cudaStream_t st) {
-    auto kern = gemv_w8a8_kernel<QT, DT, MT, D>;
+    auto kern = gemv_w8a8_kernel<QT, DT, MT, D, WIDE>;
     // per instantiation and device: opt in to large dynamic shared memory and ask how many CTAs fit on an SM
     static thread_local int cfg_dev = -1;
     static thread_local size_t cfg_smem = ~size_t(0);
@@ -201,8 +235,12 @@ template <int QT, int DT>
 static int32_t dispatch_mt(const W8Args& a, int64_t tiles, size_t smem, cudaStream_t st) {
     const int units = (a.K + 63) / 64;
     const bool deep = units > 4 * kWarps;          // more than 4 units per warp and tile: keep 8 loads in flight
-    if (a.M <= 16) return deep ? launch_one<QT, DT, 1, 8>(a, tiles, smem, st) : launch_one<QT, DT, 1, 4>(a, tiles, smem, st);
-    return deep ? launch_one<QT, DT, 2, 8>(a, tiles, smem, st) : launch_one<QT, DT, 2, 4>(a, tiles, smem, st);
+    if (QT == QT_FP8 && fp8_wide()) {
+        if (a.M <= 16) return deep ? launch_one<QT, DT, 1, 8, true>(a, tiles, smem, st) : launch_one<QT, DT, 1, 4, true>(a, tiles, smem, st);
+        return deep ? launch_one<QT, DT, 2, 8, true>(a, tiles, smem, st) : launch_one<QT, DT, 2, 4, true>(a, tiles, smem, st);
+    }
+    if (a.M <= 16) return deep ? launch_one<QT, DT, 1, 8, false>(a, tiles, smem, st) : launch_one<QT, DT, 1, 4, false>(a, tiles, smem, st);
+    return deep ? launch_one<QT, DT, 2, 8, false>(a, tiles, smem, st) : launch_one<QT, DT, 2, 4, false>(a, tiles, smem, st);
 }
 
 template <int QT>
@@ -222,7 +260,9 @@ static int32_t run_fused(W8Args a, int x_dtype, cudaStream_t st, const char* who
     if (a.M == 0 || a.N == 0) return RWKVQ_OK;
     RWKVQ_REQUIRE(a.K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
     const int MT = a.M <= 16 ? 1 : 2;
-    a.pitch = ((a.K + 127) / 128) * 128 + 64;
+    // shared-memory row pitch of the activation tile: int8 codes (1 B) or f16 values of the e4m3 codes (2 B);
+    // the odd 64 / 16 bytes keep the fragment loads of different rows on different banks
+    a.pitch = (QT == QT_FP8 && fp8_wide()) ? ((2 * a.K + 127) / 128) * 128 + 16 : ((a.K + 127) / 128) * 128 + 64;
     const size_t smem = smem_bytes(MT, a.M, a.pitch);
     RWKVQ_REQUIRE(smem <= kFusedSmemMax, RWKVQ_E_SHAPE, "%s: M*K = %d*%d does not fit the fused kernel's shared memory", who, a.M, a.K);
     const int64_t tiles = (int64_t)a.nmat * ((a.N + 7) / 8);

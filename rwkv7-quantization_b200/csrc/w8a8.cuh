@@ -47,6 +47,11 @@ __device__ __forceinline__ void mma_s8(int32_t (&c)[4], uint32_t a0, uint32_t a1
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 template <int QT, typename T>
 __device__ __forceinline__ void mma8(T (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     if constexpr (QT == QT_FP8) mma_e4m3(c, a0, a1, a2, a3, b0, b1);
@@ -67,8 +72,29 @@ __device__ __forceinline__ float cta_max(float v, float* sh) {
 // ---- fused prologue, FP8: per-call amax then e4m3 codes into shared memory; returns max(amax, 1e-12).
 // Up to 4 vectors of 8 activations per thread stay in registers between the two phases (M*K <= 8192, i.e. the
 // M = 1 and M = 2 decode cases at K = 4096); larger calls read x a second time (L1/L2 hits).
+// ---- per-vector helpers (8 activations = one uint4).  They are written for instruction count: every CTA of the
+// decode kernels quantizes the whole activation block itself, so these few lines are executed by all SMs.
+
+// |x| maximum of 8 packed 16-bit values, exact, with packed abs/max (two values per instruction)
+template <int DT>
+__device__ __forceinline__ float packed_absmax8(const uint4& v) {
+    if constexpr (DT == RWKVQ_F16) {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+        const __half2 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+        return fmaxf(__low2float(m), __high2float(m));
+    } else {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const __nv_bfloat162 m = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+        return fmaxf(__low2float(m), __high2float(m));
+    }
+}
+
 template <int DT>
 __device__ __forceinline__ void fp8_vec_amax(const uint4& v, const float* awq, int k, int div_mode, bool after, float& m) {
+    if (awq == nullptr && !(DT == RWKVQ_F16 && after)) {      // the common case: max over the raw 16-bit values
+        m = fmaxf(m, packed_absmax8<DT>(v));
+        return;
+    }
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -81,6 +107,7 @@ __device__ __forceinline__ void fp8_vec_amax(const uint4& v, const float* awq, i
         m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
     }
 }
+// codes = e4m3_rn_sat(bf16(x [/ awq]) * inv): the saturating conversion is the clamp to +-448
 template <int DT>
 __device__ __forceinline__ uint2 fp8_vec_codes(const uint4& v, const float* awq, int k, int div_mode, float inv) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -92,12 +119,22 @@ __device__ __forceinline__ uint2 fp8_vec_codes(const uint4& v, const float* awq,
             f.x = div_mode_f32(f.x, awq[k + 2 * q], div_mode);
             f.y = div_mode_f32(f.y, awq[k + 2 * q + 1], div_mode);
         }
-        c[q] = e4m3x2(clamp448(bf16_round(f.x) * inv), clamp448(bf16_round(f.y) * inv));
+        if (DT == RWKVQ_F16 || awq) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }   // bf16 input is its own rounding
+        c[q] = e4m3x2(f.x * inv, f.y * inv);
     }
     return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
 }
 
-template <int DT>
+// 8 e4m3 codes (uint2) -> the same 8 values as f16 (exact: every e4m3 value is an f16 value)
+__device__ __forceinline__ uint4 e4m3x8_to_f16x8(uint2 c) {
+    return make_uint4(e4m3x2_to_f16x2(c.x & 0xffffu), e4m3x2_to_f16x2(c.x >> 16), e4m3x2_to_f16x2(c.y & 0xffffu),
+                      e4m3x2_to_f16x2(c.y >> 16));
+}
+
+// The decode GEMV keeps the quantized FP8 activations as f16 VALUES in shared memory (2 bytes per element): on sm_100
+// mma.sync has no fast e4m3 path, so weights are widened to f16 in registers and multiplied with m16n8k16.f16
+// (products of two e4m3 values and their fp32 sums are exact).
+template <int DT, bool WIDE>
 __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh) {
     const char* x = reinterpret_cast<const char*>(a.x[mat]);
     const float* awq = a.awq[mat];
@@ -125,21 +162,43 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
         const float inv = div_mode_f32(448.f, amax, a.div_mode);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            if (rr[j] >= 0)
-                *reinterpret_cast<uint2*>(xq + (size_t)rr[j] * a.pitch + kk[j]) = fp8_vec_codes<DT>(v[j], awq, kk[j], a.div_mode, inv);
+            if (rr[j] >= 0) {
+                const uint2 c = fp8_vec_codes<DT>(v[j], awq, kk[j], a.div_mode, inv);
+                if constexpr (WIDE) *reinterpret_cast<uint4*>(xq + (size_t)rr[j] * a.pitch + kk[j] * 2) = e4m3x8_to_f16x8(c);
+                else *reinterpret_cast<uint2*>(xq + (size_t)rr[j] * a.pitch + kk[j]) = c;
+            }
         return amax;
     }
-    for (int i = threadIdx.x; i < nvec; i += kThr) {
-        const int r = i / kv, k = (i - r * kv) << 3;
-        const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
-        fp8_vec_amax<DT>(v, awq, k, a.div_mode, after, m);
+    // larger blocks: row by row, four independent loads in flight per thread, no integer division
+    for (int r = 0; r < a.M; ++r) {
+        const char* xr = x + (int64_t)r * a.ldx * 2;
+        for (int b = threadIdx.x; b < kv; b += 4 * kThr) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const uint4*>(xr + (size_t)min(b + j * kThr, kv - 1) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) fp8_vec_amax<DT>(v[j], awq, min(b + j * kThr, kv - 1) << 3, a.div_mode, after, m);
+        }
     }
     const float amax = fmaxf(cta_max(m, sh), 1e-12f);
     const float inv = div_mode_f32(448.f, amax, a.div_mode);
-    for (int i = threadIdx.x; i < nvec; i += kThr) {
-        const int r = i / kv, k = (i - r * kv) << 3;
-        const uint4 v = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + k) * 2);
-        *reinterpret_cast<uint2*>(xq + (size_t)r * a.pitch + k) = fp8_vec_codes<DT>(v, awq, k, a.div_mode, inv);
+    for (int r = 0; r < a.M; ++r) {
+        const char* xr = x + (int64_t)r * a.ldx * 2;
+        uint8_t* qr = xq + (size_t)r * a.pitch;
+        for (int b = threadIdx.x; b < kv; b += 4 * kThr) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const uint4*>(xr + (size_t)min(b + j * kThr, kv - 1) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int kvi = b + j * kThr;
+                if (kvi < kv) {
+                    const uint2 c = fp8_vec_codes<DT>(v[j], awq, kvi << 3, a.div_mode, inv);
+                    if constexpr (WIDE) *reinterpret_cast<uint4*>(qr + (size_t)kvi * 16) = e4m3x8_to_f16x8(c);
+                    else *reinterpret_cast<uint2*>(qr + (size_t)kvi * 8) = c;
+                }
+            }
+        }
     }
     return amax;
 }
@@ -148,26 +207,20 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
 // Few rows (M <= 4): the whole CTA works on one row at a time; more rows: one warp per row.
 template <int DT>
 __device__ __forceinline__ float int8_vec_amax(const uint4& v, float m) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float2 f = cvt2<DT>(w[q]);
-        m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
-    }
-    return m;
+    return fmaxf(m, packed_absmax8<DT>(v));
+}
+// codes = trunc(clamp(x * s, -128, 127)): truncating float->int conversion, then a saturating pack to int8
+__device__ __forceinline__ uint32_t pack_s8x4(int a0, int a1, int a2, int a3) {
+    uint32_t hi, r;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(a3), "r"(a2), "r"(0));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a1), "r"(a0), "r"(hi));
+    return r;
 }
 template <int DT>
 __device__ __forceinline__ uint2 int8_vec_codes(const uint4& v, float s) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t c[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float2 f = cvt2<DT>(w[q]);
-        const uint32_t lo = (uint32_t)__float2int_rz(fminf(fmaxf(f.x * s, -128.f), 127.f)) & 0xffu;
-        const uint32_t hi = (uint32_t)__float2int_rz(fminf(fmaxf(f.y * s, -128.f), 127.f)) & 0xffu;
-        c[q] = lo | (hi << 8);
-    }
-    return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+    const float2 f0 = cvt2<DT>(v.x), f1 = cvt2<DT>(v.y), f2 = cvt2<DT>(v.z), f3 = cvt2<DT>(v.w);
+    return make_uint2(pack_s8x4(__float2int_rz(f0.x * s), __float2int_rz(f0.y * s), __float2int_rz(f1.x * s), __float2int_rz(f1.y * s)),
+                      pack_s8x4(__float2int_rz(f2.x * s), __float2int_rz(f2.y * s), __float2int_rz(f3.x * s), __float2int_rz(f3.y * s)));
 }
 
 template <int DT>

@@ -10,12 +10,15 @@ Outputs are freshly allocated tensors owned by the caller; weights are borrowed;
 CUDA stream without host synchronisation -- the conventions of the reference wrappers
 (fused_fp8_gemm.py:55-79, 645-679, 785-818, 944-1098).
 
-Routing by M = rows of the flattened activation (tensor-memory kernels: TMA -> tcgen05.mma):
-    M <= 4      one fused launch: activation quantization by dedicated warps of the weight-streaming kernel
-    M <= 128    activation-quantization kernels, then the weight-streaming kernel on the codes
-    larger M    activation-quantization kernels, then the 128 x 256 tile prefill GEMM
-RWKVQ_ROUTE=mma selects the register-streaming mma.sync kernels instead (M <= 32 fused, codes GEMM above);
-they compute the same results and serve as the cross-check of the tensor-memory path.
+Routing by M = rows of the flattened activation:
+    M <= 8      ONE fused launch of the register-streaming GEMV (activation quantization in its prologue, weights
+                streamed once from HBM into mma.sync fragments) -- the decode path
+    M <= 128    activation-quantization kernels, then the tensor-memory weight-streaming kernel
+                (TMA -> tcgen05.mma, weights as the 128-row operand, stream-K over the SMs) on the codes
+    larger M    activation-quantization kernels, then the 128 x 256 tile tcgen05 prefill GEMM
+RWKVQ_ROUTE=tc  sends M <= 4 to the tensor-memory kernel with the quantization fused into it as well;
+RWKVQ_ROUTE=mma keeps everything on the mma.sync kernels (M <= 32 fused, codes GEMM above).  All routes compute the
+same results (INT8 bit for bit) and cross-check each other in the tests.
 """
 from __future__ import annotations
 
@@ -33,7 +36,8 @@ GEMV_M_MAX = 32
 _GEMV_SMEM_BUDGET = 200 * 1024 - 5 * 1024
 TC_FUSED_M_MAX = 4                 # rows up to which the activation quantization rides inside the streaming kernel
 _TC_CACHE_MAX = 100 * 1024        # shared memory for the activations (2 B) and their codes (1 B) in the fused kernel
-ROUTE = os.environ.get("RWKVQ_ROUTE", "tc").lower()
+ROUTE = os.environ.get("RWKVQ_ROUTE", "auto").lower()   # auto | tc | mma
+GEMV_AUTO_M_MAX = 8
 
 
 # --------------------------------------------------------------------------- helpers
@@ -55,9 +59,12 @@ def _unpack(weight_info_or_w, res_scale=None):
     return weight_info_or_w, res_scale
 
 
-def _gemv_fits(m: int, k: int) -> bool:
-    pitch = (k + 127) // 128 * 128 + 64
-    return 0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0
+def _gemv_fits(m: int, k: int, fp8: bool = True) -> bool:
+    """The fused mma.sync GEMV keeps the quantized activations in shared memory (FP8: 2 bytes each, INT8: 1)."""
+    pitch = (2 * k + 127) // 128 * 128 + 16 if fp8 else (k + 127) // 128 * 128 + 64
+    if not (0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0):
+        return False
+    return ROUTE == "mma" or (ROUTE == "auto" and m <= GEMV_AUTO_M_MAX)
 
 
 def _tc_fused_fits(m: int, k: int, nmat: int = 1) -> bool:
@@ -137,8 +144,10 @@ def prep3_x_int8(xr, xk, xv):
 def _cfg_for(M, N=None, K=None):
     """(rows of activations, weight rows, K bytes per step, warps) of the kernel a shape is routed to."""
     if K is not None and _gemv_fits(M, K):
-        return (16 if M <= 16 else 32, 8, 64, 8)
-    return (32, 8, 64, 8)
+        return (16 if M <= 16 else 32, 8, 64, 8)       # mma.sync GEMV: 8 weight rows per CTA, 8 warps split K
+    if M <= 128:
+        return (16 if M <= 16 else 128, 128, 128, 10)  # tcgen05, weights as the 128-row operand
+    return (128, 256, 128, 10)                         # tcgen05 prefill tile
 
 
 def _cfg_for_rkv(M, N=None, K=None):
@@ -147,7 +156,7 @@ def _cfg_for_rkv(M, N=None, K=None):
 
 
 def _best_method(M, N, K):
-    return "gemv_fused" if _gemv_fits(M, K) else "actq+gemm"
+    return "gemv_fused" if _gemv_fits(M, K) else ("actq+tcgen05_stream" if M <= 128 else "actq+tcgen05_gemm")
 
 
 # --------------------------------------------------------------------------- FP8
@@ -177,7 +186,7 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     st = abi.stream_ptr()
     abi.call("rwkvq_actq_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
              codes.data_ptr(), k, amax.data_ptr(), None, abi.DEFAULT_DIV, act_flags, st)
-    if ROUTE == "tc":
+    if ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
                  w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(), st)
@@ -204,7 +213,7 @@ def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float1
     if m == 1:
         return linear_fp8_m1_fused(x, {"weight": w, "tensor_scale": w_ts}, out_dtype)
     x2 = _rows16(x)
-    if _tc_fused_fits(m, k) or (ROUTE != "tc" and _gemv_fits(m, k)):
+    if _tc_fused_fits(m, k) or _gemv_fits(m, k):
         out = _fp8_gemv(x2, _u8(w), w_ts, None, 0)
     else:
         out = _fp8_codes_gemm(x2, _u8(w), w_ts, abi.FLAG_QUANT_FROM_BF16)
@@ -234,7 +243,7 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
                  wr_info["tensor_scale"].data_ptr(), wk_info["tensor_scale"].data_ptr(),
                  wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
                  m, n, k, k, abi.DEFAULT_DIV, 0, ws.data_ptr(), ws.numel(), abi.stream_ptr())
-    elif ROUTE != "tc" and _gemv_fits(m, k) and same_ld:
+    elif _gemv_fits(m, k) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
         awq_r, awq_k = f32(awq_r), f32(awq_k)
@@ -246,7 +255,7 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     else:
         outs = []
         for x2, w, info, awq in zip(xs, ws_, (wr_info, wk_info, wv_info), (awq_r, awq_k, None)):
-            if _tc_fused_fits(m, k):                 # three fused launches when one for all three does not fit
+            if _tc_fused_fits(m, k) or _gemv_fits(m, k):   # three fused launches when one for all three does not fit
                 outs.append(_fp8_gemv(x2.contiguous(), w, info["tensor_scale"], f32(awq), 0))
                 continue
             if awq is not None:                      # AWQ division, then the plain route on the bf16 copy
@@ -266,7 +275,7 @@ def _int8_any(x2, w, w_scale, acc_out=None):
         abi.call("rwkvq_tc_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
                  out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0,
                  ws.data_ptr(), ws.numel(), st)
-    elif ROUTE != "tc" and _gemv_fits(m, k):
+    elif _gemv_fits(m, k, fp8=False):
         abi.call("rwkvq_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
                  out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0, st)
     else:
@@ -274,7 +283,7 @@ def _int8_any(x2, w, w_scale, acc_out=None):
         xs = torch.empty(m, dtype=torch.float32, device=x2.device)
         abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
                  codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
-        if ROUTE == "tc":
+        if ROUTE != "mma":
             ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
             abi.call("rwkvq_tc_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0),
                      w_scale.data_ptr(), out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, ws.data_ptr(), ws.numel(), st)
@@ -313,7 +322,7 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
                  ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0), scales[0].data_ptr(),
                  scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(),
                  outs[2].data_ptr(), n, m, n, k, k, abi.DEFAULT_DIV, 0, wsp.data_ptr(), wsp.numel(), abi.stream_ptr())
-    elif ROUTE != "tc" and _gemv_fits(m, k) and same_ld:
+    elif _gemv_fits(m, k, fp8=False) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=xs[0].device) for _ in range(3)]
         abi.call("rwkvq_gemv_int8_rkv", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]),
