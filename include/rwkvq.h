@@ -192,6 +192,45 @@ int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_sc
                            int64_t M, int64_t N, int64_t K, uint32_t flags, void* workspace, int64_t workspace_bytes,
                            void* stream);
 
+/* ---------------------------------------------------------------- weight-only INT4 / INT8 GEMV (fp16 activations, M <= 16)
+ *
+ * Layouts are the ones int4/quantize_int4.py and int8/quantize_int8.py of the reference write: packed nibbles
+ * [N, K/2] with the even k in the low nibble; fp32 scales / zeros [N, K/group]; MM4 / MM8 vectors mx, rx [K] and
+ * my, ry [N].  x is fp16 [M, ldx]; results fp16 [M, ldo] with fp32 accumulation (what the reference's GEMV kernels
+ * are written to compute, int4/fused_int4_gemm.py:27-171, int8/fused_int8_gemm.py:32-103). */
+
+/* _int4_gemv_kernel / linear_int4_per_tensor (int4/fused_int4_gemm.py:27-69, int4/int4_ops.py:79-101):
+ * signed nibble * scale[0]. */
+int32_t rwkvq_gemv_int4_tensor(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw, const float* scale,
+                               void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream);
+/* _int4_affine_gemv_kernel / linear_int4_affine (int4/fused_int4_gemm.py:72-117, int4/int4_ops.py:104-130):
+ * w = (u4 + 0.5) * ry[n] * rx[k] * 16 + my[n] + mx[k]. */
+int32_t rwkvq_gemv_int4_affine(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw, const float* mx,
+                               const float* rx, const float* my, const float* ry, void* out_f16, int64_t ldo, int64_t M,
+                               int64_t N, int64_t K, void* stream);
+/* _int4_groupwise_gemv_kernel / linear_int4_groupwise (int4/fused_int4_gemm.py:120-171, int4/int4_ops.py:133-157):
+ * w = u4 * scale[n, k/group] + zero[n, k/group]; scales fp32 or fp16 (scale_is_f16), zeros fp32 or NULL
+ * (symmetric: zero = -8 * scale).  Any group size that divides K; one warp per output row. */
+int32_t rwkvq_gemv_int4_group_generic(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw,
+                                      const void* scales, const float* zeros, int32_t scale_is_f16, int32_t group,
+                                      void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream);
+/* _int8_gemv_kernel / linear_int8_per_tensor (int8/fused_int8_gemm.py:32-61, int8/int8_ops.py:48-78). */
+int32_t rwkvq_gemv_int8_w8a16(const void* x_f16, int64_t ldx, const int8_t* w, int64_t ldw, const float* scale,
+                              void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream);
+/* _int8_affine_gemv_kernel / linear_int8_affine (int8/fused_int8_gemm.py:64-103, int8/int8_ops.py:81-110):
+ * w = (u8 + 0.5) * ry[n] * rx[k] * 256 + my[n] + mx[k]. */
+int32_t rwkvq_gemv_int8_affine(const void* x_f16, int64_t ldx, const uint8_t* w_u8, int64_t ldw, const float* mx,
+                               const float* rx, const float* my, const float* ry, void* out_f16, int64_t ldo, int64_t M,
+                               int64_t N, int64_t K, void* stream);
+
+/* The group-wise INT4 decode kernel (same reference lines as rwkvq_gemv_int4_group_generic): group 128 or 256, K a
+ * multiple of 128, M <= 16, activations staged in shared memory (rwkvq_gemv_int4_group_smem_bytes() <= 200 KiB),
+ * weights streamed once into mma.sync.m16n8k16.f16 fragments. */
+int64_t rwkvq_gemv_int4_group_smem_bytes(int64_t M, int64_t K);
+int32_t rwkvq_gemv_int4_group(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw, const void* scales,
+                              const float* zeros, int32_t scale_is_f16, int32_t group, void* out_f16, int64_t ldo,
+                              int64_t M, int64_t N, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,52 @@
 
 namespace rwkvq {
 
+// One chunk of the K loop: D ring slots are consumed and refilled.  The unrolled body touches memory only through
+// base pointers plus compile-time offsets (slot j lies 512*j bytes after slot 0 in the weight row and in the
+// activation tile), so a slot costs a handful of instructions.  PF: a next chunk exists and is prefetched;
+// CHECK: K is not a multiple of the chunk span, so every slot is tested against K.
+template <int QT, int MT, int D, bool WIDE, bool PF, bool CHECK, typename T>
+__device__ __forceinline__ void chunk_body(uint4 (&ring)[D], T (&c)[MT][4], T (&c2)[MT][4], const uint8_t* pf, int pfk, int k0, int K,
+                                           const uint8_t* const (&xr)[MT][2]) {
+    constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;        // bytes per activation in the shared-memory tile
+#pragma unroll
+    for (int j = 0; j < D; ++j) {
+        const uint4 wv = ring[j];
+        if (PF && (!CHECK || pfk + j * 512 < K)) ring[j] = ldg_stream(pf + j * 512);
+        else ring[j] = make_uint4(0, 0, 0, 0);
+        const bool kin = !CHECK || (k0 + j * 512 < K);
+        if constexpr (QT == QT_FP8 && WIDE) {
+            // widen the 16 weight bytes to f16 pairs; four m16n8k16 MMAs per 16 bytes on two accumulators
+            const uint4 w01 = e4m3x8_to_f16x8(make_uint2(wv.x, wv.y)), w23 = e4m3x8_to_f16x8(make_uint2(wv.z, wv.w));
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                uint4 a00 = make_uint4(0, 0, 0, 0), a01 = a00, a10 = a00, a11 = a00;
+                if (kin && xr[i][0]) {
+                    a00 = *reinterpret_cast<const uint4*>(xr[i][0] + j * 512 * AB);
+                    a01 = *reinterpret_cast<const uint4*>(xr[i][0] + j * 512 * AB + 16);
+                }
+                if (kin && xr[i][1]) {
+                    a10 = *reinterpret_cast<const uint4*>(xr[i][1] + j * 512 * AB);
+                    a11 = *reinterpret_cast<const uint4*>(xr[i][1] + j * 512 * AB + 16);
+                }
+                mma_f16(c[i], a00.x, a10.x, a00.y, a10.y, w01.x, w01.y);
+                mma_f16(c[i], a00.z, a10.z, a00.w, a10.w, w01.z, w01.w);
+                mma_f16(c2[i], a01.x, a11.x, a01.y, a11.y, w23.x, w23.y);
+                mma_f16(c2[i], a01.z, a11.z, a01.w, a11.w, w23.z, w23.w);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+                if (kin && xr[i][0]) a0 = *reinterpret_cast<const uint4*>(xr[i][0] + j * 512);
+                if (kin && xr[i][1]) a1 = *reinterpret_cast<const uint4*>(xr[i][1] + j * 512);
+                mma8<QT>(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
+                mma8<QT>(c2[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+            }
+        }
+    }
+}
+
 // WIDE (FP8 only): activations kept as f16 values and weights widened in registers (m16n8k16.f16) instead of
 // e4m3 codes multiplied by mma.sync.m16n8k32.e4m3.
 template <int QT, int DT, int MT, int D, bool WIDE>
@@ -88,56 +134,44 @@ __global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W
         }
         const uint8_t* nxt = tile + 1 < te ? tile_base(tile + 1) : nullptr;
 
-        T c[MT][4];
+        T c[MT][4], c2[MT][4];
 #pragma unroll
         for (int i = 0; i < MT; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) c[i][j] = 0;
+            for (int j = 0; j < 4; ++j) c[i][j] = c2[i][j] = 0;
 
+        // this lane's rows of the activation tile (rows g and g+8 of each 16-row block); null = row beyond M
+        constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;
+        const uint8_t* xr[MT][2];
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+            xr[i][0] = i * 16 + g < a.M ? xq + (size_t)(i * 16 + g) * a.pitch + (size_t)koff * AB : nullptr;
+            xr[i][1] = i * 16 + g + 8 < a.M ? xq + (size_t)(i * 16 + g + 8) * a.pitch + (size_t)koff * AB : nullptr;
+        }
+        const bool check = (a.K % (D * 512)) != 0;
         for (int ch = 0; ch < nchunks; ++ch) {
             const bool last = ch + 1 == nchunks;
-            const uint8_t* pf = last ? nxt : cur;
-            const int pfc = last ? 0 : ch + 1;
+            const uint8_t* pf = last ? nxt : cur + (ch + 1) * D * 512;
+            const int pfk = koff + (last ? 0 : (ch + 1) * D * 512), k0 = koff + ch * D * 512;
+            const uint8_t* xc[MT][2];
 #pragma unroll
-            for (int j = 0; j < D; ++j) {
-                const uint4 wv = ring[j];
-                ring[j] = fetch(pf, pfc, j);
-                const int k = koff + (ch * D + j) * (kWarps << 6);
-                const bool kin = k < a.K;
-                if constexpr (QT == QT_FP8 && WIDE) {
-                    // widen the 16 weight bytes to f16 pairs; four m16n8k16 MMAs per 16 bytes
-                    const uint4 w01 = e4m3x8_to_f16x8(make_uint2(wv.x, wv.y)), w23 = e4m3x8_to_f16x8(make_uint2(wv.z, wv.w));
-#pragma unroll
-                    for (int i = 0; i < MT; ++i) {
-                        const int r0 = i * 16 + g, r1 = r0 + 8;
-                        uint4 a00 = make_uint4(0, 0, 0, 0), a01 = a00, a10 = a00, a11 = a00;
-                        if (kin && r0 < a.M) {
-                            a00 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k * 2);
-                            a01 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k * 2 + 16);
-                        }
-                        if (kin && r1 < a.M) {
-                            a10 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k * 2);
-                            a11 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k * 2 + 16);
-                        }
-                        mma_f16(c[i], a00.x, a10.x, a00.y, a10.y, w01.x, w01.y);
-                        mma_f16(c[i], a00.z, a10.z, a00.w, a10.w, w01.z, w01.w);
-                        mma_f16(c[i], a01.x, a11.x, a01.y, a11.y, w23.x, w23.y);
-                        mma_f16(c[i], a01.z, a11.z, a01.w, a11.w, w23.z, w23.w);
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < MT; ++i) {
-                        const int r0 = i * 16 + g, r1 = r0 + 8;
-                        uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
-                        if (kin && r0 < a.M) a0 = *reinterpret_cast<const uint4*>(xq + (size_t)r0 * a.pitch + k);
-                        if (kin && r1 < a.M) a1 = *reinterpret_cast<const uint4*>(xq + (size_t)r1 * a.pitch + k);
-                        mma8<QT>(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
-                        mma8<QT>(c[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
-                    }
-                }
+            for (int i = 0; i < MT; ++i) {
+                xc[i][0] = xr[i][0] ? xr[i][0] + (size_t)ch * D * 512 * AB : nullptr;
+                xc[i][1] = xr[i][1] ? xr[i][1] + (size_t)ch * D * 512 * AB : nullptr;
+            }
+            if (check) {
+                if (pf) chunk_body<QT, MT, D, WIDE, true, true>(ring, c, c2, pf, pfk, k0, a.K, xc);
+                else chunk_body<QT, MT, D, WIDE, false, true>(ring, c, c2, pf, pfk, k0, a.K, xc);
+            } else {
+                if (pf) chunk_body<QT, MT, D, WIDE, true, false>(ring, c, c2, pf, pfk, k0, a.K, xc);
+                else chunk_body<QT, MT, D, WIDE, false, false>(ring, c, c2, pf, pfk, k0, a.K, xc);
             }
         }
         cur = nxt;
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) c[i][j] += c2[i][j];      // the two accumulators halve the dependent MMA chains
 
         // split-K reduction across the 8 warps, fixed order
 #pragma unroll

@@ -1,0 +1,149 @@
+"""GPU parity of the weight-only INT4 / INT8 GEMVs (stand-alone int4/ and int8/ tools) against the CPU oracle and
+the golden outputs of the reference's own CPU dequant-matmul route.  Bar: max-rel-err <= 1e-2 on fp16 outputs, an
+element's error measured against max(|ref|, 0.02*rms(ref))."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import rwkvq_oracle as O
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def gen(seed, shape, std=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+def rel_err(out, ref):
+    out, ref = out.detach().cpu().float(), ref.detach().cpu().float()
+    floor = 0.02 * ref.pow(2).mean().sqrt().item() + 1e-30
+    return ((out - ref).abs() / ref.abs().clamp(min=floor)).max().item()
+
+
+def dev(info):
+    return {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in info.items()}
+
+
+@pytest.fixture(scope="module")
+def mods():
+    import rwkvq_abi as abi
+    abi.require_device()
+    from int4 import int4_ops, fused_int4_gemm, quantize_int4
+    from int8 import int8_ops, fused_int8_gemm, quantize_int8
+    return int4_ops, fused_int4_gemm, quantize_int4, int8_ops, fused_int8_gemm, quantize_int8
+
+
+# BASELINE config 3: 7.2B shapes, group 128, B in {1, 4, 16}
+@pytest.mark.parametrize("n,k", [(4096, 4096), (16384, 4096), (4096, 16384)])
+def test_int4_groupwise_7b_shapes(mods, n, k):
+    i4, f4, q4 = mods[0], mods[1], mods[2]
+    w = gen(n + k, (n, k), (1.0 / k) ** 0.5)
+    info = q4.quantize_to_int4_groupwise(w, 128)
+    info["qtype"] = "int4_groupwise"
+    wdq = O.dequant_int4_groupwise(info)
+    d = dev(info)
+    for b in (1, 4, 16):
+        x = gen(b, (b, k), 1.0, torch.float16)
+        out = i4.linear_int4(x.cuda(), d)
+        assert out.shape == (b, n) and out.dtype == torch.float16
+        assert rel_err(out, O.linear_w4a16_kernel_semantics(x, wdq)) <= 1e-2
+    # single-vector form of the reference's GEMV entry point
+    x1 = gen(99, (k,), 1.0, torch.float16)
+    y = f4.linear_int4_groupwise_gemv_triton(x1.cuda(), d["packed"], d["scales"], d["zeros"], 128)
+    assert y.shape == (n,)
+    assert rel_err(y, O.linear_w4a16_kernel_semantics(x1.reshape(1, -1), wdq).reshape(-1)) <= 1e-2
+
+
+@pytest.mark.parametrize("group", [128, 256, 64, 32])
+@pytest.mark.parametrize("m", [1, 3, 16, 20])
+def test_int4_groupwise_variants(mods, group, m, monkeypatch):
+    i4, _, q4 = mods[0], mods[1], mods[2]
+    n, k = 200, 768
+    w = gen(group + m, (n, k), 0.05)
+    info = q4.quantize_to_int4_groupwise(w, group)
+    info["qtype"] = "int4_groupwise"
+    x = gen(m, (2, m, k) if m == 3 else (m, k), 1.0, torch.float16)
+    want = O.linear_w4a16_kernel_semantics(x, O.dequant_int4_groupwise(info))
+    assert rel_err(i4.linear_int4(x.cuda(), dev(info)), want) <= 1e-2
+    # fast kernel and general kernel agree
+    monkeypatch.setenv("RWKVQ_INT4", "generic")
+    assert rel_err(i4.linear_int4(x.cuda(), dev(info)), want) <= 1e-2
+    # symmetric form: fp16 scales, no zeros (zero = -8 * scale)
+    sym = {"packed": info["packed"], "scales": info["scales"].half(), "group_size": group, "qtype": "int4_groupwise"}
+    full = dict(sym, scales=sym["scales"].float(), zeros=-8.0 * sym["scales"].float())
+    monkeypatch.delenv("RWKVQ_INT4")
+    assert rel_err(i4.linear_int4(x.cuda(), dev(sym)), O.linear_w4a16_kernel_semantics(x, O.dequant_int4_groupwise(full))) <= 1e-2
+
+
+@pytest.mark.parametrize("m", [1, 5, 16])
+def test_int4_per_tensor_and_affine(mods, m):
+    i4, f4, q4 = mods[0], mods[1], mods[2]
+    n, k = 136, 512
+    w = gen(7, (n, k), 0.05)
+    x = gen(m + 1, (m, k), 1.0, torch.float16)
+    p, s = q4.quantize_to_int4_per_tensor(w)
+    info = {"packed": p, "scale": s, "qtype": "int4_per_tensor"}
+    assert rel_err(i4.linear_int4(x.cuda(), dev(info)), O.linear_w4a16_kernel_semantics(x, O.dequant_int4_per_tensor(info))) <= 1e-2
+    aff = q4.quantize_to_int4_affine(w)
+    aff["qtype"] = "int4_affine"
+    assert rel_err(i4.linear_int4(x.cuda(), dev(aff)), O.linear_w4a16_kernel_semantics(x, O.dequant_int4_affine(aff))) <= 1e-2
+    y = f4.linear_int4_gemv_triton(x[0].cuda(), p.cuda(), s.cuda())
+    assert y.shape == (n,)
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 33])
+def test_int8_w8a16(mods, m):
+    i8, f8, q8 = mods[3], mods[4], mods[5]
+    n, k = 136, 768
+    w = gen(8, (n, k), 0.05)
+    x = gen(m + 2, (m, k), 1.0, torch.float16)
+    q, s = q8.quantize_to_int8_per_tensor(w)
+    info = {"weight": q, "tensor_scale": s, "qtype": "int8_per_tensor"}
+    assert rel_err(i8.linear_int8(x.cuda(), dev(info)), O.linear_w4a16_kernel_semantics(x, O.dequant_int8_per_tensor(info))) <= 1e-2
+    a = q8.quantize_to_int8_affine(w)
+    aff = {"weight": a["w_u8"], "mx": a["mx"], "rx": a["rx"], "my": a["my"], "ry": a["ry"], "qtype": "int8_affine"}
+    assert rel_err(i8.linear_int8(x.cuda(), dev(aff)), O.linear_w4a16_kernel_semantics(x, O.dequant_int8_affine(aff))) <= 1e-2
+    assert f8.linear_int8_gemv_triton(x[0].cuda(), q.cuda(), s.cuda()).shape == (n,)
+
+
+def test_against_reference_cpu_outputs(mods):
+    """Golden outputs of the reference's int4_ops / int8_ops CPU route.  That route rounds the dequantized weights
+    to fp16 and multiplies in fp16, so it carries fp16 noise of its own: the bound here is 2e-2, the 1e-2 bar is
+    applied against the fp32-accumulating oracle in the tests above."""
+    i4, _, q4, i8, _, q8 = mods
+    W = dict(np.load(os.path.join(G, "weights.npz")))
+    w = torch.from_numpy(W["w"])
+    x = torch.from_numpy(W["x"].view(np.int16).copy()).view(torch.float16)
+    fb = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.float16)
+    p, s = q4.quantize_to_int4_per_tensor(w)
+    assert rel_err(i4.linear_int4(x.cuda(), dev({"packed": p, "scale": s, "qtype": "int4_per_tensor"})), fb(W["lin4pt"])) <= 2e-2
+    g = q4.quantize_to_int4_groupwise(w, 128); g["qtype"] = "int4_groupwise"
+    assert rel_err(i4.linear_int4(x.cuda(), dev(g)), fb(W["lin4gw"])) <= 2e-2
+    a = q4.quantize_to_int4_affine(w); a["qtype"] = "int4_affine"
+    assert rel_err(i4.linear_int4(x.cuda(), dev(a)), fb(W["lin4af"])) <= 2e-2
+    q, s8 = q8.quantize_to_int8_per_tensor(w)
+    assert rel_err(i8.linear_int8(x.cuda(), dev({"weight": q, "tensor_scale": s8, "qtype": "int8_per_tensor"})), fb(W["lin8pt"])) <= 2e-2
+    a8 = q8.quantize_to_int8_affine(w)
+    aff = {"weight": a8["w_u8"], "mx": a8["mx"], "rx": a8["rx"], "my": a8["my"], "ry": a8["ry"], "qtype": "int8_affine"}
+    assert rel_err(i8.linear_int8(x.cuda(), dev(aff)), fb(W["lin8af"])) <= 2e-2
+
+
+def test_loaders_and_errors(mods):
+    i4, _, q4, i8, _, q8 = mods
+    w = gen(3, (16, 256), 0.05)
+    g = q4.quantize_to_int4_groupwise(w, 128)
+    z = {"k.int4_" + n: v for n, v in g.items()}
+    assert i4.is_int4_weight(z, "k") and i4.load_int4_weight(z, "k", "cuda")["qtype"] == "int4_groupwise"
+    with pytest.raises(KeyError):
+        i4.load_int4_weight({}, "k")
+    with pytest.raises(ValueError):
+        i4.linear_int4(torch.zeros(1, 256).cuda(), {"qtype": "nope"})
+    q, s = q8.quantize_to_int8_per_tensor(w)
+    z8 = {"k.int8_weight": q, "k.int8_scale": s}
+    assert i8.is_int8_weight(z8, "k") and i8.load_int8_weight(z8, "k", "cuda")["qtype"] == "int8_per_tensor"
+    with pytest.raises(KeyError):
+        i8.load_int8_weight({}, "k")
