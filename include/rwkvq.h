@@ -231,6 +231,25 @@ int32_t rwkvq_gemv_int4_group(const void* x_f16, int64_t ldx, const uint8_t* pac
                               const float* zeros, int32_t scale_is_f16, int32_t group, void* out_f16, int64_t ldo,
                               int64_t M, int64_t N, int64_t K, void* stream);
 
+/* ---------------------------------------------------------------- NVFP4 (W4A4, block-scaled)
+ *
+ * The reference has no NVFP4 code left; format and arithmetic follow its reports
+ * (iterations/phase1_nvfp4_exploration/reports/03_fused_kernel_en.md:22-34, 07_quantization_toolchain_v2_en.md:18-25,
+ * iterations/phase3_x5_residual_scheme/reports/11_fused_gemm_ops_en.md:20-26): e2m1 codes packed two per byte
+ * (even k in the low nibble) [rows, K/2]; one e4m3 scale per 16 consecutive k [rows, K/16]; one fp32 tensor scale. */
+
+/* Activation quantization: pts[0] = amax/2688; block scale = e4m3(clamp(max|x|_16 * 448/amax, 2^-6, 448));
+ * code = e2m1_rn(x * (1/pts) / block scale).  amax_scratch: one fp32 owned by the caller. */
+int32_t rwkvq_actq_nvfp4(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                         uint8_t* block_scales, int64_t lds, float* pts, float* amax_scratch, void* stream);
+/* out = fp16((sum_k codeA*bsA * codeB*bsB) * a_pts[0] * w_tscale[0]) for M <= 16 rows, K a multiple of 128;
+ * rwkvq_gemv_nvfp4_smem_bytes(M, K) must not exceed 200 KiB. */
+int64_t rwkvq_gemv_nvfp4_smem_bytes(int64_t M, int64_t K);
+int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_block_scales, int64_t ldas,
+                         const float* a_pts, const uint8_t* w_codes, int64_t ldw, const uint8_t* w_block_scales,
+                         int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,249 @@
+// NVFP4 (W4A4, block-scaled): e2m1 values, one e4m3 scale per 16 consecutive K, one fp32 scale per tensor.
+//
+//   activation quantization (per call):  pts = amax / 2688;  block scale = e4m3(clamp(max|x|_16 * 448 / amax, 2^-6, 448));
+//                                        code = e2m1_rn(x * (1/pts) / block_scale)
+//   projection:                          out = fp16( (sum_k codeA*bsA * codeB*bsB) * ptsA * ptsW )
+//
+// The reference repository holds no NVFP4 code any more (only its reports describe the format:
+// iterations/phase1_nvfp4_exploration/reports/03_fused_kernel_en.md:22-34, 07_quantization_toolchain_v2_en.md:18-25,
+// iterations/phase3_x5_residual_scheme/reports/11_fused_gemm_ops_en.md:20-26), so these kernels follow that text.
+//
+// Decode GEMV (M <= 16): code * block scale is an exact fp16 value (6 significant bits, magnitude 2^-7 .. 2688), so
+// both operands are dequantized to fp16 -- the activations once per CTA into shared memory, the weights in registers
+// from the streamed 16-byte loads (cvt.f16x2.e2m1x2 + one HMUL2 per pair) -- and multiplied with mma.sync.m16n8k16
+// with fp32 accumulation: every product is exact.  Same work split as the INT4 GEMV: 8 weight rows per CTA, the 8
+// warps on alternating 128-k units, register ring of loads across row tiles, fixed-order reduction.
+#include <cstdlib>
+
+#include "w8a8.cuh"
+
+namespace rwkvq {
+
+// two floats -> one byte of two e2m1 codes (lo in the low nibble), round-to-nearest-even, saturating
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+    unsigned short r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t)r;
+}
+// one byte of two e2m1 codes -> f16 pair (low nibble in the low half), exact
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
+    uint32_t r;
+    const unsigned short b = (unsigned short)(byte & 0xffu);
+    asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "h"(b));
+    return r;
+}
+__device__ __forceinline__ float e4m3_to_float(uint32_t code) {
+    const uint32_t h2 = e4m3x2_to_f16x2(code & 0xffu);
+    return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
+}
+
+// ---------------------------------------------------------------------------------------- activation quantization
+// one thread per 16-block
+template <int DT>
+__global__ void __launch_bounds__(256) actq_nvfp4_kernel(const void* x, uint8_t* codes, uint8_t* bscale, float* pts_out,
+                                                         const float* amax_p, int64_t M, int64_t K, int64_t ldx, int64_t ldc,
+                                                         int64_t lds) {
+    const int64_t nblk = K >> 4;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const float amax = fmaxf(*amax_p, 1e-12f);
+    const float pts = __fdiv_rn(amax, 2688.f);
+    if (i == 0) *pts_out = pts;
+    if (i >= M * nblk) return;
+    const int64_t r = i / nblk, b = i - r * nblk;
+    const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + (r * ldx + b * 16) * 2);
+    const uint4 v0 = p[0], v1 = p[1];
+    const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    float f[16], m = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const float2 t = cvt2<DT>(w[q]);
+        f[2 * q] = t.x;
+        f[2 * q + 1] = t.y;
+        m = fmaxf(m, fmaxf(fabsf(t.x), fabsf(t.y)));
+    }
+    const float sb = fminf(fmaxf(m * __fdiv_rn(448.f, amax), 0.015625f), 448.f);
+    const uint32_t sc = e4m3x2(sb, 0.f) & 0xffu;
+    const float bs = e4m3_to_float(sc);
+    const float inv_pts = __fdiv_rn(1.f, pts);
+    uint32_t out[2] = {0u, 0u};
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+        out[q >> 2] |= e2m1x2(__fdiv_rn(f[2 * q] * inv_pts, bs), __fdiv_rn(f[2 * q + 1] * inv_pts, bs)) << (8 * (q & 3));
+    *reinterpret_cast<uint2*>(codes + r * ldc + b * 8) = make_uint2(out[0], out[1]);
+    bscale[r * lds + b] = (uint8_t)sc;
+}
+
+// ---------------------------------------------------------------------------------------- decode GEMV
+struct Nf4Args {
+    const uint8_t* a_codes;    // [M, lda] packed activation codes
+    const uint8_t* a_bs;       // [M, ldas] e4m3 block scales
+    const float* a_pts;        // [1]
+    const uint8_t* w;          // [N, ldw] packed weight codes
+    const uint8_t* w_bs;       // [N, ldws] e4m3 block scales
+    const float* w_ts;         // [1]
+    __half* out;               // [M, ldo]
+    int64_t lda, ldas, ldw, ldws, ldo;
+    int M, N, K, pitch;
+};
+
+struct Nf4Slot {
+    uint4 w;
+    uint32_t sc;               // two e4m3 block scales (this lane's 32 codes = blocks 2t, 2t+1 of the unit)
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThr, 2) gemv_nvfp4_kernel(const Nf4Args a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* red = reinterpret_cast<float*>(smem);                       // [kWarps][4][32]
+    uint8_t* xs = smem + kWarps * 4 * 32 * 4;                          // [M][pitch] fp16 values code * block scale
+    griddep_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int units = a.K >> 7;
+    const int ntile = (a.N + 7) >> 3;
+    const int tb = (int)((int64_t)ntile * blockIdx.x / gridDim.x), te = (int)((int64_t)ntile * (blockIdx.x + 1) / gridDim.x);
+    const int upw = (units + kWarps - 1) / kWarps, nchunks = (upw + D - 1) / D;
+
+    auto fetch = [&](int tile, int c, int j) -> Nf4Slot {
+        Nf4Slot s;
+        s.w = make_uint4(0, 0, 0, 0);
+        s.sc = 0;
+        const int u = warp + (c * D + j) * kWarps;
+        if (tile >= te || u >= units) return s;
+        const int64_t row = min((tile << 3) + g, a.N - 1);
+        s.w = ldg_stream(a.w + row * a.ldw + (u << 6) + 16 * t);
+        s.sc = __ldg(reinterpret_cast<const unsigned short*>(a.w_bs + row * a.ldws + (u << 3) + 2 * t));
+        return s;
+    };
+    Nf4Slot ring[D];
+#pragma unroll
+    for (int j = 0; j < D; ++j) ring[j] = fetch(tb, 0, j);
+
+    griddep_wait();
+    // prologue: activations dequantized to fp16 (exact), one thread per 16-block
+    for (int i = threadIdx.x; i < a.M * (a.K >> 4); i += kThr) {
+        const int r = i / (a.K >> 4), b = i - r * (a.K >> 4);
+        const uint2 cw = *reinterpret_cast<const uint2*>(a.a_codes + (int64_t)r * a.lda + b * 8);
+        const uint32_t s2 = e4m3x2_to_f16x2(a.a_bs[(int64_t)r * a.ldas + b]);
+        const uint32_t ss = __byte_perm(s2, s2, 0x1010);               // (bs, bs)
+        uint32_t h[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const uint32_t pair = e2m1x2_to_f16x2(((q < 4 ? cw.x : cw.y) >> (8 * (q & 3))) & 0xffu);
+            const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&ss));
+            h[q] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)r * a.pitch + (size_t)b * 32);
+        dst[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        dst[1] = make_uint4(h[4], h[5], h[6], h[7]);
+    }
+    __syncthreads();
+    const float out_scale = a.a_pts[0] * a.w_ts[0];
+
+    for (int tile = tb; tile < te; ++tile) {
+        const int n0 = tile << 3;
+        float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int ch = 0; ch < nchunks; ++ch) {
+            const bool last = ch + 1 == nchunks;
+#pragma unroll
+            for (int j = 0; j < D; ++j) {
+                const Nf4Slot sl = ring[j];
+                ring[j] = fetch(last ? tile + 1 : tile, last ? 0 : ch + 1, j);
+                const int u = warp + (ch * D + j) * kWarps;
+                if (u < units) {
+                    const uint32_t s2 = e4m3x2_to_f16x2(sl.sc);        // (bs of block 2t, bs of block 2t+1)
+                    const uint32_t sA = __byte_perm(s2, s2, 0x1010), sB = __byte_perm(s2, s2, 0x3232);
+                    const uint32_t wd[4] = {sl.w.x, sl.w.y, sl.w.z, sl.w.w};
+                    const size_t koff = ((size_t)u << 8) + (size_t)t * 64;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {                      // word i = 8 codes; words 0,1 = first block, 2,3 = second
+                        uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+                        if (g < a.M) a0 = *reinterpret_cast<const uint4*>(xs + (size_t)g * a.pitch + koff + i * 16);
+                        if (g + 8 < a.M) a1 = *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * a.pitch + koff + i * 16);
+                        const uint32_t sc = i < 2 ? sA : sB;
+                        uint32_t b[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t pair = e2m1x2_to_f16x2((wd[i] >> (8 * q)) & 0xffu);
+                            const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&sc));
+                            b[q] = *reinterpret_cast<const uint32_t*>(&v);
+                        }
+                        mma_f16(c, a0.x, a1.x, a0.y, a1.y, b[0], b[1]);
+                        mma_f16(c2, a0.z, a1.z, a0.w, a1.w, b[2], b[3]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) red[(warp * 4 + j) * 32 + lane] = c[j] + c2[j];
+        __syncthreads();
+        if (threadIdx.x < 128) {
+            const int j = threadIdx.x >> 5, l = threadIdx.x & 31;
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += red[(w * 4 + j) * 32 + l];
+            const int m = (l >> 2) + ((j & 2) ? 8 : 0), n = n0 + 2 * (l & 3) + (j & 1);
+            if (m < a.M && n < a.N) a.out[(int64_t)m * a.ldo + n] = __float2half_rn(s * out_scale);
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace rwkvq
+
+using namespace rwkvq;
+
+extern "C" {
+
+int32_t rwkvq_actq_nvfp4(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                         uint8_t* block_scales, int64_t lds, float* pts, float* amax_scratch, void* stream) {
+    const char* who = "actq_nvfp4";
+    RWKVQ_REQUIRE(x && codes && block_scales && pts && amax_scratch, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(M >= 0 && K >= 0 && K % 16 == 0, RWKVQ_E_SHAPE, "%s: K=%lld must be a multiple of 16", who, (long long)K);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(((uintptr_t)codes & 7) == 0 && ldc % 8 == 0 && ldc >= K / 2 && lds >= K / 16, RWKVQ_E_ALIGN, "%s: code rows must be 8-byte aligned", who);
+    int32_t rc = rwkvq_prep_x(x, x_dtype, M, K, ldx, nullptr, nullptr, K, amax_scratch, RWKVQ_DIV_IEEE, stream);
+    if (rc) return rc;
+    const int64_t nthreads = std::max<int64_t>(1, M * (K / 16));
+    const unsigned grid = (unsigned)((nthreads + 255) / 256);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == RWKVQ_F16) actq_nvfp4_kernel<RWKVQ_F16><<<grid, 256, 0, st>>>(x, codes, block_scales, pts, amax_scratch, M, K, ldx, ldc, lds);
+    else actq_nvfp4_kernel<RWKVQ_BF16><<<grid, 256, 0, st>>>(x, codes, block_scales, pts, amax_scratch, M, K, ldx, ldc, lds);
+    return check_launch(who);
+}
+
+int64_t rwkvq_gemv_nvfp4_smem_bytes(int64_t M, int64_t K) { return kWarps * 4 * 32 * 4 + M * (2 * K + 16); }
+
+int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_block_scales, int64_t ldas, const float* a_pts,
+                         const uint8_t* w_codes, int64_t ldw, const uint8_t* w_block_scales, int64_t ldws, const float* w_tscale,
+                         void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream) {
+    const char* who = "gemv_nvfp4";
+    RWKVQ_REQUIRE(a_codes && a_block_scales && a_pts && w_codes && w_block_scales && w_tscale && out_f16, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M <= 16, RWKVQ_E_SHAPE, "%s: M=%lld (at most 16 rows per call)", who, (long long)M);
+    RWKVQ_REQUIRE(K % 128 == 0, RWKVQ_E_SHAPE, "%s: K=%lld must be a multiple of 128", who, (long long)K);
+    RWKVQ_REQUIRE(aligned16(w_codes) && ldw % 16 == 0 && ldw >= K / 2, RWKVQ_E_ALIGN, "%s: weight code rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(((uintptr_t)w_block_scales & 1) == 0 && ldws % 2 == 0 && ldws >= K / 16, RWKVQ_E_ALIGN, "%s: weight scale rows must be 2-byte aligned", who);
+    RWKVQ_REQUIRE(((uintptr_t)a_codes & 7) == 0 && lda % 8 == 0 && lda >= K / 2 && ldas >= K / 16, RWKVQ_E_ALIGN, "%s: activation code rows must be 8-byte aligned", who);
+    RWKVQ_REQUIRE(ldo >= N, RWKVQ_E_SHAPE, "%s: ldo < N", who);
+    if (M == 0 || N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
+    const size_t smem = (size_t)rwkvq_gemv_nvfp4_smem_bytes(M, K);
+    RWKVQ_REQUIRE(smem <= 200 * 1024, RWKVQ_E_SHAPE, "%s: M*K = %lld*%lld does not fit shared memory; call with fewer rows", who, (long long)M, (long long)K);
+    Nf4Args a{};
+    a.a_codes = a_codes; a.a_bs = a_block_scales; a.a_pts = a_pts; a.w = w_codes; a.w_bs = w_block_scales; a.w_ts = w_tscale;
+    a.out = (__half*)out_f16; a.lda = lda; a.ldas = ldas; a.ldw = ldw; a.ldws = ldws; a.ldo = ldo;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.pitch = (int)(2 * K + 16);
+    auto kern = gemv_nvfp4_kernel<4>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    RWKVQ_REQUIRE(e == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(e));
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThr, smem);
+    RWKVQ_REQUIRE(e == cudaSuccess && per_sm >= 1, RWKVQ_E_LAUNCH, "%s: occupancy query failed", who);
+    const int64_t tiles = (N + 7) / 8;
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, (int64_t)sm_count() * per_sm);
+    kern<<<grid, kThr, smem, (cudaStream_t)stream>>>(a);
+    return check_launch(who);
+}
+
+}  // extern "C"

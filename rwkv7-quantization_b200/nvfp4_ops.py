@@ -1,0 +1,104 @@
+"""NVFP4 (W4A4) scheme: offline weight quantizer, loader and projection.
+
+The reference repository describes this format in its reports but ships no code for it any more, so this module is
+an addition behind the same conventions as fp8_ops.py:
+
+    storage (07_quantization_toolchain_v2_en.md:18-25)
+        <key>                 uint8 [N, K/2]   two e2m1 codes per byte, even k in the low nibble
+        <key>.nf4_b_scale     float8_e4m3fn [N, K/16]   one scale per 16 consecutive k
+        <key>.nvfp4_t_scale   float32 scalar            amax / 2688  (2688 = 448 * 6)
+    weight-info dict   {"weight", "block_scale", "tensor_scale", "qtype": "nvfp4"}
+    arithmetic (03_fused_kernel_en.md:22-34, 11_fused_gemm_ops_en.md:20-26)
+        block scale = e4m3(clamp(max|x|_16 * 448 / amax, 2^-6, 448));  code = e2m1_rn(x / pts / block scale)
+        out = (sum codeA*bsA * codeB*bsB) * ptsA * ptsW
+"""
+from __future__ import annotations
+
+import torch
+
+import rwkvq_abi as abi
+
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+BLOCK = 16
+GEMV_ROWS = 16
+
+
+def _e2m1_codes(v: torch.Tensor) -> torch.Tensor:
+    """fp32 -> 4-bit e2m1 codes (sign << 3 | index), round-to-nearest-even on the value grid, saturating."""
+    a = v.abs().clamp(max=6.0)
+    # thresholds are the midpoints; a tie goes to the neighbour with an even index
+    idx = ((a > 0.25).to(torch.uint8) + (a >= 0.75) + (a > 1.25) + (a >= 1.75) + (a > 2.5) + (a >= 3.5) + (a > 5.0))
+    return (idx | (torch.signbit(v).to(torch.uint8) << 3)).to(torch.uint8)
+
+
+def quantize_to_nvfp4(w: torch.Tensor):
+    """Offline weight quantization (any device).  Returns the weight-info dict; store it with `to_state`."""
+    wf = w.float()
+    n, k = wf.shape
+    assert k % BLOCK == 0, f"K={k} must be a multiple of {BLOCK}"
+    amax = wf.abs().max().clamp(min=1e-12)
+    pts = amax / 2688.0
+    blk = wf.reshape(n, k // BLOCK, BLOCK)
+    sb = (blk.abs().amax(dim=2) * (448.0 / amax)).clamp(2.0 ** -6, 448.0)
+    bs = sb.to(torch.float8_e4m3fn)
+    codes = _e2m1_codes((blk * (1.0 / pts) / bs.float().unsqueeze(2)).reshape(n, k))
+    packed = codes[:, 0::2] | (codes[:, 1::2] << 4)
+    return {"weight": packed.contiguous(), "block_scale": bs.contiguous(), "tensor_scale": pts.reshape(()).float(), "qtype": "nvfp4"}
+
+
+def dequantize_nvfp4(info) -> torch.Tensor:
+    """code * block scale * tensor scale as fp32 [N, K]."""
+    p = info["weight"]
+    codes = torch.stack((p & 0xF, p >> 4), dim=-1).reshape(p.shape[0], -1).long()
+    table = torch.tensor(E2M1_VALUES + tuple(-x for x in E2M1_VALUES), dtype=torch.float32, device=p.device)
+    vals = table[codes]
+    return vals * info["block_scale"].float().repeat_interleave(BLOCK, dim=1) * info["tensor_scale"].float()
+
+
+def to_state(key: str, info) -> dict:
+    return {key: info["weight"], key + ".nf4_b_scale": info["block_scale"], key + ".nvfp4_t_scale": info["tensor_scale"]}
+
+
+def is_nvfp4_weight(z, key) -> bool:
+    return (key + ".nf4_b_scale") in z
+
+
+def load_nvfp4_weight(z, key, dev):
+    """Move an NVFP4 weight to `dev`, drop its side keys from `z` (as load_fp8_weight does) and describe it."""
+    return {"weight": z[key].to(dev).contiguous(), "block_scale": z.pop(key + ".nf4_b_scale").to(dev).contiguous(),
+            "tensor_scale": z.pop(key + ".nvfp4_t_scale").to(dev).float(), "qtype": "nvfp4"}
+
+
+def quantize_activations_nvfp4(x: torch.Tensor):
+    """On-the-fly activation quantization on the device: (packed codes [M,K/2], block scales [M,K/16] e4m3, pts [1])."""
+    from fused_fp8_gemm import _rows16
+    x2 = _rows16(x).contiguous()
+    m, k = x2.shape
+    dev = x2.device
+    codes = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+    bs = torch.empty((m, k // BLOCK), dtype=torch.float8_e4m3fn, device=dev)
+    pts = torch.empty(1, dtype=torch.float32, device=dev)
+    amax = torch.empty(1, dtype=torch.float32, device=dev)
+    abi.call("rwkvq_actq_nvfp4", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k // 2, bs.data_ptr(),
+             k // BLOCK, pts.data_ptr(), amax.data_ptr(), abi.stream_ptr())
+    return codes, bs, pts
+
+
+def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
+    """W4A4 projection: activations quantized per call, weights streamed in packed form."""
+    w, wbs, wts = weight_info["weight"], weight_info["block_scale"], weight_info["tensor_scale"]
+    n, k = w.shape[0], w.shape[1] * 2
+    codes, bs, pts = quantize_activations_nvfp4(x)
+    m = codes.shape[0]
+    out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
+    rows = GEMV_ROWS
+    while rows > 1 and abi.lib().rwkvq_gemv_nvfp4_smem_bytes(rows, k) > 200 * 1024:
+        rows //= 2
+    wts = wts.reshape(1)
+    for r0 in range(0, m, rows):
+        r = min(rows, m - r0)
+        abi.call("rwkvq_gemv_nvfp4", codes[r0:].data_ptr(), k // 2, bs[r0:].data_ptr(), k // BLOCK, pts.data_ptr(),
+                 w.data_ptr(), w.stride(0), wbs.data_ptr(), wbs.stride(0), wts.data_ptr(), out[r0:].data_ptr(), n, r, n, k,
+                 abi.stream_ptr())
+    out = out.reshape(*x.shape[:-1], n)
+    return out if out_dtype in (None, out.dtype) else out.to(out_dtype)

@@ -1,0 +1,92 @@
+"""NVFP4 (W4A4) on the GPU against the CPU restatement of the format described in the reference's reports
+(parity unpinned: the reference holds no NVFP4 code).  Activation codes, block scales and the tensor scale are
+compared bit for bit (IEEE arithmetic on both sides); projections within max-rel-err 1e-2, an element's error
+measured against max(|ref|, 0.02*rms(ref)) -- every product is exact in the kernel, only the summation order differs."""
+import pytest
+import torch
+
+from oracle import rwkvq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def gen(seed, shape, std=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+def rel_err(out, ref):
+    out, ref = out.detach().cpu().float(), ref.detach().cpu().float()
+    floor = 0.02 * ref.pow(2).mean().sqrt().item() + 1e-30
+    return ((out - ref).abs() / ref.abs().clamp(min=floor)).max().item()
+
+
+@pytest.fixture(scope="module")
+def nf():
+    import rwkvq_abi as abi
+    abi.require_device()
+    import nvfp4_ops
+    return nvfp4_ops
+
+
+def dev(info):
+    return {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in info.items()}
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k", [(1, 4096), (7, 768), (256, 4096), (3, 16384)])
+def test_activation_quantization_bit_exact(nf, dt, m, k):
+    x = gen(m + k, (m, k), 1.0).to(dt)
+    if m > 2:
+        x[1].zero_()
+    codes, bs, pts = nf.quantize_activations_nvfp4(x.cuda())
+    want_codes, want_bs, want_pts = O.nvfp4_actq(x)
+    assert torch.equal(codes.cpu(), want_codes)
+    assert torch.equal(bs.cpu().view(torch.uint8), want_bs)
+    assert torch.equal(pts.cpu(), want_pts)
+
+
+def test_weight_quantizer_matches_oracle_and_runs_on_device(nf):
+    w = gen(5, (96, 512), 1.0 / 16)
+    a, b = nf.quantize_to_nvfp4(w), O.nvfp4_quantize_weight(w)
+    assert torch.equal(a["weight"], b["weight"]) and torch.equal(a["block_scale"].view(torch.uint8), b["block_scale"])
+    g = nf.quantize_to_nvfp4(w.cuda())
+    assert torch.equal(g["weight"].cpu(), a["weight"]) and torch.equal(g["block_scale"].cpu().view(torch.uint8), b["block_scale"])
+    z = nf.to_state("k", a)
+    assert nf.is_nvfp4_weight(z, "k")
+    info = nf.load_nvfp4_weight(z, "k", "cuda")
+    assert info["qtype"] == "nvfp4" and "k.nf4_b_scale" not in z
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 40])
+@pytest.mark.parametrize("n,k", [(1000, 768), (512, 4096), (136, 16384)])
+def test_linear_nvfp4(nf, m, n, k):
+    w = gen(n + k, (n, k), (1.0 / k) ** 0.5)
+    info = nf.quantize_to_nvfp4(w)
+    x = gen(m, (m, k), 1.0, torch.bfloat16)
+    out = nf.linear_nvfp4(x.cuda(), dev(info))
+    oinfo = {"weight": info["weight"], "block_scale": info["block_scale"].view(torch.uint8), "tensor_scale": info["tensor_scale"]}
+    want = O.linear_nvfp4(x, oinfo)
+    assert out.shape == want.shape and out.dtype == torch.float16
+    assert rel_err(out, want) <= 1e-2
+
+
+def test_config5_ffn_shapes(nf):
+    """BASELINE config 5: FFN key [16384,4096] and value [4096,16384], M in {1, 256}; M = 4096 on a slice of rows."""
+    import fp8_ops
+    for n, k in ((16384, 4096), (4096, 16384)):
+        w = gen(n, (n, k), (1.0 / k) ** 0.5)
+        info = nf.quantize_to_nvfp4(w.cuda())
+        cpu = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
+               "tensor_scale": info["tensor_scale"].cpu()}
+        for m in (1, 256):
+            x = gen(m + n, (m, k), 1.0, torch.bfloat16)
+            out = fp8_ops.linear_quantized(x.cuda(), info)            # routed by qtype "nvfp4"
+            cols = slice(0, 640)                                      # the oracle checks 640 of the output columns
+            sub = {"weight": cpu["weight"][cols], "block_scale": cpu["block_scale"][cols], "tensor_scale": cpu["tensor_scale"]}
+            assert rel_err(out[:, cols], O.linear_nvfp4(x, sub)) <= 1e-2
+    w = gen(9, (256, 4096), 1.0 / 64)
+    info = nf.quantize_to_nvfp4(w)
+    x = gen(10, (4096, 4096), 1.0, torch.bfloat16)
+    oinfo = {"weight": info["weight"], "block_scale": info["block_scale"].view(torch.uint8), "tensor_scale": info["tensor_scale"]}
+    assert rel_err(nf.linear_nvfp4(x.cuda(), dev(info)), O.linear_nvfp4(x, oinfo)) <= 1e-2
