@@ -31,6 +31,7 @@ for _p in (ROOT, PKG):
 import torch  # noqa: E402
 
 C, F, LAYERS = 4096, 16384, 32
+PREFILL_T = 2048          # tokens per sequence of the prefill leg (BASELINE config: T=2048)
 METRIC = "B=1 quantized GEMV HBM GB/s + prefill GEMM TFLOPS, RWKV-7 7.2B shapes, 1-8 GPU"
 WORKLOAD = "rwkv7-7.2B fp8 w8a8 decode B=1: 32 layers x (rkv-fused 3x[4096,4096] + att_out [4096,4096] + ffn_key [16384,4096] + ffn_value [4096,16384])"
 
@@ -104,10 +105,10 @@ def make_fp8_weight(n, k, gen, dev):
     return {"weight": q, "tensor_scale": scale, "qtype": "fp8"}
 
 
-def make_model(dev, seed):
+def make_model(dev, seed, nlayers=LAYERS):
     gen = torch.Generator(device=dev).manual_seed(seed)
     layers = []
-    for _ in range(LAYERS):
+    for _ in range(nlayers):
         layers.append({
             "r": make_fp8_weight(C, C, gen, dev), "k": make_fp8_weight(C, C, gen, dev), "v": make_fp8_weight(C, C, gen, dev),
             "o": make_fp8_weight(C, C, gen, dev), "ffn_k": make_fp8_weight(F, C, gen, dev),
@@ -139,6 +140,25 @@ def decode_step(layers, x):
 
 
 LAUNCHES_PER_STEP = 4 * LAYERS
+# dram__bytes_read.sum + dram__bytes_write.sum per gemv_w8a8_kernel launch of this workload, from the ncu launch list
+# summarised in profiles/gemv_w8a8_fp8_decode_launch_list.md (4-layer capture; traffic per launch does not depend on
+# the number of layers).  Algorithmic bytes per launch: 50 368 518.
+DRAM_TRAFFIC_PER_LAUNCH = 49_870_000
+
+
+def prefill_pass(layers, x):
+    """One sequence of PREFILL_T tokens through the six projections of every layer (rows > FUSED_M_MAX, so r, k, v
+    are separate calls, as in the reference engine)."""
+    import fused_fp8_gemm as f
+    y = None
+    for L in layers:
+        for name, inp in (("r", "xr"), ("k", "xk"), ("v", "xv"), ("o", "xo"), ("ffn_k", "xf"), ("ffn_v", "xg")):
+            y = f.linear_quantized_fused(x[inp], L[name])
+    return y
+
+
+def prefill_flops(nlayers):
+    return 2 * PREFILL_T * (4 * C * C + 2 * C * F) * nlayers
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
@@ -220,7 +240,8 @@ def run_ours(args, rank, world, local_rank):
     if dist_on:
         dist.init_process_group("nccl", device_id=dev)
 
-    layers = make_model(dev, seed=100 + rank)
+    layers = make_model(dev, seed=100 + rank, nlayers=args.layers)
+    scale_l = args.layers / LAYERS
     host, x = make_inputs(dev, seed=7 + rank, pinned_host=True)
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -262,7 +283,24 @@ def run_ours(args, rank, world, local_rank):
         ms_eager = timed(step_eager, max(1, args.steps // 4), dist_on) / max(1, args.steps // 4) * args.steps
         eager_launches = abi.launch_count() - l0
 
-    nbytes = step_bytes(1)
+    prefill = None
+    if not args.no_prefill:
+        with torch.cuda.stream(stream):
+            gen = torch.Generator(device=dev).manual_seed(5 + rank)
+            xp = {name: torch.randn((PREFILL_T, k), generator=gen, device=dev).to(torch.bfloat16)
+                  for name, k in (("xr", C), ("xk", C), ("xv", C), ("xo", C), ("xf", C), ("xg", F))}
+            for _ in range(2):
+                prefill_pass(layers, xp)
+            reps = 3
+            ms_p = timed(lambda: prefill_pass(layers, xp), reps, dist_on) / reps
+        tfl = prefill_flops(args.layers) * world / (ms_p * 1e-3) / 1e12
+        prefill = {"metric": "prefill GEMM TFLOPS (FP8 W8A8, T=2048 tokens, all projections incl. activation quantization)",
+                   "value": round(tfl, 1), "unit": "TFLOP/s", "ms_per_sequence": round(ms_p, 3),
+                   "roofline": {"bound": "tensor", "achieved": round(tfl / world, 1), "peak": round(2 * peaks()["bf16_tflops"], 1),
+                                "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),
+                                "peak_note": "2 x the measured dense bf16 cuBLAS rate (fp8 runs at twice the bf16 rate)"}}
+        del xp
+    nbytes = int(step_bytes(1) * scale_l)
     per_step = ms / args.steps
     gbs = nbytes * world / (per_step * 1e-3) / 1e9
     gbs_e2e = nbytes * world / (ms_e2e / args.steps * 1e-3) / 1e9
@@ -277,17 +315,19 @@ def run_ours(args, rank, world, local_rank):
                    "l2": "6.44 GB of distinct weights per step (inputs larger than L2)",
                    "launch": "CUDA graph of the 128 public-API calls"},
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(per_gpu / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
-                     "kernel": "gemv_w8a8_kernel<fp8>", "bytes_per_launch": nbytes // LAUNCHES_PER_STEP,
-                     "us_per_launch": round(per_step * 1e3 / LAUNCHES_PER_STEP, 3)},
+                     "frac": round(per_gpu / pk["hbm_gbs"], 4), "traffic": DRAM_TRAFFIC_PER_LAUNCH if args.layers == LAYERS else None,
+                     "peak_source": pk["source"],
+                     "kernel": "gemv_w8a8_kernel<fp8>", "bytes_per_launch": nbytes // (4 * args.layers),
+                     "us_per_launch": round(per_step * 1e3 / (4 * args.layers), 3)},
         "e2e": {"value": round(gbs_e2e, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()),
                 "d2h_bytes_per_step": y_host.numel() * y_host.element_size(),
                 "mode": "pinned host -> device copies, graph replay of the public API calls, device -> host result",
                 "eager_python_calls_gbs": round(gbs_eager, 2)},
-        "gpu_launches": LAUNCHES_PER_STEP * args.steps,
+        "gpu_launches": 4 * args.layers * args.steps,
         "launches_counted_eager": int(eager_launches),
         "clocks": clocks.summary(),
+        "prefill": prefill,
     }
     if rank == 0:
         if world == 1 and not args.no_cpu:
@@ -300,6 +340,77 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------ per-shape mode
+SHAPES = {"att": (C, C), "ffn_key": (F, C), "ffn_value": (C, F), "c2": (2560, 2560), "c1": (768, 768)}
+
+
+def _rand_weight(scheme, n, k, dev):
+    """Random codes with valid scales: enough for timing (values do not change the work)."""
+    if scheme == "fp8":
+        return {"weight": torch.randint(0, 120, (n, k), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+                "tensor_scale": torch.tensor(0.01, device=dev), "qtype": "fp8"}
+    if scheme == "int8":
+        return {"weight": torch.randint(-127, 127, (n, k), dtype=torch.int8, device=dev),
+                "tensor_scale": torch.tensor(0.01, device=dev), "qtype": "int8"}
+    if scheme == "int4":
+        return {"packed": torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device=dev),
+                "scales": torch.rand(n, k // 128, device=dev) * 0.01, "zeros": -torch.rand(n, k // 128, device=dev) * 0.05,
+                "group_size": 128, "qtype": "int4_groupwise"}
+    if scheme == "nvfp4":
+        return {"weight": torch.randint(0, 255, (n, k // 2), dtype=torch.uint8, device=dev),
+                "block_scale": torch.randint(40, 100, (n, k // 16), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+                "tensor_scale": torch.tensor(0.001, device=dev), "qtype": "nvfp4"}
+    raise ValueError(scheme)
+
+
+def _weight_bytes(scheme, n, k):
+    return {"fp8": n * k + 4, "int8": n * k + 4, "int4": n * k // 2 + n * (k // 128) * 8,
+            "nvfp4": n * k // 2 + n * k // 16 + 4}[scheme]
+
+
+def _linear(scheme):
+    import fp8_ops
+    if scheme == "int4":
+        from int4 import int4_ops
+        return int4_ops.linear_int4
+    return fp8_ops.linear_quantized_fused if scheme in ("fp8", "int8") else fp8_ops.linear_quantized
+
+
+def run_shape(args):
+    """One projection shape, one scheme, one M: rotates over enough distinct weight buffers to exceed L2, replays a
+    CUDA graph of the public calls, prints one JSON line (GB/s for M <= 128, TFLOP/s above)."""
+    import rwkvq_abi as abi
+    abi.require_device()
+    dev = torch.device("cuda", 0)
+    n, k = SHAPES[args.shape]
+    wb = _weight_bytes(args.scheme, n, k)
+    nbuf = max(2, int(400e6 / wb) + 1)
+    ws = [_rand_weight(args.scheme, n, k, dev) for _ in range(nbuf)]
+    x = torch.randn(args.m, k, device=dev).to(torch.float16 if args.scheme == "int4" else torch.bfloat16)
+    lin = _linear(args.scheme)
+
+    def fn():
+        for w in ws:
+            lin(x, w)
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(max(1, args.warmup)):
+            fn()
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            fn()
+        for _ in range(max(1, args.warmup)):
+            g.replay()
+        ms = timed(g.replay, args.steps, False)
+    us = ms * 1e3 / (args.steps * nbuf)
+    nbytes = wb + args.m * k * 2 + args.m * n * 2
+    line = {"case": "shape", "scheme": args.scheme, "shape": args.shape, "M": args.m, "N": n, "K": k, "us_per_call": round(us, 3),
+            "algorithmic_bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks()["hbm_gbs"], 4),
+            "TFLOPs": round(2 * args.m * n * k / us / 1e6, 1), "distinct_weight_buffers": nbuf}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -307,11 +418,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the stack (32 = the benchmark; fewer only for profiler captures)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
+    ap.add_argument("--case", default="decode", choices=["decode", "shape"], help="decode = the benchmark; shape = one projection")
+    ap.add_argument("--scheme", default="fp8", choices=["fp8", "int8", "int4", "nvfp4"])
+    ap.add_argument("--shape", default="ffn_key", choices=sorted(SHAPES))
+    ap.add_argument("--m", type=int, default=1, help="rows of activations in --case shape")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.case == "shape":
+        if rank == 0:
+            run_shape(args)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, world, local_rank)
