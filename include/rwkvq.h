@@ -250,6 +250,16 @@ int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_b
                          int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                          void* stream);
 
+/* No counterpart in the reference.  rwkvq_tc_gemm_fp8 (M <= 128) for callers that cannot supply device scratch --
+ * a host runtime that owns every byte of device memory and forbids allocation inside its serving loop, or code
+ * running where cudaMalloc is not allowed.  The scratch is an 8 MiB array built into the library on each GPU; no
+ * allocation happens in this call or below it.  The first call on a device resolves the array's address and should be
+ * made outside stream capture; shapes needing more than 8 MiB are refused (RWKVQ_E_WORKSPACE); the array is shared by
+ * all calls on a device, is re-cleared on `stream` by every call, and calls that overlap on the GPU race on it. */
+int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
+                                 const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo,
+                                 int64_t M, int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -707,6 +707,33 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
 
 }  // namespace rwkvq
 
+// ---------------------------------------------------------------------------------------------------------------
+// Built-in scratch for callers that cannot provide a workspace (see rwkvq_tc_gemm_fp8_static below).  The array lives
+// in every GPU's memory from the moment the library is loaded on it until the process exits.
+namespace rwkvq {
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;      // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol; the device address has to be asked for, once per
+// device and with that device current.
+static int32_t static_scratch_ptr(void** out) {
+    static std::mutex mu;
+    static void* ptrs[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    RWKVQ_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, RWKVQ_E_LAUNCH, "static scratch: cudaGetDevice: %s", cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        RWKVQ_REQUIRE(e == cudaSuccess && p != nullptr, RWKVQ_E_LAUNCH, "static scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return RWKVQ_OK;
+}
+}  // namespace rwkvq
+
 using namespace rwkvq;
 
 extern "C" {
@@ -811,6 +838,36 @@ int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_sc
     TcCall c{};
     c.kind = KIND_I8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8");
+}
+
+/* rwkvq_tc_gemm_fp8 for M <= 128 without a caller workspace: the split-K partial sums and arrival counters live in
+ * an 8 MiB array that is part of the library image on every GPU.  Nothing is allocated, here or in anything this calls.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     outside any stream capture.  Later calls only enqueue work.
+ *   - Shapes whose scratch need (rwkvq_workspace_bytes(M, N, K, 1)) exceeds 8 MiB, and M > 128, are refused with
+ *     RWKVQ_E_WORKSPACE / RWKVQ_E_SHAPE.
+ *   - All calls on a device share the one array and it keeps what the previous call left in it; this entry point
+ *     therefore clears the counters and the status word on `stream` before the kernel.  Two calls that can overlap
+ *     on the GPU (different streams, or concurrent host threads on different streams) race on it: order them. */
+int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
+                                 int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                 int32_t div_mode, uint32_t flags, void* stream) {
+    const char* who = "tc_gemm_fp8_static";
+    RWKVQ_REQUIRE(M <= 128, RWKVQ_E_SHAPE, "%s: M=%lld > 128 (the large-M kernel needs no scratch: use rwkvq_tc_gemm_fp8)", who, (long long)M);
+    const int64_t need = rwkvq_workspace_bytes(M, N, K, 1);
+    RWKVQ_REQUIRE(need <= (int64_t)kStaticScratchBytes, RWKVQ_E_WORKSPACE, "%s: this shape needs %lld bytes of scratch, the built-in array has %lld",
+                  who, (long long)need, (long long)kStaticScratchBytes);
+    void* ws = nullptr;
+    int32_t rc = static_scratch_ptr(&ws);
+    if (rc != RWKVQ_OK) return rc;
+    const cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)kWsHeaderBytes, (cudaStream_t)stream);
+    RWKVQ_REQUIRE(e == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaMemsetAsync: %s", who, cudaGetErrorString(e));
+    TcArgs a{};
+    a.a_scale[0] = amax; a.amax_is_amax = amax_is_amax; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    fill_common(a, 1, M, N, K, 0, ldo, div_mode, flags);
+    TcCall c{};
+    c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = ws; c.workspace_bytes = (int64_t)kStaticScratchBytes;
+    return run_tc(a, c, (cudaStream_t)stream, who);
 }
 
 }  // extern "C"
