@@ -87,6 +87,14 @@ int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, i
 int32_t rwkvq_actq_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
                        float* amax, float* scale, int32_t div_mode, uint32_t flags, void* stream);
 
+/* rwkvq_actq_fp8 in ONE cooperative launch (no memset, no second kernel): same arguments and results; `scratch`
+ * (rwkvq_actq_fp8_fused_scratch_bytes() bytes, 4-byte aligned, any contents) carries the per-CTA maxima and the
+ * rendezvous flags; `status` (optional) receives RWKVQ_E_TIMEOUT if the bounded grid rendezvous gives up. */
+int64_t rwkvq_actq_fp8_fused_scratch_bytes(void);
+int32_t rwkvq_actq_fp8_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes,
+                             int64_t ldc, float* amax, float* scale, void* scratch, int64_t scratch_bytes,
+                             int32_t* status, int32_t div_mode, uint32_t flags, void* stream);
+
 /* prep_x_int8 / _prep_x_int8_kernel (fused_fp8_gemm.py:687-731): per-ROW amax (floor 1e-12), s = 127/amax,
  * codes = trunc(clamp(x*s, -128, 127)), scales[m] = amax/127. */
 int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes,

@@ -1,6 +1,8 @@
 // Activation preparation kernels: bf16 copy + per-call amax (FP8 path), per-call e4m3 codes
 // (large-M FP8 path) and per-row int8 codes (INT8 path).  All HBM/L2-bound elementwise work:
 // 128-bit loads and stores, one row segment per CTA, block reduction + one atomic per CTA.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace rwkvq {
@@ -221,6 +223,112 @@ __global__ void __launch_bounds__(kThreads) quant_int8_kernel(const void* x, int
     }
 }
 
+// ----------------------------------------------------------------------------------------
+// FP8 activation quantization in ONE launch: per-CTA partial maxima, a grid-wide rendezvous through a token that is
+// unique per launch (nothing has to be zeroed beforehand), then the code pass (second read of x hits L2).
+// The grid is launched cooperatively (all CTAs resident); the rendezvous spin is bounded all the same.
+constexpr int kFusedThreads = 512;
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kFusedThreads) actq_fp8_fused_kernel(const void* x, uint8_t* codes, float* amax_out, float* scale_out,
+                                                                      float* slots, uint32_t* flags, uint32_t token, int* status,
+                                                                      int M, int K, int64_t ldx, int64_t ldc, int div_mode,
+                                                                      int after_bf16, int from_bf16) {
+    __shared__ float sh[kFusedThreads / 32];
+    __shared__ float s_amax;
+    __shared__ int s_fail;
+    const int kv = K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // ---- pass 1: partial maximum of this CTA's rows
+    float m = 0.f;
+    for (int r = blockIdx.x; r < M; r += gridDim.x) {
+        const char* xr = reinterpret_cast<const char*>(x) + (int64_t)r * ldx * 2;
+        for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)i * 16);
+            if (DT == RWKVQ_F16 && after_bf16) {
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = cvt2<DT>(w[q]);
+                    m = fmaxf(m, fmaxf(fabsf(bf16_round(f.x)), fabsf(bf16_round(f.y))));
+                }
+            } else if (DT == RWKVQ_F16) {
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+                const __half2 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+                m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+            } else {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+                const __nv_bfloat162 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+                m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+            }
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) sh[warp] = m;
+    if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = sh[0];
+        for (int i = 1; i < kFusedThreads / 32; ++i) b = fmaxf(b, sh[i]);
+        slots[blockIdx.x] = b;
+        __threadfence();
+        st_release_u32(flags + blockIdx.x, token);
+    }
+    // ---- rendezvous: thread t waits for CTA t's flag, then the maxima are combined
+    float g = 0.f;
+    if ((int)threadIdx.x < (int)gridDim.x) {
+        bool ok = false;
+        for (int spin = 0; spin < (1 << 22); ++spin) {          // a few seconds at most
+            if (ld_acquire_u32(flags + threadIdx.x) == token) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (ok) g = __ldcg(slots + threadIdx.x);
+        else s_fail = 1;
+    }
+    g = warp_max(g);
+    __syncthreads();
+    if (lane == 0) sh[warp] = g;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = sh[0];
+        for (int i = 1; i < kFusedThreads / 32; ++i) b = fmaxf(b, sh[i]);
+        s_amax = b;
+        if (blockIdx.x == 0) {
+            *amax_out = b;
+            if (scale_out) *scale_out = div_mode_f32(b, 448.f, div_mode);
+        }
+        if (s_fail && status) atomicExch(status, RWKVQ_E_TIMEOUT);
+    }
+    __syncthreads();
+    if (s_fail) return;
+    // ---- pass 2: codes
+    const float inv = div_mode_f32(448.f, fmaxf(s_amax, 1e-12f), div_mode);
+    for (int r = blockIdx.x; r < M; r += gridDim.x) {
+        const char* xr = reinterpret_cast<const char*>(x) + (int64_t)r * ldx * 2;
+        uint8_t* cr = codes + (int64_t)r * ldc;
+        for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)i * 16);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float2 f = cvt2<DT>(w[q]);
+                if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                c[q] = e4m3x2(f.x * inv, f.y * inv);
+            }
+            *reinterpret_cast<uint2*>(cr + (size_t)i * 8) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+        }
+    }
+}
+
 __global__ void div_kernel(const float* a, const float* b, float* o, int64_t n, int mode) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) o[i] = div_mode_f32(a[i], b[i], mode);
@@ -312,6 +420,39 @@ int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, 
     else                      { if (vec) RWKVQ_Q(RWKVQ_BF16, true); else RWKVQ_Q(RWKVQ_BF16, false); }
 #undef RWKVQ_Q
     return check_launch("prep_x_int8");
+}
+
+int64_t rwkvq_actq_fp8_fused_scratch_bytes(void) { return 2 * 512 * 4; }
+
+int32_t rwkvq_actq_fp8_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                             float* amax, float* scale, void* scratch, int64_t scratch_bytes, int32_t* status, int32_t div_mode,
+                             uint32_t flags, void* stream) {
+    const char* who = "actq_fp8_fused";
+    RWKVQ_REQUIRE(x && codes && amax && scratch, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
+    RWKVQ_REQUIRE(M > 0 && K > 0 && K % 8 == 0 && M < (1 << 30), RWKVQ_E_SHAPE, "%s: M=%lld K=%lld (K must be a multiple of 8)", who, (long long)M, (long long)K);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K && ldc % 8 == 0 && ldc >= K && ((uintptr_t)codes & 7) == 0, RWKVQ_E_ALIGN,
+                  "%s: rows must be 16-byte (x) / 8-byte (codes) aligned", who);
+    RWKVQ_REQUIRE(scratch_bytes >= rwkvq_actq_fp8_fused_scratch_bytes() && ((uintptr_t)scratch & 3) == 0, RWKVQ_E_WORKSPACE,
+                  "%s: scratch of %lld bytes needed", who, (long long)rwkvq_actq_fp8_fused_scratch_bytes());
+    static std::atomic<uint32_t> next_token{0x9e3779b9u};
+    const uint32_t token = next_token.fetch_add(0x61c88647u) | 1u;
+    int grid = (int)std::min<int64_t>(M, std::min<int64_t>(512, 2 * (int64_t)sm_count()));
+    int after = (flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? 1 : 0, from_bf16 = (flags & RWKVQ_FLAG_QUANT_FROM_BF16) ? 1 : 0;
+    int m = (int)M, k = (int)K;
+    float* slots = reinterpret_cast<float*>(scratch);
+    uint32_t* fl = reinterpret_cast<uint32_t*>(scratch) + 512;
+    int* st_ptr = status;
+    void* args[] = {(void*)&x, (void*)&codes, (void*)&amax, (void*)&scale, (void*)&slots, (void*)&fl, (void*)&token, (void*)&st_ptr,
+                    (void*)&m, (void*)&k, (void*)&ldx, (void*)&ldc, (void*)&div_mode, (void*)&after, (void*)&from_bf16};
+    const void* fn = x_dtype == RWKVQ_F16 ? (const void*)actq_fp8_fused_kernel<RWKVQ_F16> : (const void*)actq_fp8_fused_kernel<RWKVQ_BF16>;
+    const cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kFusedThreads), args, 0, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return check_launch(who);
 }
 
 }  // extern "C"

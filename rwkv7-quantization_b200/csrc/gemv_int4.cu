@@ -164,9 +164,131 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_group_kernel(const I4Args a
     }
 }
 
-template <int D>
-static int32_t launch_i4(const I4Args& a, size_t smem, cudaStream_t st) {
-    auto kern = gemv_int4_group_kernel<D>;
+// ---- fast path: K a multiple of 4096, group 128, fp32 scales (zeros optional).  Each warp owns a CONTIGUOUS run of
+// units of its 8 rows, so the scales / zeros of four units are one 128-bit load per row, every address in the unrolled
+// body is a base pointer plus a compile-time offset, and a row streams 256 contiguous bytes per chunk.
+struct I4Quad {
+    uint4 w[4];
+    float4 s0, s1, z0, z1;      // scales / zeros of rows n0+2t and n0+2t+1 for the chunk's four groups
+};
+
+__global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4Args a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int units = a.K >> 7;
+    float* red = reinterpret_cast<float*>(smem);
+    float* xsum = red + kWarps * 4 * 32;
+    uint8_t* xs = reinterpret_cast<uint8_t*>(xsum + ((a.M * units + 3) & ~3));
+
+    griddep_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int ntile = (a.N + 7) >> 3;
+    const int tb = (int)((int64_t)ntile * blockIdx.x / gridDim.x), te = (int)((int64_t)ntile * (blockIdx.x + 1) / gridDim.x);
+    const int upw = units >> 3, nchunks = upw >> 2;           // units per warp (multiple of 4), chunks of 4 units
+    const float* scales = reinterpret_cast<const float*>(a.scales);
+
+    auto fetch = [&](int tile, int c) -> I4Quad {
+        I4Quad q;
+        const int n0 = tile << 3;
+        const uint8_t* wp = a.w + (int64_t)min(n0 + g, a.N - 1) * a.ldw + ((warp * upw + c * 4) << 6) + 16 * t;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q.w[j] = ldg_stream(wp + j * 64);
+        const int64_t i0 = (int64_t)min(n0 + 2 * t, a.N - 1) * a.ngroups + warp * upw + c * 4;
+        const int64_t i1 = (int64_t)min(n0 + 2 * t + 1, a.N - 1) * a.ngroups + warp * upw + c * 4;
+        q.s0 = __ldg(reinterpret_cast<const float4*>(scales + i0));
+        q.s1 = __ldg(reinterpret_cast<const float4*>(scales + i1));
+        if (a.zeros) {
+            q.z0 = __ldg(reinterpret_cast<const float4*>(a.zeros + i0));
+            q.z1 = __ldg(reinterpret_cast<const float4*>(a.zeros + i1));
+        } else {
+            q.z0 = make_float4(-8.f * q.s0.x, -8.f * q.s0.y, -8.f * q.s0.z, -8.f * q.s0.w);
+            q.z1 = make_float4(-8.f * q.s1.x, -8.f * q.s1.y, -8.f * q.s1.z, -8.f * q.s1.w);
+        }
+        return q;
+    };
+    I4Quad cur = fetch(min(tb, max(te - 1, 0)), 0);
+
+    griddep_wait();
+    {   // prologue: permuted fp16 activations (odd pairs / 16) and per-unit activation sums
+        const int kv = a.K >> 3;
+        const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+        for (int r = 0; r < a.M; ++r) {
+            const char* xr = reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx);
+            for (int i = threadIdx.x; i < kv; i += kThr) {
+                const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)i * 16);
+                uint4 p;
+                p.x = __byte_perm(v.x, v.z, 0x5410);
+                p.y = __byte_perm(v.x, v.z, 0x7632);
+                p.z = __byte_perm(v.y, v.w, 0x5410);
+                p.w = __byte_perm(v.y, v.w, 0x7632);
+                *reinterpret_cast<__half2*>(&p.y) = __hmul2(*reinterpret_cast<__half2*>(&p.y), sixteenth);
+                *reinterpret_cast<__half2*>(&p.w) = __hmul2(*reinterpret_cast<__half2*>(&p.w), sixteenth);
+                *reinterpret_cast<uint4*>(xs + (size_t)r * a.pitch + (size_t)i * 16) = p;
+            }
+        }
+        for (int i = warp; i < a.M * units; i += kWarps) {
+            const int r = i / units, u = i - r * units;
+            const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx) + ((size_t)u << 8) + lane * 8);
+            const float2 f0 = cvt2<RWKVQ_F16>(v.x), f1 = cvt2<RWKVQ_F16>(v.y);
+            const float sum = warp_sum((f0.x + f0.y) + (f1.x + f1.y));
+            if (lane == 0) xsum[i] = sum;
+        }
+        __syncthreads();
+    }
+    // this lane's activation rows (g and g + 8) at its warp's first unit
+    const uint8_t* xr0 = g < a.M ? xs + (size_t)g * a.pitch + ((size_t)(warp * upw) << 8) + t * 64 : nullptr;
+    const uint8_t* xr1 = g + 8 < a.M ? xs + (size_t)(g + 8) * a.pitch + ((size_t)(warp * upw) << 8) + t * 64 : nullptr;
+    const float* xs0p = xsum + (g < a.M ? g : 0) * units + warp * upw;
+    const float* xs1p = xsum + (g + 8 < a.M ? g + 8 : 0) * units + warp * upw;
+    const float m0 = g < a.M ? 1.f : 0.f, m1 = g + 8 < a.M ? 1.f : 0.f;
+
+    for (int tile = tb; tile < te; ++tile) {
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int ch = 0; ch < nchunks; ++ch) {
+            const I4Quad q = cur;
+            const bool last = ch + 1 == nchunks;
+            if (!last || tile + 1 < te) cur = fetch(last ? tile + 1 : tile, last ? 0 : ch + 1);
+            const float sc0[4] = {q.s0.x, q.s0.y, q.s0.z, q.s0.w}, sc1[4] = {q.s1.x, q.s1.y, q.s1.z, q.s1.w};
+            const float zr0[4] = {q.z0.x, q.z0.y, q.z0.z, q.z0.w}, zr1[4] = {q.z1.x, q.z1.y, q.z1.z, q.z1.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
+                const uint32_t wd[4] = {q.w[j].x, q.w[j].y, q.w[j].z, q.w[j].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
+                    if (xr0) a0 = *reinterpret_cast<const uint4*>(xr0 + ch * 1024 + j * 256 + i * 16);
+                    if (xr1) a1 = *reinterpret_cast<const uint4*>(xr1 + ch * 1024 + j * 256 + i * 16);
+                    const uint32_t hi = wd[i] >> 8;
+                    mma_f16((i & 1) ? cb : ca, a0.x, a1.x, a0.y, a1.y, wd[i] & 0x000F000Fu, wd[i] & 0x00F000F0u);
+                    mma_f16((i & 1) ? cb : ca, a0.z, a1.z, a0.w, a1.w, hi & 0x000F000Fu, hi & 0x00F000F0u);
+                }
+                const float xs0 = m0 * xs0p[ch * 4 + j], xs1 = m1 * xs1p[ch * 4 + j];
+                const float e0 = sc0[j] * 16777216.f, e1 = sc1[j] * 16777216.f;
+                tot[0] += e0 * (ca[0] + cb[0]) + zr0[j] * xs0;
+                tot[1] += e1 * (ca[1] + cb[1]) + zr1[j] * xs0;
+                tot[2] += e0 * (ca[2] + cb[2]) + zr0[j] * xs1;
+                tot[3] += e1 * (ca[3] + cb[3]) + zr1[j] * xs1;
+            }
+        }
+        const int n0 = tile << 3;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) red[(warp * 4 + j) * 32 + lane] = tot[j];
+        __syncthreads();
+        if (threadIdx.x < 128) {
+            const int j = threadIdx.x >> 5, l = threadIdx.x & 31;
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) s += red[(w * 4 + j) * 32 + l];
+            const int m = (l >> 2) + ((j & 2) ? 8 : 0), n = n0 + 2 * (l & 3) + (j & 1);
+            if (m < a.M && n < a.N) a.out[(int64_t)m * a.ldo + n] = __float2half_rn(s);
+        }
+        __syncthreads();
+    }
+}
+
+template <typename Kern>
+static int32_t launch_i4(Kern kern, const I4Args& a, size_t smem, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     int per_sm = 0;
@@ -224,7 +346,12 @@ int32_t rwkvq_gemv_int4_group(const void* x_f16, int64_t ldx, const uint8_t* pac
     a.x = (const __half*)x_f16; a.w = packed; a.scales = scales; a.zeros = zeros; a.out = (__half*)out_f16;
     a.ldx = ldx; a.ldw = ldw; a.ldo = ldo; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.group = group; a.scale_f16 = scale_is_f16;
     a.pitch = (int)(2 * K + 16); a.ngroups = (int)(K / group);
-    return (K / 128 > 4 * kWarps) ? launch_i4<8>(a, smem, (cudaStream_t)stream) : launch_i4<4>(a, smem, (cudaStream_t)stream);
+    const char* env = std::getenv("RWKVQ_INT4_FAST");
+    const bool fast = K % 4096 == 0 && group == 128 && !scale_is_f16 && !(env && env[0] == '0')
+                      && ((uintptr_t)scales & 15) == 0 && (zeros == nullptr || ((uintptr_t)zeros & 15) == 0);
+    if (fast) return launch_i4(gemv_int4_g128_kernel, a, smem, (cudaStream_t)stream);
+    return (K / 128 > 4 * kWarps) ? launch_i4(gemv_int4_group_kernel<8>, a, smem, (cudaStream_t)stream)
+                                  : launch_i4(gemv_int4_group_kernel<4>, a, smem, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -43,9 +43,7 @@ def linear_fp8(x, weight_info, out_dtype=torch.float16):
     scale = torch.empty(1, dtype=torch.float32, device=dev)
     out = torch.empty((m, n), dtype=torch.float16, device=dev)
     st = abi.stream_ptr()
-    abi.call("rwkvq_actq_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k, codes.data_ptr(),
-             k, amax.data_ptr(), scale.data_ptr(), abi.DIV_IEEE,
-             abi.FLAG_AMAX_AFTER_BF16 | abi.FLAG_QUANT_FROM_BF16, st)
+    f._actq_fp8(x2, codes, amax, scale, abi.DIV_IEEE, abi.FLAG_AMAX_AFTER_BF16 | abi.FLAG_QUANT_FROM_BF16, st)
     if f.ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, dev)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),

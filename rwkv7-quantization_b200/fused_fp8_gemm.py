@@ -176,6 +176,19 @@ def _fp8_gemv(x2, w, w_ts, awq, flags):
     return out
 
 
+def _actq_fp8(x2, codes, amax, scale, div, flags, st):
+    """FP8 activation codes + per-call amax: one cooperative launch (K a multiple of 8), else memset + two kernels."""
+    m, k = x2.shape
+    ldx = x2.stride(0) if m > 1 else k
+    if k % 8 == 0 and m > 0 and os.environ.get("RWKVQ_ACTQ", "fused") == "fused":
+        scratch = torch.empty(1024, dtype=torch.int32, device=x2.device)
+        abi.call("rwkvq_actq_fp8_fused", x2.data_ptr(), abi.dtype_code(x2), m, k, ldx, codes.data_ptr(), k, amax.data_ptr(),
+                 abi.ptr(scale), scratch.data_ptr(), scratch.numel() * 4, None, div, flags, st)
+    else:
+        abi.call("rwkvq_actq_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, ldx, codes.data_ptr(), k, amax.data_ptr(),
+                 abi.ptr(scale), div, flags, st)
+
+
 def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     """Activation quantization kernels, then the GEMM on codes (any M)."""
     m, k = x2.shape
@@ -184,8 +197,7 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     amax = torch.empty(1, dtype=torch.float32, device=x2.device)
     out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
     st = abi.stream_ptr()
-    abi.call("rwkvq_actq_fp8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
-             codes.data_ptr(), k, amax.data_ptr(), None, abi.DEFAULT_DIV, act_flags, st)
+    _actq_fp8(x2, codes, amax, None, abi.DEFAULT_DIV, act_flags, st)
     if ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
