@@ -27,19 +27,28 @@
 
 namespace rwkvq {
 
-// One chunk of the K loop: D ring slots are consumed and refilled.  The unrolled body touches memory only through
-// base pointers plus compile-time offsets (slot j lies 512*j bytes after slot 0 in the weight row and in the
-// activation tile), so a slot costs a handful of instructions.  PF: a next chunk exists and is prefetched;
-// CHECK: K is not a multiple of the chunk span, so every slot is tested against K.
-template <int QT, int MT, int D, bool WIDE, bool PF, bool CHECK, typename T>
-__device__ __forceinline__ void chunk_body(uint4 (&ring)[D], T (&c)[MT][4], T (&c2)[MT][4], const uint8_t* pf, int pfk, int k0, int K,
+// ---- asynchronous 16-byte copies global -> shared (bypassing L1): the bytes in flight live in shared memory, not in
+// registers, so a CTA keeps S-1 whole chunks (S-1 x D x 4 KB) of weights in flight.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int n = valid ? 16 : 0;                  // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// One chunk of the K loop: D slots of this thread's staged weights (slot j lies j*4096 bytes further in the stage and
+// 512*j bytes further along K) against the activation tile.  All addresses are base pointers plus compile-time
+// offsets.  CHECK: K is not a multiple of the chunk span, so every slot is tested against K (staged bytes beyond K
+// are zero, the activation loads are skipped).
+template <int QT, int MT, int D, bool WIDE, bool CHECK, typename T>
+__device__ __forceinline__ void chunk_body(const uint8_t* stage, T (&c)[MT][4], T (&c2)[MT][4], int k0, int K,
                                            const uint8_t* const (&xr)[MT][2]) {
     constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;        // bytes per activation in the shared-memory tile
 #pragma unroll
     for (int j = 0; j < D; ++j) {
-        const uint4 wv = ring[j];
-        if (PF && (!CHECK || pfk + j * 512 < K)) ring[j] = ldg_stream(pf + j * 512);
-        else ring[j] = make_uint4(0, 0, 0, 0);
+        const uint4 wv = *reinterpret_cast<const uint4*>(stage + j * 4096);
         const bool kin = !CHECK || (k0 + j * 512 < K);
         if constexpr (QT == QT_FP8 && WIDE) {
             // widen the 16 weight bytes to f16 pairs; four m16n8k16 MMAs per 16 bytes on two accumulators
@@ -74,52 +83,62 @@ __device__ __forceinline__ void chunk_body(uint4 (&ring)[D], T (&c)[MT][4], T (&
 }
 
 // WIDE (FP8 only): activations kept as f16 values and weights widened in registers (m16n8k16.f16) instead of
-// e4m3 codes multiplied by mma.sync.m16n8k32.e4m3.
-template <int QT, int DT, int MT, int D, bool WIDE>
-__global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W8Args a) {
+// e4m3 codes multiplied by mma.sync.m16n8k32.e4m3.  S: stages of the shared-memory weight ring.
+template <int QT, int DT, int MT, int D, bool WIDE, int S>
+__global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
     extern __shared__ __align__(16) uint8_t smem[];
-    // layout: red[kWarps][MT*4][32] | xs[32] | sh[8] | xq[M][pitch]
+    // layout: red[kWarps][MT*4][32] | xs[32] | sh[8] | ring[S][D][256] x 16 B | xq[M][pitch]
     T* red = reinterpret_cast<T*>(smem);
     float* xs = reinterpret_cast<float*>(smem + kWarps * MT * 4 * 32 * 4);
     float* sh = xs + 32;
-    uint8_t* xq = reinterpret_cast<uint8_t*>(sh + 8);
+    uint8_t* ring = reinterpret_cast<uint8_t*>(sh + 8);
+    uint8_t* xq = ring + (size_t)S * D * 4096;
 
     griddep_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int ntile = (a.N + 7) >> 3;
-    const int64_t total = (int64_t)a.nmat * ntile;
-    const int64_t tb = total * blockIdx.x / gridDim.x, te = total * (blockIdx.x + 1) / gridDim.x;
+    const int total = a.nmat * ntile;
+    const int tb = (int)((int64_t)total * blockIdx.x / gridDim.x), te = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
     const int units = (a.K + 63) >> 6;
     const int upw = (units + kWarps - 1) / kWarps;   // 64-byte units per warp and row tile
     const int nchunks = (upw + D - 1) / D;
     const int koff = (warp << 6) + 16 * t;            // this lane's byte offset inside a row for slot 0
+    const bool check = (a.K % (D * 512)) != 0;
+    uint8_t* my_ring = ring + threadIdx.x * 16;       // this thread's 16 bytes of every slot
 
-    auto tile_base = [&](int64_t tile) -> const uint8_t* {
-        const int mat = (int)(tile / ntile);
-        const int n0 = (int)(tile - (int64_t)mat * ntile) << 3;
-        return a.w[mat] + (int64_t)min(n0 + g, a.N - 1) * a.ldw + koff;
-    };
-    auto fetch = [&](const uint8_t* base, int c, int j) -> uint4 {
-        const int off = (c * D + j) * (kWarps << 6);
-        return (base != nullptr && koff + off < a.K) ? ldg_stream(base + off) : make_uint4(0, 0, 0, 0);
-    };
-
-    uint4 ring[D];
-    const uint8_t* cur = tb < te ? tile_base(tb) : nullptr;
+    // producer side of the ring: chunk (itile, ich) goes to stage istage; one commit group per chunk
+    int itile = tb, ich = 0, istage = 0;
+    auto issue = [&]() {
+        if (itile < te) {
+            const int mat = itile >= 2 * ntile ? 2 : (itile >= ntile ? 1 : 0);
+            const int n0 = (itile - mat * ntile) << 3;
+            const uint8_t* src = a.w[mat] + (int64_t)min(n0 + g, a.N - 1) * a.ldw + koff + ich * D * 512;
+            uint8_t* dst = my_ring + (size_t)istage * D * 4096;
 #pragma unroll
-    for (int j = 0; j < D; ++j) ring[j] = fetch(cur, 0, j);
+            for (int j = 0; j < D; ++j) {
+                const bool valid = !check || (koff + (ich * D + j) * 512 < a.K);
+                cp_async16(dst + j * 4096, valid ? src + j * 512 : a.w[mat], valid);
+            }
+            if (++ich == nchunks) { ich = 0; ++itile; }
+        }
+        cp_async_commit();
+        if (++istage == S) istage = 0;
+    };
+#pragma unroll
+    for (int i = 0; i < S - 1; ++i) issue();
 
     griddep_wait();   // activations may come from the previous kernel; results may overwrite what it read
 
-    int cur_mat = -1;
+    int cur_mat = -1, stage = 0;
     float out_scale = 0.f;   // FP8: (amax/448)*w_scale
     float wscale = 0.f;      // INT8: w_scale
-    for (int64_t tile = tb; tile < te; ++tile) {
-        const int mat = (int)(tile / ntile);
-        const int n0 = (int)(tile - (int64_t)mat * ntile) << 3;
+    constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;
+    for (int tile = tb; tile < te; ++tile) {
+        const int mat = tile >= 2 * ntile ? 2 : (tile >= ntile ? 1 : 0);
+        const int n0 = (tile - mat * ntile) << 3;
         if (mat != cur_mat) {
             cur_mat = mat;
             __syncthreads();   // nobody still reads the previous matrix's codes
@@ -132,42 +151,32 @@ __global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W
             }
             __syncthreads();
         }
-        const uint8_t* nxt = tile + 1 < te ? tile_base(tile + 1) : nullptr;
-
         T c[MT][4], c2[MT][4];
 #pragma unroll
         for (int i = 0; i < MT; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) c[i][j] = c2[i][j] = 0;
-
         // this lane's rows of the activation tile (rows g and g+8 of each 16-row block); null = row beyond M
-        constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;
         const uint8_t* xr[MT][2];
 #pragma unroll
         for (int i = 0; i < MT; ++i) {
             xr[i][0] = i * 16 + g < a.M ? xq + (size_t)(i * 16 + g) * a.pitch + (size_t)koff * AB : nullptr;
             xr[i][1] = i * 16 + g + 8 < a.M ? xq + (size_t)(i * 16 + g + 8) * a.pitch + (size_t)koff * AB : nullptr;
         }
-        const bool check = (a.K % (D * 512)) != 0;
         for (int ch = 0; ch < nchunks; ++ch) {
-            const bool last = ch + 1 == nchunks;
-            const uint8_t* pf = last ? nxt : cur + (ch + 1) * D * 512;
-            const int pfk = koff + (last ? 0 : (ch + 1) * D * 512), k0 = koff + ch * D * 512;
+            issue();                       // keep S-1 chunks in flight
+            cp_async_wait<S - 1>();        // this thread's copies of the current chunk have landed
             const uint8_t* xc[MT][2];
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
                 xc[i][0] = xr[i][0] ? xr[i][0] + (size_t)ch * D * 512 * AB : nullptr;
                 xc[i][1] = xr[i][1] ? xr[i][1] + (size_t)ch * D * 512 * AB : nullptr;
             }
-            if (check) {
-                if (pf) chunk_body<QT, MT, D, WIDE, true, true>(ring, c, c2, pf, pfk, k0, a.K, xc);
-                else chunk_body<QT, MT, D, WIDE, false, true>(ring, c, c2, pf, pfk, k0, a.K, xc);
-            } else {
-                if (pf) chunk_body<QT, MT, D, WIDE, true, false>(ring, c, c2, pf, pfk, k0, a.K, xc);
-                else chunk_body<QT, MT, D, WIDE, false, false>(ring, c, c2, pf, pfk, k0, a.K, xc);
-            }
+            const uint8_t* st = my_ring + (size_t)stage * D * 4096;
+            if (check) chunk_body<QT, MT, D, WIDE, true>(st, c, c2, koff + ch * D * 512, a.K, xc);
+            else chunk_body<QT, MT, D, WIDE, false>(st, c, c2, koff + ch * D * 512, a.K, xc);
+            if (++stage == S) stage = 0;
         }
-        cur = nxt;
 #pragma unroll
         for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -201,10 +210,11 @@ __global__ void __launch_bounds__(kThr, D == 8 ? 2 : 3) gemv_w8a8_kernel(const W
         }
         __syncthreads();
     }
+    cp_async_wait<0>();
 }
 
-static size_t smem_bytes(int MT, int M, int pitch) {
-    return (size_t)kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + (size_t)M * pitch;
+static size_t smem_bytes(int MT, int M, int pitch, int D, int S) {
+    return (size_t)kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + (size_t)S * D * 4096 + (size_t)M * pitch;
 }
 
 constexpr size_t kFusedSmemMax = 200 * 1024;
@@ -227,9 +237,9 @@ static bool use_pdl() {
     return on;
 }
 
-template <int QT, int DT, int MT, int D, bool WIDE>
+template <int QT, int DT, int MT, int D, bool WIDE, int S>
 static int32_t launch_one(const W8Args& a, int64_t tiles, size_t smem, cudaStream_t st) {
-    auto kern = gemv_w8a8_kernel<QT, DT, MT, D, WIDE>;
+    auto kern = gemv_w8a8_kernel<QT, DT, MT, D, WIDE, S>;
     // per instantiation and device: opt in to large dynamic shared memory and ask how many CTAs fit on an SM
     static thread_local int cfg_dev = -1;
     static thread_local size_t cfg_smem = ~size_t(0);
@@ -265,16 +275,26 @@ static int32_t launch_one(const W8Args& a, int64_t tiles, size_t smem, cudaStrea
     return check_launch("gemv_w8a8");
 }
 
+constexpr size_t kTwoPerSm = 110 * 1024;     // shared memory per CTA that still lets two CTAs share an SM
+
+template <int QT, int DT, int MT, int D, bool WIDE>
+static int32_t dispatch_s(const W8Args& a, int64_t tiles, cudaStream_t st) {
+    const size_t s3 = smem_bytes(MT, a.M, a.pitch, D, 3), s2 = smem_bytes(MT, a.M, a.pitch, D, 2);
+    if (s3 <= kTwoPerSm) return launch_one<QT, DT, MT, D, WIDE, 3>(a, tiles, s3, st);
+    RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the fused kernel's shared memory", a.M, a.K);
+    return launch_one<QT, DT, MT, D, WIDE, 2>(a, tiles, s2, st);
+}
+
 template <int QT, int DT>
-static int32_t dispatch_mt(const W8Args& a, int64_t tiles, size_t smem, cudaStream_t st) {
+static int32_t dispatch_mt(const W8Args& a, int64_t tiles, cudaStream_t st) {
     const int units = (a.K + 63) / 64;
-    const bool deep = units > 4 * kWarps;          // more than 4 units per warp and tile: keep 8 loads in flight
+    const bool deep = units > 4 * kWarps;          // more than 4 units per warp and tile: chunks of 8 slots
     if (QT == QT_FP8 && fp8_wide()) {
-        if (a.M <= 16) return deep ? launch_one<QT, DT, 1, 8, true>(a, tiles, smem, st) : launch_one<QT, DT, 1, 4, true>(a, tiles, smem, st);
-        return deep ? launch_one<QT, DT, 2, 8, true>(a, tiles, smem, st) : launch_one<QT, DT, 2, 4, true>(a, tiles, smem, st);
+        if (a.M <= 16) return deep ? dispatch_s<QT, DT, 1, 8, true>(a, tiles, st) : dispatch_s<QT, DT, 1, 4, true>(a, tiles, st);
+        return deep ? dispatch_s<QT, DT, 2, 8, true>(a, tiles, st) : dispatch_s<QT, DT, 2, 4, true>(a, tiles, st);
     }
-    if (a.M <= 16) return deep ? launch_one<QT, DT, 1, 8, false>(a, tiles, smem, st) : launch_one<QT, DT, 1, 4, false>(a, tiles, smem, st);
-    return deep ? launch_one<QT, DT, 2, 8, false>(a, tiles, smem, st) : launch_one<QT, DT, 2, 4, false>(a, tiles, smem, st);
+    if (a.M <= 16) return deep ? dispatch_s<QT, DT, 1, 8, false>(a, tiles, st) : dispatch_s<QT, DT, 1, 4, false>(a, tiles, st);
+    return deep ? dispatch_s<QT, DT, 2, 8, false>(a, tiles, st) : dispatch_s<QT, DT, 2, 4, false>(a, tiles, st);
 }
 
 template <int QT>
@@ -297,10 +317,10 @@ static int32_t run_fused(W8Args a, int x_dtype, cudaStream_t st, const char* who
     // shared-memory row pitch of the activation tile: int8 codes (1 B) or f16 values of the e4m3 codes (2 B);
     // the odd 64 / 16 bytes keep the fragment loads of different rows on different banks
     a.pitch = (QT == QT_FP8 && fp8_wide()) ? ((2 * a.K + 127) / 128) * 128 + 16 : ((a.K + 127) / 128) * 128 + 64;
-    const size_t smem = smem_bytes(MT, a.M, a.pitch);
-    RWKVQ_REQUIRE(smem <= kFusedSmemMax, RWKVQ_E_SHAPE, "%s: M*K = %d*%d does not fit the fused kernel's shared memory", who, a.M, a.K);
+    (void)MT;
     const int64_t tiles = (int64_t)a.nmat * ((a.N + 7) / 8);
-    return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16>(a, tiles, smem, st) : dispatch_mt<QT, RWKVQ_BF16>(a, tiles, smem, st);
+    RWKVQ_REQUIRE(tiles < (int64_t(1) << 30), RWKVQ_E_SHAPE, "%s: N too large", who);
+    return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16>(a, tiles, st) : dispatch_mt<QT, RWKVQ_BF16>(a, tiles, st);
 }
 
 }  // namespace rwkvq

@@ -33,7 +33,7 @@ FUSED_M_MAX = 512      # kept for importers (fused_fp8_gemm.py:1101); this build
 USE_CUDA_GRAPH = False  # kept for importers (fused_fp8_gemm.py:941); graphs are the caller's business here
 
 GEMV_M_MAX = 32
-_GEMV_SMEM_BUDGET = 200 * 1024 - 5 * 1024
+_GEMV_SMEM_BUDGET = 200 * 1024 - 70 * 1024     # what the activation tile may take beside the weight ring
 TC_FUSED_M_MAX = 4                 # rows up to which the activation quantization rides inside the streaming kernel
 _TC_CACHE_MAX = 100 * 1024        # shared memory for the activations (2 B) and their codes (1 B) in the fused kernel
 ROUTE = os.environ.get("RWKVQ_ROUTE", "auto").lower()   # auto | tc | mma
