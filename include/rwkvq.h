@@ -258,6 +258,22 @@ int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_b
                          int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                          void* stream);
 
+/* Many-token NVFP4 projection on the block-scaled tensor cores (tcgen05 kind::mxf4nvf4, 16-wide blocks): the path
+ * the reference's reports call "block-scaled NVFP4 MMAs" (11_fused_gemm_ops_en.md:20-26).  Same arithmetic and
+ * operands as rwkvq_gemv_nvfp4 for any M, except that both scale arrays are given BLOCKED: 512-byte chunks
+ * [ceil(rows/256)*2 row tiles of 128][K/64][(r%32)*16 + (r/32)*4 + (k/16)%4], the order in which the tensor core
+ * takes them from tensor memory; rows past `rows` hold zero.  rwkvq_nvfp4_pack_scales converts row-major scales
+ * [rows, K/16] (once per weight; per call for activations) into a buffer of rwkvq_nvfp4_blocked_scale_bytes(rows, K).
+ * K must be a multiple of 256; code rows 16-byte aligned.  workspace (may be NULL) receives the status word read by
+ * rwkvq_workspace_status: every wait in the kernel is bounded and a timeout is reported there. */
+int64_t rwkvq_nvfp4_blocked_scale_bytes(int64_t rows, int64_t K);
+int32_t rwkvq_nvfp4_pack_scales(const uint8_t* block_scales, int64_t lds, int64_t rows, int64_t K, uint8_t* blocked,
+                                void* stream);
+int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts,
+                            const uint8_t* w_codes, int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale,
+                            void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
+                            int64_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  rwkvq_tc_gemm_fp8 (M <= 128) for callers that cannot supply device scratch --
  * a host runtime that owns every byte of device memory and forbids allocation inside its serving loop, or code
  * running where cudaMalloc is not allowed.  The scratch is an 8 MiB array built into the library on each GPU; no

@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "tc_common.cuh"
+#include "tc_host.cuh"
 #include "w8a8.cuh"
 
 namespace rwkvq {
@@ -537,38 +538,6 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) p = nullptr;
-        return reinterpret_cast<EncodeTiledFn>(p);
-    }();
-    return fn;
-}
-
-// uint8 matrix [rows, K] with `ld` bytes between rows, tiles of box_rows x 128 bytes, 128-byte swizzle, zero fill
-static int32_t make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t K, int64_t ld, int box_rows, const char* who) {
-    EncodeTiledFn fn = encode_fn();
-    RWKVQ_REQUIRE(fn != nullptr, RWKVQ_E_LAUNCH, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
-    RWKVQ_REQUIRE(aligned16(ptr) && ld % 16 == 0 && ld >= K, RWKVQ_E_ALIGN, "%s: TMA needs a 16-byte aligned base and row pitch", who);
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld};
-    const cuuint32_t box[2] = {(cuuint32_t)kChunk, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    RWKVQ_REQUIRE(r == CUDA_SUCCESS, RWKVQ_E_LAUNCH, "%s: cuTensorMapEncodeTiled failed (%d)", who, (int)r);
-    return RWKVQ_OK;
-}
-
-constexpr int64_t kWsCounterInts = 1024;                       // arrival counters (row tiles of all matrices)
-constexpr int64_t kWsHeaderBytes = (kWsCounterInts + 16) * 4;  // counters + status word, then the partial sums
 constexpr size_t kTcSmemBudget = 225 * 1024;
 constexpr size_t kTcSmemBudgetHalf = 110 * 1024;   // SWAP: two CTAs per SM, so the next launch can set up early
 constexpr size_t kTcCacheMax = 100 * 1024;      // FUSED: the activations of a call and their codes live in shared memory

@@ -14,6 +14,8 @@ an addition behind the same conventions as fp8_ops.py:
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 import rwkvq_abi as abi
@@ -21,6 +23,7 @@ import rwkvq_abi as abi
 E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 BLOCK = 16
 GEMV_ROWS = 16
+TC_MIN_M = 16      # more tokens than this go to the tensor-core GEMM
 
 
 def _e2m1_codes(v: torch.Tensor) -> torch.Tensor:
@@ -84,21 +87,53 @@ def quantize_activations_nvfp4(x: torch.Tensor):
     return codes, bs, pts
 
 
+def pack_scales(block_scales: torch.Tensor, k: int) -> torch.Tensor:
+    """Row-major scales [rows, K/16] -> the blocked order the tensor core reads (512-byte chunks per 128 rows x 64 k)."""
+    rows = block_scales.shape[0]
+    out = torch.empty(int(abi.lib().rwkvq_nvfp4_blocked_scale_bytes(rows, k)), dtype=torch.uint8, device=block_scales.device)
+    abi.call("rwkvq_nvfp4_pack_scales", block_scales.data_ptr(), block_scales.stride(0), rows, k, out.data_ptr(), abi.stream_ptr())
+    return out
+
+
+def _blocked_weight_scales(weight_info, k: int) -> torch.Tensor:
+    """The weight's scales in blocked order, packed on first use and kept in the weight-info dict."""
+    blk = weight_info.get("block_scale_blocked")
+    if blk is None or blk.device != weight_info["block_scale"].device:
+        blk = pack_scales(weight_info["block_scale"], k)
+        weight_info["block_scale_blocked"] = blk
+    return blk
+
+
+def _route(m: int, k: int) -> str:
+    """'tc' = block-scaled tensor-core GEMM (more than TC_MIN_M tokens, K a multiple of 256), 'gemv' otherwise."""
+    forced = os.environ.get("RWKVQ_NVFP4_ROUTE", "auto")
+    if forced == "gemv" or k % 256 != 0:
+        return "gemv"
+    return "tc" if (forced == "tc" or m > TC_MIN_M) else "gemv"
+
+
 def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
-    """W4A4 projection: activations quantized per call, weights streamed in packed form."""
+    """W4A4 projection: activations quantized per call, weights streamed in packed form.  Few tokens run the
+    weight-streaming GEMV; more than TC_MIN_M tokens run the tcgen05 block-scaled GEMM."""
     w, wbs, wts = weight_info["weight"], weight_info["block_scale"], weight_info["tensor_scale"]
     n, k = w.shape[0], w.shape[1] * 2
     codes, bs, pts = quantize_activations_nvfp4(x)
     m = codes.shape[0]
     out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
-    rows = GEMV_ROWS
-    while rows > 1 and abi.lib().rwkvq_gemv_nvfp4_smem_bytes(rows, k) > 200 * 1024:
-        rows //= 2
     wts = wts.reshape(1)
-    for r0 in range(0, m, rows):
-        r = min(rows, m - r0)
-        abi.call("rwkvq_gemv_nvfp4", codes[r0:].data_ptr(), k // 2, bs[r0:].data_ptr(), k // BLOCK, pts.data_ptr(),
-                 w.data_ptr(), w.stride(0), wbs.data_ptr(), wbs.stride(0), wts.data_ptr(), out[r0:].data_ptr(), n, r, n, k,
-                 abi.stream_ptr())
+    if _route(m, k) == "tc":
+        ws = abi.workspace(1, 1, 1, 1, codes.device)
+        a_blk, w_blk = pack_scales(bs, k), _blocked_weight_scales(weight_info, k)     # both alive until the launch
+        abi.call("rwkvq_tc_gemm_nvfp4", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),
+                 w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), n, m, n, k, ws.data_ptr(), ws.numel(), abi.stream_ptr())
+    else:
+        rows = GEMV_ROWS
+        while rows > 1 and abi.lib().rwkvq_gemv_nvfp4_smem_bytes(rows, k) > 200 * 1024:
+            rows //= 2
+        for r0 in range(0, m, rows):
+            r = min(rows, m - r0)
+            abi.call("rwkvq_gemv_nvfp4", codes[r0:].data_ptr(), k // 2, bs[r0:].data_ptr(), k // BLOCK, pts.data_ptr(),
+                     w.data_ptr(), w.stride(0), wbs.data_ptr(), wbs.stride(0), wts.data_ptr(), out[r0:].data_ptr(), n, r, n, k,
+                     abi.stream_ptr())
     out = out.reshape(*x.shape[:-1], n)
     return out if out_dtype in (None, out.dtype) else out.to(out_dtype)

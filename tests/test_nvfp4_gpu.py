@@ -90,3 +90,42 @@ def test_config5_ffn_shapes(nf):
     x = gen(10, (4096, 4096), 1.0, torch.bfloat16)
     oinfo = {"weight": info["weight"], "block_scale": info["block_scale"].view(torch.uint8), "tensor_scale": info["tensor_scale"]}
     assert rel_err(nf.linear_nvfp4(x.cuda(), dev(info)), O.linear_nvfp4(x, oinfo)) <= 1e-2
+
+
+def test_pack_scales_blocked_order(nf):
+    """Blocked scale order: 512-byte chunks per (128-row tile, 64 k), byte (r%32)*16 + (r/32)*4 + (k/16)%4; row tiles
+    padded to a multiple of 256 rows with zeros."""
+    import numpy as np
+    rows, k = 300, 512
+    g = torch.Generator().manual_seed(3)
+    sf = torch.randint(0, 256, (rows, k // 16), generator=g, dtype=torch.uint8)
+    got = nf.pack_scales(sf.cuda(), k).cpu().numpy()
+    tiles, k64 = ((rows + 255) // 256) * 2, k // 64
+    want = np.zeros((tiles, k64, 512), dtype=np.uint8)
+    src = sf.numpy()
+    for r in range(rows):
+        for b in range(k // 16):
+            want[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4] = src[r, b]
+    assert got.shape[0] == want.size and (got == want.reshape(-1)).all()
+
+
+@pytest.mark.parametrize("bn", ["128", "256"])
+@pytest.mark.parametrize("m,n,k", [(17, 128, 256), (130, 520, 1024), (300, 384, 2048), (128, 2048, 4096), (513, 1000, 768)])
+def test_tensor_core_route(nf, monkeypatch, bn, m, n, k):
+    """The tcgen05 block-scaled GEMM (both tile widths) against the oracle and against the GEMV route; ragged M and N."""
+    import rwkvq_abi as abi
+    monkeypatch.setenv("RWKVQ_NF4_BN", bn)
+    w = gen(n * 3 + k, (n, k), (1.0 / k) ** 0.5)
+    info = dev(nf.quantize_to_nvfp4(w))
+    x = gen(m + 11, (m, k), 1.0, torch.bfloat16)
+    x[m // 2].zero_()
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "tc")
+    out = nf.linear_nvfp4(x.cuda(), info)
+    torch.cuda.synchronize()
+    assert abi.workspace_status(abi.workspace(1, 1, 1, 1, out.device)) == 0
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "gemv")
+    via_gemv = nf.linear_nvfp4(x.cuda(), info)
+    assert rel_err(out, via_gemv) <= 2e-3
+    oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
+             "tensor_scale": info["tensor_scale"].cpu()}
+    assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
