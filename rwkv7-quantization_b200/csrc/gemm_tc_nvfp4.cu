@@ -333,7 +333,10 @@ int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* 
                   "%s: the workspace needs at least %lld bytes, 16-byte aligned", who, (long long)kWsHeaderBytes);
     const char* bn_env = std::getenv("RWKVQ_NF4_BN");          // read per call: a test switches tiles in one process
     const int forced_bn = bn_env ? std::atoi(bn_env) : 0;
-    const int bn = forced_bn == 128 || forced_bn == 256 ? forced_bn : 128;
+    // 256-row weight tiles halve the activation re-reads per flop but keep one accumulator; they pay once there are
+    // enough of them to fill the SMs
+    const int64_t tiles256 = ((M + kNfTileM - 1) / kNfTileM) * ((N + 255) / 256);
+    const int bn = forced_bn == 128 || forced_bn == 256 ? forced_bn : (tiles256 * 4 >= (int64_t)sm_count() * 3 ? 256 : 128);
     NfArgs a{};
     a.sfa = a_scales_blocked; a.sfw = w_scales_blocked; a.a_pts = a_pts; a.w_pts = w_tscale; a.out = (__half*)out_f16; a.ldo = ldo;
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
