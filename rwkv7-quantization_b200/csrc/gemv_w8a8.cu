@@ -1,25 +1,31 @@
 // W8A8 projections for small M (decode): FP8 e4m3 x e4m3 and INT8 x INT8, single matrix or r/k/v in one launch.
 //
-// The kernel is HBM-bound: the weight matrix [N,K] (one byte per element) is read exactly once with 128-bit
-// streaming loads straight into registers, and those registers ARE the B fragments of mma.sync.m16n8k32
-// (8 weight rows x 32 k per instruction): lane (g = lane/4, t = lane%4) loads the 16 bytes W[n0+g][k0+16t ..+15]
-// and feeds them to two MMAs.  An MMA sums over its 32 k-slots, so the slots may be filled in any order as long
-// as A and B agree; the A fragment (quantized activations, 16 token rows) is read with the same permutation
-// from the code tile in shared memory.
+// The kernel is HBM-bound and written for instruction count: at the HBM rate an SM has about 88 issue slots per
+// 512 bytes of weights, and everything that is not a copy, a shared-memory load or an MMA eats into them.
 //
-// Work split: a CTA is 8 warps working on the same 8 weight rows, each warp on every 8th 64-byte column unit
-// (split-K inside the CTA, fixed-order reduction through shared memory, so results are run-to-run identical).
-// CTAs are persistent: each takes a contiguous range of the (matrix, row-tile) list, so the activation
-// quantization of the prologue is done once per CTA and matrix.
+// Data path.  The weight matrix [N,K] (one byte per element) is read exactly once.  A warp owns 8 weight rows
+// (one "row tile") over a contiguous K range; lane (g = lane/4, t = lane%4) copies the 16 bytes
+// W[n0+g][k0+16t .. +15] of each 64-byte unit with cp.async straight into its own 16 bytes of a per-warp ring in
+// shared memory, reads them back with one 128-bit load, and they ARE the B fragments of two mma.sync.m16n8k32
+// (INT8) or, widened to f16 in registers, of four m16n8k16 (FP8: mma.sync has no fast e4m3 path on sm_100).
+// An MMA sums over its k-slots, so the slots may be filled in any order as long as A and B agree; the A fragment
+// (quantized activations) is read with the same permutation from the activation tile in shared memory.
+// All addresses inside a chunk of D units are a base register plus a compile-time offset.
 //
-// Latency hiding: every lane keeps a ring of D weight loads in flight; a consumed slot is refilled at once with
-// the unit D steps ahead, across row-tile boundaries, and the first D loads are issued BEFORE the prologue.
-// With programmatic dependent launch the whole prefetch also overlaps the tail of the previous kernel in the
-// stream: only the weights (never written by any kernel) are touched before griddepcontrol.wait.
+// Work split.  A CTA (8 warps, two CTAs per SM) takes a contiguous range of the row tiles of ONE matrix and works
+// through it in rounds of R tiles (R = 1, 2, 4 or 8, chosen on the host so that a CTA usually needs one round);
+// 8/R warps share a tile, each with its own contiguous part of K, and add their partial sums in a fixed order
+// through shared memory (run-to-run identical results).  R = 8: no reduction, the lanes store their results.
+// A-fragment rows beyond M are read from row M-1: they only feed accumulator rows that are never stored.
+//
+// Latency hiding.  Every warp keeps S-1 chunks (D x 512 bytes each) in flight; the ring runs ahead across rounds
+// and its first S-1 chunks are issued BEFORE the prologue.  With programmatic dependent launch that prefetch also
+// overlaps the tail of the previous kernel in the stream: only the weights (never written by any kernel) are
+// touched before griddepcontrol.wait.
 //
 // Fused prologue (what prep_x / prep3_x / prep_x_int8 + the in-kernel quantization of the reference do):
 //   FP8 : amax over the whole [M,K] call, inv = 448/max(amax,1e-12), code = e4m3(clamp(bf16(x)*inv)),
-//         result scale (amax/448)*w_scale.
+//         result scale (amax/448)*w_scale; the codes are kept as f16 values (2 bytes) in shared memory.
 //   INT8: per row amax, s = 127/amax, code = trunc(clamp(x*s,-128,127)), row scale amax/127.
 #include <cstdlib>
 
@@ -27,207 +33,261 @@
 
 namespace rwkvq {
 
-// ---- asynchronous 16-byte copies global -> shared (bypassing L1): the bytes in flight live in shared memory, not in
-// registers, so a CTA keeps S-1 whole chunks (S-1 x D x 4 KB) of weights in flight.
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    const int n = valid ? 16 : 0;                  // 0 source bytes: the 16 destination bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
-}
+constexpr int kGemvD = 4;                 // 64-byte units per chunk (one cp.async group): 2 KB per warp
+
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// One chunk of the K loop: D slots of this thread's staged weights (slot j lies j*4096 bytes further in the stage and
-// 512*j bytes further along K) against the activation tile.  All addresses are base pointers plus compile-time
-// offsets.  CHECK: K is not a multiple of the chunk span, so every slot is tested against K (staged bytes beyond K
-// are zero, the activation loads are skipped).
-template <int QT, int MT, int D, bool WIDE, bool CHECK, typename T>
-__device__ __forceinline__ void chunk_body(const uint8_t* stage, T (&c)[MT][4], T (&c2)[MT][4], int k0, int K,
-                                           const uint8_t* const (&xr)[MT][2]) {
-    constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;        // bytes per activation in the shared-memory tile
+// The D asynchronous 16-byte copies (global -> shared, bypassing L1) of one chunk: slot J lies J*64 bytes further
+// along the weight row and J*512 bytes further in the warp's ring stage, both as immediates of the instruction.
+// FULL: every slot lies inside the row; otherwise a slot whose first byte is at or beyond kend copies nothing and
+// zero-fills its 16 bytes.
+template <int J, int D, bool FULL>
+__device__ __forceinline__ void issue_slots(uint32_t dst, const uint8_t* src, int kbyte, int kend, const uint8_t* safe) {
+    if constexpr (J < D) {
+        if constexpr (FULL) {
+            asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(dst), "l"(src), "n"(J * 512), "n"(J * 64) : "memory");
+        } else {
+            const bool valid = kbyte + J * 64 < kend;
+            const uint8_t* p = valid ? src + J * 64 : safe;
+            const int n = valid ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0+%3], [%1], 16, %2;" ::"r"(dst), "l"(p), "r"(n), "n"(J * 512) : "memory");
+        }
+        issue_slots<J + 1, D, FULL>(dst, src, kbyte, kend, safe);
+    }
+}
+
+// One chunk of the K loop: D staged 16-byte weight slots of this lane against the activation tile.  xa[i][0] / [1]
+// point at this lane's bytes of rows g / g+8 of 16-row block i for slot 0; HALF: M <= 8, rows g+8 are zero.
+template <int QT, int MT, int D, bool HALF, typename T>
+__device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* const (&xa)[MT][2], T (&c)[MT][4], T (&c2)[MT][4]) {
 #pragma unroll
     for (int j = 0; j < D; ++j) {
-        const uint4 wv = *reinterpret_cast<const uint4*>(stage + j * 4096);
-        const bool kin = !CHECK || (k0 + j * 512 < K);
-        if constexpr (QT == QT_FP8 && WIDE) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(st + j * 512);
+        if constexpr (QT == QT_FP8) {
             // widen the 16 weight bytes to f16 pairs; four m16n8k16 MMAs per 16 bytes on two accumulators
             const uint4 w01 = e4m3x8_to_f16x8(make_uint2(wv.x, wv.y)), w23 = e4m3x8_to_f16x8(make_uint2(wv.z, wv.w));
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
-                uint4 a00 = make_uint4(0, 0, 0, 0), a01 = a00, a10 = a00, a11 = a00;
-                if (kin && xr[i][0]) {
-                    a00 = *reinterpret_cast<const uint4*>(xr[i][0] + j * 512 * AB);
-                    a01 = *reinterpret_cast<const uint4*>(xr[i][0] + j * 512 * AB + 16);
+                const uint4 a00 = *reinterpret_cast<const uint4*>(xa[i][0] + j * 128);
+                const uint4 a01 = *reinterpret_cast<const uint4*>(xa[i][0] + j * 128 + 16);
+                if constexpr (HALF) {
+                    mma_f16(c[i], a00.x, 0u, a00.y, 0u, w01.x, w01.y);
+                    mma_f16(c[i], a00.z, 0u, a00.w, 0u, w01.z, w01.w);
+                    mma_f16(c2[i], a01.x, 0u, a01.y, 0u, w23.x, w23.y);
+                    mma_f16(c2[i], a01.z, 0u, a01.w, 0u, w23.z, w23.w);
+                } else {
+                    const uint4 a10 = *reinterpret_cast<const uint4*>(xa[i][1] + j * 128);
+                    const uint4 a11 = *reinterpret_cast<const uint4*>(xa[i][1] + j * 128 + 16);
+                    mma_f16(c[i], a00.x, a10.x, a00.y, a10.y, w01.x, w01.y);
+                    mma_f16(c[i], a00.z, a10.z, a00.w, a10.w, w01.z, w01.w);
+                    mma_f16(c2[i], a01.x, a11.x, a01.y, a11.y, w23.x, w23.y);
+                    mma_f16(c2[i], a01.z, a11.z, a01.w, a11.w, w23.z, w23.w);
                 }
-                if (kin && xr[i][1]) {
-                    a10 = *reinterpret_cast<const uint4*>(xr[i][1] + j * 512 * AB);
-                    a11 = *reinterpret_cast<const uint4*>(xr[i][1] + j * 512 * AB + 16);
-                }
-                mma_f16(c[i], a00.x, a10.x, a00.y, a10.y, w01.x, w01.y);
-                mma_f16(c[i], a00.z, a10.z, a00.w, a10.w, w01.z, w01.w);
-                mma_f16(c2[i], a01.x, a11.x, a01.y, a11.y, w23.x, w23.y);
-                mma_f16(c2[i], a01.z, a11.z, a01.w, a11.w, w23.z, w23.w);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
-                uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
-                if (kin && xr[i][0]) a0 = *reinterpret_cast<const uint4*>(xr[i][0] + j * 512);
-                if (kin && xr[i][1]) a1 = *reinterpret_cast<const uint4*>(xr[i][1] + j * 512);
-                mma8<QT>(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
-                mma8<QT>(c2[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+                const uint4 a0 = *reinterpret_cast<const uint4*>(xa[i][0] + j * 64);
+                if constexpr (HALF) {
+                    mma_s8(c[i], a0.x, 0u, a0.y, 0u, wv.x, wv.y);
+                    mma_s8(c2[i], a0.z, 0u, a0.w, 0u, wv.z, wv.w);
+                } else {
+                    const uint4 a1 = *reinterpret_cast<const uint4*>(xa[i][1] + j * 64);
+                    mma_s8(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
+                    mma_s8(c2[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
+                }
             }
         }
     }
 }
 
-// WIDE (FP8 only): activations kept as f16 values and weights widened in registers (m16n8k16.f16) instead of
-// e4m3 codes multiplied by mma.sync.m16n8k32.e4m3.  S: stages of the shared-memory weight ring.
-template <int QT, int DT, int MT, int D, bool WIDE, int S>
+// Results of one row tile, straight from the accumulator fragments: lane (g, t) holds rows g and g+8 of each 16-row
+// block and the two columns n0+2t, n0+2t+1.
+template <int QT, int MT, bool HALF, typename T>
+__device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[MT][4], float out_scale,
+                                           const float* xs, float wscale, bool pair_ok) {
+    const int n = n0 + 2 * t;
+    if (n >= a.N) return;
+    const bool two = n + 1 < a.N;
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int h = 0; h < (HALF ? 1 : 2); ++h) {
+            const int m = i * 16 + g + 8 * h;
+            if (m >= a.M) continue;
+            float f0, f1;
+            if constexpr (QT == QT_FP8) {
+                f0 = c[i][2 * h] * out_scale;
+                f1 = c[i][2 * h + 1] * out_scale;
+            } else {
+                if (a.acc[mat]) {
+                    a.acc[mat][(int64_t)m * a.ldacc + n] = c[i][2 * h];
+                    if (two) a.acc[mat][(int64_t)m * a.ldacc + n + 1] = c[i][2 * h + 1];
+                }
+                const float rs = xs[m] * wscale;
+                f0 = (float)c[i][2 * h] * rs;
+                f1 = (float)c[i][2 * h + 1] * rs;
+            }
+            if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
+            __half* o = a.out[mat] + (int64_t)m * a.ldo + n;
+            if (two && pair_ok) {
+                *reinterpret_cast<__half2*>(o) = __floats2half2_rn(f0, f1);
+            } else {
+                o[0] = __float2half_rn(f0);
+                if (two) o[1] = __float2half_rn(f1);
+            }
+        }
+}
+
+// S: stages of each warp's shared-memory weight ring.  HALF: M <= 8.
+template <int QT, int DT, int MT, bool HALF, int S>
 __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
+    constexpr int D = kGemvD;
+    constexpr int AB = QT == QT_FP8 ? 2 : 1;          // bytes per activation in the shared-memory tile
     extern __shared__ __align__(16) uint8_t smem[];
-    // layout: red[kWarps][MT*4][32] | xs[32] | sh[8] | ring[S][D][256] x 16 B | xq[M][pitch]
+    // layout: red[2][kWarps][MT*4][32] | xs[32] | sh[8] | ring[kWarps][S][D][32 lanes] x 16 B | xq[M][pitch] + 512 B
     T* red = reinterpret_cast<T*>(smem);
-    float* xs = reinterpret_cast<float*>(smem + kWarps * MT * 4 * 32 * 4);
+    float* xs = reinterpret_cast<float*>(smem + 2 * kWarps * MT * 4 * 32 * 4);
     float* sh = xs + 32;
     uint8_t* ring = reinterpret_cast<uint8_t*>(sh + 8);
-    uint8_t* xq = ring + (size_t)S * D * 4096;
+    uint8_t* xq = ring + (size_t)kWarps * S * D * 512;
 
     griddep_launch_dependents();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int mat = blockIdx.x / a.cpm, cb = blockIdx.x - mat * a.cpm;
     const int ntile = (a.N + 7) >> 3;
-    const int total = a.nmat * ntile;
-    const int tb = (int)((int64_t)total * blockIdx.x / gridDim.x), te = (int)((int64_t)total * (blockIdx.x + 1) / gridDim.x);
-    const int units = (a.K + 63) >> 6;
-    const int upw = (units + kWarps - 1) / kWarps;   // 64-byte units per warp and row tile
-    const int nchunks = (upw + D - 1) / D;
-    const int koff = (warp << 6) + 16 * t;            // this lane's byte offset inside a row for slot 0
-    const bool check = (a.K % (D * 512)) != 0;
-    uint8_t* my_ring = ring + threadIdx.x * 16;       // this thread's 16 bytes of every slot
+    const int tb = (int)((int64_t)ntile * cb / a.cpm), te = (int)((int64_t)ntile * (cb + 1) / a.cpm);
+    const int R = a.R, KS = kWarps / R;
+    const int slot = warp / KS, ks = warp - slot * KS;       // which tile of a round, which part of K
+    const int rounds = (te - tb + R - 1) / R;
+    const int units = (a.K + 63) >> 6, upw = (units + KS - 1) / KS;
+    const int ub = ks * upw, ue = min(ub + upw, units);
+    const int nch = (max(ue - ub, 0) + D - 1) / D;           // chunks per tile for this warp
+    const int kbeg = ub * 64 + 16 * t;                       // this lane's first byte of a weight row
+    const int kend = min(ue * 64, a.K);
+    const bool full = ((ue - ub) % D == 0) && (a.K % 64 == 0);
+    const int my_rounds = (nch > 0 && te - tb > slot) ? (te - tb - slot + R - 1) / R : 0;   // rounds in which this warp has a tile
+    uint8_t* my_ring = ring + (size_t)warp * S * D * 512 + lane * 16;
+    const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
+    const uint8_t* wbase = a.w[mat];
 
-    // producer side of the ring: chunk (itile, ich) goes to stage istage; one commit group per chunk
-    int itile = tb, ich = 0, istage = 0;
+    // producer side of the ring: chunk p_ch of the tile of round p_round goes to stage p_stage; one group per chunk
+    int p_round = 0, p_ch = 0, p_stage = 0;
+    auto row_ptr = [&](int round) { return wbase + (int64_t)min((tb + round * R + slot) * 8 + g, a.N - 1) * a.ldw + kbeg; };
+    const uint8_t* p_src = my_rounds > 0 ? row_ptr(0) : wbase;
     auto issue = [&]() {
-        if (itile < te) {
-            const int mat = itile >= 2 * ntile ? 2 : (itile >= ntile ? 1 : 0);
-            const int n0 = (itile - mat * ntile) << 3;
-            const uint8_t* src = a.w[mat] + (int64_t)min(n0 + g, a.N - 1) * a.ldw + koff + ich * D * 512;
-            uint8_t* dst = my_ring + (size_t)istage * D * 4096;
-#pragma unroll
-            for (int j = 0; j < D; ++j) {
-                const bool valid = !check || (koff + (ich * D + j) * 512 < a.K);
-                cp_async16(dst + j * 4096, valid ? src + j * 512 : a.w[mat], valid);
+        if (p_round < my_rounds) {
+            const uint32_t dst = my_ring_s + p_stage * (D * 512);
+            if (full) issue_slots<0, D, true>(dst, p_src, 0, 0, wbase);
+            else issue_slots<0, D, false>(dst, p_src, kbeg + p_ch * (D * 64), kend, wbase);
+            p_src += D * 64;
+            if (++p_ch == nch) {
+                p_ch = 0;
+                if (++p_round < my_rounds) p_src = row_ptr(p_round);
             }
-            if (++ich == nchunks) { ich = 0; ++itile; }
         }
         cp_async_commit();
-        if (++istage == S) istage = 0;
+        if (++p_stage == S) p_stage = 0;
     };
 #pragma unroll
     for (int i = 0; i < S - 1; ++i) issue();
 
     griddep_wait();   // activations may come from the previous kernel; results may overwrite what it read
 
-    int cur_mat = -1, stage = 0;
+    // bytes of the activation tile that chunk overruns and rows shorter than their pitch can touch must be finite
+    {
+        const int padv = (a.pitch - a.K * AB) >> 4;          // 16-byte vectors of padding per row
+        for (int i = threadIdx.x; i < a.M * padv; i += kThr) {
+            const int r = i / padv, v = i - r * padv;
+            *reinterpret_cast<uint4*>(xq + (size_t)r * a.pitch + a.K * AB + v * 16) = make_uint4(0, 0, 0, 0);
+        }
+        if (threadIdx.x < 32) *reinterpret_cast<uint4*>(xq + (size_t)a.M * a.pitch + threadIdx.x * 16) = make_uint4(0, 0, 0, 0);
+    }
     float out_scale = 0.f;   // FP8: (amax/448)*w_scale
     float wscale = 0.f;      // INT8: w_scale
-    constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;
-    for (int tile = tb; tile < te; ++tile) {
-        const int mat = tile >= 2 * ntile ? 2 : (tile >= ntile ? 1 : 0);
-        const int n0 = (tile - mat * ntile) << 3;
-        if (mat != cur_mat) {
-            cur_mat = mat;
-            __syncthreads();   // nobody still reads the previous matrix's codes
-            if constexpr (QT == QT_FP8) {
-                const float amax = quantize_fp8_to_smem<DT, WIDE>(a, mat, xq, sh);
-                out_scale = div_mode_f32(amax, 448.f, a.div_mode) * a.ws[mat][0];
-            } else {
-                quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
-                wscale = a.ws[mat][0];
-            }
-            __syncthreads();
-        }
+    if constexpr (QT == QT_FP8) {
+        const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh);
+        out_scale = div_mode_f32(amax, 448.f, a.div_mode) * a.ws[mat][0];
+    } else {
+        quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
+        wscale = a.ws[mat][0];
+    }
+    __syncthreads();
+
+    // this lane's rows of the activation tile (rows g and g+8 of each 16-row block); rows beyond M read row M-1
+    const uint8_t* xa0[MT][2];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+        xa0[i][0] = xq + (size_t)min(i * 16 + g, a.M - 1) * a.pitch + kbeg * AB;
+        xa0[i][1] = xq + (size_t)min(i * 16 + g + 8, a.M - 1) * a.pitch + kbeg * AB;
+    }
+    const bool pair_ok = (a.ldo % 2 == 0) && ((reinterpret_cast<uintptr_t>(a.out[mat]) & 3) == 0);
+    int stage = 0;
+    for (int r = 0; r < rounds; ++r) {
         T c[MT][4], c2[MT][4];
 #pragma unroll
         for (int i = 0; i < MT; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) c[i][j] = c2[i][j] = 0;
-        // this lane's rows of the activation tile (rows g and g+8 of each 16-row block); null = row beyond M
-        const uint8_t* xr[MT][2];
-#pragma unroll
-        for (int i = 0; i < MT; ++i) {
-            xr[i][0] = i * 16 + g < a.M ? xq + (size_t)(i * 16 + g) * a.pitch + (size_t)koff * AB : nullptr;
-            xr[i][1] = i * 16 + g + 8 < a.M ? xq + (size_t)(i * 16 + g + 8) * a.pitch + (size_t)koff * AB : nullptr;
-        }
-        for (int ch = 0; ch < nchunks; ++ch) {
-            issue();                       // keep S-1 chunks in flight
-            cp_async_wait<S - 1>();        // this thread's copies of the current chunk have landed
-            const uint8_t* xc[MT][2];
+        if (r < my_rounds) {
+            const uint8_t* xa[MT][2];
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
-                xc[i][0] = xr[i][0] ? xr[i][0] + (size_t)ch * D * 512 * AB : nullptr;
-                xc[i][1] = xr[i][1] ? xr[i][1] + (size_t)ch * D * 512 * AB : nullptr;
+                xa[i][0] = xa0[i][0];
+                xa[i][1] = xa0[i][1];
             }
-            const uint8_t* st = my_ring + (size_t)stage * D * 4096;
-            if (check) chunk_body<QT, MT, D, WIDE, true>(st, c, c2, koff + ch * D * 512, a.K, xc);
-            else chunk_body<QT, MT, D, WIDE, false>(st, c, c2, koff + ch * D * 512, a.K, xc);
-            if (++stage == S) stage = 0;
-        }
+            for (int ch = 0; ch < nch; ++ch) {
+                issue();                       // keep S-1 chunks in flight
+                cp_async_wait<S - 1>();        // this lane's copies of the current chunk have landed
+                chunk_body<QT, MT, D, HALF>(my_ring + stage * (D * 512), xa, c, c2);
 #pragma unroll
-        for (int i = 0; i < MT; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) c[i][j] += c2[i][j];      // the two accumulators halve the dependent MMA chains
-
-        // split-K reduction across the 8 warps, fixed order
-#pragma unroll
-        for (int i = 0; i < MT; ++i)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) red[(warp * MT * 4 + i * 4 + j) * 32 + lane] = c[i][j];
-        __syncthreads();
-        if (threadIdx.x < MT * 128) {
-            const int ij = threadIdx.x >> 5, l = threadIdx.x & 31;      // ij = i*4 + j
-            T s = 0;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) s += red[(w * MT * 4 + ij) * 32 + l];
-            const int i = ij >> 2, j = ij & 3;
-            const int m = i * 16 + (l >> 2) + ((j & 2) ? 8 : 0);
-            const int n = n0 + 2 * (l & 3) + (j & 1);
-            if (m < a.M && n < a.N) {
-                float v;
-                if constexpr (QT == QT_FP8) {
-                    v = s * out_scale;
-                } else {
-                    if (a.acc[mat]) a.acc[mat][(int64_t)m * a.ldacc + n] = s;
-                    v = (float)s * (xs[m] * wscale);
+                for (int i = 0; i < MT; ++i) {
+                    xa[i][0] += D * 64 * AB;
+                    xa[i][1] += D * 64 * AB;
                 }
-                if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) v = bf16_round(v);
-                a.out[mat][(int64_t)m * a.ldo + n] = __float2half_rn(v);
+                if (++stage == S) stage = 0;
             }
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[i][j] += c2[i][j];      // the two accumulators halve the dependent MMA chains
         }
-        __syncthreads();
+        const int tile = tb + r * R + slot;
+        if (KS > 1) {
+            // the warps of a tile add their parts of K in warp order; the buffer alternates between rounds
+            T* rb = red + (size_t)(r & 1) * kWarps * MT * 4 * 32;
+            if (ks > 0) {
+#pragma unroll
+                for (int i = 0; i < MT; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) rb[((warp * MT + i) * 4 + j) * 32 + lane] = c[i][j];
+            }
+            __syncthreads();
+            if (ks == 0 && tile < te) {
+                for (int kk = 1; kk < KS; ++kk)
+#pragma unroll
+                    for (int i = 0; i < MT; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) c[i][j] += rb[(((warp + kk) * MT + i) * 4 + j) * 32 + lane];
+                store_tile<QT, MT, HALF>(a, mat, tile * 8, g, t, c, out_scale, xs, wscale, pair_ok);
+            }
+        } else if (tile < te) {
+            store_tile<QT, MT, HALF>(a, mat, tile * 8, g, t, c, out_scale, xs, wscale, pair_ok);
+        }
     }
     cp_async_wait<0>();
 }
 
-static size_t smem_bytes(int MT, int M, int pitch, int D, int S) {
-    return (size_t)kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + (size_t)S * D * 4096 + (size_t)M * pitch;
+static size_t smem_bytes(int MT, int M, int pitch, int S) {
+    return (size_t)2 * kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + (size_t)kWarps * S * kGemvD * 512 + (size_t)M * pitch + 512;
 }
 
 constexpr size_t kFusedSmemMax = 200 * 1024;
-
-// FP8 weights are widened to f16 in registers by default: measured on B200, mma.sync.m16n8k32.e4m3 is slower than
-// cvt.f16x2.e4m3x2 + m16n8k16.f16 for this HBM-bound loop.  RWKVQ_F8_MMA=native selects the e4m3 instruction.
-static bool fp8_wide() {
-    static const bool on = [] {
-        const char* e = std::getenv("RWKVQ_F8_MMA");
-        return !(e && e[0] == 'n');
-    }();
-    return on;
-}
 
 static bool use_pdl() {
     static const bool on = [] {
@@ -237,9 +297,9 @@ static bool use_pdl() {
     return on;
 }
 
-template <int QT, int DT, int MT, int D, bool WIDE, int S>
-static int32_t launch_one(const W8Args& a, int64_t tiles, size_t smem, cudaStream_t st) {
-    auto kern = gemv_w8a8_kernel<QT, DT, MT, D, WIDE, S>;
+template <int QT, int DT, int MT, bool HALF, int S>
+static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
+    auto kern = gemv_w8a8_kernel<QT, DT, MT, HALF, S>;
     // per instantiation and device: opt in to large dynamic shared memory and ask how many CTAs fit on an SM
     static thread_local int cfg_dev = -1;
     static thread_local size_t cfg_smem = ~size_t(0);
@@ -256,9 +316,21 @@ static int32_t launch_one(const W8Args& a, int64_t tiles, size_t smem, cudaStrea
         cfg_dev = dev;
         cfg_smem = smem;
     }
-    const int64_t grid = std::min<int64_t>(tiles, (int64_t)sm_count() * per_sm);
+    // every CTA works on one matrix: the grid is a multiple of the matrix count, at most one wave
+    const int ntile = (a.N + 7) / 8;
+    a.cpm = std::max(1, std::min(ntile, sm_count() * per_sm / a.nmat));
+    // Tiles per round from the density of ONE matrix over the whole GPU, whatever the matrix count: the split of K
+    // (and with it the order of the fp32 additions) is then the same for a fused r/k/v launch and for three single
+    // launches, which keeps their results bit-identical.
+    const int tpc = (ntile + sm_count() * per_sm - 1) / (sm_count() * per_sm);
+    a.R = 1;
+    while (a.R < kWarps && a.R < tpc) a.R *= 2;
+    if (const char* e = std::getenv(a.nmat == 3 ? "RWKVQ_GEMV_R3" : "RWKVQ_GEMV_R")) {       // experiments only
+        const int r = std::atoi(e);
+        if (r == 1 || r == 2 || r == 4 || r == 8) a.R = r;
+    }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)(a.cpm * a.nmat));
     cfg.blockDim = dim3(kThr);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -277,24 +349,22 @@ static int32_t launch_one(const W8Args& a, int64_t tiles, size_t smem, cudaStrea
 
 constexpr size_t kTwoPerSm = 110 * 1024;     // shared memory per CTA that still lets two CTAs share an SM
 
-template <int QT, int DT, int MT, int D, bool WIDE>
-static int32_t dispatch_s(const W8Args& a, int64_t tiles, cudaStream_t st) {
-    const size_t s3 = smem_bytes(MT, a.M, a.pitch, D, 3), s2 = smem_bytes(MT, a.M, a.pitch, D, 2);
-    if (s3 <= kTwoPerSm) return launch_one<QT, DT, MT, D, WIDE, 3>(a, tiles, s3, st);
+// deepest ring that still leaves room for two CTAs per SM; a big activation tile gets a shallow ring and one CTA
+template <int QT, int DT, int MT, bool HALF>
+static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
+    const size_t s5 = smem_bytes(MT, a.M, a.pitch, 5), s3 = smem_bytes(MT, a.M, a.pitch, 3), s2 = smem_bytes(MT, a.M, a.pitch, 2);
+    if (s5 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 5>(a, s5, st);
+    if (s3 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 3>(a, s3, st);
     RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the fused kernel's shared memory", a.M, a.K);
-    return launch_one<QT, DT, MT, D, WIDE, 2>(a, tiles, s2, st);
+    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, MT, HALF, 5>(a, s5, st);
+    return launch_one<QT, DT, MT, HALF, 2>(a, s2, st);
 }
 
 template <int QT, int DT>
-static int32_t dispatch_mt(const W8Args& a, int64_t tiles, cudaStream_t st) {
-    const int units = (a.K + 63) / 64;
-    const bool deep = units > 4 * kWarps;          // more than 4 units per warp and tile: chunks of 8 slots
-    if (QT == QT_FP8 && fp8_wide()) {
-        if (a.M <= 16) return deep ? dispatch_s<QT, DT, 1, 8, true>(a, tiles, st) : dispatch_s<QT, DT, 1, 4, true>(a, tiles, st);
-        return deep ? dispatch_s<QT, DT, 2, 8, true>(a, tiles, st) : dispatch_s<QT, DT, 2, 4, true>(a, tiles, st);
-    }
-    if (a.M <= 16) return deep ? dispatch_s<QT, DT, 1, 8, false>(a, tiles, st) : dispatch_s<QT, DT, 1, 4, false>(a, tiles, st);
-    return deep ? dispatch_s<QT, DT, 2, 8, false>(a, tiles, st) : dispatch_s<QT, DT, 2, 4, false>(a, tiles, st);
+static int32_t dispatch_mt(const W8Args& a, cudaStream_t st) {
+    if (a.M <= 8) return dispatch_s<QT, DT, 1, true>(a, st);
+    if (a.M <= 16) return dispatch_s<QT, DT, 1, false>(a, st);
+    return dispatch_s<QT, DT, 2, false>(a, st);
 }
 
 template <int QT>
@@ -313,14 +383,11 @@ static int32_t run_fused(W8Args a, int x_dtype, cudaStream_t st, const char* who
     }
     if (a.M == 0 || a.N == 0) return RWKVQ_OK;
     RWKVQ_REQUIRE(a.K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
-    const int MT = a.M <= 16 ? 1 : 2;
     // shared-memory row pitch of the activation tile: int8 codes (1 B) or f16 values of the e4m3 codes (2 B);
     // the odd 64 / 16 bytes keep the fragment loads of different rows on different banks
-    a.pitch = (QT == QT_FP8 && fp8_wide()) ? ((2 * a.K + 127) / 128) * 128 + 16 : ((a.K + 127) / 128) * 128 + 64;
-    (void)MT;
-    const int64_t tiles = (int64_t)a.nmat * ((a.N + 7) / 8);
-    RWKVQ_REQUIRE(tiles < (int64_t(1) << 30), RWKVQ_E_SHAPE, "%s: N too large", who);
-    return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16>(a, tiles, st) : dispatch_mt<QT, RWKVQ_BF16>(a, tiles, st);
+    a.pitch = QT == QT_FP8 ? ((2 * a.K + 127) / 128) * 128 + 16 : ((a.K + 127) / 128) * 128 + 64;
+    RWKVQ_REQUIRE((int64_t)a.nmat * ((a.N + 7) / 8) < (int64_t(1) << 27), RWKVQ_E_SHAPE, "%s: N too large", who);
+    return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16>(a, st) : dispatch_mt<QT, RWKVQ_BF16>(a, st);
 }
 
 }  // namespace rwkvq

@@ -30,6 +30,8 @@ struct W8Args {
     int div_mode, amax_is_amax;
     uint32_t flags;
     int pitch;                // fused: bytes between rows of the code tile in shared memory
+    int R;                    // decode GEMV: row tiles per round of a CTA (1, 2, 4 or 8); 8/R warps share a tile
+    int cpm;                  // decode GEMV: CTAs per matrix (grid = nmat * cpm)
 };
 
 template <int QT>
