@@ -35,6 +35,8 @@ namespace rwkvq {
 
 constexpr int kGemvD = 4;                 // 64-byte units per chunk (one cp.async group): 2 KB per warp
 
+static unsigned long long* g_gemv_trace = nullptr;
+
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -142,6 +144,10 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
 }
 
 // S: stages of each warp's shared-memory weight ring.  HALF: M <= 8.
+// Everything between the kernel's entry and its first copies, and between the dependency release and the first
+// MMA, is a single pass of dependent scalar code and shows up in full in a 5-15 us launch: the tile split and all
+// divisions are done on the host (W8Args::tq, trem, lgR), and whatever does not need the activations is computed
+// before griddepcontrol.wait.
 template <int QT, int DT, int MT, bool HALF, int S>
 __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
@@ -156,22 +162,23 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     uint8_t* xq = ring + (size_t)kWarps * S * D * 512;
 
     griddep_launch_dependents();
+    w8_mark(a, 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int mat = blockIdx.x / a.cpm, cb = blockIdx.x - mat * a.cpm;
-    const int ntile = (a.N + 7) >> 3;
-    const int tb = (int)((int64_t)ntile * cb / a.cpm), te = (int)((int64_t)ntile * (cb + 1) / a.cpm);
-    const int R = a.R, KS = kWarps / R;
-    const int slot = warp / KS, ks = warp - slot * KS;       // which tile of a round, which part of K
-    const int rounds = (te - tb + R - 1) / R;
-    const int units = (a.K + 63) >> 6, upw = (units + KS - 1) / KS;
+    const int mat = ((int)blockIdx.x >= a.cpm) + ((int)blockIdx.x >= 2 * a.cpm);
+    const int cb = (int)blockIdx.x - mat * a.cpm;
+    const int tb = cb * a.tq + min(cb, a.trem), te = tb + a.tq + (cb < a.trem ? 1 : 0);   // this CTA's row tiles
+    const int lgR = a.lgR, R = 1 << lgR, lgKS = 3 - lgR, KS = 1 << lgKS;
+    const int slot = warp >> lgKS, ks = warp & (KS - 1);     // which tile of a round, which part of K
+    const int rounds = (te - tb + R - 1) >> lgR;
+    const int units = (a.K + 63) >> 6, upw = (units + KS - 1) >> lgKS;
     const int ub = ks * upw, ue = min(ub + upw, units);
-    const int nch = (max(ue - ub, 0) + D - 1) / D;           // chunks per tile for this warp
+    const int nch = (max(ue - ub, 0) + D - 1) / D;           // chunks per tile for this warp (D is a power of two)
     const int kbeg = ub * 64 + 16 * t;                       // this lane's first byte of a weight row
     const int kend = min(ue * 64, a.K);
     const bool full = ((ue - ub) % D == 0) && (a.K % 64 == 0);
-    const int my_rounds = (nch > 0 && te - tb > slot) ? (te - tb - slot + R - 1) / R : 0;   // rounds in which this warp has a tile
+    const int my_rounds = (nch > 0 && te - tb > slot) ? ((te - tb - slot + R - 1) >> lgR) : 0;   // rounds in which this warp has a tile
     uint8_t* my_ring = ring + (size_t)warp * S * D * 512 + lane * 16;
     const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
     const uint8_t* wbase = a.w[mat];
@@ -196,37 +203,39 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     };
 #pragma unroll
     for (int i = 0; i < S - 1; ++i) issue();
-
-    griddep_wait();   // activations may come from the previous kernel; results may overwrite what it read
+    w8_mark(a, 1);
 
     // bytes of the activation tile that chunk overruns and rows shorter than their pitch can touch must be finite
     {
         const int padv = (a.pitch - a.K * AB) >> 4;          // 16-byte vectors of padding per row
-        for (int i = threadIdx.x; i < a.M * padv; i += kThr) {
-            const int r = i / padv, v = i - r * padv;
-            *reinterpret_cast<uint4*>(xq + (size_t)r * a.pitch + a.K * AB + v * 16) = make_uint4(0, 0, 0, 0);
-        }
-        if (threadIdx.x < 32) *reinterpret_cast<uint4*>(xq + (size_t)a.M * a.pitch + threadIdx.x * 16) = make_uint4(0, 0, 0, 0);
+        for (int r = 0; r < a.M; ++r)
+            if ((int)threadIdx.x < padv) *reinterpret_cast<uint4*>(xq + (size_t)r * a.pitch + a.K * AB + threadIdx.x * 16) = make_uint4(0, 0, 0, 0);
+        if (threadIdx.x >= 32 && threadIdx.x < 64)
+            *reinterpret_cast<uint4*>(xq + (size_t)a.M * a.pitch + (threadIdx.x - 32) * 16) = make_uint4(0, 0, 0, 0);
     }
-    float out_scale = 0.f;   // FP8: (amax/448)*w_scale
-    float wscale = 0.f;      // INT8: w_scale
-    if constexpr (QT == QT_FP8) {
-        const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh);
-        out_scale = div_mode_f32(amax, 448.f, a.div_mode) * a.ws[mat][0];
-    } else {
-        quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
-        wscale = a.ws[mat][0];
-    }
-    __syncthreads();
-
     // this lane's rows of the activation tile (rows g and g+8 of each 16-row block); rows beyond M read row M-1
     const uint8_t* xa0[MT][2];
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
-        xa0[i][0] = xq + (size_t)min(i * 16 + g, a.M - 1) * a.pitch + kbeg * AB;
-        xa0[i][1] = xq + (size_t)min(i * 16 + g + 8, a.M - 1) * a.pitch + kbeg * AB;
+        xa0[i][0] = xq + min(i * 16 + g, a.M - 1) * a.pitch + kbeg * AB;
+        xa0[i][1] = xq + min(i * 16 + g + 8, a.M - 1) * a.pitch + kbeg * AB;
     }
     const bool pair_ok = (a.ldo % 2 == 0) && ((reinterpret_cast<uintptr_t>(a.out[mat]) & 3) == 0);
+    const float wscale = a.ws[mat][0];       // weights and their scale are never written by a kernel
+
+    griddep_wait();   // activations may come from the previous kernel; results may overwrite what it read
+    w8_mark(a, 2);
+
+    float out_scale = 0.f;   // FP8: (amax/448)*w_scale
+    if constexpr (QT == QT_FP8) {
+        const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh);
+        out_scale = div_mode_f32(amax, 448.f, a.div_mode) * wscale;
+    } else {
+        quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
+    }
+    __syncthreads();
+    w8_mark(a, 3);
+
     int stage = 0;
     for (int r = 0; r < rounds; ++r) {
         T c[MT][4], c2[MT][4];
@@ -281,6 +290,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
         }
     }
     cp_async_wait<0>();
+    w8_mark(a, 4);
 }
 
 static size_t smem_bytes(int MT, int M, int pitch, int S) {
@@ -319,16 +329,15 @@ static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
     // every CTA works on one matrix: the grid is a multiple of the matrix count, at most one wave
     const int ntile = (a.N + 7) / 8;
     a.cpm = std::max(1, std::min(ntile, sm_count() * per_sm / a.nmat));
+    a.tq = ntile / a.cpm;                 // CTA cb of a matrix takes tq row tiles, the first trem CTAs one more
+    a.trem = ntile % a.cpm;
     // Tiles per round from the density of ONE matrix over the whole GPU, whatever the matrix count: the split of K
     // (and with it the order of the fp32 additions) is then the same for a fused r/k/v launch and for three single
     // launches, which keeps their results bit-identical.
     const int tpc = (ntile + sm_count() * per_sm - 1) / (sm_count() * per_sm);
-    a.R = 1;
-    while (a.R < kWarps && a.R < tpc) a.R *= 2;
-    if (const char* e = std::getenv(a.nmat == 3 ? "RWKVQ_GEMV_R3" : "RWKVQ_GEMV_R")) {       // experiments only
-        const int r = std::atoi(e);
-        if (r == 1 || r == 2 || r == 4 || r == 8) a.R = r;
-    }
+    a.lgR = 0;
+    while ((1 << a.lgR) < kWarps && (1 << a.lgR) < tpc) ++a.lgR;
+    a.trace = g_gemv_trace;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(a.cpm * a.nmat));
     cfg.blockDim = dim3(kThr);
@@ -395,6 +404,9 @@ static int32_t run_fused(W8Args a, int x_dtype, cudaStream_t st, const char* who
 using namespace rwkvq;
 
 extern "C" {
+
+/* profiling aid: device buffer of [grid][8] uint64 that every decode GEMV launch stamps with CTA milestones */
+void rwkvq_gemv_set_trace(void* device_buffer) { g_gemv_trace = reinterpret_cast<unsigned long long*>(device_buffer); }
 
 int32_t rwkvq_gemv_fp8(const void* x, int32_t x_dtype, const float* awq, const uint8_t* w, int64_t ldw, const float* w_scale,
                        void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,

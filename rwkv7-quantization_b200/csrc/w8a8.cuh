@@ -30,9 +30,20 @@ struct W8Args {
     int div_mode, amax_is_amax;
     uint32_t flags;
     int pitch;                // fused: bytes between rows of the code tile in shared memory
-    int R;                    // decode GEMV: row tiles per round of a CTA (1, 2, 4 or 8); 8/R warps share a tile
+    int lgR;                  // decode GEMV: log2 of the row tiles per round of a CTA (R = 1, 2, 4 or 8); 8/R warps share a tile
     int cpm;                  // decode GEMV: CTAs per matrix (grid = nmat * cpm)
+    int tq, trem;             // decode GEMV: row tiles per CTA (quotient, remainder) within a matrix
+    unsigned long long* trace;   // profiling aid: [grid][8] timestamps of the CTA's milestones, or null
 };
+
+// profiling aid: thread 0 of a CTA stamps milestone `slot` (0..7) with the global timer when a trace buffer is set
+__device__ __forceinline__ void w8_mark(const W8Args& a, int slot) {
+    if (a.trace && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+        a.trace[(size_t)blockIdx.x * 8 + slot] = t;
+    }
+}
 
 template <int QT>
 struct Acc { using T = float; };
@@ -152,7 +163,7 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
             const int i = threadIdx.x + j * kThr;
             rr[j] = -1;
             if (i < nvec) {
-                rr[j] = i / kv;
+                rr[j] = (kv & (kv - 1)) == 0 ? (i >> (31 - __clz(kv))) : i / kv;
                 kk[j] = (i - rr[j] * kv) << 3;
                 v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)rr[j] * a.ldx + kk[j]) * 2);
             }
@@ -160,7 +171,9 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
 #pragma unroll
         for (int j = 0; j < 4; ++j)
             if (rr[j] >= 0) fp8_vec_amax<DT>(v[j], awq, kk[j], a.div_mode, after, m);
+        w8_mark(a, 5);
         const float amax = fmaxf(cta_max(m, sh), 1e-12f);
+        w8_mark(a, 6);
         const float inv = div_mode_f32(448.f, amax, a.div_mode);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
