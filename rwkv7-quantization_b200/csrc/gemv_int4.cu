@@ -17,10 +17,15 @@
 // per CTA.  Scales and zeros travel in the same register ring as the weights, so their latency is hidden too.
 // Work split, persistence and the fixed-order cross-warp reduction are those of the W8A8 GEMV.
 #include <cstdlib>
+#include <type_traits>
 
 #include "w8a8.cuh"
 
 namespace rwkvq {
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 struct I4Args {
     const __half* x;        // [M, ldx] fp16
@@ -164,49 +169,101 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_group_kernel(const I4Args a
     }
 }
 
-// ---- fast path: K a multiple of 4096, group 128, fp32 scales (zeros optional).  Each warp owns a CONTIGUOUS run of
-// units of its 8 rows, so the scales / zeros of four units are one 128-bit load per row, every address in the unrolled
-// body is a base pointer plus a compile-time offset, and a row streams 256 contiguous bytes per chunk.
-struct I4Quad {
-    uint4 w[4];
-    float4 s0, s1, z0, z1;      // scales / zeros of rows n0+2t and n0+2t+1 for the chunk's four groups
+// ---- fast path: group 128, fp32 scales, K a multiple of 512.
+//
+// Written like the W8A8 decode kernel (instruction count, per-warp cp.async rings, host-side tile split), with the
+// operand roles of the MMA swapped: the WEIGHTS are the 16-row A operand and up to 8 tokens the B operand, so one
+// m16n8k16 covers 16 weight rows x 16 k -- half the MMAs per byte -- and a lane's accumulators belong to the two
+// weight rows (g and g+8) it loads, so it applies the scales and zeros of exactly those rows.
+//
+// A warp owns 16 weight rows over a contiguous K range.  Unit = 128 k (one group): lane (g, t) copies
+// W[n0+g][..] and W[n0+g+8][..], 16 bytes (32 nibbles, k = 32t .. 32t+31 of the unit) each.  A chunk is 4 units
+// plus the 4 scales and 4 zeros of the 16 rows (lane t = 0..3 of row pair g copies scales g, scales g+8, zeros g,
+// zeros g+8 as one 16-byte vector each).  A 32-bit word of each row gives the A registers of two MMAs (masks
+// 0x000F000F / 0x00F000F0 on the word and on the word >> 8, see the file header); the activations of token
+// min(g, M-1) are read with the matching permutation, tokens beyond M feed accumulator columns that are never stored.
+// NT: token tiles of 8 (M <= 8 NT).  S: ring stages per warp.
+constexpr int kI4D = 4;                                   // units per chunk
+constexpr int kI4Stage = kI4D * 1024 + 512;               // bytes per warp and stage: weights + scales/zeros
+
+struct I4FastArgs {
+    I4Args b;
+    int lgR, tq, trem;            // log2 of the 16-row tiles per round; tiles per CTA (quotient, remainder)
 };
 
-__global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4Args a) {
+template <int NT, int S>
+__global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArgs fa) {
+    const I4Args& a = fa.b;
     extern __shared__ __align__(16) uint8_t smem[];
+    // layout: red[2][kWarps][NT*4][32] floats | ring[kWarps][S][kI4Stage] | xsum[M][units] floats | xs[M][pitch]
     const int units = a.K >> 7;
     float* red = reinterpret_cast<float*>(smem);
-    float* xsum = red + kWarps * 4 * 32;
+    uint8_t* ring = smem + 2 * kWarps * NT * 4 * 32 * 4;
+    float* xsum = reinterpret_cast<float*>(ring + (size_t)kWarps * S * kI4Stage);
     uint8_t* xs = reinterpret_cast<uint8_t*>(xsum + ((a.M * units + 3) & ~3));
 
     griddep_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int ntile = (a.N + 7) >> 3;
-    const int tb = (int)((int64_t)ntile * blockIdx.x / gridDim.x), te = (int)((int64_t)ntile * (blockIdx.x + 1) / gridDim.x);
-    const int upw = units >> 3, nchunks = upw >> 2;           // units per warp (multiple of 4), chunks of 4 units
+    const int cb = blockIdx.x;
+    const int tb = cb * fa.tq + min(cb, fa.trem), te = tb + fa.tq + (cb < fa.trem ? 1 : 0);   // this CTA's 16-row tiles
+    const int lgR = fa.lgR, R = 1 << lgR, lgKS = 3 - lgR, KS = 1 << lgKS;
+    const int slot = warp >> lgKS, ks = warp & (KS - 1);
+    const int rounds = (te - tb + R - 1) >> lgR;
+    const int upw = (((units + KS - 1) >> lgKS) + 3) & ~3;           // units per warp and tile, whole chunks
+    const int ub = ks * upw, ue = min(ub + upw, units);
+    const int nch = max(ue - ub, 0) >> 2;
+    const int my_rounds = (nch > 0 && te - tb > slot) ? ((te - tb - slot + R - 1) >> lgR) : 0;
+    uint8_t* my_ring = ring + (size_t)warp * S * kI4Stage;
+    const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
     const float* scales = reinterpret_cast<const float*>(a.scales);
+    const bool has_z = a.zeros != nullptr;
 
-    auto fetch = [&](int tile, int c) -> I4Quad {
-        I4Quad q;
-        const int n0 = tile << 3;
-        const uint8_t* wp = a.w + (int64_t)min(n0 + g, a.N - 1) * a.ldw + ((warp * upw + c * 4) << 6) + 16 * t;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) q.w[j] = ldg_stream(wp + j * 64);
-        const int64_t i0 = (int64_t)min(n0 + 2 * t, a.N - 1) * a.ngroups + warp * upw + c * 4;
-        const int64_t i1 = (int64_t)min(n0 + 2 * t + 1, a.N - 1) * a.ngroups + warp * upw + c * 4;
-        q.s0 = __ldg(reinterpret_cast<const float4*>(scales + i0));
-        q.s1 = __ldg(reinterpret_cast<const float4*>(scales + i1));
-        if (a.zeros) {
-            q.z0 = __ldg(reinterpret_cast<const float4*>(a.zeros + i0));
-            q.z1 = __ldg(reinterpret_cast<const float4*>(a.zeros + i1));
-        } else {
-            q.z0 = make_float4(-8.f * q.s0.x, -8.f * q.s0.y, -8.f * q.s0.z, -8.f * q.s0.w);
-            q.z1 = make_float4(-8.f * q.s1.x, -8.f * q.s1.y, -8.f * q.s1.z, -8.f * q.s1.w);
-        }
-        return q;
+    // producer: per chunk 8 weight copies per lane and one scale / zero vector
+    int p_round = 0, p_ch = 0, p_stage = 0;
+    const uint8_t *p_w0 = a.w, *p_w1 = a.w;
+    const float* p_sz = scales;
+    const bool sz_on = t < 2 || has_z;
+    auto set_rows = [&](int round) {
+        const int n0 = (tb + round * R + slot) << 4;
+        const int r0 = min(n0 + g, a.N - 1), r1 = min(n0 + g + 8, a.N - 1);
+        p_w0 = a.w + (int64_t)r0 * a.ldw + ub * 64 + 16 * t;
+        p_w1 = a.w + (int64_t)r1 * a.ldw + ub * 64 + 16 * t;
+        p_sz = ((t & 2) ? a.zeros : scales) + (int64_t)((t & 1) ? r1 : r0) * a.ngroups + ub;
     };
-    I4Quad cur = fetch(min(tb, max(te - 1, 0)), 0);
+    if (my_rounds > 0) set_rows(0);
+    auto issue = [&]() {
+        if (p_round < my_rounds) {
+            const uint32_t dst = my_ring_s + p_stage * kI4Stage;
+#pragma unroll
+            for (int j = 0; j < kI4D; ++j) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 1024 + lane * 16), "l"(p_w0 + j * 64) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 1024 + 512 + lane * 16), "l"(p_w1 + j * 64) : "memory");
+            }
+            if (sz_on) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + kI4D * 1024 + (t * 8 + g) * 16), "l"(p_sz) : "memory");
+            p_w0 += kI4D * 64;
+            p_w1 += kI4D * 64;
+            p_sz += kI4D;
+            if (++p_ch == nch) {
+                p_ch = 0;
+                if (++p_round < my_rounds) set_rows(p_round);
+            }
+        }
+        cp_async_commit();
+        if (++p_stage == S) p_stage = 0;
+    };
+#pragma unroll
+    for (int i = 0; i < S - 1; ++i) issue();
+
+    // this lane's token rows of the activation tile and of the per-unit activation sums (tokens beyond M read M-1)
+    const uint8_t* xb0[NT];
+    const float *xq0[NT], *xq1[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        xb0[i] = xs + min(i * 8 + g, a.M - 1) * a.pitch + ub * 256 + t * 64;
+        xq0[i] = xsum + min(i * 8 + 2 * t, a.M - 1) * units + ub;
+        xq1[i] = xsum + min(i * 8 + 2 * t + 1, a.M - 1) * units + ub;
+    }
 
     griddep_wait();
     {   // prologue: permuted fp16 activations (odd pairs / 16) and per-unit activation sums
@@ -225,78 +282,131 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4Args a)
                 *reinterpret_cast<__half2*>(&p.w) = __hmul2(*reinterpret_cast<__half2*>(&p.w), sixteenth);
                 *reinterpret_cast<uint4*>(xs + (size_t)r * a.pitch + (size_t)i * 16) = p;
             }
-        }
-        for (int i = warp; i < a.M * units; i += kWarps) {
-            const int r = i / units, u = i - r * units;
-            const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx) + ((size_t)u << 8) + lane * 8);
-            const float2 f0 = cvt2<RWKVQ_F16>(v.x), f1 = cvt2<RWKVQ_F16>(v.y);
-            const float sum = warp_sum((f0.x + f0.y) + (f1.x + f1.y));
-            if (lane == 0) xsum[i] = sum;
-        }
-        __syncthreads();
-    }
-    // this lane's activation rows (g and g + 8) at its warp's first unit
-    const uint8_t* xr0 = g < a.M ? xs + (size_t)g * a.pitch + ((size_t)(warp * upw) << 8) + t * 64 : nullptr;
-    const uint8_t* xr1 = g + 8 < a.M ? xs + (size_t)(g + 8) * a.pitch + ((size_t)(warp * upw) << 8) + t * 64 : nullptr;
-    const float* xs0p = xsum + (g < a.M ? g : 0) * units + warp * upw;
-    const float* xs1p = xsum + (g + 8 < a.M ? g + 8 : 0) * units + warp * upw;
-    const float m0 = g < a.M ? 1.f : 0.f, m1 = g + 8 < a.M ? 1.f : 0.f;
-
-    for (int tile = tb; tile < te; ++tile) {
-        float tot[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int ch = 0; ch < nchunks; ++ch) {
-            const I4Quad q = cur;
-            const bool last = ch + 1 == nchunks;
-            if (!last || tile + 1 < te) cur = fetch(last ? tile + 1 : tile, last ? 0 : ch + 1);
-            const float sc0[4] = {q.s0.x, q.s0.y, q.s0.z, q.s0.w}, sc1[4] = {q.s1.x, q.s1.y, q.s1.z, q.s1.w};
-            const float zr0[4] = {q.z0.x, q.z0.y, q.z0.z, q.z0.w}, zr1[4] = {q.z1.x, q.z1.y, q.z1.z, q.z1.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint32_t wd[4] = {q.w[j].x, q.w[j].y, q.w[j].z, q.w[j].w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0;
-                    if (xr0) a0 = *reinterpret_cast<const uint4*>(xr0 + ch * 1024 + j * 256 + i * 16);
-                    if (xr1) a1 = *reinterpret_cast<const uint4*>(xr1 + ch * 1024 + j * 256 + i * 16);
-                    const uint32_t hi = wd[i] >> 8;
-                    mma_f16((i & 1) ? cb : ca, a0.x, a1.x, a0.y, a1.y, wd[i] & 0x000F000Fu, wd[i] & 0x00F000F0u);
-                    mma_f16((i & 1) ? cb : ca, a0.z, a1.z, a0.w, a1.w, hi & 0x000F000Fu, hi & 0x00F000F0u);
-                }
-                const float xs0 = m0 * xs0p[ch * 4 + j], xs1 = m1 * xs1p[ch * 4 + j];
-                const float e0 = sc0[j] * 16777216.f, e1 = sc1[j] * 16777216.f;
-                tot[0] += e0 * (ca[0] + cb[0]) + zr0[j] * xs0;
-                tot[1] += e1 * (ca[1] + cb[1]) + zr1[j] * xs0;
-                tot[2] += e0 * (ca[2] + cb[2]) + zr0[j] * xs1;
-                tot[3] += e1 * (ca[3] + cb[3]) + zr1[j] * xs1;
+            const char* xrow = reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx);
+            for (int u = warp; u < units; u += kWarps) {
+                const uint2 v = *reinterpret_cast<const uint2*>(xrow + ((size_t)u << 8) + lane * 8);
+                const float2 f0 = cvt2<RWKVQ_F16>(v.x), f1 = cvt2<RWKVQ_F16>(v.y);
+                const float sum = warp_sum((f0.x + f0.y) + (f1.x + f1.y));
+                if (lane == 0) xsum[r * units + u] = sum;
             }
         }
-        const int n0 = tile << 3;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) red[(warp * 4 + j) * 32 + lane] = tot[j];
-        __syncthreads();
-        if (threadIdx.x < 128) {
-            const int j = threadIdx.x >> 5, l = threadIdx.x & 31;
-            float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) s += red[(w * 4 + j) * 32 + l];
-            const int m = (l >> 2) + ((j & 2) ? 8 : 0), n = n0 + 2 * (l & 3) + (j & 1);
-            if (m < a.M && n < a.N) a.out[(int64_t)m * a.ldo + n] = __float2half_rn(s);
-        }
         __syncthreads();
     }
+
+    int stage = 0;
+    for (int r = 0; r < rounds; ++r) {
+        float tot[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; ++i) tot[i][0] = tot[i][1] = tot[i][2] = tot[i][3] = 0.f;
+        if (r < my_rounds) {
+            const uint8_t* xb[NT];
+            const float *q0[NT], *q1[NT];
+#pragma unroll
+            for (int i = 0; i < NT; ++i) { xb[i] = xb0[i]; q0[i] = xq0[i]; q1[i] = xq1[i]; }
+            for (int ch = 0; ch < nch; ++ch) {
+                issue();
+                cp_async_wait<S - 1>();
+                __syncwarp();                              // the scale / zero vectors are read across lanes
+                const uint8_t* st = my_ring + stage * kI4Stage;
+                const float4 sg = *reinterpret_cast<const float4*>(st + kI4D * 1024 + (0 * 8 + g) * 16);
+                const float4 sh = *reinterpret_cast<const float4*>(st + kI4D * 1024 + (1 * 8 + g) * 16);
+                float4 zg, zh;
+                if (has_z) {
+                    zg = *reinterpret_cast<const float4*>(st + kI4D * 1024 + (2 * 8 + g) * 16);
+                    zh = *reinterpret_cast<const float4*>(st + kI4D * 1024 + (3 * 8 + g) * 16);
+                } else {
+                    zg = make_float4(-8.f * sg.x, -8.f * sg.y, -8.f * sg.z, -8.f * sg.w);
+                    zh = make_float4(-8.f * sh.x, -8.f * sh.y, -8.f * sh.z, -8.f * sh.w);
+                }
+                const float sgv[4] = {sg.x, sg.y, sg.z, sg.w}, shv[4] = {sh.x, sh.y, sh.z, sh.w};
+                const float zgv[4] = {zg.x, zg.y, zg.z, zg.w}, zhv[4] = {zh.x, zh.y, zh.z, zh.w};
+#pragma unroll
+                for (int j = 0; j < kI4D; ++j) {
+                    const uint4 wg = *reinterpret_cast<const uint4*>(st + j * 1024 + lane * 16);
+                    const uint4 wh = *reinterpret_cast<const uint4*>(st + j * 1024 + 512 + lane * 16);
+                    const uint32_t wgw[4] = {wg.x, wg.y, wg.z, wg.w}, whw[4] = {wh.x, wh.y, wh.z, wh.w};
+                    const float eg = sgv[j] * 16777216.f, eh = shv[j] * 16777216.f;     // undo the 2^-24 of the subnormals
+#pragma unroll
+                    for (int i = 0; i < NT; ++i) {
+                        float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 bx = *reinterpret_cast<const uint4*>(xb[i] + j * 256 + q * 16);
+                            const uint32_t hg = wgw[q] >> 8, hh = whw[q] >> 8;
+                            mma_f16((q & 1) ? cb2 : ca, wgw[q] & 0x000F000Fu, whw[q] & 0x000F000Fu, wgw[q] & 0x00F000F0u, whw[q] & 0x00F000F0u, bx.x, bx.y);
+                            mma_f16((q & 1) ? cb2 : ca, hg & 0x000F000Fu, hh & 0x000F000Fu, hg & 0x00F000F0u, hh & 0x00F000F0u, bx.z, bx.w);
+                        }
+                        const float x0 = q0[i][j], x1 = q1[i][j];
+                        tot[i][0] += eg * (ca[0] + cb2[0]) + zgv[j] * x0;
+                        tot[i][1] += eg * (ca[1] + cb2[1]) + zgv[j] * x1;
+                        tot[i][2] += eh * (ca[2] + cb2[2]) + zhv[j] * x0;
+                        tot[i][3] += eh * (ca[3] + cb2[3]) + zhv[j] * x1;
+                    }
+                }
+                __syncwarp();                              // all lanes have read this stage before it is refilled
+#pragma unroll
+                for (int i = 0; i < NT; ++i) { xb[i] += kI4D * 256; q0[i] += kI4D; q1[i] += kI4D; }
+                if (++stage == S) stage = 0;
+            }
+        }
+        const int tile = tb + r * R + slot;
+        bool store = tile < te;
+        if (KS > 1) {
+            float* rb = red + (size_t)(r & 1) * kWarps * NT * 4 * 32;
+            if (ks > 0) {
+#pragma unroll
+                for (int i = 0; i < NT; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) rb[((warp * NT + i) * 4 + j) * 32 + lane] = tot[i][j];
+            }
+            __syncthreads();
+            store = store && ks == 0;
+            if (store) {
+                for (int kk = 1; kk < KS; ++kk)
+#pragma unroll
+                    for (int i = 0; i < NT; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) tot[i][j] += rb[(((warp + kk) * NT + i) * 4 + j) * 32 + lane];
+            }
+        }
+        if (store) {
+            // lane (g, t): weight rows n0+g (values 0, 1) and n0+g+8 (values 2, 3), tokens 8i+2t and 8i+2t+1
+            const int n0 = tile << 4;
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int m = i * 8 + 2 * t + (j & 1), n = n0 + g + ((j & 2) ? 8 : 0);
+                    if (m < a.M && n < a.N) a.out[(int64_t)m * a.ldo + n] = __float2half_rn(tot[i][j]);
+                }
+        }
+    }
+    cp_async_wait<0>();
 }
 
-template <typename Kern>
-static int32_t launch_i4(Kern kern, const I4Args& a, size_t smem, cudaStream_t st) {
+static size_t i4_fast_smem(int NT, int S, int M, int K) {
+    const int units = K / 128;
+    return (size_t)2 * kWarps * NT * 4 * 32 * 4 + (size_t)kWarps * S * kI4Stage + (size_t)((M * units + 3) & ~3) * 4 + (size_t)M * (2 * K + 16);
+}
+
+template <typename Kern, typename Args>
+static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64_t tiles, bool fast) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     int per_sm = 0;
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThr, smem);
     if (e != cudaSuccess || per_sm < 1) return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: occupancy query failed");
-    const int64_t tiles = (a.N + 7) / 8;
+    const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * std::min(per_sm, 2));
+    if constexpr (std::is_same<Args, I4FastArgs>::value) {
+        a.tq = (int)(tiles / grid);
+        a.trem = (int)(tiles % grid);
+        const int tpc = (int)((tiles + grid - 1) / grid);
+        a.lgR = 0;
+        while ((1 << a.lgR) < kWarps && (1 << a.lgR) < tpc) ++a.lgR;
+    }
+    (void)fast;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)std::min<int64_t>(tiles, (int64_t)sm_count() * per_sm));
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kThr);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -312,6 +422,22 @@ static int32_t launch_i4(Kern kern, const I4Args& a, size_t smem, cudaStream_t s
         return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: %s", cudaGetErrorString(e));
     }
     return check_launch("gemv_int4_group");
+}
+
+template <int NT>
+static int32_t launch_i4_fast(const I4Args& a, cudaStream_t st, bool* done) {
+    constexpr size_t kTwo = 110 * 1024, kMax = 200 * 1024;
+    I4FastArgs fa{};
+    fa.b = a;
+    const int64_t tiles = (a.N + 15) / 16;
+    const size_t s4 = i4_fast_smem(NT, 4, a.M, a.K), s3 = i4_fast_smem(NT, 3, a.M, a.K), s2 = i4_fast_smem(NT, 2, a.M, a.K);
+    *done = true;
+    if (s2 <= kTwo) return launch_i4(gemv_int4_g128_kernel<NT, 2>, fa, s2, st, tiles, true);
+    if (s4 <= kMax) return launch_i4(gemv_int4_g128_kernel<NT, 4>, fa, s4, st, tiles, true);
+    if (s3 <= kMax) return launch_i4(gemv_int4_g128_kernel<NT, 3>, fa, s3, st, tiles, true);
+    if (s2 <= kMax) return launch_i4(gemv_int4_g128_kernel<NT, 2>, fa, s2, st, tiles, true);
+    *done = false;      // the activation tile leaves no room for a ring: the register-ring kernel takes the call
+    return RWKVQ_OK;
 }
 
 }  // namespace rwkvq
@@ -347,11 +473,31 @@ int32_t rwkvq_gemv_int4_group(const void* x_f16, int64_t ldx, const uint8_t* pac
     a.ldx = ldx; a.ldw = ldw; a.ldo = ldo; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.group = group; a.scale_f16 = scale_is_f16;
     a.pitch = (int)(2 * K + 16); a.ngroups = (int)(K / group);
     const char* env = std::getenv("RWKVQ_INT4_FAST");
-    const bool fast = K % 4096 == 0 && group == 128 && !scale_is_f16 && !(env && env[0] == '0')
+    const bool fast = K % 512 == 0 && group == 128 && !scale_is_f16 && !(env && env[0] == '0')
                       && ((uintptr_t)scales & 15) == 0 && (zeros == nullptr || ((uintptr_t)zeros & 15) == 0);
-    if (fast) return launch_i4(gemv_int4_g128_kernel, a, smem, (cudaStream_t)stream);
-    return (K / 128 > 4 * kWarps) ? launch_i4(gemv_int4_group_kernel<8>, a, smem, (cudaStream_t)stream)
-                                  : launch_i4(gemv_int4_group_kernel<4>, a, smem, (cudaStream_t)stream);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (fast) {
+        bool done = false;
+        const int32_t rc = M <= 8 ? launch_i4_fast<1>(a, st, &done) : launch_i4_fast<2>(a, st, &done);
+        if (done) return rc;
+        // the activation tile of all M rows leaves no room for a weight ring: run blocks of as many rows as fit
+        int rows = 8;
+        while (rows > 0 && i4_fast_smem(1, 2, rows, a.K) > 200 * 1024) --rows;
+        if (rows > 0) {
+            for (int r0 = 0; r0 < (int)M; r0 += rows) {
+                I4Args b = a;
+                b.M = std::min(rows, (int)M - r0);
+                b.x = a.x + (int64_t)r0 * a.ldx;
+                b.out = a.out + (int64_t)r0 * a.ldo;
+                const int32_t rcb = launch_i4_fast<1>(b, st, &done);
+                if (rcb != RWKVQ_OK || !done) return rcb != RWKVQ_OK ? rcb : fail(RWKVQ_E_SHAPE, "%s: internal: row block does not fit", who);
+            }
+            return RWKVQ_OK;
+        }
+    }
+    const int64_t tiles = (N + 7) / 8;
+    return (K / 128 > 4 * kWarps) ? launch_i4(gemv_int4_group_kernel<8>, a, smem, st, tiles, false)
+                                  : launch_i4(gemv_int4_group_kernel<4>, a, smem, st, tiles, false);
 }
 
 }  // extern "C"
