@@ -34,6 +34,7 @@
 namespace rwkvq {
 
 constexpr int kGemvD = 4;                 // 64-byte units per chunk (one cp.async group): 2 KB per warp
+constexpr int kGemvHeadPad = 96;          // red | xs[32] | sh[8] | pad: 160 + 96 = 256 bytes before the ring
 
 static unsigned long long* g_gemv_trace = nullptr;
 
@@ -153,12 +154,13 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
     constexpr int D = kGemvD;
     constexpr int AB = QT == QT_FP8 ? 2 : 1;          // bytes per activation in the shared-memory tile
-    extern __shared__ __align__(16) uint8_t smem[];
-    // layout: red[2][kWarps][MT*4][32] | xs[32] | sh[8] | ring[kWarps][S][D][32 lanes] x 16 B | xq[M][pitch] + 512 B
+    extern __shared__ __align__(128) uint8_t smem[];
+    // layout: red[2][kWarps][MT*4][32] | xs[32] | sh[8] | xbar + pad (96 B) | ring[kWarps][S][D][32 lanes] x 16 B | xq[M][pitch] + 512 B
     T* red = reinterpret_cast<T*>(smem);
     float* xs = reinterpret_cast<float*>(smem + 2 * kWarps * MT * 4 * 32 * 4);
     float* sh = xs + 32;
-    uint8_t* ring = reinterpret_cast<uint8_t*>(sh + 8);
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(sh + 8);          // FP8: the raw activations have landed in the tile
+    uint8_t* ring = reinterpret_cast<uint8_t*>(sh + 8) + kGemvHeadPad;   // ring and tile start on a 128-byte boundary
     uint8_t* xq = ring + (size_t)kWarps * S * D * 512;
 
     griddep_launch_dependents();
@@ -223,12 +225,18 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     const bool pair_ok = (a.ldo % 2 == 0) && ((reinterpret_cast<uintptr_t>(a.out[mat]) & 3) == 0);
     const float wscale = a.ws[mat][0];       // weights and their scale are never written by a kernel
 
+    if (QT == QT_FP8 && threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(xbar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();  // the barrier and the zeroed pads are visible before anybody uses them
+
     griddep_wait();   // activations may come from the previous kernel; results may overwrite what it read
     w8_mark(a, 2);
 
     float out_scale = 0.f;   // FP8: (amax/448)*w_scale
     if constexpr (QT == QT_FP8) {
-        const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh);
+        const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh, xbar);
         out_scale = div_mode_f32(amax, 448.f, a.div_mode) * wscale;
     } else {
         quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
@@ -294,7 +302,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
 }
 
 static size_t smem_bytes(int MT, int M, int pitch, int S) {
-    return (size_t)2 * kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + (size_t)kWarps * S * kGemvD * 512 + (size_t)M * pitch + 512;
+    return (size_t)2 * kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + kGemvHeadPad + (size_t)kWarps * S * kGemvD * 512 + (size_t)M * pitch + 512;
 }
 
 constexpr size_t kFusedSmemMax = 200 * 1024;

@@ -147,72 +147,83 @@ __device__ __forceinline__ uint4 e4m3x8_to_f16x8(uint2 c) {
 // The decode GEMV keeps the quantized FP8 activations as f16 VALUES in shared memory (2 bytes per element): on sm_100
 // mma.sync has no fast e4m3 path, so weights are widened to f16 in registers and multiplied with m16n8k16.f16
 // (products of two e4m3 values and their fp32 sums are exact).
+//
+// The prologue runs once per CTA, straight after the dependency release, on cold instruction and data caches, and
+// every CTA of a launch reads the same few kilobytes of activations at the same moment.  So it is written for few
+// instructions and one read: thread 0 fetches the raw 16-bit rows with bulk copies (global -> shared, completion on
+// an mbarrier, independent of the weight ring's cp.async groups) INTO the tile itself -- a raw row and its row of f16
+// codes have the same size -- and two short loops (abs-max, then convert in place) work from shared memory.
+// `bar` must have been initialised with count 1 and made visible to the CTA.  A wait that runs out (seconds) falls
+// back to reading the row from global memory.
+__device__ __forceinline__ bool w8_bar_wait(uint64_t* bar) {
+    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+    for (int i = 0; i < (1 << 22); ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(b) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 template <int DT, bool WIDE>
-__device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh) {
+__device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh, uint64_t* bar) {
+    static_assert(WIDE, "the tile holds f16 values");
     const char* x = reinterpret_cast<const char*>(a.x[mat]);
     const float* awq = a.awq[mat];
     const int kv = a.K >> 3;                  // 8-element vectors per row
-    const int nvec = a.M * kv;
     const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
-    float m = 0.f;
-    if (nvec <= 4 * kThr) {
-        uint4 v[4];
-        int rr[4], kk[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int i = threadIdx.x + j * kThr;
-            rr[j] = -1;
-            if (i < nvec) {
-                rr[j] = (kv & (kv - 1)) == 0 ? (i >> (31 - __clz(kv))) : i / kv;
-                kk[j] = (i - rr[j] * kv) << 3;
-                v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)rr[j] * a.ldx + kk[j]) * 2);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (rr[j] >= 0) fp8_vec_amax<DT>(v[j], awq, kk[j], a.div_mode, after, m);
+    if (a.M * kv <= 2 * kThr) {
+        // one or two vectors per thread (M = 1 at K <= 4096): plain loads kept in registers are a little quicker
+        // than the staging copy
+        const int i0 = threadIdx.x, i1 = threadIdx.x + kThr, nvec = a.M * kv;
+        int r0 = 0, r1 = 0;
+        if (a.M > 1) { r0 = i0 / kv; r1 = i1 / kv; }
+        const int k0 = (i0 - r0 * kv) << 3, k1 = (i1 - r1 * kv) << 3;
+        uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+        if (i0 < nvec) v0 = *reinterpret_cast<const uint4*>(x + ((int64_t)r0 * a.ldx + k0) * 2);
+        if (i1 < nvec) v1 = *reinterpret_cast<const uint4*>(x + ((int64_t)r1 * a.ldx + k1) * 2);
+        float m = 0.f;
+        if (i0 < nvec) fp8_vec_amax<DT>(v0, awq, k0, a.div_mode, after, m);
+        if (i1 < nvec) fp8_vec_amax<DT>(v1, awq, k1, a.div_mode, after, m);
         w8_mark(a, 5);
         const float amax = fmaxf(cta_max(m, sh), 1e-12f);
         w8_mark(a, 6);
         const float inv = div_mode_f32(448.f, amax, a.div_mode);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (rr[j] >= 0) {
-                const uint2 c = fp8_vec_codes<DT>(v[j], awq, kk[j], a.div_mode, inv);
-                if constexpr (WIDE) *reinterpret_cast<uint4*>(xq + (size_t)rr[j] * a.pitch + kk[j] * 2) = e4m3x8_to_f16x8(c);
-                else *reinterpret_cast<uint2*>(xq + (size_t)rr[j] * a.pitch + kk[j]) = c;
-            }
+        if (i0 < nvec) *reinterpret_cast<uint4*>(xq + (size_t)r0 * a.pitch + k0 * 2) = e4m3x8_to_f16x8(fp8_vec_codes<DT>(v0, awq, k0, a.div_mode, inv));
+        if (i1 < nvec) *reinterpret_cast<uint4*>(xq + (size_t)r1 * a.pitch + k1 * 2) = e4m3x8_to_f16x8(fp8_vec_codes<DT>(v1, awq, k1, a.div_mode, inv));
         return amax;
     }
-    // larger blocks: row by row, four independent loads in flight per thread, no integer division
-    for (int r = 0; r < a.M; ++r) {
-        const char* xr = x + (int64_t)r * a.ldx * 2;
-        for (int b = threadIdx.x; b < kv; b += 4 * kThr) {
-            uint4 v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const uint4*>(xr + (size_t)min(b + j * kThr, kv - 1) * 16);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) fp8_vec_amax<DT>(v[j], awq, min(b + j * kThr, kv - 1) << 3, a.div_mode, after, m);
-        }
+    if (threadIdx.x == 0) {
+        const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K * 2)) : "memory");
+#pragma unroll 1
+        for (int r = 0; r < a.M; ++r)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(x + (int64_t)r * a.ldx * 2),
+                           "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
     }
-    const float amax = fmaxf(cta_max(m, sh), 1e-12f);
-    const float inv = div_mode_f32(448.f, amax, a.div_mode);
+    const bool staged = w8_bar_wait(bar);
+    float m = 0.f;
+#pragma unroll 1
     for (int r = 0; r < a.M; ++r) {
-        const char* xr = x + (int64_t)r * a.ldx * 2;
+        const char* src = staged ? reinterpret_cast<const char*>(xq + (size_t)r * a.pitch) : x + (int64_t)r * a.ldx * 2;
+#pragma unroll 1
+        for (int i = threadIdx.x; i < kv; i += kThr)
+            fp8_vec_amax<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, after, m);
+    }
+    w8_mark(a, 5);
+    const float amax = fmaxf(cta_max(m, sh), 1e-12f);
+    w8_mark(a, 6);
+    const float inv = div_mode_f32(448.f, amax, a.div_mode);
+#pragma unroll 1
+    for (int r = 0; r < a.M; ++r) {
         uint8_t* qr = xq + (size_t)r * a.pitch;
-        for (int b = threadIdx.x; b < kv; b += 4 * kThr) {
-            uint4 v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const uint4*>(xr + (size_t)min(b + j * kThr, kv - 1) * 16);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int kvi = b + j * kThr;
-                if (kvi < kv) {
-                    const uint2 c = fp8_vec_codes<DT>(v[j], awq, kvi << 3, a.div_mode, inv);
-                    if constexpr (WIDE) *reinterpret_cast<uint4*>(qr + (size_t)kvi * 16) = e4m3x8_to_f16x8(c);
-                    else *reinterpret_cast<uint2*>(qr + (size_t)kvi * 8) = c;
-                }
-            }
+        const char* src = staged ? reinterpret_cast<const char*>(qr) : x + (int64_t)r * a.ldx * 2;
+#pragma unroll 1
+        for (int i = threadIdx.x; i < kv; i += kThr) {
+            const uint2 c = fp8_vec_codes<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, inv);
+            *reinterpret_cast<uint4*>(qr + (size_t)i * 16) = e4m3x8_to_f16x8(c);      // in place: same thread, same 16 bytes
         }
     }
     return amax;

@@ -12,7 +12,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librwkvq.so")
+LIB_PATH = os.environ.get("RWKVQ_LIB") or os.path.join(_HERE, "librwkvq.so")   # RWKVQ_LIB: another build of the library
 
 OK = 0
 F16, BF16 = 0, 1
