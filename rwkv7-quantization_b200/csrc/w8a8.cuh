@@ -253,6 +253,33 @@ template <int DT>
 __device__ void quantize_int8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* xs, float* sh) {
     const char* x = reinterpret_cast<const char*>(a.x[mat]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (a.M <= 4 && a.K > 2 * kThr * 8 && a.K <= 8 * kThr * 8) {
+        // long rows: the whole CTA works on one row at a time and keeps it in registers between amax and codes
+        // (one read; measured quicker than two passes above K = 4096, slower below because of its code size)
+#pragma unroll 1
+        for (int r = 0; r < a.M; ++r) {
+            const char* xr = x + (int64_t)r * a.ldx * 2;
+            uint4 v[8];
+            float m = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int k = (threadIdx.x + j * kThr) * 8;
+                if (k < a.K) v[j] = *reinterpret_cast<const uint4*>(xr + k * 2);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((int)(threadIdx.x + j * kThr) * 8 < a.K) m = int8_vec_amax<DT>(v[j], m);
+            m = fmaxf(cta_max(m, sh), 1e-12f);
+            const float s = div_mode_f32(127.f, m, a.div_mode);
+            if (threadIdx.x == 0) xs[r] = div_mode_f32(m, 127.f, a.div_mode);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int k = (threadIdx.x + j * kThr) * 8;
+                if (k < a.K) *reinterpret_cast<uint2*>(xq + (size_t)r * a.pitch + k) = int8_vec_codes<DT>(v[j], s);
+            }
+        }
+        return;
+    }
     if (a.M <= 4) {
         for (int r = 0; r < a.M; ++r) {
             const char* xr = x + (int64_t)r * a.ldx * 2;
