@@ -194,13 +194,14 @@ struct I4FastArgs {
 template <int NT, int S>
 __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArgs fa) {
     const I4Args& a = fa.b;
-    extern __shared__ __align__(16) uint8_t smem[];
-    // layout: red[2][kWarps][NT*4][32] floats | ring[kWarps][S][kI4Stage] | xsum[M][units] floats | xs[M][pitch]
+    extern __shared__ __align__(128) uint8_t smem[];
+    // layout: red[2][kWarps][NT*4][32] floats | ring[kWarps][S][kI4Stage] | xbar (128 B) | xsum[M][units] floats | xs[M][pitch]
     const int units = a.K >> 7;
     float* red = reinterpret_cast<float*>(smem);
     uint8_t* ring = smem + 2 * kWarps * NT * 4 * 32 * 4;
-    float* xsum = reinterpret_cast<float*>(ring + (size_t)kWarps * S * kI4Stage);
-    uint8_t* xs = reinterpret_cast<uint8_t*>(xsum + ((a.M * units + 3) & ~3));
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(ring + (size_t)kWarps * S * kI4Stage);          // 128 bytes reserved
+    float* xsum = reinterpret_cast<float*>(ring + (size_t)kWarps * S * kI4Stage + 128);
+    uint8_t* xs = reinterpret_cast<uint8_t*>(xsum + ((a.M * units + 31) & ~31));       // 128-byte boundary
 
     griddep_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,14 +266,37 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
         xq1[i] = xsum + min(i * 8 + 2 * t + 1, a.M - 1) * units + ub;
     }
 
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(xbar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
     griddep_wait();
-    {   // prologue: permuted fp16 activations (odd pairs / 16) and per-unit activation sums
+    {   // prologue, one read of the activations.  Thread 0 fetches the raw fp16 rows with bulk copies INTO the tile
+        // (a raw row and its permuted copy have the same size; completion on an mbarrier, independent of the ring's
+        // cp.async groups); a short loop then permutes in place (odd pairs / 16) and sums each unit's 16 vectors
+        // over the 16 lanes that hold them.  A wait that runs out (seconds) falls back to reading global memory.
         const int kv = a.K >> 3;
         const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+        if (threadIdx.x == 0) {
+            const uint32_t b = (uint32_t)__cvta_generic_to_shared(xbar);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K * 2)) : "memory");
+#pragma unroll 1
+            for (int r = 0; r < a.M; ++r)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"((uint32_t)__cvta_generic_to_shared(xs + (size_t)r * a.pitch)), "l"(a.x + (int64_t)r * a.ldx),
+                               "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
+        }
+        const bool staged = w8_bar_wait(xbar);
+#pragma unroll 1
         for (int r = 0; r < a.M; ++r) {
-            const char* xr = reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx);
-            for (int i = threadIdx.x; i < kv; i += kThr) {
-                const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)i * 16);
+            uint8_t* row = xs + (size_t)r * a.pitch;
+            const char* src = staged ? reinterpret_cast<const char*>(row) : reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx);
+#pragma unroll 1
+            for (int i = threadIdx.x; i - lane < kv; i += kThr) {          // kv is a multiple of 16: half-warps are whole
+                const bool on = i < kv;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (on) v = *reinterpret_cast<const uint4*>(src + (size_t)i * 16);
                 uint4 p;
                 p.x = __byte_perm(v.x, v.z, 0x5410);
                 p.y = __byte_perm(v.x, v.z, 0x7632);
@@ -280,14 +304,12 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
                 p.w = __byte_perm(v.y, v.w, 0x7632);
                 *reinterpret_cast<__half2*>(&p.y) = __hmul2(*reinterpret_cast<__half2*>(&p.y), sixteenth);
                 *reinterpret_cast<__half2*>(&p.w) = __hmul2(*reinterpret_cast<__half2*>(&p.w), sixteenth);
-                *reinterpret_cast<uint4*>(xs + (size_t)r * a.pitch + (size_t)i * 16) = p;
-            }
-            const char* xrow = reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx);
-            for (int u = warp; u < units; u += kWarps) {
-                const uint2 v = *reinterpret_cast<const uint2*>(xrow + ((size_t)u << 8) + lane * 8);
-                const float2 f0 = cvt2<RWKVQ_F16>(v.x), f1 = cvt2<RWKVQ_F16>(v.y);
-                const float sum = warp_sum((f0.x + f0.y) + (f1.x + f1.y));
-                if (lane == 0) xsum[r * units + u] = sum;
+                if (on) *reinterpret_cast<uint4*>(row + (size_t)i * 16) = p;            // in place: same thread, same 16 bytes
+                const float2 f0 = cvt2<RWKVQ_F16>(v.x), f1 = cvt2<RWKVQ_F16>(v.y), f2 = cvt2<RWKVQ_F16>(v.z), f3 = cvt2<RWKVQ_F16>(v.w);
+                float s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (on && (lane & 15) == 0) xsum[r * units + (i >> 4)] = s;
             }
         }
         __syncthreads();
@@ -386,7 +408,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
 
 static size_t i4_fast_smem(int NT, int S, int M, int K) {
     const int units = K / 128;
-    return (size_t)2 * kWarps * NT * 4 * 32 * 4 + (size_t)kWarps * S * kI4Stage + (size_t)((M * units + 3) & ~3) * 4 + (size_t)M * (2 * K + 16);
+    return (size_t)2 * kWarps * NT * 4 * 32 * 4 + (size_t)kWarps * S * kI4Stage + 128 + (size_t)((M * units + 31) & ~31) * 4 + (size_t)M * (2 * K + 16);
 }
 
 template <typename Kern, typename Args>
