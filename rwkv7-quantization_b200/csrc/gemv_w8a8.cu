@@ -370,7 +370,9 @@ constexpr size_t kTwoPerSm = 110 * 1024;     // shared memory per CTA that still
 template <int QT, int DT, int MT, bool HALF>
 static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
     const size_t s5 = smem_bytes(MT, a.M, a.pitch, 5), s3 = smem_bytes(MT, a.M, a.pitch, 3), s2 = smem_bytes(MT, a.M, a.pitch, 2);
+    const size_t s4 = smem_bytes(MT, a.M, a.pitch, 4);
     if (s5 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 5>(a, s5, st);
+    if (s4 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 4>(a, s4, st);
     if (s3 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 3>(a, s3, st);
     RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the fused kernel's shared memory", a.M, a.K);
     if (s5 <= kFusedSmemMax) return launch_one<QT, DT, MT, HALF, 5>(a, s5, st);
