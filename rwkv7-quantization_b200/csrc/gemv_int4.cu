@@ -182,6 +182,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_group_kernel(const I4Args a
 // zeros g+8 as one 16-byte vector each).  A 32-bit word of each row gives the A registers of two MMAs (masks
 // 0x000F000F / 0x00F000F0 on the word and on the word >> 8, see the file header); the activations of token
 // min(g, M-1) are read with the matching permutation, tokens beyond M feed accumulator columns that are never stored.
+// In shared memory the 16 vectors of a unit are ordered [word q][lane t] (fast-path kernel only).
 // NT: token tiles of 8 (M <= 8 NT).  S: ring stages per warp.
 constexpr int kI4D = 4;                                   // units per chunk
 constexpr int kI4Stage = kI4D * 1024 + 512;               // bytes per warp and stage: weights + scales/zeros
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
     const float *xq0[NT], *xq1[NT];
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
-        xb0[i] = xs + min(i * 8 + g, a.M - 1) * a.pitch + ub * 256 + t * 64;
+        xb0[i] = xs + min(i * 8 + g, a.M - 1) * a.pitch + ub * 256 + t * 16;
         xq0[i] = xsum + min(i * 8 + 2 * t, a.M - 1) * units + ub;
         xq1[i] = xsum + min(i * 8 + 2 * t + 1, a.M - 1) * units + ub;
     }
@@ -304,7 +305,11 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
                 p.w = __byte_perm(v.y, v.w, 0x7632);
                 *reinterpret_cast<__half2*>(&p.y) = __hmul2(*reinterpret_cast<__half2*>(&p.y), sixteenth);
                 *reinterpret_cast<__half2*>(&p.w) = __hmul2(*reinterpret_cast<__half2*>(&p.w), sixteenth);
-                if (on) *reinterpret_cast<uint4*>(row + (size_t)i * 16) = p;            // in place: same thread, same 16 bytes
+                // Inside a unit (16 vectors, held by 16 neighbouring lanes) vector 4t+q goes to place 4q+t, so that the
+                // four t-lanes of a quarter-warp later read 64 contiguous bytes (no bank conflict).  In place: every
+                // lane has read its vector before any lane of the warp writes.
+                __syncwarp();
+                if (on) *reinterpret_cast<uint4*>(row + (size_t)((i & ~15) | ((i & 3) << 2) | ((i >> 2) & 3)) * 16) = p;
                 const float2 f0 = cvt2<RWKVQ_F16>(v.x), f1 = cvt2<RWKVQ_F16>(v.y), f2 = cvt2<RWKVQ_F16>(v.z), f3 = cvt2<RWKVQ_F16>(v.w);
                 float s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
 #pragma unroll
@@ -353,7 +358,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
                         float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            const uint4 bx = *reinterpret_cast<const uint4*>(xb[i] + j * 256 + q * 16);
+                            const uint4 bx = *reinterpret_cast<const uint4*>(xb[i] + j * 256 + q * 64);
                             const uint32_t hg = wgw[q] >> 8, hh = whw[q] >> 8;
                             mma_f16((q & 1) ? cb2 : ca, wgw[q] & 0x000F000Fu, whw[q] & 0x000F000Fu, wgw[q] & 0x00F000F0u, whw[q] & 0x00F000F0u, bx.x, bx.y);
                             mma_f16((q & 1) ? cb2 : ca, hg & 0x000F000Fu, hh & 0x000F000Fu, hg & 0x00F000F0u, hh & 0x00F000F0u, bx.z, bx.w);
