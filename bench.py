@@ -143,7 +143,7 @@ LAUNCHES_PER_STEP = 4 * LAYERS
 # dram__bytes_read.sum + dram__bytes_write.sum per gemv_w8a8_kernel launch of this workload, from the ncu launch list
 # summarised in profiles/gemv_w8a8_fp8_decode_launch_list.md (4-layer capture; traffic per launch does not depend on
 # the number of layers).  Algorithmic bytes per launch: 50 368 518.
-DRAM_TRAFFIC_PER_LAUNCH = 49_870_000
+DRAM_TRAFFIC_PER_LAUNCH = 50_200_000
 
 
 def prefill_pass(layers, x):
