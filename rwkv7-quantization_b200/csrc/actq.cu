@@ -247,28 +247,37 @@ __global__ void __launch_bounds__(kFusedThreads) actq_fp8_fused_kernel(const voi
     __shared__ float s_amax;
     __shared__ int s_fail;
     const int kv = K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // ---- pass 1: partial maximum of this CTA's rows
+    // ---- pass 1: partial maximum of this CTA's rows; four rows per step, so four loads per thread are in flight
     float m = 0.f;
-    for (int r = blockIdx.x; r < M; r += gridDim.x) {
-        const char* xr = reinterpret_cast<const char*>(x) + (int64_t)r * ldx * 2;
-        for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
-            const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)i * 16);
-            if (DT == RWKVQ_F16 && after_bf16) {
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    auto vec_max = [&](const uint4& v) {
+        if (DT == RWKVQ_F16 && after_bf16) {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = cvt2<DT>(w[q]);
-                    m = fmaxf(m, fmaxf(fabsf(bf16_round(f.x)), fabsf(bf16_round(f.y))));
-                }
-            } else if (DT == RWKVQ_F16) {
-                const __half2* h = reinterpret_cast<const __half2*>(&v);
-                const __half2 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-                m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
-            } else {
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-                const __nv_bfloat162 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-                m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                m = fmaxf(m, fmaxf(fabsf(bf16_round(f.x)), fabsf(bf16_round(f.y))));
             }
+        } else if (DT == RWKVQ_F16) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const __half2 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+            m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+        } else {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const __nv_bfloat162 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+            m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+        }
+    };
+    const int G = gridDim.x;
+    for (int r = blockIdx.x; r < M; r += 4 * G) {
+        for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int rj = min(r + j * G, M - 1);              // a clamped row repeats a value: harmless for a maximum
+                v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) vec_max(v[j]);
         }
     }
     m = warp_max(m);
@@ -311,20 +320,29 @@ __global__ void __launch_bounds__(kFusedThreads) actq_fp8_fused_kernel(const voi
     if (s_fail) return;
     // ---- pass 2: codes
     const float inv = div_mode_f32(448.f, fmaxf(s_amax, 1e-12f), div_mode);
-    for (int r = blockIdx.x; r < M; r += gridDim.x) {
-        const char* xr = reinterpret_cast<const char*>(x) + (int64_t)r * ldx * 2;
-        uint8_t* cr = codes + (int64_t)r * ldc;
+    for (int r = blockIdx.x; r < M; r += 4 * G) {
         for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
-            const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)i * 16);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t c[4];
+            uint4 v[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float2 f = cvt2<DT>(w[q]);
-                if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
-                c[q] = e4m3x2(f.x * inv, f.y * inv);
+            for (int j = 0; j < 4; ++j) {
+                const int rj = min(r + j * G, M - 1);
+                v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
             }
-            *reinterpret_cast<uint2*>(cr + (size_t)i * 8) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int rj = r + j * G;
+                if (rj < M) {
+                    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                    uint32_t c[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        float2 f = cvt2<DT>(w[q]);
+                        if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                        c[q] = e4m3x2(f.x * inv, f.y * inv);
+                    }
+                    *reinterpret_cast<uint2*>(codes + (int64_t)rj * ldc + (size_t)i * 8) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+                }
+            }
         }
     }
 }

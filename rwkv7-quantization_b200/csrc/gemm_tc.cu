@@ -113,8 +113,10 @@ struct PartIter {
             p.tile = (int)pos;
             p.mat = (int)(pos / (uint32_t)per_mat);
             const int r = (int)(pos - (uint32_t)p.mat * per_mat);
-            p.prow = (r / a.qtiles) * kTileP;
-            p.qrow = (r % a.qtiles) * a.NB;
+            // token tiles fastest: the CTAs running at one time share a few weight tiles (each read from HBM once and
+            // served to the others from L2), while the much smaller activation codes stay in L2 for the whole GEMM
+            p.prow = (r % a.ptiles) * kTileP;
+            p.qrow = (r / a.ptiles) * a.NB;
             p.kc0 = 0;
             p.kc1 = a.kchunks;
             p.slot = 0;
