@@ -238,8 +238,10 @@ __device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-template <int DT>
-__global__ void __launch_bounds__(kFusedThreads) actq_fp8_fused_kernel(const void* x, uint8_t* codes, float* amax_out, float* scale_out,
+// KEEP: a CTA has at most 8 rows of at most kFusedThreads vectors: every thread holds its vectors in registers across
+// the rendezvous, so the activations are read once and all of a thread's loads are in flight together.
+template <int DT, bool KEEP>
+__global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const void* x, uint8_t* codes, float* amax_out, float* scale_out,
                                                                       float* slots, uint32_t* flags, uint32_t token, int* status,
                                                                       int M, int K, int64_t ldx, int64_t ldc, int div_mode,
                                                                       int after_bf16, int from_bf16) {
@@ -268,16 +270,29 @@ __global__ void __launch_bounds__(kFusedThreads) actq_fp8_fused_kernel(const voi
         }
     };
     const int G = gridDim.x;
-    for (int r = blockIdx.x; r < M; r += 4 * G) {
-        for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
-            uint4 v[4];
+    uint4 keep[KEEP ? 8 : 1];
+    if constexpr (KEEP) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int rj = min(r + j * G, M - 1);              // a clamped row repeats a value: harmless for a maximum
-                v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
+        for (int j = 0; j < 8; ++j) {
+            const int rj = blockIdx.x + j * G;
+            keep[j] = make_uint4(0, 0, 0, 0);
+            if (rj < M && (int)threadIdx.x < kv)
+                keep[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)threadIdx.x * 8) * 2);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vec_max(keep[j]);
+    } else {
+        for (int r = blockIdx.x; r < M; r += 4 * G) {
+            for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
+                uint4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int rj = min(r + j * G, M - 1);              // a clamped row repeats a value: harmless for a maximum
+                    v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) vec_max(v[j]);
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) vec_max(v[j]);
         }
     }
     m = warp_max(m);
@@ -320,28 +335,35 @@ __global__ void __launch_bounds__(kFusedThreads) actq_fp8_fused_kernel(const voi
     if (s_fail) return;
     // ---- pass 2: codes
     const float inv = div_mode_f32(448.f, fmaxf(s_amax, 1e-12f), div_mode);
-    for (int r = blockIdx.x; r < M; r += 4 * G) {
-        for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
-            uint4 v[4];
+    auto vec_codes = [&](const uint4& v, int rj, int i) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t c[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int rj = min(r + j * G, M - 1);
-                v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
-            }
+        for (int q = 0; q < 4; ++q) {
+            float2 f = cvt2<DT>(w[q]);
+            if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+            c[q] = e4m3x2(f.x * inv, f.y * inv);
+        }
+        *reinterpret_cast<uint2*>(codes + (int64_t)rj * ldc + (size_t)i * 8) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+    };
+    if constexpr (KEEP) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int rj = r + j * G;
-                if (rj < M) {
-                    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-                    uint32_t c[4];
+        for (int j = 0; j < 8; ++j) {
+            const int rj = blockIdx.x + j * G;
+            if (rj < M && (int)threadIdx.x < kv) vec_codes(keep[j], rj, threadIdx.x);
+        }
+    } else {
+        for (int r = blockIdx.x; r < M; r += 4 * G) {
+            for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
+                uint4 v[4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        float2 f = cvt2<DT>(w[q]);
-                        if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
-                        c[q] = e4m3x2(f.x * inv, f.y * inv);
-                    }
-                    *reinterpret_cast<uint2*>(codes + (int64_t)rj * ldc + (size_t)i * 8) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+                for (int j = 0; j < 4; ++j) {
+                    const int rj = min(r + j * G, M - 1);
+                    v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
                 }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (r + j * G < M) vec_codes(v[j], r + j * G, i);
             }
         }
     }
@@ -464,7 +486,10 @@ int32_t rwkvq_actq_fp8_fused(const void* x, int32_t x_dtype, int64_t M, int64_t 
     int* st_ptr = status;
     void* args[] = {(void*)&x, (void*)&codes, (void*)&amax, (void*)&scale, (void*)&slots, (void*)&fl, (void*)&token, (void*)&st_ptr,
                     (void*)&m, (void*)&k, (void*)&ldx, (void*)&ldc, (void*)&div_mode, (void*)&after, (void*)&from_bf16};
-    const void* fn = x_dtype == RWKVQ_F16 ? (const void*)actq_fp8_fused_kernel<RWKVQ_F16> : (const void*)actq_fp8_fused_kernel<RWKVQ_BF16>;
+    const bool keep = K / 8 <= kFusedThreads && M <= 8 * (int64_t)grid;
+    const void* fn = x_dtype == RWKVQ_F16
+                         ? (keep ? (const void*)actq_fp8_fused_kernel<RWKVQ_F16, true> : (const void*)actq_fp8_fused_kernel<RWKVQ_F16, false>)
+                         : (keep ? (const void*)actq_fp8_fused_kernel<RWKVQ_BF16, true> : (const void*)actq_fp8_fused_kernel<RWKVQ_BF16, false>);
     const cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kFusedThreads), args, 0, (cudaStream_t)stream);
     if (e != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);

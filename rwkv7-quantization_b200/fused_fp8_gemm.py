@@ -11,8 +11,9 @@ CUDA stream without host synchronisation -- the conventions of the reference wra
 (fused_fp8_gemm.py:55-79, 645-679, 785-818, 944-1098).
 
 Routing by M = rows of the flattened activation:
-    M <= 8      ONE fused launch of the register-streaming GEMV (activation quantization in its prologue, weights
-                streamed once from HBM into mma.sync fragments) -- the decode path
+    M <= 32     ONE fused launch of the weight-streaming GEMV (activation quantization in its prologue, weights
+                streamed once from HBM through per-warp cp.async rings into mma.sync fragments) -- the decode path;
+                measured faster than the route below up to 32 rows
     M <= 128    activation-quantization kernels, then the tensor-memory weight-streaming kernel
                 (TMA -> tcgen05.mma, weights as the 128-row operand, stream-K over the SMs) on the codes
     larger M    activation-quantization kernels, then the 128 x 256 tile tcgen05 prefill GEMM
@@ -37,7 +38,7 @@ _GEMV_SMEM_BUDGET = 200 * 1024 - 70 * 1024     # what the activation tile may ta
 TC_FUSED_M_MAX = 4                 # rows up to which the activation quantization rides inside the streaming kernel
 _TC_CACHE_MAX = 100 * 1024        # shared memory for the activations (2 B) and their codes (1 B) in the fused kernel
 ROUTE = os.environ.get("RWKVQ_ROUTE", "auto").lower()   # auto | tc | mma
-GEMV_AUTO_M_MAX = 8
+GEMV_AUTO_M_MAX = 32
 
 
 # --------------------------------------------------------------------------- helpers
