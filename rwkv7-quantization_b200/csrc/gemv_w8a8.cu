@@ -3,20 +3,22 @@
 // The kernel is HBM-bound and written for instruction count: at the HBM rate an SM has about 88 issue slots per
 // 512 bytes of weights, and everything that is not a copy, a shared-memory load or an MMA eats into them.
 //
-// Data path.  The weight matrix [N,K] (one byte per element) is read exactly once.  A warp owns 8 weight rows
+// Data path.  The weight matrix [N,K] (one byte per element) is read exactly once.  A warp owns 16 weight rows
 // (one "row tile") over a contiguous K range; lane (g = lane/4, t = lane%4) copies the 16 bytes
-// W[n0+g][k0+16t .. +15] of each 64-byte unit with cp.async straight into its own 16 bytes of a per-warp ring in
-// shared memory, reads them back with one 128-bit load, and they ARE the B fragments of two mma.sync.m16n8k32
-// (INT8) or, widened to f16 in registers, of four m16n8k16 (FP8: mma.sync has no fast e4m3 path on sm_100).
-// An MMA sums over its k-slots, so the slots may be filled in any order as long as A and B agree; the A fragment
-// (quantized activations) is read with the same permutation from the activation tile in shared memory.
+// W[n0+g][k0+16t .. +15] and W[n0+g+8][same] of each 64-byte unit with cp.async straight into its own slots of a
+// per-warp ring in shared memory and reads them back with two 128-bit loads.  The WEIGHTS are the 16-row A operand
+// of mma.sync (rows g and g+8 of the lane) and up to 8 tokens the B operand: INT8 two m16n8k32 per unit; FP8 the
+// bytes are widened to f16 in registers (mma.sync has no fast e4m3 path on sm_100) for four m16n8k16 -- the
+// converted values land directly in the A registers, so no register moves surround the MMAs.  An MMA sums over its
+// k-slots, so the slots may be filled in any order as long as A and B agree; the B fragment (quantized
+// activations of token g) is a consecutive register pair of a 128-bit load from the activation tile.
 // All addresses inside a chunk of D units are a base register plus a compile-time offset.
 //
 // Work split.  A CTA (8 warps, two CTAs per SM) takes a contiguous range of the row tiles of ONE matrix and works
 // through it in rounds of R tiles (R = 1, 2, 4 or 8, chosen on the host so that a CTA usually needs one round);
 // 8/R warps share a tile, each with its own contiguous part of K, and add their partial sums in a fixed order
 // through shared memory (run-to-run identical results).  R = 8: no reduction, the lanes store their results.
-// A-fragment rows beyond M are read from row M-1: they only feed accumulator rows that are never stored.
+// B-fragment tokens beyond M are read from row M-1: they only feed accumulator columns that are never stored.
 //
 // Latency hiding.  Every warp keeps S-1 chunks (D x 512 bytes each) in flight; the ring runs ahead across rounds
 // and its first S-1 chunks are issued BEFORE the prologue.  With programmatic dependent launch that prefetch also
@@ -33,7 +35,7 @@
 
 namespace rwkvq {
 
-constexpr int kGemvD = 4;                 // 64-byte units per chunk (one cp.async group): 2 KB per warp
+constexpr int kGemvD = 2;                 // units per chunk (one cp.async group); a unit is 16 rows x 64 bytes = 1 KB per warp
 constexpr int kGemvHeadPad = 96;          // red | xs[32] | sh[8] | pad: 160 + 96 = 256 bytes before the ring
 
 static unsigned long long* g_gemv_trace = nullptr;
@@ -42,126 +44,100 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// The D asynchronous 16-byte copies (global -> shared, bypassing L1) of one chunk: slot J lies J*64 bytes further
-// along the weight row and J*512 bytes further in the warp's ring stage, both as immediates of the instruction.
-// FULL: every slot lies inside the row; otherwise a slot whose first byte is at or beyond kend copies nothing and
-// zero-fills its 16 bytes.
+// The 2 D asynchronous 16-byte copies (global -> shared, bypassing L1) of one chunk: unit J lies J*64 bytes further
+// along the two weight rows of this lane (g and g+8) and J*1024 bytes further in the warp's ring stage (row g+8 at
+// +512), all as immediates of the instruction.  FULL: every unit lies inside the row; otherwise a unit whose first
+// byte is at or beyond kend copies nothing and zero-fills its 16 bytes.
 template <int J, int D, bool FULL>
-__device__ __forceinline__ void issue_slots(uint32_t dst, const uint8_t* src, int kbyte, int kend, const uint8_t* safe) {
+__device__ __forceinline__ void issue_slots(uint32_t dst, const uint8_t* src0, const uint8_t* src1, int kbyte, int kend, const uint8_t* safe) {
     if constexpr (J < D) {
         if constexpr (FULL) {
-            asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(dst), "l"(src), "n"(J * 512), "n"(J * 64) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(dst), "l"(src0), "n"(J * 1024), "n"(J * 64) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(dst), "l"(src1), "n"(J * 1024 + 512), "n"(J * 64) : "memory");
         } else {
             const bool valid = kbyte + J * 64 < kend;
-            const uint8_t* p = valid ? src + J * 64 : safe;
             const int n = valid ? 16 : 0;
-            asm volatile("cp.async.cg.shared.global [%0+%3], [%1], 16, %2;" ::"r"(dst), "l"(p), "r"(n), "n"(J * 512) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0+%3], [%1], 16, %2;" ::"r"(dst), "l"(valid ? src0 + J * 64 : safe), "r"(n), "n"(J * 1024) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0+%3], [%1], 16, %2;" ::"r"(dst), "l"(valid ? src1 + J * 64 : safe), "r"(n), "n"(J * 1024 + 512) : "memory");
         }
-        issue_slots<J + 1, D, FULL>(dst, src, kbyte, kend, safe);
+        issue_slots<J + 1, D, FULL>(dst, src0, src1, kbyte, kend, safe);
     }
 }
 
-// One chunk of the K loop: D staged 16-byte weight slots of this lane against the activation tile.  xa[i][0] / [1]
-// point at this lane's bytes of rows g / g+8 of 16-row block i for slot 0; HALF: M <= 8, rows g+8 are zero.
-template <int QT, int MT, int D, bool HALF, typename T>
-__device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* const (&xa)[MT][2], T (&c)[MT][4], T (&c2)[MT][4]) {
+// One chunk of the K loop.  The WEIGHTS are the 16-row A operand of the MMA (rows g and g+8 of this lane), up to 8
+// tokens the B operand: xb[i] points at this lane's 16 k-values of token min(8i+g, M-1) for unit 0.  FP8: a lane's
+// 16 bytes per row are widened to eight f16 pairs and feed four m16n8k16 together with the other row's; the B
+// registers are consecutive pairs of two 128-bit loads.  INT8: two m16n8k32 per unit, B from one 128-bit load.
+template <int QT, int NT, int D, typename T>
+__device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* const (&xb)[NT], T (&c)[NT][4], T (&c2)[NT][4]) {
 #pragma unroll
     for (int j = 0; j < D; ++j) {
-        const uint4 wv = *reinterpret_cast<const uint4*>(st + j * 512);
+        const uint4 wg = *reinterpret_cast<const uint4*>(st + j * 1024);
+        const uint4 wh = *reinterpret_cast<const uint4*>(st + j * 1024 + 512);
         if constexpr (QT == QT_FP8) {
-            // widen the 16 weight bytes to f16 pairs; four m16n8k16 MMAs per 16 bytes on two accumulators
-            const uint4 w01 = e4m3x8_to_f16x8(make_uint2(wv.x, wv.y)), w23 = e4m3x8_to_f16x8(make_uint2(wv.z, wv.w));
+            const uint4 g01 = e4m3x8_to_f16x8(make_uint2(wg.x, wg.y)), g23 = e4m3x8_to_f16x8(make_uint2(wg.z, wg.w));
+            const uint4 h01 = e4m3x8_to_f16x8(make_uint2(wh.x, wh.y)), h23 = e4m3x8_to_f16x8(make_uint2(wh.z, wh.w));
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                const uint4 a00 = *reinterpret_cast<const uint4*>(xa[i][0] + j * 128);
-                const uint4 a01 = *reinterpret_cast<const uint4*>(xa[i][0] + j * 128 + 16);
-                if constexpr (HALF) {
-                    mma_f16(c[i], a00.x, 0u, a00.y, 0u, w01.x, w01.y);
-                    mma_f16(c[i], a00.z, 0u, a00.w, 0u, w01.z, w01.w);
-                    mma_f16(c2[i], a01.x, 0u, a01.y, 0u, w23.x, w23.y);
-                    mma_f16(c2[i], a01.z, 0u, a01.w, 0u, w23.z, w23.w);
-                } else {
-                    const uint4 a10 = *reinterpret_cast<const uint4*>(xa[i][1] + j * 128);
-                    const uint4 a11 = *reinterpret_cast<const uint4*>(xa[i][1] + j * 128 + 16);
-                    mma_f16(c[i], a00.x, a10.x, a00.y, a10.y, w01.x, w01.y);
-                    mma_f16(c[i], a00.z, a10.z, a00.w, a10.w, w01.z, w01.w);
-                    mma_f16(c2[i], a01.x, a11.x, a01.y, a11.y, w23.x, w23.y);
-                    mma_f16(c2[i], a01.z, a11.z, a01.w, a11.w, w23.z, w23.w);
-                }
+            for (int i = 0; i < NT; ++i) {
+                const uint4 b0 = *reinterpret_cast<const uint4*>(xb[i] + j * 128);
+                const uint4 b1 = *reinterpret_cast<const uint4*>(xb[i] + j * 128 + 16);
+                mma_f16(c[i], g01.x, h01.x, g01.y, h01.y, b0.x, b0.y);
+                mma_f16(c2[i], g01.z, h01.z, g01.w, h01.w, b0.z, b0.w);
+                mma_f16(c[i], g23.x, h23.x, g23.y, h23.y, b1.x, b1.y);
+                mma_f16(c2[i], g23.z, h23.z, g23.w, h23.w, b1.z, b1.w);
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                const uint4 a0 = *reinterpret_cast<const uint4*>(xa[i][0] + j * 64);
-                if constexpr (HALF) {
-                    mma_s8(c[i], a0.x, 0u, a0.y, 0u, wv.x, wv.y);
-                    mma_s8(c2[i], a0.z, 0u, a0.w, 0u, wv.z, wv.w);
-                } else {
-                    const uint4 a1 = *reinterpret_cast<const uint4*>(xa[i][1] + j * 64);
-                    mma_s8(c[i], a0.x, a1.x, a0.y, a1.y, wv.x, wv.y);
-                    mma_s8(c2[i], a0.z, a1.z, a0.w, a1.w, wv.z, wv.w);
-                }
+            for (int i = 0; i < NT; ++i) {
+                const uint4 b = *reinterpret_cast<const uint4*>(xb[i] + j * 64);
+                mma_s8(c[i], wg.x, wh.x, wg.y, wh.y, b.x, b.y);
+                mma_s8(c2[i], wg.z, wh.z, wg.w, wh.w, b.z, b.w);
             }
         }
     }
 }
 
-// Results of one row tile, straight from the accumulator fragments: lane (g, t) holds rows g and g+8 of each 16-row
-// block and the two columns n0+2t, n0+2t+1.
-template <int QT, int MT, bool HALF, typename T>
-__device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[MT][4], float out_scale,
-                                           const float* xs, float wscale, bool pair_ok) {
-    const int n = n0 + 2 * t;
-    if (n >= a.N) return;
-    const bool two = n + 1 < a.N;
+// Results of one 16-row tile, straight from the accumulator fragments: lane (g, t) holds weight rows n0+g (values 0, 1)
+// and n0+g+8 (values 2, 3) for the tokens 8i+2t and 8i+2t+1.
+template <int QT, int NT, typename T>
+__device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[NT][4], float out_scale,
+                                           const float* xs, float wscale) {
 #pragma unroll
-    for (int i = 0; i < MT; ++i)
+    for (int i = 0; i < NT; ++i)
 #pragma unroll
-        for (int h = 0; h < (HALF ? 1 : 2); ++h) {
-            const int m = i * 16 + g + 8 * h;
-            if (m >= a.M) continue;
-            float f0, f1;
+        for (int j = 0; j < 4; ++j) {
+            const int m = i * 8 + 2 * t + (j & 1), n = n0 + g + ((j & 2) ? 8 : 0);
+            if (m >= a.M || n >= a.N) continue;
+            float f;
             if constexpr (QT == QT_FP8) {
-                f0 = c[i][2 * h] * out_scale;
-                f1 = c[i][2 * h + 1] * out_scale;
+                f = c[i][j] * out_scale;
             } else {
-                if (a.acc[mat]) {
-                    a.acc[mat][(int64_t)m * a.ldacc + n] = c[i][2 * h];
-                    if (two) a.acc[mat][(int64_t)m * a.ldacc + n + 1] = c[i][2 * h + 1];
-                }
-                const float rs = xs[m] * wscale;
-                f0 = (float)c[i][2 * h] * rs;
-                f1 = (float)c[i][2 * h + 1] * rs;
+                if (a.acc[mat]) a.acc[mat][(int64_t)m * a.ldacc + n] = c[i][j];
+                f = (float)c[i][j] * (xs[m] * wscale);
             }
-            if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
-            __half* o = a.out[mat] + (int64_t)m * a.ldo + n;
-            if (two && pair_ok) {
-                *reinterpret_cast<__half2*>(o) = __floats2half2_rn(f0, f1);
-            } else {
-                o[0] = __float2half_rn(f0);
-                if (two) o[1] = __float2half_rn(f1);
-            }
+            if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
+            a.out[mat][(int64_t)m * a.ldo + n] = __float2half_rn(f);
         }
 }
 
-// S: stages of each warp's shared-memory weight ring.  HALF: M <= 8.
+// S: stages of each warp's shared-memory weight ring.  NT: token tiles of 8 (M <= 8 NT).
 // Everything between the kernel's entry and its first copies, and between the dependency release and the first
 // MMA, is a single pass of dependent scalar code and shows up in full in a 5-15 us launch: the tile split and all
 // divisions are done on the host (W8Args::tq, trem, lgR), and whatever does not need the activations is computed
 // before griddepcontrol.wait.
-template <int QT, int DT, int MT, bool HALF, int S>
+template <int QT, int DT, int NT, int S>
 __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
     constexpr int D = kGemvD;
     constexpr int AB = QT == QT_FP8 ? 2 : 1;          // bytes per activation in the shared-memory tile
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: red[2][kWarps][MT*4][32] | xs[32] | sh[8] | xbar + pad (96 B) | ring[kWarps][S][D][32 lanes] x 16 B | xq[M][pitch] + 512 B
+    // layout: red[2][kWarps][NT*4][32] | xs[32] | sh[8] | xbar + pad (96 B) | ring[kWarps][S][D][2][32 lanes] x 16 B | xq[M][pitch] + 512 B
     T* red = reinterpret_cast<T*>(smem);
-    float* xs = reinterpret_cast<float*>(smem + 2 * kWarps * MT * 4 * 32 * 4);
+    float* xs = reinterpret_cast<float*>(smem + 2 * kWarps * NT * 4 * 32 * 4);
     float* sh = xs + 32;
     uint64_t* xbar = reinterpret_cast<uint64_t*>(sh + 8);          // FP8: the raw activations have landed in the tile
     uint8_t* ring = reinterpret_cast<uint8_t*>(sh + 8) + kGemvHeadPad;   // ring and tile start on a 128-byte boundary
-    uint8_t* xq = ring + (size_t)kWarps * S * D * 512;
+    uint8_t* xq = ring + (size_t)kWarps * S * D * 1024;
 
     griddep_launch_dependents();
     w8_mark(a, 0);
@@ -170,7 +146,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     const int g = lane >> 2, t = lane & 3;
     const int mat = ((int)blockIdx.x >= a.cpm) + ((int)blockIdx.x >= 2 * a.cpm);
     const int cb = (int)blockIdx.x - mat * a.cpm;
-    const int tb = cb * a.tq + min(cb, a.trem), te = tb + a.tq + (cb < a.trem ? 1 : 0);   // this CTA's row tiles
+    const int tb = cb * a.tq + min(cb, a.trem), te = tb + a.tq + (cb < a.trem ? 1 : 0);   // this CTA's 16-row tiles
     const int lgR = a.lgR, R = 1 << lgR, lgKS = 3 - lgR, KS = 1 << lgKS;
     const int slot = warp >> lgKS, ks = warp & (KS - 1);     // which tile of a round, which part of K
     const int rounds = (te - tb + R - 1) >> lgR;
@@ -181,23 +157,29 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     const int kend = min(ue * 64, a.K);
     const bool full = ((ue - ub) % D == 0) && (a.K % 64 == 0);
     const int my_rounds = (nch > 0 && te - tb > slot) ? ((te - tb - slot + R - 1) >> lgR) : 0;   // rounds in which this warp has a tile
-    uint8_t* my_ring = ring + (size_t)warp * S * D * 512 + lane * 16;
+    uint8_t* my_ring = ring + (size_t)warp * S * D * 1024 + lane * 16;
     const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
     const uint8_t* wbase = a.w[mat];
 
     // producer side of the ring: chunk p_ch of the tile of round p_round goes to stage p_stage; one group per chunk
     int p_round = 0, p_ch = 0, p_stage = 0;
-    auto row_ptr = [&](int round) { return wbase + (int64_t)min((tb + round * R + slot) * 8 + g, a.N - 1) * a.ldw + kbeg; };
-    const uint8_t* p_src = my_rounds > 0 ? row_ptr(0) : wbase;
+    const uint8_t *p_src0 = wbase, *p_src1 = wbase;
+    auto set_rows = [&](int round) {
+        const int n0 = (tb + round * R + slot) << 4;
+        p_src0 = wbase + (int64_t)min(n0 + g, a.N - 1) * a.ldw + kbeg;
+        p_src1 = wbase + (int64_t)min(n0 + g + 8, a.N - 1) * a.ldw + kbeg;
+    };
+    if (my_rounds > 0) set_rows(0);
     auto issue = [&]() {
         if (p_round < my_rounds) {
-            const uint32_t dst = my_ring_s + p_stage * (D * 512);
-            if (full) issue_slots<0, D, true>(dst, p_src, 0, 0, wbase);
-            else issue_slots<0, D, false>(dst, p_src, kbeg + p_ch * (D * 64), kend, wbase);
-            p_src += D * 64;
+            const uint32_t dst = my_ring_s + p_stage * (D * 1024);
+            if (full) issue_slots<0, D, true>(dst, p_src0, p_src1, 0, 0, wbase);
+            else issue_slots<0, D, false>(dst, p_src0, p_src1, kbeg + p_ch * (D * 64), kend, wbase);
+            p_src0 += D * 64;
+            p_src1 += D * 64;
             if (++p_ch == nch) {
                 p_ch = 0;
-                if (++p_round < my_rounds) p_src = row_ptr(p_round);
+                if (++p_round < my_rounds) set_rows(p_round);
             }
         }
         cp_async_commit();
@@ -215,14 +197,10 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
         if (threadIdx.x >= 32 && threadIdx.x < 64)
             *reinterpret_cast<uint4*>(xq + (size_t)a.M * a.pitch + (threadIdx.x - 32) * 16) = make_uint4(0, 0, 0, 0);
     }
-    // this lane's rows of the activation tile (rows g and g+8 of each 16-row block); rows beyond M read row M-1
-    const uint8_t* xa0[MT][2];
+    // this lane's token rows of the activation tile; tokens beyond M read row M-1 (columns that are never stored)
+    const uint8_t* xb0[NT];
 #pragma unroll
-    for (int i = 0; i < MT; ++i) {
-        xa0[i][0] = xq + min(i * 16 + g, a.M - 1) * a.pitch + kbeg * AB;
-        xa0[i][1] = xq + min(i * 16 + g + 8, a.M - 1) * a.pitch + kbeg * AB;
-    }
-    const bool pair_ok = (a.ldo % 2 == 0) && ((reinterpret_cast<uintptr_t>(a.out[mat]) & 3) == 0);
+    for (int i = 0; i < NT; ++i) xb0[i] = xq + min(i * 8 + g, a.M - 1) * a.pitch + kbeg * AB;
     const float wscale = a.ws[mat][0];       // weights and their scale are never written by a kernel
 
     if (QT == QT_FP8 && threadIdx.x == 0) {
@@ -246,63 +224,57 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
 
     int stage = 0;
     for (int r = 0; r < rounds; ++r) {
-        T c[MT][4], c2[MT][4];
+        T c[NT][4], c2[NT][4];
 #pragma unroll
-        for (int i = 0; i < MT; ++i)
+        for (int i = 0; i < NT; ++i)
 #pragma unroll
             for (int j = 0; j < 4; ++j) c[i][j] = c2[i][j] = 0;
         if (r < my_rounds) {
-            const uint8_t* xa[MT][2];
+            const uint8_t* xb[NT];
 #pragma unroll
-            for (int i = 0; i < MT; ++i) {
-                xa[i][0] = xa0[i][0];
-                xa[i][1] = xa0[i][1];
-            }
+            for (int i = 0; i < NT; ++i) xb[i] = xb0[i];
             for (int ch = 0; ch < nch; ++ch) {
                 issue();                       // keep S-1 chunks in flight
                 cp_async_wait<S - 1>();        // this lane's copies of the current chunk have landed
-                chunk_body<QT, MT, D, HALF>(my_ring + stage * (D * 512), xa, c, c2);
+                chunk_body<QT, NT, D>(my_ring + stage * (D * 1024), xb, c, c2);
 #pragma unroll
-                for (int i = 0; i < MT; ++i) {
-                    xa[i][0] += D * 64 * AB;
-                    xa[i][1] += D * 64 * AB;
-                }
+                for (int i = 0; i < NT; ++i) xb[i] += D * 64 * AB;
                 if (++stage == S) stage = 0;
             }
 #pragma unroll
-            for (int i = 0; i < MT; ++i)
+            for (int i = 0; i < NT; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) c[i][j] += c2[i][j];      // the two accumulators halve the dependent MMA chains
         }
         const int tile = tb + r * R + slot;
         if (KS > 1) {
             // the warps of a tile add their parts of K in warp order; the buffer alternates between rounds
-            T* rb = red + (size_t)(r & 1) * kWarps * MT * 4 * 32;
+            T* rb = red + (size_t)(r & 1) * kWarps * NT * 4 * 32;
             if (ks > 0) {
 #pragma unroll
-                for (int i = 0; i < MT; ++i)
+                for (int i = 0; i < NT; ++i)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) rb[((warp * MT + i) * 4 + j) * 32 + lane] = c[i][j];
+                    for (int j = 0; j < 4; ++j) rb[((warp * NT + i) * 4 + j) * 32 + lane] = c[i][j];
             }
             __syncthreads();
             if (ks == 0 && tile < te) {
                 for (int kk = 1; kk < KS; ++kk)
 #pragma unroll
-                    for (int i = 0; i < MT; ++i)
+                    for (int i = 0; i < NT; ++i)
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) c[i][j] += rb[(((warp + kk) * MT + i) * 4 + j) * 32 + lane];
-                store_tile<QT, MT, HALF>(a, mat, tile * 8, g, t, c, out_scale, xs, wscale, pair_ok);
+                        for (int j = 0; j < 4; ++j) c[i][j] += rb[(((warp + kk) * NT + i) * 4 + j) * 32 + lane];
+                store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale);
             }
         } else if (tile < te) {
-            store_tile<QT, MT, HALF>(a, mat, tile * 8, g, t, c, out_scale, xs, wscale, pair_ok);
+            store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale);
         }
     }
     cp_async_wait<0>();
     w8_mark(a, 4);
 }
 
-static size_t smem_bytes(int MT, int M, int pitch, int S) {
-    return (size_t)2 * kWarps * MT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + kGemvHeadPad + (size_t)kWarps * S * kGemvD * 512 + (size_t)M * pitch + 512;
+static size_t smem_bytes(int NT, int M, int pitch, int S) {
+    return (size_t)2 * kWarps * NT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + kGemvHeadPad + (size_t)kWarps * S * kGemvD * 1024 + (size_t)M * pitch + 512;
 }
 
 constexpr size_t kFusedSmemMax = 200 * 1024;
@@ -315,9 +287,9 @@ static bool use_pdl() {
     return on;
 }
 
-template <int QT, int DT, int MT, bool HALF, int S>
+template <int QT, int DT, int NT, int S>
 static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
-    auto kern = gemv_w8a8_kernel<QT, DT, MT, HALF, S>;
+    auto kern = gemv_w8a8_kernel<QT, DT, NT, S>;
     // per instantiation and device: opt in to large dynamic shared memory and ask how many CTAs fit on an SM
     static thread_local int cfg_dev = -1;
     static thread_local size_t cfg_smem = ~size_t(0);
@@ -335,7 +307,7 @@ static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
         cfg_smem = smem;
     }
     // every CTA works on one matrix: the grid is a multiple of the matrix count, at most one wave
-    const int ntile = (a.N + 7) / 8;
+    const int ntile = (a.N + 15) / 16;
     a.cpm = std::max(1, std::min(ntile, sm_count() * per_sm / a.nmat));
     a.tq = ntile / a.cpm;                 // CTA cb of a matrix takes tq row tiles, the first trem CTAs one more
     a.trem = ntile % a.cpm;
@@ -367,23 +339,23 @@ static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
 constexpr size_t kTwoPerSm = 110 * 1024;     // shared memory per CTA that still lets two CTAs share an SM
 
 // deepest ring that still leaves room for two CTAs per SM; a big activation tile gets a shallow ring and one CTA
-template <int QT, int DT, int MT, bool HALF>
+template <int QT, int DT, int NT>
 static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
-    const size_t s5 = smem_bytes(MT, a.M, a.pitch, 5), s3 = smem_bytes(MT, a.M, a.pitch, 3), s2 = smem_bytes(MT, a.M, a.pitch, 2);
-    const size_t s4 = smem_bytes(MT, a.M, a.pitch, 4);
-    if (s5 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 5>(a, s5, st);
-    if (s4 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 4>(a, s4, st);
-    if (s3 <= kTwoPerSm) return launch_one<QT, DT, MT, HALF, 3>(a, s3, st);
+    const size_t s5 = smem_bytes(NT, a.M, a.pitch, 5), s4 = smem_bytes(NT, a.M, a.pitch, 4), s3 = smem_bytes(NT, a.M, a.pitch, 3),
+                 s2 = smem_bytes(NT, a.M, a.pitch, 2);
+    if (s5 <= kTwoPerSm) return launch_one<QT, DT, NT, 5>(a, s5, st);
+    if (s4 <= kTwoPerSm) return launch_one<QT, DT, NT, 4>(a, s4, st);
+    if (s3 <= kTwoPerSm) return launch_one<QT, DT, NT, 3>(a, s3, st);
     RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the fused kernel's shared memory", a.M, a.K);
-    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, MT, HALF, 5>(a, s5, st);
-    return launch_one<QT, DT, MT, HALF, 2>(a, s2, st);
+    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, NT, 5>(a, s5, st);
+    return launch_one<QT, DT, NT, 2>(a, s2, st);
 }
 
 template <int QT, int DT>
 static int32_t dispatch_mt(const W8Args& a, cudaStream_t st) {
-    if (a.M <= 8) return dispatch_s<QT, DT, 1, true>(a, st);
-    if (a.M <= 16) return dispatch_s<QT, DT, 1, false>(a, st);
-    return dispatch_s<QT, DT, 2, false>(a, st);
+    if (a.M <= 8) return dispatch_s<QT, DT, 1>(a, st);
+    if (a.M <= 16) return dispatch_s<QT, DT, 2>(a, st);
+    return dispatch_s<QT, DT, 4>(a, st);
 }
 
 template <int QT>
@@ -405,7 +377,7 @@ static int32_t run_fused(W8Args a, int x_dtype, cudaStream_t st, const char* who
     // shared-memory row pitch of the activation tile: int8 codes (1 B) or f16 values of the e4m3 codes (2 B);
     // the odd 64 / 16 bytes keep the fragment loads of different rows on different banks
     a.pitch = QT == QT_FP8 ? ((2 * a.K + 127) / 128) * 128 + 16 : ((a.K + 127) / 128) * 128 + 64;
-    RWKVQ_REQUIRE((int64_t)a.nmat * ((a.N + 7) / 8) < (int64_t(1) << 27), RWKVQ_E_SHAPE, "%s: N too large", who);
+    RWKVQ_REQUIRE((int64_t)a.nmat * ((a.N + 15) / 16) < (int64_t(1) << 27), RWKVQ_E_SHAPE, "%s: N too large", who);
     return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16>(a, st) : dispatch_mt<QT, RWKVQ_BF16>(a, st);
 }
 
