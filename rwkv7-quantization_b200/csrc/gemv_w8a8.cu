@@ -35,7 +35,8 @@
 
 namespace rwkvq {
 
-constexpr int kGemvD = 2;                 // units per chunk (one cp.async group); a unit is 16 rows x 64 bytes = 1 KB per warp
+constexpr int kGemvD = 4;                 // units per chunk (one cp.async group); a unit is 16 rows x 64 bytes = 1 KB per warp:
+                                          // a lane streams 256 contiguous bytes of each of its two rows per chunk
 constexpr int kGemvHeadPad = 96;          // red | xs[32] | sh[8] | pad: 160 + 96 = 256 bytes before the ring
 
 static unsigned long long* g_gemv_trace = nullptr;
@@ -131,9 +132,9 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     constexpr int D = kGemvD;
     constexpr int AB = QT == QT_FP8 ? 2 : 1;          // bytes per activation in the shared-memory tile
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: red[2][kWarps][NT*4][32] | xs[32] | sh[8] | xbar + pad (96 B) | ring[kWarps][S][D][2][32 lanes] x 16 B | xq[M][pitch] + 512 B
+    // layout: red[kWarps][NT*4][32] | xs[32] | sh[8] | xbar + pad (96 B) | ring[kWarps][S][D][2][32 lanes] x 16 B | xq[M][pitch] + 512 B
     T* red = reinterpret_cast<T*>(smem);
-    float* xs = reinterpret_cast<float*>(smem + 2 * kWarps * NT * 4 * 32 * 4);
+    float* xs = reinterpret_cast<float*>(smem + kWarps * NT * 4 * 32 * 4);
     float* sh = xs + 32;
     uint64_t* xbar = reinterpret_cast<uint64_t*>(sh + 8);          // FP8: the raw activations have landed in the tile
     uint8_t* ring = reinterpret_cast<uint8_t*>(sh + 8) + kGemvHeadPad;   // ring and tile start on a 128-byte boundary
@@ -248,8 +249,9 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
         }
         const int tile = tb + r * R + slot;
         if (KS > 1) {
-            // the warps of a tile add their parts of K in warp order; the buffer alternates between rounds
-            T* rb = red + (size_t)(r & 1) * kWarps * NT * 4 * 32;
+            // the warps of a tile add their parts of K in warp order
+            T* rb = red;
+            if (r > 0) __syncthreads();        // the previous round's partial sums have been read
             if (ks > 0) {
 #pragma unroll
                 for (int i = 0; i < NT; ++i)
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
 }
 
 static size_t smem_bytes(int NT, int M, int pitch, int S) {
-    return (size_t)2 * kWarps * NT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + kGemvHeadPad + (size_t)kWarps * S * kGemvD * 1024 + (size_t)M * pitch + 512;
+    return (size_t)kWarps * NT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + kGemvHeadPad + (size_t)kWarps * S * kGemvD * 1024 + (size_t)M * pitch + 512;
 }
 
 constexpr size_t kFusedSmemMax = 200 * 1024;
