@@ -642,7 +642,9 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
         a.status = a.counters + kWsCounterInts;
         a.scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(c.workspace) + kWsHeaderBytes);
     } else {
+        // 256 weight rows per tile; narrower tiles while halving them still leaves no more tiles than SMs
         a.NB = 256;
+        while (a.NB > 64 && 2 * (int64_t)a.nmat * ((a.M + kTileP - 1) / kTileP) * ((a.N + a.NB - 1) / a.NB) <= tc_grid()) a.NB >>= 1;
         a.ptiles = (a.M + kTileP - 1) / kTileP;
         a.qtiles = (a.N + a.NB - 1) / a.NB;
         grid = (int)std::min<int64_t>(tc_grid(), (int64_t)a.nmat * a.ptiles * a.qtiles);

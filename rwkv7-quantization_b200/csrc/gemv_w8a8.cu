@@ -348,6 +348,7 @@ static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
     if (s5 <= kTwoPerSm) return launch_one<QT, DT, NT, 5>(a, s5, st);
     if (s4 <= kTwoPerSm) return launch_one<QT, DT, NT, 4>(a, s4, st);
     if (s3 <= kTwoPerSm) return launch_one<QT, DT, NT, 3>(a, s3, st);
+    // long rows (K = 16384): one CTA per SM with the deep ring measured faster than two CTAs with two stages
     RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the fused kernel's shared memory", a.M, a.K);
     if (s5 <= kFusedSmemMax) return launch_one<QT, DT, NT, 5>(a, s5, st);
     return launch_one<QT, DT, NT, 2>(a, s2, st);
