@@ -279,7 +279,7 @@ static size_t smem_bytes(int NT, int M, int pitch, int S) {
     return (size_t)kWarps * NT * 4 * 32 * 4 + 32 * 4 + 8 * 4 + kGemvHeadPad + (size_t)kWarps * S * kGemvD * 1024 + (size_t)M * pitch + 512;
 }
 
-constexpr size_t kFusedSmemMax = 200 * 1024;
+constexpr size_t kFusedSmemMax = 224 * 1024;    // of the 227 KB a CTA may opt in to
 
 static bool use_pdl() {
     static const bool on = [] {

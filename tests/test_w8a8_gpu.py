@@ -259,6 +259,22 @@ def test_fp8_linear_fused(mods, m, n, k, dt):
     assert rel_err(out, want) <= 1e-2
 
 
+@pytest.mark.parametrize("scheme", ["fp8", "int8"])
+@pytest.mark.parametrize("m", [9, 15, 16, 31])
+def test_decode_width_4096_many_rows(mods, scheme, m):
+    """K = 4096 with as many rows as the fused GEMV takes by itself: the activation tile is at its largest here
+    (shared-memory sizing of the ring beside it)."""
+    _, f, _ = mods
+    n, k = 520, 4096
+    x = outliers(gen(m + 5, (m, k), 1.0)).to(torch.bfloat16)
+    if scheme == "fp8":
+        info = fp8_weight(3, n, k)
+        assert rel_err(f.linear_fp8_fused(x.cuda(), to_dev(info)), O.linear_fp8_fused(x, info, _lib_div(mods))) <= 1e-2
+    else:
+        info = int8_weight(4, n, k)
+        bits_equal(f.linear_int8_fused(x.cuda(), to_dev(info)), O.linear_int8_fused(x, info, _lib_div(mods)))
+
+
 @pytest.mark.parametrize("m", [1, 8, 32, 64])
 def test_fp8_rkv_config2(mods, m):
     """BASELINE config 2: three [2560,2560] e4m3 matrices, bf16 activations with outlier channels."""
