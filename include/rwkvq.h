@@ -258,6 +258,15 @@ int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_b
                          int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                          void* stream);
 
+/* Decode projection in ONE launch, M <= 16, K a multiple of 512: the activation quantization above runs in the kernel's
+ * prologue (same arithmetic: amax, tensor scale, block scales, codes) and the weights are streamed once; the result
+ * equals rwkvq_actq_nvfp4 followed by rwkvq_gemv_nvfp4 up to the order of the fp32 additions.  Weight code rows and
+ * weight scale rows 16-byte aligned.  rwkvq_gemv_nvfp4_fused_smem_bytes(M, K) must not exceed 224 KiB. */
+int64_t rwkvq_gemv_nvfp4_fused_smem_bytes(int64_t M, int64_t K);
+int32_t rwkvq_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, const uint8_t* w_codes, int64_t ldw,
+                               const uint8_t* w_block_scales, int64_t ldws, const float* w_tscale, void* out_f16,
+                               int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Many-token NVFP4 projection on the block-scaled tensor cores (tcgen05 kind::mxf4nvf4, 16-wide blocks): the path
  * the reference's reports call "block-scaled NVFP4 MMAs" (11_fused_gemm_ops_en.md:20-26).  Same arithmetic and
  * operands as rwkvq_gemv_nvfp4 for any M, except that both scale arrays are given BLOCKED: 512-byte chunks

@@ -189,6 +189,309 @@ __global__ void __launch_bounds__(kThr, 2) gemv_nvfp4_kernel(const Nf4Args a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------- fused decode GEMV
+// One launch per projection for M <= 16 (K a multiple of 512): the activation quantization of rwkvq_actq_nvfp4 runs in
+// the prologue (amax, tensor scale, block scales, codes -- and straight on to the dequantized fp16 values
+// code * block scale, which is all the MMA needs), and the weight stream is organised like the INT4 group kernel:
+// the WEIGHTS are the 16-row A operand of m16n8k16 (rows g and g+8 of lane (g, t)), up to 8 tokens the B operand;
+// a warp owns 16 weight rows over a contiguous K range; a unit is 128 k (64 bytes per row, 8 scale blocks); a chunk is
+// 4 units plus the 32 scale bytes of each of the 16 rows, all copied with cp.async into a per-warp ring.  A lane's
+// 16 bytes of a row are 32 codes = two scale blocks: 16 cvt.f16x2.e2m1x2 and 16 HMUL2 per row make the A registers
+// of 8 MMAs.  Activations of a unit are stored [word][lane] (see the INT4 kernel) so that the B-fragment loads have no
+// bank conflicts.  8/R warps share a row tile and add their K parts in warp order.
+constexpr int kNfD = 4;
+constexpr int kNfStage = kNfD * 1024 + 512;       // bytes per warp and stage: codes of 4 units + scales of 16 rows
+
+__device__ __forceinline__ void nf_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void nf_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct NfFusedArgs {
+    const void* x;             // [M, ldx] fp16 / bf16
+    const uint8_t* w;          // [N, ldw] packed codes
+    const uint8_t* w_bs;       // [N, ldws] e4m3 block scales
+    const float* w_ts;         // [1]
+    __half* out;               // [M, ldo]
+    int64_t ldx, ldw, ldws, ldo;
+    int M, N, K, pitch;
+    int lgR, tq, trem;
+};
+
+template <int DT, int NT, int S>
+__global__ void __launch_bounds__(kThr, 2) gemv_nvfp4_fused_kernel(const NfFusedArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // layout: red[kWarps][NT*4][32] floats | ring[kWarps][S][kNfStage] | sh[8] floats + barrier (128 B) | xs[M][pitch]
+    float* red = reinterpret_cast<float*>(smem);
+    uint8_t* ring = smem + kWarps * NT * 4 * 32 * 4;
+    float* sh = reinterpret_cast<float*>(ring + (size_t)kWarps * S * kNfStage);
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(sh + 16);
+    uint8_t* xs = reinterpret_cast<uint8_t*>(sh) + 128;
+
+    griddep_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int units = a.K >> 7;
+    const int cb = blockIdx.x;
+    const int tb = cb * a.tq + min(cb, a.trem), te = tb + a.tq + (cb < a.trem ? 1 : 0);   // this CTA's 16-row tiles
+    const int lgR = a.lgR, R = 1 << lgR, lgKS = 3 - lgR, KS = 1 << lgKS;
+    const int slot = warp >> lgKS, ks = warp & (KS - 1);
+    const int rounds = (te - tb + R - 1) >> lgR;
+    const int upw = (((units + KS - 1) >> lgKS) + 3) & ~3;           // units per warp and tile, whole chunks
+    const int ub = ks * upw, ue = min(ub + upw, units);
+    const int nch = max(ue - ub, 0) >> 2;
+    const int my_rounds = (nch > 0 && te - tb > slot) ? ((te - tb - slot + R - 1) >> lgR) : 0;
+    uint8_t* my_ring = ring + (size_t)warp * S * kNfStage;
+    const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
+
+    // producer: per chunk 8 code copies per lane and one 16-byte piece of the scales (t = 0, 1: row g; t = 2, 3: row g+8)
+    int p_round = 0, p_ch = 0, p_stage = 0;
+    const uint8_t *p_w0 = a.w, *p_w1 = a.w, *p_sc = a.w_bs;
+    auto set_rows = [&](int round) {
+        const int n0 = (tb + round * R + slot) << 4;
+        const int r0 = min(n0 + g, a.N - 1), r1 = min(n0 + g + 8, a.N - 1);
+        p_w0 = a.w + (int64_t)r0 * a.ldw + ub * 64 + 16 * t;
+        p_w1 = a.w + (int64_t)r1 * a.ldw + ub * 64 + 16 * t;
+        p_sc = a.w_bs + (int64_t)((t & 2) ? r1 : r0) * a.ldws + ub * 8 + 16 * (t & 1);
+    };
+    if (my_rounds > 0) set_rows(0);
+    auto issue = [&]() {
+        if (p_round < my_rounds) {
+            const uint32_t dst = my_ring_s + p_stage * kNfStage;
+#pragma unroll
+            for (int j = 0; j < kNfD; ++j) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 1024 + lane * 16), "l"(p_w0 + j * 64) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 1024 + 512 + lane * 16), "l"(p_w1 + j * 64) : "memory");
+            }
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + kNfD * 1024 + (((t >> 1) * 8 + g) * 32) + (t & 1) * 16), "l"(p_sc) : "memory");
+            p_w0 += kNfD * 64;
+            p_w1 += kNfD * 64;
+            p_sc += kNfD * 8;
+            if (++p_ch == nch) {
+                p_ch = 0;
+                if (++p_round < my_rounds) set_rows(p_round);
+            }
+        }
+        nf_cp_async_commit();
+        if (++p_stage == S) p_stage = 0;
+    };
+#pragma unroll
+    for (int i = 0; i < S - 1; ++i) issue();
+
+    // this lane's token rows of the activation tile (tokens beyond M read row M-1: columns that are never stored)
+    const uint8_t* xb0[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) xb0[i] = xs + min(i * 8 + g, a.M - 1) * a.pitch + ub * 256 + t * 16;
+    const float w_ts = a.w_ts[0];
+
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(xbar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    griddep_wait();
+
+    // ---- prologue: activation quantization, fused.  Raw rows by bulk copy into the tile; amax; then every thread turns
+    // 16-blocks into dequantized fp16 values in place.
+    float pts;
+    {
+        if (threadIdx.x == 0) {
+            const uint32_t b = (uint32_t)__cvta_generic_to_shared(xbar);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K * 2)) : "memory");
+#pragma unroll 1
+            for (int r = 0; r < a.M; ++r)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"((uint32_t)__cvta_generic_to_shared(xs + (size_t)r * a.pitch)),
+                               "l"(reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2), "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
+        }
+        const bool staged = w8_bar_wait(xbar);
+        const int kv = a.K >> 3;
+        float m = 0.f;
+#pragma unroll 1
+        for (int r = 0; r < a.M; ++r) {
+            const char* src = staged ? reinterpret_cast<const char*>(xs + (size_t)r * a.pitch) : reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
+#pragma unroll 1
+            for (int i = threadIdx.x; i < kv; i += kThr) m = fmaxf(m, packed_absmax8<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16)));
+        }
+        const float amax = fmaxf(cta_max(m, sh), 1e-12f);
+        pts = __fdiv_rn(amax, 2688.f);
+        const float inv_pts = __fdiv_rn(1.f, pts), k448 = __fdiv_rn(448.f, amax);
+        const int nb = a.K >> 4;                                   // 16-blocks per row (a multiple of 32)
+#pragma unroll 1
+        for (int r = 0; r < a.M; ++r) {
+            uint8_t* row = xs + (size_t)r * a.pitch;
+            const char* src = staged ? reinterpret_cast<const char*>(row) : reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
+#pragma unroll 1
+            for (int b = threadIdx.x; b < nb; b += kThr) {
+                const uint4 v0 = *reinterpret_cast<const uint4*>(src + (size_t)b * 32), v1 = *reinterpret_cast<const uint4*>(src + (size_t)b * 32 + 16);
+                const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                float f[16], bm = 0.f;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const float2 p = cvt2<DT>(wv[q]);
+                    f[2 * q] = p.x;
+                    f[2 * q + 1] = p.y;
+                    bm = fmaxf(bm, fmaxf(fabsf(p.x), fabsf(p.y)));
+                }
+                const float sb = fminf(fmaxf(bm * k448, 0.015625f), 448.f);
+                const uint32_t sc = e4m3x2(sb, 0.f) & 0xffu;
+                const uint32_t s2 = e4m3x2_to_f16x2(sc);
+                const uint32_t ss = __byte_perm(s2, s2, 0x1010);           // (bs, bs) as fp16
+                const float bs = __half2float(__ushort_as_half((unsigned short)(s2 & 0xffffu)));
+                uint32_t h[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const uint32_t pair = e2m1x2_to_f16x2(e2m1x2(__fdiv_rn(f[2 * q] * inv_pts, bs), __fdiv_rn(f[2 * q + 1] * inv_pts, bs)));
+                    const __half2 d = __hmul2(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&ss));
+                    h[q] = *reinterpret_cast<const uint32_t*>(&d);
+                }
+                // vectors 2b, 2b+1 of the row; inside a unit (16 vectors) vector 4t+i goes to place 4i+t.  In place: the
+                // eight blocks of a unit sit in eight neighbouring lanes, all of which have read before any writes.
+                __syncwarp();
+                const int v = 2 * b, u16 = v & ~15, tt = (v >> 2) & 3, i0 = v & 3;
+                *reinterpret_cast<uint4*>(row + (size_t)(u16 | (i0 << 2) | tt) * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4*>(row + (size_t)(u16 | ((i0 + 1) << 2) | tt) * 16) = make_uint4(h[4], h[5], h[6], h[7]);
+            }
+        }
+        __syncthreads();
+    }
+    const float out_scale = pts * w_ts;
+
+    int stage = 0;
+    for (int r = 0; r < rounds; ++r) {
+        float c[NT][4], c2[NT][4];
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) c[i][j] = c2[i][j] = 0.f;
+        if (r < my_rounds) {
+            const uint8_t* xb[NT];
+#pragma unroll
+            for (int i = 0; i < NT; ++i) xb[i] = xb0[i];
+            for (int ch = 0; ch < nch; ++ch) {
+                issue();
+                nf_cp_async_wait<S - 1>();
+                __syncwarp();                              // the scale bytes are read across lanes
+                const uint8_t* st = my_ring + stage * kNfStage;
+#pragma unroll
+                for (int j = 0; j < kNfD; ++j) {
+                    const uint4 wg = *reinterpret_cast<const uint4*>(st + j * 1024 + lane * 16);
+                    const uint4 wh = *reinterpret_cast<const uint4*>(st + j * 1024 + 512 + lane * 16);
+                    // this lane's two scale blocks of the unit, rows g and g+8, as fp16 pairs (s, s)
+                    const uint32_t sg = e4m3x2_to_f16x2(*reinterpret_cast<const unsigned short*>(st + kNfD * 1024 + g * 32 + j * 8 + 2 * t));
+                    const uint32_t shh = e4m3x2_to_f16x2(*reinterpret_cast<const unsigned short*>(st + kNfD * 1024 + (8 + g) * 32 + j * 8 + 2 * t));
+                    const uint32_t sgv[2] = {__byte_perm(sg, sg, 0x1010), __byte_perm(sg, sg, 0x3232)};
+                    const uint32_t shv[2] = {__byte_perm(shh, shh, 0x1010), __byte_perm(shh, shh, 0x3232)};
+                    const uint32_t wgw[4] = {wg.x, wg.y, wg.z, wg.w}, whw[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {          // word q: codes 8q .. 8q+7 of the lane's 32; block q / 2
+                        uint32_t ag[4], ah[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const uint32_t pg = e2m1x2_to_f16x2((wgw[q] >> (8 * e)) & 0xffu), ph = e2m1x2_to_f16x2((whw[q] >> (8 * e)) & 0xffu);
+                            const __half2 dg = __hmul2(*reinterpret_cast<const __half2*>(&pg), *reinterpret_cast<const __half2*>(&sgv[q >> 1]));
+                            const __half2 dh = __hmul2(*reinterpret_cast<const __half2*>(&ph), *reinterpret_cast<const __half2*>(&shv[q >> 1]));
+                            ag[e] = *reinterpret_cast<const uint32_t*>(&dg);
+                            ah[e] = *reinterpret_cast<const uint32_t*>(&dh);
+                        }
+#pragma unroll
+                        for (int i = 0; i < NT; ++i) {
+                            const uint4 bx = *reinterpret_cast<const uint4*>(xb[i] + j * 256 + q * 64);
+                            mma_f16(c[i], ag[0], ah[0], ag[1], ah[1], bx.x, bx.y);
+                            mma_f16(c2[i], ag[2], ah[2], ag[3], ah[3], bx.z, bx.w);
+                        }
+                    }
+                }
+                __syncwarp();                              // all lanes have read this stage before it is refilled
+#pragma unroll
+                for (int i = 0; i < NT; ++i) xb[i] += kNfD * 256;
+                if (++stage == S) stage = 0;
+            }
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[i][j] += c2[i][j];
+        }
+        const int tile = tb + r * R + slot;
+        bool store = tile < te;
+        if (KS > 1) {
+            if (r > 0) __syncthreads();
+            if (ks > 0) {
+#pragma unroll
+                for (int i = 0; i < NT; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) red[((warp * NT + i) * 4 + j) * 32 + lane] = c[i][j];
+            }
+            __syncthreads();
+            store = store && ks == 0;
+            if (store) {
+                for (int kk = 1; kk < KS; ++kk)
+#pragma unroll
+                    for (int i = 0; i < NT; ++i)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) c[i][j] += red[(((warp + kk) * NT + i) * 4 + j) * 32 + lane];
+            }
+        }
+        if (store) {
+            const int n0 = tile << 4;
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int m = i * 8 + 2 * t + (j & 1), n = n0 + g + ((j & 2) ? 8 : 0);
+                    if (m < a.M && n < a.N) a.out[(int64_t)m * a.ldo + n] = __float2half_rn(c[i][j] * out_scale);
+                }
+        }
+    }
+    nf_cp_async_wait<0>();
+}
+
+static size_t nf_fused_smem(int NT, int S, int M, int K) {
+    return (size_t)kWarps * NT * 4 * 32 * 4 + (size_t)kWarps * S * kNfStage + 128 + (size_t)M * (2 * K + 16);
+}
+
+template <int DT, int NT, int S>
+static int32_t launch_nf_fused(NfFusedArgs a, size_t smem, cudaStream_t st) {
+    auto kern = gemv_nvfp4_fused_kernel<DT, NT, S>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_nvfp4_fused: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThr, smem);
+    if (e != cudaSuccess || per_sm < 1) return fail(RWKVQ_E_LAUNCH, "gemv_nvfp4_fused: occupancy query failed");
+    const int64_t tiles = (a.N + 15) / 16;
+    const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * std::min(per_sm, 2));
+    a.tq = (int)(tiles / grid);
+    a.trem = (int)(tiles % grid);
+    const int tpc = (int)((tiles + grid - 1) / grid);
+    a.lgR = 0;
+    while ((1 << a.lgR) < kWarps && (1 << a.lgR) < tpc) ++a.lgR;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThr);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    const char* env = std::getenv("RWKVQ_PDL");
+    cfg.numAttrs = (env && env[0] == '0') ? 0 : 1;
+    e = cudaLaunchKernelEx(&cfg, kern, a);
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "gemv_nvfp4_fused: %s", cudaGetErrorString(e));
+    }
+    return check_launch("gemv_nvfp4_fused");
+}
+
+template <int DT, int NT>
+static int32_t dispatch_nf_fused(const NfFusedArgs& a, cudaStream_t st) {
+    const size_t s2 = nf_fused_smem(NT, 2, a.M, a.K), s4 = nf_fused_smem(NT, 4, a.M, a.K);
+    if (s2 <= 110 * 1024) return launch_nf_fused<DT, NT, 2>(a, s2, st);
+    if (s4 <= 224 * 1024) return launch_nf_fused<DT, NT, 4>(a, s4, st);
+    RWKVQ_REQUIRE(s2 <= 224 * 1024, RWKVQ_E_SHAPE, "gemv_nvfp4_fused: M*K = %d*%d does not fit shared memory; call with fewer rows", a.M, a.K);
+    return launch_nf_fused<DT, NT, 2>(a, s2, st);
+}
+
 }  // namespace rwkvq
 
 using namespace rwkvq;
@@ -244,6 +547,30 @@ int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_b
     const unsigned grid = (unsigned)std::min<int64_t>(tiles, (int64_t)sm_count() * per_sm);
     kern<<<grid, kThr, smem, (cudaStream_t)stream>>>(a);
     return check_launch(who);
+}
+
+int64_t rwkvq_gemv_nvfp4_fused_smem_bytes(int64_t M, int64_t K) { return (int64_t)nf_fused_smem(M <= 8 ? 1 : 2, 2, (int)M, (int)K); }
+
+int32_t rwkvq_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, const uint8_t* w_codes, int64_t ldw,
+                               const uint8_t* w_block_scales, int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo,
+                               int64_t M, int64_t N, int64_t K, void* stream) {
+    const char* who = "gemv_nvfp4_fused";
+    RWKVQ_REQUIRE(x && w_codes && w_block_scales && w_tscale && out_f16, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M <= 16, RWKVQ_E_SHAPE, "%s: M=%lld (at most 16 rows per call)", who, (long long)M);
+    RWKVQ_REQUIRE(K % 512 == 0, RWKVQ_E_SHAPE, "%s: K=%lld must be a multiple of 512", who, (long long)K);
+    RWKVQ_REQUIRE(aligned16(w_codes) && ldw % 16 == 0 && ldw >= K / 2, RWKVQ_E_ALIGN, "%s: weight code rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(aligned16(w_block_scales) && ldws % 16 == 0 && ldws >= K / 16, RWKVQ_E_ALIGN, "%s: weight scale rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(ldo >= N, RWKVQ_E_SHAPE, "%s: ldo < N", who);
+    if (M == 0 || N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
+    NfFusedArgs a{};
+    a.x = x; a.w = w_codes; a.w_bs = w_block_scales; a.w_ts = w_tscale; a.out = (__half*)out_f16;
+    a.ldx = ldx; a.ldw = ldw; a.ldws = ldws; a.ldo = ldo; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.pitch = (int)(2 * K + 16);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == RWKVQ_F16) return M <= 8 ? dispatch_nf_fused<RWKVQ_F16, 1>(a, st) : dispatch_nf_fused<RWKVQ_F16, 2>(a, st);
+    return M <= 8 ? dispatch_nf_fused<RWKVQ_BF16, 1>(a, st) : dispatch_nf_fused<RWKVQ_BF16, 2>(a, st);
 }
 
 }  // extern "C"

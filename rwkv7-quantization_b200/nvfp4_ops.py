@@ -105,11 +105,18 @@ def _blocked_weight_scales(weight_info, k: int) -> torch.Tensor:
 
 
 def _route(m: int, k: int) -> str:
-    """'tc' = block-scaled tensor-core GEMM (more than TC_MIN_M tokens, K a multiple of 256), 'gemv' otherwise."""
+    """'fused' = one launch, activation quantization in the GEMV's prologue (up to TC_MIN_M tokens, K a multiple of 512);
+    'tc' = block-scaled tensor-core GEMM (more tokens, K a multiple of 256); 'gemv' = quantization kernels + the
+    16-row GEMV (any K that is a multiple of 128)."""
     forced = os.environ.get("RWKVQ_NVFP4_ROUTE", "auto")
     if forced == "gemv" or k % 256 != 0:
         return "gemv"
-    return "tc" if (forced == "tc" or m > TC_MIN_M) else "gemv"
+    if forced == "tc" or m > TC_MIN_M:
+        return "tc"
+    # the tensor scale is per call: all rows must go into one launch
+    if k % 512 == 0 and abi.lib().rwkvq_gemv_nvfp4_fused_smem_bytes(m, k) <= 224 * 1024:
+        return "fused"
+    return "gemv"
 
 
 def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
@@ -117,11 +124,20 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
     weight-streaming GEMV; more than TC_MIN_M tokens run the tcgen05 block-scaled GEMM."""
     w, wbs, wts = weight_info["weight"], weight_info["block_scale"], weight_info["tensor_scale"]
     n, k = w.shape[0], w.shape[1] * 2
-    codes, bs, pts = quantize_activations_nvfp4(x)
-    m = codes.shape[0]
-    out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
     wts = wts.reshape(1)
-    if _route(m, k) == "tc":
+    from fused_fp8_gemm import _rows16
+    x2 = _rows16(x).contiguous()
+    m = x2.shape[0]
+    route = _route(m, k)
+    if route == "fused" and wbs.stride(0) % 16 == 0 and wbs.data_ptr() % 16 == 0:
+        out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+        abi.call("rwkvq_gemv_nvfp4_fused", x2.data_ptr(), abi.dtype_code(x2), k, w.data_ptr(), w.stride(0), wbs.data_ptr(),
+                 wbs.stride(0), wts.data_ptr(), out.data_ptr(), n, m, n, k, abi.stream_ptr())
+        out = out.reshape(*x.shape[:-1], n)
+        return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
+    codes, bs, pts = quantize_activations_nvfp4(x)
+    out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
+    if route == "tc":
         ws = abi.workspace(1, 1, 1, 1, codes.device)
         a_blk, w_blk = pack_scales(bs, k), _blocked_weight_scales(weight_info, k)     # both alive until the launch
         abi.call("rwkvq_tc_gemm_nvfp4", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),

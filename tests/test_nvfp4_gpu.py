@@ -129,3 +129,24 @@ def test_tensor_core_route(nf, monkeypatch, bn, m, n, k):
     oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
              "tensor_scale": info["tensor_scale"].cpu()}
     assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (3, 520, 1024), (8, 136, 512), (9, 1000, 2048), (16, 256, 4096), (2, 264, 16384)])
+def test_fused_decode_route(nf, monkeypatch, dt, m, n, k):
+    """One-launch decode GEMV (activation quantization in its prologue) against the oracle and against the
+    quantize-then-GEMV route."""
+    w = gen(n + k + 1, (n, k), (1.0 / k) ** 0.5)
+    info = dev(nf.quantize_to_nvfp4(w))
+    x = gen(m * 7 + 1, (m, k), 1.0).to(dt)
+    if m > 2:
+        x[1].zero_()
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "auto")
+    assert nf._route(m, k) == "fused"
+    out = nf.linear_nvfp4(x.cuda(), info)
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "gemv")
+    via_gemv = nf.linear_nvfp4(x.cuda(), info)
+    assert rel_err(out, via_gemv) <= 2e-3
+    oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
+             "tensor_scale": info["tensor_scale"].cpu()}
+    assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
