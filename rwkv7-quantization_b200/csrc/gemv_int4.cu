@@ -418,7 +418,7 @@ static size_t i4_fast_smem(int NT, int S, int M, int K) {
 
 template <typename Kern, typename Args>
 static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64_t tiles, bool fast) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
     if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     int per_sm = 0;
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThr, smem);
@@ -453,7 +453,7 @@ static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64
 
 template <int NT>
 static int32_t launch_i4_fast(const I4Args& a, cudaStream_t st, bool* done) {
-    constexpr size_t kTwo = 110 * 1024, kMax = 200 * 1024;
+    constexpr size_t kTwo = 110 * 1024, kMax = 224 * 1024;
     I4FastArgs fa{};
     fa.b = a;
     const int64_t tiles = (a.N + 15) / 16;
@@ -509,7 +509,7 @@ int32_t rwkvq_gemv_int4_group(const void* x_f16, int64_t ldx, const uint8_t* pac
         if (done) return rc;
         // the activation tile of all M rows leaves no room for a weight ring: run blocks of as many rows as fit
         int rows = 8;
-        while (rows > 0 && i4_fast_smem(1, 2, rows, a.K) > 200 * 1024) --rows;
+        while (rows > 0 && i4_fast_smem(1, 2, rows, a.K) > 224 * 1024) --rows;
         if (rows > 0) {
             for (int r0 = 0; r0 < (int)M; r0 += rows) {
                 I4Args b = a;
