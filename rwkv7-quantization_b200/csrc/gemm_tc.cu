@@ -619,7 +619,11 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
     if (a.M == 0 || a.N == 0) return RWKVQ_OK;
     RWKVQ_REQUIRE(a.K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
 
-    const bool swap = c.fused || a.M <= 128;
+    // Weights as the 128-row operand with stream-K (SWAP) pays for few tokens only: measured on the 7.2B shapes, the
+    // GEMM mode below (tokens as the 128-row operand, narrow weight tiles) is 2-4 x faster from 33 tokens on, except
+    // for a long K against few weight tiles (FFN value: K = 16384, N = 4096), where stream-K wins up to 48 tokens.
+    const int64_t narrow_tiles = (int64_t)a.nmat * ((a.M + kTileP - 1) / kTileP) * ((a.N + 63) / 64);
+    const bool swap = c.fused || a.M <= 16 || (a.M <= 48 && a.K >= 8192 && 2 * narrow_tiles <= tc_grid());
     if (c.fused) RWKVQ_REQUIRE(a.M <= 16, RWKVQ_E_SHAPE, "%s: the fused kernel takes M <= 16, got %d", who, a.M);
     a.kchunks = (a.K + kChunk - 1) / kChunk;
     TcMaps maps;

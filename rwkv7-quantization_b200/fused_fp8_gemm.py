@@ -14,9 +14,10 @@ Routing by M = rows of the flattened activation:
     M <= 32     ONE fused launch of the weight-streaming GEMV (activation quantization in its prologue, weights
                 streamed once from HBM through per-warp cp.async rings into mma.sync fragments) -- the decode path;
                 measured faster than the route below up to 32 rows
-    M <= 128    activation-quantization kernels, then the tensor-memory weight-streaming kernel
-                (TMA -> tcgen05.mma, weights as the 128-row operand, stream-K over the SMs) on the codes
-    larger M    activation-quantization kernels, then the 128 x 256 tile tcgen05 prefill GEMM
+    larger M    activation-quantization kernel, then the tcgen05 GEMM on the codes: tokens as the 128-row operand,
+                128 x 256 tiles (narrower while there are fewer tiles than SMs); only a long K against few weight rows
+                (FFN value) with at most 48 tokens, or a call whose activations do not fit the GEMV's shared memory,
+                takes the weight-streaming form (weights as the 128-row operand, stream-K over the SMs)
 RWKVQ_ROUTE=tc  sends M <= 4 to the tensor-memory kernel with the quantization fused into it as well;
 RWKVQ_ROUTE=mma keeps everything on the mma.sync kernels (M <= 32 fused, codes GEMM above).  All routes compute the
 same results (INT8 bit for bit) and cross-check each other in the tests.
