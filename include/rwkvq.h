@@ -258,6 +258,16 @@ int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_b
                          int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                          void* stream);
 
+/* The same quantization in ONE cooperative launch (amax, grid-wide rendezvous with a bounded wait, codes and scales).
+ * block_scales (row-major) and block_scales_blocked (the order rwkvq_tc_gemm_nvfp4 takes, K a multiple of 64, buffer
+ * of rwkvq_nvfp4_blocked_scale_bytes(M, K); rows past M are left unwritten) may each be NULL, not both.  scratch:
+ * rwkvq_actq_nvfp4_fused_scratch_bytes() bytes owned by the caller, not shared by overlapping calls; status (may be
+ * NULL) receives RWKVQ_E_TIMEOUT if the rendezvous gives up. */
+int64_t rwkvq_actq_nvfp4_fused_scratch_bytes(void);
+int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes,
+                               int64_t ldc, uint8_t* block_scales, int64_t lds, uint8_t* block_scales_blocked, float* pts,
+                               void* scratch, int64_t scratch_bytes, int32_t* status, void* stream);
+
 /* Decode projection in ONE launch, M <= 16, K a multiple of 512: the activation quantization above runs in the kernel's
  * prologue (same arithmetic: amax, tensor scale, block scales, codes) and the weights are streamed once; the result
  * equals rwkvq_actq_nvfp4 followed by rwkvq_gemv_nvfp4 up to the order of the fp32 additions.  Weight code rows and

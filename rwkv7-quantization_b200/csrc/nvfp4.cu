@@ -13,6 +13,7 @@
 // from the streamed 16-byte loads (cvt.f16x2.e2m1x2 + one HMUL2 per pair) -- and multiplied with mma.sync.m16n8k16
 // with fp32 accumulation: every product is exact.  Same work split as the INT4 GEMV: 8 weight rows per CTA, the 8
 // warps on alternating 128-k units, register ring of loads across row tiles, fixed-order reduction.
+#include <atomic>
 #include <cstdlib>
 
 #include "w8a8.cuh"
@@ -492,6 +493,132 @@ static int32_t dispatch_nf_fused(const NfFusedArgs& a, cudaStream_t st) {
     return launch_nf_fused<DT, NT, 2>(a, s2, st);
 }
 
+// ---------------------------------------------------------------------------------------- fused activation quantization
+// rwkvq_actq_nvfp4 in ONE cooperative launch (the structure of the fused FP8 quantizer): per-CTA partial maxima, a
+// grid-wide rendezvous through a token that is unique per launch, then codes and block scales.  A 16-block is two
+// 8-element vectors held by two neighbouring threads, which exchange their maxima with one shuffle.  The block scales
+// are written row-major and / or in the blocked order the tensor-core GEMM reads (either pointer may be null).
+constexpr int kNfQThreads = 512;
+
+__device__ __forceinline__ uint32_t nf_ld_acquire(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void nf_st_release(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+struct NfQArgs {
+    const void* x;
+    uint8_t* codes;
+    uint8_t* bs_rows;        // [M, lds] or null
+    uint8_t* bs_blocked;     // blocked order or null
+    float* pts;
+    float* slots;
+    uint32_t* flags;
+    int* status;
+    int64_t ldx, ldc, lds;
+    int M, K;
+    uint32_t token;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(kNfQThreads, 2) actq_nvfp4_fused_kernel(const NfQArgs a) {
+    __shared__ float sh[kNfQThreads / 32];
+    __shared__ float s_amax;
+    __shared__ int s_fail;
+    const int kv = a.K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = gridDim.x;
+    // ---- pass 1: partial maximum of this CTA's rows, four rows per step
+    float m = 0.f;
+    for (int r = blockIdx.x; r < a.M; r += 4 * G) {
+        for (int i = threadIdx.x; i < kv; i += kNfQThreads) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int rj = min(r + j * G, a.M - 1);
+                v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(a.x) + ((int64_t)rj * a.ldx + (int64_t)i * 8) * 2);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m = fmaxf(m, packed_absmax8<DT>(v[j]));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) sh[warp] = m;
+    if (threadIdx.x == 0) s_fail = 0;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = sh[0];
+        for (int i = 1; i < kNfQThreads / 32; ++i) b = fmaxf(b, sh[i]);
+        a.slots[blockIdx.x] = b;
+        __threadfence();
+        nf_st_release(a.flags + blockIdx.x, a.token);
+    }
+    // ---- rendezvous: thread t waits for CTA t's flag (bounded), then the maxima are combined
+    float g = 0.f;
+    if ((int)threadIdx.x < G) {
+        bool ok = false;
+        for (int spin = 0; spin < (1 << 22); ++spin) {
+            if (nf_ld_acquire(a.flags + threadIdx.x) == a.token) { ok = true; break; }
+            __nanosleep(100);
+        }
+        if (ok) g = __ldcg(a.slots + threadIdx.x);
+        else s_fail = 1;
+    }
+    g = warp_max(g);
+    __syncthreads();
+    if (lane == 0) sh[warp] = g;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float b = sh[0];
+        for (int i = 1; i < kNfQThreads / 32; ++i) b = fmaxf(b, sh[i]);
+        s_amax = b;
+        if (s_fail && a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
+    }
+    __syncthreads();
+    if (s_fail) return;
+    // ---- pass 2: block scales and codes (the second read of x hits L2)
+    const float amax = fmaxf(s_amax, 1e-12f);
+    const float pts = __fdiv_rn(amax, 2688.f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.pts = pts;
+    const float inv_pts = __fdiv_rn(1.f, pts), k448 = __fdiv_rn(448.f, amax);
+    const int64_t k64 = a.K >> 6;
+    for (int r = blockIdx.x; r < a.M; r += G) {
+        for (int i0 = 0; i0 < kv; i0 += kNfQThreads) {           // whole warps: kv is even, a block is lanes 2j, 2j+1
+            const int i = i0 + threadIdx.x;
+            const bool on = i < kv;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (on) v = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(a.x) + ((int64_t)r * a.ldx + (int64_t)i * 8) * 2);
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+            float f[8], bm = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 p = cvt2<DT>(wv[q]);
+                f[2 * q] = p.x;
+                f[2 * q + 1] = p.y;
+                bm = fmaxf(bm, fmaxf(fabsf(p.x), fabsf(p.y)));
+            }
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+            const float sb = fminf(fmaxf(bm * k448, 0.015625f), 448.f);
+            const uint32_t sc = e4m3x2(sb, 0.f) & 0xffu;
+            const float bs = e4m3_to_float(sc);
+            uint32_t out = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) out |= e2m1x2(__fdiv_rn(f[2 * q] * inv_pts, bs), __fdiv_rn(f[2 * q + 1] * inv_pts, bs)) << (8 * q);
+            if (on) {
+                *reinterpret_cast<uint32_t*>(a.codes + (int64_t)r * a.ldc + (int64_t)i * 4) = out;
+                if ((i & 1) == 0) {
+                    const int b = i >> 1;
+                    if (a.bs_rows) a.bs_rows[(int64_t)r * a.lds + b] = (uint8_t)sc;
+                    if (a.bs_blocked)
+                        a.bs_blocked[((int64_t)(r >> 7) * k64 + (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)] = (uint8_t)sc;
+                }
+            }
+        }
+    }
+}
+
 }  // namespace rwkvq
 
 using namespace rwkvq;
@@ -571,6 +698,38 @@ int32_t rwkvq_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, cons
     cudaStream_t st = (cudaStream_t)stream;
     if (x_dtype == RWKVQ_F16) return M <= 8 ? dispatch_nf_fused<RWKVQ_F16, 1>(a, st) : dispatch_nf_fused<RWKVQ_F16, 2>(a, st);
     return M <= 8 ? dispatch_nf_fused<RWKVQ_BF16, 1>(a, st) : dispatch_nf_fused<RWKVQ_BF16, 2>(a, st);
+}
+
+int64_t rwkvq_actq_nvfp4_fused_scratch_bytes(void) { return 2 * 512 * 4; }
+
+int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                               uint8_t* block_scales, int64_t lds, uint8_t* block_scales_blocked, float* pts, void* scratch,
+                               int64_t scratch_bytes, int32_t* status, void* stream) {
+    const char* who = "actq_nvfp4_fused";
+    RWKVQ_REQUIRE(x && codes && pts && scratch && (block_scales || block_scales_blocked), RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(M > 0 && K > 0 && K % 16 == 0 && M < (1 << 30), RWKVQ_E_SHAPE, "%s: M=%lld K=%lld (K must be a multiple of 16)", who, (long long)M, (long long)K);
+    RWKVQ_REQUIRE(block_scales_blocked == nullptr || K % 64 == 0, RWKVQ_E_SHAPE, "%s: blocked scales need K %% 64 == 0", who);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(((uintptr_t)codes & 3) == 0 && ldc % 4 == 0 && ldc >= K / 2 && (block_scales == nullptr || lds >= K / 16), RWKVQ_E_ALIGN,
+                  "%s: code rows must be 4-byte aligned", who);
+    RWKVQ_REQUIRE(scratch_bytes >= rwkvq_actq_nvfp4_fused_scratch_bytes() && ((uintptr_t)scratch & 3) == 0, RWKVQ_E_WORKSPACE,
+                  "%s: scratch of %lld bytes needed", who, (long long)rwkvq_actq_nvfp4_fused_scratch_bytes());
+    static std::atomic<uint32_t> next_token{0x51ed270bu};
+    NfQArgs a{};
+    a.x = x; a.codes = codes; a.bs_rows = block_scales; a.bs_blocked = block_scales_blocked; a.pts = pts;
+    a.slots = reinterpret_cast<float*>(scratch); a.flags = reinterpret_cast<uint32_t*>(scratch) + 512; a.status = status;
+    a.ldx = ldx; a.ldc = ldc; a.lds = lds; a.M = (int)M; a.K = (int)K;
+    a.token = next_token.fetch_add(0x61c88647u) | 1u;
+    const int grid = (int)std::min<int64_t>(M, std::min<int64_t>(512, 2 * (int64_t)sm_count()));
+    void* args[] = {(void*)&a};
+    const void* fn = x_dtype == RWKVQ_F16 ? (const void*)actq_nvfp4_fused_kernel<RWKVQ_F16> : (const void*)actq_nvfp4_fused_kernel<RWKVQ_BF16>;
+    const cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kNfQThreads), args, 0, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return check_launch(who);
 }
 
 }  // extern "C"

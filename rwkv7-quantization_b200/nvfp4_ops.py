@@ -72,18 +72,31 @@ def load_nvfp4_weight(z, key, dev):
             "tensor_scale": z.pop(key + ".nvfp4_t_scale").to(dev).float(), "qtype": "nvfp4"}
 
 
-def quantize_activations_nvfp4(x: torch.Tensor):
-    """On-the-fly activation quantization on the device: (packed codes [M,K/2], block scales [M,K/16] e4m3, pts [1])."""
+def quantize_activations_nvfp4(x: torch.Tensor, blocked: bool = False):
+    """On-the-fly activation quantization on the device, one cooperative launch:
+    (packed codes [M,K/2], block scales [M,K/16] e4m3, pts [1]); with blocked=True the scales come in the blocked
+    order of the tensor-core GEMM (a flat uint8 buffer) instead of row-major."""
     from fused_fp8_gemm import _rows16
     x2 = _rows16(x).contiguous()
     m, k = x2.shape
     dev = x2.device
     codes = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
-    bs = torch.empty((m, k // BLOCK), dtype=torch.float8_e4m3fn, device=dev)
     pts = torch.empty(1, dtype=torch.float32, device=dev)
-    amax = torch.empty(1, dtype=torch.float32, device=dev)
-    abi.call("rwkvq_actq_nvfp4", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k // 2, bs.data_ptr(),
-             k // BLOCK, pts.data_ptr(), amax.data_ptr(), abi.stream_ptr())
+    if os.environ.get("RWKVQ_NVFP4_ACTQ", "fused") != "fused" or m == 0 or (blocked and k % 64):
+        bs = torch.empty((m, k // BLOCK), dtype=torch.float8_e4m3fn, device=dev)
+        amax = torch.empty(1, dtype=torch.float32, device=dev)
+        abi.call("rwkvq_actq_nvfp4", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k // 2, bs.data_ptr(),
+                 k // BLOCK, pts.data_ptr(), amax.data_ptr(), abi.stream_ptr())
+        return codes, (pack_scales(bs, k) if blocked else bs), pts
+    scratch = torch.empty(1024, dtype=torch.int32, device=dev)
+    if blocked:
+        bs = torch.empty(int(abi.lib().rwkvq_nvfp4_blocked_scale_bytes(m, k)), dtype=torch.uint8, device=dev)
+        rows_ptr, blk_ptr = None, bs.data_ptr()
+    else:
+        bs = torch.empty((m, k // BLOCK), dtype=torch.float8_e4m3fn, device=dev)
+        rows_ptr, blk_ptr = bs.data_ptr(), None
+    abi.call("rwkvq_actq_nvfp4_fused", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k // 2, rows_ptr, k // BLOCK,
+             blk_ptr, pts.data_ptr(), scratch.data_ptr(), scratch.numel() * 4, None, abi.stream_ptr())
     return codes, bs, pts
 
 
@@ -135,11 +148,11 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
                  wbs.stride(0), wts.data_ptr(), out.data_ptr(), n, m, n, k, abi.stream_ptr())
         out = out.reshape(*x.shape[:-1], n)
         return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
-    codes, bs, pts = quantize_activations_nvfp4(x)
+    codes, bs, pts = quantize_activations_nvfp4(x, blocked=(route == "tc"))
     out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
     if route == "tc":
         ws = abi.workspace(1, 1, 1, 1, codes.device)
-        a_blk, w_blk = pack_scales(bs, k), _blocked_weight_scales(weight_info, k)     # both alive until the launch
+        a_blk, w_blk = bs, _blocked_weight_scales(weight_info, k)     # both alive until the launch
         abi.call("rwkvq_tc_gemm_nvfp4", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),
                  w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), n, m, n, k, ws.data_ptr(), ws.numel(), abi.stream_ptr())
     else:

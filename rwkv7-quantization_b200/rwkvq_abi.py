@@ -70,6 +70,8 @@ SIGNATURES = {
     "rwkvq_actq_nvfp4": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _p, _p],
     "rwkvq_gemv_nvfp4_smem_bytes": [_i64, _i64],
     "rwkvq_gemv_nvfp4": [_p, _i64, _p, _i64, _p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _p],
+    "rwkvq_actq_nvfp4_fused_scratch_bytes": [],
+    "rwkvq_actq_nvfp4_fused": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _p, _p, _i64, _p, _p],
     "rwkvq_gemv_nvfp4_fused_smem_bytes": [_i64, _i64],
     "rwkvq_gemv_nvfp4_fused": [_p, _i32, _i64, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _p],
     "rwkvq_nvfp4_blocked_scale_bytes": [_i64, _i64],
@@ -79,7 +81,7 @@ SIGNATURES = {
     "rwkvq_actq_fp8_fused_scratch_bytes": [],
     "rwkvq_actq_fp8_fused": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _i64, _p, _i32, _u32, _p],
 }
-_RESTYPES = {"rwkvq_gemv_nvfp4_fused_smem_bytes": ctypes.c_int64, "rwkvq_nvfp4_blocked_scale_bytes": ctypes.c_int64, "rwkvq_actq_fp8_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_smem_bytes": ctypes.c_int64, "rwkvq_gemv_int4_group_smem_bytes": ctypes.c_int64, "rwkvq_workspace_bytes": ctypes.c_int64, "rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64}
+_RESTYPES = {"rwkvq_actq_nvfp4_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_fused_smem_bytes": ctypes.c_int64, "rwkvq_nvfp4_blocked_scale_bytes": ctypes.c_int64, "rwkvq_actq_fp8_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_smem_bytes": ctypes.c_int64, "rwkvq_gemv_int4_group_smem_bytes": ctypes.c_int64, "rwkvq_workspace_bytes": ctypes.c_int64, "rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64}
 
 _lib = None
 _device_checked = False

@@ -150,3 +150,23 @@ def test_fused_decode_route(nf, monkeypatch, dt, m, n, k):
     oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
              "tensor_scale": info["tensor_scale"].cpu()}
     assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
+
+
+@pytest.mark.parametrize("m,k", [(1, 512), (130, 1024), (300, 4096)])
+def test_fused_activation_quantizer_routes_agree(nf, monkeypatch, m, k):
+    """One-launch quantizer against the three-kernel route (codes, scales, tensor scale bit for bit), and its blocked
+    scales against pack_scales of the row-major ones on every valid row."""
+    import numpy as np
+    x = gen(m * 5 + k, (m, k), 1.0, torch.bfloat16).cuda()
+    monkeypatch.setenv("RWKVQ_NVFP4_ACTQ", "split")
+    c0, s0, p0 = nf.quantize_activations_nvfp4(x)
+    monkeypatch.setenv("RWKVQ_NVFP4_ACTQ", "fused")
+    c1, s1, p1 = nf.quantize_activations_nvfp4(x)
+    assert torch.equal(c0, c1) and torch.equal(s0.view(torch.uint8), s1.view(torch.uint8)) and torch.equal(p0, p1)
+    c2, blk, p2 = nf.quantize_activations_nvfp4(x, blocked=True)
+    assert torch.equal(c0, c2) and torch.equal(p0, p2)
+    got = blk.cpu().numpy().reshape(-1, k // 64, 512)
+    src = s0.view(torch.uint8).cpu().numpy()
+    r = np.arange(m)[:, None]
+    b = np.arange(k // 16)[None, :]
+    assert (got[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4] == src).all()
