@@ -15,8 +15,10 @@
  *   - `x_dtype` is RWKVQ_F16 or RWKVQ_BF16;
  *   - `div_mode` selects how the fp32 scale divisions (448/amax, amax/448, 127/amax, amax/127,
  *     x/awq) are evaluated: RWKVQ_DIV_FULL = PTX div.full.f32, which is what the reference's
- *     Triton kernels execute on a GPU; RWKVQ_DIV_IEEE = round-to-nearest, which is what
- *     torch (and the Triton CPU interpreter) compute.
+ *     Triton kernels execute on a GPU; RWKVQ_DIV_IEEE = round-to-nearest, which is what the Triton CPU
+ *     interpreter computes; RWKVQ_DIV_TORCH (rwkvq_actq_fp8 / rwkvq_actq_fp8_fused only) = the two-step forms torch
+ *     evaluates on a GPU for `448.0 / amax` and `amax / 448.0` in prep_x_fp8 (fused_fp8_gemm.py:377, 389):
+ *     rn(rn(1/amax) * 448) and rn(amax * rn(1/448)); checked bit for bit against the reference run on a B200.
  *
  * Each declaration names the reference function it replaces (file:line in the reference tree).
  */
@@ -44,11 +46,13 @@ extern "C" {
 
 #define RWKVQ_DIV_IEEE 0
 #define RWKVQ_DIV_FULL 1
+#define RWKVQ_DIV_TORCH 2 /* activation-quantization entry points only: see below */
 
 /* flags of the W8A8 entry points */
 #define RWKVQ_FLAG_AMAX_AFTER_BF16 1u /* amax over bf16-rounded x (reference M==1 kernel, fused_fp8_gemm.py:662) */
 #define RWKVQ_FLAG_INT8_SHARED_WSCALE 2u /* k and v use r's weight scale (reference defect, fused_fp8_gemm.py:855-857) */
 #define RWKVQ_FLAG_OUT_VIA_BF16 4u    /* round the result to bf16 before fp16 (fp8_ops.py:77-86)        */
+#define RWKVQ_FLAG_WSCALE_PER_ROW 16u  /* w_scale holds N values, one per output row (schemes.py:26-34 "fp8_perchannel"; no reference kernel reads them) */
 #define RWKVQ_FLAG_QUANT_FROM_BF16 8u /* quantize bf16(x) instead of x (the GEMM kernels read prep_x's bf16 copy, fused_fp8_gemm.py:248-250) */
 
 int32_t rwkvq_version(void);
@@ -74,8 +78,9 @@ int32_t rwkvq_prep3_x(const void* xr, const void* xk, const void* xv, int32_t x_
                       int64_t ldx, const float* awq_r, const float* awq_k, void* out_r, void* out_k, void* out_v,
                       int64_t ldo, float* amax3, int32_t div_mode, void* stream);
 
-/* prep_x_fp8 (fused_fp8_gemm.py:341-390): per-call amax, inv = 448 / max(amax, 1e-12) (IEEE, as torch),
- * codes = e4m3_rn(clamp(x * inv, +-448)), scale[0] = amax / 448.  amax_scratch: one fp32 owned by the caller. */
+/* prep_x_fp8 (fused_fp8_gemm.py:341-390): per-call amax, inv = 448 / max(amax, 1e-12) and scale[0] = amax / 448 as
+ * torch evaluates them on a GPU (RWKVQ_DIV_TORCH), codes = e4m3_rn(clamp(x * inv, +-448)).  amax_scratch: one fp32
+ * owned by the caller. */
 int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes,
                          int64_t ldc, float* scale, float* amax_scratch, void* stream);
 
@@ -87,13 +92,22 @@ int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, i
 int32_t rwkvq_actq_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
                        float* amax, float* scale, int32_t div_mode, uint32_t flags, void* stream);
 
-/* rwkvq_actq_fp8 in ONE cooperative launch (no memset, no second kernel): same arguments and results; `scratch`
- * (rwkvq_actq_fp8_fused_scratch_bytes() bytes, 4-byte aligned, any contents) carries the per-CTA maxima and the
- * rendezvous flags; `status` (optional) receives RWKVQ_E_TIMEOUT if the bounded grid rendezvous gives up. */
+/* rwkvq_actq_fp8 in ONE cooperative launch (no memset, no second kernel): same arguments and results.  `scratch`
+ * (rwkvq_actq_fp8_fused_scratch_bytes() bytes, 4-byte aligned, ZEROED ONCE before its first use) carries the per-CTA
+ * maxima, the rendezvous flags and an epoch word that every launch advances on the device: calls that are ordered on
+ * a stream may share one scratch, and a call captured in a CUDA graph may be replayed any number of times (nothing
+ * about the rendezvous is fixed on the host).  Calls that can overlap on the GPU need separate scratch buffers.
+ * `status` (optional) receives RWKVQ_E_TIMEOUT if the bounded grid rendezvous gives up; zero the scratch again after
+ * that.  rwkvq_actq_fp8_fused3 does the same for xr, xk, xv in one launch (the activation half of linear_rkv_fused,
+ * fused_fp8_gemm.py:86-150 + 264-334): three code matrices, amax3[0..2]. */
 int64_t rwkvq_actq_fp8_fused_scratch_bytes(void);
 int32_t rwkvq_actq_fp8_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes,
                              int64_t ldc, float* amax, float* scale, void* scratch, int64_t scratch_bytes,
                              int32_t* status, int32_t div_mode, uint32_t flags, void* stream);
+int32_t rwkvq_actq_fp8_fused3(const void* xr, const void* xk, const void* xv, int32_t x_dtype, int64_t M, int64_t K,
+                              int64_t ldx, uint8_t* codes_r, uint8_t* codes_k, uint8_t* codes_v, int64_t ldc,
+                              float* amax3, void* scratch, int64_t scratch_bytes, int32_t* status, int32_t div_mode,
+                              uint32_t flags, void* stream);
 
 /* prep_x_int8 / _prep_x_int8_kernel (fused_fp8_gemm.py:687-731): per-ROW amax (floor 1e-12), s = 127/amax,
  * codes = trunc(clamp(x*s, -128, 127)), scales[m] = amax/127. */
@@ -132,7 +146,9 @@ int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int3
 
 /* ---------------------------------------------------------------- W8A8 GEMM on pre-quantized codes (any M) */
 
-/* The GEMM half of linear_fp8_fused / linear_fp8 (fused_fp8_gemm.py:219-257, fp8_ops.py:77-80):
+/* These two run on the register-streaming mma.sync kernel (any M, no workspace); the tensor-memory entries further
+ * down compute the same results on tcgen05 and are what the Python wrappers route to.
+ * The GEMM half of linear_fp8_fused / linear_fp8 (fused_fp8_gemm.py:219-257, fp8_ops.py:77-80):
  * out = fp16( (a_codes . W^T) * (a_scale * w_scale[0]) ), where a_scale = amax[0]/448 if amax_is_amax != 0
  * (div_mode applies) or a_scale = amax[0] taken as the scale itself otherwise. */
 int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
@@ -143,15 +159,6 @@ int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, i
 int32_t rwkvq_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
                         const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M,
                         int64_t N, int64_t K, uint32_t flags, void* stream);
-
-/* The same two GEMMs forced onto the register-streaming mma.sync kernel (any M; the dispatchers above use it
- * below the tensor-memory kernel's range).  Same reference lines. */
-int32_t rwkvq_gemm_fp8_mma(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
-                           const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M,
-                           int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
-int32_t rwkvq_gemm_int8_mma(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
-                            const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc,
-                            int64_t M, int64_t N, int64_t K, uint32_t flags, void* stream);
 
 /* ---------------------------------------------------------------- tensor-memory kernels (tcgen05 + TMA)
  *
@@ -188,12 +195,27 @@ int32_t rwkvq_tc_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, i
                                int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags, void* workspace,
                                int64_t workspace_bytes, void* stream);
 /* GEMM on pre-quantized codes, any M (fused_fp8_hwdot_gemm_kernel fused_fp8_gemm.py:219-257, torch._scaled_mm
- * fp8_ops.py:77-80): M <= 128 streams the weights once (needs the workspace); larger M runs the 128 x 256 tile
- * prefill kernel (workspace optional, used for the status word only). */
+ * fp8_ops.py:77-80): at most 16 tokens (or at most 48 against K >= 8192 and few weight rows) stream the weights once
+ * with a stream-K split (needs the workspace); everything else runs the tiled GEMM with tokens as the 128-row operand
+ * (workspace optional, used for the status word only). */
 int32_t rwkvq_tc_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
                           const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M,
                           int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* workspace,
                           int64_t workspace_bytes, void* stream);
+/* The GEMM half of linear_rkv_fused / fused_rkv_fp8_kernel (fused_fp8_gemm.py:264-334) on codes: r, k, v in ONE launch
+ * (three code matrices [M, lda], amax3[0..2], three weights of one shape).  Same results as three rwkvq_tc_gemm_fp8. */
+int32_t rwkvq_tc_gemm_fp8_rkv(const uint8_t* codes_r, const uint8_t* codes_k, const uint8_t* codes_v, int64_t lda,
+                              const float* amax3, int32_t amax_is_amax, const uint8_t* wr, const uint8_t* wk,
+                              const uint8_t* wv, int64_t ldw, const float* sr, const float* sk, const float* sv,
+                              void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                              int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream);
+/* The GEMM half of linear_rkv_int8_fused / fused_rkv_int8_kernel (fused_fp8_gemm.py:825-886) on codes, one launch;
+ * RWKVQ_FLAG_INT8_SHARED_WSCALE mirrors the reference (k and v scaled by r's weight scale). */
+int32_t rwkvq_tc_gemm_int8_rkv(const int8_t* codes_r, const int8_t* codes_k, const int8_t* codes_v, int64_t lda,
+                               const float* scales_r, const float* scales_k, const float* scales_v, const int8_t* wr,
+                               const int8_t* wk, const int8_t* wv, int64_t ldw, const float* sr, const float* sk,
+                               const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N,
+                               int64_t K, uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream);
 /* fused_int8_gemm_kernel (fused_fp8_gemm.py:734-782) on codes, any M. */
 int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
                            const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc,
@@ -258,7 +280,8 @@ int32_t rwkvq_gemv_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_b
                          int64_t ldws, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                          void* stream);
 
-/* The same quantization in ONE cooperative launch (amax, grid-wide rendezvous with a bounded wait, codes and scales).
+/* The same quantization in ONE cooperative launch (amax, grid-wide rendezvous with a bounded wait, codes and scales;
+ * scratch rules as for rwkvq_actq_fp8_fused: zeroed once, epoch advanced on the device, safe under graph replay).
  * block_scales (row-major) and block_scales_blocked (the order rwkvq_tc_gemm_nvfp4 takes, K a multiple of 64, buffer
  * of rwkvq_nvfp4_blocked_scale_bytes(M, K); rows past M are left unwritten) may each be NULL, not both.  scratch:
  * rwkvq_actq_nvfp4_fused_scratch_bytes() bytes owned by the caller, not shared by overlapping calls; status (may be
@@ -293,15 +316,39 @@ int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* 
                             void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
                             int64_t workspace_bytes, void* stream);
 
-/* No counterpart in the reference.  rwkvq_tc_gemm_fp8 (M <= 128) for callers that cannot supply device scratch --
- * a host runtime that owns every byte of device memory and forbids allocation inside its serving loop, or code
- * running where cudaMalloc is not allowed.  The scratch is an 8 MiB array built into the library on each GPU; no
- * allocation happens in this call or below it.  The first call on a device resolves the array's address and should be
- * made outside stream capture; shapes needing more than 8 MiB are refused (RWKVQ_E_WORKSPACE); the array is shared by
- * all calls on a device, is re-cleared on `stream` by every call, and calls that overlap on the GPU race on it. */
+/* No counterpart in the reference.  rwkvq_tc_gemm_fp8 for callers that cannot supply device scratch -- a host runtime
+ * that owns every byte of device memory and forbids allocation inside its serving loop, or code running where
+ * cudaMalloc is not allowed.  The scratch is an 8 MiB array built into the library on each GPU; no allocation happens
+ * in this call or below it.  The first call on a device resolves the array's address and should be made outside
+ * stream capture.  Only the weight-streaming form (at most 16 tokens, or at most 48 against K >= 8192) keeps partial
+ * sums there; such a call is refused (RWKVQ_E_WORKSPACE) when it needs more than 8 MiB; every other shape is accepted.
+ * The array is shared by all calls on a device, its header is re-cleared on `stream` by every call, and calls that
+ * overlap on the GPU race on it.  rwkvq_tc_static_status copies its status word to the host (synchronizes). */
 int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
                                  const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo,
                                  int64_t M, int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
+int32_t rwkvq_tc_static_status(int32_t* host_status);
+
+/* ---------------------------------------------------------------- bounded waits, status, diagnostics
+ *
+ * No counterpart in the reference (its kernels have no device-side waits).  Every device-side wait of this library
+ * (mbarriers of the tensor-memory kernels, staging copies of the decode GEMVs, the grid rendezvous of the one-launch
+ * quantizers) gives up after a wall-time limit: 1.5 s by default, RWKVQ_WAIT_LIMIT_US in the environment (read once)
+ * or rwkvq_set_wait_limit_us (0 restores the default) change it for launches made afterwards.  A kernel that gives up
+ * records RWKVQ_E_TIMEOUT -- in the caller's status pointer / workspace where the entry point takes one, else in a
+ * status word the library keeps on each device -- stops issuing work, waits (bounded) for its own copies in flight,
+ * frees its tensor memory and returns; its results are then undefined.
+ *   rwkvq_device_status   copies the per-device word to the host (synchronizes), optionally clearing it.
+ *   rwkvq_selftest_timeout launches one CTA that waits, with limit_us, for an mbarrier phase nobody completes
+ *                         (mode 0) or for a flag nobody writes (mode 1; scratch4 = 4 bytes of device memory) and must
+ *                         leave RWKVQ_E_TIMEOUT in *status (device pointer) -- the give-up path without any fault. */
+void rwkvq_set_wait_limit_us(int64_t microseconds);
+int32_t rwkvq_device_status(int32_t* host_status, int32_t clear);
+int32_t rwkvq_selftest_timeout(int32_t* status, void* scratch4, int64_t limit_us, int32_t mode, void* stream);
+/* Profiling aids: a device buffer ([grid][8] uint64 for the decode GEMV, [grid][16] for the tensor-memory kernels) that
+ * every later launch stamps with %globaltimer values at its CTAs' milestones; NULL (the default) switches them off. */
+void rwkvq_gemv_set_trace(void* device_buffer);
+void rwkvq_tc_set_trace(void* device_buffer);
 
 #ifdef __cplusplus
 }

@@ -373,14 +373,17 @@ def prep3_x(xr, xk, xv, awq_r=None, awq_k=None, div=ieee_div):
 
 
 def prep_x_fp8(x: torch.Tensor):
-    """fused_fp8_gemm.py:341-390 -- per-call amax, inv = 448/clamp(amax,1e-12) and
-    x_scale = amax/448 evaluated by torch (IEEE), codes = RNE(clamp(x*inv, +-448))."""
+    """fused_fp8_gemm.py:341-390 -- per-call amax; inv = 448/clamp(amax,1e-12) and x_scale = amax/448 as torch
+    evaluates them ON A GPU, which is where the reference runs: `scalar / tensor` is reciprocal-then-multiply
+    (Tensor.__rtruediv__), `tensor / python scalar` multiplies by the fp32-rounded reciprocal of the scalar (the CUDA
+    true-division kernel's scalar fast path).  Both checked bit for bit against the reference's outputs recorded on a
+    B200 (tests/golden/fp8_triton_b200.npz).  codes = RNE(clamp(x*inv, +-448))."""
     x2 = _as_2d_16bit(x)
     xf = x2.float()
     amax = torch.maximum(xf.abs().max().reshape(1), torch.zeros(1)).float()
-    inv = F8_MAX / amax.clamp(min=1e-12)
+    inv = amax.clamp(min=1e-12).reciprocal() * torch.tensor(F8_MAX, dtype=torch.float32)
     codes = _to_e4m3((xf * inv).clamp(-F8_MAX, F8_MAX))
-    return codes, amax / F8_MAX
+    return codes, amax * (torch.tensor(1.0, dtype=torch.float32) / torch.tensor(F8_MAX, dtype=torch.float32))
 
 
 def prep_x_int8(x: torch.Tensor, div=ieee_div):
@@ -407,9 +410,11 @@ def _fp8_codes_from_bf16(x_bf16: torch.Tensor, amax: torch.Tensor, div):
 
 def _fp8_scaled_out(a_codes, w_codes, amax_v, w_ts, div):
     """acc = sum_k a*w in fp32 (here: float64 then rounded, the order-independent limit);
-    out = fp16(acc * (amax/448 * w_ts))  (fused_fp8_gemm.py:253-257)."""
+    out = fp16(acc * (amax/448 * w_ts))  (fused_fp8_gemm.py:253-257).  A weight scale of N values (the
+    "fp8_perchannel" scheme, schemes.py:26-34; no reference kernel consumes it) scales output column n by w_ts[n]."""
     acc = (a_codes.float().double() @ w_codes.float().double().t()).float()
-    s = div(amax_v, torch.full_like(amax_v, F8_MAX)) * w_ts.float().reshape(-1)[0]
+    wv = w_ts.float().reshape(-1)
+    s = div(amax_v, torch.full_like(amax_v, F8_MAX)) * (wv[0] if wv.numel() == 1 else wv.reshape(1, -1))
     return (acc * s).to(torch.float16)
 
 
@@ -458,7 +463,8 @@ def linear_fp8(x, weight_info, out_dtype=torch.float16):
         x2 = x2.to(torch.bfloat16)
     codes, xs = prep_x_fp8(x2)
     acc = (codes.float().double() @ w.float().double().t()).float()
-    out = (acc * (xs.float() * w_ts.float().reshape(-1)[0])).to(torch.bfloat16)
+    wv = w_ts.float().reshape(-1)
+    out = (acc * (xs.float() * (wv[0] if wv.numel() == 1 else wv.reshape(1, -1)))).to(torch.bfloat16)
     return out.reshape(*x.shape[:-1], w.shape[0]).to(out_dtype)
 
 

@@ -2,6 +2,10 @@
 // (large-M FP8 path) and per-row int8 codes (INT8 path).  All HBM/L2-bound elementwise work:
 // 128-bit loads and stores, one row segment per CTA, block reduction + one atomic per CTA.
 #include <algorithm>
+#include <cstdlib>
+#include <mutex>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 
@@ -34,6 +38,80 @@ int sm_count() {
         cached_dev = dev;
     }
     return cached > 0 ? cached : 148;
+}
+
+extern "C" void rwkvq_set_wait_limit_us(int64_t);
+static std::atomic<long long>& wait_limit_override();
+
+unsigned long long wait_limit_ns() {
+    static const long long from_env = [] {
+        const char* e = std::getenv("RWKVQ_WAIT_LIMIT_US");
+        const long long v = e ? std::atoll(e) : 0;
+        return v > 0 ? v : 1500000ll;
+    }();
+    const long long o = wait_limit_override().load(std::memory_order_relaxed);
+    return (unsigned long long)(o > 0 ? o : from_env) * 1000ull;
+}
+
+// per kernel and device: opt in to `bytes` of dynamic shared memory once
+int32_t ensure_smem_optin(const void* kern, int bytes, const char* who) {
+    static std::mutex mu;
+    static std::vector<std::pair<const void*, int>> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    for (const auto& d : done)
+        if (d.first == kern && d.second == dev) return RWKVQ_OK;
+    const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    RWKVQ_REQUIRE(e == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(e));
+    done.emplace_back(kern, dev);
+    return RWKVQ_OK;
+}
+
+int32_t kernel_plan(const void* kern, int threads, size_t smem, int optin_bytes, int* per_sm, const char* who) {
+    struct Entry { const void* kern; int dev; size_t smem; int per_sm; };
+    static std::mutex mu;
+    static std::vector<Entry> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const auto& d : done)
+            if (d.kern == kern && d.dev == dev && d.smem == smem) { *per_sm = d.per_sm; return RWKVQ_OK; }
+    }
+    const int32_t rc = ensure_smem_optin(kern, optin_bytes, who);
+    if (rc != RWKVQ_OK) return rc;
+    int n = 0;
+    const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
+    RWKVQ_REQUIRE(e == cudaSuccess && n >= 1, RWKVQ_E_LAUNCH, "%s: occupancy query failed (%s)", who, cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(mu);
+    done.push_back({kern, dev, smem, n});
+    *per_sm = n;
+    return RWKVQ_OK;
+}
+
+bool use_pdl() {
+    static const bool on = [] {
+        const char* e = std::getenv("RWKVQ_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+static __device__ int g_device_status;
+
+int* device_status_ptr() {
+    static std::mutex mu;
+    static int* ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+        ptrs[dev] = reinterpret_cast<int*>(p);
+    }
+    return ptrs[dev];
 }
 
 constexpr int kThreads = 256;
@@ -117,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) prep_x_kernel(Prep3Args a, int64_t K
 static int32_t launch_prep(const Prep3Args& a, int nt, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int64_t ldo,
                            int32_t div_mode, cudaStream_t st, int after_bf16 = 0) {
     RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "prep_x: x_dtype %d", x_dtype);
-    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "prep_x: div_mode %d", div_mode);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL || div_mode == RWKVQ_DIV_TORCH, RWKVQ_E_BADARG, "prep_x: div_mode %d", div_mode);
     RWKVQ_REQUIRE(M >= 0 && K >= 0 && ldx >= K, RWKVQ_E_SHAPE, "prep_x: M=%lld K=%lld ldx=%lld", (long long)M, (long long)K, (long long)ldx);
     RWKVQ_REQUIRE(a.amax != nullptr, RWKVQ_E_BADARG, "prep_x: amax is null");
     if (cudaMemsetAsync(a.amax, 0, sizeof(float) * nt, st) != cudaSuccess) return check_launch("prep_x memset");
@@ -146,8 +224,8 @@ __global__ void __launch_bounds__(kThreads) quant_fp8_kernel(const void* x, uint
     const int64_t row = blockIdx.x;
     const int64_t k0 = (int64_t)blockIdx.y * kSegElems;
     const float amax = *amax_p;
-    const float inv = div_mode_f32(448.f, fmaxf(amax, 1e-12f), div_mode);
-    if (scale && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale = div_mode_f32(amax, 448.f, div_mode);
+    const float inv = scale_inv(448.f, fmaxf(amax, 1e-12f), div_mode);
+    if (scale && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *scale = scale_fwd(amax, 448.f, div_mode);
     const char* xrow = reinterpret_cast<const char*>(x) + row * ldx * 2;
     uint8_t* crow = codes + row * ldc;
     if (VEC) {
@@ -224,31 +302,52 @@ __global__ void __launch_bounds__(kThreads) quant_int8_kernel(const void* x, int
 }
 
 // ----------------------------------------------------------------------------------------
-// FP8 activation quantization in ONE launch: per-CTA partial maxima, a grid-wide rendezvous through a token that is
-// unique per launch (nothing has to be zeroed beforehand), then the code pass (second read of x hits L2).
-// The grid is launched cooperatively (all CTAs resident); the rendezvous spin is bounded all the same.
+// FP8 activation quantization in ONE launch, for one tensor or for xr, xk, xv together: per-CTA partial maxima, a
+// grid-wide rendezvous, then the code pass (rows kept in registers, or a second read that hits L2).  The grid is
+// launched cooperatively (all CTAs resident); the rendezvous wait is bounded all the same.
+//
+// Rendezvous.  The scratch holds one slot and one flag per CTA and an EPOCH word.  Every CTA reads the epoch E when it
+// starts, publishes its maximum and then the value E+1 in its flag; a CTA passes once all flags of its tensor read
+// E+1; CTA 0 stores E+1 as the new epoch on its way out.  All epoch reads happen before any CTA can pass, and the bump
+// after, so the next launch on the scratch -- a later call, or the next replay of a captured graph -- starts from
+// E+1 and cannot be satisfied by the flags this launch left behind.  Nothing is drawn on the host.
 constexpr int kFusedThreads = 512;
+constexpr int kFusedMaxCtas = 512;
+constexpr int kFusedEpochWord = 2 * kFusedMaxCtas;          // slots[512] | flags[512] | epoch
 
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
+struct ActqArgs {
+    const void* x[3];
+    uint8_t* codes[3];
+    float* amax_out;          // [nt]
+    float* scale_out[3];      // optional, one float each
+    float* slots;
+    uint32_t* flags;          // flags[kFusedMaxCtas] is the epoch word
+    int* status;
+    unsigned long long wait_ns;
+    int64_t ldx, ldc;
+    int M, K, nt, cpt;        // tensors, CTAs per tensor (grid = nt * cpt)
+    int div_mode, after_bf16, from_bf16;
+};
 
 // KEEP: a CTA has at most 8 rows of at most kFusedThreads vectors: every thread holds its vectors in registers across
 // the rendezvous, so the activations are read once and all of a thread's loads are in flight together.
 template <int DT, bool KEEP>
-__global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const void* x, uint8_t* codes, float* amax_out, float* scale_out,
-                                                                      float* slots, uint32_t* flags, uint32_t token, int* status,
-                                                                      int M, int K, int64_t ldx, int64_t ldc, int div_mode,
-                                                                      int after_bf16, int from_bf16) {
+__global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const ActqArgs a) {
     __shared__ float sh[kFusedThreads / 32];
     __shared__ float s_amax;
     __shared__ int s_fail;
-    const int kv = K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ uint32_t s_token;
+    const int kv = a.K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = (int)blockIdx.x / a.cpt, cb = (int)blockIdx.x - t * a.cpt, G = a.cpt;
+    const char* x = reinterpret_cast<const char*>(a.x[t]);
+    uint8_t* codes = a.codes[t];
+    const int M = a.M;
+    const int64_t ldx = a.ldx, ldc = a.ldc;
+    const bool after_bf16 = a.after_bf16 != 0, from_bf16 = a.from_bf16 != 0;
+    if (threadIdx.x == 0) {
+        s_token = ld_acquire_u32(a.flags + kFusedMaxCtas) + 1u;
+        s_fail = 0;
+    }
     // ---- pass 1: partial maximum of this CTA's rows; four rows per step, so four loads per thread are in flight
     float m = 0.f;
     auto vec_max = [&](const uint4& v) {
@@ -261,34 +360,33 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
             }
         } else if (DT == RWKVQ_F16) {
             const __half2* h = reinterpret_cast<const __half2*>(&v);
-            const __half2 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-            m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+            const __half2 t2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+            m = fmaxf(m, fmaxf(__low2float(t2), __high2float(t2)));
         } else {
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-            const __nv_bfloat162 t = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-            m = fmaxf(m, fmaxf(__low2float(t), __high2float(t)));
+            const __nv_bfloat162 t2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+            m = fmaxf(m, fmaxf(__low2float(t2), __high2float(t2)));
         }
     };
-    const int G = gridDim.x;
     uint4 keep[KEEP ? 8 : 1];
     if constexpr (KEEP) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const int rj = blockIdx.x + j * G;
+            const int rj = cb + j * G;
             keep[j] = make_uint4(0, 0, 0, 0);
             if (rj < M && (int)threadIdx.x < kv)
-                keep[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)threadIdx.x * 8) * 2);
+                keep[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)rj * ldx + (int64_t)threadIdx.x * 8) * 2);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) vec_max(keep[j]);
     } else {
-        for (int r = blockIdx.x; r < M; r += 4 * G) {
+        for (int r = cb; r < M; r += 4 * G) {
             for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
                 uint4 v[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int rj = min(r + j * G, M - 1);              // a clamped row repeats a value: harmless for a maximum
-                    v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
+                    v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) vec_max(v[j]);
@@ -297,25 +395,22 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
     }
     m = warp_max(m);
     if (lane == 0) sh[warp] = m;
-    if (threadIdx.x == 0) s_fail = 0;
     __syncthreads();
+    const uint32_t token = s_token;
     if (threadIdx.x == 0) {
         float b = sh[0];
         for (int i = 1; i < kFusedThreads / 32; ++i) b = fmaxf(b, sh[i]);
-        slots[blockIdx.x] = b;
+        a.slots[blockIdx.x] = b;
         __threadfence();
-        st_release_u32(flags + blockIdx.x, token);
+        st_release_u32(a.flags + blockIdx.x, token);    // the epoch was read before this store (release orders it)
     }
-    // ---- rendezvous: thread t waits for CTA t's flag, then the maxima are combined
+    // ---- rendezvous: thread i waits for the flag of CTA i of this tensor, then the maxima are combined.  CTA 0 waits
+    // for the flags of ALL tensors' CTAs: once they all read E+1, every CTA of the launch has read the epoch.
+    const int nwait = blockIdx.x == 0 ? a.nt * G : G, base = blockIdx.x == 0 ? 0 : t * G;
     float g = 0.f;
-    if ((int)threadIdx.x < (int)gridDim.x) {
-        bool ok = false;
-        for (int spin = 0; spin < (1 << 22); ++spin) {          // a few seconds at most
-            if (ld_acquire_u32(flags + threadIdx.x) == token) { ok = true; break; }
-            __nanosleep(100);
-        }
-        if (ok) g = __ldcg(slots + threadIdx.x);
-        else s_fail = 1;
+    if ((int)threadIdx.x < nwait) {
+        if (!wait_flag_eq(a.flags + base + threadIdx.x, token, a.wait_ns)) s_fail = 1;
+        else if ((int)threadIdx.x < G) g = __ldcg(a.slots + base + threadIdx.x);
     }
     g = warp_max(g);
     __syncthreads();
@@ -325,16 +420,19 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
         float b = sh[0];
         for (int i = 1; i < kFusedThreads / 32; ++i) b = fmaxf(b, sh[i]);
         s_amax = b;
-        if (blockIdx.x == 0) {
-            *amax_out = b;
-            if (scale_out) *scale_out = div_mode_f32(b, 448.f, div_mode);
+        if (cb == 0) {
+            a.amax_out[t] = b;
+            if (a.scale_out[t]) *a.scale_out[t] = scale_fwd(b, 448.f, a.div_mode);
         }
-        if (s_fail && status) atomicExch(status, RWKVQ_E_TIMEOUT);
+        if (s_fail && a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
+        // all flags read E+1, so nobody will read the old epoch any more: move it on for the next launch.  After a
+        // timeout the epoch stays and the caller has to clear the scratch.
+        if (blockIdx.x == 0 && !s_fail) st_release_u32(a.flags + kFusedMaxCtas, token);
     }
     __syncthreads();
     if (s_fail) return;
     // ---- pass 2: codes
-    const float inv = div_mode_f32(448.f, fmaxf(s_amax, 1e-12f), div_mode);
+    const float inv = scale_inv(448.f, fmaxf(s_amax, 1e-12f), a.div_mode);
     auto vec_codes = [&](const uint4& v, int rj, int i) {
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         uint32_t c[4];
@@ -349,17 +447,17 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
     if constexpr (KEEP) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const int rj = blockIdx.x + j * G;
+            const int rj = cb + j * G;
             if (rj < M && (int)threadIdx.x < kv) vec_codes(keep[j], rj, threadIdx.x);
         }
     } else {
-        for (int r = blockIdx.x; r < M; r += 4 * G) {
+        for (int r = cb; r < M; r += 4 * G) {
             for (int i = threadIdx.x; i < kv; i += kFusedThreads) {
                 uint4 v[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int rj = min(r + j * G, M - 1);
-                    v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
+                    v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)rj * ldx + (int64_t)i * 8) * 2);
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
@@ -369,12 +467,47 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
     }
 }
 
+// A kernel whose only job is to let a bounded wait run out: one CTA waits for an mbarrier phase that nothing
+// completes (mode 0) or for a flag value that nothing stores (mode 1), gives up after `limit_ns`, records
+// RWKVQ_E_TIMEOUT in *status and returns normally -- the path every kernel of this library takes when a producer
+// never shows up, exercised without any fault or hang.
+__global__ void selftest_timeout_kernel(int* status, uint32_t* never_written, unsigned long long limit_ns, int mode) {
+    __shared__ uint64_t bar;
+    bool ok;
+    if (mode == 0) {
+        const uint32_t b = (uint32_t)__cvta_generic_to_shared(&bar);
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(b) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const unsigned long long t0 = global_ns();
+        ok = false;
+        for (;;) {
+            uint32_t done = 0;
+#pragma unroll 1
+            for (int i = 0; i < 256 && !done; ++i) {
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(done) : "r"(b) : "memory");
+                __nanosleep(64);
+            }
+            if (done) { ok = true; break; }
+            if (global_ns() - t0 > limit_ns) break;
+        }
+    } else {
+        ok = wait_flag_eq(never_written, ld_acquire_u32(never_written) + 1u, limit_ns);
+    }
+    if (!ok) atomicExch(status, RWKVQ_E_TIMEOUT);
+}
+
 __global__ void div_kernel(const float* a, const float* b, float* o, int64_t n, int mode) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) o[i] = div_mode_f32(a[i], b[i], mode);
 }
 
 }  // namespace rwkvq
+
+static std::atomic<long long>& rwkvq::wait_limit_override() {
+    static std::atomic<long long> v{-1};
+    return v;
+}
 
 using namespace rwkvq;
 
@@ -443,7 +576,7 @@ int32_t rwkvq_actq_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int
 int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
                          float* scale, float* amax_scratch, void* stream) {
     RWKVQ_REQUIRE(scale != nullptr, RWKVQ_E_BADARG, "prep_x_fp8: scale is null");
-    return rwkvq_actq_fp8(x, x_dtype, M, K, ldx, codes, ldc, amax_scratch, scale, RWKVQ_DIV_IEEE, 0u, stream);
+    return rwkvq_actq_fp8(x, x_dtype, M, K, ldx, codes, ldc, amax_scratch, scale, RWKVQ_DIV_TORCH, 0u, stream);
 }
 
 int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes, int64_t ldc,
@@ -462,40 +595,79 @@ int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, 
     return check_launch("prep_x_int8");
 }
 
-int64_t rwkvq_actq_fp8_fused_scratch_bytes(void) { return 2 * 512 * 4; }
+int64_t rwkvq_actq_fp8_fused_scratch_bytes(void) { return (kFusedEpochWord + 32) * 4; }
 
-int32_t rwkvq_actq_fp8_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
-                             float* amax, float* scale, void* scratch, int64_t scratch_bytes, int32_t* status, int32_t div_mode,
-                             uint32_t flags, void* stream) {
-    const char* who = "actq_fp8_fused";
-    RWKVQ_REQUIRE(x && codes && amax && scratch, RWKVQ_E_BADARG, "%s: null pointer", who);
+static int32_t launch_actq_fused(ActqArgs a, int nt, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int64_t ldc, void* scratch,
+                                 int64_t scratch_bytes, int32_t* status, int32_t div_mode, uint32_t flags, cudaStream_t st, const char* who) {
+    RWKVQ_REQUIRE(scratch != nullptr && a.amax_out != nullptr, RWKVQ_E_BADARG, "%s: null pointer", who);
+    for (int t = 0; t < nt; ++t) {
+        RWKVQ_REQUIRE(a.x[t] && a.codes[t], RWKVQ_E_BADARG, "%s: null pointer (tensor %d)", who, t);
+        RWKVQ_REQUIRE(aligned16(a.x[t]) && ((uintptr_t)a.codes[t] & 7) == 0, RWKVQ_E_ALIGN, "%s: rows must be 16-byte (x) / 8-byte (codes) aligned", who);
+    }
     RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
-    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL || div_mode == RWKVQ_DIV_TORCH, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
     RWKVQ_REQUIRE(M > 0 && K > 0 && K % 8 == 0 && M < (1 << 30), RWKVQ_E_SHAPE, "%s: M=%lld K=%lld (K must be a multiple of 8)", who, (long long)M, (long long)K);
-    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K && ldc % 8 == 0 && ldc >= K && ((uintptr_t)codes & 7) == 0, RWKVQ_E_ALIGN,
-                  "%s: rows must be 16-byte (x) / 8-byte (codes) aligned", who);
+    RWKVQ_REQUIRE(ldx % 8 == 0 && ldx >= K && ldc % 8 == 0 && ldc >= K, RWKVQ_E_ALIGN, "%s: rows must be 16-byte (x) / 8-byte (codes) aligned", who);
     RWKVQ_REQUIRE(scratch_bytes >= rwkvq_actq_fp8_fused_scratch_bytes() && ((uintptr_t)scratch & 3) == 0, RWKVQ_E_WORKSPACE,
                   "%s: scratch of %lld bytes needed", who, (long long)rwkvq_actq_fp8_fused_scratch_bytes());
-    static std::atomic<uint32_t> next_token{0x9e3779b9u};
-    const uint32_t token = next_token.fetch_add(0x61c88647u) | 1u;
-    int grid = (int)std::min<int64_t>(M, std::min<int64_t>(512, 2 * (int64_t)sm_count()));
-    int after = (flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? 1 : 0, from_bf16 = (flags & RWKVQ_FLAG_QUANT_FROM_BF16) ? 1 : 0;
-    int m = (int)M, k = (int)K;
-    float* slots = reinterpret_cast<float*>(scratch);
-    uint32_t* fl = reinterpret_cast<uint32_t*>(scratch) + 512;
-    int* st_ptr = status;
-    void* args[] = {(void*)&x, (void*)&codes, (void*)&amax, (void*)&scale, (void*)&slots, (void*)&fl, (void*)&token, (void*)&st_ptr,
-                    (void*)&m, (void*)&k, (void*)&ldx, (void*)&ldc, (void*)&div_mode, (void*)&after, (void*)&from_bf16};
-    const bool keep = K / 8 <= kFusedThreads && M <= 8 * (int64_t)grid;
+    a.nt = nt;
+    a.cpt = (int)std::min<int64_t>(M, std::min<int64_t>(kFusedMaxCtas, 2 * (int64_t)sm_count()) / nt);
+    a.after_bf16 = (flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? 1 : 0;
+    a.from_bf16 = (flags & RWKVQ_FLAG_QUANT_FROM_BF16) ? 1 : 0;
+    a.M = (int)M; a.K = (int)K; a.ldx = ldx; a.ldc = ldc; a.div_mode = div_mode; a.status = status ? status : device_status_ptr();
+    a.slots = reinterpret_cast<float*>(scratch);
+    a.flags = reinterpret_cast<uint32_t*>(scratch) + kFusedMaxCtas;
+    a.wait_ns = wait_limit_ns();
+    void* args[] = {(void*)&a};
+    const bool keep = K / 8 <= kFusedThreads && M <= 8 * (int64_t)a.cpt;
     const void* fn = x_dtype == RWKVQ_F16
                          ? (keep ? (const void*)actq_fp8_fused_kernel<RWKVQ_F16, true> : (const void*)actq_fp8_fused_kernel<RWKVQ_F16, false>)
                          : (keep ? (const void*)actq_fp8_fused_kernel<RWKVQ_BF16, true> : (const void*)actq_fp8_fused_kernel<RWKVQ_BF16, false>);
-    const cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kFusedThreads), args, 0, (cudaStream_t)stream);
+    const cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(a.cpt * nt), dim3(kFusedThreads), args, 0, st);
     if (e != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
     }
     return check_launch(who);
+}
+
+int32_t rwkvq_actq_fp8_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
+                             float* amax, float* scale, void* scratch, int64_t scratch_bytes, int32_t* status, int32_t div_mode,
+                             uint32_t flags, void* stream) {
+    ActqArgs a{};
+    a.x[0] = x; a.codes[0] = codes; a.amax_out = amax; a.scale_out[0] = scale;
+    return launch_actq_fused(a, 1, x_dtype, M, K, ldx, ldc, scratch, scratch_bytes, status, div_mode, flags, (cudaStream_t)stream, "actq_fp8_fused");
+}
+
+int32_t rwkvq_actq_fp8_fused3(const void* xr, const void* xk, const void* xv, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx,
+                              uint8_t* codes_r, uint8_t* codes_k, uint8_t* codes_v, int64_t ldc, float* amax3, void* scratch,
+                              int64_t scratch_bytes, int32_t* status, int32_t div_mode, uint32_t flags, void* stream) {
+    ActqArgs a{};
+    a.x[0] = xr; a.x[1] = xk; a.x[2] = xv; a.codes[0] = codes_r; a.codes[1] = codes_k; a.codes[2] = codes_v; a.amax_out = amax3;
+    return launch_actq_fused(a, 3, x_dtype, M, K, ldx, ldc, scratch, scratch_bytes, status, div_mode, flags, (cudaStream_t)stream, "actq_fp8_fused3");
+}
+
+
+void rwkvq_set_wait_limit_us(int64_t microseconds) { wait_limit_override().store(microseconds > 0 ? microseconds : -1); }
+
+int32_t rwkvq_device_status(int32_t* host_status, int32_t clear) {
+    RWKVQ_REQUIRE(host_status != nullptr, RWKVQ_E_BADARG, "device_status: null pointer");
+    int* p = device_status_ptr();
+    RWKVQ_REQUIRE(p != nullptr, RWKVQ_E_LAUNCH, "device_status: the status word's address is not available");
+    cudaError_t e = cudaMemcpy(host_status, p, sizeof(int32_t), cudaMemcpyDeviceToHost);
+    RWKVQ_REQUIRE(e == cudaSuccess, RWKVQ_E_LAUNCH, "device_status: %s", cudaGetErrorString(e));
+    if (clear && *host_status != 0) {
+        e = cudaMemset(p, 0, sizeof(int32_t));
+        RWKVQ_REQUIRE(e == cudaSuccess, RWKVQ_E_LAUNCH, "device_status: %s", cudaGetErrorString(e));
+    }
+    return RWKVQ_OK;
+}
+
+int32_t rwkvq_selftest_timeout(int32_t* status, void* scratch4, int64_t limit_us, int32_t mode, void* stream) {
+    RWKVQ_REQUIRE(status != nullptr && scratch4 != nullptr, RWKVQ_E_BADARG, "selftest_timeout: null pointer");
+    RWKVQ_REQUIRE(limit_us > 0 && limit_us <= 1000000 && (mode == 0 || mode == 1), RWKVQ_E_BADARG, "selftest_timeout: limit_us in (0, 1e6], mode 0 or 1");
+    selftest_timeout_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(status, reinterpret_cast<uint32_t*>(scratch4), (unsigned long long)limit_us * 1000ull, mode);
+    return check_launch("selftest_timeout");
 }
 
 }  // extern "C"

@@ -22,6 +22,18 @@ extern std::atomic<int64_t> g_launches;
 int32_t fail(int32_t code, const char* fmt, ...);
 int32_t check_launch(const char* what);   // cudaGetLastError() -> status, counts the launch
 int sm_count();
+// wall-time limit of every bounded device-side wait, nanoseconds: 1.5 s unless RWKVQ_WAIT_LIMIT_US (read once) or
+// rwkvq_set_wait_limit_us changed it
+unsigned long long wait_limit_ns();
+// per kernel and device: opt in to `bytes` of dynamic shared memory (once)
+int32_t ensure_smem_optin(const void* kern, int bytes, const char* who);
+// per (kernel, device, dynamic shared memory size): the opt-in above plus the resident CTAs per SM, looked up once
+int32_t kernel_plan(const void* kern, int threads, size_t smem, int optin_bytes, int* per_sm, const char* who);
+// programmatic dependent launch unless RWKVQ_PDL=0 (read once)
+bool use_pdl();
+// The library's per-device status word (device address): kernels whose entry points take no status pointer set it to
+// RWKVQ_E_TIMEOUT when a bounded wait gives up; rwkvq_device_status reads it.  Null if the lookup failed.
+int* device_status_ptr();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -38,6 +50,17 @@ __device__ __forceinline__ float div_full(float a, float b) {
 }
 __device__ __forceinline__ float div_mode_f32(float a, float b, int mode) {
     return mode == RWKVQ_DIV_FULL ? div_full(a, b) : __fdiv_rn(a, b);
+}
+
+// qmax / amax and amax / qmax of the activation scales.  RWKVQ_DIV_TORCH: what torch's GPU kernels compute for
+// `scalar / tensor` (reciprocal, then a product) and `tensor / scalar` (product with the rounded reciprocal).
+__device__ __forceinline__ float scale_inv(float qmax, float amax, int mode) {
+    if (mode == RWKVQ_DIV_TORCH) return __fmul_rn(__frcp_rn(amax), qmax);
+    return div_mode_f32(qmax, amax, mode);
+}
+__device__ __forceinline__ float scale_fwd(float amax, float qmax, int mode) {
+    if (mode == RWKVQ_DIV_TORCH) return __fmul_rn(amax, __frcp_rn(qmax));
+    return div_mode_f32(amax, qmax, mode);
 }
 
 template <int DT>
@@ -89,6 +112,38 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                  : "l"(p));
     return r;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for *p == want (a flag another CTA of the same cooperative launch publishes with st_release_u32).
+// The clock costs hundreds of nanoseconds to read, so it is consulted only after a few hundred failed polls.
+__device__ __forceinline__ bool wait_flag_eq(const uint32_t* p, uint32_t want, unsigned long long limit_ns) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+        if (ld_acquire_u32(p) == want) return true;
+        __nanosleep(64);
+    }
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i) {
+            if (ld_acquire_u32(p) == want) return true;
+            __nanosleep(128);
+        }
+        if (global_ns() - t0 > limit_ns) return false;
+    }
 }
 
 // atomic max of a non-negative float through its bit pattern

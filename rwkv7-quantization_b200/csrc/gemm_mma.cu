@@ -19,10 +19,11 @@ __global__ void __launch_bounds__(kThr, 2) gemm_mma_kernel(const W8Args a) {
     const int m0 = blockIdx.y * (16 * MT);
     const int units = (a.K + 63) >> 6;
 
-    float out_scale = 0.f, wscale = a.ws[0][0];
+    const bool per_row = (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) != 0;     // one weight scale per output row n
+    float act_scale = 0.f, wscale = a.ws[0][0];
     if constexpr (QT == QT_FP8) {
         const float am = a.a_scale[0];
-        out_scale = (a.amax_is_amax ? div_mode_f32(fmaxf(am, 1e-12f), 448.f, a.div_mode) : am) * wscale;
+        act_scale = a.amax_is_amax ? div_mode_f32(fmaxf(am, 1e-12f), 448.f, a.div_mode) : am;
     }
     for (int64_t tile = tb; tile < te; ++tile) {
         const int n0 = (int)tile << 3;
@@ -72,11 +73,12 @@ __global__ void __launch_bounds__(kThr, 2) gemm_mma_kernel(const W8Args a) {
             const int n = n0 + 2 * (l & 3) + (j & 1);
             if (m < a.M && n < a.N) {
                 float v;
+                const float wsn = per_row ? a.ws[0][n] : wscale;
                 if constexpr (QT == QT_FP8) {
-                    v = s * out_scale;
+                    v = s * (act_scale * wsn);
                 } else {
                     if (a.acc[0]) a.acc[0][(int64_t)m * a.ldacc + n] = s;
-                    v = (float)s * (a.a_scale[m] * wscale);
+                    v = (float)s * (a.a_scale[m] * wsn);
                 }
                 if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) v = bf16_round(v);
                 a.out[0][(int64_t)m * a.ldo + n] = __float2half_rn(v);
@@ -113,26 +115,26 @@ using namespace rwkvq;
 
 extern "C" {
 
-int32_t rwkvq_gemm_fp8_mma(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
+int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
                            int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                            int32_t div_mode, uint32_t flags, void* stream) {
     W8Args a{};
     a.a_codes = a_codes; a.lda = lda; a.a_scale = amax; a.amax_is_amax = amax_is_amax;
     a.w[0] = w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
     a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = div_mode; a.flags = flags;
-    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "gemm_fp8_mma: div_mode %d", div_mode);
-    return run_codes<QT_FP8>(a, (cudaStream_t)stream, "gemm_fp8_mma");
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "gemm_fp8: div_mode %d", div_mode);
+    return run_codes<QT_FP8>(a, (cudaStream_t)stream, "gemm_fp8");
 }
 
-int32_t rwkvq_gemm_int8_mma(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+int32_t rwkvq_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
                             const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M,
                             int64_t N, int64_t K, uint32_t flags, void* stream) {
     W8Args a{};
     a.a_codes = (const uint8_t*)a_codes; a.lda = lda; a.a_scale = a_scales;
     a.w[0] = (const uint8_t*)w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16; a.acc[0] = acc_out; a.ldacc = ldacc;
     a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = flags;
-    RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "gemm_int8_mma: ldacc < N");
-    return run_codes<QT_INT8>(a, (cudaStream_t)stream, "gemm_int8_mma");
+    RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "gemm_int8: ldacc < N");
+    return run_codes<QT_INT8>(a, (cudaStream_t)stream, "gemm_int8");
 }
 
 }  // extern "C"

@@ -53,6 +53,7 @@ struct TcArgs {
     int* counters;             // SWAP: arrivals per row tile, zero before the first use, left zero by every launch
     int* status;               // set to RWKVQ_E_TIMEOUT if a bounded wait gave up
     unsigned long long* trace; // optional [grid][16] timestamps of role milestones (profiling aid), else null
+    unsigned long long wait_ns; // wall-time limit of every mbarrier wait
     int64_t ldx, ldo, ldacc;
     int M, N, K, nmat;
     int NB;                    // rows of the B operand (UMMA N)
@@ -250,7 +251,7 @@ __device__ __noinline__ bool fused_prologue(const TcArgs& a, TcShared& s, uint8_
     }
     if (kpad != a.K)
         for (int i = qt; i < a.nmat * a.M * kpad / 16; i += kQThreads) reinterpret_cast<uint4*>(cache)[i] = make_uint4(0, 0, 0, 0);
-    const bool ok = mbar_wait(&s.xbar, 0, abort_flag);
+    const bool ok = mbar_wait(&s.xbar, 0, abort_flag, a.wait_ns);
     named_bar_sync(2, kQThreads);
     if (ok) quantizer_prologue<KIND, DT>(a, s, cache, xstage, kpad, qt);
     return ok;
@@ -309,7 +310,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 for (int kc = p.kc0; kc < p.kc1 && ok; ++kc, ++n) {
                     const int st = n % a.stages;
                     const uint32_t ph = (n / a.stages) & 1;
-                    if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
+                    if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag, a.wait_ns)) { tc_abort(s, a); ok = false; break; }
                     uint8_t* dst = ring + (size_t)st * stage_bytes;
                     mbar_expect_tx(&s.full[st], FUSED ? kABytes : stage_bytes);
                     tma_load_2d(dst, SWAP ? &maps.w[p.mat] : &maps.a[p.mat], kc * kChunk, p.prow, &s.full[st]);
@@ -333,12 +334,12 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
             bool ok = true;
             while (ok && it.next(p)) {
                 const int buf = pc & 1;
-                if (!mbar_wait(&s.tempty[buf], ((pc >> 1) & 1) ^ 1, abort_flag)) { tc_abort(s, a); break; }
+                if (!mbar_wait(&s.tempty[buf], ((pc >> 1) & 1) ^ 1, abort_flag, a.wait_ns)) { tc_abort(s, a); break; }
                 tc_fence_after_sync();
                 const uint32_t d = tmem_base + (uint32_t)(buf * a.acc_stride);
                 for (int kc = p.kc0; kc < p.kc1; ++kc, ++n) {
                     const int st = n % a.stages;
-                    if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
+                    if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag, a.wait_ns)) { tc_abort(s, a); ok = false; break; }
                     tc_fence_after_sync();
                     if (n == 0) tc_mark(a, 5);
                     const uint32_t sa = smem_u32(ring + (size_t)st * stage_bytes);
@@ -367,13 +368,15 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
         uint32_t pc = 0;
         while (it.next(p)) {
             const int buf = pc & 1;
-            if (!mbar_wait(&s.tfull[buf], (pc >> 1) & 1, abort_flag)) { tc_abort(s, a); break; }
+            if (!mbar_wait(&s.tfull[buf], (pc >> 1) & 1, abort_flag, a.wait_ns)) { tc_abort(s, a); break; }
             tc_fence_after_sync();
             if (pc == 0 && et == 0) tc_mark(a, 7);
             const uint32_t taddr = tmem_base + (uint32_t)(buf * a.acc_stride) + ((uint32_t)(q * 32) << 16);
-            const float wsc = a.ws[p.mat][0];
+            const bool per_row = (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) != 0;   // one weight scale per output row
+            float wsc = a.ws[p.mat][0];
             if constexpr (SWAP) {
                 const int n = p.prow + prow_l;          // weight row
+                if (per_row) wsc = a.ws[p.mat][min(n, a.N - 1)];
                 const bool partial = p.nslots > 1;
                 float out_scale = 0.f;
                 if constexpr (KIND == KIND_F8) {
@@ -444,13 +447,14 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 }
             } else {
                 const int m = p.prow + prow_l;          // token row
-                float rowscale;
+                float actscale;                         // scale of this thread's token row; the weight scale joins below
                 if constexpr (KIND == KIND_F8) {
                     const float am = a.a_scale[p.mat][0];
-                    rowscale = (a.amax_is_amax ? div_mode_f32(fmaxf(am, 1e-12f), 448.f, a.div_mode) : am) * wsc;
+                    actscale = a.amax_is_amax ? div_mode_f32(fmaxf(am, 1e-12f), 448.f, a.div_mode) : am;
                 } else {
-                    rowscale = (m < a.M ? a.a_scale[p.mat][m] : 0.f) * wsc;
+                    actscale = m < a.M ? a.a_scale[p.mat][m] : 0.f;
                 }
+                const float rowscale = actscale * wsc;
                 const bool vec_ok = (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out[p.mat]) & 15) == 0);
                 for (int c0 = 0; c0 < a.NB; c0 += 16) {
                     uint32_t r[16];
@@ -461,13 +465,18 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                         uint32_t h[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
+                            float s0 = rowscale, s1 = rowscale;
+                            if (per_row) {
+                                s0 = actscale * a.ws[p.mat][min(n0 + 2 * j, a.N - 1)];
+                                s1 = actscale * a.ws[p.mat][min(n0 + 2 * j + 1, a.N - 1)];
+                            }
                             float f0, f1;
                             if constexpr (KIND == KIND_F8) {
-                                f0 = __uint_as_float(r[2 * j]) * rowscale;
-                                f1 = __uint_as_float(r[2 * j + 1]) * rowscale;
+                                f0 = __uint_as_float(r[2 * j]) * s0;
+                                f1 = __uint_as_float(r[2 * j + 1]) * s1;
                             } else {
-                                f0 = (float)(int32_t)r[2 * j] * rowscale;
-                                f1 = (float)(int32_t)r[2 * j + 1] * rowscale;
+                                f0 = (float)(int32_t)r[2 * j] * s0;
+                                f1 = (float)(int32_t)r[2 * j + 1] * s1;
                             }
                             if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
                             const __half2 hh = __floats2half2_rn(f0, f1);
@@ -519,7 +528,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
             for (int kc = p.kc0; kc < p.kc1; ++kc, ++n) {
                 if ((int)(n & 3) != qw) continue;
                 const int st = n % a.stages;
-                if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag)) { tc_abort(s, a); ok = false; break; }
+                if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { tc_abort(s, a); ok = false; break; }
                 copy_chunk(a, cache, kpad, p.mat, kc, ring + (size_t)st * stage_bytes + kABytes, lane);
                 fence_proxy_async();
                 __syncwarp();
@@ -533,7 +542,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
     __syncthreads();
     if (warp == 1) {
         // the accumulators are released only after every epilogue warp has read its last one
-        if (!mbar_wait(&s.done, 0, abort_flag)) tc_abort(s, a);
+        if (!mbar_wait(&s.done, 0, abort_flag, a.wait_ns)) tc_abort(s, a);
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, tmem_cols);
     }
@@ -561,10 +570,8 @@ static int max_slots_for(int64_t total_units, int kchunks, int grid) {
 template <int KIND, bool SWAP, bool FUSED, int DT>
 static int32_t launch_tc(const TcMaps& maps, const TcArgs& a, int grid, cudaStream_t st, const char* who) {
     auto kern = gemm_tc_kernel<KIND, SWAP, FUSED, DT>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBudget); });
-    RWKVQ_REQUIRE(attr_err == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(attr_err));
+    const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudget, who);   // per device
+    if (rc != RWKVQ_OK) return rc;
     const size_t cache = FUSED ? (size_t)a.nmat * a.M * ((size_t)a.kchunks * kChunk + (size_t)a.K * 2) : 0;
     const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.NB * kChunk) + cache + 1024;
     cudaLaunchConfig_t cfg{};
@@ -576,14 +583,22 @@ static int32_t launch_tc(const TcMaps& maps, const TcArgs& a, int grid, cudaStre
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    const char* e = std::getenv("RWKVQ_PDL");
-    cfg.numAttrs = (e && e[0] == '0') ? 0 : 1;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, maps, a);
     if (err != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(err));
     }
     return check_launch(who);
+}
+
+// Weights as the 128-row operand with stream-K (SWAP, the only form that uses the workspace's partial sums) pays for
+// few tokens only: measured on the 7.2B shapes, the GEMM mode (tokens as the 128-row operand, narrow weight tiles) is
+// 2-4 x faster from 33 tokens on, except for a long K against few weight tiles (FFN value: K = 16384, N = 4096), where
+// stream-K wins up to 48 tokens.
+static bool takes_swap_route(int64_t M, int64_t N, int64_t K, int nmat, bool fused) {
+    const int64_t narrow_tiles = (int64_t)nmat * ((M + kTileP - 1) / kTileP) * ((N + 63) / 64);
+    return fused || M <= 16 || (M <= 48 && K >= 8192 && 2 * narrow_tiles <= tc_grid());
 }
 
 struct TcCall {
@@ -602,6 +617,7 @@ static unsigned long long* g_trace = nullptr;
 
 static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
     a.trace = g_trace;
+    a.wait_ns = wait_limit_ns();
     RWKVQ_REQUIRE(a.M >= 0 && a.N >= 0 && a.K >= 0, RWKVQ_E_SHAPE, "%s: negative size", who);
     RWKVQ_REQUIRE(a.K % 16 == 0, RWKVQ_E_SHAPE, "%s: K=%d must be a multiple of 16", who, a.K);
     RWKVQ_REQUIRE(a.ldo >= a.N, RWKVQ_E_SHAPE, "%s: ldo=%lld < N", who, (long long)a.ldo);
@@ -619,11 +635,7 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
     if (a.M == 0 || a.N == 0) return RWKVQ_OK;
     RWKVQ_REQUIRE(a.K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
 
-    // Weights as the 128-row operand with stream-K (SWAP) pays for few tokens only: measured on the 7.2B shapes, the
-    // GEMM mode below (tokens as the 128-row operand, narrow weight tiles) is 2-4 x faster from 33 tokens on, except
-    // for a long K against few weight tiles (FFN value: K = 16384, N = 4096), where stream-K wins up to 48 tokens.
-    const int64_t narrow_tiles = (int64_t)a.nmat * ((a.M + kTileP - 1) / kTileP) * ((a.N + 63) / 64);
-    const bool swap = c.fused || a.M <= 16 || (a.M <= 48 && a.K >= 8192 && 2 * narrow_tiles <= tc_grid());
+    const bool swap = takes_swap_route(a.M, a.N, a.K, a.nmat, c.fused);
     if (c.fused) RWKVQ_REQUIRE(a.M <= 16, RWKVQ_E_SHAPE, "%s: the fused kernel takes M <= 16, got %d", who, a.M);
     a.kchunks = (a.K + kChunk - 1) / kChunk;
     TcMaps maps;
@@ -817,12 +829,47 @@ int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_sc
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8");
 }
 
-/* rwkvq_tc_gemm_fp8 for M <= 128 without a caller workspace: the split-K partial sums and arrival counters live in
+int32_t rwkvq_tc_gemm_fp8_rkv(const uint8_t* codes_r, const uint8_t* codes_k, const uint8_t* codes_v, int64_t lda, const float* amax3,
+                              int32_t amax_is_amax, const uint8_t* wr, const uint8_t* wk, const uint8_t* wv, int64_t ldw, const float* sr,
+                              const float* sk, const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M,
+                              int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes,
+                              void* stream) {
+    RWKVQ_REQUIRE(amax3 != nullptr, RWKVQ_E_BADARG, "tc_gemm_fp8_rkv: null amax");
+    TcArgs a{};
+    a.a_scale[0] = amax3; a.a_scale[1] = amax3 + 1; a.a_scale[2] = amax3 + 2; a.amax_is_amax = amax_is_amax;
+    a.ws[0] = sr; a.ws[1] = sk; a.ws[2] = sv;
+    a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
+    fill_common(a, 3, M, N, K, 0, ldo, div_mode, flags);
+    TcCall c{};
+    c.kind = KIND_F8; c.w[0] = wr; c.w[1] = wk; c.w[2] = wv; c.ldw = ldw; c.codes[0] = codes_r; c.codes[1] = codes_k; c.codes[2] = codes_v;
+    c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_fp8_rkv");
+}
+
+int32_t rwkvq_tc_gemm_int8_rkv(const int8_t* codes_r, const int8_t* codes_k, const int8_t* codes_v, int64_t lda, const float* scales_r,
+                               const float* scales_k, const float* scales_v, const int8_t* wr, const int8_t* wk, const int8_t* wv,
+                               int64_t ldw, const float* sr, const float* sk, const float* sv, void* out_r, void* out_k, void* out_v,
+                               int64_t ldo, int64_t M, int64_t N, int64_t K, uint32_t flags, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
+    TcArgs a{};
+    a.a_scale[0] = scales_r; a.a_scale[1] = scales_k; a.a_scale[2] = scales_v;
+    const bool shared = (flags & RWKVQ_FLAG_INT8_SHARED_WSCALE) != 0;
+    a.ws[0] = sr; a.ws[1] = shared ? sr : sk; a.ws[2] = shared ? sr : sv;
+    a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
+    fill_common(a, 3, M, N, K, 0, ldo, RWKVQ_DIV_IEEE, flags);
+    TcCall c{};
+    c.kind = KIND_I8; c.w[0] = wr; c.w[1] = wk; c.w[2] = wv; c.ldw = ldw; c.codes[0] = codes_r; c.codes[1] = codes_k; c.codes[2] = codes_v;
+    c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8_rkv");
+}
+
+/* rwkvq_tc_gemm_fp8 without a caller workspace: the split-K partial sums, arrival counters and status word live in
  * an 8 MiB array that is part of the library image on every GPU.  Nothing is allocated, here or in anything this calls.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
  *     outside any stream capture.  Later calls only enqueue work.
- *   - Shapes whose scratch need (rwkvq_workspace_bytes(M, N, K, 1)) exceeds 8 MiB, and M > 128, are refused with
- *     RWKVQ_E_WORKSPACE / RWKVQ_E_SHAPE.
+ *   - Only calls that take the weight-streaming form (at most 16 tokens, or at most 48 against a long K) keep partial
+ *     sums in the scratch; such a call is refused with RWKVQ_E_WORKSPACE if rwkvq_workspace_bytes(M, N, K, 1) exceeds
+ *     8 MiB (a matrix of more than about 60 000 rows).  Every other shape needs the header only and is accepted.
  *   - All calls on a device share the one array and it keeps what the previous call left in it; this entry point
  *     therefore clears the counters and the status word on `stream` before the kernel.  Two calls that can overlap
  *     on the GPU (different streams, or concurrent host threads on different streams) race on it: order them. */
@@ -830,8 +877,8 @@ int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const floa
                                  int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                                  int32_t div_mode, uint32_t flags, void* stream) {
     const char* who = "tc_gemm_fp8_static";
-    RWKVQ_REQUIRE(M <= 128, RWKVQ_E_SHAPE, "%s: M=%lld > 128 (the large-M kernel needs no scratch: use rwkvq_tc_gemm_fp8)", who, (long long)M);
-    const int64_t need = rwkvq_workspace_bytes(M, N, K, 1);
+    // only the weight-streaming form (few tokens) keeps partial sums in the scratch; the tiled GEMM uses the status word alone
+    const int64_t need = (M > 0 && N > 0 && K > 0 && takes_swap_route(M, N, K, 1, false)) ? rwkvq_workspace_bytes(M, N, K, 1) : kWsHeaderBytes;
     RWKVQ_REQUIRE(need <= (int64_t)kStaticScratchBytes, RWKVQ_E_WORKSPACE, "%s: this shape needs %lld bytes of scratch, the built-in array has %lld",
                   who, (long long)need, (long long)kStaticScratchBytes);
     void* ws = nullptr;
@@ -845,6 +892,16 @@ int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const floa
     TcCall c{};
     c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = ws; c.workspace_bytes = (int64_t)kStaticScratchBytes;
     return run_tc(a, c, (cudaStream_t)stream, who);
+}
+
+/* The status word of the built-in array (RWKVQ_E_TIMEOUT if a bounded wait of a rwkvq_tc_gemm_fp8_static call gave up
+ * since the last call cleared it).  Copies four bytes to the host: synchronizes, allocates nothing. */
+int32_t rwkvq_tc_static_status(int32_t* host_status) {
+    RWKVQ_REQUIRE(host_status != nullptr, RWKVQ_E_BADARG, "tc_static_status: null pointer");
+    void* ws = nullptr;
+    const int32_t rc = static_scratch_ptr(&ws);
+    if (rc != RWKVQ_OK) return rc;
+    return rwkvq_workspace_status(ws, host_status);
 }
 
 }  // extern "C"

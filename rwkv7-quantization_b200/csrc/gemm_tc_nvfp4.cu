@@ -54,6 +54,7 @@ struct NfArgs {
     int M, N, K;
     int mtiles, ntiles, kstages, stages;
     int* status;
+    unsigned long long wait_ns;   // wall-time limit of every mbarrier wait
 };
 
 struct NfShared {
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
                 const int mt = t % a.mtiles, nt = t / a.mtiles;
                 for (int kc = 0; kc < a.kstages; ++kc, ++n) {
                     const int st = n % a.stages;
-                    if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag)) { nf_abort(s, a); ok = false; break; }
+                    if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { nf_abort(s, a); ok = false; break; }
                     uint8_t* dst = ring + (size_t)st * kStage;
                     mbar_expect_tx(&s.full[st], kStage);
                     tma_load_2d(dst, &maps.a, kc * (int)kNfRowBytes, mt * kNfTileM, &s.full[st]);
@@ -163,12 +164,12 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
             bool ok = true;
             for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++pc) {
                 const int buf = pc % NACC;
-                if (!mbar_wait(&s.tempty[buf], ((pc / NACC) & 1) ^ 1, abort_flag)) { nf_abort(s, a); break; }
+                if (!mbar_wait(&s.tempty[buf], ((pc / NACC) & 1) ^ 1, abort_flag, a.wait_ns)) { nf_abort(s, a); break; }
                 tc_fence_after_sync();
                 const uint32_t d = tmem_base + (uint32_t)(buf * BN);
                 for (int kc = 0; kc < a.kstages; ++kc, ++n) {
                     const int st = n % a.stages;
-                    if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag)) { nf_abort(s, a); ok = false; break; }
+                    if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag, a.wait_ns)) { nf_abort(s, a); ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(ring + (size_t)st * kStage);
                     const uint32_t ssf = sa + kNfABytes + kBBytes;
@@ -203,7 +204,7 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++pc) {
             const int mt = t % a.mtiles, nt = t / a.mtiles;
             const int buf = pc % NACC;
-            if (!mbar_wait(&s.tfull[buf], (pc / NACC) & 1, abort_flag)) { nf_abort(s, a); break; }
+            if (!mbar_wait(&s.tfull[buf], (pc / NACC) & 1, abort_flag, a.wait_ns)) { nf_abort(s, a); break; }
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
             const int m = mt * kNfTileM + q * 32 + lane;
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
     __syncthreads();
     if (warp == 1) {
         // the accumulators are released only after every epilogue warp has read its last one
-        if (!mbar_wait(&s.done, 0, abort_flag)) nf_abort(s, a);
+        if (!mbar_wait(&s.done, 0, abort_flag, a.wait_ns)) nf_abort(s, a);
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kNfTmemCols);
     }
@@ -266,10 +267,8 @@ __global__ void __launch_bounds__(256) nvfp4_pack_scales_kernel(const uint8_t* _
 template <int BN>
 static int32_t launch_nvfp4(const NfMaps& maps, NfArgs a, int grid, cudaStream_t st, const char* who) {
     auto kern = gemm_tc_nvfp4_kernel<BN>;
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNfSmemBudget); });
-    RWKVQ_REQUIRE(attr_err == cudaSuccess, RWKVQ_E_LAUNCH, "%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(attr_err));
+    const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kNfSmemBudget, who);   // per device
+    if (rc != RWKVQ_OK) return rc;
     const size_t stage = kNfABytes + (size_t)BN * kNfRowBytes + kNfSfStage * (1 + BN / 128);
     a.stages = (int)std::min<size_t>(kNfMaxStages, (kNfSmemBudget - 1024) / stage);
     const size_t smem = (size_t)a.stages * stage + 1024;
@@ -282,8 +281,7 @@ static int32_t launch_nvfp4(const NfMaps& maps, NfArgs a, int grid, cudaStream_t
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    const char* e = std::getenv("RWKVQ_PDL");
-    cfg.numAttrs = (e && e[0] == '0') ? 0 : 1;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, maps, a);
     if (err != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -338,6 +336,7 @@ int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* 
     const int64_t tiles256 = ((M + kNfTileM - 1) / kNfTileM) * ((N + 255) / 256);
     const int bn = forced_bn == 128 || forced_bn == 256 ? forced_bn : (tiles256 * 4 >= (int64_t)sm_count() * 3 ? 256 : 128);
     NfArgs a{};
+    a.wait_ns = wait_limit_ns();
     a.sfa = a_scales_blocked; a.sfw = w_scales_blocked; a.a_pts = a_pts; a.w_pts = w_tscale; a.out = (__half*)out_f16; a.ldo = ldo;
     a.M = (int)M; a.N = (int)N; a.K = (int)K;
     a.mtiles = (int)((M + kNfTileM - 1) / kNfTileM);

@@ -35,6 +35,8 @@ struct I4Args {
     __half* out;            // [M, ldo]
     int64_t ldx, ldw, ldo;
     int M, N, K, group, scale_f16, pitch, ngroups;
+    int* status;                 // the library's per-device status word
+    unsigned long long wait_ns;  // wall-time limit of the bounded waits
 };
 
 struct I4Slot {
@@ -288,11 +290,14 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
                              ::"r"((uint32_t)__cvta_generic_to_shared(xs + (size_t)r * a.pitch)), "l"(a.x + (int64_t)r * a.ldx),
                                "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
-        const bool staged = w8_bar_wait(xbar);
+        if (!w8_staged_or_report(xbar, a.status, a.wait_ns)) {     // reported: drain the weight ring and stop
+            cp_async_wait<0>();
+            return;
+        }
 #pragma unroll 1
         for (int r = 0; r < a.M; ++r) {
             uint8_t* row = xs + (size_t)r * a.pitch;
-            const char* src = staged ? reinterpret_cast<const char*>(row) : reinterpret_cast<const char*>(a.x + (int64_t)r * a.ldx);
+            const char* src = reinterpret_cast<const char*>(row);
 #pragma unroll 1
             for (int i = threadIdx.x; i - lane < kv; i += kThr) {          // kv is a multiple of 16: half-warps are whole
                 const bool on = i < kv;
@@ -418,13 +423,14 @@ static size_t i4_fast_smem(int NT, int S, int M, int K) {
 
 template <typename Kern, typename Args>
 static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64_t tiles, bool fast) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-    if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThr, smem);
-    if (e != cudaSuccess || per_sm < 1) return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: occupancy query failed");
+    const int32_t rc = kernel_plan(reinterpret_cast<const void*>(kern), kThr, smem, 224 * 1024, &per_sm, "gemv_int4_group");
+    if (rc != RWKVQ_OK) return rc;
+    cudaError_t e;
     const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * std::min(per_sm, 2));
     if constexpr (std::is_same<Args, I4FastArgs>::value) {
+        a.b.status = device_status_ptr();
+        a.b.wait_ns = wait_limit_ns();
         a.tq = (int)(tiles / grid);
         a.trem = (int)(tiles % grid);
         const int tpc = (int)((tiles + grid - 1) / grid);
@@ -441,8 +447,7 @@ static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    const char* env = std::getenv("RWKVQ_PDL");
-    cfg.numAttrs = (env && env[0] == '0') ? 0 : 1;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, kern, a);
     if (e != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -101,8 +101,15 @@ __device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* con
 // Results of one 16-row tile, straight from the accumulator fragments: lane (g, t) holds weight rows n0+g (values 0, 1)
 // and n0+g+8 (values 2, 3) for the tokens 8i+2t and 8i+2t+1.
 template <int QT, int NT, typename T>
-__device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[NT][4], float out_scale,
+__device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[NT][4], float act_scale,
                                            const float* xs, float wscale) {
+    // weight scale of this lane's two rows: one per matrix, or one per output row with RWKVQ_FLAG_WSCALE_PER_ROW
+    float wlo = wscale, whi = wscale;
+    if (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) {
+        wlo = a.ws[mat][min(n0 + g, a.N - 1)];
+        whi = a.ws[mat][min(n0 + g + 8, a.N - 1)];
+    }
+    const float out_lo = act_scale * wlo, out_hi = act_scale * whi;     // FP8: (amax/448) * w_scale, formed before the product
 #pragma unroll
     for (int i = 0; i < NT; ++i)
 #pragma unroll
@@ -111,10 +118,10 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
             if (m >= a.M || n >= a.N) continue;
             float f;
             if constexpr (QT == QT_FP8) {
-                f = c[i][j] * out_scale;
+                f = c[i][j] * ((j & 2) ? out_hi : out_lo);
             } else {
                 if (a.acc[mat]) a.acc[mat][(int64_t)m * a.ldacc + n] = c[i][j];
-                f = (float)c[i][j] * (xs[m] * wscale);
+                f = (float)c[i][j] * (xs[m] * ((j & 2) ? whi : wlo));
             }
             if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
             a.out[mat][(int64_t)m * a.ldo + n] = __float2half_rn(f);
@@ -213,10 +220,14 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     griddep_wait();   // activations may come from the previous kernel; results may overwrite what it read
     w8_mark(a, 2);
 
-    float out_scale = 0.f;   // FP8: (amax/448)*w_scale
+    float out_scale = 0.f;   // FP8: amax/448 (the weight scale joins it in store_tile)
     if constexpr (QT == QT_FP8) {
         const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh, xbar);
-        out_scale = div_mode_f32(amax, 448.f, a.div_mode) * wscale;
+        if (amax < 0.f) {          // the staging copy timed out (reported): drain the weight ring and stop
+            cp_async_wait<0>();
+            return;
+        }
+        out_scale = div_mode_f32(amax, 448.f, a.div_mode);
     } else {
         quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
     }
@@ -281,14 +292,6 @@ static size_t smem_bytes(int NT, int M, int pitch, int S) {
 
 constexpr size_t kFusedSmemMax = 224 * 1024;    // of the 227 KB a CTA may opt in to
 
-static bool use_pdl() {
-    static const bool on = [] {
-        const char* e = std::getenv("RWKVQ_PDL");
-        return !(e && e[0] == '0');
-    }();
-    return on;
-}
-
 template <int QT, int DT, int NT, int S>
 static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
     auto kern = gemv_w8a8_kernel<QT, DT, NT, S>;
@@ -320,6 +323,8 @@ static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
     a.lgR = 0;
     while ((1 << a.lgR) < kWarps && (1 << a.lgR) < tpc) ++a.lgR;
     a.trace = g_gemv_trace;
+    a.status = device_status_ptr();
+    a.wait_ns = wait_limit_ns();
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(a.cpm * a.nmat));
     cfg.blockDim = dim3(kThr);

@@ -216,6 +216,8 @@ struct NfFusedArgs {
     int64_t ldx, ldw, ldws, ldo;
     int M, N, K, pitch;
     int lgR, tq, trem;
+    int* status;                 // the library's per-device status word
+    unsigned long long wait_ns;  // wall-time limit of the bounded waits
 };
 
 template <int DT, int NT, int S>
@@ -304,12 +306,15 @@ __global__ void __launch_bounds__(kThr, 2) gemv_nvfp4_fused_kernel(const NfFused
                              ::"r"((uint32_t)__cvta_generic_to_shared(xs + (size_t)r * a.pitch)),
                                "l"(reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2), "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
-        const bool staged = w8_bar_wait(xbar);
+        if (!w8_staged_or_report(xbar, a.status, a.wait_ns)) {     // reported: drain the weight ring and stop
+            nf_cp_async_wait<0>();
+            return;
+        }
         const int kv = a.K >> 3;
         float m = 0.f;
 #pragma unroll 1
         for (int r = 0; r < a.M; ++r) {
-            const char* src = staged ? reinterpret_cast<const char*>(xs + (size_t)r * a.pitch) : reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
+            const char* src = reinterpret_cast<const char*>(xs + (size_t)r * a.pitch);
 #pragma unroll 1
             for (int i = threadIdx.x; i < kv; i += kThr) m = fmaxf(m, packed_absmax8<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16)));
         }
@@ -320,7 +325,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_nvfp4_fused_kernel(const NfFused
 #pragma unroll 1
         for (int r = 0; r < a.M; ++r) {
             uint8_t* row = xs + (size_t)r * a.pitch;
-            const char* src = staged ? reinterpret_cast<const char*>(row) : reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
+            const char* src = reinterpret_cast<const char*>(row);
 #pragma unroll 1
             for (int b = threadIdx.x; b < nb; b += kThr) {
                 const uint4 v0 = *reinterpret_cast<const uint4*>(src + (size_t)b * 32), v1 = *reinterpret_cast<const uint4*>(src + (size_t)b * 32 + 16);
@@ -453,11 +458,12 @@ static size_t nf_fused_smem(int NT, int S, int M, int K) {
 template <int DT, int NT, int S>
 static int32_t launch_nf_fused(NfFusedArgs a, size_t smem, cudaStream_t st) {
     auto kern = gemv_nvfp4_fused_kernel<DT, NT, S>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-    if (e != cudaSuccess) return fail(RWKVQ_E_LAUNCH, "gemv_nvfp4_fused: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     int per_sm = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThr, smem);
-    if (e != cudaSuccess || per_sm < 1) return fail(RWKVQ_E_LAUNCH, "gemv_nvfp4_fused: occupancy query failed");
+    const int32_t rc = kernel_plan(reinterpret_cast<const void*>(kern), kThr, smem, 224 * 1024, &per_sm, "gemv_nvfp4_fused");
+    if (rc != RWKVQ_OK) return rc;
+    cudaError_t e;
+    a.status = device_status_ptr();
+    a.wait_ns = wait_limit_ns();
     const int64_t tiles = (a.N + 15) / 16;
     const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * std::min(per_sm, 2));
     a.tq = (int)(tiles / grid);
@@ -474,8 +480,7 @@ static int32_t launch_nf_fused(NfFusedArgs a, size_t smem, cudaStream_t st) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    const char* env = std::getenv("RWKVQ_PDL");
-    cfg.numAttrs = (env && env[0] == '0') ? 0 : 1;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, kern, a);
     if (e != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -500,14 +505,7 @@ static int32_t dispatch_nf_fused(const NfFusedArgs& a, cudaStream_t st) {
 // are written row-major and / or in the blocked order the tensor-core GEMM reads (either pointer may be null).
 constexpr int kNfQThreads = 512;
 
-__device__ __forceinline__ uint32_t nf_ld_acquire(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void nf_st_release(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
+constexpr int kNfQMaxCtas = 512;       // slots[512] | flags[512] | epoch word
 
 struct NfQArgs {
     const void* x;
@@ -520,7 +518,7 @@ struct NfQArgs {
     int* status;
     int64_t ldx, ldc, lds;
     int M, K;
-    uint32_t token;
+    unsigned long long wait_ns;
 };
 
 template <int DT>
@@ -528,8 +526,15 @@ __global__ void __launch_bounds__(kNfQThreads, 2) actq_nvfp4_fused_kernel(const 
     __shared__ float sh[kNfQThreads / 32];
     __shared__ float s_amax;
     __shared__ int s_fail;
+    __shared__ uint32_t s_token;
     const int kv = a.K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x;
+    // The rendezvous value is the scratch's epoch + 1, read on the device (see actq_fp8_fused_kernel): a captured launch
+    // can be replayed, because nothing about it is fixed on the host.
+    if (threadIdx.x == 0) {
+        s_token = ld_acquire_u32(a.flags + kNfQMaxCtas) + 1u;
+        s_fail = 0;
+    }
     // ---- pass 1: partial maximum of this CTA's rows, four rows per step
     float m = 0.f;
     for (int r = blockIdx.x; r < a.M; r += 4 * G) {
@@ -546,24 +551,19 @@ __global__ void __launch_bounds__(kNfQThreads, 2) actq_nvfp4_fused_kernel(const 
     }
     m = warp_max(m);
     if (lane == 0) sh[warp] = m;
-    if (threadIdx.x == 0) s_fail = 0;
     __syncthreads();
+    const uint32_t token = s_token;
     if (threadIdx.x == 0) {
         float b = sh[0];
         for (int i = 1; i < kNfQThreads / 32; ++i) b = fmaxf(b, sh[i]);
         a.slots[blockIdx.x] = b;
         __threadfence();
-        nf_st_release(a.flags + blockIdx.x, a.token);
+        st_release_u32(a.flags + blockIdx.x, token);
     }
     // ---- rendezvous: thread t waits for CTA t's flag (bounded), then the maxima are combined
     float g = 0.f;
     if ((int)threadIdx.x < G) {
-        bool ok = false;
-        for (int spin = 0; spin < (1 << 22); ++spin) {
-            if (nf_ld_acquire(a.flags + threadIdx.x) == a.token) { ok = true; break; }
-            __nanosleep(100);
-        }
-        if (ok) g = __ldcg(a.slots + threadIdx.x);
+        if (wait_flag_eq(a.flags + threadIdx.x, token, a.wait_ns)) g = __ldcg(a.slots + threadIdx.x);
         else s_fail = 1;
     }
     g = warp_max(g);
@@ -575,6 +575,7 @@ __global__ void __launch_bounds__(kNfQThreads, 2) actq_nvfp4_fused_kernel(const 
         for (int i = 1; i < kNfQThreads / 32; ++i) b = fmaxf(b, sh[i]);
         s_amax = b;
         if (s_fail && a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
+        if (blockIdx.x == 0 && !s_fail) st_release_u32(a.flags + kNfQMaxCtas, token);   // every CTA has read the old epoch
     }
     __syncthreads();
     if (s_fail) return;
@@ -700,7 +701,7 @@ int32_t rwkvq_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, cons
     return M <= 8 ? dispatch_nf_fused<RWKVQ_BF16, 1>(a, st) : dispatch_nf_fused<RWKVQ_BF16, 2>(a, st);
 }
 
-int64_t rwkvq_actq_nvfp4_fused_scratch_bytes(void) { return 2 * 512 * 4; }
+int64_t rwkvq_actq_nvfp4_fused_scratch_bytes(void) { return (2 * kNfQMaxCtas + 32) * 4; }
 
 int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc,
                                uint8_t* block_scales, int64_t lds, uint8_t* block_scales_blocked, float* pts, void* scratch,
@@ -715,12 +716,11 @@ int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_
                   "%s: code rows must be 4-byte aligned", who);
     RWKVQ_REQUIRE(scratch_bytes >= rwkvq_actq_nvfp4_fused_scratch_bytes() && ((uintptr_t)scratch & 3) == 0, RWKVQ_E_WORKSPACE,
                   "%s: scratch of %lld bytes needed", who, (long long)rwkvq_actq_nvfp4_fused_scratch_bytes());
-    static std::atomic<uint32_t> next_token{0x51ed270bu};
     NfQArgs a{};
     a.x = x; a.codes = codes; a.bs_rows = block_scales; a.bs_blocked = block_scales_blocked; a.pts = pts;
-    a.slots = reinterpret_cast<float*>(scratch); a.flags = reinterpret_cast<uint32_t*>(scratch) + 512; a.status = status;
+    a.slots = reinterpret_cast<float*>(scratch); a.flags = reinterpret_cast<uint32_t*>(scratch) + kNfQMaxCtas; a.status = status ? status : device_status_ptr();
     a.ldx = ldx; a.ldc = ldc; a.lds = lds; a.M = (int)M; a.K = (int)K;
-    a.token = next_token.fetch_add(0x61c88647u) | 1u;
+    a.wait_ns = wait_limit_ns();
     const int grid = (int)std::min<int64_t>(M, std::min<int64_t>(512, 2 * (int64_t)sm_count()));
     void* args[] = {(void*)&a};
     const void* fn = x_dtype == RWKVQ_F16 ? (const void*)actq_nvfp4_fused_kernel<RWKVQ_F16> : (const void*)actq_nvfp4_fused_kernel<RWKVQ_BF16>;

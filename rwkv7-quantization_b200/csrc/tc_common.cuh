@@ -1,8 +1,9 @@
 // PTX wrappers for the Blackwell (sm_100a) data path used by the tensor-memory kernels:
 // mbarrier with BOUNDED waits, TMA tiled loads, tcgen05 MMA / commit / load, tensor-memory allocation.
 //
-// Every wait on an mbarrier gives up after kWaitLimitNs of wall time and reports it; a kernel that sees a
-// timeout records RWKVQ_E_TIMEOUT in its status word, stops issuing work, drains and frees its tensor memory.
+// Every wait on an mbarrier gives up after the wall-time limit the host passes to the kernel (wait_limit_ns(): 1.5 s
+// unless changed) and reports it; a kernel that sees a timeout records RWKVQ_E_TIMEOUT in its status word, stops
+// issuing work, drains and frees its tensor memory.
 #pragma once
 
 #include <cuda.h>
@@ -12,15 +13,7 @@
 namespace rwkvq {
 namespace tc {
 
-constexpr unsigned long long kWaitLimitNs = 1500ull * 1000ull * 1000ull;   // 1.5 s
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
-    return t;
-}
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -52,7 +45,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Waits for the phase with the given parity; false = gave up (time limit) or another role already aborted.
 // Reading %globaltimer costs hundreds of nanoseconds, so the clock is consulted only after a few thousand failed
 // polls (tens of microseconds); short waits never touch it.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag, unsigned long long limit_ns) {
 #pragma unroll 1
     for (int i = 0; i < 4096; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -64,7 +57,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
             __nanosleep(64);
         }
         if (*abort_flag) return false;
-        if (global_ns() - t0 > kWaitLimitNs) return false;
+        if (global_ns() - t0 > limit_ns) return false;
     }
 }
 

@@ -34,6 +34,8 @@ struct W8Args {
     int cpm;                  // decode GEMV: CTAs per matrix (grid = nmat * cpm)
     int tq, trem;             // decode GEMV: row tiles per CTA (quotient, remainder) within a matrix
     unsigned long long* trace;   // profiling aid: [grid][8] timestamps of the CTA's milestones, or null
+    int* status;                 // the library's per-device status word: RWKVQ_E_TIMEOUT if a bounded wait gave up
+    unsigned long long wait_ns;  // wall-time limit of the bounded waits
 };
 
 // profiling aid: thread 0 of a CTA stamps milestone `slot` (0..7) with the global timer when a trace buffer is set
@@ -153,19 +155,40 @@ __device__ __forceinline__ uint4 e4m3x8_to_f16x8(uint2 c) {
 // instructions and one read: thread 0 fetches the raw 16-bit rows with bulk copies (global -> shared, completion on
 // an mbarrier, independent of the weight ring's cp.async groups) INTO the tile itself -- a raw row and its row of f16
 // codes have the same size -- and two short loops (abs-max, then convert in place) work from shared memory.
-// `bar` must have been initialised with count 1 and made visible to the CTA.  A wait that runs out (seconds) falls
-// back to reading the row from global memory.
-__device__ __forceinline__ bool w8_bar_wait(uint64_t* bar) {
+// `bar` must have been initialised with count 1 and made visible to the CTA.  If the copy has not landed within the
+// wait limit the CTA reports RWKVQ_E_TIMEOUT through the status word, gives the copy a second bounded wait (its target
+// is the CTA's own shared memory) and stops without touching the tile or writing results.
+__device__ __forceinline__ bool w8_bar_wait(uint64_t* bar, unsigned long long limit_ns) {
     const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
-    for (int i = 0; i < (1 << 22); ++i) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(b) : "memory");
-        if (ok) return true;
+    auto poll = [&](int n) {
+#pragma unroll 1
+        for (int i = 0; i < n; ++i) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(b) : "memory");
+            if (ok) return true;
+        }
+        return false;
+    };
+    if (poll(1 << 14)) return true;          // the clock is costly to read: only consulted after many failed polls
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        if (poll(1 << 10)) return true;
+        if (global_ns() - t0 > limit_ns) return false;
     }
-    return false;
+}
+// CTA-uniform verdict on a staging copy: true = landed for every thread; false = reported, the CTA must return
+__device__ __forceinline__ bool w8_staged_or_report(uint64_t* bar, int* status, unsigned long long limit_ns) {
+    const bool staged = w8_bar_wait(bar, limit_ns);
+    if (__syncthreads_or(!staged)) {
+        if (threadIdx.x == 0 && status) atomicExch(status, RWKVQ_E_TIMEOUT);
+        if (!staged) w8_bar_wait(bar, limit_ns);
+        return false;
+    }
+    return true;
 }
 
+// Returns max(amax, 1e-12), or a negative value if the staging copy timed out (the CTA must then return).
 template <int DT, bool WIDE>
 __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh, uint64_t* bar) {
     static_assert(WIDE, "the tile holds f16 values");
@@ -203,11 +226,11 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
                          ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(x + (int64_t)r * a.ldx * 2),
                            "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
     }
-    const bool staged = w8_bar_wait(bar);
+    if (!w8_staged_or_report(bar, a.status, a.wait_ns)) return -1.f;
     float m = 0.f;
 #pragma unroll 1
     for (int r = 0; r < a.M; ++r) {
-        const char* src = staged ? reinterpret_cast<const char*>(xq + (size_t)r * a.pitch) : x + (int64_t)r * a.ldx * 2;
+        const char* src = reinterpret_cast<const char*>(xq + (size_t)r * a.pitch);
 #pragma unroll 1
         for (int i = threadIdx.x; i < kv; i += kThr)
             fp8_vec_amax<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, after, m);
@@ -219,7 +242,7 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
 #pragma unroll 1
     for (int r = 0; r < a.M; ++r) {
         uint8_t* qr = xq + (size_t)r * a.pitch;
-        const char* src = staged ? reinterpret_cast<const char*>(qr) : x + (int64_t)r * a.ldx * 2;
+        const char* src = reinterpret_cast<const char*>(qr);
 #pragma unroll 1
         for (int i = threadIdx.x; i < kv; i += kThr) {
             const uint2 c = fp8_vec_codes<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, inv);

@@ -30,7 +30,7 @@ def load_fp8_weight(z, key, dev):
 
 
 def linear_fp8(x, weight_info, out_dtype=torch.float16):
-    """The large-M FP8 route (fp8_ops.py:58-86): fp16 activations are taken as bf16, quantized per call with IEEE
+    """The large-M FP8 route (fp8_ops.py:58-86): fp16 activations are taken as bf16, quantized per call with torch's
     scale arithmetic, multiplied on the tensor cores, and the result is rounded to bf16 before `out_dtype`."""
     import fused_fp8_gemm as f
     w, w_ts = weight_info["weight"], weight_info["tensor_scale"]
@@ -43,15 +43,17 @@ def linear_fp8(x, weight_info, out_dtype=torch.float16):
     scale = torch.empty(1, dtype=torch.float32, device=dev)
     out = torch.empty((m, n), dtype=torch.float16, device=dev)
     st = abi.stream_ptr()
-    f._actq_fp8(x2, codes, amax, scale, abi.DIV_IEEE, abi.FLAG_AMAX_AFTER_BF16 | abi.FLAG_QUANT_FROM_BF16, st)
+    # inv = 448/amax and scale = amax/448 the way torch evaluates them on a GPU in prep_x_fp8 (DIV_TORCH)
+    f._actq_fp8(x2, codes, amax, scale, abi.DIV_TORCH, abi.FLAG_AMAX_AFTER_BF16 | abi.FLAG_QUANT_FROM_BF16, st)
+    gflags = abi.FLAG_OUT_VIA_BF16 | f._wscale_flag(w_ts, n)
     if f.ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, dev)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),
-                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DIV_IEEE, abi.FLAG_OUT_VIA_BF16, ws.data_ptr(),
-                 ws.numel(), st)
+                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DIV_IEEE, gflags, ws.data_ptr(), ws.numel(), st)
+        abi.after_call(ws)
     else:
         abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),
-                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DIV_IEEE, abi.FLAG_OUT_VIA_BF16, st)
+                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DIV_IEEE, gflags, st)
     return f._finish(out, x.shape[:-1], n, out_dtype)
 
 
@@ -69,6 +71,9 @@ def linear_quantized(x, weight_info, out_dtype=torch.float16):
     if qtype == "nvfp4":
         from nvfp4_ops import linear_nvfp4
         return linear_nvfp4(x, weight_info, out_dtype)
+    if qtype.startswith("int4_"):          # weight-info dicts of int4/int4_ops.load_int4_weight
+        from int4.int4_ops import linear_int4
+        return linear_int4(x, weight_info, out_dtype)
     return linear_fp8(x, weight_info, out_dtype)
 
 

@@ -40,6 +40,7 @@ TC_FUSED_M_MAX = 4                 # rows up to which the activation quantizatio
 _TC_CACHE_MAX = 100 * 1024        # shared memory for the activations (2 B) and their codes (1 B) in the fused kernel
 ROUTE = os.environ.get("RWKVQ_ROUTE", "auto").lower()   # auto | tc | mma
 GEMV_AUTO_M_MAX = 32
+_ACTQ_FUSED = os.environ.get("RWKVQ_ACTQ", "fused") == "fused"   # one cooperative launch; else memset + two kernels
 
 
 # --------------------------------------------------------------------------- helpers
@@ -80,6 +81,17 @@ def _finish(out2d: torch.Tensor, lead, n: int, out_dtype):
 
 def _u8(t: torch.Tensor) -> torch.Tensor:
     return t if t.dtype in (torch.uint8, torch.int8) else t.view(torch.uint8)
+
+
+def _wscale_flag(w_ts: torch.Tensor, n: int) -> int:
+    """A weight scale of N values (scheme "fp8_perchannel", schemes.py:26-34) is applied per output row; the reference
+    kernels load one scalar (fused_fp8_gemm.py:242) and so cannot run such weights."""
+    cnt = w_ts.numel()
+    if cnt == 1:
+        return 0
+    if cnt != n or w_ts.dtype != torch.float32 or not w_ts.is_contiguous():
+        raise ValueError(f"rwkvq: tensor_scale must hold 1 or N={n} contiguous fp32 values, got {tuple(w_ts.shape)} {w_ts.dtype}")
+    return abi.FLAG_WSCALE_PER_ROW
 
 
 # --------------------------------------------------------------------------- activation preparation
@@ -165,16 +177,19 @@ def _best_method(M, N, K):
 def _fp8_gemv(x2, w, w_ts, awq, flags):
     m, k = x2.shape
     n = w.shape[0]
+    flags |= _wscale_flag(w_ts, n)
     out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
     if _tc_fused_fits(m, k):
         ws = abi.workspace(m, n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
                  w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
                  ws.data_ptr(), ws.numel(), abi.stream_ptr())
+        abi.after_call(ws)
         return out
     abi.call("rwkvq_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
              w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
              abi.stream_ptr())
+    abi.after_call()
     return out
 
 
@@ -182,8 +197,8 @@ def _actq_fp8(x2, codes, amax, scale, div, flags, st):
     """FP8 activation codes + per-call amax: one cooperative launch (K a multiple of 8), else memset + two kernels."""
     m, k = x2.shape
     ldx = x2.stride(0) if m > 1 else k
-    if k % 8 == 0 and m > 0 and os.environ.get("RWKVQ_ACTQ", "fused") == "fused":
-        scratch = torch.empty(1024, dtype=torch.int32, device=x2.device)
+    if k % 8 == 0 and m > 0 and _ACTQ_FUSED:
+        scratch = abi.actq_scratch(x2.device)
         abi.call("rwkvq_actq_fp8_fused", x2.data_ptr(), abi.dtype_code(x2), m, k, ldx, codes.data_ptr(), k, amax.data_ptr(),
                  abi.ptr(scale), scratch.data_ptr(), scratch.numel() * 4, None, div, flags, st)
     else:
@@ -199,15 +214,41 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     amax = torch.empty(1, dtype=torch.float32, device=x2.device)
     out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
     st = abi.stream_ptr()
+    gemm_flags |= _wscale_flag(w_ts, n)
     _actq_fp8(x2, codes, amax, None, abi.DEFAULT_DIV, act_flags, st)
     if ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
                  w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(), st)
+        abi.after_call(ws)
     else:
         abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
                  out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, st)
     return out
+
+
+def _fp8_codes_gemm_rkv(xs, ws_, scales):
+    """r, k, v above the decode kernel's range: ONE activation-quantization launch for the three inputs and ONE
+    tensor-core GEMM launch for the three projections (the reference: prep3_x + fused_rkv_fp8_kernel)."""
+    m, k = xs[0].shape
+    n = ws_[0].shape[0]
+    dev = xs[0].device
+    codes = torch.empty((3, m, k), dtype=torch.uint8, device=dev)
+    amax = torch.empty(3, dtype=torch.float32, device=dev)
+    outs = torch.empty((3, m, n), dtype=torch.float16, device=dev)
+    st = abi.stream_ptr()
+    scratch = abi.actq_scratch(dev)
+    flags = _wscale_flag(scales[0], n)
+    abi.call("rwkvq_actq_fp8_fused3", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]), m, k, k,
+             codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, amax.data_ptr(), scratch.data_ptr(),
+             scratch.numel() * 4, None, abi.DEFAULT_DIV, abi.FLAG_QUANT_FROM_BF16, st)
+    ws = abi.workspace(min(m, 128), n, k, 3, dev)
+    abi.call("rwkvq_tc_gemm_fp8_rkv", codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, amax.data_ptr(), 1,
+             ws_[0].data_ptr(), ws_[1].data_ptr(), ws_[2].data_ptr(), ws_[0].stride(0), scales[0].data_ptr(),
+             scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
+             m, n, k, abi.DEFAULT_DIV, flags, ws.data_ptr(), ws.numel(), st)
+    abi.after_call(ws)
+    return [outs[0], outs[1], outs[2]]
 
 
 def linear_fp8_m1_fused(x, weight_info, out_dtype=torch.float16):
@@ -245,7 +286,9 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     n = ws_[0].shape[0]
     dev = xs[0].device
     awq_r, awq_k = wr_info.get("awq_scale"), wk_info.get("awq_scale")
-    same_ld = len({w.stride(0) for w in ws_}) == 1 and all(w.shape == ws_[0].shape for w in ws_)
+    wflags = {_wscale_flag(i["tensor_scale"], n) for i in (wr_info, wk_info, wv_info)}
+    same_ld = len({w.stride(0) for w in ws_}) == 1 and all(w.shape == ws_[0].shape for w in ws_) and len(wflags) == 1
+    wflag = next(iter(wflags)) if len(wflags) == 1 else 0
     f32 = lambda a: None if a is None else a.to(device=dev, dtype=torch.float32).contiguous()
     if _tc_fused_fits(m, k, 3) and same_ld:
         xs = [t.contiguous() for t in xs]
@@ -256,7 +299,8 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
                  abi.ptr(awq_r), abi.ptr(awq_k), ws_[0].data_ptr(), ws_[1].data_ptr(), ws_[2].data_ptr(), ws_[0].stride(0),
                  wr_info["tensor_scale"].data_ptr(), wk_info["tensor_scale"].data_ptr(),
                  wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
-                 m, n, k, k, abi.DEFAULT_DIV, 0, ws.data_ptr(), ws.numel(), abi.stream_ptr())
+                 m, n, k, k, abi.DEFAULT_DIV, wflag, ws.data_ptr(), ws.numel(), abi.stream_ptr())
+        abi.after_call(ws)
     elif _gemv_fits(m, k) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
@@ -265,7 +309,10 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
                  abi.ptr(awq_r), abi.ptr(awq_k), ws_[0].data_ptr(), ws_[1].data_ptr(), ws_[2].data_ptr(), ws_[0].stride(0),
                  wr_info["tensor_scale"].data_ptr(), wk_info["tensor_scale"].data_ptr(),
                  wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
-                 m, n, k, k, abi.DEFAULT_DIV, 0, abi.stream_ptr())
+                 m, n, k, k, abi.DEFAULT_DIV, wflag, abi.stream_ptr())
+        abi.after_call()
+    elif ROUTE != "mma" and _ACTQ_FUSED and same_ld and awq_r is None and awq_k is None and k % 8 == 0 and m > 0:
+        outs = _fp8_codes_gemm_rkv([t.contiguous() for t in xs], ws_, [i["tensor_scale"] for i in (wr_info, wk_info, wv_info)])
     else:
         outs = []
         for x2, w, info, awq in zip(xs, ws_, (wr_info, wk_info, wv_info), (awq_r, awq_k, None)):
@@ -343,6 +390,24 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
                  ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0), scales[0].data_ptr(),
                  scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(),
                  outs[2].data_ptr(), n, m, n, k, k, abi.DEFAULT_DIV, 0, abi.stream_ptr())
+    elif ROUTE != "mma" and same_ld and m > 0:
+        # above the decode kernel's range: three row-quantization launches and ONE tensor-core GEMM launch for r, k, v
+        # (the reference: 3 x _prep_x_int8_kernel + fused_rkv_int8_kernel)
+        dev = xs[0].device
+        st = abi.stream_ptr()
+        codes = torch.empty((3, m, k), dtype=torch.int8, device=dev)
+        xsc = torch.empty((3, m), dtype=torch.float32, device=dev)
+        outs3 = torch.empty((3, m, n), dtype=torch.float16, device=dev)
+        for i, x2 in enumerate(xs):
+            abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
+                     codes[i].data_ptr(), k, xsc[i].data_ptr(), abi.DEFAULT_DIV, st)
+        wsp = abi.workspace(min(m, 128), n, k, 3, dev)
+        abi.call("rwkvq_tc_gemm_int8_rkv", codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, xsc[0].data_ptr(),
+                 xsc[1].data_ptr(), xsc[2].data_ptr(), ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0),
+                 scales[0].data_ptr(), scales[1].data_ptr(), scales[2].data_ptr(), outs3[0].data_ptr(), outs3[1].data_ptr(),
+                 outs3[2].data_ptr(), n, m, n, k, 0, wsp.data_ptr(), wsp.numel(), st)
+        abi.after_call(wsp)
+        outs = [outs3[0], outs3[1], outs3[2]]
     else:
         outs = [_int8_any(x2, w, s) for x2, w, s in zip(xs, ws, scales)]
     return tuple(_finish(o, lead, n, out_dtype) for o in outs)
@@ -359,6 +424,9 @@ def linear_quantized_fused(x, weight_info, out_dtype=torch.float16):
     if qtype == "nvfp4":
         from nvfp4_ops import linear_nvfp4
         return linear_nvfp4(x, weight_info, out_dtype)
+    if qtype.startswith("int4_"):          # weight-info dicts of int4/int4_ops.load_int4_weight
+        from int4.int4_ops import linear_int4
+        return linear_int4(x, weight_info, out_dtype)
     if m <= FUSED_M_MAX:
         return linear_fp8_fused(x, weight_info, out_dtype=out_dtype)
     from fp8_ops import linear_fp8

@@ -88,7 +88,7 @@ def quantize_activations_nvfp4(x: torch.Tensor, blocked: bool = False):
         abi.call("rwkvq_actq_nvfp4", x2.data_ptr(), abi.dtype_code(x2), m, k, k, codes.data_ptr(), k // 2, bs.data_ptr(),
                  k // BLOCK, pts.data_ptr(), amax.data_ptr(), abi.stream_ptr())
         return codes, (pack_scales(bs, k) if blocked else bs), pts
-    scratch = torch.empty(1024, dtype=torch.int32, device=dev)
+    scratch = abi.actq_scratch(dev)
     if blocked:
         bs = torch.empty(int(abi.lib().rwkvq_nvfp4_blocked_scale_bytes(m, k)), dtype=torch.uint8, device=dev)
         rows_ptr, blk_ptr = None, bs.data_ptr()

@@ -16,11 +16,12 @@ LIB_PATH = os.environ.get("RWKVQ_LIB") or os.path.join(_HERE, "librwkvq.so")   #
 
 OK = 0
 F16, BF16 = 0, 1
-DIV_IEEE, DIV_FULL = 0, 1
+DIV_IEEE, DIV_FULL, DIV_TORCH = 0, 1, 2
 FLAG_AMAX_AFTER_BF16 = 1
 FLAG_INT8_SHARED_WSCALE = 2
 FLAG_OUT_VIA_BF16 = 4
 FLAG_QUANT_FROM_BF16 = 8
+FLAG_WSCALE_PER_ROW = 16
 
 # The reference's Triton kernels divide with div.full.f32 on a GPU; RWKVQ_DIV=ieee switches every wrapper
 # to IEEE division (what torch and the Triton CPU interpreter compute).
@@ -48,8 +49,6 @@ SIGNATURES = {
                             _i32, _u32, _p],
     "rwkvq_gemm_fp8": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
     "rwkvq_gemm_int8": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p],
-    "rwkvq_gemm_fp8_mma": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
-    "rwkvq_gemm_int8_mma": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p],
     "rwkvq_workspace_bytes": [_i64, _i64, _i64, _i32],
     "rwkvq_workspace_status": [_p, _p],
     "rwkvq_tc_gemv_fp8": [_p, _i32, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _i64, _p],
@@ -80,8 +79,20 @@ SIGNATURES = {
     "rwkvq_tc_gemm_fp8_static": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
     "rwkvq_actq_fp8_fused_scratch_bytes": [],
     "rwkvq_actq_fp8_fused": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _i64, _p, _i32, _u32, _p],
+    "rwkvq_actq_fp8_fused3": [_p, _p, _p, _i32, _i64, _i64, _i64, _p, _p, _p, _i64, _p, _p, _i64, _p, _i32, _u32, _p],
+    "rwkvq_tc_gemm_fp8_rkv": [_p, _p, _p, _i64, _p, _i32, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
+                              _i32, _u32, _p, _i64, _p],
+    "rwkvq_tc_gemm_int8_rkv": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
+                               _u32, _p, _i64, _p],
+    "rwkvq_tc_static_status": [_p],
+    "rwkvq_set_wait_limit_us": [_i64],
+    "rwkvq_device_status": [_p, _i32],
+    "rwkvq_selftest_timeout": [_p, _p, _i64, _i32, _p],
+    "rwkvq_gemv_set_trace": [_p],
+    "rwkvq_tc_set_trace": [_p],
 }
-_RESTYPES = {"rwkvq_actq_nvfp4_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_fused_smem_bytes": ctypes.c_int64, "rwkvq_nvfp4_blocked_scale_bytes": ctypes.c_int64, "rwkvq_actq_fp8_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_smem_bytes": ctypes.c_int64, "rwkvq_gemv_int4_group_smem_bytes": ctypes.c_int64, "rwkvq_workspace_bytes": ctypes.c_int64, "rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64}
+_RESTYPES = {"rwkvq_actq_nvfp4_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_fused_smem_bytes": ctypes.c_int64, "rwkvq_nvfp4_blocked_scale_bytes": ctypes.c_int64, "rwkvq_actq_fp8_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_smem_bytes": ctypes.c_int64, "rwkvq_gemv_int4_group_smem_bytes": ctypes.c_int64, "rwkvq_workspace_bytes": ctypes.c_int64, "rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64,
+             "rwkvq_set_wait_limit_us": None, "rwkvq_gemv_set_trace": None, "rwkvq_tc_set_trace": None}
 
 _lib = None
 _device_checked = False
@@ -156,14 +167,66 @@ def div_on_device(a: torch.Tensor, b: torch.Tensor, mode: int = DIV_FULL) -> tor
     return out
 
 
+# ---------------------------------------------------------------------------- status of the bounded device-side waits
+# RWKVQ_CHECK_STATUS=1: every wrapper call that can time out on the device is followed by a read of the status words
+# (this synchronizes, so it is a debugging mode); a timeout then raises instead of leaving undefined results behind.
+CHECK_STATUS = os.environ.get("RWKVQ_CHECK_STATUS", "0") == "1"
+E_TIMEOUT = -6
+
+
+def device_status(clear: bool = True) -> int:
+    """The library's per-device status word (set by kernels whose entry points take no status pointer)."""
+    out = ctypes.c_int32(0)
+    call("rwkvq_device_status", ctypes.addressof(out), 1 if clear else 0)
+    return out.value
+
+
+def check_status(ws: "torch.Tensor | None" = None) -> None:
+    """Raise if a bounded wait gave up since the last check: the per-device word and, if given, a workspace's word.
+    A workspace that reported a timeout is cleared again (its arrival counters may be left non-zero)."""
+    st = device_status()
+    if ws is not None:
+        st = st or workspace_status(ws)
+        if st:
+            ws.zero_()
+    if st:
+        raise RuntimeError(f"rwkvq: a device-side wait gave up (status {st}); results of the last calls are undefined")
+
+
+def after_call(ws: "torch.Tensor | None" = None) -> None:
+    if CHECK_STATUS:
+        check_status(ws)
+
+
+# ---------------------------------------------------------------------------- scratch of the one-launch quantizers
+_scratch: dict = {}
+
+
+def actq_scratch(device) -> torch.Tensor:
+    """Zero-initialised rendezvous scratch of the one-launch activation quantizers, one per (device, stream): calls on
+    a stream are ordered, so they share it; the kernels advance its epoch word themselves."""
+    key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
+    sc = _scratch.get(key)
+    if sc is None:
+        need = max(int(lib().rwkvq_actq_fp8_fused_scratch_bytes()), int(lib().rwkvq_actq_nvfp4_fused_scratch_bytes()))
+        sc = torch.zeros(need // 4 + 16, dtype=torch.int32, device=device)
+        _scratch[key] = sc
+    return sc
+
+
 # ---------------------------------------------------------------------------- workspace of the tensor-memory kernels
 _workspaces: dict = {}
+
+
+_ws_need: dict = {}
 
 
 def workspace(m: int, n: int, k: int, nmat: int, device) -> torch.Tensor:
     """Zero-initialised scratch for the tcgen05 kernels, one per (device, stream), grown on demand.
     Launches on one stream are ordered, so they can share it; the kernels leave its counters zero."""
-    need = int(lib().rwkvq_workspace_bytes(m, n, k, nmat))
+    need = _ws_need.get((m, n, k, nmat))
+    if need is None:
+        need = _ws_need[(m, n, k, nmat)] = int(lib().rwkvq_workspace_bytes(m, n, k, nmat))
     key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:

@@ -28,9 +28,16 @@ def shard_sequences(num_sequences: int, rank: int, world: int) -> list[int]:
     return list(range(rank, num_sequences, world))
 
 
+# weight-info entries with one row per OUTPUT feature (sliced) -- everything else is per input channel or per tensor
+_ROW_KEYS = ("weight", "packed", "block_scale", "scales", "zeros", "my", "ry")
+# entries derived from the full matrix and cached in the dict by the wrappers: a slice must rebuild its own
+_DERIVED_KEYS = ("block_scale_blocked",)
+
+
 def slice_weight_info(info: dict, rank: int, world: int, align: int = 128) -> dict:
     """Rows [start, end) of a quantized weight (output features) for a column-split projection.  Per-row tensors
-    (weight codes, block scales, group scales / zeros, per-channel scales) are sliced; per-tensor scalars are shared.
+    (weight codes, block scales, group scales / zeros, MM4 / MM8 row vectors, a per-row `tensor_scale`) are sliced;
+    per-tensor scalars and per-input-channel vectors (`awq_scale`, `mx`, `rx`) are shared; derived caches are dropped.
     Slice boundaries fall on multiples of `align` rows (the kernels' row tile)."""
     n = info["weight" if "weight" in info else "packed"].shape[0]
     if n % (world * align):
@@ -38,10 +45,10 @@ def slice_weight_info(info: dict, rank: int, world: int, align: int = 128) -> di
     start, end = rank * (n // world), (rank + 1) * (n // world)
     out = {}
     for key, value in info.items():
-        if torch.is_tensor(value) and value.dim() >= 1 and value.shape[0] == n:
-            out[key] = value[start:end].contiguous()
-        else:
-            out[key] = value
+        if key in _DERIVED_KEYS:
+            continue
+        per_row = key in _ROW_KEYS or (key == "tensor_scale" and torch.is_tensor(value) and value.dim() == 1 and value.numel() == n and n > 1)
+        out[key] = value[start:end].contiguous() if per_row else value
     return out
 
 

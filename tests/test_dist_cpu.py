@@ -30,6 +30,13 @@ def test_slice_weight_info_layouts():
     assert parts[1]["tensor_scale"] is info["tensor_scale"] and parts[0]["qtype"] == "nvfp4"
     with pytest.raises(ValueError):
         D.slice_weight_info(info, 0, 3)
+    # a cache derived from the FULL matrix must not travel with a slice; per-input-channel vectors are not sliced even
+    # when K happens to equal N; a per-row tensor_scale is
+    sq = {"weight": torch.zeros(512, 512), "awq_scale": torch.arange(512.0), "tensor_scale": torch.arange(512.0),
+          "block_scale": torch.zeros(512, 32), "block_scale_blocked": torch.zeros(99), "qtype": "nvfp4"}
+    p1 = D.slice_weight_info(sq, 1, 2)
+    assert "block_scale_blocked" not in p1 and "block_scale_blocked" in sq
+    assert p1["awq_scale"].shape == (512,) and torch.equal(p1["tensor_scale"], torch.arange(256.0, 512.0))
 
 
 def _free_port():

@@ -1,0 +1,232 @@
+"""GPU tests of the pieces around the kernels' waits: CUDA-graph replay of the one-launch activation quantizers (their
+grid rendezvous must not depend on anything fixed at capture time), a bounded wait that is seen to run out and to
+report RWKVQ_E_TIMEOUT without disturbing the context, the one-launch r/k/v GEMM route, and per-row weight scales.
+Everything goes through the C ABI (ctypes)."""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import rwkvq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def gen(seed, shape, std=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+@pytest.fixture(scope="module")
+def mods():
+    import rwkvq_abi as abi
+    import fused_fp8_gemm as f
+    import fp8_ops
+    abi.require_device()
+    return abi, f, fp8_ops
+
+
+def bits_equal(a, b, what=""):
+    a, b = a.detach().cpu().contiguous(), b.detach().cpu().contiguous()
+    assert a.shape == b.shape and a.dtype == b.dtype, (what, a.shape, b.shape)
+    view = {1: torch.uint8, 2: torch.int16, 4: torch.int32}[a.element_size()]
+    ne = a.view(view) != b.view(view)
+    assert not ne.any(), f"{what}: {int(ne.sum())} of {a.numel()} elements differ"
+
+
+def rel_err(out, ref):
+    out, ref = out.detach().cpu().float(), ref.detach().cpu().float()
+    floor = 0.02 * ref.pow(2).mean().sqrt().item() + 1e-30
+    return ((out - ref).abs() / ref.abs().clamp(min=floor)).max().item()
+
+
+def fp8_weight(seed, n, k, perchannel=False):
+    w = gen(seed, (n, k), (1.0 / k) ** 0.5)
+    if perchannel:
+        w = w * (0.25 + torch.arange(n).float().remainder(7).reshape(-1, 1))     # rows of very different magnitude
+        q, s = O.q_fp8_perchannel(w)
+    else:
+        q, s = O.q_fp8(w)
+    return {"weight": q, "tensor_scale": s, "qtype": "fp8"}
+
+
+def dev(info):
+    return {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in info.items()}
+
+
+def lib_div(abi):
+    return lambda a, b: abi.div_on_device(torch.as_tensor(a, dtype=torch.float32),
+                                          torch.broadcast_to(torch.as_tensor(b, dtype=torch.float32), torch.as_tensor(a).shape),
+                                          abi.DEFAULT_DIV).cpu()
+
+
+# ------------------------------------------------------------------------------------------------ graph replay
+def test_captured_projection_replays_with_new_activations(mods):
+    """ONE linear_fp8_fused call at M = 64 (activation-quantization launch + tensor-core GEMM) captured in a graph and
+    replayed with different inputs -- a large amax first, then small ones -- equals the eager result bit for bit."""
+    abi, f, _ = mods
+    info = dev(fp8_weight(1, 256, 1024))
+    xs = [gen(10 + i, (64, 1024), s).to(torch.bfloat16).cuda() for i, s in enumerate((50.0, 0.01, 1.0, 3.0))]
+    eager = [f.linear_fp8_fused(x, info).clone() for x in xs]
+    static_x = xs[0].clone()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        f.linear_fp8_fused(static_x, info)              # warm-up on the capture stream (allocates its scratch)
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            out = f.linear_fp8_fused(static_x, info)
+        for x, want in zip(xs, eager):
+            static_x.copy_(x)
+            g.replay()
+            st.synchronize()
+            bits_equal(out, want, "replay")
+
+
+@pytest.mark.parametrize("which", ["fp8", "nvfp4"])
+def test_captured_quantizer_with_own_scratch_replays(mods, which):
+    """The raw one-launch quantizer with caller-owned scratch, captured alone: every replay must rendezvous afresh."""
+    abi, f, _ = mods
+    L = abi.lib()
+    m, k = 96, 2048
+    xs = [gen(20 + i, (m, k), s).to(torch.bfloat16).cuda() for i, s in enumerate((40.0, 0.02, 2.0))]
+    x = xs[0].clone()
+    amax = torch.zeros(1, device="cuda")
+    if which == "fp8":
+        codes = torch.empty((m, k), dtype=torch.uint8, device="cuda")
+        scratch = torch.zeros(int(L.rwkvq_actq_fp8_fused_scratch_bytes()) // 4, dtype=torch.int32, device="cuda")
+
+        def launch(stream):
+            abi.call("rwkvq_actq_fp8_fused", x.data_ptr(), abi.BF16, m, k, k, codes.data_ptr(), k, amax.data_ptr(), None,
+                     scratch.data_ptr(), scratch.numel() * 4, None, abi.DIV_FULL, 0, stream)
+        results = lambda: (codes.clone(), amax.clone())
+    else:
+        codes = torch.empty((m, k // 2), dtype=torch.uint8, device="cuda")
+        bs = torch.empty((m, k // 16), dtype=torch.uint8, device="cuda")
+        scratch = torch.zeros(int(L.rwkvq_actq_nvfp4_fused_scratch_bytes()) // 4, dtype=torch.int32, device="cuda")
+
+        def launch(stream):
+            abi.call("rwkvq_actq_nvfp4_fused", x.data_ptr(), abi.BF16, m, k, k, codes.data_ptr(), k // 2, bs.data_ptr(), k // 16,
+                     None, amax.data_ptr(), scratch.data_ptr(), scratch.numel() * 4, None, stream)
+        results = lambda: (codes.clone(), bs.clone(), amax.clone())
+    eager = []
+    for xi in xs:
+        x.copy_(xi)
+        launch(abi.stream_ptr())
+        torch.cuda.synchronize()
+        eager.append(results())
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            launch(st.cuda_stream)
+        for xi, want in zip(xs + xs[::-1], eager + eager[::-1]):
+            x.copy_(xi)
+            g.replay()
+            st.synchronize()
+            for got, w in zip(results(), want):
+                bits_equal(got, w, which)
+
+
+# ------------------------------------------------------------------------------------------------ bounded waits
+@pytest.mark.parametrize("mode", [0, 1])
+def test_bounded_wait_runs_out_and_reports(mods, mode):
+    """A wait for something that never comes gives up after its limit, records RWKVQ_E_TIMEOUT and the kernel returns
+    normally: the context stays usable (a projection right after it is correct)."""
+    abi, f, _ = mods
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    abi.call("rwkvq_selftest_timeout", status.data_ptr(), word.data_ptr(), 200, mode, abi.stream_ptr())
+    t1.record()
+    torch.cuda.synchronize()
+    assert status.item() == abi.E_TIMEOUT
+    assert 0.15 <= t0.elapsed_time(t1) < 500.0, t0.elapsed_time(t1)       # waited at least the limit, not seconds
+    info = fp8_weight(3, 128, 512)
+    x = gen(4, (3, 512), 1.0, torch.bfloat16)
+    assert rel_err(f.linear_fp8_fused(x.cuda(), dev(info)), O.linear_fp8_fused(x, info, lib_div(abi))) <= 1e-2
+
+
+def test_device_status_word_reads_and_clears(mods):
+    abi, _, _ = mods
+    assert abi.device_status() == 0
+    abi.check_status()                                                    # nothing pending: no exception
+    L = abi.lib()
+    assert L.rwkvq_selftest_timeout(None, None, 10, 0, abi.stream_ptr()) == -1
+    L.rwkvq_set_wait_limit_us(2_000_000)
+    L.rwkvq_set_wait_limit_us(0)                                          # back to the default
+
+
+# ------------------------------------------------------------------------------------------------ r/k/v GEMM route
+@pytest.mark.parametrize("m", [33, 64, 200, 600])
+def test_fp8_rkv_gemm_route_equals_single_calls(mods, m):
+    """Above the decode kernel's range r, k, v run as one quantization launch + one GEMM launch; results equal three
+    single projections bit for bit and the oracle within 1e-2."""
+    abi, f, _ = mods
+    infos = [fp8_weight(30 + i, 384, 1024) for i in range(3)]
+    xs = [gen(40 + i + m, (m, 1024), 1.0 + i).to(torch.bfloat16) for i in range(3)]
+    d = [dev(i) for i in infos]
+    before = abi.launch_count()
+    got = f.linear_rkv_fused(*[x.cuda() for x in xs], *d)
+    assert abi.launch_count() - before == 2
+    want = O.linear_rkv_fused(*xs, *infos, div=lib_div(abi))
+    for g, w, x, i in zip(got, want, xs, d):
+        assert rel_err(g, w) <= 1e-2
+        bits_equal(g, f.linear_fp8_fused(x.cuda(), i), "fused vs single")
+
+
+@pytest.mark.parametrize("m", [40, 300])
+def test_int8_rkv_gemm_route_exact(mods, m):
+    abi, f, _ = mods
+    infos = []
+    for i in range(3):
+        q, s = O.q_int8_sym(gen(50 + i, (256, 768), 0.02, torch.float16))
+        infos.append({"weight": q, "tensor_scale": s, "qtype": "int8"})
+    xs = [gen(60 + i + m, (m, 768), 1.0, torch.float16) for i in range(3)]
+    d = [dev(i) for i in infos]
+    for shared in (True, False):
+        before = abi.launch_count()
+        got = f.linear_rkv_int8_fused(*[x.cuda() for x in xs], *d, compat_shared_scale=shared)
+        assert abi.launch_count() - before == 4
+        want = O.linear_rkv_int8_fused(*xs, *infos, div=lib_div(abi), shared_scale=shared)
+        for g, w in zip(got, want):
+            bits_equal(g, w, f"int8 rkv shared={shared}")
+
+
+# ------------------------------------------------------------------------------------------------ per-row weight scales
+@pytest.mark.parametrize("m", [1, 8, 32, 48, 300, 600])
+def test_fp8_perchannel_weight_scales(mods, m):
+    """Weights of the "fp8_perchannel" scheme (one scale per output row): every route applies scale[n] to column n."""
+    abi, f, fp8_ops = mods
+    info = fp8_weight(70, 200, 768, perchannel=True)
+    assert info["tensor_scale"].shape == (200,)
+    x = gen(71 + m, (m, 768), 1.0, torch.bfloat16)
+    want = O.linear_fp8_fused(x, info, lib_div(abi))
+    for route in ("auto", "mma"):
+        old, f.ROUTE = f.ROUTE, route
+        try:
+            assert rel_err(f.linear_fp8_fused(x.cuda(), dev(info)), want) <= 1e-2, route
+        finally:
+            f.ROUTE = old
+    if m > 512:
+        assert rel_err(fp8_ops.linear_quantized_fused(x.cuda(), dev(info)), O.linear_fp8(x, info)) <= 1e-2
+    infos = [info, fp8_weight(72, 200, 768, perchannel=True), fp8_weight(73, 200, 768, perchannel=True)]
+    xs = [x, gen(74, (m, 768), 2.0, torch.bfloat16), gen(75, (m, 768), 0.5, torch.bfloat16)]
+    got = f.linear_rkv_fused(*[t.cuda() for t in xs], *[dev(i) for i in infos])
+    for g, w in zip(got, O.linear_rkv_fused(*xs, *infos, div=lib_div(abi))):
+        assert rel_err(g, w) <= 1e-2
+
+
+def test_quantized_dispatch_routes_int4(mods):
+    """linear_quantized / linear_quantized_fused accept the INT4 weight-info dicts of int4_ops.load_int4_weight."""
+    _, f, fp8_ops = mods
+    from int4 import int4_ops, quantize_int4
+    w = gen(80, (256, 512), 512 ** -0.5)
+    q = quantize_int4.quantize_to_int4_groupwise(w, 128)
+    info = {"packed": q["packed"].cuda(), "scales": q["scales"].cuda(), "zeros": q["zeros"].cuda(), "group_size": 128,
+            "qtype": "int4_groupwise"}
+    x = gen(81, (4, 512), 1.0, torch.float16).cuda()
+    want = int4_ops.linear_int4(x, info)
+    bits_equal(fp8_ops.linear_quantized(x, info), want)
+    bits_equal(f.linear_quantized_fused(x, info), want)
