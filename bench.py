@@ -341,7 +341,8 @@ def run_ours(args, rank, world, local_rank):
 
 
 # ------------------------------------------------------------------------------------------ per-shape mode
-SHAPES = {"att": (C, C), "ffn_key": (F, C), "ffn_value": (C, F), "c2": (2560, 2560), "c1": (768, 768)}
+SHAPES = {"att": (C, C), "ffn_key": (F, C), "ffn_value": (C, F), "c2": (2560, 2560), "c1": (768, 768),
+          "att_rkv": (C, C), "c2_rkv": (2560, 2560)}      # *_rkv: three matrices of that shape in one r/k/v call
 
 
 def _rand_weight(scheme, n, k, dev):
@@ -383,15 +384,23 @@ def run_shape(args):
     abi.require_device()
     dev = torch.device("cuda", 0)
     n, k = SHAPES[args.shape]
-    wb = _weight_bytes(args.scheme, n, k)
+    nmat = 3 if args.shape.endswith("_rkv") else 1
+    wb = _weight_bytes(args.scheme, n, k) * nmat
     nbuf = max(2, int(400e6 / wb) + 1)
-    ws = [_rand_weight(args.scheme, n, k, dev) for _ in range(nbuf)]
-    x = torch.randn(args.m, k, device=dev).to(torch.float16 if args.scheme == "int4" else torch.bfloat16)
+    ws = [[_rand_weight(args.scheme, n, k, dev) for _ in range(nmat)] for _ in range(nbuf)]
+    xs = [torch.randn(args.m, k, device=dev).to(torch.float16 if args.scheme == "int4" else torch.bfloat16) for _ in range(nmat)]
+    x = xs[0]
     lin = _linear(args.scheme)
+    if nmat == 3:
+        import fused_fp8_gemm as f
+        rkv = {"fp8": f.linear_rkv_fused, "int8": f.linear_rkv_int8_fused}[args.scheme]
 
     def fn():
         for w in ws:
-            lin(x, w)
+            if nmat == 3:
+                rkv(xs[0], xs[1], xs[2], w[0], w[1], w[2])
+            else:
+                lin(x, w[0])
     st = torch.cuda.Stream()
     with torch.cuda.stream(st):
         for _ in range(max(1, args.warmup)):
@@ -404,10 +413,10 @@ def run_shape(args):
             g.replay()
         ms = timed(g.replay, args.steps, False)
     us = ms * 1e3 / (args.steps * nbuf)
-    nbytes = wb + args.m * k * 2 + args.m * n * 2
+    nbytes = wb + nmat * (args.m * k * 2 + args.m * n * 2)
     line = {"case": "shape", "scheme": args.scheme, "shape": args.shape, "M": args.m, "N": n, "K": k, "us_per_call": round(us, 3),
             "algorithmic_bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks()["hbm_gbs"], 4),
-            "TFLOPs": round(2 * args.m * n * k / us / 1e6, 1), "distinct_weight_buffers": nbuf}
+            "TFLOPs": round(2 * nmat * args.m * n * k / us / 1e6, 1), "distinct_weight_buffers": nbuf}
     print(json.dumps(line))
 
 

@@ -113,6 +113,10 @@ int32_t rwkvq_actq_fp8_fused3(const void* xr, const void* xk, const void* xv, in
  * codes = trunc(clamp(x*s, -128, 127)), scales[m] = amax/127. */
 int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes,
                           int64_t ldc, float* scales, int32_t div_mode, void* stream);
+/* prep3_x_int8 (fused_fp8_gemm.py:889-894: three prep_x_int8 calls) in ONE launch. */
+int32_t rwkvq_prep3_x_int8(const void* xr, const void* xk, const void* xv, int32_t x_dtype, int64_t M, int64_t K,
+                           int64_t ldx, int8_t* codes_r, int8_t* codes_k, int8_t* codes_v, int64_t ldc, float* scales_r,
+                           float* scales_k, float* scales_v, int32_t div_mode, void* stream);
 
 /* ---------------------------------------------------------------- W8A8 decode GEMV (M <= 32) */
 
@@ -146,14 +150,33 @@ int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int3
 
 /* ---------------------------------------------------------------- W8A8 GEMM on pre-quantized codes (any M) */
 
-/* These two run on the register-streaming mma.sync kernel (any M, no workspace); the tensor-memory entries further
- * down compute the same results on tcgen05 and are what the Python wrappers route to.
+/* These run on mma.sync kernels and need no workspace: the weight-streaming decode kernel for M <= 32 (code tile in
+ * shared memory), a register-streaming kernel for any other M; the tensor-memory entries further down compute the
+ * same results on tcgen05 and are what the Python wrappers route larger M to.
  * The GEMM half of linear_fp8_fused / linear_fp8 (fused_fp8_gemm.py:219-257, fp8_ops.py:77-80):
  * out = fp16( (a_codes . W^T) * (a_scale * w_scale[0]) ), where a_scale = amax[0]/448 if amax_is_amax != 0
  * (div_mode applies) or a_scale = amax[0] taken as the scale itself otherwise. */
 int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
                        const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M,
                        int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
+
+/* The GEMM half of linear_rkv_fused / linear_rkv_int8_fused on codes (fused_rkv_fp8_kernel fused_fp8_gemm.py:264-334,
+ * fused_rkv_int8_kernel :825-886): r, k, v in ONE launch of the weight-streaming decode kernel when M <= 32 and the
+ * code tile fits shared memory (each CTA copies the M*K bytes of codes once: the activations are quantized once per
+ * call, not once per CTA), three launches of the any-M kernel otherwise.  amax3 / scales_*: as amax / a_scales of the
+ * single-matrix entries.  The single-matrix entries take the same decode route for such M.  Same results as three
+ * single calls, bit for bit. */
+int32_t rwkvq_gemm_decode_route(int64_t M, int64_t K); /* 1: M rows of K codes take the decode kernel */
+int32_t rwkvq_gemm_fp8_rkv(const uint8_t* codes_r, const uint8_t* codes_k, const uint8_t* codes_v, int64_t lda,
+                           const float* amax3, int32_t amax_is_amax, const uint8_t* wr, const uint8_t* wk,
+                           const uint8_t* wv, int64_t ldw, const float* sr, const float* sk, const float* sv, void* out_r,
+                           void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N, int64_t K, int32_t div_mode,
+                           uint32_t flags, void* stream);
+int32_t rwkvq_gemm_int8_rkv(const int8_t* codes_r, const int8_t* codes_k, const int8_t* codes_v, int64_t lda,
+                            const float* scales_r, const float* scales_k, const float* scales_v, const int8_t* wr,
+                            const int8_t* wk, const int8_t* wv, int64_t ldw, const float* sr, const float* sk,
+                            const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N,
+                            int64_t K, uint32_t flags, void* stream);
 
 /* The GEMM half of linear_int8_fused (fused_fp8_gemm.py:734-782): codes int8 [M,K], a_scales fp32 [M]. */
 int32_t rwkvq_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,

@@ -1,6 +1,8 @@
 // Activation preparation kernels: bf16 copy + per-call amax (FP8 path), per-call e4m3 codes
 // (large-M FP8 path) and per-row int8 codes (INT8 path).  All HBM/L2-bound elementwise work:
 // 128-bit loads and stores, one row segment per CTA, block reduction + one atomic per CTA.
+#include <cooperative_groups.h>
+
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
@@ -256,14 +258,23 @@ __global__ void __launch_bounds__(kThreads) quant_fp8_kernel(const void* x, uint
 }
 
 // ----------------------------------------------------------------------------------------
-// prep_x_int8: one CTA per row; the row is read twice (second read hits L1/L2).
+// prep_x_int8 (and the three of prep3_x_int8 in one launch: blockIdx.y picks the tensor): one CTA per row; the row is
+// read twice (second read hits L1/L2).
+struct QInt8Args {
+    const void* x[3];
+    int8_t* codes[3];
+    float* scales[3];
+};
+
 template <int DT, bool VEC>
-__global__ void __launch_bounds__(kThreads) quant_int8_kernel(const void* x, int8_t* codes, float* scales, int64_t K, int64_t ldx,
-                                                              int64_t ldc, int div_mode) {
+__global__ void __launch_bounds__(kThreads) quant_int8_kernel(const QInt8Args qa, int64_t K, int64_t ldx, int64_t ldc, int div_mode) {
     __shared__ float sh[kThreads / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a projection behind this launch may prefetch its weights
+    asm volatile("griddepcontrol.wait;" ::: "memory");                // launched early itself: wait for the producer of x
     const int64_t row = blockIdx.x;
-    const char* xrow = reinterpret_cast<const char*>(x) + row * ldx * 2;
-    int8_t* crow = codes + row * ldc;
+    const char* xrow = reinterpret_cast<const char*>(qa.x[blockIdx.y]) + row * ldx * 2;
+    int8_t* crow = qa.codes[blockIdx.y] + row * ldc;
+    float* scales = qa.scales[blockIdx.y];
     float m = 0.f;
     if (VEC) {
         for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += kThreads * 8) {
@@ -337,6 +348,9 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
     __shared__ float s_amax;
     __shared__ int s_fail;
     __shared__ uint32_t s_token;
+    // a projection launched behind this kernel with programmatic dependent launch may start now and prefetch its
+    // weights; it waits (griddepcontrol.wait) for this grid to finish before it reads the codes
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int kv = a.K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = (int)blockIdx.x / a.cpt, cb = (int)blockIdx.x - t * a.cpt, G = a.cpt;
     const char* x = reinterpret_cast<const char*>(a.x[t]);
@@ -467,6 +481,115 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
     }
 }
 
+// Few rows (decode): a CLUSTER of 1 to 8 CTAs of 1024 threads per tensor does the whole job -- abs-max over the block,
+// then the codes -- with up to 8 vectors per thread kept in registers between the two (one read of the activations,
+// all loads in flight together).  The CTAs of a cluster exchange their maxima through distributed shared memory and
+// one cluster barrier; there is no grid rendezvous and no scratch, so the kernel can be launched with programmatic
+// dependent launch: it becomes resident while its predecessor drains, releases its own dependents at once (the
+// projection behind it starts prefetching weights) and waits for its input.
+constexpr int kSmallThreads = 1024;
+constexpr int kSmallKeep = 8;
+
+template <int DT>
+__global__ void __launch_bounds__(kSmallThreads, 1) actq_fp8_small_kernel(const ActqArgs a) {
+    __shared__ float sh[kSmallThreads / 32];
+    __shared__ float s_part[8];           // maxima of the cluster's CTAs (each CTA writes its slot in every CTA)
+    __shared__ float s_amax;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    cooperative_groups::cluster_group cl = cooperative_groups::this_cluster();
+    const int C = (int)cl.num_blocks(), cr = (int)cl.block_rank();
+    const int t = (int)blockIdx.x / C, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const char* x = reinterpret_cast<const char*>(a.x[t]);
+    uint8_t* codes = a.codes[t];
+    const int kv = a.K >> 3, nvec = a.M * kv;
+    const uint32_t inv_kv = 0xFFFFFFFFu / (uint32_t)kv + 1u;          // row of a flat vector index without a division
+    const bool after_bf16 = a.after_bf16 != 0, from_bf16 = a.from_bf16 != 0;
+    const bool keep = nvec <= kSmallKeep * kSmallThreads * C;
+    asm volatile("griddepcontrol.wait;" ::: "memory");                // the activations may come from the previous kernel
+    auto vec_ptr = [&](int idx) {
+        const int r = (int)__umulhi((uint32_t)idx, inv_kv), c = idx - r * kv;
+        return x + ((int64_t)r * a.ldx + (int64_t)c * 8) * 2;
+    };
+    auto vec_max = [&](const uint4& v, float m) {
+        if (DT == RWKVQ_F16 && after_bf16) {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                m = fmaxf(m, fmaxf(fabsf(bf16_round(f.x)), fabsf(bf16_round(f.y))));
+            }
+            return m;
+        } else if (DT == RWKVQ_F16) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const __half2 t2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+            return fmaxf(m, fmaxf(__low2float(t2), __high2float(t2)));
+        } else {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const __nv_bfloat162 t2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+            return fmaxf(m, fmaxf(__low2float(t2), __high2float(t2)));
+        }
+    };
+    // the cluster's threads take the vectors round-robin: thread (cr, tid) vectors first, first + step, ...
+    const int first = cr * kSmallThreads + threadIdx.x, step = C * kSmallThreads;
+    uint4 v[kSmallKeep];
+    float m = 0.f;
+#pragma unroll 1
+    for (int i0 = first; i0 < nvec; i0 += kSmallKeep * step) {
+#pragma unroll
+        for (int j = 0; j < kSmallKeep; ++j)
+            if (i0 + j * step < nvec) v[j] = *reinterpret_cast<const uint4*>(vec_ptr(i0 + j * step));
+#pragma unroll
+        for (int j = 0; j < kSmallKeep; ++j)
+            if (i0 + j * step < nvec) m = vec_max(v[j], m);
+    }
+    m = warp_max(m);
+    if (lane == 0) sh[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        const float b = warp_max(sh[lane]);
+        if (lane < C) *cl.map_shared_rank(&s_part[cr], lane) = b;      // this CTA's maximum into slot cr of CTA `lane`
+    }
+    cl.sync();                                                          // all slots written (and visible) in every CTA
+    if (threadIdx.x == 0) {
+        float b = s_part[0];
+        for (int i = 1; i < C; ++i) b = fmaxf(b, s_part[i]);
+        s_amax = b;
+        if (cr == 0) {
+            a.amax_out[t] = b;
+            if (a.scale_out[t]) *a.scale_out[t] = scale_fwd(b, 448.f, a.div_mode);
+        }
+    }
+    __syncthreads();
+    const float inv = scale_inv(448.f, fmaxf(s_amax, 1e-12f), a.div_mode);
+    auto vec_codes = [&](const uint4& vv, int idx) {
+        const uint32_t w[4] = {vv.x, vv.y, vv.z, vv.w};
+        uint32_t c[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float2 f = cvt2<DT>(w[q]);
+            if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+            c[q] = e4m3x2(f.x * inv, f.y * inv);
+        }
+        const int r = (int)__umulhi((uint32_t)idx, inv_kv), cc = idx - r * kv;
+        *reinterpret_cast<uint2*>(codes + (int64_t)r * a.ldc + (size_t)cc * 8) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+    };
+    if (keep) {
+#pragma unroll
+        for (int j = 0; j < kSmallKeep; ++j)
+            if (first + j * step < nvec) vec_codes(v[j], first + j * step);
+    } else {
+#pragma unroll 1
+        for (int i0 = first; i0 < nvec; i0 += kSmallKeep * step) {
+#pragma unroll
+            for (int j = 0; j < kSmallKeep; ++j)
+                if (i0 + j * step < nvec) v[j] = *reinterpret_cast<const uint4*>(vec_ptr(i0 + j * step));
+#pragma unroll
+            for (int j = 0; j < kSmallKeep; ++j)
+                if (i0 + j * step < nvec) vec_codes(v[j], i0 + j * step);
+        }
+    }
+}
+
 // A kernel whose only job is to let a bounded wait run out: one CTA waits for an mbarrier phase that nothing
 // completes (mode 0) or for a flag value that nothing stores (mode 1), gives up after `limit_ns`, records
 // RWKVQ_E_TIMEOUT in *status and returns normally -- the path every kernel of this library takes when a producer
@@ -579,20 +702,53 @@ int32_t rwkvq_prep_x_fp8(const void* x, int32_t x_dtype, int64_t M, int64_t K, i
     return rwkvq_actq_fp8(x, x_dtype, M, K, ldx, codes, ldc, amax_scratch, scale, RWKVQ_DIV_TORCH, 0u, stream);
 }
 
-int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes, int64_t ldc,
-                          float* scales, int32_t div_mode, void* stream) {
-    RWKVQ_REQUIRE(x && codes && scales, RWKVQ_E_BADARG, "prep_x_int8: null pointer");
-    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "prep_x_int8: x_dtype %d", x_dtype);
-    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "prep_x_int8: div_mode %d", div_mode);
-    RWKVQ_REQUIRE(M >= 0 && K >= 0 && ldx >= K && ldc >= K, RWKVQ_E_SHAPE, "prep_x_int8: M=%lld K=%lld", (long long)M, (long long)K);
+static int32_t launch_quant_int8(const QInt8Args& qa, int nt, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int64_t ldc,
+                                 int32_t div_mode, cudaStream_t st, const char* who) {
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
+    RWKVQ_REQUIRE(M >= 0 && K >= 0 && ldx >= K && ldc >= K, RWKVQ_E_SHAPE, "%s: M=%lld K=%lld", who, (long long)M, (long long)K);
+    bool vec = (K % 8 == 0) && (ldx % 8 == 0) && (ldc % 8 == 0);
+    for (int t = 0; t < nt; ++t) {
+        RWKVQ_REQUIRE(qa.x[t] && qa.codes[t] && qa.scales[t], RWKVQ_E_BADARG, "%s: null pointer", who);
+        vec = vec && aligned16(qa.x[t]) && ((uintptr_t)qa.codes[t] % 8 == 0);
+    }
     if (M == 0) return RWKVQ_OK;
-    cudaStream_t st = (cudaStream_t)stream;
-    const bool vec = (K % 8 == 0) && (ldx % 8 == 0) && aligned16(x) && (ldc % 8 == 0) && ((uintptr_t)codes % 8 == 0);
-#define RWKVQ_Q(DT, V) quant_int8_kernel<DT, V><<<(unsigned)M, kThreads, 0, st>>>(x, codes, scales, K, ldx, ldc, div_mode)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)M, (unsigned)nt);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    const int dm = div_mode;
+    cudaError_t e;
+#define RWKVQ_Q(DT, V) e = cudaLaunchKernelEx(&cfg, quant_int8_kernel<DT, V>, qa, K, ldx, ldc, dm)
     if (x_dtype == RWKVQ_F16) { if (vec) RWKVQ_Q(RWKVQ_F16, true); else RWKVQ_Q(RWKVQ_F16, false); }
     else                      { if (vec) RWKVQ_Q(RWKVQ_BF16, true); else RWKVQ_Q(RWKVQ_BF16, false); }
 #undef RWKVQ_Q
-    return check_launch("prep_x_int8");
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return check_launch(who);
+}
+
+int32_t rwkvq_prep_x_int8(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes, int64_t ldc,
+                          float* scales, int32_t div_mode, void* stream) {
+    QInt8Args qa{};
+    qa.x[0] = x; qa.codes[0] = codes; qa.scales[0] = scales;
+    return launch_quant_int8(qa, 1, x_dtype, M, K, ldx, ldc, div_mode, (cudaStream_t)stream, "prep_x_int8");
+}
+
+int32_t rwkvq_prep3_x_int8(const void* xr, const void* xk, const void* xv, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx,
+                           int8_t* codes_r, int8_t* codes_k, int8_t* codes_v, int64_t ldc, float* scales_r, float* scales_k,
+                           float* scales_v, int32_t div_mode, void* stream) {
+    QInt8Args qa{};
+    qa.x[0] = xr; qa.x[1] = xk; qa.x[2] = xv; qa.codes[0] = codes_r; qa.codes[1] = codes_k; qa.codes[2] = codes_v;
+    qa.scales[0] = scales_r; qa.scales[1] = scales_k; qa.scales[2] = scales_v;
+    return launch_quant_int8(qa, 3, x_dtype, M, K, ldx, ldc, div_mode, (cudaStream_t)stream, "prep3_x_int8");
 }
 
 int64_t rwkvq_actq_fp8_fused_scratch_bytes(void) { return (kFusedEpochWord + 32) * 4; }
@@ -618,6 +774,32 @@ static int32_t launch_actq_fused(ActqArgs a, int nt, int32_t x_dtype, int64_t M,
     a.slots = reinterpret_cast<float*>(scratch);
     a.flags = reinterpret_cast<uint32_t*>(scratch) + kFusedMaxCtas;
     a.wait_ns = wait_limit_ns();
+    if (M <= 64 && M * (K / 8) <= 32768 && K / 8 < 65536) {
+        // decode-sized block: a cluster of CTAs per tensor (about 4 vectors per thread), no grid rendezvous, programmatic
+        // dependent launch (the scratch is not touched)
+        int cluster = 1;
+        while (cluster < 8 && M * (K / 8) > (int64_t)cluster * 4 * kSmallThreads) cluster <<= 1;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(nt * cluster));
+        cfg.blockDim = dim3(kSmallThreads);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl() ? 2 : 1;
+        const cudaError_t e = x_dtype == RWKVQ_F16 ? cudaLaunchKernelEx(&cfg, actq_fp8_small_kernel<RWKVQ_F16>, a)
+                                                   : cudaLaunchKernelEx(&cfg, actq_fp8_small_kernel<RWKVQ_BF16>, a);
+        if (e != cudaSuccess) {
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+        }
+        return check_launch(who);
+    }
     void* args[] = {(void*)&a};
     const bool keep = K / 8 <= kFusedThreads && M <= 8 * (int64_t)a.cpt;
     const void* fn = x_dtype == RWKVQ_F16

@@ -115,9 +115,16 @@ using namespace rwkvq;
 
 extern "C" {
 
+// Few rows whose code tile fits shared memory go to the weight-streaming decode GEMV (gemv_w8a8.cu, activation codes
+// copied once per CTA); everything else to the any-M kernel above.
+static bool decode_route(int64_t M, int64_t K) { return M <= 32 && gemv_codes_fits((int)M, (int)K); }
+
 int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
                            int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                            int32_t div_mode, uint32_t flags, void* stream) {
+    if (decode_route(M, K))
+        return rwkvq_gemm_fp8_rkv(a_codes, nullptr, nullptr, lda, amax, amax_is_amax, w, nullptr, nullptr, ldw, w_scale, nullptr, nullptr,
+                                  out_f16, nullptr, nullptr, ldo, M, N, K, div_mode, flags, stream);
     W8Args a{};
     a.a_codes = a_codes; a.lda = lda; a.a_scale = amax; a.amax_is_amax = amax_is_amax;
     a.w[0] = w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
@@ -129,12 +136,87 @@ int32_t rwkvq_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax, i
 int32_t rwkvq_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
                             const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M,
                             int64_t N, int64_t K, uint32_t flags, void* stream) {
+    if (decode_route(M, K)) {
+        W8Args a{};
+        a.codes[0] = (const uint8_t*)a_codes; a.lda = lda; a.ascale[0] = a_scales;
+        a.w[0] = (const uint8_t*)w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16; a.acc[0] = acc_out; a.ldacc = ldacc;
+        a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = flags;
+        RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "gemm_int8: ldacc < N");
+        return gemv_codes_run(a, QT_INT8, (cudaStream_t)stream, "gemm_int8");
+    }
     W8Args a{};
     a.a_codes = (const uint8_t*)a_codes; a.lda = lda; a.a_scale = a_scales;
     a.w[0] = (const uint8_t*)w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16; a.acc[0] = acc_out; a.ldacc = ldacc;
     a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = flags;
     RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "gemm_int8: ldacc < N");
     return run_codes<QT_INT8>(a, (cudaStream_t)stream, "gemm_int8");
+}
+
+/* 1 when rwkvq_gemm_fp8 / rwkvq_gemm_int8 (and the _rkv forms) run M rows of K codes on the weight-streaming decode
+ * kernel, 0 when they fall to the any-M kernel. */
+int32_t rwkvq_gemm_decode_route(int64_t M, int64_t K) { return decode_route(M, K) ? 1 : 0; }
+
+/* r, k, v on codes in one launch (decode GEMV, M <= 32 and the code tile fits); otherwise three launches of the any-M
+ * kernel.  Passing only the first matrix (wk == NULL) runs a single projection. */
+int32_t rwkvq_gemm_fp8_rkv(const uint8_t* codes_r, const uint8_t* codes_k, const uint8_t* codes_v, int64_t lda, const float* amax3,
+                           int32_t amax_is_amax, const uint8_t* wr, const uint8_t* wk, const uint8_t* wv, int64_t ldw, const float* sr,
+                           const float* sk, const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N,
+                           int64_t K, int32_t div_mode, uint32_t flags, void* stream) {
+    RWKVQ_REQUIRE(amax3 != nullptr, RWKVQ_E_BADARG, "gemm_fp8_rkv: null amax");
+    const int nmat = wk ? 3 : 1;
+    if (!decode_route(M, K)) {
+        const uint8_t* c[3] = {codes_r, codes_k, codes_v};
+        const uint8_t* w[3] = {wr, wk, wv};
+        const float* s[3] = {sr, sk, sv};
+        void* o[3] = {out_r, out_k, out_v};
+        for (int i = 0; i < nmat; ++i) {
+            W8Args a{};
+            a.a_codes = c[i]; a.lda = lda; a.a_scale = amax3 + i; a.amax_is_amax = amax_is_amax;
+            a.w[0] = w[i]; a.ws[0] = s[i]; a.out[0] = (__half*)o[i];
+            a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = div_mode; a.flags = flags;
+            RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "gemm_fp8_rkv: div_mode %d", div_mode);
+            const int32_t rc = run_codes<QT_FP8>(a, (cudaStream_t)stream, "gemm_fp8_rkv");
+            if (rc != RWKVQ_OK) return rc;
+        }
+        return RWKVQ_OK;
+    }
+    W8Args a{};
+    a.codes[0] = codes_r; a.codes[1] = codes_k; a.codes[2] = codes_v; a.lda = lda;
+    a.ascale[0] = amax3; a.ascale[1] = amax3 + 1; a.ascale[2] = amax3 + 2; a.amax_is_amax = amax_is_amax;
+    a.w[0] = wr; a.w[1] = wk; a.w[2] = wv; a.ws[0] = sr; a.ws[1] = sk; a.ws[2] = sv;
+    a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
+    a.nmat = nmat; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = div_mode; a.flags = flags;
+    return gemv_codes_run(a, QT_FP8, (cudaStream_t)stream, "gemm_fp8_rkv");
+}
+
+int32_t rwkvq_gemm_int8_rkv(const int8_t* codes_r, const int8_t* codes_k, const int8_t* codes_v, int64_t lda, const float* scales_r,
+                            const float* scales_k, const float* scales_v, const int8_t* wr, const int8_t* wk, const int8_t* wv,
+                            int64_t ldw, const float* sr, const float* sk, const float* sv, void* out_r, void* out_k, void* out_v,
+                            int64_t ldo, int64_t M, int64_t N, int64_t K, uint32_t flags, void* stream) {
+    const bool shared = (flags & RWKVQ_FLAG_INT8_SHARED_WSCALE) != 0;
+    const float* s[3] = {sr, shared ? sr : sk, shared ? sr : sv};
+    if (!decode_route(M, K)) {
+        const int8_t* c[3] = {codes_r, codes_k, codes_v};
+        const float* xs[3] = {scales_r, scales_k, scales_v};
+        const int8_t* w[3] = {wr, wk, wv};
+        void* o[3] = {out_r, out_k, out_v};
+        for (int i = 0; i < 3; ++i) {
+            W8Args a{};
+            a.a_codes = (const uint8_t*)c[i]; a.lda = lda; a.a_scale = xs[i];
+            a.w[0] = (const uint8_t*)w[i]; a.ws[0] = s[i]; a.out[0] = (__half*)o[i];
+            a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = flags;
+            const int32_t rc = run_codes<QT_INT8>(a, (cudaStream_t)stream, "gemm_int8_rkv");
+            if (rc != RWKVQ_OK) return rc;
+        }
+        return RWKVQ_OK;
+    }
+    W8Args a{};
+    a.codes[0] = (const uint8_t*)codes_r; a.codes[1] = (const uint8_t*)codes_k; a.codes[2] = (const uint8_t*)codes_v; a.lda = lda;
+    a.ascale[0] = scales_r; a.ascale[1] = scales_k; a.ascale[2] = scales_v;
+    a.w[0] = (const uint8_t*)wr; a.w[1] = (const uint8_t*)wk; a.w[2] = (const uint8_t*)wv; a.ws[0] = s[0]; a.ws[1] = s[1]; a.ws[2] = s[2];
+    a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
+    a.nmat = 3; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldw = ldw; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = flags;
+    return gemv_codes_run(a, QT_INT8, (cudaStream_t)stream, "gemm_int8_rkv");
 }
 
 }  // extern "C"

@@ -69,7 +69,9 @@ __device__ __forceinline__ void issue_slots(uint32_t dst, const uint8_t* src0, c
 // tokens the B operand: xb[i] points at this lane's 16 k-values of token min(8i+g, M-1) for unit 0.  FP8: a lane's
 // 16 bytes per row are widened to eight f16 pairs and feed four m16n8k16 together with the other row's; the B
 // registers are consecutive pairs of two 128-bit loads.  INT8: two m16n8k32 per unit, B from one 128-bit load.
-template <int QT, int NT, int D, typename T>
+// FP8 on pre-quantized codes (WIDE = false): the tile holds the e4m3 codes as they come (1 byte each), a lane's 16 codes of
+// a unit arrive with one 128-bit load and are widened here (8 conversions per token tile and unit).
+template <int QT, bool WIDE, int NT, int D, typename T>
 __device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* const (&xb)[NT], T (&c)[NT][4], T (&c2)[NT][4]) {
 #pragma unroll
     for (int j = 0; j < D; ++j) {
@@ -80,8 +82,15 @@ __device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* con
             const uint4 h01 = e4m3x8_to_f16x8(make_uint2(wh.x, wh.y)), h23 = e4m3x8_to_f16x8(make_uint2(wh.z, wh.w));
 #pragma unroll
             for (int i = 0; i < NT; ++i) {
-                const uint4 b0 = *reinterpret_cast<const uint4*>(xb[i] + j * 128);
-                const uint4 b1 = *reinterpret_cast<const uint4*>(xb[i] + j * 128 + 16);
+                uint4 b0, b1;
+                if constexpr (WIDE) {
+                    b0 = *reinterpret_cast<const uint4*>(xb[i] + j * 128);
+                    b1 = *reinterpret_cast<const uint4*>(xb[i] + j * 128 + 16);
+                } else {
+                    const uint4 bc = *reinterpret_cast<const uint4*>(xb[i] + j * 64);
+                    b0 = e4m3x8_to_f16x8(make_uint2(bc.x, bc.y));
+                    b1 = e4m3x8_to_f16x8(make_uint2(bc.z, bc.w));
+                }
                 mma_f16(c[i], g01.x, h01.x, g01.y, h01.y, b0.x, b0.y);
                 mma_f16(c2[i], g01.z, h01.z, g01.w, h01.w, b0.z, b0.w);
                 mma_f16(c[i], g23.x, h23.x, g23.y, h23.y, b1.x, b1.y);
@@ -133,11 +142,14 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
 // MMA, is a single pass of dependent scalar code and shows up in full in a 5-15 us launch: the tile split and all
 // divisions are done on the host (W8Args::tq, trem, lgR), and whatever does not need the activations is computed
 // before griddepcontrol.wait.
-template <int QT, int DT, int NT, int S>
+// PRE: the activations arrive as codes (a.codes / a.ascale, quantized once by an earlier launch) and the prologue is
+// one bulk copy per row into the tile -- no arithmetic, M*K bytes per CTA; otherwise the prologue quantizes x itself.
+template <int QT, int DT, int NT, int S, bool PRE>
 __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
     constexpr int D = kGemvD;
-    constexpr int AB = QT == QT_FP8 ? 2 : 1;          // bytes per activation in the shared-memory tile
+    constexpr bool WIDE = !PRE;
+    constexpr int AB = (QT == QT_FP8 && WIDE) ? 2 : 1;          // bytes per activation in the shared-memory tile
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: red[kWarps][NT*4][32] | xs[32] | sh[8] | xbar + pad (96 B) | ring[kWarps][S][D][2][32 lanes] x 16 B | xq[M][pitch] + 512 B
     T* red = reinterpret_cast<T*>(smem);
@@ -211,7 +223,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     for (int i = 0; i < NT; ++i) xb0[i] = xq + min(i * 8 + g, a.M - 1) * a.pitch + kbeg * AB;
     const float wscale = a.ws[mat][0];       // weights and their scale are never written by a kernel
 
-    if (QT == QT_FP8 && threadIdx.x == 0) {
+    if ((QT == QT_FP8 || PRE) && threadIdx.x == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(xbar)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -221,8 +233,28 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     w8_mark(a, 2);
 
     float out_scale = 0.f;   // FP8: amax/448 (the weight scale joins it in store_tile)
-    if constexpr (QT == QT_FP8) {
-        const float amax = quantize_fp8_to_smem<DT, true>(a, mat, xq, sh, xbar);
+    if constexpr (PRE) {
+        if (threadIdx.x == 0) {
+            const uint32_t b = (uint32_t)__cvta_generic_to_shared(xbar);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K)) : "memory");
+#pragma unroll 1
+            for (int r = 0; r < a.M; ++r)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(a.codes[mat] + (int64_t)r * a.lda),
+                               "r"((uint32_t)a.K), "r"(b) : "memory");
+        }
+        if constexpr (QT == QT_FP8) {
+            const float am = a.ascale[mat][0];
+            out_scale = a.amax_is_amax ? div_mode_f32(fmaxf(am, 1e-12f), 448.f, a.div_mode) : am;
+        } else {
+            if ((int)threadIdx.x < a.M) xs[threadIdx.x] = a.ascale[mat][threadIdx.x];
+        }
+        if (!w8_staged_or_report(xbar, a.status, a.wait_ns)) {     // reported: drain the weight ring and stop
+            cp_async_wait<0>();
+            return;
+        }
+    } else if constexpr (QT == QT_FP8) {
+        const float amax = quantize_fp8_to_smem<DT, WIDE>(a, mat, xq, sh, xbar);
         if (amax < 0.f) {          // the staging copy timed out (reported): drain the weight ring and stop
             cp_async_wait<0>();
             return;
@@ -248,7 +280,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
             for (int ch = 0; ch < nch; ++ch) {
                 issue();                       // keep S-1 chunks in flight
                 cp_async_wait<S - 1>();        // this lane's copies of the current chunk have landed
-                chunk_body<QT, NT, D>(my_ring + stage * (D * 1024), xb, c, c2);
+                chunk_body<QT, WIDE, NT, D>(my_ring + stage * (D * 1024), xb, c, c2);
 #pragma unroll
                 for (int i = 0; i < NT; ++i) xb[i] += D * 64 * AB;
                 if (++stage == S) stage = 0;
@@ -292,9 +324,9 @@ static size_t smem_bytes(int NT, int M, int pitch, int S) {
 
 constexpr size_t kFusedSmemMax = 224 * 1024;    // of the 227 KB a CTA may opt in to
 
-template <int QT, int DT, int NT, int S>
+template <int QT, int DT, int NT, int S, bool PRE>
 static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
-    auto kern = gemv_w8a8_kernel<QT, DT, NT, S>;
+    auto kern = gemv_w8a8_kernel<QT, DT, NT, S, PRE>;
     // per instantiation and device: opt in to large dynamic shared memory and ask how many CTAs fit on an SM
     static thread_local int cfg_dev = -1;
     static thread_local size_t cfg_smem = ~size_t(0);
@@ -345,25 +377,54 @@ static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
 
 constexpr size_t kTwoPerSm = 110 * 1024;     // shared memory per CTA that still lets two CTAs share an SM
 
-// deepest ring that still leaves room for two CTAs per SM; a big activation tile gets a shallow ring and one CTA
-template <int QT, int DT, int NT>
+// Ring depth: the deepest ring (5, 4, 3 stages) that leaves room for two CTAs per SM; failing that, one CTA per SM with
+// the deepest ring that fits beside the activation tile (long rows, many tokens) -- one CTA with a deep ring measured
+// faster than two CTAs with two stages.
+template <int QT, int DT, int NT, bool PRE>
 static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
     const size_t s5 = smem_bytes(NT, a.M, a.pitch, 5), s4 = smem_bytes(NT, a.M, a.pitch, 4), s3 = smem_bytes(NT, a.M, a.pitch, 3),
                  s2 = smem_bytes(NT, a.M, a.pitch, 2);
-    if (s5 <= kTwoPerSm) return launch_one<QT, DT, NT, 5>(a, s5, st);
-    if (s4 <= kTwoPerSm) return launch_one<QT, DT, NT, 4>(a, s4, st);
-    if (s3 <= kTwoPerSm) return launch_one<QT, DT, NT, 3>(a, s3, st);
-    // long rows (K = 16384): one CTA per SM with the deep ring measured faster than two CTAs with two stages
-    RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the fused kernel's shared memory", a.M, a.K);
-    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, NT, 5>(a, s5, st);
-    return launch_one<QT, DT, NT, 2>(a, s2, st);
+    if (s5 <= kTwoPerSm) return launch_one<QT, DT, NT, 5, PRE>(a, s5, st);
+    if (s4 <= kTwoPerSm) return launch_one<QT, DT, NT, 4, PRE>(a, s4, st);
+    if (s3 <= kTwoPerSm) return launch_one<QT, DT, NT, 3, PRE>(a, s3, st);
+    RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the kernel's shared memory", a.M, a.K);
+    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, NT, 5, PRE>(a, s5, st);
+    if (s4 <= kFusedSmemMax) return launch_one<QT, DT, NT, 4, PRE>(a, s4, st);
+    if (s3 <= kFusedSmemMax) return launch_one<QT, DT, NT, 3, PRE>(a, s3, st);
+    return launch_one<QT, DT, NT, 2, PRE>(a, s2, st);
 }
 
-template <int QT, int DT>
+template <int QT, int DT, bool PRE>
 static int32_t dispatch_mt(const W8Args& a, cudaStream_t st) {
-    if (a.M <= 8) return dispatch_s<QT, DT, 1>(a, st);
-    if (a.M <= 16) return dispatch_s<QT, DT, 2>(a, st);
-    return dispatch_s<QT, DT, 4>(a, st);
+    if (a.M <= 8) return dispatch_s<QT, DT, 1, PRE>(a, st);
+    if (a.M <= 16) return dispatch_s<QT, DT, 2, PRE>(a, st);
+    return dispatch_s<QT, DT, 4, PRE>(a, st);
+}
+
+static int pitch_codes(int K) { return ((K + 127) / 128) * 128 + 64; }     // 1 byte per code
+static int pitch_wide(int K) { return ((2 * K + 127) / 128) * 128 + 16; }  // f16 values of the e4m3 codes
+
+bool gemv_codes_fits(int M, int K) {
+    const int NT = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    return M > 0 && M <= 32 && K % 16 == 0 && smem_bytes(NT, M, pitch_codes(K), 2) <= kFusedSmemMax;
+}
+
+int32_t gemv_codes_run(W8Args a, int qt, cudaStream_t st, const char* who) {
+    RWKVQ_REQUIRE(a.M >= 0 && a.N >= 0 && a.K >= 0, RWKVQ_E_SHAPE, "%s: negative size", who);
+    RWKVQ_REQUIRE(a.K % 16 == 0, RWKVQ_E_SHAPE, "%s: K=%d must be a multiple of 16", who, a.K);
+    RWKVQ_REQUIRE(a.ldw >= a.K && a.ldw % 16 == 0, RWKVQ_E_ALIGN, "%s: ldw=%lld must be >= K and a multiple of 16", who, (long long)a.ldw);
+    RWKVQ_REQUIRE(a.lda >= a.K && a.lda % 16 == 0, RWKVQ_E_ALIGN, "%s: lda=%lld must be >= K and a multiple of 16", who, (long long)a.lda);
+    RWKVQ_REQUIRE(a.ldo >= a.N, RWKVQ_E_SHAPE, "%s: ldo=%lld < N", who, (long long)a.ldo);
+    RWKVQ_REQUIRE(a.div_mode == RWKVQ_DIV_IEEE || a.div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, a.div_mode);
+    for (int i = 0; i < a.nmat; ++i) {
+        RWKVQ_REQUIRE(a.w[i] && a.ws[i] && a.out[i] && a.codes[i] && a.ascale[i], RWKVQ_E_BADARG, "%s: null pointer (matrix %d)", who, i);
+        RWKVQ_REQUIRE(aligned16(a.w[i]) && aligned16(a.codes[i]), RWKVQ_E_ALIGN, "%s: weight / code pointer not 16-byte aligned", who);
+    }
+    if (a.M == 0 || a.N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(gemv_codes_fits(a.M, a.K), RWKVQ_E_SHAPE, "%s: M=%d K=%d does not fit the decode kernel (M <= 32, code tile in shared memory)", who, a.M, a.K);
+    RWKVQ_REQUIRE((int64_t)a.nmat * ((a.N + 15) / 16) < (int64_t(1) << 27), RWKVQ_E_SHAPE, "%s: N too large", who);
+    a.pitch = pitch_codes(a.K);
+    return qt == QT_FP8 ? dispatch_mt<QT_FP8, RWKVQ_BF16, true>(a, st) : dispatch_mt<QT_INT8, RWKVQ_BF16, true>(a, st);
 }
 
 template <int QT>
@@ -382,11 +443,12 @@ static int32_t run_fused(W8Args a, int x_dtype, cudaStream_t st, const char* who
     }
     if (a.M == 0 || a.N == 0) return RWKVQ_OK;
     RWKVQ_REQUIRE(a.K > 0, RWKVQ_E_SHAPE, "%s: K=0", who);
-    // shared-memory row pitch of the activation tile: int8 codes (1 B) or f16 values of the e4m3 codes (2 B);
-    // the odd 64 / 16 bytes keep the fragment loads of different rows on different banks
-    a.pitch = QT == QT_FP8 ? ((2 * a.K + 127) / 128) * 128 + 16 : ((a.K + 127) / 128) * 128 + 64;
+    // shared-memory row pitch of the activation tile: one byte per code (INT8, or FP8 with the narrow tile: dispatch_w)
+    // or the f16 values of the e4m3 codes (2 B); the odd 64 / 16 bytes keep the fragment loads of different rows on
+    // different banks
+    a.pitch = QT == QT_FP8 ? pitch_wide(a.K) : pitch_codes(a.K);
     RWKVQ_REQUIRE((int64_t)a.nmat * ((a.N + 15) / 16) < (int64_t(1) << 27), RWKVQ_E_SHAPE, "%s: N too large", who);
-    return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16>(a, st) : dispatch_mt<QT, RWKVQ_BF16>(a, st);
+    return x_dtype == RWKVQ_F16 ? dispatch_mt<QT, RWKVQ_F16, false>(a, st) : dispatch_mt<QT, RWKVQ_BF16, false>(a, st);
 }
 
 }  // namespace rwkvq

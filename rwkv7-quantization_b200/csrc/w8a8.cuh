@@ -23,8 +23,10 @@ struct W8Args {
     const float* ws[3];       // weight scale (one fp32 each)
     __half* out[3];
     int32_t* acc[3];          // INT8: optional raw accumulators
-    const uint8_t* a_codes;   // pre-quantized mode
+    const uint8_t* a_codes;   // pre-quantized mode (any-M mma.sync kernel)
     const float* a_scale;     // pre-quantized: FP8 amax-or-scale [1], INT8 per-row scales [M]
+    const uint8_t* codes[3];  // pre-quantized mode of the decode GEMV: activation codes [M, lda] per matrix
+    const float* ascale[3];   //   and their scales (FP8: amax-or-scale [1]; INT8: per-row scales [M])
     int64_t ldx, ldw, ldo, ldacc, lda;
     int M, N, K, nmat;
     int div_mode, amax_is_amax;
@@ -188,18 +190,53 @@ __device__ __forceinline__ bool w8_staged_or_report(uint64_t* bar, int* status, 
     return true;
 }
 
+// The activation block as a flat list of 8-element vectors (M * K/8 of them): thread t takes vectors t, t + kThr, ...
+// in batches of U, all U loads of a batch issued before the first use.  The prologue loops are bound by load latency
+// (shared memory ~30 cycles, L2 ~700), not by arithmetic: with one load in flight a CTA of 256 threads needs
+// 20 dependent round trips for 16 rows of 2560, with U = 4 or 8 it needs 3 to 5.
+// (row, vector-in-row) of a flat index without a division: r = floor(idx * ceil(2^32 / kv) / 2^32), exact for
+// idx < 65536 and kv < 65536.
+template <int U, typename Load, typename Use>
+__device__ __forceinline__ void vec_batches(int nvec, int kv, uint32_t inv_kv, Load load, Use use) {
+#pragma unroll 1
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += U * kThr) {
+        uint4 v[U];
+        int r[U], c[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int idx = i0 + j * kThr;
+            r[j] = (int)__umulhi((uint32_t)idx, inv_kv);
+            c[j] = idx - r[j] * kv;
+            if (idx < nvec) v[j] = load(r[j], c[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+            if (i0 + j * kThr < nvec) use(v[j], r[j], c[j]);
+    }
+}
+
+// 128-bit load of activations served from L2 (they were written by an earlier kernel that may still have been running
+// when this CTA started under programmatic dependent launch, so a line this SM's L1 kept from before is not trusted)
+__device__ __forceinline__ uint4 ldg_l2_16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+}
+
 // Returns max(amax, 1e-12), or a negative value if the staging copy timed out (the CTA must then return).
+// The tile holds the codes as f16 values (2 bytes each, no conversion in the K loop).
 template <int DT, bool WIDE>
 __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh, uint64_t* bar) {
-    static_assert(WIDE, "the tile holds f16 values");
     const char* x = reinterpret_cast<const char*>(a.x[mat]);
     const float* awq = a.awq[mat];
     const int kv = a.K >> 3;                  // 8-element vectors per row
     const bool after = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
-    if (a.M * kv <= 2 * kThr) {
+    static_assert(WIDE, "the fused prologue fills the f16 tile; e4m3 tiles are filled from pre-quantized codes");
+    const int nvec = a.M * kv;
+    if (nvec <= 2 * kThr) {
         // one or two vectors per thread (M = 1 at K <= 4096): plain loads kept in registers are a little quicker
         // than the staging copy
-        const int i0 = threadIdx.x, i1 = threadIdx.x + kThr, nvec = a.M * kv;
+        const int i0 = threadIdx.x, i1 = threadIdx.x + kThr;
         int r0 = 0, r1 = 0;
         if (a.M > 1) { r0 = i0 / kv; r1 = i1 / kv; }
         const int k0 = (i0 - r0 * kv) << 3, k1 = (i1 - r1 * kv) << 3;
@@ -217,39 +254,36 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
         if (i1 < nvec) *reinterpret_cast<uint4*>(xq + (size_t)r1 * a.pitch + k1 * 2) = e4m3x8_to_f16x8(fp8_vec_codes<DT>(v1, awq, k1, a.div_mode, inv));
         return amax;
     }
-    if (threadIdx.x == 0) {
-        const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K * 2)) : "memory");
-#pragma unroll 1
-        for (int r = 0; r < a.M; ++r)
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(x + (int64_t)r * a.ldx * 2),
-                           "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
-    }
-    if (!w8_staged_or_report(bar, a.status, a.wait_ns)) return -1.f;
+    const uint32_t inv_kv = 0xFFFFFFFFu / (uint32_t)kv + 1u;
+    const int64_t ldx2 = a.ldx * 2;
     float m = 0.f;
+    {
+        // raw rows into the tile by bulk copies (one read of the activations), abs-max and in-place conversion from there
+        if (threadIdx.x == 0) {
+            const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K * 2)) : "memory");
 #pragma unroll 1
-    for (int r = 0; r < a.M; ++r) {
-        const char* src = reinterpret_cast<const char*>(xq + (size_t)r * a.pitch);
-#pragma unroll 1
-        for (int i = threadIdx.x; i < kv; i += kThr)
-            fp8_vec_amax<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, after, m);
-    }
-    w8_mark(a, 5);
-    const float amax = fmaxf(cta_max(m, sh), 1e-12f);
-    w8_mark(a, 6);
-    const float inv = div_mode_f32(448.f, amax, a.div_mode);
-#pragma unroll 1
-    for (int r = 0; r < a.M; ++r) {
-        uint8_t* qr = xq + (size_t)r * a.pitch;
-        const char* src = reinterpret_cast<const char*>(qr);
-#pragma unroll 1
-        for (int i = threadIdx.x; i < kv; i += kThr) {
-            const uint2 c = fp8_vec_codes<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, inv);
-            *reinterpret_cast<uint4*>(qr + (size_t)i * 16) = e4m3x8_to_f16x8(c);      // in place: same thread, same 16 bytes
+            for (int r = 0; r < a.M; ++r)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(x + (int64_t)r * ldx2),
+                               "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
+        if (!w8_staged_or_report(bar, a.status, a.wait_ns)) return -1.f;
+        vec_batches<4>(nvec, kv, inv_kv,
+                       [&](int r, int c) { return *reinterpret_cast<const uint4*>(xq + (size_t)r * a.pitch + (size_t)c * 16); },
+                       [&](const uint4& v, int, int c) { fp8_vec_amax<DT>(v, awq, c << 3, a.div_mode, after, m); });
+        w8_mark(a, 5);
+        const float amax = fmaxf(cta_max(m, sh), 1e-12f);
+        w8_mark(a, 6);
+        const float inv = div_mode_f32(448.f, amax, a.div_mode);
+        vec_batches<4>(nvec, kv, inv_kv,
+                       [&](int r, int c) { return *reinterpret_cast<const uint4*>(xq + (size_t)r * a.pitch + (size_t)c * 16); },
+                       [&](const uint4& v, int r, int c) {          // in place: same thread, same 16 bytes
+                           *reinterpret_cast<uint4*>(xq + (size_t)r * a.pitch + (size_t)c * 16) =
+                               e4m3x8_to_f16x8(fp8_vec_codes<DT>(v, awq, c << 3, a.div_mode, inv));
+                       });
+        return amax;
     }
-    return amax;
 }
 
 // ---- fused prologue, INT8: per-row amax / codes; row scales amax/127 into xs[].
@@ -316,16 +350,43 @@ __device__ void quantize_int8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
         }
         return;
     }
+    // more rows: one warp per row, two passes with 8 loads in flight per lane.  (Calls with many rows are better served
+    // by quantizing once, rwkvq_prep_x_int8, and running the projection on the codes: rwkvq_gemm_int8.)
+    const int kvl = a.K >> 3;                              // vectors per row
+#pragma unroll 1
     for (int r = warp; r < a.M; r += kWarps) {
         const char* xr = x + (int64_t)r * a.ldx * 2;
+        uint8_t* qr = xq + (size_t)r * a.pitch;
         float m = 0.f;
-        for (int k = lane * 8; k < a.K; k += 256) m = int8_vec_amax<DT>(*reinterpret_cast<const uint4*>(xr + k * 2), m);
+#pragma unroll 1
+        for (int i0 = lane; i0 < kvl; i0 += 8 * 32) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + 32 * j < kvl) v[j] = ldg_l2_16(xr + (size_t)(i0 + 32 * j) * 16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + 32 * j < kvl) m = int8_vec_amax<DT>(v[j], m);
+        }
         m = fmaxf(warp_max(m), 1e-12f);
         const float s = div_mode_f32(127.f, m, a.div_mode);
         if (lane == 0) xs[r] = div_mode_f32(m, 127.f, a.div_mode);
-        for (int k = lane * 8; k < a.K; k += 256)
-            *reinterpret_cast<uint2*>(xq + (size_t)r * a.pitch + k) = int8_vec_codes<DT>(*reinterpret_cast<const uint4*>(xr + k * 2), s);
+#pragma unroll 1
+        for (int i0 = lane; i0 < kvl; i0 += 8 * 32) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + 32 * j < kvl) v[j] = ldg_l2_16(xr + (size_t)(i0 + 32 * j) * 16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + 32 * j < kvl) *reinterpret_cast<uint2*>(qr + (size_t)(i0 + 32 * j) * 8) = int8_vec_codes<DT>(v[j], s);
+        }
     }
 }
+
+// The decode GEMV on pre-quantized codes (gemv_w8a8.cu): a.codes / a.ascale / a.w / a.ws / a.out filled for a.nmat
+// matrices, M <= 32.  Returns RWKVQ_E_SHAPE without launching when the code tile does not fit shared memory.
+bool gemv_codes_fits(int M, int K);
+int32_t gemv_codes_run(W8Args a, int qt, cudaStream_t st, const char* who);
 
 }  // namespace rwkvq

@@ -11,9 +11,14 @@ CUDA stream without host synchronisation -- the conventions of the reference wra
 (fused_fp8_gemm.py:55-79, 645-679, 785-818, 944-1098).
 
 Routing by M = rows of the flattened activation:
-    M <= 32     ONE fused launch of the weight-streaming GEMV (activation quantization in its prologue, weights
-                streamed once from HBM through per-warp cp.async rings into mma.sync fragments) -- the decode path;
-                measured faster than the route below up to 32 rows
+    M <= 8      ONE fused launch of the weight-streaming GEMV (activation quantization in its prologue, weights
+                streamed once from HBM through per-warp cp.async rings into mma.sync fragments) -- the decode path
+    9 .. 32     (and from 3 rows on when K is long) the same weight-streaming kernel on PRE-QUANTIZED codes: one small
+                quantization launch (r, k, v together; a cluster of CTAs per tensor, launched with programmatic
+                dependent launch), then every CTA copies the M*K bytes of codes instead of re-quantizing the whole
+                block -- with many rows the per-CTA quantization (bound by the SMs' conversion throughput) costs more
+                than the weight stream it precedes.  RWKVQ_CODES_M_MIN moves the boundary; shapes whose code tile
+                does not fit shared memory fall to the routes around
     larger M    activation-quantization kernel, then the tcgen05 GEMM on the codes: tokens as the 128-row operand,
                 128 x 256 tiles (narrower while there are fewer tiles than SMs); only a long K against few weight rows
                 (FFN value) with at most 48 tokens, or a call whose activations do not fit the GEMV's shared memory,
@@ -41,6 +46,19 @@ _TC_CACHE_MAX = 100 * 1024        # shared memory for the activations (2 B) and 
 ROUTE = os.environ.get("RWKVQ_ROUTE", "auto").lower()   # auto | tc | mma
 GEMV_AUTO_M_MAX = 32
 _ACTQ_FUSED = os.environ.get("RWKVQ_ACTQ", "fused") == "fused"   # one cooperative launch; else memset + two kernels
+CODES_M_MIN = int(os.environ.get("RWKVQ_CODES_M_MIN", "9"))      # rows from which the decode GEMV runs on pre-quantized codes
+CODES_MK_MIN = 49152       # ... and already from 3 rows when the block is this large (long rows: K = 16384); measured
+_decode_route_cache: dict = {}
+
+
+def _codes_gemv_fits(m: int, k: int) -> bool:
+    """The decode GEMV on pre-quantized codes: CODES_M_MIN..32 rows whose 1-byte code tile fits shared memory."""
+    if not (m >= CODES_M_MIN or (m >= 3 and m * k >= CODES_MK_MIN and CODES_M_MIN <= GEMV_M_MAX)) or m > GEMV_M_MAX or ROUTE != "auto" or k % 16:
+        return False
+    fits = _decode_route_cache.get((m, k))
+    if fits is None:
+        fits = _decode_route_cache[(m, k)] = bool(abi.lib().rwkvq_gemm_decode_route(m, k))
+    return fits
 
 
 # --------------------------------------------------------------------------- helpers
@@ -227,6 +245,43 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     return out
 
 
+def _fp8_codes_gemv(x2, w, w_ts):
+    """9..32 rows: quantize once (one cooperative launch), then the weight-streaming decode kernel on the codes."""
+    m, k = x2.shape
+    n = w.shape[0]
+    dev = x2.device
+    codes = torch.empty((m, k), dtype=torch.uint8, device=dev)
+    amax = torch.empty(1, dtype=torch.float32, device=dev)
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    st = abi.stream_ptr()
+    _actq_fp8(x2, codes, amax, None, abi.DEFAULT_DIV, abi.FLAG_QUANT_FROM_BF16, st)
+    abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
+             out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, _wscale_flag(w_ts, n), st)
+    abi.after_call()
+    return out
+
+
+def _fp8_codes_gemv_rkv(xs, ws_, scales):
+    """r, k, v with 9..32 rows: ONE quantization launch for the three inputs, ONE weight-streaming launch on the codes."""
+    m, k = xs[0].shape
+    n = ws_[0].shape[0]
+    dev = xs[0].device
+    codes = torch.empty((3, m, k), dtype=torch.uint8, device=dev)
+    amax = torch.empty(3, dtype=torch.float32, device=dev)
+    outs = torch.empty((3, m, n), dtype=torch.float16, device=dev)
+    st = abi.stream_ptr()
+    scratch = abi.actq_scratch(dev)
+    abi.call("rwkvq_actq_fp8_fused3", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]), m, k, k,
+             codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, amax.data_ptr(), scratch.data_ptr(),
+             scratch.numel() * 4, None, abi.DEFAULT_DIV, abi.FLAG_QUANT_FROM_BF16, st)
+    abi.call("rwkvq_gemm_fp8_rkv", codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, amax.data_ptr(), 1,
+             ws_[0].data_ptr(), ws_[1].data_ptr(), ws_[2].data_ptr(), ws_[0].stride(0), scales[0].data_ptr(),
+             scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
+             m, n, k, abi.DEFAULT_DIV, _wscale_flag(scales[0], n), st)
+    abi.after_call()
+    return [outs[0], outs[1], outs[2]]
+
+
 def _fp8_codes_gemm_rkv(xs, ws_, scales):
     """r, k, v above the decode kernel's range: ONE activation-quantization launch for the three inputs and ONE
     tensor-core GEMM launch for the three projections (the reference: prep3_x + fused_rkv_fp8_kernel)."""
@@ -268,7 +323,9 @@ def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float1
     if m == 1:
         return linear_fp8_m1_fused(x, {"weight": w, "tensor_scale": w_ts}, out_dtype)
     x2 = _rows16(x)
-    if _tc_fused_fits(m, k) or _gemv_fits(m, k):
+    if _codes_gemv_fits(m, k) and _ACTQ_FUSED and k % 8 == 0:
+        out = _fp8_codes_gemv(x2, _u8(w), w_ts)
+    elif _tc_fused_fits(m, k) or _gemv_fits(m, k):
         out = _fp8_gemv(x2, _u8(w), w_ts, None, 0)
     else:
         out = _fp8_codes_gemm(x2, _u8(w), w_ts, abi.FLAG_QUANT_FROM_BF16)
@@ -290,7 +347,9 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     same_ld = len({w.stride(0) for w in ws_}) == 1 and all(w.shape == ws_[0].shape for w in ws_) and len(wflags) == 1
     wflag = next(iter(wflags)) if len(wflags) == 1 else 0
     f32 = lambda a: None if a is None else a.to(device=dev, dtype=torch.float32).contiguous()
-    if _tc_fused_fits(m, k, 3) and same_ld:
+    if (_codes_gemv_fits(m, k) and _ACTQ_FUSED and same_ld and awq_r is None and awq_k is None and k % 8 == 0):
+        outs = _fp8_codes_gemv_rkv([t.contiguous() for t in xs], ws_, [i["tensor_scale"] for i in (wr_info, wk_info, wv_info)])
+    elif _tc_fused_fits(m, k, 3) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
         awq_r, awq_k = f32(awq_r), f32(awq_k)
@@ -331,7 +390,16 @@ def _int8_any(x2, w, w_scale, acc_out=None):
     n = w.shape[0]
     out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
     st = abi.stream_ptr()
-    if _tc_fused_fits(m, k):
+    if _codes_gemv_fits(m, k):
+        # 9..32 rows: quantize the rows once, then the weight-streaming decode kernel on the codes
+        codes = torch.empty((m, k), dtype=torch.int8, device=x2.device)
+        xs = torch.empty(m, dtype=torch.float32, device=x2.device)
+        abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
+                 codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
+        abi.call("rwkvq_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
+                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, st)
+        abi.after_call()
+    elif _tc_fused_fits(m, k):
         ws = abi.workspace(m, n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
                  out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0,
@@ -375,7 +443,23 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
     n = ws[0].shape[0]
     scales = [wr_info["tensor_scale"]] * 3 if compat_shared_scale else [i["tensor_scale"] for i in infos]
     same_ld = len({w.stride(0) for w in ws}) == 1 and all(w.shape == ws[0].shape for w in ws)
-    if _tc_fused_fits(m, k, 3) and same_ld:
+    if _codes_gemv_fits(m, k) and same_ld:
+        dev = xs[0].device
+        st = abi.stream_ptr()
+        xs = [t.contiguous() for t in xs]
+        codes = torch.empty((3, m, k), dtype=torch.int8, device=dev)
+        xsc = torch.empty((3, m), dtype=torch.float32, device=dev)
+        outs3 = torch.empty((3, m, n), dtype=torch.float16, device=dev)
+        abi.call("rwkvq_prep3_x_int8", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]), m, k, k,
+                 codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, xsc[0].data_ptr(), xsc[1].data_ptr(),
+                 xsc[2].data_ptr(), abi.DEFAULT_DIV, st)
+        abi.call("rwkvq_gemm_int8_rkv", codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, xsc[0].data_ptr(),
+                 xsc[1].data_ptr(), xsc[2].data_ptr(), ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0),
+                 scales[0].data_ptr(), scales[1].data_ptr(), scales[2].data_ptr(), outs3[0].data_ptr(), outs3[1].data_ptr(),
+                 outs3[2].data_ptr(), n, m, n, k, 0, st)
+        abi.after_call()
+        outs = [outs3[0], outs3[1], outs3[2]]
+    elif _tc_fused_fits(m, k, 3) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=xs[0].device) for _ in range(3)]
         wsp = abi.workspace(m, n, k, 3, xs[0].device)
@@ -391,16 +475,17 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
                  scales[1].data_ptr(), scales[2].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(),
                  outs[2].data_ptr(), n, m, n, k, k, abi.DEFAULT_DIV, 0, abi.stream_ptr())
     elif ROUTE != "mma" and same_ld and m > 0:
-        # above the decode kernel's range: three row-quantization launches and ONE tensor-core GEMM launch for r, k, v
+        # above the decode kernel's range: ONE row-quantization launch and ONE tensor-core GEMM launch for r, k, v
         # (the reference: 3 x _prep_x_int8_kernel + fused_rkv_int8_kernel)
         dev = xs[0].device
         st = abi.stream_ptr()
+        xs = [t.contiguous() for t in xs]
         codes = torch.empty((3, m, k), dtype=torch.int8, device=dev)
         xsc = torch.empty((3, m), dtype=torch.float32, device=dev)
         outs3 = torch.empty((3, m, n), dtype=torch.float16, device=dev)
-        for i, x2 in enumerate(xs):
-            abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
-                     codes[i].data_ptr(), k, xsc[i].data_ptr(), abi.DEFAULT_DIV, st)
+        abi.call("rwkvq_prep3_x_int8", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), abi.dtype_code(xs[0]), m, k, k,
+                 codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, xsc[0].data_ptr(), xsc[1].data_ptr(),
+                 xsc[2].data_ptr(), abi.DEFAULT_DIV, st)
         wsp = abi.workspace(min(m, 128), n, k, 3, dev)
         abi.call("rwkvq_tc_gemm_int8_rkv", codes[0].data_ptr(), codes[1].data_ptr(), codes[2].data_ptr(), k, xsc[0].data_ptr(),
                  xsc[1].data_ptr(), xsc[2].data_ptr(), ws[0].data_ptr(), ws[1].data_ptr(), ws[2].data_ptr(), ws[0].stride(0),

@@ -85,6 +85,10 @@ SIGNATURES = {
     "rwkvq_tc_gemm_int8_rkv": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
                                _u32, _p, _i64, _p],
     "rwkvq_tc_static_status": [_p],
+    "rwkvq_prep3_x_int8": [_p, _p, _p, _i32, _i64, _i64, _i64, _p, _p, _p, _i64, _p, _p, _p, _i32, _p],
+    "rwkvq_gemm_decode_route": [_i64, _i64],
+    "rwkvq_gemm_fp8_rkv": [_p, _p, _p, _i64, _p, _i32, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
+    "rwkvq_gemm_int8_rkv": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _u32, _p],
     "rwkvq_set_wait_limit_us": [_i64],
     "rwkvq_device_status": [_p, _i32],
     "rwkvq_selftest_timeout": [_p, _p, _i64, _i32, _p],

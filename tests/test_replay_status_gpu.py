@@ -188,7 +188,7 @@ def test_int8_rkv_gemm_route_exact(mods, m):
     for shared in (True, False):
         before = abi.launch_count()
         got = f.linear_rkv_int8_fused(*[x.cuda() for x in xs], *d, compat_shared_scale=shared)
-        assert abi.launch_count() - before == 4
+        assert abi.launch_count() - before == 2
         want = O.linear_rkv_int8_fused(*xs, *infos, div=lib_div(abi), shared_scale=shared)
         for g, w in zip(got, want):
             bits_equal(g, w, f"int8 rkv shared={shared}")
@@ -216,6 +216,42 @@ def test_fp8_perchannel_weight_scales(mods, m):
     got = f.linear_rkv_fused(*[t.cuda() for t in xs], *[dev(i) for i in infos])
     for g, w in zip(got, O.linear_rkv_fused(*xs, *infos, div=lib_div(abi))):
         assert rel_err(g, w) <= 1e-2
+
+
+@pytest.mark.parametrize("scheme", ["fp8", "int8"])
+@pytest.mark.parametrize("m,n,k", [(9, 2560, 2560), (16, 520, 4096), (32, 2560, 2560), (32, 300, 4096), (12, 192, 8192)])
+def test_decode_on_codes_route(mods, scheme, m, n, k):
+    """9..32 rows: the activations are quantized once and the weight-streaming kernel copies the codes; two launches
+    for a single projection and for r, k, v alike, r/k/v equal to single calls bit for bit."""
+    abi, f, _ = mods
+    assert f._codes_gemv_fits(m, k)
+    xs = [gen(90 + i + m, (m, k), 1.0 + i).to(torch.bfloat16) for i in range(3)]
+    if scheme == "fp8":
+        infos = [fp8_weight(91 + i, n, k) for i in range(3)]
+        d = [dev(i) for i in infos]
+        before = abi.launch_count()
+        got = f.linear_rkv_fused(*[x.cuda() for x in xs], *d)
+        assert abi.launch_count() - before == 2
+        for g, w, x, i in zip(got, O.linear_rkv_fused(*xs, *infos, div=lib_div(abi)), xs, d):
+            assert rel_err(g, w) <= 1e-2
+            before = abi.launch_count()
+            single = f.linear_fp8_fused(x.cuda(), i)
+            assert abi.launch_count() - before == 2
+            bits_equal(g, single, "fused vs single")
+    else:
+        infos = []
+        for i in range(3):
+            q, s = O.q_int8_sym(gen(95 + i, (n, k), 0.02, torch.float16))
+            infos.append({"weight": q, "tensor_scale": s, "qtype": "int8"})
+        d = [dev(i) for i in infos]
+        before = abi.launch_count()
+        got = f.linear_rkv_int8_fused(*[x.cuda() for x in xs], *d, compat_shared_scale=False)
+        assert abi.launch_count() - before == 2
+        acc = torch.empty((m, n), dtype=torch.int32, device="cuda")
+        for j, (g, w, x, i) in enumerate(zip(got, O.linear_rkv_int8_fused(*xs, *infos, div=lib_div(abi), shared_scale=False), xs, d)):
+            bits_equal(g, w, "int8 rkv")
+            bits_equal(f.linear_int8_fused(x.cuda(), i, acc_out=acc), w, "int8 single")
+            bits_equal(acc, O.linear_int8_fused(x, infos[j], lib_div(abi), return_acc=True)[1], "int8 acc")
 
 
 def test_quantized_dispatch_routes_int4(mods):
