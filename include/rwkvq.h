@@ -352,6 +352,35 @@ int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const floa
                                  int64_t M, int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* stream);
 int32_t rwkvq_tc_static_status(int32_t* host_status);
 
+/* ---------------------------------------------------------------- column-split projection across GPUs (NVLink peer memory)
+ *
+ * No counterpart in the reference (single process, single GPU).  The FFN key weight [F, C] is split by output rows
+ * over `world` ranks (one process per GPU); every rank computes its [M, F/world] slice and the slices are gathered
+ * along the features.  Every rank owns one buffer OUT [M, ld >= F] fp16 that its peers can address (exchange the
+ * pointers once, e.g. through CUDA IPC handles) and one array of `world` 32-bit flags, zeroed once, also addressable
+ * by the peers.  Per call, on one stream: (1) the projection entry point writes the rank's own columns straight into
+ * OUT (out = OUT + rank * n_local, ldo = ld); (2) rwkvq_peer_signal stores `epoch` into flags[rank] of EVERY rank's
+ * flag array (system-scope release behind a system-scope fence); (3) rwkvq_allgather_cols_pull waits, bounded, for
+ * flags[s] == epoch of each source rank s and copies that rank's columns out of its OUT into the local OUT with
+ * ordinary 16-byte peer loads.  `outs` and `flag_arrays` are HOST arrays of `world` device pointers in rank order.
+ * Use a strictly increasing epoch per call and two OUT buffers in turn (a peer may still be reading the previous
+ * call's columns while this rank computes the next).  A rank that never signals makes the pull give up after the
+ * wait limit: RWKVQ_E_TIMEOUT in *status (device pointer; NULL = the per-device status word).  No TMA and no
+ * multicast touches peer memory.
+ * Set-up (the only entry points that allocate; not for the serving loop): rwkvq_peer_alloc returns `bytes` of zeroed
+ * memory on the current device with its 64-byte CUDA IPC handle; rwkvq_peer_open maps another process's buffer from
+ * such a handle -- call it with this process's own device current, the open sets up peer access between the two
+ * devices; rwkvq_peer_close / rwkvq_peer_free undo them.  rwkvq_enable_peer_access(d) makes device d's ordinary
+ * allocations of THIS process addressable from kernels of the current device (single-process use). */
+int32_t rwkvq_peer_alloc(int64_t bytes, void** ptr_out, void* handle64_out);
+int32_t rwkvq_peer_open(const void* handle64, void** ptr_out);
+int32_t rwkvq_peer_close(void* ptr);
+int32_t rwkvq_peer_free(void* ptr);
+int32_t rwkvq_enable_peer_access(int32_t peer_device);
+int32_t rwkvq_peer_signal(void* const* flag_arrays, int32_t rank, int32_t world, uint32_t epoch, void* stream);
+int32_t rwkvq_allgather_cols_pull(void* const* outs, const uint32_t* my_flags, uint32_t epoch, int32_t rank, int32_t world,
+                                  int64_t M, int64_t n_local, int64_t ld, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------- bounded waits, status, diagnostics
  *
  * No counterpart in the reference (its kernels have no device-side waits).  Every device-side wait of this library

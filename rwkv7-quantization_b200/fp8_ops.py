@@ -41,7 +41,7 @@ def linear_fp8(x, weight_info, out_dtype=torch.float16):
     codes = torch.empty((m, k), dtype=torch.uint8, device=dev)
     amax = torch.empty(1, dtype=torch.float32, device=dev)
     scale = torch.empty(1, dtype=torch.float32, device=dev)
-    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    out = abi.new_out(m, n, dev)
     st = abi.stream_ptr()
     # inv = 448/amax and scale = amax/448 the way torch evaluates them on a GPU in prep_x_fp8 (DIV_TORCH)
     f._actq_fp8(x2, codes, amax, scale, abi.DIV_TORCH, abi.FLAG_AMAX_AFTER_BF16 | abi.FLAG_QUANT_FROM_BF16, st)
@@ -49,11 +49,11 @@ def linear_fp8(x, weight_info, out_dtype=torch.float16):
     if f.ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, dev)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),
-                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DIV_IEEE, gflags, ws.data_ptr(), ws.numel(), st)
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DIV_IEEE, gflags, ws.data_ptr(), ws.numel(), st)
         abi.after_call(ws)
     else:
         abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),
-                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DIV_IEEE, gflags, st)
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DIV_IEEE, gflags, st)
     return f._finish(out, x.shape[:-1], n, out_dtype)
 
 

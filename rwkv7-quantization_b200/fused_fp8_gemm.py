@@ -93,7 +93,7 @@ def _tc_fused_fits(m: int, k: int, nmat: int = 1) -> bool:
 
 
 def _finish(out2d: torch.Tensor, lead, n: int, out_dtype):
-    out = out2d.reshape(*lead, n)
+    out = out2d if len(lead) == 1 else out2d.reshape(*lead, n)
     return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
 
 
@@ -196,16 +196,16 @@ def _fp8_gemv(x2, w, w_ts, awq, flags):
     m, k = x2.shape
     n = w.shape[0]
     flags |= _wscale_flag(w_ts, n)
-    out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    out = abi.new_out(m, n, x2.device)
     if _tc_fused_fits(m, k):
         ws = abi.workspace(m, n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
-                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
                  ws.data_ptr(), ws.numel(), abi.stream_ptr())
         abi.after_call(ws)
         return out
     abi.call("rwkvq_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), abi.ptr(awq), w.data_ptr(), w.stride(0),
-             w_ts.data_ptr(), out.data_ptr(), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
+             w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags,
              abi.stream_ptr())
     abi.after_call()
     return out
@@ -230,18 +230,18 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     n = w.shape[0]
     codes = torch.empty((m, k), dtype=torch.uint8, device=x2.device)
     amax = torch.empty(1, dtype=torch.float32, device=x2.device)
-    out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    out = abi.new_out(m, n, x2.device)
     st = abi.stream_ptr()
     gemm_flags |= _wscale_flag(w_ts, n)
     _actq_fp8(x2, codes, amax, None, abi.DEFAULT_DIV, act_flags, st)
     if ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
-                 w_ts.data_ptr(), out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(), st)
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(), st)
         abi.after_call(ws)
     else:
         abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
-                 out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, gemm_flags, st)
+                 out.data_ptr(), out.stride(0), m, n, k, abi.DEFAULT_DIV, gemm_flags, st)
     return out
 
 
@@ -252,11 +252,11 @@ def _fp8_codes_gemv(x2, w, w_ts):
     dev = x2.device
     codes = torch.empty((m, k), dtype=torch.uint8, device=dev)
     amax = torch.empty(1, dtype=torch.float32, device=dev)
-    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    out = abi.new_out(m, n, dev)
     st = abi.stream_ptr()
     _actq_fp8(x2, codes, amax, None, abi.DEFAULT_DIV, abi.FLAG_QUANT_FROM_BF16, st)
     abi.call("rwkvq_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0), w_ts.data_ptr(),
-             out.data_ptr(), n, m, n, k, abi.DEFAULT_DIV, _wscale_flag(w_ts, n), st)
+             out.data_ptr(), out.stride(0), m, n, k, abi.DEFAULT_DIV, _wscale_flag(w_ts, n), st)
     abi.after_call()
     return out
 
@@ -388,7 +388,7 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
 def _int8_any(x2, w, w_scale, acc_out=None):
     m, k = x2.shape
     n = w.shape[0]
-    out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+    out = abi.new_out(m, n, x2.device)
     st = abi.stream_ptr()
     if _codes_gemv_fits(m, k):
         # 9..32 rows: quantize the rows once, then the weight-streaming decode kernel on the codes
@@ -397,16 +397,16 @@ def _int8_any(x2, w, w_scale, acc_out=None):
         abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
                  codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
         abi.call("rwkvq_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
-                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, st)
+                 out.data_ptr(), out.stride(0), abi.ptr(acc_out), n, m, n, k, 0, st)
         abi.after_call()
     elif _tc_fused_fits(m, k):
         ws = abi.workspace(m, n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
-                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0,
+                 out.data_ptr(), out.stride(0), abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0,
                  ws.data_ptr(), ws.numel(), st)
     elif _gemv_fits(m, k, fp8=False):
         abi.call("rwkvq_gemv_int8", x2.data_ptr(), abi.dtype_code(x2), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
-                 out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0, st)
+                 out.data_ptr(), out.stride(0), abi.ptr(acc_out), n, m, n, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0, st)
     else:
         codes = torch.empty((m, k), dtype=torch.int8, device=x2.device)
         xs = torch.empty(m, dtype=torch.float32, device=x2.device)
@@ -415,10 +415,10 @@ def _int8_any(x2, w, w_scale, acc_out=None):
         if ROUTE != "mma":
             ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
             abi.call("rwkvq_tc_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0),
-                     w_scale.data_ptr(), out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, ws.data_ptr(), ws.numel(), st)
+                     w_scale.data_ptr(), out.data_ptr(), out.stride(0), abi.ptr(acc_out), n, m, n, k, 0, ws.data_ptr(), ws.numel(), st)
         else:
             abi.call("rwkvq_gemm_int8", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
-                     out.data_ptr(), n, abi.ptr(acc_out), n, m, n, k, 0, st)
+                     out.data_ptr(), out.stride(0), abi.ptr(acc_out), n, m, n, k, 0, st)
     return out
 
 

@@ -143,18 +143,18 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
     m = x2.shape[0]
     route = _route(m, k)
     if route == "fused" and wbs.stride(0) % 16 == 0 and wbs.data_ptr() % 16 == 0:
-        out = torch.empty((m, n), dtype=torch.float16, device=x2.device)
+        out = abi.new_out(m, n, x2.device)
         abi.call("rwkvq_gemv_nvfp4_fused", x2.data_ptr(), abi.dtype_code(x2), k, w.data_ptr(), w.stride(0), wbs.data_ptr(),
-                 wbs.stride(0), wts.data_ptr(), out.data_ptr(), n, m, n, k, abi.stream_ptr())
+                 wbs.stride(0), wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.stream_ptr())
         out = out.reshape(*x.shape[:-1], n)
         return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
     codes, bs, pts = quantize_activations_nvfp4(x, blocked=(route == "tc"))
-    out = torch.empty((m, n), dtype=torch.float16, device=codes.device)
+    out = abi.new_out(m, n, codes.device)
     if route == "tc":
         ws = abi.workspace(1, 1, 1, 1, codes.device)
         a_blk, w_blk = bs, _blocked_weight_scales(weight_info, k)     # both alive until the launch
         abi.call("rwkvq_tc_gemm_nvfp4", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),
-                 w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), n, m, n, k, ws.data_ptr(), ws.numel(), abi.stream_ptr())
+                 w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, ws.data_ptr(), ws.numel(), abi.stream_ptr())
     else:
         rows = GEMV_ROWS
         while rows > 1 and abi.lib().rwkvq_gemv_nvfp4_smem_bytes(rows, k) > 200 * 1024:
@@ -162,7 +162,7 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
         for r0 in range(0, m, rows):
             r = min(rows, m - r0)
             abi.call("rwkvq_gemv_nvfp4", codes[r0:].data_ptr(), k // 2, bs[r0:].data_ptr(), k // BLOCK, pts.data_ptr(),
-                     w.data_ptr(), w.stride(0), wbs.data_ptr(), wbs.stride(0), wts.data_ptr(), out[r0:].data_ptr(), n, r, n, k,
+                     w.data_ptr(), w.stride(0), wbs.data_ptr(), wbs.stride(0), wts.data_ptr(), out[r0:].data_ptr(), out.stride(0), r, n, k,
                      abi.stream_ptr())
     out = out.reshape(*x.shape[:-1], n)
     return out if out_dtype in (None, out.dtype) else out.to(out_dtype)

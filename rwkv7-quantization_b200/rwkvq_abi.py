@@ -85,6 +85,13 @@ SIGNATURES = {
     "rwkvq_tc_gemm_int8_rkv": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
                                _u32, _p, _i64, _p],
     "rwkvq_tc_static_status": [_p],
+    "rwkvq_enable_peer_access": [_i32],
+    "rwkvq_peer_alloc": [_i64, _p, _p],
+    "rwkvq_peer_open": [_p, _p],
+    "rwkvq_peer_close": [_p],
+    "rwkvq_peer_free": [_p],
+    "rwkvq_peer_signal": [_p, _i32, _i32, _u32, _p],
+    "rwkvq_allgather_cols_pull": [_p, _p, _u32, _i32, _i32, _i64, _i64, _i64, _p, _p],
     "rwkvq_prep3_x_int8": [_p, _p, _p, _i32, _i64, _i64, _i64, _p, _p, _p, _i64, _p, _p, _p, _i32, _p],
     "rwkvq_gemm_decode_route": [_i64, _i64],
     "rwkvq_gemm_fp8_rkv": [_p, _p, _p, _i64, _p, _i32, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
@@ -169,6 +176,35 @@ def div_on_device(a: torch.Tensor, b: torch.Tensor, mode: int = DIV_FULL) -> tor
     out = torch.empty_like(a32)
     call("rwkvq_div_f32", a32.data_ptr(), b32.data_ptr(), out.data_ptr(), a32.numel(), mode, stream_ptr())
     return out
+
+
+# ---------------------------------------------------------------------------- where a projection writes its result
+_out_override: list = []
+
+
+class output_into:
+    """`with output_into(view):` the next single-matrix projection writes its fp16 [M, N] result into `view` (rows may
+    be strided: a column range of a wider buffer) instead of a fresh tensor -- the kernels take a leading dimension."""
+
+    def __init__(self, view: torch.Tensor):
+        assert view.dim() == 2 and view.dtype == torch.float16 and view.stride(1) == 1 and view.data_ptr() % 16 == 0
+        self.view = view
+
+    def __enter__(self):
+        _out_override.append(self.view)
+        return self.view
+
+    def __exit__(self, *exc):
+        _out_override.pop()
+
+
+def new_out(m: int, n: int, device) -> torch.Tensor:
+    if _out_override:
+        v = _out_override[-1]
+        if tuple(v.shape) != (m, n) or v.device != torch.device(device):
+            raise ValueError(f"rwkvq: output view {tuple(v.shape)} on {v.device} does not match the result [{m}, {n}] on {device}")
+        return v
+    return torch.empty((m, n), dtype=torch.float16, device=device)
 
 
 # ---------------------------------------------------------------------------- status of the bounded device-side waits

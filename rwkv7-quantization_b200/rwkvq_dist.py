@@ -52,23 +52,131 @@ def slice_weight_info(info: dict, rank: int, world: int, align: int = 128) -> di
     return out
 
 
+class PeerGather:
+    """The all-gather of a column-split projection over NVLink peer memory, by this library's own kernels.
+
+    Every rank allocates two result buffers [max_rows, N] fp16 and a flag array, exports them to the other ranks of
+    the group as CUDA IPC handles (exchanged once through the process group) and maps theirs.  Per call the local
+    projection writes its columns straight into the current buffer, `rwkvq_peer_signal` publishes that on every rank,
+    and `rwkvq_allgather_cols_pull` copies the other ranks' columns in with peer loads behind bounded flag waits: the
+    result is assembled in its final [M, N] layout, without NCCL, staging or a transposing copy.  The two buffers are
+    used in turn, so a rank may compute call i+1 while a peer still reads its columns of call i."""
+
+    def __init__(self, max_rows: int, n_total: int, group=None, device=None):
+        import ctypes
+        import rwkvq_abi as abi
+        self.abi, self.ctypes = abi, ctypes
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if n_total % (8 * self.world):
+            raise ValueError(f"{n_total} columns cannot be split into {self.world} slices of a multiple of 8")
+        self.n, self.nl, self.max_rows = n_total, n_total // self.world, max_rows
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        abi.require_device()
+        buf_bytes = max_rows * n_total * 2
+        total = 2 * buf_bytes + 512                      # two result buffers, the flag array, the status word
+        with torch.cuda.device(self.device):
+            ptr, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+            abi.call("rwkvq_peer_alloc", total, ctypes.byref(ptr), handle)
+            self._base = ptr.value
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, bytes(handle.raw), group=group)
+            bases, self._opened = [], []
+            for r, h in enumerate(everyone):
+                if r == self.rank:
+                    bases.append(self._base)
+                    continue
+                p = ctypes.c_void_p()
+                abi.call("rwkvq_peer_open", ctypes.create_string_buffer(h, 64), ctypes.byref(p))   # this rank's device is current
+                self._opened.append(p.value)
+                bases.append(p.value)
+
+        class _Raw:                                       # the library's allocation as a torch tensor (zero copy)
+            def __init__(self, address, nbytes):
+                self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 3}
+        raw = torch.as_tensor(_Raw(self._base, total), device=self.device)
+        self.bufs = [raw[i * buf_bytes:(i + 1) * buf_bytes].view(torch.float16).view(max_rows, n_total) for i in range(2)]
+        self.flags = raw[2 * buf_bytes:2 * buf_bytes + 256].view(torch.int32)
+        self.status = raw[2 * buf_bytes + 256:2 * buf_bytes + 260].view(torch.int32)
+        arr = ctypes.c_void_p * self.world
+        self._out_arrays = [arr(*[b + i * buf_bytes for b in bases]) for i in range(2)]
+        self._flag_array = arr(*[b + 2 * buf_bytes for b in bases])
+        self.epoch = 0
+        dist.barrier(group=group)      # every rank has mapped every buffer before anyone signals
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (after a barrier: nobody may still be reading it)."""
+        if self._base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self.abi.call("rwkvq_peer_close", p)
+            dist.barrier(group=self.group)
+            self.bufs, self.flags, self.status = [], None, None
+            self.abi.call("rwkvq_peer_free", self._base)
+        self._base = None
+
+    def next_buffer(self, m: int) -> torch.Tensor:
+        """Advance to the next call; returns this rank's column view [m, N/world] of the buffer to write into."""
+        if m > self.max_rows:
+            raise ValueError(f"{m} rows exceed the {self.max_rows} the peer buffers were sized for")
+        self.epoch += 1
+        self.m = m
+        buf = self.bufs[self.epoch & 1]
+        return buf[:m, self.rank * self.nl:(self.rank + 1) * self.nl]
+
+    def gather(self) -> torch.Tensor:
+        """Signal this rank's columns, pull everybody else's; returns the assembled [m, N] (a view of the buffer, valid
+        until the call after next)."""
+        abi, b = self.abi, self.epoch & 1
+        st = abi.stream_ptr()
+        abi.call("rwkvq_peer_signal", self._flag_array, self.rank, self.world, self.epoch, st)
+        abi.call("rwkvq_allgather_cols_pull", self._out_arrays[b], self.flags.data_ptr(), self.epoch, self.rank, self.world,
+                 self.m, self.nl, self.n, self.status.data_ptr(), st)
+        return self.bufs[b][:self.m]
+
+    def check(self) -> None:
+        """Raise if a pull gave up waiting for a peer (synchronizes)."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise RuntimeError("rwkvq: a rank did not deliver its columns within the wait limit")
+
+
 class ColumnSplitLinear:
-    """y = x @ W^T with W split by output rows across the ranks of `group`, slices all-gathered along the features.
+    """y = x @ W^T with W split by output rows across the ranks of `group`, slices gathered along the features.
 
     `linear_fn(x, weight_info, out_dtype)` is the projection to run on the local slice (fp8_ops.linear_quantized for
-    FP8 / INT8 / NVFP4 weight-info dicts, int4.int4_ops.linear_int4 for INT4 ones)."""
+    FP8 / INT8 / NVFP4 weight-info dicts, int4.int4_ops.linear_int4 for INT4 ones).  gather="nccl": an NCCL all-gather
+    (rank-major) followed by one copy into the [M, N] layout; gather="peer": PeerGather above (GPU only, fp16 results;
+    `max_rows` sizes its buffers)."""
 
-    def __init__(self, weight_info: dict, linear_fn, group=None, already_sliced: bool = False):
+    def __init__(self, weight_info: dict, linear_fn, group=None, already_sliced: bool = False, gather: str = "nccl", max_rows: int = 4096):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.local = weight_info if already_sliced else slice_weight_info(weight_info, self.rank, self.world)
         self.linear_fn = linear_fn
+        self.n_local = self.local["weight" if "weight" in self.local else "packed"].shape[0]
+        self.peer = PeerGather(max_rows, self.n_local * self.world, group) if gather == "peer" else None
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
+        if self.peer is not None:
+            import rwkvq_abi as abi
+            x2 = x.reshape(-1, x.shape[-1])
+            with abi.output_into(self.peer.next_buffer(x2.shape[0])):
+                self.linear_fn(x2, self.local, torch.float16)             # writes this rank's columns in place
+            y = self.peer.gather().reshape(*x.shape[:-1], self.n_local * self.world)
+            return y if out_dtype in (None, torch.float16) else y.to(out_dtype)
         local = self.linear_fn(x, self.local, out_dtype)                  # [..., N/world]
         lead, nl = local.shape[:-1], local.shape[-1]
         flat = local.reshape(-1, nl).contiguous()
         gathered = torch.empty((self.world * flat.shape[0], nl), dtype=flat.dtype, device=flat.device)
-        dist.all_gather_into_tensor(gathered, flat, group=self.group)    # NCCL all-gather over NVLink; rank-major rows
-        return gathered.reshape(self.world, flat.shape[0], nl).permute(1, 0, 2).reshape(*lead, nl * self.world)
+        dist.all_gather_into_tensor(gathered, flat, group=self.group)    # NCCL all-gather over NVLink; rank-major
+        gathered = gathered.view(self.world, flat.shape[0], nl)
+        if flat.shape[0] == 1:
+            return gathered.reshape(*lead, nl * self.world)               # one row: rank-major IS the feature order
+        out = torch.empty((flat.shape[0], self.world, nl), dtype=flat.dtype, device=flat.device)
+        out.copy_(gathered.permute(1, 0, 2))                              # one strided copy into the [M, N] layout
+        return out.reshape(*lead, nl * self.world)
