@@ -300,6 +300,10 @@ def run_ours(args, rank, world, local_rank):
                                 "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),
                                 "peak_note": "2 x the measured dense bf16 cuBLAS rate (fp8 runs at twice the bf16 rate)"}}
         del xp
+    colsplit = None
+    if dist_on and not args.no_colsplit:
+        with torch.cuda.stream(stream):
+            colsplit = colsplit_leg(world, dev, dist_on)
     nbytes = int(step_bytes(1) * scale_l)
     per_step = ms / args.steps
     gbs = nbytes * world / (per_step * 1e-3) / 1e9
@@ -328,6 +332,7 @@ def run_ours(args, rank, world, local_rank):
         "launches_counted_eager": int(eager_launches),
         "clocks": clocks.summary(),
         "prefill": prefill,
+        "colsplit": colsplit,
     }
     if rank == 0:
         if world == 1 and not args.no_cpu:
@@ -338,6 +343,55 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps(line))
     if dist_on:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------ column-split FFN key (N > 1)
+def colsplit_leg(world, dev, dist_on):
+    """NVFP4 FFN key [16384, 4096] split by output rows over the ranks, activations replicated, slices gathered along
+    the features: per M the local GEMM, the gather alone (NCCL all-gather + layout copy vs the library's peer-memory
+    pull) and both end to end; microseconds are maxima over ranks, GB/s counts the bytes a rank RECEIVES over NVLink."""
+    import fp8_ops
+    import nvfp4_ops
+    import rwkvq_dist as D
+    gen = torch.Generator(device=dev).manual_seed(11)                    # same weights on every rank
+    w = torch.randn((F, C), generator=gen, device=dev) * C ** -0.5
+    info = nvfp4_ops.quantize_to_nvfp4(w)
+    del w
+    lin = fp8_ops.linear_quantized
+    rows = []
+    splits = {"nccl": D.ColumnSplitLinear(info, lin, gather="nccl"), "peer": D.ColumnSplitLinear(info, lin, gather="peer", max_rows=4096)}
+    local = splits["nccl"].local
+    nl = F // world
+    for m in (1, 256, 4096):
+        x = torch.randn((m, C), generator=gen, device=dev).to(torch.bfloat16)
+        reps = 20 if m <= 256 else 8
+        flat = lin(x, local)
+        gathered = torch.empty((world * m, nl), dtype=torch.float16, device=dev)
+        full = torch.empty((m, world, nl), dtype=torch.float16, device=dev)
+
+        def nccl_gather():
+            torch.distributed.all_gather_into_tensor(gathered, flat)
+            if m > 1:
+                full.copy_(gathered.view(world, m, nl).permute(1, 0, 2))
+
+        def peer_gather():
+            splits["peer"].peer.next_buffer(m)
+            splits["peer"].peer.gather()
+        legs = {"local_gemm": lambda: lin(x, local), "nccl_gather": nccl_gather, "peer_gather": peer_gather,
+                "nccl_e2e": lambda: splits["nccl"](x), "peer_e2e": lambda: splits["peer"](x)}
+        row = {"M": m, "bytes_received_per_rank": m * (F - nl) * 2}
+        for name, fn in legs.items():
+            for _ in range(3):
+                fn()
+            row[name + "_us"] = round(timed(fn, reps, dist_on) * 1e3 / reps, 2)
+        for mode in ("nccl", "peer"):
+            row[mode + "_gather_GBps"] = round(row["bytes_received_per_rank"] / row[mode + "_gather_us"] / 1e3, 1)
+        row["peer_vs_nccl_e2e"] = round(row["nccl_e2e_us"] / row["peer_e2e_us"], 2)
+        rows.append(row)
+    splits["peer"].peer.check()
+    splits["peer"].peer.close()
+    return {"workload": "NVFP4 FFN key [16384,4096] column-split over the ranks, bf16 activations replicated, fp16 [M,16384] gathered on every rank",
+            "timing": "CUDA events on the launching stream, eager calls, max over ranks", "nvlink_peak_GBps_per_direction": 770.0, "rows": rows}
 
 
 # ------------------------------------------------------------------------------------------ per-shape mode
@@ -429,6 +483,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--layers", type=int, default=LAYERS, help="layers of the stack (32 = the benchmark; fewer only for profiler captures)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
+    ap.add_argument("--no-colsplit", action="store_true", help="N > 1: skip the column-split FFN key measurement")
     ap.add_argument("--case", default="decode", choices=["decode", "shape"], help="decode = the benchmark; shape = one projection")
     ap.add_argument("--scheme", default="fp8", choices=["fp8", "int8", "int4", "nvfp4"])
     ap.add_argument("--shape", default="ffn_key", choices=sorted(SHAPES))
