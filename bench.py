@@ -242,7 +242,7 @@ def run_ours(args, rank, world, local_rank):
 
     layers = make_model(dev, seed=100 + rank, nlayers=args.layers)
     scale_l = args.layers / LAYERS
-    host, x = make_inputs(dev, seed=7 + rank, pinned_host=True)
+    host, x = make_inputs(dev, seed=7 + rank, m=args.tokens, pinned_host=True)
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
@@ -283,6 +283,29 @@ def run_ours(args, rank, world, local_rank):
         ms_eager = timed(step_eager, max(1, args.steps // 4), dist_on) / max(1, args.steps // 4) * args.steps
         eager_launches = abi.launch_count() - l0
 
+        # the same step through the per-layer helper of the package (weights, shapes and outputs bound once; one
+        # boundary crossing per layer): what an engine's Python decode loop can use instead of four drop-in calls
+        from rwkvq_layer import DecodeLayer, MAX_ROWS
+        try:
+            dl = [DecodeLayer(L["r"], L["k"], L["v"], L["o"], L["ffn_k"], L["ffn_v"], rows=args.tokens) for L in layers] if args.tokens <= MAX_ROWS else []
+        except ValueError:      # more rows than the one-launch kernel holds at K = 16384: no per-layer helper for this batch
+            dl = []
+
+        def step_layers():
+            for k in x:
+                x[k].copy_(host[k], non_blocking=True)
+            for d in dl:
+                out = d.all(x["xr"], x["xk"], x["xv"], x["xo"], x["xf"], x["xg"])
+            y_host.copy_(out[5], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        if dl:
+            for _ in range(3):
+                step_layers()
+            ms_layers = timed(step_layers, args.steps, dist_on)
+        else:
+            ms_layers = float("nan")
+
     prefill = None
     if not args.no_prefill:
         with torch.cuda.stream(stream):
@@ -304,18 +327,19 @@ def run_ours(args, rank, world, local_rank):
     if dist_on and not args.no_colsplit:
         with torch.cuda.stream(stream):
             colsplit = colsplit_leg(world, dev, dist_on)
-    nbytes = int(step_bytes(1) * scale_l)
+    nbytes = int(step_bytes(args.tokens) * scale_l)
     per_step = ms / args.steps
     gbs = nbytes * world / (per_step * 1e-3) / 1e9
     gbs_e2e = nbytes * world / (ms_e2e / args.steps * 1e-3) / 1e9
     gbs_eager = nbytes * world / (ms_eager / args.steps * 1e-3) / 1e9
+    gbs_layers = nbytes * world / (ms_layers / args.steps * 1e-3) / 1e9
     pk = peaks()
     per_gpu = gbs / world
     line = {
         "metric": METRIC, "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": round(per_step, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens_per_step_per_gpu": 1, "parallelism": f"sequence-sharded x{world}",
+        "config": {"workload": WORKLOAD if args.tokens == 1 else WORKLOAD.replace("B=1", f"B={args.tokens}"), "tokens_per_step_per_gpu": args.tokens, "parallelism": f"sequence-sharded x{world}",
                    "l2": "6.44 GB of distinct weights per step (inputs larger than L2)",
                    "launch": "CUDA graph of the 128 public-API calls"},
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -327,8 +351,11 @@ def run_ours(args, rank, world, local_rank):
                 "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()),
                 "d2h_bytes_per_step": y_host.numel() * y_host.element_size(),
                 "mode": "pinned host -> device copies, graph replay of the public API calls, device -> host result",
-                "eager_python_calls_gbs": round(gbs_eager, 2)},
-        "gpu_launches": 4 * args.layers * args.steps,
+                "eager_python_calls_gbs": round(gbs_eager, 2),
+                "eager_layer_calls_gbs": round(gbs_layers, 2),
+                "eager_note": "no CUDA graph: eager_python_calls = the 128 drop-in calls per step; eager_layer_calls = 32 "
+                              "rwkvq_layer.DecodeLayer.all calls per step (descriptors bound once, one boundary crossing per layer)"},
+        "gpu_launches": int(round(eager_launches / (3 + max(1, args.steps // 4)))) * args.steps,   # counted per eager step, x timed steps
         "launches_counted_eager": int(eager_launches),
         "clocks": clocks.summary(),
         "prefill": prefill,
@@ -488,6 +515,7 @@ def main():
     ap.add_argument("--scheme", default="fp8", choices=["fp8", "int8", "int4", "nvfp4"])
     ap.add_argument("--shape", default="ffn_key", choices=sorted(SHAPES))
     ap.add_argument("--m", type=int, default=1, help="rows of activations in --case shape")
+    ap.add_argument("--tokens", type=int, default=1, help="rows per projection in the decode step (1 = the benchmark; more = batched decode)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

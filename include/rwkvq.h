@@ -148,6 +148,28 @@ int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int3
                             const float* sv, void* out_r, void* out_k, void* out_v, int64_t ldo, int64_t M, int64_t N,
                             int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags, void* stream);
 
+/* Several decode projections with ONE call across the boundary (the per-layer loop of the engine, rwkv7_fast_v3a.py:819,
+ * makes four such calls per layer and its host-side cost per call exceeds the kernels' run time at batch 1): the
+ * descriptors are walked in order and each is launched exactly as rwkvq_gemv_fp8 / _fp8_rkv / _int8 / _int8_rkv would
+ * launch it -- same kernels, same results.  Fields not used by a kind are ignored. */
+#define RWKVQ_PROJ_FP8 0
+#define RWKVQ_PROJ_FP8_RKV 1
+#define RWKVQ_PROJ_INT8 2
+#define RWKVQ_PROJ_INT8_RKV 3
+typedef struct rwkvq_proj_desc {
+    int32_t kind;            /* RWKVQ_PROJ_*                                   */
+    int32_t x_dtype;         /* RWKVQ_F16 / RWKVQ_BF16                         */
+    const void* x[3];        /* activations [M, ldx]; x[1], x[2] for r/k/v     */
+    const float* awq[2];     /* FP8 r/k/v: optional per-channel divisors       */
+    const void* w[3];        /* weights [N, ldw]                               */
+    const float* w_scale[3];
+    void* out[3];            /* fp16 [M, ldo]                                  */
+    int64_t ldw, ldo, ldx, M, N, K;
+    int32_t div_mode;
+    uint32_t flags;
+} rwkvq_proj_desc;
+int32_t rwkvq_gemv_batch(const rwkvq_proj_desc* descs, int32_t count, void* stream);
+
 /* ---------------------------------------------------------------- W8A8 GEMM on pre-quantized codes (any M) */
 
 /* These run on mma.sync kernels and need no workspace: the weight-streaming decode kernel for M <= 32 (code tile in

@@ -512,4 +512,38 @@ int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int3
     return run_fused<QT_INT8>(a, x_dtype, (cudaStream_t)stream, "gemv_int8_rkv");
 }
 
+/* Several decode projections with ONE call across the boundary: the descriptors are walked in order and each is
+ * launched exactly as the entry point of its kind would launch it (same kernels, same results). */
+int32_t rwkvq_gemv_batch(const rwkvq_proj_desc* descs, int32_t count, void* stream) {
+    RWKVQ_REQUIRE(descs != nullptr || count == 0, RWKVQ_E_BADARG, "gemv_batch: null descriptors");
+    for (int32_t i = 0; i < count; ++i) {
+        const rwkvq_proj_desc& d = descs[i];
+        int32_t rc;
+        switch (d.kind) {
+            case RWKVQ_PROJ_FP8:
+                rc = rwkvq_gemv_fp8(d.x[0], d.x_dtype, d.awq[0], (const uint8_t*)d.w[0], d.ldw, d.w_scale[0], d.out[0], d.ldo, d.M, d.N, d.K,
+                                    d.ldx, d.div_mode, d.flags, stream);
+                break;
+            case RWKVQ_PROJ_FP8_RKV:
+                rc = rwkvq_gemv_fp8_rkv(d.x[0], d.x[1], d.x[2], d.x_dtype, d.awq[0], d.awq[1], (const uint8_t*)d.w[0], (const uint8_t*)d.w[1],
+                                        (const uint8_t*)d.w[2], d.ldw, d.w_scale[0], d.w_scale[1], d.w_scale[2], d.out[0], d.out[1], d.out[2],
+                                        d.ldo, d.M, d.N, d.K, d.ldx, d.div_mode, d.flags, stream);
+                break;
+            case RWKVQ_PROJ_INT8:
+                rc = rwkvq_gemv_int8(d.x[0], d.x_dtype, (const int8_t*)d.w[0], d.ldw, d.w_scale[0], d.out[0], d.ldo, nullptr, 0, d.M, d.N, d.K,
+                                     d.ldx, d.div_mode, d.flags, stream);
+                break;
+            case RWKVQ_PROJ_INT8_RKV:
+                rc = rwkvq_gemv_int8_rkv(d.x[0], d.x[1], d.x[2], d.x_dtype, (const int8_t*)d.w[0], (const int8_t*)d.w[1], (const int8_t*)d.w[2],
+                                         d.ldw, d.w_scale[0], d.w_scale[1], d.w_scale[2], d.out[0], d.out[1], d.out[2], d.ldo, d.M, d.N, d.K,
+                                         d.ldx, d.div_mode, d.flags, stream);
+                break;
+            default:
+                return fail(RWKVQ_E_BADARG, "gemv_batch: descriptor %d has unknown kind %d", i, d.kind);
+        }
+        if (rc != RWKVQ_OK) return rc;
+    }
+    return RWKVQ_OK;
+}
+
 }  // extern "C"

@@ -190,31 +190,6 @@ __device__ __forceinline__ bool w8_staged_or_report(uint64_t* bar, int* status, 
     return true;
 }
 
-// The activation block as a flat list of 8-element vectors (M * K/8 of them): thread t takes vectors t, t + kThr, ...
-// in batches of U, all U loads of a batch issued before the first use.  The prologue loops are bound by load latency
-// (shared memory ~30 cycles, L2 ~700), not by arithmetic: with one load in flight a CTA of 256 threads needs
-// 20 dependent round trips for 16 rows of 2560, with U = 4 or 8 it needs 3 to 5.
-// (row, vector-in-row) of a flat index without a division: r = floor(idx * ceil(2^32 / kv) / 2^32), exact for
-// idx < 65536 and kv < 65536.
-template <int U, typename Load, typename Use>
-__device__ __forceinline__ void vec_batches(int nvec, int kv, uint32_t inv_kv, Load load, Use use) {
-#pragma unroll 1
-    for (int i0 = threadIdx.x; i0 < nvec; i0 += U * kThr) {
-        uint4 v[U];
-        int r[U], c[U];
-#pragma unroll
-        for (int j = 0; j < U; ++j) {
-            const int idx = i0 + j * kThr;
-            r[j] = (int)__umulhi((uint32_t)idx, inv_kv);
-            c[j] = idx - r[j] * kv;
-            if (idx < nvec) v[j] = load(r[j], c[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < U; ++j)
-            if (i0 + j * kThr < nvec) use(v[j], r[j], c[j]);
-    }
-}
-
 // 128-bit load of activations served from L2 (they were written by an earlier kernel that may still have been running
 // when this CTA started under programmatic dependent launch, so a line this SM's L1 kept from before is not trusted)
 __device__ __forceinline__ uint4 ldg_l2_16(const void* p) {
@@ -254,11 +229,14 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
         if (i1 < nvec) *reinterpret_cast<uint4*>(xq + (size_t)r1 * a.pitch + k1 * 2) = e4m3x8_to_f16x8(fp8_vec_codes<DT>(v1, awq, k1, a.div_mode, inv));
         return amax;
     }
-    const uint32_t inv_kv = 0xFFFFFFFFu / (uint32_t)kv + 1u;
     const int64_t ldx2 = a.ldx * 2;
     float m = 0.f;
     {
-        // raw rows into the tile by bulk copies (one read of the activations), abs-max and in-place conversion from there
+        // raw rows into the tile by bulk copies (one read of the activations), abs-max and in-place conversion from there.
+        // The two loops are deliberately compact (one vector per iteration, not unrolled): they run once per CTA on a
+        // cold instruction cache, and inside a sequence of different kernels a four-way unrolled, load-batched version
+        // of them measured 2 us SLOWER per launch at M = 1, K = 16384 although it is faster when the same kernel
+        // repeats.
         if (threadIdx.x == 0) {
             const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"((uint32_t)(a.M * a.K * 2)) : "memory");
@@ -269,19 +247,26 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
                                "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
         if (!w8_staged_or_report(bar, a.status, a.wait_ns)) return -1.f;
-        vec_batches<4>(nvec, kv, inv_kv,
-                       [&](int r, int c) { return *reinterpret_cast<const uint4*>(xq + (size_t)r * a.pitch + (size_t)c * 16); },
-                       [&](const uint4& v, int, int c) { fp8_vec_amax<DT>(v, awq, c << 3, a.div_mode, after, m); });
+#pragma unroll 1
+        for (int r = 0; r < a.M; ++r) {
+            const char* src = reinterpret_cast<const char*>(xq + (size_t)r * a.pitch);
+#pragma unroll 1
+            for (int i = threadIdx.x; i < kv; i += kThr)
+                fp8_vec_amax<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, after, m);
+        }
         w8_mark(a, 5);
         const float amax = fmaxf(cta_max(m, sh), 1e-12f);
         w8_mark(a, 6);
         const float inv = div_mode_f32(448.f, amax, a.div_mode);
-        vec_batches<4>(nvec, kv, inv_kv,
-                       [&](int r, int c) { return *reinterpret_cast<const uint4*>(xq + (size_t)r * a.pitch + (size_t)c * 16); },
-                       [&](const uint4& v, int r, int c) {          // in place: same thread, same 16 bytes
-                           *reinterpret_cast<uint4*>(xq + (size_t)r * a.pitch + (size_t)c * 16) =
-                               e4m3x8_to_f16x8(fp8_vec_codes<DT>(v, awq, c << 3, a.div_mode, inv));
-                       });
+#pragma unroll 1
+        for (int r = 0; r < a.M; ++r) {
+            uint8_t* qr = xq + (size_t)r * a.pitch;
+#pragma unroll 1
+            for (int i = threadIdx.x; i < kv; i += kThr) {
+                const uint2 c = fp8_vec_codes<DT>(*reinterpret_cast<const uint4*>(qr + (size_t)i * 16), awq, i << 3, a.div_mode, inv);
+                *reinterpret_cast<uint4*>(qr + (size_t)i * 16) = e4m3x8_to_f16x8(c);
+            }
+        }
         return amax;
     }
 }

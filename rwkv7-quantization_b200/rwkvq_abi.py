@@ -85,6 +85,7 @@ SIGNATURES = {
     "rwkvq_tc_gemm_int8_rkv": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64,
                                _u32, _p, _i64, _p],
     "rwkvq_tc_static_status": [_p],
+    "rwkvq_gemv_batch": [_p, _i32, _p],
     "rwkvq_enable_peer_access": [_i32],
     "rwkvq_peer_alloc": [_i64, _p, _p],
     "rwkvq_peer_open": [_p, _p],
@@ -104,6 +105,17 @@ SIGNATURES = {
 }
 _RESTYPES = {"rwkvq_actq_nvfp4_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_fused_smem_bytes": ctypes.c_int64, "rwkvq_nvfp4_blocked_scale_bytes": ctypes.c_int64, "rwkvq_actq_fp8_fused_scratch_bytes": ctypes.c_int64, "rwkvq_gemv_nvfp4_smem_bytes": ctypes.c_int64, "rwkvq_gemv_int4_group_smem_bytes": ctypes.c_int64, "rwkvq_workspace_bytes": ctypes.c_int64, "rwkvq_last_error_string": ctypes.c_char_p, "rwkvq_launch_count": ctypes.c_int64,
              "rwkvq_set_wait_limit_us": None, "rwkvq_gemv_set_trace": None, "rwkvq_tc_set_trace": None}
+
+
+
+class ProjDesc(ctypes.Structure):
+    """rwkvq_proj_desc of include/rwkvq.h."""
+    _fields_ = [("kind", _i32), ("x_dtype", _i32), ("x", _p * 3), ("awq", _p * 2), ("w", _p * 3), ("w_scale", _p * 3),
+                ("out", _p * 3), ("ldw", _i64), ("ldo", _i64), ("ldx", _i64), ("M", _i64), ("N", _i64), ("K", _i64),
+                ("div_mode", _i32), ("flags", _u32)]
+
+
+PROJ_FP8, PROJ_FP8_RKV, PROJ_INT8, PROJ_INT8_RKV = 0, 1, 2, 3
 
 _lib = None
 _device_checked = False
@@ -145,10 +157,16 @@ def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_fn_cache: dict = {}
+
+
 def call(name: str, *args) -> None:
     """Invoke an entry point; a non-zero status becomes RuntimeError carrying the library's message."""
-    require_device()
-    rc = getattr(lib(), name)(*args)
+    fn = _fn_cache.get(name)
+    if fn is None:
+        require_device()
+        fn = _fn_cache[name] = getattr(lib(), name)
+    rc = fn(*args)
     if rc != OK:
         raise RuntimeError(f"{name} failed with status {rc}: {last_error()}")
 

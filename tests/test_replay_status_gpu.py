@@ -266,3 +266,47 @@ def test_quantized_dispatch_routes_int4(mods):
     want = int4_ops.linear_int4(x, info)
     bits_equal(fp8_ops.linear_quantized(x, info), want)
     bits_equal(f.linear_quantized_fused(x, info), want)
+
+
+# ------------------------------------------------------------------------------------------------ decode layer helper
+@pytest.mark.parametrize("scheme", ["fp8", "int8"])
+@pytest.mark.parametrize("rows,dt", [(1, torch.bfloat16), (1, torch.float16), (4, torch.bfloat16)])
+def test_decode_layer_equals_dropin_calls(mods, scheme, rows, dt):
+    """DecodeLayer (descriptors bound once, one boundary crossing) against the drop-in calls: same kernels, same bits."""
+    abi, f, _ = mods
+    from rwkvq_layer import DecodeLayer
+    c, ff = 512, 1024
+    shapes = [(c, c)] * 4 + [(ff, c), (c, ff)]
+    infos = []
+    for i, (n, k) in enumerate(shapes):
+        if scheme == "fp8":
+            infos.append(dev(fp8_weight(120 + i, n, k)))
+        else:
+            q, s = O.q_int8_sym(gen(130 + i, (n, k), 0.02, torch.float16))
+            infos.append({"weight": q.cuda(), "tensor_scale": s.cuda(), "qtype": "int8"})
+    xs = [gen(140 + i, (rows, k), 1.0).to(dt).cuda() for i, k in enumerate((c, c, c, c, c, ff))]
+    layer = DecodeLayer(*infos, rows=rows, x_dtype=dt)
+    before = abi.launch_count()
+    got = [t.clone() for t in layer.all(*xs)]
+    assert abi.launch_count() - before == 4
+    if scheme == "fp8":
+        want = list(f.linear_rkv_fused(xs[0], xs[1], xs[2], *infos[:3]))
+    else:
+        want = list(f.linear_rkv_int8_fused(xs[0], xs[1], xs[2], *infos[:3]))
+    want += [f.linear_quantized_fused(x, i) for x, i in zip(xs[3:], infos[3:])]
+    for g, w in zip(got, want):
+        bits_equal(g, w.reshape(g.shape), "layer vs drop-in")
+    per_op = [*layer.rkv(*xs[:3]), layer.att_out(xs[3]), layer.ffn_key(xs[4]), layer.ffn_value(xs[5])]
+    for g, w in zip(per_op, want):
+        bits_equal(g, w.reshape(g.shape), "per projection")
+    graph, outs = layer.capture(*xs)
+    for t in xs:
+        t.mul_(0.5)
+    graph.replay()
+    torch.cuda.synchronize()
+    want2 = list(f.linear_rkv_fused(*xs[:3], *infos[:3]) if scheme == "fp8" else f.linear_rkv_int8_fused(*xs[:3], *infos[:3]))
+    want2 += [f.linear_quantized_fused(x, i) for x, i in zip(xs[3:], infos[3:])]
+    for g, w in zip(outs, want2):
+        bits_equal(g, w.reshape(g.shape), "graph replay")
+    with pytest.raises(ValueError):
+        layer.att_out(xs[3][:, :-16])
