@@ -53,6 +53,8 @@ extern "C" {
 #define RWKVQ_FLAG_INT8_SHARED_WSCALE 2u /* k and v use r's weight scale (reference defect, fused_fp8_gemm.py:855-857) */
 #define RWKVQ_FLAG_OUT_VIA_BF16 4u    /* round the result to bf16 before fp16 (fp8_ops.py:77-86)        */
 #define RWKVQ_FLAG_WSCALE_PER_ROW 16u  /* w_scale holds N values, one per output row (schemes.py:26-34 "fp8_perchannel"; no reference kernel reads them) */
+#define RWKVQ_FLAG_RELU2 32u       /* set by rwkvq_gemv_fp8_relu2 (ignored elsewhere): relu^2 in the epilogue, amax published  */
+#define RWKVQ_FLAG_AMAX_GIVEN 64u  /* set by rwkvq_gemv_fp8_preamax (ignored elsewhere): quantize with the published amax      */
 #define RWKVQ_FLAG_QUANT_FROM_BF16 8u /* quantize bf16(x) instead of x (the GEMM kernels read prep_x's bf16 copy, fused_fp8_gemm.py:248-250) */
 
 int32_t rwkvq_version(void);
@@ -126,6 +128,22 @@ int32_t rwkvq_prep3_x_int8(const void* xr, const void* xk, const void* xv, int32
 int32_t rwkvq_gemv_fp8(const void* x, int32_t x_dtype, const float* awq, const uint8_t* w, int64_t ldw,
                        const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                        int64_t ldx, int32_t div_mode, uint32_t flags, void* stream);
+
+/* The FFN of a layer, decode: key projection -> relu_square -> value projection (rwkv7_fast_v3a.py:1109, 1136-1144).
+ * rwkvq_gemv_fp8_relu2 is rwkvq_gemv_fp8 whose epilogue also applies the engine's relu_square to its fp16 result
+ * (cuda/rwkv7_fast_ops_fp16.cu:787-799: h = fp16(max(y, 0)^2) in fp32 arithmetic), stores h and publishes max|h| (over
+ * the bf16-rounded values with RWKVQ_FLAG_AMAX_AFTER_BF16, i.e. where the consumer takes its amax).
+ * rwkvq_gemv_fp8_preamax is rwkvq_gemv_fp8 on x = h that quantizes with the published amax instead of deriving it: no
+ * abs-max pass and no reduction in its prologue.  Results equal the three separate steps bit for bit.
+ * ffn_scratch: 8 bytes of device memory owned by the caller, 8-byte aligned, ZEROED ONCE; the relu2 launch accumulates
+ * into it, the preamax launch consumes and clears it, so one scratch serves every pair issued in order on a stream
+ * (also under CUDA-graph replay).  Pass the same flags to both (RWKVQ_FLAG_AMAX_AFTER_BF16 for M == 1). */
+int32_t rwkvq_gemv_fp8_relu2(const void* x, int32_t x_dtype, const uint8_t* w, int64_t ldw, const float* w_scale,
+                             void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                             uint32_t flags, void* ffn_scratch, void* stream);
+int32_t rwkvq_gemv_fp8_preamax(const void* x, int32_t x_dtype, const uint8_t* w, int64_t ldw, const float* w_scale,
+                               void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                               uint32_t flags, void* ffn_scratch, void* stream);
 
 /* linear_rkv_fused / fused_rkv_fp8_kernel (fused_fp8_gemm.py:944-1017, 264-334): r, k, v in ONE launch;
  * three activations, three amax, three weight scales.  awq_r / awq_k may be NULL. */

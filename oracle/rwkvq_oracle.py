@@ -454,6 +454,18 @@ def linear_rkv_fused(xr, xk, xv, wr, wk, wv, div=ieee_div):
     return tuple(outs)
 
 
+def relu_square(x: torch.Tensor) -> torch.Tensor:
+    """The engine's relu_square on fp16 (cuda/rwkv7_fast_ops_fp16.cu:787-799): fp16(max(float(x), 0)^2)."""
+    v = x.to(torch.float16).float().clamp(min=0.0)
+    return (v * v).to(torch.float16)
+
+
+def ffn_relu2_fp8(x, key_info, value_info, div=ieee_div):
+    """key projection -> relu_square -> value projection as the engine chains them (rwkv7_fast_v3a.py:1109, 1136-1144)."""
+    hid = relu_square(linear_fp8_fused(x, key_info, div))
+    return linear_fp8_fused(hid, value_info, div), hid
+
+
 def linear_fp8(x, weight_info, out_dtype=torch.float16):
     """fp8_ops.py:58-86 -- M > 512: fp16 -> bf16, prep_x_fp8, scaled matmul with a
     bf16 result, then the cast to fp16 (the result passes through bf16)."""

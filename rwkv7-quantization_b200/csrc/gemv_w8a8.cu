@@ -111,7 +111,7 @@ __device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* con
 // and n0+g+8 (values 2, 3) for the tokens 8i+2t and 8i+2t+1.
 template <int QT, int NT, typename T>
 __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[NT][4], float act_scale,
-                                           const float* xs, float wscale) {
+                                           const float* xs, float wscale, float& hmax) {
     // weight scale of this lane's two rows: one per matrix, or one per output row with RWKVQ_FLAG_WSCALE_PER_ROW
     float wlo = wscale, whi = wscale;
     if (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) {
@@ -133,7 +133,16 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
                 f = (float)c[i][j] * (xs[m] * ((j & 2) ? whi : wlo));
             }
             if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
-            a.out[mat][(int64_t)m * a.ldo + n] = __float2half_rn(f);
+            __half y = __float2half_rn(f);
+            if (a.flags & RWKVQ_FLAG_RELU2) {
+                // the engine's relu_square on the fp16 result: fp16(max(y, 0)^2) in fp32 arithmetic; its maximum (over the
+                // bf16-rounded values where the consumer takes its amax there) is published for the projection that follows
+                const float v = fmaxf(__half2float(y), 0.f);
+                y = __float2half_rn(v * v);
+                const float hv = __half2float(y);
+                hmax = fmaxf(hmax, (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? bf16_round(hv) : hv);
+            }
+            a.out[mat][(int64_t)m * a.ldo + n] = y;
         }
 }
 
@@ -265,7 +274,17 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     }
     __syncthreads();
     w8_mark(a, 3);
+    if ((a.flags & RWKVQ_FLAG_AMAX_GIVEN) && threadIdx.x == 0) {
+        // every thread of this CTA has used the published amax; the last CTA to say so clears it for the next producer
+        __threadfence();
+        if (atomicAdd(a.ffn_count, 1) == (int)gridDim.x - 1) {
+            *a.ffn_amax = 0.f;
+            __threadfence();
+            *a.ffn_count = 0;
+        }
+    }
 
+    float hmax = 0.f;
     int stage = 0;
     for (int r = 0; r < rounds; ++r) {
         T c[NT][4], c2[NT][4];
@@ -308,13 +327,25 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
                     for (int i = 0; i < NT; ++i)
 #pragma unroll
                         for (int j = 0; j < 4; ++j) c[i][j] += rb[(((warp + kk) * NT + i) * 4 + j) * 32 + lane];
-                store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale);
+                store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale, hmax);
             }
         } else if (tile < te) {
-            store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale);
+            store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale, hmax);
         }
     }
     cp_async_wait<0>();
+    if (a.flags & RWKVQ_FLAG_RELU2) {          // one atomic per CTA
+        hmax = warp_max(hmax);
+        __syncthreads();
+        if (lane == 0) sh[warp] = hmax;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float b = sh[0];
+#pragma unroll
+            for (int i = 1; i < kWarps; ++i) b = fmaxf(b, sh[i]);
+            atomic_max_nonneg(a.ffn_amax, b);
+        }
+    }
     w8_mark(a, 4);
 }
 
@@ -424,6 +455,7 @@ int32_t gemv_codes_run(W8Args a, int qt, cudaStream_t st, const char* who) {
     RWKVQ_REQUIRE(gemv_codes_fits(a.M, a.K), RWKVQ_E_SHAPE, "%s: M=%d K=%d does not fit the decode kernel (M <= 32, code tile in shared memory)", who, a.M, a.K);
     RWKVQ_REQUIRE((int64_t)a.nmat * ((a.N + 15) / 16) < (int64_t(1) << 27), RWKVQ_E_SHAPE, "%s: N too large", who);
     a.pitch = pitch_codes(a.K);
+    a.flags &= ~(RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN);
     return qt == QT_FP8 ? dispatch_mt<QT_FP8, RWKVQ_BF16, true>(a, st) : dispatch_mt<QT_INT8, RWKVQ_BF16, true>(a, st);
 }
 
@@ -466,8 +498,36 @@ int32_t rwkvq_gemv_fp8(const void* x, int32_t x_dtype, const float* awq, const u
     W8Args a{};
     a.x[0] = x; a.awq[0] = awq; a.w[0] = w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
     a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
-    a.div_mode = div_mode; a.flags = flags;
+    a.div_mode = div_mode; a.flags = flags & ~(RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN);
     return run_fused<QT_FP8>(a, x_dtype, (cudaStream_t)stream, "gemv_fp8");
+}
+
+/* FFN key projection with the engine's relu_square folded into its epilogue, and the FFN value projection that takes
+ * the amax the first one published.  ffn_scratch: 8 bytes owned by the caller, zeroed once; the pair leaves it zero. */
+int32_t rwkvq_gemv_fp8_relu2(const void* x, int32_t x_dtype, const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16,
+                             int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags,
+                             void* ffn_scratch, void* stream) {
+    RWKVQ_REQUIRE(ffn_scratch != nullptr && ((uintptr_t)ffn_scratch & 7) == 0, RWKVQ_E_BADARG, "gemv_fp8_relu2: ffn_scratch must be 8 aligned bytes");
+    W8Args a{};
+    a.x[0] = x; a.w[0] = w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
+    a.div_mode = div_mode; a.flags = (flags & ~RWKVQ_FLAG_AMAX_GIVEN) | RWKVQ_FLAG_RELU2;
+    a.ffn_amax = reinterpret_cast<float*>(ffn_scratch);
+    a.ffn_count = reinterpret_cast<int*>(ffn_scratch) + 1;
+    return run_fused<QT_FP8>(a, x_dtype, (cudaStream_t)stream, "gemv_fp8_relu2");
+}
+
+int32_t rwkvq_gemv_fp8_preamax(const void* x, int32_t x_dtype, const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16,
+                               int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags,
+                               void* ffn_scratch, void* stream) {
+    RWKVQ_REQUIRE(ffn_scratch != nullptr && ((uintptr_t)ffn_scratch & 7) == 0, RWKVQ_E_BADARG, "gemv_fp8_preamax: ffn_scratch must be 8 aligned bytes");
+    W8Args a{};
+    a.x[0] = x; a.w[0] = w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
+    a.div_mode = div_mode; a.flags = (flags & ~RWKVQ_FLAG_RELU2) | RWKVQ_FLAG_AMAX_GIVEN;
+    a.ffn_amax = reinterpret_cast<float*>(ffn_scratch);
+    a.ffn_count = reinterpret_cast<int*>(ffn_scratch) + 1;
+    return run_fused<QT_FP8>(a, x_dtype, (cudaStream_t)stream, "gemv_fp8_preamax");
 }
 
 int32_t rwkvq_gemv_fp8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const float* awq_r,
@@ -482,7 +542,7 @@ int32_t rwkvq_gemv_fp8_rkv(const void* xr, const void* xk, const void* xv, int32
     a.ws[0] = sr; a.ws[1] = sk; a.ws[2] = sv;
     a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
     a.nmat = 3; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
-    a.div_mode = div_mode; a.flags = flags;
+    a.div_mode = div_mode; a.flags = flags & ~(RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN);
     return run_fused<QT_FP8>(a, x_dtype, (cudaStream_t)stream, "gemv_fp8_rkv");
 }
 
@@ -492,7 +552,7 @@ int32_t rwkvq_gemv_int8(const void* x, int32_t x_dtype, const int8_t* w, int64_t
     W8Args a{};
     a.x[0] = x; a.w[0] = (const uint8_t*)w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16; a.acc[0] = acc_out;
     a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo; a.ldacc = ldacc;
-    a.div_mode = div_mode; a.flags = flags;
+    a.div_mode = div_mode; a.flags = flags & ~(RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN);
     RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "gemv_int8: ldacc < N");
     return run_fused<QT_INT8>(a, x_dtype, (cudaStream_t)stream, "gemv_int8");
 }
@@ -508,7 +568,7 @@ int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int3
     a.ws[0] = sr; a.ws[1] = shared ? sr : sk; a.ws[2] = shared ? sr : sv;
     a.out[0] = (__half*)out_r; a.out[1] = (__half*)out_k; a.out[2] = (__half*)out_v;
     a.nmat = 3; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
-    a.div_mode = div_mode; a.flags = flags;
+    a.div_mode = div_mode; a.flags = flags & ~(RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN);
     return run_fused<QT_INT8>(a, x_dtype, (cudaStream_t)stream, "gemv_int8_rkv");
 }
 

@@ -36,6 +36,8 @@ struct W8Args {
     int cpm;                  // decode GEMV: CTAs per matrix (grid = nmat * cpm)
     int tq, trem;             // decode GEMV: row tiles per CTA (quotient, remainder) within a matrix
     unsigned long long* trace;   // profiling aid: [grid][8] timestamps of the CTA's milestones, or null
+    float* ffn_amax;             // RELU2: maximum of the relu^2 results (atomic max); AMAX_GIVEN: the amax to quantize with
+    int* ffn_count;              // AMAX_GIVEN: CTAs that have read ffn_amax; the last one clears both words for the next pair
     int* status;                 // the library's per-device status word: RWKVQ_E_TIMEOUT if a bounded wait gave up
     unsigned long long wait_ns;  // wall-time limit of the bounded waits
 };
@@ -218,12 +220,17 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
         uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
         if (i0 < nvec) v0 = *reinterpret_cast<const uint4*>(x + ((int64_t)r0 * a.ldx + k0) * 2);
         if (i1 < nvec) v1 = *reinterpret_cast<const uint4*>(x + ((int64_t)r1 * a.ldx + k1) * 2);
-        float m = 0.f;
-        if (i0 < nvec) fp8_vec_amax<DT>(v0, awq, k0, a.div_mode, after, m);
-        if (i1 < nvec) fp8_vec_amax<DT>(v1, awq, k1, a.div_mode, after, m);
-        w8_mark(a, 5);
-        const float amax = fmaxf(cta_max(m, sh), 1e-12f);
-        w8_mark(a, 6);
+        float amax;
+        if (a.flags & RWKVQ_FLAG_AMAX_GIVEN) {          // published by the kernel that produced x: no abs-max pass, no reduction
+            amax = fmaxf(__ldcg(a.ffn_amax), 1e-12f);
+        } else {
+            float m = 0.f;
+            if (i0 < nvec) fp8_vec_amax<DT>(v0, awq, k0, a.div_mode, after, m);
+            if (i1 < nvec) fp8_vec_amax<DT>(v1, awq, k1, a.div_mode, after, m);
+            w8_mark(a, 5);
+            amax = fmaxf(cta_max(m, sh), 1e-12f);
+            w8_mark(a, 6);
+        }
         const float inv = div_mode_f32(448.f, amax, a.div_mode);
         if (i0 < nvec) *reinterpret_cast<uint4*>(xq + (size_t)r0 * a.pitch + k0 * 2) = e4m3x8_to_f16x8(fp8_vec_codes<DT>(v0, awq, k0, a.div_mode, inv));
         if (i1 < nvec) *reinterpret_cast<uint4*>(xq + (size_t)r1 * a.pitch + k1 * 2) = e4m3x8_to_f16x8(fp8_vec_codes<DT>(v1, awq, k1, a.div_mode, inv));
@@ -246,17 +253,22 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
                              ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(x + (int64_t)r * ldx2),
                                "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
+        const bool given = (a.flags & RWKVQ_FLAG_AMAX_GIVEN) != 0;
+        float amax = given ? __ldcg(a.ffn_amax) : 0.f;       // in flight while the copy lands
         if (!w8_staged_or_report(bar, a.status, a.wait_ns)) return -1.f;
+        if (!given) {
 #pragma unroll 1
-        for (int r = 0; r < a.M; ++r) {
-            const char* src = reinterpret_cast<const char*>(xq + (size_t)r * a.pitch);
+            for (int r = 0; r < a.M; ++r) {
+                const char* src = reinterpret_cast<const char*>(xq + (size_t)r * a.pitch);
 #pragma unroll 1
-            for (int i = threadIdx.x; i < kv; i += kThr)
-                fp8_vec_amax<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, after, m);
+                for (int i = threadIdx.x; i < kv; i += kThr)
+                    fp8_vec_amax<DT>(*reinterpret_cast<const uint4*>(src + (size_t)i * 16), awq, i << 3, a.div_mode, after, m);
+            }
+            w8_mark(a, 5);
+            amax = cta_max(m, sh);
+            w8_mark(a, 6);
         }
-        w8_mark(a, 5);
-        const float amax = fmaxf(cta_max(m, sh), 1e-12f);
-        w8_mark(a, 6);
+        amax = fmaxf(amax, 1e-12f);
         const float inv = div_mode_f32(448.f, amax, a.div_mode);
 #pragma unroll 1
         for (int r = 0; r < a.M; ++r) {

@@ -384,6 +384,49 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     return tuple(_finish(o, lead, n, out_dtype) for o in outs)
 
 
+_ffn_scratch: dict = {}
+
+
+def ffn_scratch(device) -> torch.Tensor:
+    """8 zeroed bytes per (device, stream) through which the key projection hands max|relu^2| to the value projection."""
+    key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
+    sc = _ffn_scratch.get(key)
+    if sc is None:
+        sc = _ffn_scratch[key] = torch.zeros(2, dtype=torch.int32, device=device)
+    return sc
+
+
+def ffn_relu2_fp8(x, key_info, value_info, out_dtype=torch.float16, return_hidden=False):
+    """The FFN of a layer on FP8 weights: value( relu_square( key(x) ) ), the chain the engine runs as three steps
+    (rwkv7_fast_v3a.py:1109, 1136-1144).  For decode-sized calls (rows that fit the one-launch kernel) relu_square is
+    folded into the key projection's epilogue and the value projection quantizes with the amax that epilogue publishes:
+    two launches, no separate relu kernel, no abs-max pass over the [M, F] hidden activations.  Other sizes run the
+    three steps.  Results equal the three-step chain bit for bit."""
+    wk, sk = _unpack(key_info)
+    wv, sv = _unpack(value_info)
+    x2 = _rows16(x)
+    m, k = x2.shape
+    f_dim, n = wk.shape[0], wv.shape[0]
+    if ROUTE == "auto" and 0 < m <= 8 and _gemv_fits(m, k) and _gemv_fits(m, f_dim) and not _codes_gemv_fits(m, k) and not _codes_gemv_fits(m, f_dim):
+        flags = abi.FLAG_AMAX_AFTER_BF16 if m == 1 else 0           # the M == 1 kernel takes its amax after the bf16 rounding
+        hid = torch.empty((m, f_dim), dtype=torch.float16, device=x2.device)
+        out = abi.new_out(m, n, x2.device)
+        sc = ffn_scratch(x2.device)
+        st = abi.stream_ptr()
+        abi.call("rwkvq_gemv_fp8_relu2", x2.data_ptr(), abi.dtype_code(x2), _u8(wk).data_ptr(), wk.stride(0), sk.data_ptr(),
+                 hid.data_ptr(), f_dim, m, f_dim, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, flags | _wscale_flag(sk, f_dim),
+                 sc.data_ptr(), st)
+        abi.call("rwkvq_gemv_fp8_preamax", hid.data_ptr(), abi.F16, _u8(wv).data_ptr(), wv.stride(0), sv.data_ptr(),
+                 out.data_ptr(), out.stride(0), m, n, f_dim, f_dim, abi.DEFAULT_DIV, flags | _wscale_flag(sv, n), sc.data_ptr(), st)
+        abi.after_call()
+    else:
+        hid = linear_quantized_fused(x2, {"weight": wk, "tensor_scale": sk, "qtype": "fp8"})
+        hid = (hid.float().clamp_(min=0.0) ** 2).to(torch.float16)       # relu_square: fp16(max(y, 0)^2), fp32 arithmetic
+        out = linear_quantized_fused(hid, {"weight": wv, "tensor_scale": sv, "qtype": "fp8"})
+    out = _finish(out.reshape(m, n), x.shape[:-1], n, out_dtype)
+    return (out, hid.reshape(*x.shape[:-1], f_dim)) if return_hidden else out
+
+
 # --------------------------------------------------------------------------- INT8
 def _int8_any(x2, w, w_scale, acc_out=None):
     m, k = x2.shape

@@ -310,3 +310,34 @@ def test_decode_layer_equals_dropin_calls(mods, scheme, rows, dt):
         bits_equal(g, w.reshape(g.shape), "graph replay")
     with pytest.raises(ValueError):
         layer.att_out(xs[3][:, :-16])
+
+
+# ------------------------------------------------------------------------------------------------ FFN pair with relu^2 folded in
+@pytest.mark.parametrize("m,dt", [(1, torch.bfloat16), (1, torch.float16), (3, torch.bfloat16), (8, torch.float16), (20, torch.bfloat16)])
+def test_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
+    """key -> relu_square -> value: the fused pair (relu^2 in the key epilogue, published amax) equals the three steps
+    run separately bit for bit, and the oracle's chain within 1e-2.  Twice in a row: the scratch is left clean."""
+    abi, f, _ = mods
+    c, ff = 768, 3072
+    key, val = fp8_weight(150, ff, c), fp8_weight(151, c, ff)
+    dk, dv = dev(key), dev(val)
+    for rep in range(2):
+        x = gen(152 + m + rep, (m, c), 1.0 + rep).to(dt)
+        before = abi.launch_count()
+        out, hid = f.ffn_relu2_fp8(x.cuda(), dk, dv, return_hidden=True)
+        launches = abi.launch_count() - before
+        y = f.linear_quantized_fused(x.cuda(), dk)
+        h = (y.float().clamp(min=0) ** 2).half()
+        bits_equal(hid, h, "hidden")
+        bits_equal(out, f.linear_quantized_fused(h, dv), "ffn output")
+        want, want_h = O.ffn_relu2_fp8(x, key, val, lib_div(abi))
+        assert rel_err(hid, want_h) <= 2e-2 and rel_err(out, want) <= 2e-2      # the square doubles the relative error of y
+        if m <= 8:
+            assert launches == 2
+            assert int(f.ffn_scratch("cuda").abs().sum().item()) == 0
+    if m <= 8:
+        from rwkvq_layer import DecodeLayer
+        sq = dev(fp8_weight(153, c, c))
+        layer = DecodeLayer(sq, sq, sq, sq, dk, dv, rows=m, x_dtype=dt)
+        out2, hid2 = layer.ffn(x.cuda())
+        bits_equal(out2.reshape(out.shape), out, "DecodeLayer.ffn")
