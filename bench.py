@@ -323,6 +323,37 @@ def run_ours(args, rank, world, local_rank):
                                 "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),
                                 "peak_note": "2 x the measured dense bf16 cuBLAS rate (fp8 runs at twice the bf16 rate)"}}
         del xp
+    # FFN pair (key -> relu_square -> value) at one token: three separate steps against the fused pair, CUDA-graph replay over
+    # all layers' FFN weights (4.3 GB of distinct weights per pass)
+    ffn_pair = None
+    if args.tokens == 1:
+        import fused_fp8_gemm as f
+        with torch.cuda.stream(stream):
+            xf = x["xf"]
+
+            def three_steps():
+                for L in layers:
+                    h = f.linear_quantized_fused(xf, L["ffn_k"])
+                    h = (h.float().clamp_(min=0.0) ** 2).to(torch.float16)      # stand-in for the engine's relu_square kernel
+                    f.linear_quantized_fused(h, L["ffn_v"])
+
+            def fused_pair():
+                for L in layers:
+                    f.ffn_relu2_fp8(xf, L["ffn_k"], L["ffn_v"])
+            res = {}
+            for name, fn in (("three_steps", three_steps), ("fused_pair", fused_pair)):
+                fn()
+                stream.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    fn()
+                for _ in range(3):
+                    g.replay()
+                res[name] = timed(g.replay, args.steps, dist_on) / args.steps * 1e3 / args.layers
+            pair_bytes = gemv_bytes(1, F, C) + gemv_bytes(1, C, F)
+            ffn_pair = {"M": 1, "three_steps_us_per_layer": round(res["three_steps"], 2), "fused_pair_us_per_layer": round(res["fused_pair"], 2),
+                        "fused_pair_frac_hbm": round(pair_bytes / res["fused_pair"] / 1e3 / peaks()["hbm_gbs"], 4),
+                        "note": "three steps = key projection, relu_square (torch ops standing in for the engine's kernel), value projection"}
     colsplit = None
     if dist_on and not args.no_colsplit:
         with torch.cuda.stream(stream):
@@ -360,6 +391,7 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks.summary(),
         "prefill": prefill,
         "colsplit": colsplit,
+        "ffn_pair": ffn_pair,
     }
     if rank == 0:
         if world == 1 and not args.no_cpu:

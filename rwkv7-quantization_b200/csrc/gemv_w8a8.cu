@@ -109,7 +109,7 @@ __device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* con
 
 // Results of one 16-row tile, straight from the accumulator fragments: lane (g, t) holds weight rows n0+g (values 0, 1)
 // and n0+g+8 (values 2, 3) for the tokens 8i+2t and 8i+2t+1.
-template <int QT, int NT, typename T>
+template <int QT, int NT, bool RELU2, typename T>
 __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[NT][4], float act_scale,
                                            const float* xs, float wscale, float& hmax) {
     // weight scale of this lane's two rows: one per matrix, or one per output row with RWKVQ_FLAG_WSCALE_PER_ROW
@@ -134,7 +134,7 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
             }
             if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
             __half y = __float2half_rn(f);
-            if (a.flags & RWKVQ_FLAG_RELU2) {
+            if constexpr (RELU2) {
                 // the engine's relu_square on the fp16 result: fp16(max(y, 0)^2) in fp32 arithmetic; its maximum (over the
                 // bf16-rounded values where the consumer takes its amax there) is published for the projection that follows
                 const float v = fmaxf(__half2float(y), 0.f);
@@ -153,7 +153,9 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
 // before griddepcontrol.wait.
 // PRE: the activations arrive as codes (a.codes / a.ascale, quantized once by an earlier launch) and the prologue is
 // one bulk copy per row into the tile -- no arithmetic, M*K bytes per CTA; otherwise the prologue quantizes x itself.
-template <int QT, int DT, int NT, int S, bool PRE>
+// FFN: 0 = plain projection; 1 = relu^2 in the epilogue and its maximum published (rwkvq_gemv_fp8_relu2); 2 = quantize with
+// the published amax (rwkvq_gemv_fp8_preamax).  Separate instantiations: the plain kernel carries none of that code.
+template <int QT, int DT, int NT, int S, bool PRE, int FFN = 0>
 __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     using T = typename Acc<QT>::T;
     constexpr int D = kGemvD;
@@ -263,7 +265,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
             return;
         }
     } else if constexpr (QT == QT_FP8) {
-        const float amax = quantize_fp8_to_smem<DT, WIDE>(a, mat, xq, sh, xbar);
+        const float amax = quantize_fp8_to_smem<DT, WIDE, FFN == 2>(a, mat, xq, sh, xbar);
         if (amax < 0.f) {          // the staging copy timed out (reported): drain the weight ring and stop
             cp_async_wait<0>();
             return;
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
     }
     __syncthreads();
     w8_mark(a, 3);
-    if ((a.flags & RWKVQ_FLAG_AMAX_GIVEN) && threadIdx.x == 0) {
+    if (FFN == 2 && threadIdx.x == 0) {
         // every thread of this CTA has used the published amax; the last CTA to say so clears it for the next producer
         __threadfence();
         if (atomicAdd(a.ffn_count, 1) == (int)gridDim.x - 1) {
@@ -327,14 +329,14 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
                     for (int i = 0; i < NT; ++i)
 #pragma unroll
                         for (int j = 0; j < 4; ++j) c[i][j] += rb[(((warp + kk) * NT + i) * 4 + j) * 32 + lane];
-                store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale, hmax);
+                store_tile<QT, NT, FFN == 1>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale, hmax);
             }
         } else if (tile < te) {
-            store_tile<QT, NT>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale, hmax);
+            store_tile<QT, NT, FFN == 1>(a, mat, tile << 4, g, t, c, out_scale, xs, wscale, hmax);
         }
     }
     cp_async_wait<0>();
-    if (a.flags & RWKVQ_FLAG_RELU2) {          // one atomic per CTA
+    if constexpr (FFN == 1) {          // one atomic per CTA
         hmax = warp_max(hmax);
         __syncthreads();
         if (lane == 0) sh[warp] = hmax;
@@ -355,9 +357,9 @@ static size_t smem_bytes(int NT, int M, int pitch, int S) {
 
 constexpr size_t kFusedSmemMax = 224 * 1024;    // of the 227 KB a CTA may opt in to
 
-template <int QT, int DT, int NT, int S, bool PRE>
+template <int QT, int DT, int NT, int S, bool PRE, int FFN = 0>
 static int32_t launch_one(W8Args a, size_t smem, cudaStream_t st) {
-    auto kern = gemv_w8a8_kernel<QT, DT, NT, S, PRE>;
+    auto kern = gemv_w8a8_kernel<QT, DT, NT, S, PRE, FFN>;
     // per instantiation and device: opt in to large dynamic shared memory and ask how many CTAs fit on an SM
     static thread_local int cfg_dev = -1;
     static thread_local size_t cfg_smem = ~size_t(0);
@@ -411,22 +413,28 @@ constexpr size_t kTwoPerSm = 110 * 1024;     // shared memory per CTA that still
 // Ring depth: the deepest ring (5, 4, 3 stages) that leaves room for two CTAs per SM; failing that, one CTA per SM with
 // the deepest ring that fits beside the activation tile (long rows, many tokens) -- one CTA with a deep ring measured
 // faster than two CTAs with two stages.
-template <int QT, int DT, int NT, bool PRE>
+template <int QT, int DT, int NT, bool PRE, int FFN = 0>
 static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
     const size_t s5 = smem_bytes(NT, a.M, a.pitch, 5), s4 = smem_bytes(NT, a.M, a.pitch, 4), s3 = smem_bytes(NT, a.M, a.pitch, 3),
                  s2 = smem_bytes(NT, a.M, a.pitch, 2);
-    if (s5 <= kTwoPerSm) return launch_one<QT, DT, NT, 5, PRE>(a, s5, st);
-    if (s4 <= kTwoPerSm) return launch_one<QT, DT, NT, 4, PRE>(a, s4, st);
-    if (s3 <= kTwoPerSm) return launch_one<QT, DT, NT, 3, PRE>(a, s3, st);
+    if (s5 <= kTwoPerSm) return launch_one<QT, DT, NT, 5, PRE, FFN>(a, s5, st);
+    if (s4 <= kTwoPerSm) return launch_one<QT, DT, NT, 4, PRE, FFN>(a, s4, st);
+    if (s3 <= kTwoPerSm) return launch_one<QT, DT, NT, 3, PRE, FFN>(a, s3, st);
     RWKVQ_REQUIRE(s2 <= kFusedSmemMax, RWKVQ_E_SHAPE, "gemv_w8a8: M*K = %d*%d does not fit the kernel's shared memory", a.M, a.K);
-    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, NT, 5, PRE>(a, s5, st);
-    if (s4 <= kFusedSmemMax) return launch_one<QT, DT, NT, 4, PRE>(a, s4, st);
-    if (s3 <= kFusedSmemMax) return launch_one<QT, DT, NT, 3, PRE>(a, s3, st);
-    return launch_one<QT, DT, NT, 2, PRE>(a, s2, st);
+    if (s5 <= kFusedSmemMax) return launch_one<QT, DT, NT, 5, PRE, FFN>(a, s5, st);
+    if (s4 <= kFusedSmemMax) return launch_one<QT, DT, NT, 4, PRE, FFN>(a, s4, st);
+    if (s3 <= kFusedSmemMax) return launch_one<QT, DT, NT, 3, PRE, FFN>(a, s3, st);
+    return launch_one<QT, DT, NT, 2, PRE, FFN>(a, s2, st);
 }
 
 template <int QT, int DT, bool PRE>
 static int32_t dispatch_mt(const W8Args& a, cudaStream_t st) {
+    if constexpr (QT == QT_FP8 && !PRE) {       // the FFN pair: up to 8 rows
+        if (a.flags & (RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN)) {
+            RWKVQ_REQUIRE(a.M <= 8 && a.nmat == 1, RWKVQ_E_SHAPE, "gemv_fp8 relu2 / preamax: at most 8 rows, got %d", a.M);
+            return (a.flags & RWKVQ_FLAG_RELU2) ? dispatch_s<QT, DT, 1, PRE, 1>(a, st) : dispatch_s<QT, DT, 1, PRE, 2>(a, st);
+        }
+    }
     if (a.M <= 8) return dispatch_s<QT, DT, 1, PRE>(a, st);
     if (a.M <= 16) return dispatch_s<QT, DT, 2, PRE>(a, st);
     return dispatch_s<QT, DT, 4, PRE>(a, st);

@@ -202,7 +202,8 @@ __device__ __forceinline__ uint4 ldg_l2_16(const void* p) {
 
 // Returns max(amax, 1e-12), or a negative value if the staging copy timed out (the CTA must then return).
 // The tile holds the codes as f16 values (2 bytes each, no conversion in the K loop).
-template <int DT, bool WIDE>
+// GIVEN: the amax comes from a.ffn_amax (published by the kernel that produced x): no abs-max pass, no reduction.
+template <int DT, bool WIDE, bool GIVEN = false>
 __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* sh, uint64_t* bar) {
     const char* x = reinterpret_cast<const char*>(a.x[mat]);
     const float* awq = a.awq[mat];
@@ -221,7 +222,7 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
         if (i0 < nvec) v0 = *reinterpret_cast<const uint4*>(x + ((int64_t)r0 * a.ldx + k0) * 2);
         if (i1 < nvec) v1 = *reinterpret_cast<const uint4*>(x + ((int64_t)r1 * a.ldx + k1) * 2);
         float amax;
-        if (a.flags & RWKVQ_FLAG_AMAX_GIVEN) {          // published by the kernel that produced x: no abs-max pass, no reduction
+        if constexpr (GIVEN) {
             amax = fmaxf(__ldcg(a.ffn_amax), 1e-12f);
         } else {
             float m = 0.f;
@@ -253,10 +254,9 @@ __device__ float quantize_fp8_to_smem(const W8Args& a, int mat, uint8_t* xq, flo
                              ::"r"((uint32_t)__cvta_generic_to_shared(xq + (size_t)r * a.pitch)), "l"(x + (int64_t)r * ldx2),
                                "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
-        const bool given = (a.flags & RWKVQ_FLAG_AMAX_GIVEN) != 0;
-        float amax = given ? __ldcg(a.ffn_amax) : 0.f;       // in flight while the copy lands
+        float amax = GIVEN ? __ldcg(a.ffn_amax) : 0.f;       // in flight while the copy lands
         if (!w8_staged_or_report(bar, a.status, a.wait_ns)) return -1.f;
-        if (!given) {
+        if constexpr (!GIVEN) {
 #pragma unroll 1
             for (int r = 0; r < a.M; ++r) {
                 const char* src = reinterpret_cast<const char*>(xq + (size_t)r * a.pitch);
