@@ -323,6 +323,29 @@ def run_ours(args, rank, world, local_rank):
                                 "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),
                                 "peak_note": "2 x the measured dense bf16 cuBLAS rate (fp8 runs at twice the bf16 rate)"}}
         del xp
+    # per-shape breakdown: each of the four launch kinds of the step alone, graph replay over the 32 layers' weights
+    per_shape = {}
+    with torch.cuda.stream(stream):
+        import fused_fp8_gemm as f
+        m = args.tokens
+        kinds = {
+            "att_rkv": (lambda L: f.linear_rkv_fused(x["xr"], x["xk"], x["xv"], L["r"], L["k"], L["v"]), 3 * gemv_bytes(m, C, C)),
+            "att_out": (lambda L: f.linear_quantized_fused(x["xo"], L["o"]), gemv_bytes(m, C, C)),
+            "ffn_key": (lambda L: f.linear_quantized_fused(x["xf"], L["ffn_k"]), gemv_bytes(m, F, C)),
+            "ffn_value": (lambda L: f.linear_quantized_fused(x["xg"], L["ffn_v"]), gemv_bytes(m, C, F)),
+        }
+        for name, (fn, nb) in kinds.items():
+            for L in layers:
+                fn(L)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for L in layers:
+                    fn(L)
+            for _ in range(3):
+                g.replay()
+            us = timed(g.replay, args.steps, dist_on) / args.steps * 1e3 / args.layers
+            per_shape[name] = {"us": round(us, 2), "bytes": nb, "frac": round(nb / us / 1e3 / peaks()["hbm_gbs"], 4)}
     # FFN pair (key -> relu_square -> value) at one token: three separate steps against the fused pair, CUDA-graph replay over
     # all layers' FFN weights (4.3 GB of distinct weights per pass)
     ffn_pair = None
@@ -377,7 +400,10 @@ def run_ours(args, rank, world, local_rank):
                      "frac": round(per_gpu / pk["hbm_gbs"], 4), "traffic": DRAM_TRAFFIC_PER_LAUNCH if args.layers == LAYERS else None,
                      "peak_source": pk["source"],
                      "kernel": "gemv_w8a8_kernel<fp8>", "bytes_per_launch": nbytes // (4 * args.layers),
-                     "us_per_launch": round(per_step * 1e3 / (4 * args.layers), 3)},
+                     "us_per_launch": round(per_step * 1e3 / (4 * args.layers), 3),
+                     "launch_note": "bytes_per_launch / us_per_launch are averages over the four launch kinds of a layer; per_shape "
+                                    "times each kind alone (same kernel, graph replay over the 32 layers' weights)",
+                     "per_shape": per_shape},
         "e2e": {"value": round(gbs_e2e, 2), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()),
                 "d2h_bytes_per_step": y_host.numel() * y_host.element_size(),

@@ -438,7 +438,9 @@ void rwkvq_set_wait_limit_us(int64_t microseconds);
 int32_t rwkvq_device_status(int32_t* host_status, int32_t clear);
 int32_t rwkvq_selftest_timeout(int32_t* status, void* scratch4, int64_t limit_us, int32_t mode, void* stream);
 /* Profiling aids: a device buffer ([grid][8] uint64 for the decode GEMV, [grid][16] for the tensor-memory kernels) that
- * every later launch stamps with %globaltimer values at its CTAs' milestones; NULL (the default) switches them off. */
+ * every later launch stamps with %globaltimer values at its CTAs' milestones; NULL (the default) switches them off.
+ * The stamps are compiled into the kernels only when the library is built with -DRWKVQ_TRACE (build_ext.py --trace);
+ * in a regular build these two calls have no effect. */
 void rwkvq_gemv_set_trace(void* device_buffer);
 void rwkvq_tc_set_trace(void* device_buffer);
 

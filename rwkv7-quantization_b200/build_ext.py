@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Build librwkvq.so (hand-written CUDA for sm_100a, C ABI declared in include/rwkvq.h) in-tree with nvcc.
 
-    python build_ext.py [--force] [--verbose]
+    python build_ext.py [--force] [--verbose] [--trace]
 
 Each csrc/*.cu is compiled to an object file (in parallel) and linked into librwkvq.so next to this file.
 Nothing is cross-compiled for any other architecture: the kernels use sm_100a-only instructions.
@@ -28,7 +28,9 @@ def _newer(src, dst, deps):
     return any(os.path.getmtime(p) > t for p in [src] + deps)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, trace=False):
+    """trace=True compiles the kernels' milestone stamps in (-DRWKVQ_TRACE, see rwkvq_gemv_set_trace); rebuild with --force
+    when switching."""
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     deps = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
@@ -36,7 +38,7 @@ def build(force=False, verbose=False):
     for s in srcs:
         o = os.path.join(OBJ, os.path.basename(s)[:-3] + ".o")
         if force or _newer(s, o, deps):
-            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [NVCC] + FLAGS + (["-DRWKVQ_TRACE"] if trace else []) + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append((s, cmd))
 
     def run(job):
@@ -61,4 +63,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))

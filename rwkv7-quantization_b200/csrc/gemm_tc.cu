@@ -140,8 +140,12 @@ struct TcShared {
     uint64_t xbar;             // FUSED: the activation block has landed in shared memory
 };
 
-__device__ __forceinline__ void tc_mark(const TcArgs& a, int slot) {
+__device__ __forceinline__ void tc_mark(const TcArgs& a, int slot) {      // profiling aid, only with -DRWKVQ_TRACE
+#ifdef RWKVQ_TRACE
     if (a.trace) a.trace[(size_t)blockIdx.x * 16 + slot] = global_ns();
+#else
+    (void)a; (void)slot;
+#endif
 }
 
 __device__ __forceinline__ void tc_abort(TcShared& s, const TcArgs& a) {

@@ -42,13 +42,19 @@ struct W8Args {
     unsigned long long wait_ns;  // wall-time limit of the bounded waits
 };
 
-// profiling aid: thread 0 of a CTA stamps milestone `slot` (0..7) with the global timer when a trace buffer is set
+// profiling aid, compiled in only with -DRWKVQ_TRACE (the decode kernels run for a few microseconds and every
+// instruction between their entry and their first MMA shows in the launch time): thread 0 of a CTA stamps milestone
+// `slot` (0..7) with the global timer when a trace buffer is set
 __device__ __forceinline__ void w8_mark(const W8Args& a, int slot) {
+#ifdef RWKVQ_TRACE
     if (a.trace && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
         a.trace[(size_t)blockIdx.x * 8 + slot] = t;
     }
+#else
+    (void)a; (void)slot;
+#endif
 }
 
 template <int QT>
