@@ -18,6 +18,12 @@ import torch
 
 QUANTIZED_COMPONENTS = {"att_r", "att_k", "att_v", "att_o", "ffn_k", "ffn_v"}
 INT4_MAX = 7.0
+
+
+def _div(t: torch.Tensor, value: float) -> torch.Tensor:
+    """t / value as an IEEE division on every device (the divisor is a tensor on t's device; torch's CUDA kernel would
+    multiply by the rounded reciprocal of a Python scalar): the quantizers give the same bits on the CPU and on a GPU."""
+    return t / torch.full((), value, dtype=t.dtype if t.is_floating_point() else torch.float32, device=t.device)
 _NAMES = {("att", "receptance"): "att_r", ("att", "key"): "att_k", ("att", "value"): "att_v",
           ("att", "output"): "att_o", ("ffn", "key"): "ffn_k", ("ffn", "value"): "ffn_v"}
 
@@ -44,7 +50,7 @@ def quantize_to_int4_per_tensor(w: torch.Tensor):
     """(packed uint8 [N, K/2], scale fp32 scalar); W ~ signed_nibble * scale (int4/quantize_int4.py:51-71)."""
     w = w.float()
     assert w.shape[1] % 2 == 0, f"Output dim must be even, got {w.shape[1]}"
-    scale = (w.abs().max() / INT4_MAX).clamp(min=1e-12)
+    scale = _div(w.abs().max(), INT4_MAX).clamp(min=1e-12)
     q = (w / scale).round().clamp(-8, 7).to(torch.int8) & 0xF
     return _pack_pairs(q), scale.to(torch.float32)
 
@@ -76,7 +82,7 @@ def quantize_to_int4_groupwise(w: torch.Tensor, group_size: int = 128):
     assert k % 2 == 0, f"Output dim must be even, got {k}"
     g = w.reshape(n, k // group_size, group_size)
     lo = g.amin(dim=2, keepdim=True)
-    step = ((g.amax(dim=2, keepdim=True) - lo) / 15.0).clamp(min=1e-12)
+    step = _div(g.amax(dim=2, keepdim=True) - lo, 15.0).clamp(min=1e-12)
     q = ((g - lo) / step).round().clamp(0, 15).reshape(n, k)
     return {"packed": _pack_pairs(q), "scales": step.squeeze(2).float(), "zeros": lo.squeeze(2).float(),
             "group_size": group_size}

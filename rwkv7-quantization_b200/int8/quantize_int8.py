@@ -11,7 +11,7 @@ import os
 
 import torch
 
-from int4.quantize_int4 import QUANTIZED_COMPONENTS, classify_weight  # same six projections  # noqa: F401
+from int4.quantize_int4 import QUANTIZED_COMPONENTS, _div, classify_weight  # same six projections  # noqa: F401
 
 INT8_MAX = 127.0
 
@@ -19,7 +19,7 @@ INT8_MAX = 127.0
 def quantize_to_int8_per_tensor(w: torch.Tensor):
     """(int8 codes, fp32 scale); W ~ codes * scale (int8/quantize_int8.py:51-62)."""
     w = w.float()
-    scale = (w.abs().max() / INT8_MAX).clamp(min=1e-12)
+    scale = _div(w.abs().max(), INT8_MAX).clamp(min=1e-12)
     return (w / scale).round().clamp(-128, 127).to(torch.int8), scale.to(torch.float32)
 
 

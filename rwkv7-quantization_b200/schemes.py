@@ -14,9 +14,16 @@ import torch
 _TINY = 1e-12
 
 
+def _div(t: torch.Tensor, value: float) -> torch.Tensor:
+    """t / value with the divisor as a tensor on t's device: an IEEE division on the CPU and on a GPU alike (torch's CUDA
+    kernel turns a division by a Python scalar into a product with the rounded reciprocal, one ulp off now and then), so
+    the quantizers give the same bits wherever they run."""
+    return t / torch.full((), value, dtype=t.dtype if t.is_floating_point() else torch.float32, device=t.device)
+
+
 def _absmax_scale(w: torch.Tensor, qmax: float, dim=None) -> torch.Tensor:
     a = w.abs().max() if dim is None else w.abs().amax(dim=dim, keepdim=True)
-    return (a.clamp(min=_TINY) / qmax).float()
+    return _div(a.clamp(min=_TINY), qmax).float()
 
 
 def _q_fp8(w: torch.Tensor, **kw):
@@ -76,7 +83,7 @@ def _q_int4_gw(w: torch.Tensor, group_size: int = 128, **kw):
         f = torch.nn.functional.pad(f, (0, short))
     g = f.reshape(rows, -1, group_size)
     lo, hi = g.amin(dim=2, keepdim=True), g.amax(dim=2, keepdim=True)
-    step = ((hi - lo) / 15.0).clamp(min=_TINY)
+    step = _div(hi - lo, 15.0).clamp(min=_TINY)
     back = (((g - lo) / step).round().clamp(0, 15) * step + lo).reshape(rows, -1)[:, :cols]
     if back.numel() == w.numel():
         back = back.reshape(w.shape)
