@@ -377,6 +377,37 @@ def run_ours(args, rank, world, local_rank):
             ffn_pair = {"M": 1, "three_steps_us_per_layer": round(res["three_steps"], 2), "fused_pair_us_per_layer": round(res["fused_pair"], 2),
                         "fused_pair_frac_hbm": round(pair_bytes / res["fused_pair"] / 1e3 / peaks()["hbm_gbs"], 4),
                         "note": "three steps = key projection, relu_square (torch ops standing in for the engine's kernel), value projection"}
+            if not args.no_prefill:
+                # the same pair for one 2048-token sequence (eager calls, four layers' weights in turn)
+                xp = torch.randn((PREFILL_T, C), device=dev).to(torch.bfloat16)
+                some = layers[:4]
+
+                def three_steps_p():
+                    for L in some:
+                        h = f.linear_quantized_fused(xp, L["ffn_k"])
+                        h = (h.float().clamp_(min=0.0) ** 2).to(torch.float16)
+                        f.linear_quantized_fused(h, L["ffn_v"])
+
+                def relu_only():
+                    for L in some:
+                        (hbuf.float().clamp_(min=0.0) ** 2).to(torch.float16)
+
+                def fused_pair_p():
+                    for L in some:
+                        f.ffn_relu2_fp8(xp, L["ffn_k"], L["ffn_v"])
+                hbuf = torch.randn((PREFILL_T, F), device=dev).half()
+                resp = {}
+                for name, fn in (("three_steps", three_steps_p), ("relu_only", relu_only), ("fused_pair", fused_pair_p)):
+                    for _ in range(2):
+                        fn()
+                    resp[name] = timed(fn, 3, dist_on) / 3 * 1e3 / len(some)
+                fl = 2 * PREFILL_T * 2 * C * F
+                ffn_pair["prefill_2048"] = {
+                    "three_steps_us_per_layer": round(resp["three_steps"], 1), "of_which_relu_square_torch_us": round(resp["relu_only"], 1),
+                    "fused_pair_us_per_layer": round(resp["fused_pair"], 1), "fused_pair_TFLOPs": round(fl / resp["fused_pair"] / 1e6, 1),
+                    "note": "the engine's relu_square is ONE kernel (one read and one write of [2048, 16384] fp16); the torch stand-in "
+                            "timed here takes several passes, so compare the fused pair with three_steps minus relu_square plus one pass"}
+                del xp, hbuf
     colsplit = None
     if dist_on and not args.no_colsplit:
         with torch.cuda.stream(stream):

@@ -145,6 +145,18 @@ int32_t rwkvq_gemv_fp8_preamax(const void* x, int32_t x_dtype, const uint8_t* w,
                                void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
                                uint32_t flags, void* ffn_scratch, void* stream);
 
+/* The same pair for many rows (prefill): rwkvq_tc_gemm_fp8_relu2 is rwkvq_tc_gemm_fp8 (tiled form, M >= 17) with
+ * relu_square and the amax accumulation in its epilogue; rwkvq_actq_fp8_given then makes the codes of h with the
+ * published amax -- purely elementwise, no abs-max pass and no grid rendezvous -- writes its own copies amax_out[0]
+ * (and scale_out[0] = amax/448 under div_mode, optional) for the value GEMM and clears ffn_scratch. */
+int32_t rwkvq_tc_gemm_fp8_relu2(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,
+                                const uint8_t* w, int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo,
+                                int64_t M, int64_t N, int64_t K, int32_t div_mode, uint32_t flags, void* ffn_scratch,
+                                void* workspace, int64_t workspace_bytes, void* stream);
+int32_t rwkvq_actq_fp8_given(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes,
+                             int64_t ldc, float* amax_out, float* scale_out, void* ffn_scratch, int32_t div_mode,
+                             uint32_t flags, void* stream);
+
 /* linear_rkv_fused / fused_rkv_fp8_kernel (fused_fp8_gemm.py:944-1017, 264-334): r, k, v in ONE launch;
  * three activations, three amax, three weight scales.  awq_r / awq_k may be NULL. */
 int32_t rwkvq_gemv_fp8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const float* awq_r,

@@ -590,6 +590,58 @@ __global__ void __launch_bounds__(kSmallThreads, 1) actq_fp8_small_kernel(const 
     }
 }
 
+// FP8 codes of h with an amax that the PRODUCER of h published (the FFN key projection with relu^2 in its epilogue):
+// purely elementwise -- no abs-max pass, no grid rendezvous -- so it is launched with programmatic dependent launch.
+// ffn[0] = the published amax (float), ffn[1] = count of CTAs that have read it; the last one clears both for the next
+// producer.  amax_out / scale_out are this call's own copies for the GEMM that follows.
+template <int DT>
+__global__ void __launch_bounds__(kThreads) quant_fp8_given_kernel(const void* x, uint8_t* codes, float* amax_out, float* scale_out,
+                                                                   float* ffn, int M, int64_t K, int64_t ldx, int64_t ldc, int div_mode,
+                                                                   int from_bf16) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float amax = __ldcg(ffn);
+    const float inv = scale_inv(448.f, fmaxf(amax, 1e-12f), div_mode);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        *amax_out = amax;
+        if (scale_out) *scale_out = scale_fwd(amax, 448.f, div_mode);
+    }
+    const int64_t kv = K >> 3, nvec = (int64_t)M * kv;
+    for (int64_t i0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; i0 < nvec; i0 += (int64_t)gridDim.x * kThreads * 4) {
+        uint4 v[4];
+        int64_t r[4], c[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t idx = i0 + (int64_t)j * gridDim.x * kThreads;
+            r[j] = idx / kv;
+            c[j] = idx - r[j] * kv;
+            if (idx < nvec) v[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(x) + (r[j] * ldx + c[j] * 8) * 2);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (i0 + (int64_t)j * gridDim.x * kThreads >= nvec) continue;
+            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            uint32_t q[4];
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                float2 f = cvt2<DT>(w[p]);
+                if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                q[p] = e4m3x2(f.x * inv, f.y * inv);
+            }
+            *reinterpret_cast<uint2*>(codes + r[j] * ldc + c[j] * 8) = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+        }
+    }
+    __syncthreads();                                    // every thread of this CTA has used the amax
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(reinterpret_cast<int*>(ffn) + 1, 1) == (int)gridDim.x - 1) {
+            ffn[0] = 0.f;
+            __threadfence();
+            reinterpret_cast<int*>(ffn)[1] = 0;
+        }
+    }
+}
+
 // A kernel whose only job is to let a bounded wait run out: one CTA waits for an mbarrier phase that nothing
 // completes (mode 0) or for a flag value that nothing stores (mode 1), gives up after `limit_ns`, records
 // RWKVQ_E_TIMEOUT in *status and returns normally -- the path every kernel of this library takes when a producer
@@ -831,6 +883,37 @@ int32_t rwkvq_actq_fp8_fused3(const void* xr, const void* xk, const void* xv, in
 
 
 void rwkvq_set_wait_limit_us(int64_t microseconds) { wait_limit_override().store(microseconds > 0 ? microseconds : -1); }
+
+int32_t rwkvq_actq_fp8_given(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, uint8_t* codes, int64_t ldc, float* amax_out,
+                             float* scale_out, void* ffn_scratch, int32_t div_mode, uint32_t flags, void* stream) {
+    const char* who = "actq_fp8_given";
+    RWKVQ_REQUIRE(x && codes && amax_out && ffn_scratch, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL || div_mode == RWKVQ_DIV_TORCH, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
+    RWKVQ_REQUIRE(M > 0 && K > 0 && K % 8 == 0 && M < (1 << 30), RWKVQ_E_SHAPE, "%s: M=%lld K=%lld (K must be a multiple of 8)", who, (long long)M, (long long)K);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K && ldc % 8 == 0 && ldc >= K && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)ffn_scratch & 7) == 0,
+                  RWKVQ_E_ALIGN, "%s: rows must be 16-byte (x) / 8-byte (codes, scratch) aligned", who);
+    const int64_t nvec = M * (K / 8);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)std::min<int64_t>((nvec + kThreads * 4 - 1) / (kThreads * 4), 8 * (int64_t)sm_count()));
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    const int m = (int)M, dm = div_mode, fb = (flags & RWKVQ_FLAG_QUANT_FROM_BF16) ? 1 : 0;
+    float* ffn = reinterpret_cast<float*>(ffn_scratch);
+    const cudaError_t e = x_dtype == RWKVQ_F16
+        ? cudaLaunchKernelEx(&cfg, quant_fp8_given_kernel<RWKVQ_F16>, x, codes, amax_out, scale_out, ffn, m, K, ldx, ldc, dm, fb)
+        : cudaLaunchKernelEx(&cfg, quant_fp8_given_kernel<RWKVQ_BF16>, x, codes, amax_out, scale_out, ffn, m, K, ldx, ldc, dm, fb);
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return check_launch(who);
+}
 
 int32_t rwkvq_device_status(int32_t* host_status, int32_t clear) {
     RWKVQ_REQUIRE(host_status != nullptr, RWKVQ_E_BADARG, "device_status: null pointer");

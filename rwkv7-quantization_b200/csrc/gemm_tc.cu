@@ -54,6 +54,7 @@ struct TcArgs {
     int* status;               // set to RWKVQ_E_TIMEOUT if a bounded wait gave up
     unsigned long long* trace; // optional [grid][16] timestamps of role milestones (profiling aid), else null
     unsigned long long wait_ns; // wall-time limit of every mbarrier wait
+    float* ffn_amax;            // RWKVQ_FLAG_RELU2 (GEMM mode, FP8): maximum of the relu^2 results, atomic max
     int64_t ldx, ldo, ldacc;
     int M, N, K, nmat;
     int NB;                    // rows of the B operand (UMMA N)
@@ -460,6 +461,9 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 }
                 const float rowscale = actscale * wsc;
                 const bool vec_ok = (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out[p.mat]) & 15) == 0);
+                const bool relu2 = KIND == KIND_F8 && (a.flags & RWKVQ_FLAG_RELU2) != 0;
+                const bool hmax_bf16 = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
+                float hmax = 0.f;
                 for (int c0 = 0; c0 < a.NB; c0 += 16) {
                     uint32_t r[16];
                     tmem_ld16(taddr + c0, r);
@@ -483,7 +487,19 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                                 f1 = (float)(int32_t)r[2 * j + 1] * s1;
                             }
                             if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
-                            const __half2 hh = __floats2half2_rn(f0, f1);
+                            __half2 hh = __floats2half2_rn(f0, f1);
+                            if (relu2) {
+                                // the engine's relu_square on the fp16 result, fp32 arithmetic; its maximum (over the bf16-rounded
+                                // values where the consumer takes its amax there) goes to the projection that follows
+                                const float2 y = __half22float2(hh);
+                                const float v0 = fmaxf(y.x, 0.f), v1 = fmaxf(y.y, 0.f);
+                                hh = __floats2half2_rn(v0 * v0, v1 * v1);
+                                if (n0 + 2 * j < a.N) {
+                                    const float2 hv = __half22float2(hh);
+                                    hmax = fmaxf(hmax, hmax_bf16 ? bf16_round(hv.x) : hv.x);
+                                    if (n0 + 2 * j + 1 < a.N) hmax = fmaxf(hmax, hmax_bf16 ? bf16_round(hv.y) : hv.y);
+                                }
+                            }
                             h[j] = *reinterpret_cast<const uint32_t*>(&hh);
                         }
                         __half* o = a.out[p.mat] + (int64_t)m * a.ldo + n0;
@@ -507,6 +523,10 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.tempty[buf]);
+                if (relu2) {                                  // one atomic per warp and tile
+                    hmax = warp_max(hmax);
+                    if (lane == 0 && hmax > 0.f) atomic_max_nonneg(a.ffn_amax, hmax);
+                }
             }
             ++pc;
         }
@@ -751,6 +771,7 @@ int32_t rwkvq_workspace_status(const void* workspace, int32_t* host_status) {
 }
 
 static void fill_common(TcArgs& a, int nmat, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldo, int32_t div_mode, uint32_t flags) {
+    if (a.ffn_amax == nullptr) flags &= ~RWKVQ_FLAG_RELU2;      // only rwkvq_tc_gemm_fp8_relu2 sets the target first
     a.nmat = nmat; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldo = ldo; a.div_mode = div_mode; a.flags = flags;
 }
 
@@ -865,6 +886,24 @@ int32_t rwkvq_tc_gemm_int8_rkv(const int8_t* codes_r, const int8_t* codes_k, con
     c.kind = KIND_I8; c.w[0] = wr; c.w[1] = wk; c.w[2] = wv; c.ldw = ldw; c.codes[0] = codes_r; c.codes[1] = codes_k; c.codes[2] = codes_v;
     c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8_rkv");
+}
+
+/* rwkvq_tc_gemm_fp8 (tiled GEMM form, M >= 17) with the engine's relu_square folded into the epilogue: stores
+ * h = fp16(max(y, 0)^2) and accumulates max|h| into ffn_scratch[0] (see rwkvq_gemv_fp8_relu2). */
+int32_t rwkvq_tc_gemm_fp8_relu2(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
+                                int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                int32_t div_mode, uint32_t flags, void* ffn_scratch, void* workspace, int64_t workspace_bytes,
+                                void* stream) {
+    RWKVQ_REQUIRE(ffn_scratch != nullptr && ((uintptr_t)ffn_scratch & 7) == 0, RWKVQ_E_BADARG, "tc_gemm_fp8_relu2: ffn_scratch must be 8 aligned bytes");
+    RWKVQ_REQUIRE(!takes_swap_route(M, N, K, 1, false), RWKVQ_E_SHAPE, "tc_gemm_fp8_relu2: M=%lld runs the weight-streaming form; use rwkvq_gemv_fp8_relu2 for few rows",
+                  (long long)M);
+    TcArgs a{};
+    a.a_scale[0] = amax; a.amax_is_amax = amax_is_amax; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    a.ffn_amax = reinterpret_cast<float*>(ffn_scratch);
+    fill_common(a, 1, M, N, K, 0, ldo, div_mode, flags | RWKVQ_FLAG_RELU2);
+    TcCall c{};
+    c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_fp8_relu2");
 }
 
 /* rwkvq_tc_gemm_fp8 without a caller workspace: the split-K partial sums, arrival counters and status word live in

@@ -419,6 +419,35 @@ def ffn_relu2_fp8(x, key_info, value_info, out_dtype=torch.float16, return_hidde
         abi.call("rwkvq_gemv_fp8_preamax", hid.data_ptr(), abi.F16, _u8(wv).data_ptr(), wv.stride(0), sv.data_ptr(),
                  out.data_ptr(), out.stride(0), m, n, f_dim, f_dim, abi.DEFAULT_DIV, flags | _wscale_flag(sv, n), sc.data_ptr(), st)
         abi.after_call()
+    elif ROUTE == "auto" and m > GEMV_M_MAX and _ACTQ_FUSED and k % 8 == 0 and f_dim % 8 == 0:
+        # many rows: relu_square and the amax of its result come out of the key GEMM's epilogue; the hidden activations
+        # are then quantized by a purely elementwise kernel (no abs-max pass, no grid rendezvous).  Up to FUSED_M_MAX
+        # rows the two projections have the semantics of linear_fp8_fused, above those of fp8_ops.linear_fp8 (bf16
+        # first, torch's scale arithmetic, results through bf16), as the engine's dispatch has them.
+        big = m > FUSED_M_MAX
+        dev_, st = x2.device, abi.stream_ptr()
+        div = abi.DIV_TORCH if big else abi.DEFAULT_DIV
+        aflags = abi.FLAG_QUANT_FROM_BF16 | (abi.FLAG_AMAX_AFTER_BF16 if big else 0)
+        gflags = (abi.FLAG_OUT_VIA_BF16 | abi.FLAG_AMAX_AFTER_BF16) if big else 0
+        codes = torch.empty((m, k), dtype=torch.uint8, device=dev_)
+        sc4 = torch.empty(4, dtype=torch.float32, device=dev_)           # amax / scale of x, amax / scale of the hidden
+        hid = torch.empty((m, f_dim), dtype=torch.float16, device=dev_)
+        hcodes = torch.empty((m, f_dim), dtype=torch.uint8, device=dev_)
+        out = abi.new_out(m, n, dev_)
+        ffn = ffn_scratch(dev_)
+        _actq_fp8(x2, codes, sc4[0:1], sc4[1:2], div, aflags, st)
+        ws = abi.workspace(min(m, 128), max(f_dim, n), max(k, f_dim), 1, dev_)
+        a_ptr, is_amax = (sc4[1:2].data_ptr(), 0) if big else (sc4[0:1].data_ptr(), 1)
+        abi.call("rwkvq_tc_gemm_fp8_relu2", codes.data_ptr(), k, a_ptr, is_amax, _u8(wk).data_ptr(), wk.stride(0), sk.data_ptr(),
+                 hid.data_ptr(), f_dim, m, f_dim, k, abi.DIV_IEEE if big else abi.DEFAULT_DIV, gflags | _wscale_flag(sk, f_dim),
+                 ffn.data_ptr(), ws.data_ptr(), ws.numel(), st)
+        abi.call("rwkvq_actq_fp8_given", hid.data_ptr(), abi.F16, m, f_dim, f_dim, hcodes.data_ptr(), f_dim, sc4[2:3].data_ptr(),
+                 sc4[3:4].data_ptr(), ffn.data_ptr(), div, abi.FLAG_QUANT_FROM_BF16, st)
+        h_ptr = sc4[3:4].data_ptr() if big else sc4[2:3].data_ptr()
+        abi.call("rwkvq_tc_gemm_fp8", hcodes.data_ptr(), f_dim, h_ptr, is_amax, _u8(wv).data_ptr(), wv.stride(0), sv.data_ptr(),
+                 out.data_ptr(), out.stride(0), m, n, f_dim, abi.DIV_IEEE if big else abi.DEFAULT_DIV,
+                 (abi.FLAG_OUT_VIA_BF16 if big else 0) | _wscale_flag(sv, n), ws.data_ptr(), ws.numel(), st)
+        abi.after_call(ws)
     else:
         hid = linear_quantized_fused(x2, {"weight": wk, "tensor_scale": sk, "qtype": "fp8"})
         hid = (hid.float().clamp_(min=0.0) ** 2).to(torch.float16)       # relu_square: fp16(max(y, 0)^2), fp32 arithmetic

@@ -313,7 +313,8 @@ def test_decode_layer_equals_dropin_calls(mods, scheme, rows, dt):
 
 
 # ------------------------------------------------------------------------------------------------ FFN pair with relu^2 folded in
-@pytest.mark.parametrize("m,dt", [(1, torch.bfloat16), (1, torch.float16), (3, torch.bfloat16), (8, torch.float16), (20, torch.bfloat16)])
+@pytest.mark.parametrize("m,dt", [(1, torch.bfloat16), (1, torch.float16), (3, torch.bfloat16), (8, torch.float16), (20, torch.bfloat16),
+                                  (40, torch.bfloat16), (300, torch.float16), (600, torch.bfloat16)])
 def test_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
     """key -> relu_square -> value: the fused pair (relu^2 in the key epilogue, published amax) equals the three steps
     run separately bit for bit, and the oracle's chain within 1e-2.  Twice in a row: the scratch is left clean."""
@@ -330,10 +331,17 @@ def test_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
         h = (y.float().clamp(min=0) ** 2).half()
         bits_equal(hid, h, "hidden")
         bits_equal(out, f.linear_quantized_fused(h, dv), "ffn output")
-        want, want_h = O.ffn_relu2_fp8(x, key, val, lib_div(abi))
+        if m <= 512:
+            want, want_h = O.ffn_relu2_fp8(x, key, val, lib_div(abi))
+        else:
+            want_h = O.relu_square(O.linear_fp8(x, key))
+            want = O.linear_fp8(want_h, val)
         assert rel_err(hid, want_h) <= 2e-2 and rel_err(out, want) <= 2e-2      # the square doubles the relative error of y
         if m <= 8:
             assert launches == 2
+        if m > 32:
+            assert launches == 4                # quantize x, key GEMM (+relu^2, amax), quantize hidden (elementwise), value GEMM
+        if m <= 8 or m > 32:
             assert int(f.ffn_scratch("cuda").abs().sum().item()) == 0
     if m <= 8:
         from rwkvq_layer import DecodeLayer
