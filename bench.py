@@ -40,8 +40,9 @@ def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def gemv_bytes(m, n, k, in_bytes=2):
@@ -319,9 +320,12 @@ def run_ours(args, rank, world, local_rank):
         tfl = prefill_flops(args.layers) * world / (ms_p * 1e-3) / 1e12
         prefill = {"metric": "prefill GEMM TFLOPS (FP8 W8A8, T=2048 tokens, all projections incl. activation quantization)",
                    "value": round(tfl, 1), "unit": "TFLOP/s", "ms_per_sequence": round(ms_p, 3),
-                   "roofline": {"bound": "tensor", "achieved": round(tfl / world, 1), "peak": round(2 * peaks()["bf16_tflops"], 1),
-                                "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),
-                                "peak_note": "2 x the measured dense bf16 cuBLAS rate (fp8 runs at twice the bf16 rate)"}}
+                   "roofline": {"bound": "tensor", "achieved": round(tfl / world, 1), "peak": round(2 * peaks()["bf16_tflops_sustained"], 1),
+                                "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops_sustained"]), 4),
+                                "frac_of_burst": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),
+                                "peak_note": "2 x the measured dense bf16 cuBLAS rate (fp8 runs at twice the bf16 rate); the prefill leg is a "
+                                             "seconds-long sequence of GEMMs under the power cap, so `peak` is the SUSTAINED measurement "
+                                             "(bf16_tflops_sustained); frac_of_burst divides by the burst figure instead"}}
         del xp
     # per-shape breakdown: each of the four launch kinds of the step alone, graph replay over the 32 layers' weights
     per_shape = {}

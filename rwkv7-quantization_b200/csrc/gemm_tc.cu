@@ -682,6 +682,10 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
         a.status = a.counters + kWsCounterInts;
         a.scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(c.workspace) + kWsHeaderBytes);
     } else {
+        if (tc2_eligible(c.kind, a.M, a.N, a.K, a.nmat))      // many tokens: CTA pairs on 256 x 256 tiles (gemm_tc2.cu)
+            return run_tc2(c.kind, c.codes[0], c.lda, a.a_scale[0], a.amax_is_amax, c.w[0], c.ldw, a.ws[0], a.out[0], a.ldo, a.acc[0], a.ldacc,
+                           a.M, a.N, a.K, a.div_mode, a.flags, a.ffn_amax,
+                           c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : device_status_ptr(), st, who);
         // 256 weight rows per tile; narrower tiles while halving them still leaves no more tiles than SMs
         a.NB = 256;
         while (a.NB > 64 && 2 * (int64_t)a.nmat * ((a.M + kTileP - 1) / kTileP) * ((a.N + a.NB - 1) / a.NB) <= tc_grid()) a.NB >>= 1;

@@ -42,4 +42,11 @@ inline int32_t make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t r
     return RWKVQ_OK;
 }
 
+// W8A8 GEMM on CTA pairs (gemm_tc2.cu): eligibility (many tokens, enough 256 x 256 tiles to fill the pairs, not switched
+// off with RWKVQ_TC2=0) and the launch.  kind: tc::KIND_F8 / tc::KIND_I8.
+bool tc2_eligible(int kind, int64_t M, int64_t N, int64_t K, int nmat);
+int32_t run_tc2(int kind, const void* codes, int64_t lda, const float* a_scale, int amax_is_amax, const void* w, int64_t ldw, const float* ws,
+                __half* out, int64_t ldo, int32_t* acc, int64_t ldacc, int M, int N, int K, int div_mode, uint32_t flags, float* ffn_amax,
+                int* status, cudaStream_t st, const char* who);
+
 }  // namespace rwkvq

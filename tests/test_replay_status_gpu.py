@@ -349,3 +349,31 @@ def test_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
         layer = DecodeLayer(sq, sq, sq, sq, dk, dv, rows=m, x_dtype=dt)
         out2, hid2 = layer.ffn(x.cuda())
         bits_equal(out2.reshape(out.shape), out, "DecodeLayer.ffn")
+
+
+# ------------------------------------------------------------------------------------------------ CTA-pair GEMM (tcgen05 cta_group::2)
+@pytest.mark.parametrize("scheme", ["fp8", "int8"])
+@pytest.mark.parametrize("m,n,k", [(4096, 2560, 256), (4100, 2600, 272)])
+def test_cta_pair_gemm_many_tokens(mods, scheme, m, n, k):
+    """From 4096 tokens on the codes GEMM runs on CTA pairs (two SMs per 256 x 256 tile): INT8 accumulators and outputs
+    exact, FP8 within 1e-2 of the oracle and of the mma.sync kernel."""
+    abi, f, _ = mods
+    x = gen(200 + m, (m, k), 1.0).to(torch.bfloat16)
+    if scheme == "fp8":
+        info = fp8_weight(201, n, k)
+        out = f.linear_fp8_fused(x.cuda(), dev(info))
+        assert rel_err(out, O.linear_fp8_fused(x, info, lib_div(abi))) <= 1e-2
+        old, f.ROUTE = f.ROUTE, "mma"                                   # and against the mma.sync kernel on the same codes
+        try:
+            ref = f.linear_fp8_fused(x.cuda(), dev(info))
+        finally:
+            f.ROUTE = old
+        assert rel_err(out, ref) <= 1e-2
+    else:
+        q, s = O.q_int8_sym(gen(202, (n, k), 0.02, torch.float16))
+        info = {"weight": q, "tensor_scale": s, "qtype": "int8"}
+        acc = torch.empty((m, n), dtype=torch.int32, device="cuda")
+        out = f.linear_int8_fused(x.cuda(), dev(info), acc_out=acc)
+        want, want_acc = O.linear_int8_fused(x, info, lib_div(abi), return_acc=True)
+        bits_equal(acc, want_acc, "accumulators")
+        bits_equal(out, want, "outputs")
