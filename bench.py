@@ -31,7 +31,7 @@ for _p in (ROOT, PKG):
 import torch  # noqa: E402
 
 C, F, LAYERS = 4096, 16384, 32
-PREFILL_T = 2048          # tokens per sequence of the prefill leg (BASELINE config: T=2048)
+PREFILL_T = 2048          # tokens per sequence of the prefill leg (the reference quotes its prefill figures at T = 2048)
 METRIC = "B=1 quantized GEMV HBM GB/s + prefill GEMM TFLOPS, RWKV-7 7.2B shapes, 1-8 GPU"
 WORKLOAD = "rwkv7-7.2B fp8 w8a8 decode B=1: 32 layers x (rkv-fused 3x[4096,4096] + att_out [4096,4096] + ffn_key [16384,4096] + ffn_value [4096,16384])"
 
@@ -141,10 +141,10 @@ def decode_step(layers, x):
 
 
 LAUNCHES_PER_STEP = 4 * LAYERS
-# dram__bytes_read.sum + dram__bytes_write.sum per gemv_w8a8_kernel launch of this workload, from the ncu launch list
-# summarised in profiles/gemv_w8a8_fp8_decode_launch_list.md (4-layer capture; traffic per launch does not depend on
-# the number of layers).  Algorithmic bytes per launch: 50 368 518.
-DRAM_TRAFFIC_PER_LAUNCH = 50_200_000
+# dram__bytes_read.sum + dram__bytes_write.sum per gemv_w8a8_kernel launch of this workload, from an ncu launch list
+# of `bench.py --layers 4` (traffic per launch does not depend on the number of layers): 44.70 MB for the r/k/v, att
+# output and FFN key launches on average, 67.21 MB for the FFN value.  Algorithmic bytes per launch: 50 368 518.
+DRAM_TRAFFIC_PER_LAUNCH = 50_330_000
 
 
 def prefill_pass(layers, x):
@@ -316,10 +316,18 @@ def run_ours(args, rank, world, local_rank):
             for _ in range(2):
                 prefill_pass(layers, xp)
             reps = 3
-            ms_p = timed(lambda: prefill_pass(layers, xp), reps, dist_on) / reps
+            ms_p_eager = timed(lambda: prefill_pass(layers, xp), reps, dist_on) / reps
+            stream.synchronize()
+            gp = torch.cuda.CUDAGraph()                      # the same 192 public-API calls, replayed from a CUDA graph
+            with torch.cuda.graph(gp, stream=stream):
+                prefill_pass(layers, xp)
+            gp.replay()
+            ms_p = timed(gp.replay, reps, dist_on) / reps
+            del gp
         tfl = prefill_flops(args.layers) * world / (ms_p * 1e-3) / 1e12
         prefill = {"metric": "prefill GEMM TFLOPS (FP8 W8A8, T=2048 tokens, all projections incl. activation quantization)",
                    "value": round(tfl, 1), "unit": "TFLOP/s", "ms_per_sequence": round(ms_p, 3),
+                   "launch": "CUDA graph of the 192 public-API calls (eager Python calls: %.3f ms per sequence)" % ms_p_eager,
                    "roofline": {"bound": "tensor", "achieved": round(tfl / world, 1), "peak": round(2 * peaks()["bf16_tflops_sustained"], 1),
                                 "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops_sustained"]), 4),
                                 "frac_of_burst": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),

@@ -45,7 +45,7 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import schemes as ref_schemes
@@ -54,7 +54,7 @@ def main():
 
     out = {}
     # ---- weight quantizers ------------------------------------------------------------
-    w = gen(0, (48, 256), 0.02)                       # N(0, 0.02^2), as BASELINE config 1
+    w = gen(0, (48, 256), 0.02)                       # N(0, 0.02^2), as the reference's CPU-runnable 0.1B case
     w16 = w.to(torch.float16)
     out["w"] = w.numpy()
     for name in ("_q_fp8", "_q_fp8_perchannel", "_q_int8_sym"):
@@ -100,7 +100,7 @@ def main():
     # ---- INT8 Triton kernels + prep_x under the interpreter -------------------------------
     import fused_fp8_gemm as ref_f
     t = {}
-    C = 768                                             # RWKV-7 0.1B, BASELINE config 1
+    C = 768                                             # RWKV-7 0.1B
     ws = [gen(10 + i, (96, C), 0.02, torch.float16) for i in range(3)]
     infos = []
     for i, wi in enumerate(ws):

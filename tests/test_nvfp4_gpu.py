@@ -72,7 +72,7 @@ def test_linear_nvfp4(nf, m, n, k):
 
 
 def test_config5_ffn_shapes(nf):
-    """BASELINE config 5: FFN key [16384,4096] and value [4096,16384], M in {1, 256}; M = 4096 on a slice of rows."""
+    """NVFP4 at the 7.2B FFN shapes: key [16384,4096] and value [4096,16384], M in {1, 256}; M = 4096 on a slice of rows."""
     import fp8_ops
     for n, k in ((16384, 4096), (4096, 16384)):
         w = gen(n, (n, k), (1.0 / k) ** 0.5)

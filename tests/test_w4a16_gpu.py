@@ -37,7 +37,7 @@ def mods():
     return int4_ops, fused_int4_gemm, quantize_int4, int8_ops, fused_int8_gemm, quantize_int8
 
 
-# BASELINE config 3: 7.2B shapes, group 128, B in {1, 4, 16}
+# INT4 weight-only decode: 7.2B shapes, group 128, B in {1, 4, 16}
 @pytest.mark.parametrize("n,k", [(4096, 4096), (16384, 4096), (4096, 16384)])
 def test_int4_groupwise_7b_shapes(mods, n, k):
     i4, f4, q4 = mods[0], mods[1], mods[2]
