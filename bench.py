@@ -147,13 +147,21 @@ LAUNCHES_PER_STEP = 4 * LAYERS
 DRAM_TRAFFIC_PER_LAUNCH = 50_330_000
 
 
-def prefill_pass(layers, x):
-    """One sequence of PREFILL_T tokens through the six projections of every layer (rows > FUSED_M_MAX, so r, k, v
-    are separate calls, as in the reference engine)."""
+def prefill_pass(layers, x, fused_rkv=True):
+    """One sequence of PREFILL_T tokens through the six projections of every layer.  fused_rkv: r, k and v through
+    linear_rkv_fused (one quantizer launch for the three activations, one GEMM launch over the three matrices), the
+    call the engine makes for rows <= FUSED_M_MAX (rwkv7_fast_v3a.py:980-985); this build serves it at every row
+    count (RWKVQ_FUSED_M_MAX raises the threshold the engine imports).  False: three linear_quantized_fused calls,
+    what the engine does above the reference's threshold of 512 rows."""
     import fused_fp8_gemm as f
     y = None
     for L in layers:
-        for name, inp in (("r", "xr"), ("k", "xk"), ("v", "xv"), ("o", "xo"), ("ffn_k", "xf"), ("ffn_v", "xg")):
+        if fused_rkv:
+            f.linear_rkv_fused(x["xr"], x["xk"], x["xv"], L["r"], L["k"], L["v"])
+            rest = (("o", "xo"), ("ffn_k", "xf"), ("ffn_v", "xg"))
+        else:
+            rest = (("r", "xr"), ("k", "xk"), ("v", "xv"), ("o", "xo"), ("ffn_k", "xf"), ("ffn_v", "xg"))
+        for name, inp in rest:
             y = f.linear_quantized_fused(x[inp], L[name])
     return y
 
@@ -318,16 +326,26 @@ def run_ours(args, rank, world, local_rank):
             reps = 3
             ms_p_eager = timed(lambda: prefill_pass(layers, xp), reps, dist_on) / reps
             stream.synchronize()
-            gp = torch.cuda.CUDAGraph()                      # the same 192 public-API calls, replayed from a CUDA graph
-            with torch.cuda.graph(gp, stream=stream):
-                prefill_pass(layers, xp)
-            gp.replay()
-            ms_p = timed(gp.replay, reps, dist_on) / reps
-            del gp
+            ms_g = {}
+            for fused_rkv in (True, False):                  # the same public-API calls, replayed from a CUDA graph
+                prefill_pass(layers, xp, fused_rkv)
+                stream.synchronize()
+                gp = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gp, stream=stream):
+                    prefill_pass(layers, xp, fused_rkv)
+                gp.replay()
+                ms_g[fused_rkv] = timed(gp.replay, reps, dist_on) / reps
+                del gp
+            ms_p = ms_g[True]
         tfl = prefill_flops(args.layers) * world / (ms_p * 1e-3) / 1e12
         prefill = {"metric": "prefill GEMM TFLOPS (FP8 W8A8, T=2048 tokens, all projections incl. activation quantization)",
                    "value": round(tfl, 1), "unit": "TFLOP/s", "ms_per_sequence": round(ms_p, 3),
-                   "launch": "CUDA graph of the 192 public-API calls (eager Python calls: %.3f ms per sequence)" % ms_p_eager,
+                   "launch": "CUDA graph of the %d public-API calls (r/k/v in one linear_rkv_fused call per layer); the same "
+                             "calls eager from Python: %.3f ms per sequence" % (4 * args.layers, ms_p_eager),
+                   "separate_rkv": {"ms_per_sequence": round(ms_g[False], 3),
+                                    "tflops": round(prefill_flops(args.layers) * world / (ms_g[False] * 1e-3) / 1e12, 1),
+                                    "note": "r, k and v as three linear_quantized_fused calls (%d calls per sequence), what the "
+                                            "reference engine does above its FUSED_M_MAX of 512 rows" % (6 * args.layers)},
                    "roofline": {"bound": "tensor", "achieved": round(tfl / world, 1), "peak": round(2 * peaks()["bf16_tflops_sustained"], 1),
                                 "unit": "TFLOP/s", "frac": round(tfl / world / (2 * peaks()["bf16_tflops_sustained"]), 4),
                                 "frac_of_burst": round(tfl / world / (2 * peaks()["bf16_tflops"]), 4),

@@ -590,6 +590,122 @@ __global__ void __launch_bounds__(kSmallThreads, 1) actq_fp8_small_kernel(const 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Two plain launches for blocks between the cluster kernel above and the many-token cooperative kernel: an abs-max
+// pass and a codes pass, chained by programmatic dependent launch.  A cooperative launch costs several microseconds
+// more than a plain one and cannot start early behind its predecessor; here the second kernel is resident while the
+// first runs and re-reads the activations from L2.  `two` = 4 words of the caller's zeroed scratch: the maxima of up
+// to three tensors (float bits, non-negative, so an integer atomicMax orders them) and a count of codes-pass CTAs; the
+// last one to finish clears all four, so the words are zero again before the next launch on the stream can reach
+// them (it waits for this grid first) and a captured graph replays.
+constexpr int kTwoThreads = 256;
+constexpr int kTwoWord = kFusedEpochWord + 4;
+constexpr int64_t kTwoMaxVectors = 1 << 19;                 // up to 512 rows of 8192 elements; larger blocks: one cooperative launch
+
+template <int DT>
+__device__ __forceinline__ float two_vec_max(const uint4& v, float m, bool after_bf16) {
+    if (DT == RWKVQ_F16 && after_bf16) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 f = cvt2<DT>(w[q]);
+            m = fmaxf(m, fmaxf(fabsf(bf16_round(f.x)), fabsf(bf16_round(f.y))));
+        }
+        return m;
+    } else if (DT == RWKVQ_F16) {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+        const __half2 t2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+        return fmaxf(m, fmaxf(__low2float(t2), __high2float(t2)));
+    } else {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const __nv_bfloat162 t2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+        return fmaxf(m, fmaxf(__low2float(t2), __high2float(t2)));
+    }
+}
+
+// grid (rows * cpr, nt): CTA (b, t) takes every cpr-th group of kTwoThreads vectors of row b / cpr (and of every
+// (gridDim.x / cpr)-th row after it) of tensor t.
+template <int DT>
+__global__ void __launch_bounds__(kTwoThreads) actq_two_amax_kernel(const ActqArgs a, int cpr) {
+    __shared__ float sh[kTwoThreads / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int t = blockIdx.y, kv = a.K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = (int)blockIdx.x % cpr, rstep = (int)gridDim.x / cpr, cstep = cpr * kTwoThreads;
+    const char* x = reinterpret_cast<const char*>(a.x[t]);
+    const bool after_bf16 = a.after_bf16 != 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float m = 0.f;
+    for (int r = (int)blockIdx.x / cpr; r < a.M; r += rstep) {
+        const char* row = x + (int64_t)r * a.ldx * 2;
+        for (int c0 = seg * kTwoThreads + (int)threadIdx.x; c0 < kv; c0 += 4 * cstep) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j * cstep < kv) v[j] = *reinterpret_cast<const uint4*>(row + (int64_t)(c0 + j * cstep) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j * cstep < kv) m = two_vec_max<DT>(v[j], m, after_bf16);
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) sh[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        m = warp_max(lane < kTwoThreads / 32 ? sh[lane] : 0.f);
+        if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(a.flags) + kTwoWord - kFusedMaxCtas + t, __float_as_int(m));
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kTwoThreads) actq_two_codes_kernel(const ActqArgs a, int cpr) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int t = blockIdx.y, kv = a.K >> 3;
+    const int seg = (int)blockIdx.x % cpr, rstep = (int)gridDim.x / cpr, cstep = cpr * kTwoThreads;
+    const char* x = reinterpret_cast<const char*>(a.x[t]);
+    uint8_t* codes = a.codes[t];
+    const bool from_bf16 = a.from_bf16 != 0;
+    int* two = reinterpret_cast<int*>(a.flags) + kTwoWord - kFusedMaxCtas;
+    asm volatile("griddepcontrol.wait;" ::: "memory");              // the abs-max pass is complete and visible
+    const float amax = __int_as_float(__ldcg(two + t));
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        a.amax_out[t] = amax;
+        if (a.scale_out[t]) *a.scale_out[t] = scale_fwd(amax, 448.f, a.div_mode);
+    }
+    const float inv = scale_inv(448.f, fmaxf(amax, 1e-12f), a.div_mode);
+    for (int r = (int)blockIdx.x / cpr; r < a.M; r += rstep) {
+        const char* row = x + (int64_t)r * a.ldx * 2;
+        uint8_t* crow = codes + (int64_t)r * a.ldc;
+        for (int c0 = seg * kTwoThreads + (int)threadIdx.x; c0 < kv; c0 += 4 * cstep) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j * cstep < kv) v[j] = *reinterpret_cast<const uint4*>(row + (int64_t)(c0 + j * cstep) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (c0 + j * cstep >= kv) continue;
+                const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                uint32_t q[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float2 f = cvt2<DT>(w[i]);
+                    if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                    q[i] = e4m3x2(f.x * inv, f.y * inv);
+                }
+                *reinterpret_cast<uint2*>(crow + (int64_t)(c0 + j * cstep) * 8) = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+            }
+        }
+    }
+    __syncthreads();                                    // every thread of this CTA has read the maximum
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(two + 3, 1) == (int)(gridDim.x * gridDim.y) - 1) {
+            two[0] = 0; two[1] = 0; two[2] = 0;
+            __threadfence();
+            two[3] = 0;
+        }
+    }
+}
+
 // FP8 codes of h with an amax that the PRODUCER of h published (the FFN key projection with relu^2 in its epilogue):
 // purely elementwise -- no abs-max pass, no grid rendezvous -- so it is launched with programmatic dependent launch.
 // ffn[0] = the published amax (float), ffn[1] = count of CTAs that have read it; the last one clears both for the next
@@ -826,7 +942,7 @@ static int32_t launch_actq_fused(ActqArgs a, int nt, int32_t x_dtype, int64_t M,
     a.slots = reinterpret_cast<float*>(scratch);
     a.flags = reinterpret_cast<uint32_t*>(scratch) + kFusedMaxCtas;
     a.wait_ns = wait_limit_ns();
-    if (M <= 64 && M * (K / 8) <= 32768 && K / 8 < 65536) {
+    if (M * (K / 8) <= 8 * 8 * kSmallThreads && K / 8 < 65536) {
         // decode-sized block: a cluster of CTAs per tensor (about 4 vectors per thread), no grid rendezvous, programmatic
         // dependent launch (the scratch is not touched)
         int cluster = 1;
@@ -850,6 +966,34 @@ static int32_t launch_actq_fused(ActqArgs a, int nt, int32_t x_dtype, int64_t M,
             g_launches.fetch_add(1, std::memory_order_relaxed);
             return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
         }
+        return check_launch(who);
+    }
+    static const int64_t two_max = std::getenv("RWKVQ_ACTQ_TWO_MAX") ? std::atoll(std::getenv("RWKVQ_ACTQ_TWO_MAX")) : kTwoMaxVectors;
+    if (M * (K / 8) <= two_max) {
+        // mid-sized block: abs-max pass and codes pass as two plain launches chained by programmatic dependent launch
+        const int kv = (int)(K / 8);
+        int cpr = 1;                                     // CTAs per row: about two CTAs per SM in all, 256+ vectors each
+        while ((int64_t)M * cpr * nt < 2 * (int64_t)sm_count() && cpr * 2 * kTwoThreads <= kv) cpr <<= 1;
+        const int rows = (int)std::min<int64_t>(M, std::max<int64_t>(1, 4 * (int64_t)sm_count() / (cpr * nt)));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(rows * cpr), (unsigned)nt);
+        cfg.blockDim = dim3(kTwoThreads);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl() ? 1 : 0;
+        cudaError_t e = x_dtype == RWKVQ_F16 ? cudaLaunchKernelEx(&cfg, actq_two_amax_kernel<RWKVQ_F16>, a, cpr)
+                                             : cudaLaunchKernelEx(&cfg, actq_two_amax_kernel<RWKVQ_BF16>, a, cpr);
+        if (e == cudaSuccess)
+            e = x_dtype == RWKVQ_F16 ? cudaLaunchKernelEx(&cfg, actq_two_codes_kernel<RWKVQ_F16>, a, cpr)
+                                     : cudaLaunchKernelEx(&cfg, actq_two_codes_kernel<RWKVQ_BF16>, a, cpr);
+        if (e != cudaSuccess) {
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);         // two launches: check_launch counts the other one
         return check_launch(who);
     }
     void* args[] = {(void*)&a};

@@ -23,6 +23,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include "tc_common.cuh"
 #include "tc_host.cuh"
@@ -306,7 +307,23 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
     if (warp == 0) {
         // ============================== TMA producer ==============================
         if (lane == 0) {
-            if (!(SWAP && FUSED)) griddep_wait();       // activation codes are written by the previous kernel
+            uint32_t npre = 0;
+            if constexpr (!FUSED) {
+                // The weights do not depend on the previous kernel: the first pass over the ring loads them before the
+                // dependency wait (each stage's barrier already expects the whole stage), so under programmatic
+                // dependent launch a ring of weights is on its way while the activation quantizer still runs.
+                PartIter<SWAP> pre(a);
+                Part q;
+                while (npre < (uint32_t)a.stages && pre.next(q))
+                    for (int kc = q.kc0; kc < q.kc1 && npre < (uint32_t)a.stages; ++kc, ++npre) {
+                        uint8_t* dst = ring + (size_t)npre * stage_bytes;
+                        mbar_expect_tx(&s.full[npre], stage_bytes);
+                        if constexpr (SWAP) tma_load_2d(dst, &maps.w[q.mat], kc * kChunk, q.prow, &s.full[npre]);
+                        else tma_load_2d(dst + kABytes, &maps.w[q.mat], kc * kChunk, q.qrow, &s.full[npre]);
+                    }
+                tc_mark(a, 2);
+                griddep_wait();                         // activation codes are written by the previous kernel
+            }
             PartIter<SWAP> it(a);
             Part p;
             uint32_t n = 0;
@@ -314,13 +331,19 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
             while (ok && it.next(p)) {
                 for (int kc = p.kc0; kc < p.kc1 && ok; ++kc, ++n) {
                     const int st = n % a.stages;
-                    const uint32_t ph = (n / a.stages) & 1;
-                    if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag, a.wait_ns)) { tc_abort(s, a); ok = false; break; }
                     uint8_t* dst = ring + (size_t)st * stage_bytes;
-                    mbar_expect_tx(&s.full[st], FUSED ? kABytes : stage_bytes);
-                    tma_load_2d(dst, SWAP ? &maps.w[p.mat] : &maps.a[p.mat], kc * kChunk, p.prow, &s.full[st]);
-                    if (!FUSED) tma_load_2d(dst + kABytes, SWAP ? &maps.a[p.mat] : &maps.w[p.mat], kc * kChunk, p.qrow, &s.full[st]);
-                    if (n == 0) tc_mark(a, 2);
+                    if (FUSED || n >= npre) {
+                        const uint32_t ph = (n / a.stages) & 1;
+                        if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag, a.wait_ns)) { tc_abort(s, a); ok = false; break; }
+                        mbar_expect_tx(&s.full[st], FUSED ? kABytes : stage_bytes);
+                        if constexpr (SWAP) tma_load_2d(dst, &maps.w[p.mat], kc * kChunk, p.prow, &s.full[st]);
+                        else tma_load_2d(dst + kABytes, &maps.w[p.mat], kc * kChunk, p.qrow, &s.full[st]);
+                    }
+                    if constexpr (!FUSED) {
+                        if constexpr (SWAP) tma_load_2d(dst + kABytes, &maps.a[p.mat], kc * kChunk, p.qrow, &s.full[st]);
+                        else tma_load_2d(dst, &maps.a[p.mat], kc * kChunk, p.prow, &s.full[st]);
+                    }
+                    if (FUSED && n == 0) tc_mark(a, 2);
                 }
             }
             tc_mark(a, 10);
@@ -383,27 +406,28 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 const int n = p.prow + prow_l;          // weight row
                 if (per_row) wsc = a.ws[p.mat][min(n, a.N - 1)];
                 const bool partial = p.nslots > 1;
-                float out_scale = 0.f;
+                float act_scale = 0.f;
                 if constexpr (KIND == KIND_F8) {
                     float am;
                     if constexpr (FUSED) am = s.amax[p.mat];
                     else am = a.amax_is_amax ? fmaxf(a.a_scale[p.mat][0], 1e-12f) : a.a_scale[p.mat][0];
-                    out_scale = ((FUSED || a.amax_is_amax) ? div_mode_f32(am, 448.f, a.div_mode) : am) * wsc;
+                    act_scale = (FUSED || a.amax_is_amax) ? div_mode_f32(am, 448.f, a.div_mode) : am;
                 }
-                auto finish = [&](T v, int m) {
+                auto finish_at = [&](T v, int m, int row, float wrow) {     // element (token m, weight row) of the result
                     float f;
                     if constexpr (KIND == KIND_F8) {
-                        f = v * out_scale;
+                        f = v * (act_scale * wrow);
                     } else {
-                        if (a.acc[p.mat]) a.acc[p.mat][(int64_t)m * a.ldacc + n] = v;
+                        if (a.acc[p.mat]) a.acc[p.mat][(int64_t)m * a.ldacc + row] = v;
                         float rs;
                         if constexpr (FUSED) rs = div_mode_f32(s.xs[p.mat][m], 127.f, a.div_mode);
                         else rs = a.a_scale[p.mat][m];
-                        f = (float)v * (rs * wsc);
+                        f = (float)v * (rs * wrow);
                     }
                     if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
-                    a.out[p.mat][(int64_t)m * a.ldo + n] = __float2half_rn(f);
+                    a.out[p.mat][(int64_t)m * a.ldo + row] = __float2half_rn(f);
                 };
+                auto finish = [&](T v, int m) { finish_at(v, m, n, wsc); };
                 T* part = reinterpret_cast<T*>(a.scratch) + ((int64_t)p.tile * a.max_slots + p.slot) * a.M * kTileP;
                 for (int c0 = 0; c0 < a.M; c0 += 16) {
                     uint32_t r[16];
@@ -433,21 +457,48 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                     }
                     named_bar_sync(1, 128);
                     if (s.last_flag) {
+                        // The last arriver adds the tile's partial sums in CTA order (run-to-run identical).  This is a
+                        // chain of L2 round trips on the critical path of the whole launch, so it is laid out for
+                        // loads in flight: a thread takes FOUR neighbouring weight rows (one 16-byte load per slot and
+                        // token) and two tokens at a time, 16 independent loads per batch.
                         __threadfence();
+                        using V4 = typename std::conditional<KIND == KIND_F8, float4, int4>::type;
                         const T* base = reinterpret_cast<const T*>(a.scratch) + (int64_t)p.tile * a.max_slots * a.M * kTileP;
-                        if (n < a.N)
-                            for (int m = 0; m < a.M; ++m) {
-                                T sum = 0;
-                                for (int s0 = 0; s0 < p.nslots; s0 += 8) {       // 8 independent loads in flight
-                                    T v[8];
+                        const int rg = et & 31, tl = et >> 5;           // row group (4 rows), token lane (tokens tl, tl + 4, ...)
+                        const int row0 = p.prow + 4 * rg;
+                        float w4[4];
 #pragma unroll
-                                    for (int j = 0; j < 8; ++j)
-                                        v[j] = s0 + j < p.nslots ? __ldcg(base + ((int64_t)(s0 + j) * a.M + m) * kTileP + prow_l) : T(0);
+                        for (int i = 0; i < 4; ++i) w4[i] = per_row ? a.ws[p.mat][min(row0 + i, a.N - 1)] : wsc;
+                        for (int m0 = tl; m0 < a.M; m0 += 8) {
+                            T sum[2][4] = {};
+                            for (int s0 = 0; s0 < p.nslots; s0 += 8) {
+                                V4 v[2][8];
 #pragma unroll
-                                    for (int j = 0; j < 8; ++j) sum += v[j];     // CTA order: run-to-run identical
-                                }
-                                finish(sum, m);
+                                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        const int m = m0 + 4 * u;
+                                        if (m < a.M && s0 + j < p.nslots)
+                                            v[u][j] = __ldcg(reinterpret_cast<const V4*>(base + ((int64_t)(s0 + j) * a.M + m) * kTileP + 4 * rg));
+                                        else
+                                            v[u][j] = V4{};
+                                    }
+#pragma unroll
+                                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) {
+                                        sum[u][0] += v[u][j].x; sum[u][1] += v[u][j].y; sum[u][2] += v[u][j].z; sum[u][3] += v[u][j].w;
+                                    }
                             }
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                const int m = m0 + 4 * u;
+                                if (m < a.M)
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i)
+                                        if (row0 + i < a.N) finish_at(sum[u][i], m, row0 + i, w4[i]);
+                            }
+                        }
                     }
                 }
             } else {
@@ -622,7 +673,8 @@ static int32_t launch_tc(const TcMaps& maps, const TcArgs& a, int grid, cudaStre
 // stream-K wins up to 48 tokens.
 static bool takes_swap_route(int64_t M, int64_t N, int64_t K, int nmat, bool fused) {
     const int64_t narrow_tiles = (int64_t)nmat * ((M + kTileP - 1) / kTileP) * ((N + 63) / 64);
-    return fused || M <= 16 || (M <= 48 && K >= 8192 && 2 * narrow_tiles <= tc_grid());
+    static const int64_t long_k_max_m = std::getenv("RWKVQ_TC_SWAP_MAX_M") ? std::atoll(std::getenv("RWKVQ_TC_SWAP_MAX_M")) : 48;
+    return fused || M <= 16 || (M <= long_k_max_m && K >= 8192 && 2 * narrow_tiles <= tc_grid());
 }
 
 struct TcCall {
@@ -638,6 +690,12 @@ struct TcCall {
 };
 
 static unsigned long long* g_trace = nullptr;
+
+}  // namespace rwkvq
+
+#include "gemm_tcs.cuh"        // few tokens: K split across a thread-block cluster, partial sums through distributed shared memory
+
+namespace rwkvq {
 
 static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
     a.trace = g_trace;
@@ -662,6 +720,10 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
     const bool swap = takes_swap_route(a.M, a.N, a.K, a.nmat, c.fused);
     if (c.fused) RWKVQ_REQUIRE(a.M <= 16, RWKVQ_E_SHAPE, "%s: the fused kernel takes M <= 16, got %d", who, a.M);
     a.kchunks = (a.K + kChunk - 1) / kChunk;
+    if (!c.fused && tcs_eligible(a.M, a.N, a.K, a.flags, a.nmat)) {
+        a.status = nullptr;
+        return run_tcs(a, c, st, who);
+    }
     TcMaps maps;
     int grid;
     if (swap) {
@@ -914,8 +976,8 @@ int32_t rwkvq_tc_gemm_fp8_relu2(const uint8_t* a_codes, int64_t lda, const float
  * an 8 MiB array that is part of the library image on every GPU.  Nothing is allocated, here or in anything this calls.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
  *     outside any stream capture.  Later calls only enqueue work.
- *   - Only calls that take the weight-streaming form (at most 16 tokens, or at most 48 against a long K) keep partial
- *     sums in the scratch; such a call is refused with RWKVQ_E_WORKSPACE if rwkvq_workspace_bytes(M, N, K, 1) exceeds
+ *   - Only calls that take the stream-K form (few tokens against a matrix with too many row tiles for the cluster
+ *     kernel) keep partial sums in the scratch; such a call is refused with RWKVQ_E_WORKSPACE if rwkvq_workspace_bytes(M, N, K, 1) exceeds
  *     8 MiB (a matrix of more than about 60 000 rows).  Every other shape needs the header only and is accepted.
  *   - All calls on a device share the one array and it keeps what the previous call left in it; this entry point
  *     therefore clears the counters and the status word on `stream` before the kernel.  Two calls that can overlap
@@ -925,7 +987,8 @@ int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const floa
                                  int32_t div_mode, uint32_t flags, void* stream) {
     const char* who = "tc_gemm_fp8_static";
     // only the weight-streaming form (few tokens) keeps partial sums in the scratch; the tiled GEMM uses the status word alone
-    const int64_t need = (M > 0 && N > 0 && K > 0 && takes_swap_route(M, N, K, 1, false)) ? rwkvq_workspace_bytes(M, N, K, 1) : kWsHeaderBytes;
+    const int64_t need = (M > 0 && N > 0 && K > 0 && takes_swap_route(M, N, K, 1, false) && !tcs_eligible(M, N, K, flags, 1))
+                             ? rwkvq_workspace_bytes(M, N, K, 1) : kWsHeaderBytes;
     RWKVQ_REQUIRE(need <= (int64_t)kStaticScratchBytes, RWKVQ_E_WORKSPACE, "%s: this shape needs %lld bytes of scratch, the built-in array has %lld",
                   who, (long long)need, (long long)kStaticScratchBytes);
     void* ws = nullptr;

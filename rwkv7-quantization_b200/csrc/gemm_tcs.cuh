@@ -1,0 +1,346 @@
+// W8A8 GEMM for a FEW tokens (decode batches, up to 64 rows) on pre-quantized codes: the weights are the 128-row
+// operand of tcgen05.mma, the tokens the narrow one, and K is split across a THREAD-BLOCK CLUSTER.
+//
+// Why.  With few tokens the projection is a pure weight stream, and a matrix has far fewer 128-row tiles than the GPU
+// has SMs (N = 4096: 32), so every tile's K range has to be shared by several CTAs.  Sharing it through global memory
+// (partial sums to a scratch buffer, fence, arrival counter, last arriver adds them: the stream-K form in gemm_tc.cu)
+// puts four dependent L2 round trips plus the reduction's own loads behind the end of the stream: 6-16 us measured at
+// 16-32 tokens against 12 us for the stream itself.  Here the C CTAs of a cluster (C = 2, 4, 8) each stream 1/C of
+// the tile's K range into their own tensor memory and exchange the partial sums through DISTRIBUTED SHARED MEMORY:
+// CTA r owns 128/C of the tile's rows, every CTA stores its partial sums of those rows straight into CTA r's shared
+// memory (st.shared::cluster) and arrives on CTA r's mbarrier; CTA r adds the C contributions in rank order
+// (run-to-run identical) and writes fp16.  No scratch, no counters, nothing to clear, nothing between launches.
+//
+// Roles per CTA: warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one lane),
+// warps 2-5 = epilogue / exchange.  Two CTAs fit an SM (about 105 KB of shared memory each).  The first pass over the
+// ring loads weights BEFORE the dependency wait of programmatic dependent launch: they do not depend on the
+// activation quantizer that runs in front.  Every wait is bounded; all CTAs of a cluster meet at a cluster barrier
+// before any of them exits, so no CTA's shared memory is written after it has gone.
+//
+// Included by gemm_tc.cu (shares its argument structs and tensor maps).
+#pragma once
+
+namespace rwkvq {
+
+constexpr int kTcsThreads = 192;
+constexpr int kTcsMaxStages = 8;
+constexpr int kTcsMaxM = 64;
+
+struct TcsShared {
+    uint64_t full[kTcsMaxStages], empty[kTcsMaxStages], tfull[3], rx, rxfree;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t tcs_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void tcs_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tcs_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t tcs_mapa(uint32_t local, uint32_t rank) {      // `local` in CTA `rank` of this cluster
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+// One warp-wide store of 32 consecutive words lands as one 128-byte packet in the peer's shared memory; 16-byte
+// vector stores to 32 different rows were measured 1.8 x slower for the same bytes.
+__device__ __forceinline__ void tcs_st_remote(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tcs_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the peers' stores that precede their arrivals become visible with an acquire at cluster scope
+__device__ __forceinline__ bool tcs_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool tcs_wait_cluster(uint64_t* bar, uint32_t parity, const volatile int* abort_flag, unsigned long long limit_ns) {
+#pragma unroll 1
+    for (int i = 0; i < 4096; ++i)
+        if (tcs_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 1024; ++i) {
+            if (tcs_try_wait_cluster(bar, parity)) return true;
+            __nanosleep(64);
+        }
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > limit_ns) return false;
+    }
+}
+
+__device__ __forceinline__ void tcs_abort(TcsShared& s, const TcArgs& a) {
+    s.abort_flag = 1;
+    if (a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
+}
+
+// a.qtiles carries the cluster size C, a.ptiles the 128-row tiles of one matrix; grid = ptiles * C.  With three
+// matrices (r, k, v) a CTA streams its K range of the same row tile of each matrix in turn into three accumulators;
+// the exchange of one matrix overlaps the stream of the next.  The K split is the same as for a single matrix, so the
+// three-in-one launch and three single launches give the same bits.
+template <int KIND>
+__global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_constant__ TcMaps maps, const TcArgs a) {
+    using T = typename Acc<KIND == KIND_F8 ? QT_FP8 : QT_INT8>::T;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ TcsShared s;
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t stage_bytes = kABytes + (uint32_t)a.NB * kChunk;
+    T* rxbuf = reinterpret_cast<T*>(ring + (size_t)a.stages * stage_bytes);        // [C][M][R]: partial sums per source CTA, token, row
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = a.qtiles, R = kTileP / C;
+    const int rank = (int)tcs_ctarank();
+    const int prow = ((int)blockIdx.x / C) * kTileP;
+    const int kc0 = a.kchunks * rank / C, kc1 = a.kchunks * (rank + 1) / C;
+    const int nk = kc1 - kc0, total = a.nmat * nk;          // ring units of this CTA: matrix-major
+    const uint32_t need_cols = (uint32_t)(a.nmat * a.acc_stride);
+    const uint32_t tmem_cols = need_cols <= 32 ? 32u : (need_cols <= 64 ? 64u : (need_cols <= 128 ? 128u : 256u));
+    const volatile int* abort_flag = &s.abort_flag;
+
+    griddep_launch_dependents();
+    if (threadIdx.x == 0) tc_mark(a, 0);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < a.stages; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], 1);
+        }
+        for (int i = 0; i < 3; ++i) mbar_init(&s.tfull[i], 1);
+        mbar_init(&s.rx, (uint32_t)(C * (R >= 32 ? R / 32 : 1)));      // one arrival per sending warp (half warp) and CTA
+        mbar_init(&s.rxfree, (uint32_t)C);                              // one arrival per owner that has emptied its buffer
+        s.abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        for (int i = 0; i < a.nmat; ++i) {
+            prefetch_tmap(&maps.w[i]);
+            prefetch_tmap(&maps.a[i]);
+        }
+    }
+    if (warp == 1) tmem_alloc(&s.tmem_base, tmem_cols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = s.tmem_base;
+    tcs_cluster_arrive();            // this CTA's barriers exist; the matching wait comes just before the exchange
+    if (threadIdx.x == 0) tc_mark(a, 1);
+
+    if (warp == 0) {
+        // ============================== TMA producer ==============================
+        if (lane == 0) {
+            const int npre = min(total, a.stages);
+            for (int n = 0; n < npre; ++n) {           // weights first: they do not depend on the previous kernel
+                const int mat = n / nk, kc = kc0 + (n - mat * nk);
+                mbar_expect_tx(&s.full[n], stage_bytes);
+                tma_load_2d(ring + (size_t)n * stage_bytes, &maps.w[mat], kc * kChunk, prow, &s.full[n]);
+            }
+            tc_mark(a, 2);
+            griddep_wait();                            // the activation codes are written by the previous kernel
+            tc_mark(a, 3);
+            for (int n = 0; n < total; ++n) {
+                const int st = n % a.stages;
+                const int mat = n / nk, kc = kc0 + (n - mat * nk);
+                uint8_t* dst = ring + (size_t)st * stage_bytes;
+                if (n >= npre) {
+                    if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { tcs_abort(s, a); break; }
+                    mbar_expect_tx(&s.full[st], stage_bytes);
+                    tma_load_2d(dst, &maps.w[mat], kc * kChunk, prow, &s.full[st]);
+                }
+                tma_load_2d(dst + kABytes, &maps.a[mat], kc * kChunk, 0, &s.full[st]);
+            }
+            tc_mark(a, 10);
+        }
+    } else if (warp == 1) {
+        // ============================== MMA issuer ==============================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(KIND, kTileP, a.NB);
+            for (int n = 0; n < total; ++n) {
+                const int st = n % a.stages;
+                const int mat = n / nk, i = n - mat * nk;
+                if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag, a.wait_ns)) { tcs_abort(s, a); break; }
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(ring + (size_t)st * stage_bytes);
+                const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
+                const uint32_t d = tmem_base + (uint32_t)(mat * a.acc_stride);
+#pragma unroll
+                for (int k = 0; k < kChunk / 32; ++k)
+                    tc_mma<KIND>(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&s.empty[st]);
+                if (i == nk - 1) tc_commit(&s.tfull[mat]);
+                if (n == 0) tc_mark(a, 5);
+            }
+            tc_mark(a, 6);
+        }
+    }
+    __syncwarp();                    // single-lane roles: the other lanes wait here for their lane 0
+    tcs_cluster_wait();              // every CTA of the cluster has initialised its barriers
+    if (warp < 2) tcs_cluster_arrive();      // these warps never touch a peer's shared memory (the epilogue warps arrive after their last store)
+
+    if (warp >= 2) {
+        // ============================== exchange + epilogue ==============================
+        griddep_wait();
+        const int q = warp & 3;                         // TMEM lane quarter this warp may read
+        const int et = (warp - 2) * 32 + lane;          // thread index inside the epilogue group
+        const int l = q * 32 + lane;                    // row of the tile held by this thread
+        const uint32_t owner = (uint32_t)(l / R);
+        const int lr = l - (int)owner * R;
+        const uint32_t remote = tcs_mapa(smem_u32(rxbuf), owner) + (uint32_t)(((size_t)rank * a.M * R + lr) * 4);
+        const uint32_t remote_rx = tcs_mapa(smem_u32(&s.rx), owner);
+        // what the final pass needs from global memory is fetched now, not behind the exchange: a thread of the final
+        // pass keeps ONE weight row (R divides 128) and walks the tokens
+        const int my_c = et % R, my_m0 = et / R, m_step = 128 / R;
+        const int my_row = prow + rank * R + my_c;
+        const bool per_row = (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) != 0;
+        float wrow[3], act_scale[3];
+        for (int i = 0; i < a.nmat; ++i) {
+            wrow[i] = __ldg(a.ws[i] + (per_row ? min(my_row, a.N - 1) : 0));
+            act_scale[i] = 0.f;
+            if constexpr (KIND == KIND_F8) {
+                const float v = __ldg(a.a_scale[i]);
+                act_scale[i] = a.amax_is_amax ? div_mode_f32(fmaxf(v, 1e-12f), 448.f, a.div_mode) : v;
+            }
+        }
+        for (int mat = 0; mat < a.nmat; ++mat) {
+            bool have = mbar_wait(&s.tfull[mat], 0, abort_flag, a.wait_ns);
+            if (!have) tcs_abort(s, a);
+            have = __all_sync(0xffffffffu, have);       // the tensor-memory loads below are warp-wide
+            tc_fence_after_sync();
+            if (et == 0 && mat == a.nmat - 1) tc_mark(a, 7);
+            // the owners' buffers are reused from matrix to matrix: every owner reports when it has emptied its own
+            if (mat > 0 && !tcs_wait_cluster(&s.rxfree, (uint32_t)((mat - 1) & 1), abort_flag, a.wait_ns)) tcs_abort(s, a);
+            // this CTA's partial sums of row l go to slot `rank` of the owner's buffer (zeros after a timeout, so that
+            // the peers' waits end)
+            const uint32_t taddr = tmem_base + (uint32_t)(mat * a.acc_stride) + ((uint32_t)(q * 32) << 16);
+            for (int c0 = 0; c0 < a.M; c0 += 16) {
+                uint32_t r[16];
+                if (have) {
+                    tmem_ld16(taddr + c0, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c0 + j < a.M) tcs_st_remote(remote + (uint32_t)((c0 + j) * R * 4), r[j]);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane % min(R, 32) == 0) tcs_arrive_remote(remote_rx);
+            if (et == 0 && mat == a.nmat - 1) tc_mark(a, 8);
+            if (mat == a.nmat - 1) tcs_cluster_arrive();      // this thread's last access to a peer's shared memory is behind it
+            // ---- this CTA's rows: add the C contributions in rank order, scale, store
+            const bool got = tcs_wait_cluster(&s.rx, (uint32_t)(mat & 1), abort_flag, a.wait_ns);
+            if (!got) tcs_abort(s, a);
+            if (et == 0 && mat == a.nmat - 1) tc_mark(a, 9);
+            if (got && !*abort_flag && my_row < a.N) {
+                for (int m = my_m0; m < a.M; m += m_step) {
+                    T sum = 0;
+                    for (int src = 0; src < C; ++src) sum += rxbuf[((size_t)src * a.M + m) * R + my_c];
+                    float f;
+                    if constexpr (KIND == KIND_F8) {
+                        f = sum * (act_scale[mat] * wrow[mat]);
+                    } else {
+                        if (a.acc[mat]) a.acc[mat][(int64_t)m * a.ldacc + my_row] = sum;
+                        f = (float)sum * (__ldg(a.a_scale[mat] + m) * wrow[mat]);
+                    }
+                    if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
+                    a.out[mat][(int64_t)m * a.ldo + my_row] = __float2half_rn(f);
+                }
+            }
+            if (mat + 1 < a.nmat) {                    // this CTA's buffer is empty: tell every sender of the cluster
+                named_bar_sync(1, 128);
+                if (et < C) tcs_arrive_remote(tcs_mapa(smem_u32(&s.rxfree), (uint32_t)et));
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+    if (threadIdx.x == 64) tc_mark(a, 11);
+    tcs_cluster_wait();              // nobody leaves while a peer may still store into its shared memory
+    if (threadIdx.x == 64) tc_mark(a, 12);
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+// Cluster size for one matrix: as many CTAs per 128-row tile as keep the grid within two CTAs per SM, at most 8 and at
+// most one per 128-byte step of K.  It depends on the matrix alone (not on how many matrices a launch carries), so a
+// fused r/k/v launch and three single launches split K alike and give the same bits.
+static int tcs_cluster_size(int64_t N, int64_t K) {
+    const int64_t ptiles = (N + kTileP - 1) / kTileP, kchunks = (K + kChunk - 1) / kChunk;
+    static const int cmax = std::getenv("RWKVQ_TCS_CMAX") ? std::atoi(std::getenv("RWKVQ_TCS_CMAX")) : 8;
+    int c = 1;
+    while (c < cmax && ptiles * (c * 2) <= 2 * (int64_t)sm_count() && kchunks >= c * 2) c <<= 1;
+    return c;
+}
+
+// Measured on the 7.2B shapes: the cluster kernel wins where a matrix has few row tiles (N = 4096: 32), i.e. where the
+// tiled GEMM form cannot give every SM a tile; with 128 row tiles (N = 16384) the GEMM form is as fast or faster.
+static bool tcs_eligible(int64_t M, int64_t N, int64_t K, uint32_t flags, int nmat) {
+    (void)nmat;                  // the K split and the grid are those of one matrix
+    static const int on = std::getenv("RWKVQ_TCS") ? std::atoi(std::getenv("RWKVQ_TCS")) : 1;
+    static const int64_t max_m = std::getenv("RWKVQ_TCS_MAX_M") ? std::atoll(std::getenv("RWKVQ_TCS_MAX_M")) : kTcsMaxM;
+    if (!on || M < 1 || M > std::min<int64_t>(max_m, kTcsMaxM) || (flags & RWKVQ_FLAG_RELU2)) return false;
+    const int64_t ptiles = (N + kTileP - 1) / kTileP;
+    const int c = tcs_cluster_size(N, K);
+    return K >= 1024 && c >= 4 && ptiles * c <= 2 * (int64_t)sm_count();
+}
+
+static int32_t run_tcs(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
+    const int C = tcs_cluster_size(a.N, a.K);
+    a.NB = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : 64);
+    a.ptiles = (a.N + kTileP - 1) / kTileP;
+    a.qtiles = C;
+    a.max_slots = 1;
+    a.acc_stride = std::max(a.NB, 32);
+    if (a.status == nullptr) a.status = c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : device_status_ptr();
+    const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk;
+    const size_t rx_bytes = (size_t)a.M * kTileP * 4;       // [C][M][128 / C] partial sums
+    const int per_cta = (a.kchunks + C - 1) / C;
+    a.stages = (int)std::min<size_t>(std::min<int>(kTcsMaxStages, per_cta * a.nmat), (kTcSmemBudgetHalf - 1024 - rx_bytes) / stage_bytes);
+    RWKVQ_REQUIRE(a.stages >= 2 || per_cta * a.nmat == 1, RWKVQ_E_SHAPE, "%s: shared memory leaves fewer than two ring stages", who);
+    a.stages = std::max(a.stages, 1);
+    TcMaps maps;
+    for (int i = 0; i < a.nmat; ++i) {
+        int32_t rc = make_map(&maps.w[i], c.w[i], a.N, a.K, c.ldw, kTileP, who);
+        if (rc) return rc;
+        rc = make_map(&maps.a[i], c.codes[i], a.M, a.K, c.lda, a.NB, who);
+        if (rc) return rc;
+    }
+    auto kern = c.kind == KIND_F8 ? gemm_tcs_kernel<KIND_F8> : gemm_tcs_kernel<KIND_I8>;
+    const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudgetHalf, who);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(a.ptiles * C));
+    cfg.blockDim = dim3(kTcsThreads);
+    cfg.dynamicSmemBytes = (size_t)a.stages * stage_bytes + rx_bytes + 1024;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 2 : 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, maps, a);
+    if (err != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(err));
+    }
+    return check_launch(who);
+}
+
+}  // namespace rwkvq

@@ -4,12 +4,14 @@ linear dispatchers) on top of librwkvq.so.  Names, arguments and the weight-info
     {"weight": [N, K] float8_e4m3fn | int8 (contiguous, on the device),
      "tensor_scale": fp32 scalar on the device, "qtype": "fp8" | "int8"}          (fp8_ops.py:26-49)
 """
+import os
+
 import torch
 
 import rwkvq_abi as abi
 
 FP8_E4M3_MAX = 448.0
-FUSED_M_MAX = 512   # rows up to which the engine takes the fused r/k/v route (fp8_ops.py:118)
+FUSED_M_MAX = int(os.environ.get("RWKVQ_FUSED_M_MAX", "512"))   # rows up to which the engine takes the fused r/k/v route (fp8_ops.py:118); the fused calls here serve any row count
 
 
 def is_fp8_weight(z, key):

@@ -36,7 +36,7 @@ import torch
 import rwkvq_abi as abi
 
 F8E4M3_MAX = 448.0
-FUSED_M_MAX = 512      # kept for importers (fused_fp8_gemm.py:1101); this build has no cuBLASLt route to switch to
+FUSED_M_MAX = int(os.environ.get("RWKVQ_FUSED_M_MAX", "512"))   # kept for importers (fused_fp8_gemm.py:1101); this build has no cuBLASLt route to switch to
 USE_CUDA_GRAPH = False  # kept for importers (fused_fp8_gemm.py:941); graphs are the caller's business here
 
 GEMV_M_MAX = 32
@@ -47,13 +47,14 @@ ROUTE = os.environ.get("RWKVQ_ROUTE", "auto").lower()   # auto | tc | mma
 GEMV_AUTO_M_MAX = 32
 _ACTQ_FUSED = os.environ.get("RWKVQ_ACTQ", "fused") == "fused"   # one cooperative launch; else memset + two kernels
 CODES_M_MIN = int(os.environ.get("RWKVQ_CODES_M_MIN", "9"))      # rows from which the decode GEMV runs on pre-quantized codes
+TC_M_MIN = int(os.environ.get("RWKVQ_TC_M_MIN", "33"))          # rows from which the tensor-memory kernels take over from the decode GEMVs (never below 9)
 CODES_MK_MIN = 49152       # ... and already from 3 rows when the block is this large (long rows: K = 16384); measured
 _decode_route_cache: dict = {}
 
 
 def _codes_gemv_fits(m: int, k: int) -> bool:
     """The decode GEMV on pre-quantized codes: CODES_M_MIN..32 rows whose 1-byte code tile fits shared memory."""
-    if not (m >= CODES_M_MIN or (m >= 3 and m * k >= CODES_MK_MIN and CODES_M_MIN <= GEMV_M_MAX)) or m > GEMV_M_MAX or ROUTE != "auto" or k % 16:
+    if not (m >= CODES_M_MIN or (m >= 3 and m * k >= CODES_MK_MIN and CODES_M_MIN <= GEMV_M_MAX)) or m > GEMV_M_MAX or (m >= TC_M_MIN and m > 8) or ROUTE != "auto" or k % 16:
         return False
     fits = _decode_route_cache.get((m, k))
     if fits is None:
@@ -83,7 +84,7 @@ def _unpack(weight_info_or_w, res_scale=None):
 def _gemv_fits(m: int, k: int, fp8: bool = True) -> bool:
     """The fused mma.sync GEMV keeps the quantized activations in shared memory (FP8: 2 bytes each, INT8: 1)."""
     pitch = (2 * k + 127) // 128 * 128 + 16 if fp8 else (k + 127) // 128 * 128 + 64
-    if not (0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0):
+    if not (0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0) or (m >= TC_M_MIN and m > 8 and ROUTE == "auto"):
         return False
     return ROUTE == "mma" or (ROUTE == "auto" and m <= GEMV_AUTO_M_MAX)
 
