@@ -335,6 +335,16 @@ int64_t rwkvq_gemv_int4_group_smem_bytes(int64_t M, int64_t K);
 int32_t rwkvq_gemv_int4_group(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw, const void* scales,
                               const float* zeros, int32_t scale_is_f16, int32_t group, void* out_f16, int64_t ldo,
                               int64_t M, int64_t N, int64_t K, void* stream);
+/* The same kernel with K cut into slices, for blocks of activations too large to sit beside a deep weight ring (many
+ * rows and / or long rows: 16 rows of K = 16384 would otherwise take four passes over the weights).  Group 128, fp32
+ * scales, K a multiple of 512, M <= 16.  Two launches: the streaming kernel over (row tiles) x (K slices) stores fp32
+ * partial sums into `workspace`, a second kernel adds them in slice order (run-to-run identical).
+ * rwkvq_gemv_int4_ksplit_slices(M, N, K): slices this form uses (1: the plain entry does the same in one launch;
+ * 0: unsupported shape).  workspace: slices * M * N * 4 bytes, 16-byte aligned, contents irrelevant. */
+int32_t rwkvq_gemv_int4_ksplit_slices(int64_t M, int64_t N, int64_t K);
+int32_t rwkvq_gemv_int4_group_ksplit(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw, const float* scales,
+                                     const float* zeros, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                     void* workspace, int64_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------- NVFP4 (W4A4, block-scaled)
  *

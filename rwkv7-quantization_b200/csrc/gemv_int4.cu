@@ -192,11 +192,20 @@ constexpr int kI4Stage = kI4D * 1024 + 512;               // bytes per warp and 
 struct I4FastArgs {
     I4Args b;
     int lgR, tq, trem;            // log2 of the 16-row tiles per round; tiles per CTA (quotient, remainder)
+    float* part;                  // SPLIT: fp32 partial sums [slices][M][N]
+    int kslice;                   // SPLIT: k per slice (b.K holds the same value; b.ngroups stays the row pitch of the scales)
 };
 
-template <int NT, int S>
+// SPLIT: K is cut into gridDim.y slices (the activation tile of one slice fits beside a ring with two CTAs per SM);
+// CTA (x, y) works on columns [y * kslice, (y + 1) * kslice) of its row tiles and stores fp32 partial sums, which
+// i4_reduce_kernel adds in slice order.  A separate instantiation: the single-launch decode path carries none of it.
+template <int NT, int S, bool SPLIT = false>
 __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArgs fa) {
     const I4Args& a = fa.b;
+    const int64_t koff = SPLIT ? (int64_t)blockIdx.y * fa.kslice : 0;
+    const uint8_t* const wbase = a.w + (koff >> 1);
+    const __half* const xbase = a.x + koff;
+    const float* const zbase = a.zeros ? a.zeros + (koff >> 7) : nullptr;
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: red[2][kWarps][NT*4][32] floats | ring[kWarps][S][kI4Stage] | xbar (128 B) | xsum[M][units] floats | xs[M][pitch]
     const int units = a.K >> 7;
@@ -220,20 +229,20 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
     const int my_rounds = (nch > 0 && te - tb > slot) ? ((te - tb - slot + R - 1) >> lgR) : 0;
     uint8_t* my_ring = ring + (size_t)warp * S * kI4Stage;
     const uint32_t my_ring_s = (uint32_t)__cvta_generic_to_shared(my_ring);
-    const float* scales = reinterpret_cast<const float*>(a.scales);
+    const float* scales = reinterpret_cast<const float*>(a.scales) + (koff >> 7);
     const bool has_z = a.zeros != nullptr;
 
     // producer: per chunk 8 weight copies per lane and one scale / zero vector
     int p_round = 0, p_ch = 0, p_stage = 0;
-    const uint8_t *p_w0 = a.w, *p_w1 = a.w;
+    const uint8_t *p_w0 = wbase, *p_w1 = wbase;
     const float* p_sz = scales;
     const bool sz_on = t < 2 || has_z;
     auto set_rows = [&](int round) {
         const int n0 = (tb + round * R + slot) << 4;
         const int r0 = min(n0 + g, a.N - 1), r1 = min(n0 + g + 8, a.N - 1);
-        p_w0 = a.w + (int64_t)r0 * a.ldw + ub * 64 + 16 * t;
-        p_w1 = a.w + (int64_t)r1 * a.ldw + ub * 64 + 16 * t;
-        p_sz = ((t & 2) ? a.zeros : scales) + (int64_t)((t & 1) ? r1 : r0) * a.ngroups + ub;
+        p_w0 = wbase + (int64_t)r0 * a.ldw + ub * 64 + 16 * t;
+        p_w1 = wbase + (int64_t)r1 * a.ldw + ub * 64 + 16 * t;
+        p_sz = ((t & 2) ? zbase : scales) + (int64_t)((t & 1) ? r1 : r0) * a.ngroups + ub;
     };
     if (my_rounds > 0) set_rows(0);
     auto issue = [&]() {
@@ -287,7 +296,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
 #pragma unroll 1
             for (int r = 0; r < a.M; ++r)
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"((uint32_t)__cvta_generic_to_shared(xs + (size_t)r * a.pitch)), "l"(a.x + (int64_t)r * a.ldx),
+                             ::"r"((uint32_t)__cvta_generic_to_shared(xs + (size_t)r * a.pitch)), "l"(xbase + (int64_t)r * a.ldx),
                                "r"((uint32_t)(a.K * 2)), "r"(b) : "memory");
         }
         if (!w8_staged_or_report(xbar, a.status, a.wait_ns)) {     // reported: drain the weight ring and stop
@@ -409,11 +418,27 @@ __global__ void __launch_bounds__(kThr, 2) gemv_int4_g128_kernel(const I4FastArg
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int m = i * 8 + 2 * t + (j & 1), n = n0 + g + ((j & 2) ? 8 : 0);
-                    if (m < a.M && n < a.N) a.out[(int64_t)m * a.ldo + n] = __float2half_rn(tot[i][j]);
+                    if (m < a.M && n < a.N) {
+                        if constexpr (SPLIT) fa.part[((int64_t)blockIdx.y * a.M + m) * a.N + n] = tot[i][j];
+                        else a.out[(int64_t)m * a.ldo + n] = __float2half_rn(tot[i][j]);
+                    }
                 }
         }
     }
     cp_async_wait<0>();
+}
+
+// out[m][n] = fp16(sum over slices, in slice order, of part[s][m][n])
+__global__ void __launch_bounds__(256) i4_reduce_kernel(const float* __restrict__ part, int slices, int M, int N, __half* out, int64_t ldo) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int64_t total = (int64_t)M * N;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        float v = 0.f;
+        for (int sl = 0; sl < slices; ++sl) v += __ldcg(part + (int64_t)sl * total + i);
+        const int64_t m = i / N;
+        out[m * ldo + (i - m * N)] = __float2half_rn(v);
+    }
 }
 
 static size_t i4_fast_smem(int NT, int S, int M, int K) {
@@ -422,12 +447,12 @@ static size_t i4_fast_smem(int NT, int S, int M, int K) {
 }
 
 template <typename Kern, typename Args>
-static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64_t tiles, bool fast) {
+static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64_t tiles, bool fast, int slices = 1) {
     int per_sm = 0;
     const int32_t rc = kernel_plan(reinterpret_cast<const void*>(kern), kThr, smem, 224 * 1024, &per_sm, "gemv_int4_group");
     if (rc != RWKVQ_OK) return rc;
     cudaError_t e;
-    const int grid = (int)std::min<int64_t>(tiles, (int64_t)sm_count() * std::min(per_sm, 2));
+    const int grid = (int)std::min<int64_t>(tiles, std::max<int64_t>(1, (int64_t)sm_count() * std::min(per_sm, 2) / slices));
     if constexpr (std::is_same<Args, I4FastArgs>::value) {
         a.b.status = device_status_ptr();
         a.b.wait_ns = wait_limit_ns();
@@ -439,7 +464,7 @@ static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64
     }
     (void)fast;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)grid, (unsigned)slices);
     cfg.blockDim = dim3(kThr);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -454,6 +479,31 @@ static int32_t launch_i4(Kern kern, Args& a, size_t smem, cudaStream_t st, int64
         return fail(RWKVQ_E_LAUNCH, "gemv_int4_group: %s", cudaGetErrorString(e));
     }
     return check_launch("gemv_int4_group");
+}
+
+// K slices of the split form: the fewest (a power of two, whole 512-k chunks per slice) whose activation tile is at
+// most about 64 KB, which leaves room for a three- or four-stage weight ring; 1 = the single launch already has that;
+// 0 = not even 512-k slices fit.
+static int i4_slices(int M, int64_t N, int K) {
+    // measured on the 7.2B shapes: a block that still fits one launch is better left whole when the matrix has many
+    // row tiles (N = 16384: 21 us whole, 23 us split at 16 rows); with few (N = 4096) the split wins (11.8 -> 10.8 us)
+    if (N > 8192 && i4_fast_smem(M <= 8 ? 1 : 2, 2, M, K) <= 224 * 1024) return 1;
+    static const size_t tile_max = std::getenv("RWKVQ_INT4_SPLIT_TILE") ? (size_t)std::atoll(std::getenv("RWKVQ_INT4_SPLIT_TILE")) : 66 * 1024;
+    int sl = 1;
+    while (sl < 32 && (size_t)M * (2 * (size_t)(K / sl) + 16) > tile_max && (K / (sl * 2)) % 512 == 0 && K / (sl * 2) >= 512) sl <<= 1;
+    return i4_fast_smem(M <= 8 ? 1 : 2, 2, M, K / sl) <= 224 * 1024 ? sl : 0;
+}
+
+template <int NT>
+static int32_t launch_i4_split(I4FastArgs& fa, cudaStream_t st, int slices) {
+    constexpr size_t kTwo = 110 * 1024, kMax = 224 * 1024;
+    const I4Args& a = fa.b;
+    const int64_t tiles = (a.N + 15) / 16;
+    const size_t s4 = i4_fast_smem(NT, 4, a.M, a.K), s3 = i4_fast_smem(NT, 3, a.M, a.K), s2 = i4_fast_smem(NT, 2, a.M, a.K);
+    if (s2 <= kTwo) return launch_i4(gemv_int4_g128_kernel<NT, 2, true>, fa, s2, st, tiles, true, slices);
+    if (s4 <= kMax) return launch_i4(gemv_int4_g128_kernel<NT, 4, true>, fa, s4, st, tiles, true, slices);
+    if (s3 <= kMax) return launch_i4(gemv_int4_g128_kernel<NT, 3, true>, fa, s3, st, tiles, true, slices);
+    return launch_i4(gemv_int4_g128_kernel<NT, 2, true>, fa, s2, st, tiles, true, slices);
 }
 
 template <int NT>
@@ -477,6 +527,59 @@ static int32_t launch_i4_fast(const I4Args& a, cudaStream_t st, bool* done) {
 using namespace rwkvq;
 
 extern "C" {
+
+/* K-split form of rwkvq_gemv_int4_group for blocks of activations that do not fit beside a weight ring with two CTAs
+ * per SM (many rows, long rows): group 128, fp32 scales, K a multiple of 512, M <= 16.  Two launches: the streaming
+ * kernel over (row tiles) x (K slices) storing fp32 partial sums into `workspace`, then their sum in slice order.
+ * rwkvq_gemv_int4_ksplit_slices(M, N, K): slices this form would use (1: the plain entry does the same in one launch; 0: unsupported);
+ * workspace of slices * M * N * 4 bytes, 16-byte aligned, contents irrelevant. */
+int32_t rwkvq_gemv_int4_ksplit_slices(int64_t M, int64_t N, int64_t K) {
+    if (M < 1 || M > 16 || N < 1 || K < 512 || K % 512) return 0;
+    return i4_slices((int)M, N, (int)K);
+}
+
+int32_t rwkvq_gemv_int4_group_ksplit(const void* x_f16, int64_t ldx, const uint8_t* packed, int64_t ldw, const float* scales,
+                                     const float* zeros, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                     void* workspace, int64_t workspace_bytes, void* stream) {
+    const char* who = "gemv_int4_group_ksplit";
+    RWKVQ_REQUIRE(x_f16 && packed && scales && out_f16, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(M >= 0 && M <= 16 && N >= 0 && K >= 0, RWKVQ_E_SHAPE, "%s: M=%lld (0..16), N=%lld, K=%lld", who, (long long)M, (long long)N, (long long)K);
+    if (M == 0 || N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(K >= 512 && K % 512 == 0, RWKVQ_E_SHAPE, "%s: K=%lld must be a multiple of 512", who, (long long)K);
+    RWKVQ_REQUIRE(aligned16(packed) && ldw % 16 == 0 && ldw >= K / 2, RWKVQ_E_ALIGN, "%s: packed rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(aligned16(x_f16) && ldx % 8 == 0 && ldx >= K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(aligned16(scales) && (zeros == nullptr || aligned16(zeros)), RWKVQ_E_ALIGN, "%s: scales / zeros must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(ldo >= N, RWKVQ_E_SHAPE, "%s: ldo < N", who);
+    const int slices = i4_slices((int)M, N, (int)K);
+    RWKVQ_REQUIRE(slices >= 1, RWKVQ_E_SHAPE, "%s: %lld rows of %lld do not fit shared memory even in 512-k slices", who, (long long)M, (long long)K);
+    RWKVQ_REQUIRE(workspace && aligned16(workspace) && workspace_bytes >= (int64_t)slices * M * N * 4, RWKVQ_E_WORKSPACE,
+                  "%s: workspace of %lld bytes needed", who, (long long)slices * M * N * 4);
+    cudaStream_t st = (cudaStream_t)stream;
+    I4FastArgs fa{};
+    I4Args& a = fa.b;
+    a.x = (const __half*)x_f16; a.w = packed; a.scales = scales; a.zeros = zeros; a.out = (__half*)out_f16;
+    a.ldx = ldx; a.ldw = ldw; a.ldo = ldo; a.M = (int)M; a.N = (int)N; a.K = (int)(K / slices); a.group = 128; a.scale_f16 = 0;
+    a.pitch = (int)(2 * (K / slices) + 16); a.ngroups = (int)(K / 128);
+    fa.part = reinterpret_cast<float*>(workspace);
+    fa.kslice = (int)(K / slices);
+    int32_t rc = M <= 8 ? launch_i4_split<1>(fa, st, slices) : launch_i4_split<2>(fa, st, slices);
+    if (rc != RWKVQ_OK) return rc;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)std::min<int64_t>((M * N + 255) / 256, 2 * (int64_t)sm_count()));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, i4_reduce_kernel, (const float*)fa.part, slices, (int)M, (int)N, (__half*)out_f16, ldo);
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return check_launch(who);
+}
 
 int64_t rwkvq_gemv_int4_group_smem_bytes(int64_t M, int64_t K) {
     const int64_t units = K / 128, pitch = 2 * K + 16;

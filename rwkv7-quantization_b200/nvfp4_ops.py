@@ -23,7 +23,7 @@ import rwkvq_abi as abi
 E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 BLOCK = 16
 GEMV_ROWS = 16
-TC_MIN_M = 16      # more tokens than this go to the tensor-core GEMM
+TC_MIN_M = int(os.environ.get("RWKVQ_NVFP4_TC_MIN_M", "8"))   # more tokens than this go to the tensor-core GEMM (measured: from 9 rows it is as fast or faster on the 7.2B shapes)
 
 
 def _e2m1_codes(v: torch.Tensor) -> torch.Tensor:
@@ -129,7 +129,8 @@ def _route(m: int, k: int) -> str:
     # the tensor scale is per call: all rows must go into one launch
     if k % 512 == 0 and abi.lib().rwkvq_gemv_nvfp4_fused_smem_bytes(m, k) <= 224 * 1024:
         return "fused"
-    return "gemv"
+    # rows that do not fit one fused launch (long rows): the GEMM streams the weights once, row blocks would re-read them
+    return "tc" if m > 4 else "gemv"
 
 
 def linear_nvfp4(x, weight_info, out_dtype=torch.float16):

@@ -66,6 +66,8 @@ SIGNATURES = {
     "rwkvq_gemv_int8_affine": [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _p],
     "rwkvq_gemv_int4_group_smem_bytes": [_i64, _i64],
     "rwkvq_gemv_int4_group": [_p, _i64, _p, _i64, _p, _p, _i32, _i32, _p, _i64, _i64, _i64, _i64, _p],
+    "rwkvq_gemv_int4_ksplit_slices": [_i64, _i64, _i64],
+    "rwkvq_gemv_int4_group_ksplit": [_p, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _p],
     "rwkvq_actq_nvfp4": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _i64, _p, _p, _p],
     "rwkvq_gemv_nvfp4_smem_bytes": [_i64, _i64],
     "rwkvq_gemv_nvfp4": [_p, _i64, _p, _i64, _p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _p],
@@ -295,6 +297,20 @@ def workspace(m: int, n: int, k: int, nmat: int, device) -> torch.Tensor:
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+_plain: dict = {}
+
+
+def plain_scratch(nbytes: int, device) -> torch.Tensor:
+    """Uninitialised scratch (partial sums that a kernel writes before another reads them), one per (device, stream),
+    grown on demand.  Separate from workspace(): that one must stay zero between launches."""
+    key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
+    buf = _plain.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _plain[key] = buf
+    return buf
 
 
 def workspace_status(ws: torch.Tensor) -> int:

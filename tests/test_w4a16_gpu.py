@@ -58,6 +58,27 @@ def test_int4_groupwise_7b_shapes(mods, n, k):
     assert rel_err(y, O.linear_w4a16_kernel_semantics(x1.reshape(1, -1), wdq).reshape(-1)) <= 1e-2
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 520, 16384), (12, 100, 8192), (16, 1000, 4096), (5, 264, 16384), (40, 300, 16384)])
+def test_int4_k_split_equals_single_launch_form(mods, m, n, k, monkeypatch):
+    """Blocks of activations too large for one launch run with K in slices (fp32 partial sums added in slice order):
+    one pass over the weights; within 1e-2 of the oracle, close to the row-block form, and run-to-run identical."""
+    import rwkvq_abi as abi
+    i4, f4, q4 = mods[0], mods[1], mods[2]
+    info = q4.quantize_to_int4_groupwise(gen(n + k + m, (n, k), (1.0 / k) ** 0.5), 128)
+    info["qtype"] = "int4_groupwise"
+    d = dev(info)
+    x = gen(m + 7, (m, k), 1.0, torch.float16)
+    assert abi.lib().rwkvq_gemv_int4_ksplit_slices(min(m, 16), n, k) > 1
+    before = abi.launch_count()
+    out = i4.linear_int4(x.cuda(), d)
+    assert abi.launch_count() - before == 2 * ((m + 15) // 16)          # streaming kernel + slice sum per block of 16 rows
+    want = O.linear_w4a16_kernel_semantics(x, O.dequant_int4_groupwise(info))
+    assert rel_err(out, want) <= 1e-2
+    assert torch.equal(out, i4.linear_int4(x.cuda(), d))
+    monkeypatch.setenv("RWKVQ_INT4_KSPLIT", "0")                         # the row-block form on the same inputs
+    assert rel_err(out, i4.linear_int4(x.cuda(), d).float().cpu()) <= 2e-3
+
+
 @pytest.mark.parametrize("group", [128, 256, 64, 32])
 @pytest.mark.parametrize("m", [1, 3, 16, 20])
 def test_int4_groupwise_variants(mods, group, m, monkeypatch):
