@@ -495,7 +495,8 @@ def run_ours(args, rank, world, local_rank):
 def colsplit_leg(world, dev, dist_on):
     """NVFP4 FFN key [16384, 4096] split by output rows over the ranks, activations replicated, slices gathered along
     the features: per M the local GEMM, the gather alone (NCCL all-gather + layout copy vs the library's peer-memory
-    pull) and both end to end; microseconds are maxima over ranks, GB/s counts the bytes a rank RECEIVES over NVLink."""
+    pull), both end to end, and the fused form (push: the GEMM's epilogue stores its tiles into every rank's buffer and
+    the receivers wait for a flag); microseconds are maxima over ranks, GB/s counts the bytes a rank RECEIVES over NVLink."""
     import fp8_ops
     import nvfp4_ops
     import rwkvq_dist as D
@@ -505,7 +506,8 @@ def colsplit_leg(world, dev, dist_on):
     del w
     lin = fp8_ops.linear_quantized
     rows = []
-    splits = {"nccl": D.ColumnSplitLinear(info, lin, gather="nccl"), "peer": D.ColumnSplitLinear(info, lin, gather="peer", max_rows=4096)}
+    splits = {"nccl": D.ColumnSplitLinear(info, lin, gather="nccl"), "peer": D.ColumnSplitLinear(info, lin, gather="peer", max_rows=4096),
+              "push": D.ColumnSplitLinear(info, lin, gather="push", max_rows=4096)}
     local = splits["nccl"].local
     nl = F // world
     for m in (1, 256, 4096):
@@ -524,7 +526,7 @@ def colsplit_leg(world, dev, dist_on):
             splits["peer"].peer.next_buffer(m)
             splits["peer"].peer.gather()
         legs = {"local_gemm": lambda: lin(x, local), "nccl_gather": nccl_gather, "peer_gather": peer_gather,
-                "nccl_e2e": lambda: splits["nccl"](x), "peer_e2e": lambda: splits["peer"](x)}
+                "nccl_e2e": lambda: splits["nccl"](x), "peer_e2e": lambda: splits["peer"](x), "push_e2e": lambda: splits["push"](x)}
         row = {"M": m, "bytes_received_per_rank": m * (F - nl) * 2}
         for name, fn in legs.items():
             for _ in range(3):
@@ -533,9 +535,12 @@ def colsplit_leg(world, dev, dist_on):
         for mode in ("nccl", "peer"):
             row[mode + "_gather_GBps"] = round(row["bytes_received_per_rank"] / row[mode + "_gather_us"] / 1e3, 1)
         row["peer_vs_nccl_e2e"] = round(row["nccl_e2e_us"] / row["peer_e2e_us"], 2)
+        row["push_vs_nccl_e2e"] = round(row["nccl_e2e_us"] / row["push_e2e_us"], 2)
+        row["push_fused"] = bool(nvfp4_ops.can_push(m, C))     # False: few rows take the decode GEMV and the pull form
         rows.append(row)
-    splits["peer"].peer.check()
-    splits["peer"].peer.close()
+    for mode in ("peer", "push"):
+        splits[mode].peer.check()
+        splits[mode].peer.close()
     return {"workload": "NVFP4 FFN key [16384,4096] column-split over the ranks, bf16 activations replicated, fp16 [M,16384] gathered on every rank",
             "timing": "CUDA events on the launching stream, eager calls, max over ranks", "nvlink_peak_GBps_per_direction": 770.0, "rows": rows}
 

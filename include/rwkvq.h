@@ -400,6 +400,17 @@ int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* 
                             const uint8_t* w_codes, int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale,
                             void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
                             int64_t workspace_bytes, void* stream);
+/* rwkvq_tc_gemm_nvfp4 FUSED with the all-gather of a column-split projection (one kernel: tensor-core tiles and peer
+ * stores).  Every result vector is also stored, by plain peer stores over NVLink, at the same offset behind
+ * peer_out[p] -- this rank's column range in rank p's [M, ldo] buffer, aligned like out_f16 -- for p < npeers <= 7, so
+ * the gather travels while the next tiles are computed.  When the whole grid has stored its tiles, `epoch` is
+ * published (system-scope release) at peer_flag[p], this rank's slot in rank p's flag array; the receivers call
+ * rwkvq_peer_wait.  The workspace is required (it counts finished CTAs); M, N > 0.  No TMA on peer memory. */
+int32_t rwkvq_tc_gemm_nvfp4_push(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts,
+                                 const uint8_t* w_codes, int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale,
+                                 void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
+                                 int64_t workspace_bytes, void* const* peer_out, void* const* peer_flag, int32_t npeers,
+                                 uint32_t epoch, void* stream);
 
 /* No counterpart in the reference.  rwkvq_tc_gemm_fp8 for callers that cannot supply device scratch -- a host runtime
  * that owns every byte of device memory and forbids allocation inside its serving loop, or code running where
@@ -442,6 +453,9 @@ int32_t rwkvq_enable_peer_access(int32_t peer_device);
 int32_t rwkvq_peer_signal(void* const* flag_arrays, int32_t rank, int32_t world, uint32_t epoch, void* stream);
 int32_t rwkvq_allgather_cols_pull(void* const* outs, const uint32_t* my_flags, uint32_t epoch, int32_t rank, int32_t world,
                                   int64_t M, int64_t n_local, int64_t ld, int32_t* status, void* stream);
+/* Receiver side of a pushed result (rwkvq_tc_gemm_nvfp4_push): waits on `stream`, bounded, until flags[r] == epoch for
+ * every r != rank; a rank that never signals leaves RWKVQ_E_TIMEOUT in *status (NULL: the per-device status word). */
+int32_t rwkvq_peer_wait(const uint32_t* my_flags, uint32_t epoch, int32_t rank, int32_t world, int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------- bounded waits, status, diagnostics
  *

@@ -90,6 +90,13 @@ __global__ void __launch_bounds__(256) allgather_cols_pull_kernel(PeerPtrs outs,
     }
 }
 
+// Receiver side of a projection that PUSHES its result to the peers: wait, bounded, until every other rank has
+// published `epoch`.  One thread per source rank.
+__global__ void peer_wait_kernel(const uint32_t* my_flags, uint32_t epoch, int rank, int world, int* status, unsigned long long wait_ns) {
+    const int src = (int)threadIdx.x;
+    if (src < world && src != rank && !wait_peer_flag(my_flags + src, epoch, wait_ns) && status) atomicExch(status, RWKVQ_E_TIMEOUT);
+}
+
 }  // namespace rwkvq
 
 using namespace rwkvq;
@@ -168,6 +175,15 @@ int32_t rwkvq_peer_signal(void* const* flag_arrays, int32_t rank, int32_t world,
     }
     peer_signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pp, rank, world, epoch);
     return check_launch("peer_signal");
+}
+
+/* Wait on `stream` until flags[r] == epoch for every r != rank (the other ranks' pushed columns of this call are in
+ * this rank's buffer); a rank that never signals leaves RWKVQ_E_TIMEOUT in *status after the wait limit. */
+int32_t rwkvq_peer_wait(const uint32_t* my_flags, uint32_t epoch, int32_t rank, int32_t world, int32_t* status, void* stream) {
+    RWKVQ_REQUIRE(my_flags != nullptr && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, RWKVQ_E_BADARG, "peer_wait: rank %d of %d", rank, world);
+    if (world == 1) return RWKVQ_OK;
+    peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(my_flags, epoch, rank, world, status ? status : device_status_ptr(), wait_limit_ns());
+    return check_launch("peer_wait");
 }
 
 int32_t rwkvq_allgather_cols_pull(void* const* outs, const uint32_t* my_flags, uint32_t epoch, int32_t rank, int32_t world, int64_t M,

@@ -133,9 +133,16 @@ def _route(m: int, k: int) -> str:
     return "tc" if m > 4 else "gemv"
 
 
-def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
+def can_push(m: int, k: int) -> bool:
+    """True if linear_nvfp4 with these rows runs the kernel that can carry the all-gather of a column-split projection."""
+    return m > 0 and _route(m, k) == "tc"
+
+
+def linear_nvfp4(x, weight_info, out_dtype=torch.float16, push=None):
     """W4A4 projection: activations quantized per call, weights streamed in packed form.  Few tokens run the
-    weight-streaming GEMV; more than TC_MIN_M tokens run the tcgen05 block-scaled GEMM."""
+    weight-streaming GEMV; more than TC_MIN_M tokens run the tcgen05 block-scaled GEMM.
+    push = (peer_out_array, peer_flag_array, npeers, epoch) from rwkvq_dist.PeerGather.push_targets(): the GEMM also
+    stores its result into the peers' buffers and signals them (only on the GEMM route: check can_push first)."""
     w, wbs, wts = weight_info["weight"], weight_info["block_scale"], weight_info["tensor_scale"]
     n, k = w.shape[0], w.shape[1] * 2
     wts = wts.reshape(1)
@@ -143,6 +150,8 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
     x2 = _rows16(x).contiguous()
     m = x2.shape[0]
     route = _route(m, k)
+    if push is not None and route != "tc":
+        raise RuntimeError("rwkvq: the pushed all-gather rides in the tensor-core GEMM only (see can_push)")
     if route == "fused" and wbs.stride(0) % 16 == 0 and wbs.data_ptr() % 16 == 0:
         out = abi.new_out(m, n, x2.device)
         abi.call("rwkvq_gemv_nvfp4_fused", x2.data_ptr(), abi.dtype_code(x2), k, w.data_ptr(), w.stride(0), wbs.data_ptr(),
@@ -154,8 +163,13 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16):
     if route == "tc":
         ws = abi.workspace(1, 1, 1, 1, codes.device)
         a_blk, w_blk = bs, _blocked_weight_scales(weight_info, k)     # both alive until the launch
-        abi.call("rwkvq_tc_gemm_nvfp4", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),
-                 w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, ws.data_ptr(), ws.numel(), abi.stream_ptr())
+        if push is not None:
+            abi.call("rwkvq_tc_gemm_nvfp4_push", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),
+                     w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, ws.data_ptr(), ws.numel(),
+                     push[0], push[1], push[2], push[3], abi.stream_ptr())
+        else:
+            abi.call("rwkvq_tc_gemm_nvfp4", codes.data_ptr(), k // 2, a_blk.data_ptr(), pts.data_ptr(), w.data_ptr(), w.stride(0),
+                     w_blk.data_ptr(), wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, ws.data_ptr(), ws.numel(), abi.stream_ptr())
     else:
         rows = GEMV_ROWS
         while rows > 1 and abi.lib().rwkvq_gemv_nvfp4_smem_bytes(rows, k) > 200 * 1024:

@@ -78,6 +78,7 @@ SIGNATURES = {
     "rwkvq_nvfp4_blocked_scale_bytes": [_i64, _i64],
     "rwkvq_nvfp4_pack_scales": [_p, _i64, _i64, _i64, _p, _p],
     "rwkvq_tc_gemm_nvfp4": [_p, _i64, _p, _p, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _p],
+    "rwkvq_tc_gemm_nvfp4_push": [_p, _i64, _p, _p, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _i64, _p, _p, _i32, _u32, _p],
     "rwkvq_tc_gemm_fp8_static": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
     "rwkvq_actq_fp8_fused_scratch_bytes": [],
     "rwkvq_actq_fp8_fused": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _i64, _p, _i32, _u32, _p],
@@ -99,6 +100,7 @@ SIGNATURES = {
     "rwkvq_peer_free": [_p],
     "rwkvq_peer_signal": [_p, _i32, _i32, _u32, _p],
     "rwkvq_allgather_cols_pull": [_p, _p, _u32, _i32, _i32, _i64, _i64, _i64, _p, _p],
+    "rwkvq_peer_wait": [_p, _u32, _i32, _i32, _p, _p],
     "rwkvq_prep3_x_int8": [_p, _p, _p, _i32, _i64, _i64, _i64, _p, _p, _p, _i64, _p, _p, _p, _i32, _p],
     "rwkvq_gemm_decode_route": [_i64, _i64],
     "rwkvq_gemm_fp8_rkv": [_p, _p, _p, _i64, _p, _i32, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],

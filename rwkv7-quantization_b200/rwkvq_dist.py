@@ -101,6 +101,13 @@ class PeerGather:
         arr = ctypes.c_void_p * self.world
         self._out_arrays = [arr(*[b + i * buf_bytes for b in bases]) for i in range(2)]
         self._flag_array = arr(*[b + 2 * buf_bytes for b in bases])
+        # push form: this rank's column range in every OTHER rank's buffers, and its slot in their flag arrays
+        peers = [r for r in range(self.world) if r != self.rank]
+        parr = ctypes.c_void_p * max(len(peers), 1)
+        col0 = self.rank * self.nl * 2
+        self._push_out = [parr(*[bases[r] + i * buf_bytes + col0 for r in peers]) if peers else parr() for i in range(2)]
+        self._push_flag = parr(*[bases[r] + 2 * buf_bytes + 4 * self.rank for r in peers]) if peers else parr()
+        self._npeers = len(peers)
         self.epoch = 0
         dist.barrier(group=group)      # every rank has mapped every buffer before anyone signals
 
@@ -137,6 +144,16 @@ class PeerGather:
                  self.m, self.nl, self.n, self.status.data_ptr(), st)
         return self.bufs[b][:self.m]
 
+    def push_targets(self):
+        """What a pushing GEMM needs for the current call (after next_buffer): (peer_out, peer_flag, npeers, epoch)."""
+        return self._push_out[self.epoch & 1], self._push_flag, self._npeers, self.epoch
+
+    def wait(self) -> torch.Tensor:
+        """Receiver side of a pushed call: wait (on the stream, bounded) for every other rank's signal; returns [m, N]."""
+        abi = self.abi
+        abi.call("rwkvq_peer_wait", self.flags.data_ptr(), self.epoch, self.rank, self.world, self.status.data_ptr(), abi.stream_ptr())
+        return self.bufs[self.epoch & 1][:self.m]
+
     def check(self) -> None:
         """Raise if a pull gave up waiting for a peer (synchronizes)."""
         if int(self.status.item()) != 0:
@@ -150,24 +167,38 @@ class ColumnSplitLinear:
     `linear_fn(x, weight_info, out_dtype)` is the projection to run on the local slice (fp8_ops.linear_quantized for
     FP8 / INT8 / NVFP4 weight-info dicts, int4.int4_ops.linear_int4 for INT4 ones).  gather="nccl": an NCCL all-gather
     (rank-major) followed by one copy into the [M, N] layout; gather="peer": PeerGather above (GPU only, fp16 results;
-    `max_rows` sizes its buffers)."""
+    `max_rows` sizes its buffers); gather="push": the projection's GEMM stores its result tiles into every rank's buffer
+    itself and the receivers only wait for a flag (NVFP4 weights with more rows than the decode GEMV takes; other
+    calls fall back to "peer")."""
 
     def __init__(self, weight_info: dict, linear_fn, group=None, already_sliced: bool = False, gather: str = "nccl", max_rows: int = 4096):
+        if gather not in ("nccl", "peer", "push"):
+            raise ValueError(f"gather must be 'nccl', 'peer' or 'push', got {gather!r}")
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.local = weight_info if already_sliced else slice_weight_info(weight_info, self.rank, self.world)
         self.linear_fn = linear_fn
         self.n_local = self.local["weight" if "weight" in self.local else "packed"].shape[0]
-        self.peer = PeerGather(max_rows, self.n_local * self.world, group) if gather == "peer" else None
+        self.peer = PeerGather(max_rows, self.n_local * self.world, group) if gather in ("peer", "push") else None
+        # "push": the GEMM itself stores its tiles into every rank's buffer (one kernel computes and gathers); taken where
+        # the projection runs the kernel that can do it (NVFP4 weights on the tensor-core route), else the pull form
+        self.push = gather == "push" and self.local.get("qtype") == "nvfp4"
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
         if self.peer is not None:
             import rwkvq_abi as abi
             x2 = x.reshape(-1, x.shape[-1])
+            pushing = False
+            if self.push:
+                import nvfp4_ops
+                pushing = nvfp4_ops.can_push(x2.shape[0], x2.shape[1])
             with abi.output_into(self.peer.next_buffer(x2.shape[0])):
-                self.linear_fn(x2, self.local, torch.float16)             # writes this rank's columns in place
-            y = self.peer.gather().reshape(*x.shape[:-1], self.n_local * self.world)
+                if pushing:
+                    nvfp4_ops.linear_nvfp4(x2, self.local, torch.float16, push=self.peer.push_targets())
+                else:
+                    self.linear_fn(x2, self.local, torch.float16)         # writes this rank's columns in place
+            y = (self.peer.wait() if pushing else self.peer.gather()).reshape(*x.shape[:-1], self.n_local * self.world)
             return y if out_dtype in (None, torch.float16) else y.to(out_dtype)
         local = self.linear_fn(x, self.local, out_dtype)                  # [..., N/world]
         lead, nl = local.shape[:-1], local.shape[-1]

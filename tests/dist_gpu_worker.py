@@ -1,7 +1,8 @@
 """One NCCL rank of the multi-GPU column-split test: python dist_gpu_worker.py RANK WORLD PORT.
 
 The FFN key projection [16384, 4096] of RWKV-7 7.2B is split by output rows over the ranks; every rank computes its
-slice on its own GPU and the slices are gathered -- once through NCCL, once through the library's peer-memory gather.
+slice on its own GPU and the slices are gathered -- through NCCL, through the library's peer-memory pull, and (NVFP4,
+256 rows) by the GEMM itself storing its tiles into every rank's buffer.
 Checked per rank: both gathers equal the concatenation of the per-slice projections computed locally (bit for bit)
 and the unsplit projection within 1e-2 (INT8: bit for bit; FP8 decode splits K by the slice's tile count, so the
 order of its fp32 additions may differ from the unsplit run)."""
@@ -44,7 +45,8 @@ def main():
     verdict = []
     for scheme, info in infos.items():
         lin = fp8_ops.linear_quantized_fused if scheme != "nvfp4" else fp8_ops.linear_quantized
-        splits = {mode: D.ColumnSplitLinear(info, lin, gather=mode, max_rows=256) for mode in ("nccl", "peer")}
+        modes = ("nccl", "peer", "push") if scheme == "nvfp4" else ("nccl", "peer")     # push: the GEMM stores into the peers itself
+        splits = {mode: D.ColumnSplitLinear(info, lin, gather=mode, max_rows=256) for mode in modes}
         for m in (1, 256):
             x = (torch.randn(m, k, generator=g)).to(torch.bfloat16).to(dev)
             full = lin(x, info)
@@ -52,7 +54,7 @@ def main():
             for mode, split in splits.items():
                 y = split(x)
                 torch.cuda.synchronize()
-                if mode == "peer":
+                if mode != "nccl":
                     split.peer.check()
                 ok = y.shape == full.shape and torch.equal(y, parts) and rel_err(y, full) <= 1e-2
                 if scheme == "int8":
