@@ -412,6 +412,14 @@ int32_t rwkvq_tc_gemm_nvfp4_push(const uint8_t* a_codes, int64_t lda, const uint
                                  int64_t workspace_bytes, void* const* peer_out, void* const* peer_flag, int32_t npeers,
                                  uint32_t epoch, void* stream);
 
+/* The same fusion for the FP8 W8A8 GEMM (rwkvq_tc_gemm_fp8 + all-gather in one kernel).  Only the tiled GEMM form can
+ * carry it: rwkvq_tc_gemm_can_push(M, N, K) is 1 for the row counts it takes; the RELU2 flag is not accepted. */
+int32_t rwkvq_tc_gemm_can_push(int64_t M, int64_t N, int64_t K);
+int32_t rwkvq_tc_gemm_fp8_push(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
+                               int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                               int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes,
+                               void* const* peer_out, void* const* peer_flag, int32_t npeers, uint32_t epoch, void* stream);
+
 /* No counterpart in the reference.  rwkvq_tc_gemm_fp8 for callers that cannot supply device scratch -- a host runtime
  * that owns every byte of device memory and forbids allocation inside its serving loop, or code running where
  * cudaMalloc is not allowed.  The scratch is an 8 MiB array built into the library on each GPU; no allocation happens

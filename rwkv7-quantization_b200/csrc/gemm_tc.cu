@@ -56,6 +56,7 @@ struct TcArgs {
     unsigned long long* trace; // optional [grid][16] timestamps of role milestones (profiling aid), else null
     unsigned long long wait_ns; // wall-time limit of every mbarrier wait
     float* ffn_amax;            // RWKVQ_FLAG_RELU2 (GEMM mode, FP8): maximum of the relu^2 results, atomic max
+    TcPush push;                // GEMM mode: also store the result into the peers' buffers and signal them (n = 0: off)
     int64_t ldx, ldo, ldacc;
     int M, N, K, nmat;
     int NB;                    // rows of the B operand (UMMA N)
@@ -515,6 +516,60 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 const bool relu2 = KIND == KIND_F8 && (a.flags & RWKVQ_FLAG_RELU2) != 0;
                 const bool hmax_bf16 = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
                 float hmax = 0.f;
+                // 16 accumulator columns of this thread's token row -> 8 fp16 pairs (scales, optional bf16 hop, relu^2)
+                auto convert16 = [&](const uint32_t (&r)[16], int n0, uint32_t (&h)[8]) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float s0 = rowscale, s1 = rowscale;
+                        if (per_row) {
+                            s0 = actscale * a.ws[p.mat][min(n0 + 2 * j, a.N - 1)];
+                            s1 = actscale * a.ws[p.mat][min(n0 + 2 * j + 1, a.N - 1)];
+                        }
+                        float f0, f1;
+                        if constexpr (KIND == KIND_F8) {
+                            f0 = __uint_as_float(r[2 * j]) * s0;
+                            f1 = __uint_as_float(r[2 * j + 1]) * s1;
+                        } else {
+                            f0 = (float)(int32_t)r[2 * j] * s0;
+                            f1 = (float)(int32_t)r[2 * j + 1] * s1;
+                        }
+                        if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
+                        __half2 hh = __floats2half2_rn(f0, f1);
+                        if (relu2) {
+                            // the engine's relu_square on the fp16 result, fp32 arithmetic; its maximum (over the bf16-rounded
+                            // values where the consumer takes its amax there) goes to the projection that follows
+                            const float2 y = __half22float2(hh);
+                            const float v0 = fmaxf(y.x, 0.f), v1 = fmaxf(y.y, 0.f);
+                            hh = __floats2half2_rn(v0 * v0, v1 * v1);
+                            if (n0 + 2 * j < a.N) {
+                                const float2 hv = __half22float2(hh);
+                                hmax = fmaxf(hmax, hmax_bf16 ? bf16_round(hv.x) : hv.x);
+                                if (n0 + 2 * j + 1 < a.N) hmax = fmaxf(hmax, hmax_bf16 ? bf16_round(hv.y) : hv.y);
+                            }
+                        }
+                        h[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                    }
+                };
+                if (a.push.n > 0) {
+                    // column-split projection with the all-gather riding in this epilogue (TcPush in tc_host.cuh)
+                    uint8_t* stg = ring + (size_t)a.stages * stage_bytes + (size_t)(warp - 2) * kTcStgWarp;
+                    const bool vec8 = vec_ok && a.N % 8 == 0;
+                    for (int c0 = 0; c0 < a.NB; c0 += 64) {
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) {
+                            uint32_t r[16], h[8];
+                            tmem_ld16(taddr + c0 + cc * 16, r);
+                            tmem_ld_wait();
+                            convert16(r, p.qrow + c0 + cc * 16, h);
+                            uint4* d = reinterpret_cast<uint4*>(stg + lane * kTcStgRow + cc * 32);
+                            d[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                            d[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                        }
+                        __syncwarp();
+                        push_store_rows(a.push, stg, a.out[p.mat], a.ldo, p.prow + q * 32, p.qrow + c0, a.M, a.N, vec8, lane);
+                        __syncwarp();
+                    }
+                } else
                 for (int c0 = 0; c0 < a.NB; c0 += 16) {
                     uint32_t r[16];
                     tmem_ld16(taddr + c0, r);
@@ -522,37 +577,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                     const int n0 = p.qrow + c0;
                     if (m < a.M && n0 < a.N) {
                         uint32_t h[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            float s0 = rowscale, s1 = rowscale;
-                            if (per_row) {
-                                s0 = actscale * a.ws[p.mat][min(n0 + 2 * j, a.N - 1)];
-                                s1 = actscale * a.ws[p.mat][min(n0 + 2 * j + 1, a.N - 1)];
-                            }
-                            float f0, f1;
-                            if constexpr (KIND == KIND_F8) {
-                                f0 = __uint_as_float(r[2 * j]) * s0;
-                                f1 = __uint_as_float(r[2 * j + 1]) * s1;
-                            } else {
-                                f0 = (float)(int32_t)r[2 * j] * s0;
-                                f1 = (float)(int32_t)r[2 * j + 1] * s1;
-                            }
-                            if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) { f0 = bf16_round(f0); f1 = bf16_round(f1); }
-                            __half2 hh = __floats2half2_rn(f0, f1);
-                            if (relu2) {
-                                // the engine's relu_square on the fp16 result, fp32 arithmetic; its maximum (over the bf16-rounded
-                                // values where the consumer takes its amax there) goes to the projection that follows
-                                const float2 y = __half22float2(hh);
-                                const float v0 = fmaxf(y.x, 0.f), v1 = fmaxf(y.y, 0.f);
-                                hh = __floats2half2_rn(v0 * v0, v1 * v1);
-                                if (n0 + 2 * j < a.N) {
-                                    const float2 hv = __half22float2(hh);
-                                    hmax = fmaxf(hmax, hmax_bf16 ? bf16_round(hv.x) : hv.x);
-                                    if (n0 + 2 * j + 1 < a.N) hmax = fmaxf(hmax, hmax_bf16 ? bf16_round(hv.y) : hv.y);
-                                }
-                            }
-                            h[j] = *reinterpret_cast<const uint32_t*>(&hh);
-                        }
+                        convert16(r, n0, h);
                         __half* o = a.out[p.mat] + (int64_t)m * a.ldo + n0;
                         if (vec_ok && n0 + 16 <= a.N) {
                             reinterpret_cast<uint4*>(o)[0] = make_uint4(h[0], h[1], h[2], h[3]);
@@ -582,6 +607,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
             ++pc;
         }
         if (et == 0) tc_mark(a, 8);
+        if (!SWAP && a.push.n > 0) __threadfence_system();      // this thread's peer stores are ordered before its arrival below
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.done);
@@ -620,6 +646,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
         if (!mbar_wait(&s.done, 0, abort_flag, a.wait_ns)) tc_abort(s, a);
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, tmem_cols);
+        if (!SWAP && a.push.n > 0 && lane == 0) push_signal(a.push);
     }
 }
 
@@ -648,7 +675,7 @@ static int32_t launch_tc(const TcMaps& maps, const TcArgs& a, int grid, cudaStre
     const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudget, who);   // per device
     if (rc != RWKVQ_OK) return rc;
     const size_t cache = FUSED ? (size_t)a.nmat * a.M * ((size_t)a.kchunks * kChunk + (size_t)a.K * 2) : 0;
-    const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.NB * kChunk) + cache + 1024;
+    const size_t smem = (size_t)a.stages * (kABytes + (size_t)a.NB * kChunk) + cache + 1024 + (a.push.n > 0 ? kTcStgBytes : 0);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kTcThreads);
@@ -720,7 +747,11 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
     const bool swap = takes_swap_route(a.M, a.N, a.K, a.nmat, c.fused);
     if (c.fused) RWKVQ_REQUIRE(a.M <= 16, RWKVQ_E_SHAPE, "%s: the fused kernel takes M <= 16, got %d", who, a.M);
     a.kchunks = (a.K + kChunk - 1) / kChunk;
-    if (!c.fused && tcs_eligible(a.M, a.N, a.K, a.flags, a.nmat)) {
+    const bool pushing = a.push.n > 0 || a.push.counter != nullptr;
+    if (pushing)
+        RWKVQ_REQUIRE(!c.fused && a.nmat == 1 && !swap && !tcs_eligible(a.M, a.N, a.K, a.flags, 1) && !(a.flags & RWKVQ_FLAG_RELU2) && a.acc[0] == nullptr,
+                      RWKVQ_E_SHAPE, "%s: %d rows run a kernel that cannot carry the all-gather (see rwkvq_tc_gemm_can_push)", who, a.M);
+    if (!pushing && !c.fused && tcs_eligible(a.M, a.N, a.K, a.flags, a.nmat)) {
         a.status = nullptr;
         return run_tcs(a, c, st, who);
     }
@@ -744,7 +775,7 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
         a.status = a.counters + kWsCounterInts;
         a.scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(c.workspace) + kWsHeaderBytes);
     } else {
-        if (tc2_eligible(c.kind, a.M, a.N, a.K, a.nmat))      // many tokens: CTA pairs on 256 x 256 tiles (gemm_tc2.cu)
+        if (!pushing && tc2_eligible(c.kind, a.M, a.N, a.K, a.nmat))      // many tokens: CTA pairs on 256 x 256 tiles (gemm_tc2.cu)
             return run_tc2(c.kind, c.codes[0], c.lda, a.a_scale[0], a.amax_is_amax, c.w[0], c.ldw, a.ws[0], a.out[0], a.ldo, a.acc[0], a.ldacc,
                            a.M, a.N, a.K, a.div_mode, a.flags, a.ffn_amax,
                            c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : device_status_ptr(), st, who);
@@ -764,7 +795,7 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
                   who, a.nmat, a.M, a.K);
     const size_t budget = (swap && cache_bytes + 5 * stage_bytes + 1024 <= kTcSmemBudgetHalf && !std::getenv("RWKVQ_TC_ONE_PER_SM"))
                               ? kTcSmemBudgetHalf : kTcSmemBudget;
-    a.stages = (int)std::min<size_t>(kMaxStages, (budget - 1024 - cache_bytes) / stage_bytes);
+    a.stages = (int)std::min<size_t>(kMaxStages, (budget - 1024 - cache_bytes - (a.push.n > 0 ? kTcStgBytes : 0)) / stage_bytes);
     RWKVQ_REQUIRE(a.stages >= 2, RWKVQ_E_SHAPE, "%s: shared memory leaves fewer than two ring stages", who);
     for (int i = 0; i < a.nmat; ++i) {
         int32_t rc = make_map(&maps.w[i], c.w[i], a.N, a.K, c.ldw, swap ? kTileP : a.NB, who);
@@ -906,6 +937,31 @@ int32_t rwkvq_tc_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax
     TcCall c{};
     c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_fp8");
+}
+
+/* 1 if rwkvq_tc_gemm_fp8_push accepts this shape: the tiled GEMM form runs it (more rows than the few-token kernels
+ * take). */
+int32_t rwkvq_tc_gemm_can_push(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 16) return 0;
+    return !takes_swap_route(M, N, K, 1, false) && !tcs_eligible(M, N, K, 0, 1);
+}
+
+/* rwkvq_tc_gemm_fp8 fused with the all-gather of a column-split projection: see rwkvq_tc_gemm_nvfp4_push for
+ * peer_out / peer_flag / epoch.  Only shapes for which rwkvq_tc_gemm_can_push() is 1; no RELU2 flag. */
+int32_t rwkvq_tc_gemm_fp8_push(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax, const uint8_t* w,
+                               int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                               int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes, void* const* peer_out,
+                               void* const* peer_flag, int32_t npeers, uint32_t epoch, void* stream) {
+    const char* who = "tc_gemm_fp8_push";
+    RWKVQ_REQUIRE(M > 0 && N > 0, RWKVQ_E_SHAPE, "%s: empty result (the peers would wait for a signal that never comes)", who);
+    TcArgs a{};
+    const int32_t rc = make_push(&a.push, workspace, workspace_bytes, out_f16, peer_out, peer_flag, npeers, epoch, who);
+    if (rc != RWKVQ_OK) return rc;
+    a.a_scale[0] = amax; a.amax_is_amax = amax_is_amax; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    fill_common(a, 1, M, N, K, 0, ldo, div_mode, flags & ~RWKVQ_FLAG_RELU2);
+    TcCall c{};
+    c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, who);
 }
 
 int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,

@@ -44,24 +44,9 @@ struct NfMaps {
     CUtensorMap a, w;
 };
 
-// PUSH instantiation (column-split projection, result wanted on every rank): the epilogue stores each result vector
-// not only to this rank's buffer but, with plain peer stores over NVLink, to the same place in the buffer of every
-// other rank, so the all-gather travels while the tensor cores work on the next tiles.  When a CTA has stored its last
-// tile it fences at system scope and counts itself; the last CTA of the grid publishes `epoch` in this rank's slot of
-// every peer's flag array (system-scope release).  The receivers only wait for the flags (rwkvq_peer_wait).
-constexpr int kNfMaxPush = 7;
-constexpr uint32_t kNfStgRow = 144;                         // staging row: 64 fp16 + 16 bytes (rows start in different banks)
-constexpr uint32_t kNfStgWarp = 32 * kNfStgRow;             // 32 rows per epilogue warp
-struct NfPush {
-    __half* out[kNfMaxPush];       // this rank's column range in each peer's [M, ldo] buffer
-    uint32_t* flag[kNfMaxPush];    // this rank's slot in each peer's flag array
-    int* counter;                  // CTAs done, zero between launches
-    int n;                         // peers
-    uint32_t epoch;
-};
-
+// PUSH instantiation: the GEMM carries the all-gather of a column-split projection (TcPush in tc_host.cuh).
 struct NfArgs {
-    NfPush push;
+    TcPush push;
     const uint8_t* sfa;      // blocked activation scales
     const uint8_t* sfw;      // blocked weight scales
     const float* a_pts;
@@ -226,11 +211,8 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
             const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
             const int m = mt * kNfTileM + q * 32 + lane;
             if constexpr (PUSH) {
-                // Peer stores want long contiguous runs (NVLink moves 32-byte row fragments at a fraction of its rate:
-                // measured 2 x slower than the pull kernel at 4096 rows).  The warp turns its 32 rows x 64 columns
-                // around in shared memory and stores 128-byte row segments, four rows per instruction, to this rank's
-                // buffer and to every peer's.
-                uint8_t* stg = ring + (size_t)a.stages * kStage + (size_t)(warp - 2) * kNfStgWarp;
+                // the warp turns its 32 rows x 64 columns around in shared memory and stores whole 128-byte row segments
+                uint8_t* stg = ring + (size_t)a.stages * kStage + (size_t)(warp - 2) * kTcStgWarp;
                 const bool vec8 = vec_ok && a.N % 8 == 0;
                 for (int c0 = 0; c0 < BN; c0 += 64) {
 #pragma unroll
@@ -244,33 +226,12 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
                             const __half2 hh = __floats2half2_rn(__uint_as_float(r[2 * j]) * scale, __uint_as_float(r[2 * j + 1]) * scale);
                             h[j] = *reinterpret_cast<const uint32_t*>(&hh);
                         }
-                        uint4* d = reinterpret_cast<uint4*>(stg + lane * kNfStgRow + cc * 32);
+                        uint4* d = reinterpret_cast<uint4*>(stg + lane * kTcStgRow + cc * 32);
                         d[0] = make_uint4(h[0], h[1], h[2], h[3]);
                         d[1] = make_uint4(h[4], h[5], h[6], h[7]);
                     }
                     __syncwarp();
-#pragma unroll
-                    for (int it = 0; it < 8; ++it) {
-                        const int row = it * 4 + (lane >> 3), ch = lane & 7;
-                        const int mm = mt * kNfTileM + q * 32 + row, n0 = nt * BN + c0 + ch * 8;
-                        const uint4 v = *reinterpret_cast<const uint4*>(stg + row * kNfStgRow + ch * 16);
-                        if (mm < a.M && n0 < a.N) {
-                            const int64_t off = (int64_t)mm * a.ldo + n0;
-                            if (vec8) {
-                                *reinterpret_cast<uint4*>(a.out + off) = v;
-                                for (int p = 0; p < a.push.n; ++p) *reinterpret_cast<uint4*>(a.push.out[p] + off) = v;
-                            } else {
-                                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    if (n0 + j < a.N) {
-                                        const __half e = __ushort_as_half((unsigned short)((w4[j >> 1] >> ((j & 1) * 16)) & 0xffff));
-                                        a.out[off + j] = e;
-                                        for (int p = 0; p < a.push.n; ++p) a.push.out[p][off + j] = e;
-                                    }
-                            }
-                        }
-                    }
+                    push_store_rows(a.push, stg, a.out, a.ldo, mt * kNfTileM + q * 32, nt * BN + c0, a.M, a.N, vec8, lane);
                     __syncwarp();
                 }
             } else {
@@ -318,15 +279,7 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kNfTmemCols);
         if constexpr (PUSH) {
-            if (lane == 0) {
-                __threadfence_system();
-                if (atomicAdd(a.push.counter, 1) == (int)gridDim.x - 1) {       // every CTA's tiles are stored on every rank
-                    *a.push.counter = 0;
-                    __threadfence_system();
-                    for (int p = 0; p < a.push.n; ++p)
-                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.push.flag[p]), "r"(a.push.epoch) : "memory");
-                }
-            }
+            if (lane == 0) push_signal(a.push);
         }
     }
 }
@@ -349,7 +302,7 @@ static int32_t launch_nvfp4(const NfMaps& maps, NfArgs a, int grid, cudaStream_t
     const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kNfSmemBudget, who);   // per device
     if (rc != RWKVQ_OK) return rc;
     const size_t stage = kNfABytes + (size_t)BN * kNfRowBytes + kNfSfStage * (1 + BN / 128);
-    const size_t staging = PUSH ? 4 * (size_t)kNfStgWarp : 0;          // the pushing epilogue turns its tiles around in shared memory
+    const size_t staging = PUSH ? kTcStgBytes : 0;          // the pushing epilogue turns its tiles around in shared memory
     a.stages = (int)std::min<size_t>(kNfMaxStages, (kNfSmemBudget - 1024 - staging) / stage);
     const size_t smem = (size_t)a.stages * stage + staging + 1024;
     cudaLaunchConfig_t cfg{};
@@ -397,7 +350,7 @@ int32_t rwkvq_nvfp4_pack_scales(const uint8_t* block_scales, int64_t lds, int64_
 static int32_t run_tc_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts,
                             const uint8_t* w_codes, int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale,
                             void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes,
-                            void* stream, const NfPush* push, const char* who) {
+                            void* stream, const TcPush* push, const char* who) {
     RWKVQ_REQUIRE(M >= 0 && N >= 0 && K >= 0, RWKVQ_E_SHAPE, "%s: negative size", who);
     RWKVQ_REQUIRE(K % 256 == 0, RWKVQ_E_SHAPE, "%s: K=%lld must be a multiple of 256", who, (long long)K);
     RWKVQ_REQUIRE(ldo >= N, RWKVQ_E_SHAPE, "%s: ldo < N", who);
@@ -454,19 +407,10 @@ int32_t rwkvq_tc_gemm_nvfp4_push(const uint8_t* a_codes, int64_t lda, const uint
                                  void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes,
                                  void* const* peer_out, void* const* peer_flag, int32_t npeers, uint32_t epoch, void* stream) {
     const char* who = "tc_gemm_nvfp4_push";
-    RWKVQ_REQUIRE(npeers >= 0 && npeers <= kNfMaxPush && (npeers == 0 || (peer_out && peer_flag)), RWKVQ_E_BADARG, "%s: %d peers (0..%d)", who, npeers, kNfMaxPush);
-    RWKVQ_REQUIRE(workspace != nullptr && workspace_bytes >= kWsHeaderBytes, RWKVQ_E_WORKSPACE, "%s: needs the workspace", who);
     RWKVQ_REQUIRE(M > 0 && N > 0, RWKVQ_E_SHAPE, "%s: empty result (the peers would wait for a signal that never comes)", who);
-    NfPush push{};
-    push.n = npeers;
-    push.epoch = epoch;
-    push.counter = reinterpret_cast<int*>(workspace) + kWsCounterInts + 8;      // a spare word of the header, zero between launches
-    for (int i = 0; i < npeers; ++i) {
-        RWKVQ_REQUIRE(peer_out[i] && peer_flag[i] && ((uintptr_t)peer_flag[i] & 3) == 0, RWKVQ_E_BADARG, "%s: peer %d", who, i);
-        RWKVQ_REQUIRE(((uintptr_t)peer_out[i] & 15) == ((uintptr_t)out_f16 & 15), RWKVQ_E_ALIGN, "%s: peer buffer %d is aligned differently from out", who, i);
-        push.out[i] = reinterpret_cast<__half*>(peer_out[i]);
-        push.flag[i] = reinterpret_cast<uint32_t*>(peer_flag[i]);
-    }
+    TcPush push;
+    const int32_t rc = make_push(&push, workspace, workspace_bytes, out_f16, peer_out, peer_flag, npeers, epoch, who);
+    if (rc != RWKVQ_OK) return rc;
     return run_tc_nvfp4(a_codes, lda, a_scales_blocked, a_pts, w_codes, ldw, w_scales_blocked, w_tscale, out_f16, ldo, M, N, K, workspace,
                         workspace_bytes, stream, &push, who);
 }

@@ -42,6 +42,83 @@ inline int32_t make_map(CUtensorMap* m, const void* ptr, int64_t rows, int64_t r
     return RWKVQ_OK;
 }
 
+// A GEMM fused with the all-gather of a column-split projection (result wanted on every rank): its epilogue stores each
+// result vector not only to this rank's buffer but, with plain peer stores over NVLink, to the same place in the buffer
+// of every other rank, so the gather travels while the tensor cores work on the next tiles.  Peer stores want long
+// contiguous runs (32-byte row fragments were measured 2 x slower than a pull kernel), so an epilogue warp turns its
+// 32 rows x 64 columns around in a shared-memory staging area and stores 128-byte row segments, four rows per
+// instruction.  A CTA that has stored its last tile fences at system scope and counts itself; the last CTA of the grid
+// publishes `epoch` in this rank's slot of every peer's flag array (system-scope release).  The receivers only wait for
+// the flags (rwkvq_peer_wait).  No TMA touches peer memory.
+constexpr int kTcMaxPush = 7;
+constexpr uint32_t kTcStgRow = 144;                         // staging row: 64 fp16 + 16 bytes (rows start in different banks)
+constexpr uint32_t kTcStgWarp = 32 * kTcStgRow;             // 32 rows per epilogue warp
+constexpr size_t kTcStgBytes = 4 * (size_t)kTcStgWarp;      // four epilogue warps
+struct TcPush {
+    __half* out[kTcMaxPush];       // this rank's column range in each peer's [M, ldo] buffer
+    uint32_t* flag[kTcMaxPush];    // this rank's slot in each peer's flag array
+    int* counter;                  // CTAs done, zero between launches (a spare word of the workspace header)
+    int n;                         // peers (0: no push)
+    uint32_t epoch;
+};
+constexpr int64_t kWsPushCounter = kWsCounterInts + 8;
+
+// fills `push` from the caller's arrays; the peers' buffers must be aligned like `out`
+inline int32_t make_push(TcPush* push, void* workspace, int64_t workspace_bytes, const void* out, void* const* peer_out, void* const* peer_flag,
+                         int32_t npeers, uint32_t epoch, const char* who) {
+    RWKVQ_REQUIRE(npeers >= 0 && npeers <= kTcMaxPush && (npeers == 0 || (peer_out && peer_flag)), RWKVQ_E_BADARG, "%s: %d peers (0..%d)", who, npeers, kTcMaxPush);
+    RWKVQ_REQUIRE(workspace != nullptr && workspace_bytes >= kWsHeaderBytes, RWKVQ_E_WORKSPACE, "%s: needs the workspace", who);
+    *push = TcPush{};
+    push->n = npeers;
+    push->epoch = epoch;
+    push->counter = reinterpret_cast<int*>(workspace) + kWsPushCounter;
+    for (int i = 0; i < npeers; ++i) {
+        RWKVQ_REQUIRE(peer_out[i] && peer_flag[i] && ((uintptr_t)peer_flag[i] & 3) == 0, RWKVQ_E_BADARG, "%s: peer %d", who, i);
+        RWKVQ_REQUIRE(((uintptr_t)peer_out[i] & 15) == ((uintptr_t)out & 15), RWKVQ_E_ALIGN, "%s: peer buffer %d is aligned differently from out", who, i);
+        push->out[i] = reinterpret_cast<__half*>(peer_out[i]);
+        push->flag[i] = reinterpret_cast<uint32_t*>(peer_flag[i]);
+    }
+    return RWKVQ_OK;
+}
+
+#ifdef __CUDACC__
+// one thread per CTA, after every epilogue thread of the CTA has fenced and arrived
+__device__ __forceinline__ void push_signal(const TcPush& p) {
+    __threadfence_system();
+    if (atomicAdd(p.counter, 1) == (int)gridDim.x - 1) {            // every CTA's tiles are stored on every rank
+        *p.counter = 0;
+        __threadfence_system();
+        for (int i = 0; i < p.n; ++i) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[i]), "r"(p.epoch) : "memory");
+    }
+}
+// the coalesced half of the staged epilogue: 32 rows x 64 columns from `stg` to this rank's buffer and the peers'
+__device__ __forceinline__ void push_store_rows(const TcPush& p, const uint8_t* stg, __half* out, int64_t ldo, int row0, int col0, int M, int N,
+                                                bool vec8, int lane) {
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int row = it * 4 + (lane >> 3), ch = lane & 7;
+        const int mm = row0 + row, n0 = col0 + ch * 8;
+        const uint4 v = *reinterpret_cast<const uint4*>(stg + row * kTcStgRow + ch * 16);
+        if (mm < M && n0 < N) {
+            const int64_t off = (int64_t)mm * ldo + n0;
+            if (vec8) {
+                *reinterpret_cast<uint4*>(out + off) = v;
+                for (int i = 0; i < p.n; ++i) *reinterpret_cast<uint4*>(p.out[i] + off) = v;
+            } else {
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (n0 + j < N) {
+                        const __half e = __ushort_as_half((unsigned short)((w4[j >> 1] >> ((j & 1) * 16)) & 0xffff));
+                        out[off + j] = e;
+                        for (int i = 0; i < p.n; ++i) p.out[i][off + j] = e;
+                    }
+            }
+        }
+    }
+}
+#endif
+
 // W8A8 GEMM on CTA pairs (gemm_tc2.cu): eligibility (many tokens, enough 256 x 256 tiles to fill the pairs, not switched
 // off with RWKVQ_TC2=0) and the launch.  kind: tc::KIND_F8 / tc::KIND_I8.
 bool tc2_eligible(int kind, int64_t M, int64_t N, int64_t K, int nmat);

@@ -31,9 +31,11 @@ def load_fp8_weight(z, key, dev):
     }
 
 
-def linear_fp8(x, weight_info, out_dtype=torch.float16):
+def linear_fp8(x, weight_info, out_dtype=torch.float16, push=None):
     """The large-M FP8 route (fp8_ops.py:58-86): fp16 activations are taken as bf16, quantized per call with torch's
-    scale arithmetic, multiplied on the tensor cores, and the result is rounded to bf16 before `out_dtype`."""
+    scale arithmetic, multiplied on the tensor cores, and the result is rounded to bf16 before `out_dtype`.
+    push = (peer_out, peer_flag, npeers, epoch): the GEMM also stores its result into the other ranks' buffers and signals
+    them (column-split projection, rwkvq_dist.PeerGather.push_targets; only row counts with fused_fp8_gemm.can_push)."""
     import fused_fp8_gemm as f
     w, w_ts = weight_info["weight"], weight_info["tensor_scale"]
     x2 = f._rows16(x)
@@ -48,7 +50,15 @@ def linear_fp8(x, weight_info, out_dtype=torch.float16):
     # inv = 448/amax and scale = amax/448 the way torch evaluates them on a GPU in prep_x_fp8 (DIV_TORCH)
     f._actq_fp8(x2, codes, amax, scale, abi.DIV_TORCH, abi.FLAG_AMAX_AFTER_BF16 | abi.FLAG_QUANT_FROM_BF16, st)
     gflags = abi.FLAG_OUT_VIA_BF16 | f._wscale_flag(w_ts, n)
-    if f.ROUTE != "mma":
+    if push is not None:
+        if not f.can_push(m, n, k):
+            raise RuntimeError("rwkvq: the pushed all-gather rides in the tiled tensor-core GEMM only (see can_push)")
+        ws = abi.workspace(min(m, 128), n, k, 1, dev)
+        abi.call("rwkvq_tc_gemm_fp8_push", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DIV_IEEE, gflags, ws.data_ptr(), ws.numel(),
+                 push[0], push[1], push[2], push[3], st)
+        abi.after_call(ws)
+    elif f.ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, dev)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, scale.data_ptr(), 0, f._u8(w).data_ptr(), w.stride(0),
                  w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DIV_IEEE, gflags, ws.data_ptr(), ws.numel(), st)
@@ -79,7 +89,7 @@ def linear_quantized(x, weight_info, out_dtype=torch.float16):
     return linear_fp8(x, weight_info, out_dtype)
 
 
-def linear_quantized_fused(x, weight_info, out_dtype=torch.float16):
+def linear_quantized_fused(x, weight_info, out_dtype=torch.float16, push=None):
     """Forward to the dispatcher of fused_fp8_gemm (fp8_ops.py:109-115)."""
     from fused_fp8_gemm import linear_quantized_fused as dispatch
-    return dispatch(x, weight_info, out_dtype)
+    return dispatch(x, weight_info, out_dtype, push=push) if push is not None else dispatch(x, weight_info, out_dtype)

@@ -225,8 +225,14 @@ def _actq_fp8(x2, codes, amax, scale, div, flags, st):
                  abi.ptr(scale), div, flags, st)
 
 
-def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
-    """Activation quantization kernels, then the GEMM on codes (any M)."""
+def can_push(m: int, n: int, k: int) -> bool:
+    """True if an FP8 projection of m rows runs the GEMM that can carry the all-gather of a column-split projection."""
+    return ROUTE != "mma" and _ACTQ_FUSED and m > 0 and k % 16 == 0 and bool(abi.lib().rwkvq_tc_gemm_can_push(m, n, k))
+
+
+def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0, push=None):
+    """Activation quantization kernels, then the GEMM on codes (any M).  push = (peer_out, peer_flag, npeers, epoch): the
+    GEMM also stores its result into the peers' buffers and signals them (rwkvq_dist.PeerGather.push_targets)."""
     m, k = x2.shape
     n = w.shape[0]
     codes = torch.empty((m, k), dtype=torch.uint8, device=x2.device)
@@ -235,7 +241,13 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0):
     st = abi.stream_ptr()
     gemm_flags |= _wscale_flag(w_ts, n)
     _actq_fp8(x2, codes, amax, None, abi.DEFAULT_DIV, act_flags, st)
-    if ROUTE != "mma":
+    if push is not None:
+        ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
+        abi.call("rwkvq_tc_gemm_fp8_push", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(),
+                 push[0], push[1], push[2], push[3], st)
+        abi.after_call(ws)
+    elif ROUTE != "mma":
         ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
         abi.call("rwkvq_tc_gemm_fp8", codes.data_ptr(), k, amax.data_ptr(), 1, w.data_ptr(), w.stride(0),
                  w_ts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.DEFAULT_DIV, gemm_flags, ws.data_ptr(), ws.numel(), st)
@@ -316,11 +328,17 @@ def linear_fp8_m1_fused(x, weight_info, out_dtype=torch.float16):
     return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
 
 
-def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float16):
-    """FP8 W8A8 projection with on-the-fly activation quantization (fused_fp8_gemm.py:1020-1077)."""
+def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float16, push=None):
+    """FP8 W8A8 projection with on-the-fly activation quantization (fused_fp8_gemm.py:1020-1077).  push: see
+    _fp8_codes_gemm (only for row counts with can_push())."""
     w, w_ts = _unpack(weight_info_or_w, res_scale)
     k = x.shape[-1]
     m = x.numel() // k if k else 0
+    if push is not None:
+        if not can_push(m, w.shape[0], k):
+            raise RuntimeError("rwkvq: the pushed all-gather rides in the tiled tensor-core GEMM only (see can_push)")
+        out = _fp8_codes_gemm(_rows16(x), _u8(w), w_ts, abi.FLAG_QUANT_FROM_BF16, push=push)
+        return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
     if m == 1:
         return linear_fp8_m1_fused(x, {"weight": w, "tensor_scale": w_ts}, out_dtype)
     x2 = _rows16(x)
@@ -572,20 +590,23 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
 
 
 # --------------------------------------------------------------------------- dispatcher
-def linear_quantized_fused(x, weight_info, out_dtype=torch.float16):
+def linear_quantized_fused(x, weight_info, out_dtype=torch.float16, push=None):
     """Engine-facing dispatcher (fused_fp8_gemm.py:1080-1098): qtype "int8" -> INT8 path; otherwise FP8, with the
-    fused semantics up to FUSED_M_MAX rows and the linear_fp8 semantics (bf16 first, result through bf16) above."""
+    fused semantics up to FUSED_M_MAX rows and the linear_fp8 semantics (bf16 first, result through bf16) above.
+    push (FP8 and NVFP4 only): the GEMM also delivers its result to the other ranks of a column-split projection."""
     qtype = weight_info.get("qtype", "fp8")
     m = x.numel() // x.size(-1)
+    if push is not None and qtype not in ("fp8", "nvfp4"):
+        raise RuntimeError(f"rwkvq: no pushing GEMM for qtype {qtype!r}")
     if qtype == "int8":
         return linear_int8_fused(x, weight_info, out_dtype)
     if qtype == "nvfp4":
         from nvfp4_ops import linear_nvfp4
-        return linear_nvfp4(x, weight_info, out_dtype)
+        return linear_nvfp4(x, weight_info, out_dtype, push=push)
     if qtype.startswith("int4_"):          # weight-info dicts of int4/int4_ops.load_int4_weight
         from int4.int4_ops import linear_int4
         return linear_int4(x, weight_info, out_dtype)
     if m <= FUSED_M_MAX:
-        return linear_fp8_fused(x, weight_info, out_dtype=out_dtype)
+        return linear_fp8_fused(x, weight_info, out_dtype=out_dtype, push=push)
     from fp8_ops import linear_fp8
-    return linear_fp8(x, weight_info, out_dtype)
+    return linear_fp8(x, weight_info, out_dtype, push=push)
