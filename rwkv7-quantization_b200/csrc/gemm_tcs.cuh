@@ -1,5 +1,6 @@
-// W8A8 GEMM for a FEW tokens (decode batches, up to 64 rows) on pre-quantized codes: the weights are the 128-row
-// operand of tcgen05.mma, the tokens the narrow one, and K is split across a THREAD-BLOCK CLUSTER.
+// W8A8 GEMM for FEW tokens (decode batches, short prefill chunks: up to 256 rows) on pre-quantized codes: the weights
+// are the 128-row operand of tcgen05.mma, the tokens the other one (16 ... 128 per tile), and K is split across a
+// THREAD-BLOCK CLUSTER.
 //
 // Why.  With few tokens the projection is a pure weight stream, and a matrix has far fewer 128-row tiles than the GPU
 // has SMs (N = 4096: 32), so every tile's K range has to be shared by several CTAs.  Sharing it through global memory
@@ -12,7 +13,8 @@
 // (run-to-run identical) and writes fp16.  No scratch, no counters, nothing to clear, nothing between launches.
 //
 // Roles per CTA: warp 0 = TMA producer (one lane), warp 1 = tensor-memory owner and MMA issuer (one lane),
-// warps 2-5 = epilogue / exchange.  Two CTAs fit an SM (about 105 KB of shared memory each).  The first pass over the
+// warps 2-5 = epilogue / exchange.  Up to 64 tokens two CTAs fit an SM (about 105 KB of shared memory each); token
+// tiles of 128 take an SM each.  The first pass over the
 // ring loads weights BEFORE the dependency wait of programmatic dependent launch: they do not depend on the
 // activation quantizer that runs in front.  Every wait is bounded; all CTAs of a cluster meet at a cluster barrier
 // before any of them exits, so no CTA's shared memory is written after it has gone.
@@ -24,7 +26,7 @@ namespace rwkvq {
 
 constexpr int kTcsThreads = 192;
 constexpr int kTcsMaxStages = 8;
-constexpr int kTcsMaxM = 64;
+constexpr int kTcsMaxM = 256;              // two token tiles of 128
 
 struct TcsShared {
     uint64_t full[kTcsMaxStages], empty[kTcsMaxStages], tfull[3], rx, rxfree;
@@ -85,7 +87,8 @@ __device__ __forceinline__ void tcs_abort(TcsShared& s, const TcArgs& a) {
     if (a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
 }
 
-// a.qtiles carries the cluster size C, a.ptiles the 128-row tiles of one matrix; grid = ptiles * C.  With three
+// a.qtiles carries the cluster size C, a.ptiles the 128-row tiles of one matrix, a.max_slots the token tiles (of a.NB
+// tokens); grid = token tiles * ptiles * C.  With three
 // matrices (r, k, v) a CTA streams its K range of the same row tile of each matrix in turn into three accumulators;
 // the exchange of one matrix overlaps the stream of the next.  The K split is the same as for a single matrix, so the
 // three-in-one launch and three single launches give the same bits.
@@ -96,15 +99,17 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
     __shared__ TcsShared s;
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t stage_bytes = kABytes + (uint32_t)a.NB * kChunk;
-    T* rxbuf = reinterpret_cast<T*>(ring + (size_t)a.stages * stage_bytes);        // [C][M][R]: partial sums per source CTA, token, row
+    T* rxbuf = reinterpret_cast<T*>(ring + (size_t)a.stages * stage_bytes);        // [C][Mt][R]: partial sums per source CTA, token, row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int C = a.qtiles, R = kTileP / C;
     const int rank = (int)tcs_ctarank();
-    const int prow = ((int)blockIdx.x / C) * kTileP;
+    const int cid = (int)blockIdx.x / C;                     // cluster = (token tile, row tile), row tiles fastest
+    const int prow = (cid % a.ptiles) * kTileP;
+    const int m0 = (cid / a.ptiles) * a.NB, Mt = min(a.NB, a.M - m0);       // this cluster's tokens
     const int kc0 = a.kchunks * rank / C, kc1 = a.kchunks * (rank + 1) / C;
     const int nk = kc1 - kc0, total = a.nmat * nk;          // ring units of this CTA: matrix-major
     const uint32_t need_cols = (uint32_t)(a.nmat * a.acc_stride);
-    const uint32_t tmem_cols = need_cols <= 32 ? 32u : (need_cols <= 64 ? 64u : (need_cols <= 128 ? 128u : 256u));
+    const uint32_t tmem_cols = need_cols <= 32 ? 32u : (need_cols <= 64 ? 64u : (need_cols <= 128 ? 128u : (need_cols <= 256 ? 256u : 512u)));
     const volatile int* abort_flag = &s.abort_flag;
 
     griddep_launch_dependents();
@@ -154,7 +159,7 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
                     mbar_expect_tx(&s.full[st], stage_bytes);
                     tma_load_2d(dst, &maps.w[mat], kc * kChunk, prow, &s.full[st]);
                 }
-                tma_load_2d(dst + kABytes, &maps.a[mat], kc * kChunk, 0, &s.full[st]);
+                tma_load_2d(dst + kABytes, &maps.a[mat], kc * kChunk, m0, &s.full[st]);
             }
             tc_mark(a, 10);
         }
@@ -192,7 +197,7 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
         const int l = q * 32 + lane;                    // row of the tile held by this thread
         const uint32_t owner = (uint32_t)(l / R);
         const int lr = l - (int)owner * R;
-        const uint32_t remote = tcs_mapa(smem_u32(rxbuf), owner) + (uint32_t)(((size_t)rank * a.M * R + lr) * 4);
+        const uint32_t remote = tcs_mapa(smem_u32(rxbuf), owner) + (uint32_t)(((size_t)rank * Mt * R + lr) * 4);
         const uint32_t remote_rx = tcs_mapa(smem_u32(&s.rx), owner);
         // what the final pass needs from global memory is fetched now, not behind the exchange: a thread of the final
         // pass keeps ONE weight row (R divides 128) and walks the tokens
@@ -219,7 +224,7 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
             // this CTA's partial sums of row l go to slot `rank` of the owner's buffer (zeros after a timeout, so that
             // the peers' waits end)
             const uint32_t taddr = tmem_base + (uint32_t)(mat * a.acc_stride) + ((uint32_t)(q * 32) << 16);
-            for (int c0 = 0; c0 < a.M; c0 += 16) {
+            for (int c0 = 0; c0 < Mt; c0 += 16) {
                 uint32_t r[16];
                 if (have) {
                     tmem_ld16(taddr + c0, r);
@@ -230,7 +235,7 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    if (c0 + j < a.M) tcs_st_remote(remote + (uint32_t)((c0 + j) * R * 4), r[j]);
+                    if (c0 + j < Mt) tcs_st_remote(remote + (uint32_t)((c0 + j) * R * 4), r[j]);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -242,18 +247,18 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
             if (!got) tcs_abort(s, a);
             if (et == 0 && mat == a.nmat - 1) tc_mark(a, 9);
             if (got && !*abort_flag && my_row < a.N) {
-                for (int m = my_m0; m < a.M; m += m_step) {
+                for (int m = my_m0; m < Mt; m += m_step) {
                     T sum = 0;
-                    for (int src = 0; src < C; ++src) sum += rxbuf[((size_t)src * a.M + m) * R + my_c];
+                    for (int src = 0; src < C; ++src) sum += rxbuf[((size_t)src * Mt + m) * R + my_c];
                     float f;
                     if constexpr (KIND == KIND_F8) {
                         f = sum * (act_scale[mat] * wrow[mat]);
                     } else {
-                        if (a.acc[mat]) a.acc[mat][(int64_t)m * a.ldacc + my_row] = sum;
-                        f = (float)sum * (__ldg(a.a_scale[mat] + m) * wrow[mat]);
+                        if (a.acc[mat]) a.acc[mat][(int64_t)(m0 + m) * a.ldacc + my_row] = sum;
+                        f = (float)sum * (__ldg(a.a_scale[mat] + m0 + m) * wrow[mat]);
                     }
                     if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
-                    a.out[mat][(int64_t)m * a.ldo + my_row] = __float2half_rn(f);
+                    a.out[mat][(int64_t)(m0 + m) * a.ldo + my_row] = __float2half_rn(f);
                 }
             }
             if (mat + 1 < a.nmat) {                    // this CTA's buffer is empty: tell every sender of the cluster
@@ -274,14 +279,18 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-// Cluster size for one matrix: as many CTAs per 128-row tile as keep the grid within two CTAs per SM, at most 8 and at
-// most one per 128-byte step of K.  It depends on the matrix alone (not on how many matrices a launch carries), so a
-// fused r/k/v launch and three single launches split K alike and give the same bits.
-static int tcs_cluster_size(int64_t N, int64_t K) {
+// Cluster size: as many CTAs per (128-row tile, token tile) as keep the whole grid resident at once -- two CTAs per SM
+// up to 64 tokens, one per SM with token tiles of 128 -- at most 8 and at most one per two 128-byte steps of K.  It
+// depends on the shape alone (not on how many matrices a launch carries), so a fused r/k/v launch and three single
+// launches split K alike and give the same bits.
+static int tcs_token_tile(int64_t M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+static int tcs_cluster_size(int64_t M, int64_t N, int64_t K) {
     const int64_t ptiles = (N + kTileP - 1) / kTileP, kchunks = (K + kChunk - 1) / kChunk;
+    const int nb = tcs_token_tile(M);
+    const int64_t units = ptiles * ((M + nb - 1) / nb), room = (int64_t)sm_count() * (nb <= 64 ? 2 : 1);
     static const int cmax = std::getenv("RWKVQ_TCS_CMAX") ? std::atoi(std::getenv("RWKVQ_TCS_CMAX")) : 8;
     int c = 1;
-    while (c < cmax && ptiles * (c * 2) <= 2 * (int64_t)sm_count() && kchunks >= c * 2) c <<= 1;
+    while (c < cmax && units * (c * 2) <= room && kchunks >= c * 2) c <<= 1;
     return c;
 }
 
@@ -292,23 +301,26 @@ static bool tcs_eligible(int64_t M, int64_t N, int64_t K, uint32_t flags, int nm
     static const int on = std::getenv("RWKVQ_TCS") ? std::atoi(std::getenv("RWKVQ_TCS")) : 1;
     static const int64_t max_m = std::getenv("RWKVQ_TCS_MAX_M") ? std::atoll(std::getenv("RWKVQ_TCS_MAX_M")) : kTcsMaxM;
     if (!on || M < 1 || M > std::min<int64_t>(max_m, kTcsMaxM) || (flags & RWKVQ_FLAG_RELU2)) return false;
-    const int64_t ptiles = (N + kTileP - 1) / kTileP;
-    const int c = tcs_cluster_size(N, K);
-    return K >= 1024 && c >= 4 && ptiles * c <= 2 * (int64_t)sm_count();
+    const int c = tcs_cluster_size(M, N, K);
+    // token tiles of 128 (65 ... 256 rows): measured faster than the tiled GEMM form only against a long K (FFN value,
+    // K = 16384: 57 -> 29 us at 96 rows, 61 -> 52 us at 256); at K = 4096 the GEMM form wins from about 160 rows on and
+    // the three-matrix launch everywhere
+    return K >= 1024 && (M <= 64 ? c >= 4 : (c >= 2 && K >= 8192));
 }
 
 static int32_t run_tcs(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
-    const int C = tcs_cluster_size(a.N, a.K);
-    a.NB = a.M <= 16 ? 16 : (a.M <= 32 ? 32 : 64);
+    const int C = tcs_cluster_size(a.M, a.N, a.K);
+    a.NB = tcs_token_tile(a.M);
     a.ptiles = (a.N + kTileP - 1) / kTileP;
     a.qtiles = C;
-    a.max_slots = 1;
+    a.max_slots = (a.M + a.NB - 1) / a.NB;                       // token tiles
     a.acc_stride = std::max(a.NB, 32);
     if (a.status == nullptr) a.status = c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : device_status_ptr();
     const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk;
-    const size_t rx_bytes = (size_t)a.M * kTileP * 4;       // [C][M][128 / C] partial sums
+    const size_t rx_bytes = (size_t)std::min(a.M, a.NB) * kTileP * 4;       // [C][tokens of a tile][128 / C] partial sums
+    const size_t budget = a.NB <= 64 ? kTcSmemBudgetHalf : kTcSmemBudget;
     const int per_cta = (a.kchunks + C - 1) / C;
-    a.stages = (int)std::min<size_t>(std::min<int>(kTcsMaxStages, per_cta * a.nmat), (kTcSmemBudgetHalf - 1024 - rx_bytes) / stage_bytes);
+    a.stages = (int)std::min<size_t>(std::min<int>(kTcsMaxStages, per_cta * a.nmat), (budget - 1024 - rx_bytes) / stage_bytes);
     RWKVQ_REQUIRE(a.stages >= 2 || per_cta * a.nmat == 1, RWKVQ_E_SHAPE, "%s: shared memory leaves fewer than two ring stages", who);
     a.stages = std::max(a.stages, 1);
     TcMaps maps;
@@ -319,10 +331,10 @@ static int32_t run_tcs(TcArgs a, const TcCall& c, cudaStream_t st, const char* w
         if (rc) return rc;
     }
     auto kern = c.kind == KIND_F8 ? gemm_tcs_kernel<KIND_F8> : gemm_tcs_kernel<KIND_I8>;
-    const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudgetHalf, who);
+    const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudget, who);
     if (rc) return rc;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)(a.ptiles * C));
+    cfg.gridDim = dim3((unsigned)(a.max_slots * a.ptiles * C));
     cfg.blockDim = dim3(kTcsThreads);
     cfg.dynamicSmemBytes = (size_t)a.stages * stage_bytes + rx_bytes + 1024;
     cfg.stream = st;

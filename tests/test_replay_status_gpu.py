@@ -387,9 +387,12 @@ def test_cta_pair_gemm_many_tokens(mods, scheme, m, n, k):
                                    (48, 1000, 1040),      # ragged N and K: zero-filled tile edges; 9 K steps: cluster of 4
                                    (40, 5000, 2048),      # 40 row tiles: cluster of 4
                                    (12, 520, 16384),      # long K that the decode GEMV's code tile cannot hold
-                                   (64, 4096, 16384)])    # FFN value
+                                   (64, 4096, 16384),     # FFN value
+                                   (128, 4096, 8192),     # one token tile of 128: cluster of 4, one CTA per SM
+                                   (200, 1000, 8320),     # two token tiles (128 + 72), ragged N, 65 K steps
+                                   (256, 4096, 16384)])   # FFN value, short prefill chunk: cluster of 2
 def test_cluster_splitk_few_tokens(mods, scheme, m, n, k):
-    """Up to 64 rows against a matrix with few 128-row tiles: K is split across a thread-block cluster and the partial
+    """Up to 256 rows against a matrix with few 128-row tiles: K is split across a thread-block cluster and the partial
     sums travel through distributed shared memory.  INT8 accumulators and outputs exact; FP8 within 1e-2 of the oracle
     and of the mma.sync kernel on the same codes; two calls give the same bits."""
     abi, f, _ = mods
