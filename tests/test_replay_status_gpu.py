@@ -148,6 +148,36 @@ def test_bounded_wait_runs_out_and_reports(mods, mode):
     assert rel_err(f.linear_fp8_fused(x.cuda(), dev(info)), O.linear_fp8_fused(x, info, lib_div(abi))) <= 1e-2
 
 
+def test_peer_wait_gives_up_when_a_rank_never_signals(mods):
+    """Receiver side of a pushed / pulled all-gather with a rank that never delivers: the flag wait runs out after the
+    wait limit, the status word reads RWKVQ_E_TIMEOUT, the kernel returns and the context stays usable.  (The failure
+    is made on the host: a flag array that nothing writes; no GPU fault is involved.)"""
+    abi, f, _ = mods
+    L = abi.lib()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    flags[0] = 7                                                          # this rank's own slot is never looked at
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    L.rwkvq_set_wait_limit_us(200_000)
+    try:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        abi.call("rwkvq_peer_wait", flags.data_ptr(), 7, 0, 4, status.data_ptr(), abi.stream_ptr())     # ranks 1-3 stay silent
+        t1.record()
+        torch.cuda.synchronize()
+        assert status.item() == abi.E_TIMEOUT
+        assert 150.0 <= t0.elapsed_time(t1) < 5000.0, t0.elapsed_time(t1)
+        status.zero_()
+        flags[1:4] = 7                                                    # everybody has signalled epoch 7
+        abi.call("rwkvq_peer_wait", flags.data_ptr(), 7, 0, 4, status.data_ptr(), abi.stream_ptr())
+        torch.cuda.synchronize()
+        assert status.item() == 0
+    finally:
+        L.rwkvq_set_wait_limit_us(0)
+    info = fp8_weight(5, 128, 512)
+    x = gen(6, (3, 512), 1.0, torch.bfloat16)
+    assert rel_err(f.linear_fp8_fused(x.cuda(), dev(info)), O.linear_fp8_fused(x, info, lib_div(abi))) <= 1e-2
+
+
 def test_device_status_word_reads_and_clears(mods):
     abi, _, _ = mods
     assert abi.device_status() == 0
