@@ -441,7 +441,10 @@ def run_ours(args, rank, world, local_rank):
     colsplit = None
     if dist_on and not args.no_colsplit:
         with torch.cuda.stream(stream):
-            colsplit = colsplit_leg(world, dev, dist_on)
+            try:
+                colsplit = colsplit_leg(world, dev, dist_on)
+            except Exception as e:          # the step's own numbers above stand; say what happened to this leg
+                colsplit = {"error": f"{type(e).__name__}: {e}"[:400]}
     nbytes = int(step_bytes(args.tokens) * scale_l)
     per_step = ms / args.steps
     gbs = nbytes * world / (per_step * 1e-3) / 1e9

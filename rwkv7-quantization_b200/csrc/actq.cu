@@ -266,7 +266,9 @@ struct QInt8Args {
     float* scales[3];
 };
 
-template <int DT, bool VEC>
+// KEEP: decode-sized grids (latency counts, occupancy does not): a separate instantiation, so that the many-row form
+// keeps its small register footprint.
+template <int DT, bool VEC, bool KEEP = false>
 __global__ void __launch_bounds__(kThreads) quant_int8_kernel(const QInt8Args qa, int64_t K, int64_t ldx, int64_t ldc, int div_mode) {
     __shared__ float sh[kThreads / 32];
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a projection behind this launch may prefetch its weights
@@ -276,6 +278,45 @@ __global__ void __launch_bounds__(kThreads) quant_int8_kernel(const QInt8Args qa
     int8_t* crow = qa.codes[blockIdx.y] + row * ldc;
     float* scales = qa.scales[blockIdx.y];
     float m = 0.f;
+    if (VEC && KEEP && K <= (int64_t)kThreads * 8 * 8) {
+        // rows of up to 16384 elements: a thread's (at most 8) vectors stay in registers between the abs-max and the
+        // codes -- one read of the row, all loads in flight at once
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t k = ((int64_t)threadIdx.x + j * kThreads) * 8;
+            v[j] = make_uint4(0, 0, 0, 0);
+            if (k < K) v[j] = *reinterpret_cast<const uint4*>(xrow + k * 2);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
+        }
+        m = fmaxf(block_max(m, sh), 1e-12f);
+        const float s = div_mode_f32(127.f, m, div_mode);
+        if (threadIdx.x == 0) scales[row] = div_mode_f32(m, 127.f, div_mode);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t k = ((int64_t)threadIdx.x + j * kThreads) * 8;
+            if (k >= K) continue;
+            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            uint32_t c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                const uint32_t lo = (uint32_t)(__float2int_rz(fminf(fmaxf(f.x * s, -128.f), 127.f))) & 0xffu;
+                const uint32_t hi = (uint32_t)(__float2int_rz(fminf(fmaxf(f.y * s, -128.f), 127.f))) & 0xffu;
+                c[q] = lo | (hi << 8);
+            }
+            *reinterpret_cast<uint2*>(crow + k) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+        }
+        return;
+    }
     if (VEC) {
         for (int64_t k = (int64_t)threadIdx.x * 8; k < K; k += kThreads * 8) {
             const uint4 v = *reinterpret_cast<const uint4*>(xrow + k * 2);
@@ -892,9 +933,10 @@ static int32_t launch_quant_int8(const QInt8Args& qa, int nt, int32_t x_dtype, i
     cfg.numAttrs = use_pdl() ? 1 : 0;
     const int dm = div_mode;
     cudaError_t e;
-#define RWKVQ_Q(DT, V) e = cudaLaunchKernelEx(&cfg, quant_int8_kernel<DT, V>, qa, K, ldx, ldc, dm)
-    if (x_dtype == RWKVQ_F16) { if (vec) RWKVQ_Q(RWKVQ_F16, true); else RWKVQ_Q(RWKVQ_F16, false); }
-    else                      { if (vec) RWKVQ_Q(RWKVQ_BF16, true); else RWKVQ_Q(RWKVQ_BF16, false); }
+    const bool keep = vec && K <= (int64_t)kThreads * 8 * 8 && M * nt <= 4 * (int64_t)sm_count();     // few rows: one read, registers
+#define RWKVQ_Q(DT, V, KP) e = cudaLaunchKernelEx(&cfg, quant_int8_kernel<DT, V, KP>, qa, K, ldx, ldc, dm)
+    if (x_dtype == RWKVQ_F16) { if (keep) RWKVQ_Q(RWKVQ_F16, true, true); else if (vec) RWKVQ_Q(RWKVQ_F16, true, false); else RWKVQ_Q(RWKVQ_F16, false, false); }
+    else                      { if (keep) RWKVQ_Q(RWKVQ_BF16, true, true); else if (vec) RWKVQ_Q(RWKVQ_BF16, true, false); else RWKVQ_Q(RWKVQ_BF16, false, false); }
 #undef RWKVQ_Q
     if (e != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);

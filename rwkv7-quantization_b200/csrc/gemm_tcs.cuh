@@ -32,6 +32,7 @@ struct TcsShared {
     uint64_t full[kTcsMaxStages], empty[kTcsMaxStages], tfull[3], rx, rxfree;
     uint32_t tmem_base;
     int abort_flag;
+    float row_scale[3][128];     // INT8: the token rows' activation scales, fetched before the exchange
 };
 
 __device__ __forceinline__ uint32_t tcs_ctarank() {
@@ -211,8 +212,11 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
             if constexpr (KIND == KIND_F8) {
                 const float v = __ldg(a.a_scale[i]);
                 act_scale[i] = a.amax_is_amax ? div_mode_f32(fmaxf(v, 1e-12f), 448.f, a.div_mode) : v;
+            } else {
+                if (et < Mt) s.row_scale[i][et] = __ldg(a.a_scale[i] + m0 + et);      // read again only behind the named barrier below
             }
         }
+        if constexpr (KIND != KIND_F8) named_bar_sync(1, 128);
         for (int mat = 0; mat < a.nmat; ++mat) {
             bool have = mbar_wait(&s.tfull[mat], 0, abort_flag, a.wait_ns);
             if (!have) tcs_abort(s, a);
@@ -255,7 +259,7 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
                         f = sum * (act_scale[mat] * wrow[mat]);
                     } else {
                         if (a.acc[mat]) a.acc[mat][(int64_t)(m0 + m) * a.ldacc + my_row] = sum;
-                        f = (float)sum * (__ldg(a.a_scale[mat] + m0 + m) * wrow[mat]);
+                        f = (float)sum * (s.row_scale[mat][m] * wrow[mat]);
                     }
                     if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
                     a.out[mat][(int64_t)(m0 + m) * a.ldo + my_row] = __float2half_rn(f);
