@@ -323,9 +323,20 @@ def linear_fp8_m1_fused(x, weight_info, out_dtype=torch.float16):
     """M == 1 FP8 projection in a single launch (fused_fp8_gemm.py:645-679).  fp16 input is rounded to bf16
     before the amax, as there (:662)."""
     w, w_ts = _unpack(weight_info)
+    n, k = w.shape
+    dt = x.dtype
+    if ((dt is torch.bfloat16 or dt is torch.float16) and ROUTE == "auto" and x.numel() == k and x.is_contiguous()
+            and x.data_ptr() % 16 == 0 and _gemv_fits(1, k)):
+        # the decode call itself, without the general path's reshapes and views: one allocation, one boundary crossing
+        out = abi.new_out(1, n, x.device)
+        abi.call("rwkvq_gemv_fp8", x.data_ptr(), abi.BF16 if dt is torch.bfloat16 else abi.F16, None, w.data_ptr(), w.stride(0),
+                 w_ts.data_ptr(), out.data_ptr(), out.stride(0), 1, n, k, k, abi.DEFAULT_DIV,
+                 abi.FLAG_AMAX_AFTER_BF16 | _wscale_flag(w_ts, n), abi.stream_ptr())
+        abi.after_call()
+        return _finish(out, x.shape[:-1], n, out_dtype)
     x2 = _rows16(x.reshape(1, -1))
     out = _fp8_gemv(x2, _u8(w), w_ts, None, abi.FLAG_AMAX_AFTER_BF16)
-    return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
+    return _finish(out, x.shape[:-1], n, out_dtype)
 
 
 def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float16, push=None):
@@ -351,9 +362,43 @@ def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float1
     return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
 
 
+def _rkv_decode_fast(xr, xk, xv, wr_info, wk_info, wv_info):
+    """The decode call of linear_rkv_fused (up to 8 rows, plain contiguous inputs, no AWQ divisors) without the general
+    path's per-tensor views and checks; None = take the general path."""
+    dt = xr.dtype
+    k = xr.shape[-1]
+    m = xr.numel() // k if k else 0
+    wr, wk, wv = wr_info["weight"], wk_info["weight"], wv_info["weight"]
+    if not (0 < m <= 8 and ROUTE == "auto" and m < CODES_M_MIN and (dt is torch.bfloat16 or dt is torch.float16) and xk.dtype is dt and xv.dtype is dt
+            and xr.is_contiguous() and xk.is_contiguous() and xv.is_contiguous() and xk.shape == xr.shape and xv.shape == xr.shape
+            and wr.shape == wk.shape == wv.shape and wr.stride(0) == wk.stride(0) == wv.stride(0)
+            and "awq_scale" not in wr_info and "awq_scale" not in wk_info and not abi._out_override):
+        return None
+    n = wr.shape[0]
+    if wr.shape[1] != k or not _gemv_fits(m, k) or _codes_gemv_fits(m, k):
+        return None
+    if (xr.data_ptr() | xk.data_ptr() | xv.data_ptr()) % 16:
+        return None
+    sr, sk, sv = wr_info["tensor_scale"], wk_info["tensor_scale"], wv_info["tensor_scale"]
+    wflag = _wscale_flag(sr, n)
+    if _wscale_flag(sk, n) != wflag or _wscale_flag(sv, n) != wflag:
+        return None
+    outs = torch.empty((3, m, n), dtype=torch.float16, device=xr.device)
+    o0 = outs.data_ptr()
+    step = m * n * 2
+    abi.call("rwkvq_gemv_fp8_rkv", xr.data_ptr(), xk.data_ptr(), xv.data_ptr(), abi.BF16 if dt is torch.bfloat16 else abi.F16,
+             None, None, wr.data_ptr(), wk.data_ptr(), wv.data_ptr(), wr.stride(0), sr.data_ptr(), sk.data_ptr(), sv.data_ptr(),
+             o0, o0 + step, o0 + 2 * step, n, m, n, k, k, abi.DEFAULT_DIV, wflag, abi.stream_ptr())
+    abi.after_call()
+    return outs.unbind(0)
+
+
 def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.float16):
     """r, k, v projections (fused_fp8_gemm.py:944-1017): one launch for decode-sized M."""
     lead = xr.shape[:-1]
+    fast = _rkv_decode_fast(xr, xk, xv, wr_info, wk_info, wv_info)
+    if fast is not None:
+        return tuple(_finish(o, lead, o.shape[-1], out_dtype) for o in fast)
     xs = [_rows16(t) for t in (xr, xk, xv)]
     if len({t.dtype for t in xs}) != 1:
         xs = [t.to(torch.bfloat16) for t in xs]
@@ -596,6 +641,8 @@ def linear_quantized_fused(x, weight_info, out_dtype=torch.float16, push=None):
     push (FP8 and NVFP4 only): the GEMM also delivers its result to the other ranks of a column-split projection."""
     qtype = weight_info.get("qtype", "fp8")
     m = x.numel() // x.size(-1)
+    if m == 1 and qtype == "fp8" and push is None:          # the decode call: straight to the one-launch kernel
+        return linear_fp8_m1_fused(x, weight_info, out_dtype)
     if push is not None and qtype not in ("fp8", "nvfp4"):
         raise RuntimeError(f"rwkvq: no pushing GEMM for qtype {qtype!r}")
     if qtype == "int8":
