@@ -412,6 +412,19 @@ int32_t rwkvq_tc_gemm_nvfp4_push(const uint8_t* a_codes, int64_t lda, const uint
                                  int64_t workspace_bytes, void* const* peer_out, void* const* peer_flag, int32_t npeers,
                                  uint32_t epoch, void* stream);
 
+/* No counterpart in the reference.  FP8 projection of a few rows (up to 32) in ONE launch on the tensor-memory path,
+ * for matrices with few 128-row tiles (N = 4096: attention output, FFN value): K is split across a thread-block
+ * cluster, every CTA quantizes ITS K slice of the activations (the cluster exchanges the abs-max through distributed
+ * shared memory), writes the e4m3 codes into the operand ring itself and the partial sums are added in rank order.
+ * Same bits as rwkvq_actq_fp8_fused followed by rwkvq_tc_gemm_fp8, and measured slower than those two launches on
+ * the 7.2B shapes (every cluster quantizes the whole block again), so the drop-in dispatcher does not take it; it
+ * serves callers for whom one launch matters more than its duration.  rwkvq_tc_cluster_gemv_route(M, N, K) = 1 where
+ * the form applies.  Flags: AMAX_AFTER_BF16, QUANT_FROM_BF16, WSCALE_PER_ROW, OUT_VIA_BF16. */
+int32_t rwkvq_tc_cluster_gemv_route(int64_t M, int64_t N, int64_t K);
+int32_t rwkvq_tc_cluster_gemv_fp8(const void* x, int32_t x_dtype, int64_t ldx, const uint8_t* w, int64_t ldw, const float* w_scale,
+                                  void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int32_t div_mode, uint32_t flags,
+                                  void* stream);
+
 /* The same fusion for the FP8 W8A8 GEMM (rwkvq_tc_gemm_fp8 + all-gather in one kernel).  Only the tiled GEMM form can
  * carry it: rwkvq_tc_gemm_can_push(M, N, K) is 1 for the row counts it takes; the RELU2 flag is not accepted. */
 int32_t rwkvq_tc_gemm_can_push(int64_t M, int64_t N, int64_t K);

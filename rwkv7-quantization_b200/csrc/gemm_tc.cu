@@ -939,6 +939,31 @@ int32_t rwkvq_tc_gemm_fp8(const uint8_t* a_codes, int64_t lda, const float* amax
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_fp8");
 }
 
+/* FP8 projection of a few rows in ONE launch on the tensor-memory path: K split across a thread-block cluster, the
+ * activation quantization (per-call abs-max, e4m3 codes) done inside by the CTAs on their own K slices, partial sums
+ * exchanged through distributed shared memory.  Same bits as rwkvq_actq_fp8_fused + rwkvq_tc_gemm_fp8 on the same
+ * inputs.  rwkvq_tc_cluster_gemv_route(M, N, K): 1 where this form applies (up to 32 rows, matrices with few 128-row
+ * tiles); flags: RWKVQ_FLAG_AMAX_AFTER_BF16, RWKVQ_FLAG_QUANT_FROM_BF16, RWKVQ_FLAG_WSCALE_PER_ROW, RWKVQ_FLAG_OUT_VIA_BF16. */
+int32_t rwkvq_tc_cluster_gemv_route(int64_t M, int64_t N, int64_t K) { return tcsq_eligible(M, N, K) ? 1 : 0; }
+
+int32_t rwkvq_tc_cluster_gemv_fp8(const void* x, int32_t x_dtype, int64_t ldx, const uint8_t* w, int64_t ldw, const float* w_scale,
+                                  void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int32_t div_mode, uint32_t flags,
+                                  void* stream) {
+    const char* who = "tc_cluster_gemv_fp8";
+    RWKVQ_REQUIRE(x && w && w_scale && out_f16, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
+    RWKVQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && ldo >= N, RWKVQ_E_SHAPE, "%s: M=%lld N=%lld K=%lld ldo=%lld", who, (long long)M, (long long)N, (long long)K, (long long)ldo);
+    if (M == 0 || N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(tcsq_eligible(M, N, K), RWKVQ_E_SHAPE, "%s: %lld x %lld x %lld is not a shape of this form (see rwkvq_tc_cluster_gemv_route)", who,
+                  (long long)M, (long long)N, (long long)K);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+    TcArgs a{};
+    a.x[0] = x; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    fill_common(a, 1, M, N, K, ldx, ldo, div_mode, flags & ~RWKVQ_FLAG_RELU2);
+    return run_tcsq(a, w, ldw, x_dtype, (cudaStream_t)stream, who);
+}
+
 /* 1 if rwkvq_tc_gemm_fp8_push accepts this shape: the tiled GEMM form runs it (more rows than the few-token kernels
  * take). */
 int32_t rwkvq_tc_gemm_can_push(int64_t M, int64_t N, int64_t K) {

@@ -282,6 +282,279 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
     if (threadIdx.x == 64) tc_mark(a, 12);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same kernel with the FP8 activation quantization INSIDE (one launch per projection, up to 32 rows).  A cluster
+// spans all of K, and a CTA needs the codes of ITS K slice only: four more warps read that slice of the activations,
+// the CTAs exchange their abs-max through distributed shared memory (one float per CTA, one mbarrier), and the same
+// warps then write the e4m3 codes of each 128-byte step straight into the ring stage -- in the 128-byte-swizzled layout
+// a TMA load would have produced -- while the TMA warp loads only the weights.  No quantizer launch in front, no codes
+// in global memory; amax, codes and K split are those of the two-launch route, so the results are the same bits.
+// Measured SLOWER than the two launches on the FFN value shape (16 rows: 23.2 against 18.7 us): each of the 32 clusters
+// reads and quantizes the whole block again (the same 512 KB from L2, twice), whereas the quantizer kernel does it once
+// while this kernel's weight prefetch already runs.  Kept as an entry point of its own; the dispatcher does not use it.
+constexpr int kTcsqThreads = 320;
+constexpr int kTcsqMaxM = 32;
+
+struct TcsqShared {
+    TcsShared b;
+    uint64_t amaxbar;            // one arrival per CTA of the cluster
+    float amax_part[8];          // slot r: abs-max of CTA r's slice
+    float amax;                  // max over the cluster = over the whole block of activations
+    float red[4];
+};
+
+__device__ __forceinline__ void tcs_st_remote_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kTcsqThreads, 2) gemm_tcsq_kernel(const __grid_constant__ TcMaps maps, const TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ TcsqShared sq;
+    TcsShared& s = sq.b;
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t stage_bytes = kABytes + (uint32_t)a.NB * kChunk;
+    float* rxbuf = reinterpret_cast<float*>(ring + (size_t)a.stages * stage_bytes);    // [C][M][R]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = a.qtiles, R = kTileP / C;
+    const int rank = (int)tcs_ctarank();
+    const int prow = ((int)blockIdx.x / C) * kTileP;
+    const int Mt = a.M;
+    const int kc0 = a.kchunks * rank / C, kc1 = a.kchunks * (rank + 1) / C, nk = kc1 - kc0;
+    const uint32_t tmem_cols = 32u;                          // one accumulator of at most 32 tokens
+    const volatile int* abort_flag = &s.abort_flag;
+
+    griddep_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < a.stages; ++i) {
+            mbar_init(&s.full[i], 2);                         // the TMA warp's expect_tx arrival and the quantizer's
+            mbar_init(&s.empty[i], 1);
+        }
+        mbar_init(&s.tfull[0], 1);
+        mbar_init(&s.rx, (uint32_t)(C * (R >= 32 ? R / 32 : 1)));
+        mbar_init(&sq.amaxbar, (uint32_t)C);
+        s.abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+        prefetch_tmap(&maps.w[0]);
+    }
+    if (warp == 1) tmem_alloc(&s.tmem_base, tmem_cols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = s.tmem_base;
+    tcs_cluster_arrive();
+
+    if (warp == 0) {
+        // ============================== TMA producer: weights only, nothing to wait for ==============================
+        if (lane == 0) {
+            for (int n = 0; n < nk; ++n) {
+                const int st = n % a.stages;
+                if (n >= a.stages && !mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { tcs_abort(s, a); break; }
+                mbar_expect_tx(&s.full[st], kABytes);
+                tma_load_2d(ring + (size_t)st * stage_bytes, &maps.w[0], (kc0 + n) * kChunk, prow, &s.full[st]);
+            }
+        }
+    } else if (warp == 1) {
+        // ============================== MMA issuer ==============================
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(KIND_F8, kTileP, a.NB);
+            for (int n = 0; n < nk; ++n) {
+                const int st = n % a.stages;
+                if (!mbar_wait(&s.full[st], (n / a.stages) & 1, abort_flag, a.wait_ns)) { tcs_abort(s, a); break; }
+                tc_fence_after_sync();
+                const uint32_t sa = smem_u32(ring + (size_t)st * stage_bytes);
+                const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
+#pragma unroll
+                for (int k = 0; k < kChunk / 32; ++k)
+                    tc_mma<KIND_F8>(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (n > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&s.empty[st]);
+                if (n == nk - 1) tc_commit(&s.tfull[0]);
+            }
+        }
+    }
+    __syncwarp();
+    tcs_cluster_wait();              // every CTA of the cluster has initialised its barriers
+    if (warp < 2) tcs_cluster_arrive();
+
+    if (warp >= 6) {
+        // ============================== activation quantizer (4 warps) ==============================
+        const int qt = (int)threadIdx.x - 6 * 32;
+        const bool after_bf16 = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0, from_bf16 = (a.flags & RWKVQ_FLAG_QUANT_FROM_BF16) != 0;
+        const char* x = reinterpret_cast<const char*>(a.x[0]);
+        const int kv = a.K >> 3;                                             // 16-byte vectors per row
+        const int v0 = kc0 * 16, v1 = min(kc1 * 16, kv), vs = max(v1 - v0, 0);    // this CTA's vectors of every row
+        griddep_wait();                                                      // the activations may come from the previous kernel
+        // ---- pass 1: abs-max of the slice.  Dependent round trips to L2 are what this phase costs (the whole kernel
+        // waits for the maximum), so a thread keeps 16 loads in flight.
+        float m = 0.f;
+        const int total = Mt * vs;
+#pragma unroll 1
+        for (int i0 = qt; i0 < total; i0 += 128 * 16) {
+            uint4 v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int idx = i0 + j * 128;
+                v[j] = make_uint4(0, 0, 0, 0);
+                if (idx < total) {
+                    const int r = idx / vs, c = idx - r * vs;
+                    v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + (int64_t)(v0 + c) * 8) * 2);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float2 f = cvt2<DT>(w[q]);
+                    if (DT == RWKVQ_F16 && after_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                    m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+                }
+            }
+        }
+        m = warp_max(m);
+        if (lane == 0) sq.red[warp - 6] = m;
+        named_bar_sync(2, 128);
+        if (qt < C) {                                                        // this CTA's maximum into slot `rank` of every CTA
+            const float mine = fmaxf(fmaxf(sq.red[0], sq.red[1]), fmaxf(sq.red[2], sq.red[3]));
+            tcs_st_remote_f32(tcs_mapa(smem_u32(&sq.amax_part[rank]), (uint32_t)qt), mine);
+            tcs_arrive_remote(tcs_mapa(smem_u32(&sq.amaxbar), (uint32_t)qt));
+        }
+        if (!tcs_wait_cluster(&sq.amaxbar, 0, abort_flag, a.wait_ns)) tcs_abort(s, a);
+        float amax = sq.amax_part[0];
+        for (int i = 1; i < C; ++i) amax = fmaxf(amax, sq.amax_part[i]);
+        if (qt == 0) sq.amax = amax;
+        const float inv = scale_inv(448.f, fmaxf(amax, 1e-12f), a.div_mode);
+        // ---- pass 2: codes of one 128-byte step after the other, straight into the ring stage (128-byte swizzle: the
+        // 16-byte piece j of row r sits at piece j ^ (r % 8) of its 128-byte row inside the 8-row atom)
+        const int items = Mt * 8;                                            // (row, 16-code piece) pairs per step
+        auto load_item = [&](int n, int it, uint4 (&v)[2]) {
+            const int r = it >> 3, j = it & 7;
+            const int vec = (kc0 + n) * 16 + j * 2;                          // first of the two vectors behind the piece
+            const char* p = x + ((int64_t)r * a.ldx + (int64_t)vec * 8) * 2;
+            v[0] = vec < kv ? *reinterpret_cast<const uint4*>(p) : make_uint4(0, 0, 0, 0);
+            v[1] = vec + 1 < kv ? *reinterpret_cast<const uint4*>(p + 16) : make_uint4(0, 0, 0, 0);
+        };
+        auto codes8 = [&](const uint4& v) -> uint2 {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float2 f = cvt2<DT>(w[q]);
+                if (DT == RWKVQ_F16 && from_bf16) { f.x = bf16_round(f.x); f.y = bf16_round(f.y); }
+                c[q] = e4m3x2(f.x * inv, f.y * inv);
+            }
+            return make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+        };
+        // Each of the four warps takes every fourth step (four steps' loads are in flight at once); within its steps a
+        // warp works in batches of 128 (row, piece) items, the next batch's loads issued before the current one is
+        // converted.
+        const int qw = warp - 6;
+        const int nbatch = (items + 127) >> 7;
+        auto load_batch = [&](int n, int bt, uint4 (&v)[4][2]) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int it = bt * 128 + j * 32 + lane;
+                if (it < items) load_item(n, it, v[j]);
+            }
+        };
+        uint4 cur[4][2], nxt[4][2];
+        int n = qw, bt = 0;
+        if (n < nk) load_batch(n, 0, cur);
+#pragma unroll 1
+        while (n < nk) {
+            int n2 = n, bt2 = bt + 1;
+            if (bt2 == nbatch) { bt2 = 0; n2 = n + 4; }
+            if (n2 < nk) load_batch(n2, bt2, nxt);
+            const int st = n % a.stages;
+            if (bt == 0 && n >= a.stages) {                                  // lane 0 waits for the stage, the warp follows
+                int okv = 1;
+                if (lane == 0) okv = mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns) ? 1 : 0;
+                okv = __shfl_sync(0xffffffffu, okv, 0);
+                if (!okv) {
+                    tcs_abort(s, a);
+                    break;
+                }
+            }
+            uint8_t* btile = ring + (size_t)st * stage_bytes + kABytes;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int it = bt * 128 + j * 32 + lane;
+                if (it < items) {
+                    const int r = it >> 3, pc = it & 7;
+                    const uint2 lo = codes8(cur[j][0]), hi = codes8(cur[j][1]);
+                    *reinterpret_cast<uint4*>(btile + (r >> 3) * 1024 + (r & 7) * 128 + ((pc ^ (r & 7)) << 4)) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+                }
+            }
+            if (bt == nbatch - 1) {
+                fence_proxy_async();                                         // these generic-proxy stores are read by the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.full[st]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { cur[j][0] = nxt[j][0]; cur[j][1] = nxt[j][1]; }
+            n = n2;
+            bt = bt2;
+        }
+        tcs_cluster_arrive();
+    } else if (warp >= 2) {
+        // ============================== exchange + epilogue ==============================
+        const int q = warp & 3;
+        const int et = (warp - 2) * 32 + lane;
+        const int l = q * 32 + lane;
+        const uint32_t owner = (uint32_t)(l / R);
+        const int lr = l - (int)owner * R;
+        const uint32_t remote = tcs_mapa(smem_u32(rxbuf), owner) + (uint32_t)(((size_t)rank * Mt * R + lr) * 4);
+        const uint32_t remote_rx = tcs_mapa(smem_u32(&s.rx), owner);
+        const int my_c = et % R, my_m0 = et / R, m_step = 128 / R;
+        const int my_row = prow + rank * R + my_c;
+        const bool per_row = (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) != 0;
+        const float wrow = __ldg(a.ws[0] + (per_row ? min(my_row, a.N - 1) : 0));
+        bool have = mbar_wait(&s.tfull[0], 0, abort_flag, a.wait_ns);
+        if (!have) tcs_abort(s, a);
+        have = __all_sync(0xffffffffu, have);
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+        for (int c0 = 0; c0 < Mt; c0 += 16) {
+            uint32_t r[16];
+            if (have) {
+                tmem_ld16(taddr + c0, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (c0 + j < Mt) tcs_st_remote(remote + (uint32_t)((c0 + j) * R * 4), r[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane % min(R, 32) == 0) tcs_arrive_remote(remote_rx);
+        tcs_cluster_arrive();
+        const bool got = tcs_wait_cluster(&s.rx, 0, abort_flag, a.wait_ns);
+        if (!got) tcs_abort(s, a);
+        if (got && !*abort_flag && my_row < a.N) {
+            // the block's abs-max was written by the quantizer warps before their first arrival on a `full` barrier
+            const float act_scale = div_mode_f32(fmaxf(sq.amax, 1e-12f), 448.f, a.div_mode);
+            for (int m = my_m0; m < Mt; m += m_step) {
+                float sum = 0.f;
+                for (int src = 0; src < C; ++src) sum += rxbuf[((size_t)src * Mt + m) * R + my_c];
+                float f = sum * (act_scale * wrow);
+                if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
+                a.out[0][(int64_t)m * a.ldo + my_row] = __float2half_rn(f);
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+    tcs_cluster_wait();
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 // Cluster size: as many CTAs per (128-row tile, token tile) as keep the whole grid resident at once -- two CTAs per SM
 // up to 64 tokens, one per SM with token tiles of 128 -- at most 8 and at most one per two 128-byte steps of K.  It
@@ -340,6 +613,56 @@ static int32_t run_tcs(TcArgs a, const TcCall& c, cudaStream_t st, const char* w
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(a.max_slots * a.ptiles * C));
     cfg.blockDim = dim3(kTcsThreads);
+    cfg.dynamicSmemBytes = (size_t)a.stages * stage_bytes + rx_bytes + 1024;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 2 : 1;
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, maps, a);
+    if (err != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(err));
+    }
+    return check_launch(who);
+}
+
+// one-launch form: FP8, a single matrix, up to 32 rows, the shapes the cluster kernel takes anyway
+static bool tcsq_eligible(int64_t M, int64_t N, int64_t K) {
+    static const int on = std::getenv("RWKVQ_TCSQ") ? std::atoi(std::getenv("RWKVQ_TCSQ")) : 1;
+    return on && M >= 1 && M <= kTcsqMaxM && K % 8 == 0 && tcs_eligible(M, N, K, 0, 1);
+}
+
+static int32_t run_tcsq(TcArgs a, const void* w, int64_t ldw, int x_dtype, cudaStream_t st, const char* who) {
+    const int C = tcs_cluster_size(a.M, a.N, a.K);
+    a.NB = tcs_token_tile(a.M);
+    a.kchunks = (a.K + kChunk - 1) / kChunk;
+    a.ptiles = (a.N + kTileP - 1) / kTileP;
+    a.qtiles = C;
+    a.max_slots = 1;
+    a.acc_stride = 32;
+    a.wait_ns = wait_limit_ns();
+    a.status = device_status_ptr();
+    const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk;
+    const size_t rx_bytes = (size_t)a.M * kTileP * 4;
+    const int per_cta = (a.kchunks + C - 1) / C;
+    a.stages = (int)std::min<size_t>(std::min<int>(kTcsMaxStages, per_cta), (kTcSmemBudgetHalf - 1024 - rx_bytes) / stage_bytes);
+    RWKVQ_REQUIRE(a.stages >= 2 || per_cta == 1, RWKVQ_E_SHAPE, "%s: shared memory leaves fewer than two ring stages", who);
+    a.stages = std::max(a.stages, 1);
+    TcMaps maps;
+    const int32_t rcm = make_map(&maps.w[0], w, a.N, a.K, ldw, kTileP, who);
+    if (rcm) return rcm;
+    auto kern = x_dtype == RWKVQ_F16 ? gemm_tcsq_kernel<RWKVQ_F16> : gemm_tcsq_kernel<RWKVQ_BF16>;
+    const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudget, who);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(a.ptiles * C));
+    cfg.blockDim = dim3(kTcsqThreads);
     cfg.dynamicSmemBytes = (size_t)a.stages * stage_bytes + rx_bytes + 1024;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];

@@ -258,6 +258,38 @@ def _fp8_codes_gemm(x2, w, w_ts, act_flags, gemm_flags=0, push=None):
     return out
 
 
+# The cluster split-K kernel with the activation quantization inside (rwkvq_tc_cluster_gemv_fp8, one launch) is OFF by
+# default: measured on the FFN value shape it is slower than the quantizer kernel + the same GEMM on codes (16 rows:
+# 23.2 against 18.7 us, 32 rows: 28.8 against 21.4) -- every one of the 32 clusters re-reads and re-quantizes the whole
+# block, while the separate quantizer runs once, in parallel with the GEMM's weight prefetch.  RWKVQ_CLUSTER_ONE_LAUNCH=1
+# routes 9..32 rows to it where it applies; =first also ahead of the decode GEMV on codes.
+_CLUSTER_ONE_LAUNCH = os.environ.get("RWKVQ_CLUSTER_ONE_LAUNCH", "0").lower()
+CLUSTER_M_MIN = 9
+_CLUSTER_FIRST = _CLUSTER_ONE_LAUNCH == "first"
+_cluster_route_cache: dict = {}
+
+
+def _cluster_one_launch(m: int, n: int, k: int) -> bool:
+    """9..32 rows against a matrix with few 128-row tiles: one launch, activation quantization inside the cluster
+    split-K kernel (rwkvq_tc_cluster_gemv_fp8); opt-in, see above."""
+    if _CLUSTER_ONE_LAUNCH not in ("1", "first") or m < CLUSTER_M_MIN or m > 32 or ROUTE != "auto" or not _ACTQ_FUSED or k % 16:
+        return False
+    fits = _cluster_route_cache.get((m, n, k))
+    if fits is None:
+        fits = _cluster_route_cache[(m, n, k)] = bool(abi.lib().rwkvq_tc_cluster_gemv_route(m, n, k))
+    return fits
+
+
+def _fp8_cluster_gemv(x2, w, w_ts):
+    m, k = x2.shape
+    n = w.shape[0]
+    out = abi.new_out(m, n, x2.device)
+    abi.call("rwkvq_tc_cluster_gemv_fp8", x2.data_ptr(), abi.dtype_code(x2), x2.stride(0), w.data_ptr(), w.stride(0), w_ts.data_ptr(),
+             out.data_ptr(), out.stride(0), m, n, k, abi.DEFAULT_DIV, abi.FLAG_QUANT_FROM_BF16 | _wscale_flag(w_ts, n), abi.stream_ptr())
+    abi.after_call()
+    return out
+
+
 def _fp8_codes_gemv(x2, w, w_ts):
     """9..32 rows: quantize once (one cooperative launch), then the weight-streaming decode kernel on the codes."""
     m, k = x2.shape
@@ -353,10 +385,16 @@ def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float1
     if m == 1:
         return linear_fp8_m1_fused(x, {"weight": w, "tensor_scale": w_ts}, out_dtype)
     x2 = _rows16(x)
-    if _codes_gemv_fits(m, k) and _ACTQ_FUSED and k % 8 == 0:
+    if _CLUSTER_FIRST and _cluster_one_launch(m, w.shape[0], k):
+        out = _fp8_cluster_gemv(x2, _u8(w), w_ts)
+    elif _codes_gemv_fits(m, k) and _ACTQ_FUSED and k % 8 == 0:
         out = _fp8_codes_gemv(x2, _u8(w), w_ts)
     elif _tc_fused_fits(m, k) or _gemv_fits(m, k):
         out = _fp8_gemv(x2, _u8(w), w_ts, None, 0)
+    elif _cluster_one_launch(m, w.shape[0], k):
+        # where the two-launch route would run the cluster split-K kernel anyway: the same kernel with the activation
+        # quantization inside (same codes, same K split: same bits, also as the r/k/v form on such shapes)
+        out = _fp8_cluster_gemv(x2, _u8(w), w_ts)
     else:
         out = _fp8_codes_gemm(x2, _u8(w), w_ts, abi.FLAG_QUANT_FROM_BF16)
     return _finish(out, x.shape[:-1], w.shape[0], out_dtype)

@@ -448,3 +448,26 @@ def test_cluster_splitk_few_tokens(mods, scheme, m, n, k):
         bits_equal(acc, want_acc, "accumulators")
         bits_equal(out, want, "outputs")
     assert abi.device_status() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(9, 4096, 16384), (16, 520, 16384), (32, 1000, 8320), (12, 4096, 4096), (32, 2560, 2560)])
+def test_cluster_one_launch_equals_two_launch_route(mods, dt, m, n, k):
+    """Up to 32 rows: the cluster split-K kernel with the activation quantization inside (one launch) gives the bits of
+    the quantizer kernel followed by the same GEMM on codes, and the oracle's result within 1e-2."""
+    abi, f, _ = mods
+    assert abi.lib().rwkvq_tc_cluster_gemv_route(m, n, k) == 1
+    info = fp8_weight(400 + n, n, k, perchannel=(n == 1000))
+    d = dev(info)
+    x = gen(401 + m, (m, k), 1.0).to(dt)
+    x[m // 2, :64] *= 30.0                                            # the abs-max sits in one CTA's K slice
+    w, w_ts = f._u8(d["weight"]), d["tensor_scale"]
+    x2 = x.cuda()
+    before = abi.launch_count()
+    one = f._fp8_cluster_gemv(x2, w, w_ts)
+    assert abi.launch_count() - before == 1
+    two = f._fp8_codes_gemm(x2, w, w_ts, abi.FLAG_QUANT_FROM_BF16)
+    bits_equal(one, two, "one launch vs quantizer + GEMM")
+    bits_equal(one, f._fp8_cluster_gemv(x2, w, w_ts), "run to run")
+    assert rel_err(one, O.linear_fp8_fused(x, info, lib_div(abi))) <= 1e-2
+    assert abi.device_status() == 0
