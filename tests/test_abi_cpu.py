@@ -128,3 +128,23 @@ def test_no_cpu_fallback_without_device():
     import fused_fp8_gemm as f
     with pytest.raises(RuntimeError):
         f.prep_x_int8(torch.zeros(2, 64, dtype=torch.float16))
+
+
+def test_int4_k_split_plan_is_host_arithmetic():
+    """rwkvq_gemv_int4_ksplit_slices only does shared-memory arithmetic (no device needed): the slices the K-split
+    form uses for the 7.2B shapes, 1 where one launch already holds the block, 0 for shapes it does not take."""
+    import rwkvq_abi as abi
+    sl = abi.lib().rwkvq_gemv_int4_ksplit_slices
+    assert sl(16, 4096, 16384) == 8          # FFN value, 16 rows: 2048-k slices, 64 KB of activations each
+    assert sl(8, 4096, 16384) == 4
+    assert sl(4, 4096, 16384) == 2
+    assert sl(1, 4096, 16384) == 1           # one row fits beside a deep ring
+    assert sl(16, 4096, 4096) == 2           # attention output: few row tiles, the split pays
+    assert sl(16, 16384, 4096) == 1          # FFN key: many row tiles, the block that fits is left whole
+    assert sl(17, 4096, 4096) == 0 and sl(4, 4096, 1000) == 0 and sl(0, 4096, 4096) == 0
+
+
+def test_column_split_rejects_unknown_gather():
+    import rwkvq_dist as D
+    with pytest.raises(ValueError):
+        D.ColumnSplitLinear({"weight": None}, lambda *a: None, gather="ring")
