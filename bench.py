@@ -247,6 +247,7 @@ def run_ours(args, rank, world, local_rank):
     abi.require_device()
     dist_on = world > 1
     if dist_on:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")      # stdout carries the one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     layers = make_model(dev, seed=100 + rank, nlayers=args.layers)

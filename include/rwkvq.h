@@ -432,13 +432,19 @@ int32_t rwkvq_tc_gemm_fp8_push(const uint8_t* a_codes, int64_t lda, const float*
                                int64_t ldw, const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
                                int32_t div_mode, uint32_t flags, void* workspace, int64_t workspace_bytes,
                                void* const* peer_out, void* const* peer_flag, int32_t npeers, uint32_t epoch, void* stream);
+/* ... and for the INT8 W8A8 GEMM (rwkvq_tc_gemm_int8 without the accumulator output). */
+int32_t rwkvq_tc_gemm_int8_push(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                                const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, uint32_t flags,
+                                void* workspace, int64_t workspace_bytes, void* const* peer_out, void* const* peer_flag,
+                                int32_t npeers, uint32_t epoch, void* stream);
 
 /* No counterpart in the reference.  rwkvq_tc_gemm_fp8 for callers that cannot supply device scratch -- a host runtime
  * that owns every byte of device memory and forbids allocation inside its serving loop, or code running where
  * cudaMalloc is not allowed.  The scratch is an 8 MiB array built into the library on each GPU; no allocation happens
  * in this call or below it.  The first call on a device resolves the array's address and should be made outside
- * stream capture.  Only the weight-streaming form (at most 16 tokens, or at most 48 against K >= 8192) keeps partial
- * sums there; such a call is refused (RWKVQ_E_WORKSPACE) when it needs more than 8 MiB; every other shape is accepted.
+ * stream capture.  Only the stream-K form (few tokens against a matrix with too many 128-row tiles for the cluster
+ * kernel) keeps partial sums there; such a call is refused (RWKVQ_E_WORKSPACE) when it needs more than 8 MiB; every
+ * other shape is accepted.
  * The array is shared by all calls on a device, its header is re-cleared on `stream` by every call, and calls that
  * overlap on the GPU race on it.  rwkvq_tc_static_status copies its status word to the host (synchronizes). */
 int32_t rwkvq_tc_gemm_fp8_static(const uint8_t* a_codes, int64_t lda, const float* amax, int32_t amax_is_amax,

@@ -989,6 +989,23 @@ int32_t rwkvq_tc_gemm_fp8_push(const uint8_t* a_codes, int64_t lda, const float*
     return run_tc(a, c, (cudaStream_t)stream, who);
 }
 
+/* rwkvq_tc_gemm_int8 fused with the all-gather of a column-split projection (no accumulator output in this form). */
+int32_t rwkvq_tc_gemm_int8_push(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                                const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, uint32_t flags,
+                                void* workspace, int64_t workspace_bytes, void* const* peer_out, void* const* peer_flag, int32_t npeers,
+                                uint32_t epoch, void* stream) {
+    const char* who = "tc_gemm_int8_push";
+    RWKVQ_REQUIRE(M > 0 && N > 0, RWKVQ_E_SHAPE, "%s: empty result (the peers would wait for a signal that never comes)", who);
+    TcArgs a{};
+    const int32_t rc = make_push(&a.push, workspace, workspace_bytes, out_f16, peer_out, peer_flag, npeers, epoch, who);
+    if (rc != RWKVQ_OK) return rc;
+    a.a_scale[0] = a_scales; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    fill_common(a, 1, M, N, K, 0, ldo, RWKVQ_DIV_IEEE, flags & ~RWKVQ_FLAG_RELU2);
+    TcCall c{};
+    c.kind = KIND_I8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, who);
+}
+
 int32_t rwkvq_tc_gemm_int8(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
                            const float* w_scale, void* out_f16, int64_t ldo, int32_t* acc_out, int64_t ldacc, int64_t M,
                            int64_t N, int64_t K, uint32_t flags, void* workspace, int64_t workspace_bytes, void* stream) {

@@ -559,11 +559,24 @@ def ffn_relu2_fp8(x, key_info, value_info, out_dtype=torch.float16, return_hidde
 
 
 # --------------------------------------------------------------------------- INT8
-def _int8_any(x2, w, w_scale, acc_out=None):
+def _int8_any(x2, w, w_scale, acc_out=None, push=None):
     m, k = x2.shape
     n = w.shape[0]
     out = abi.new_out(m, n, x2.device)
     st = abi.stream_ptr()
+    if push is not None:
+        # column-split projection: the GEMM also delivers its result to the other ranks (see _fp8_codes_gemm)
+        if acc_out is not None or not can_push(m, n, k):
+            raise RuntimeError("rwkvq: the pushed all-gather rides in the tiled tensor-core GEMM only (see can_push), without acc_out")
+        codes = torch.empty((m, k), dtype=torch.int8, device=x2.device)
+        xs = torch.empty(m, dtype=torch.float32, device=x2.device)
+        abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0) if m > 1 else k,
+                 codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
+        ws = abi.workspace(min(m, 128), n, k, 1, x2.device)
+        abi.call("rwkvq_tc_gemm_int8_push", codes.data_ptr(), k, xs.data_ptr(), w.data_ptr(), w.stride(0), w_scale.data_ptr(),
+                 out.data_ptr(), out.stride(0), m, n, k, 0, ws.data_ptr(), ws.numel(), push[0], push[1], push[2], push[3], st)
+        abi.after_call(ws)
+        return out
     if _codes_gemv_fits(m, k):
         # 9..32 rows: quantize the rows once, then the weight-streaming decode kernel on the codes
         codes = torch.empty((m, k), dtype=torch.int8, device=x2.device)
@@ -596,11 +609,11 @@ def _int8_any(x2, w, w_scale, acc_out=None):
     return out
 
 
-def linear_int8_fused(x, weight_info, out_dtype=torch.float16, acc_out=None):
+def linear_int8_fused(x, weight_info, out_dtype=torch.float16, acc_out=None, push=None):
     """INT8 W8A8 projection, exact int32 accumulation (fused_fp8_gemm.py:785-818).  `acc_out` (optional int32
-    [M, N]) receives the raw accumulators."""
+    [M, N]) receives the raw accumulators.  push: see _fp8_codes_gemm."""
     w, w_scale = weight_info["weight"], weight_info["tensor_scale"]
-    out = _int8_any(_rows16(x), w, w_scale, acc_out)
+    out = _int8_any(_rows16(x), w, w_scale, acc_out, push)
     return _finish(out, x.shape[:-1], w.shape[0], out_dtype)
 
 
@@ -676,15 +689,15 @@ def linear_rkv_int8_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch
 def linear_quantized_fused(x, weight_info, out_dtype=torch.float16, push=None):
     """Engine-facing dispatcher (fused_fp8_gemm.py:1080-1098): qtype "int8" -> INT8 path; otherwise FP8, with the
     fused semantics up to FUSED_M_MAX rows and the linear_fp8 semantics (bf16 first, result through bf16) above.
-    push (FP8 and NVFP4 only): the GEMM also delivers its result to the other ranks of a column-split projection."""
+    push (FP8, INT8 and NVFP4): the GEMM also delivers its result to the other ranks of a column-split projection."""
     qtype = weight_info.get("qtype", "fp8")
     m = x.numel() // x.size(-1)
     if m == 1 and qtype == "fp8" and push is None:          # the decode call: straight to the one-launch kernel
         return linear_fp8_m1_fused(x, weight_info, out_dtype)
-    if push is not None and qtype not in ("fp8", "nvfp4"):
+    if push is not None and qtype not in ("fp8", "int8", "nvfp4"):
         raise RuntimeError(f"rwkvq: no pushing GEMM for qtype {qtype!r}")
     if qtype == "int8":
-        return linear_int8_fused(x, weight_info, out_dtype)
+        return linear_int8_fused(x, weight_info, out_dtype, push=push)
     if qtype == "nvfp4":
         from nvfp4_ops import linear_nvfp4
         return linear_nvfp4(x, weight_info, out_dtype, push=push)

@@ -168,7 +168,7 @@ class ColumnSplitLinear:
     FP8 / INT8 / NVFP4 weight-info dicts, int4.int4_ops.linear_int4 for INT4 ones).  gather="nccl": an NCCL all-gather
     (rank-major) followed by one copy into the [M, N] layout; gather="peer": PeerGather above (GPU only, fp16 results;
     `max_rows` sizes its buffers); gather="push": the projection's GEMM stores its result tiles into every rank's buffer
-    itself and the receivers only wait for a flag (FP8 and NVFP4 weights, row counts that run the tiled tensor-core
+    itself and the receivers only wait for a flag (FP8, INT8 and NVFP4 weights, row counts that run the tiled tensor-core
     GEMM; other calls fall back to "peer").  The pushed FP8 result follows linear_quantized_fused's semantics."""
 
     def __init__(self, weight_info: dict, linear_fn, group=None, already_sliced: bool = False, gather: str = "nccl", max_rows: int = 4096):
@@ -183,7 +183,7 @@ class ColumnSplitLinear:
         self.peer = PeerGather(max_rows, self.n_local * self.world, group) if gather in ("peer", "push") else None
         # "push": the GEMM itself stores its tiles into every rank's buffer (one kernel computes and gathers); taken where
         # the projection runs the kernel that can do it (NVFP4 weights on the tensor-core route), else the pull form
-        self.push = gather == "push" and self.local.get("qtype", "fp8") in ("nvfp4", "fp8")
+        self.push = gather == "push" and self.local.get("qtype", "fp8") in ("nvfp4", "fp8", "int8")
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
         if self.peer is not None:
