@@ -228,18 +228,22 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
             // this CTA's partial sums of row l go to slot `rank` of the owner's buffer (zeros after a timeout, so that
             // the peers' waits end)
             const uint32_t taddr = tmem_base + (uint32_t)(mat * a.acc_stride) + ((uint32_t)(q * 32) << 16);
-            for (int c0 = 0; c0 < Mt; c0 += 16) {
-                uint32_t r[16];
+            for (int c0 = 0; c0 < Mt; c0 += 32) {            // two tensor-memory loads in flight, then 32 warp-wide peer stores
+                uint32_t r[16], r2[16];
                 if (have) {
                     tmem_ld16(taddr + c0, r);
+                    if (c0 + 16 < Mt) tmem_ld16(taddr + c0 + 16, r2);
                     tmem_ld_wait();
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) r[j] = 0u;
+                    for (int j = 0; j < 16; ++j) r[j] = r2[j] = 0u;
                 }
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
                     if (c0 + j < Mt) tcs_st_remote(remote + (uint32_t)((c0 + j) * R * 4), r[j]);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c0 + 16 + j < Mt) tcs_st_remote(remote + (uint32_t)((c0 + 16 + j) * R * 4), r2[j]);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -252,8 +256,13 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
             if (et == 0 && mat == a.nmat - 1) tc_mark(a, 9);
             if (got && !*abort_flag && my_row < a.N) {
                 for (int m = my_m0; m < Mt; m += m_step) {
+                    T v[8];                                    // all contributions in flight, added in rank order
+#pragma unroll
+                    for (int src = 0; src < 8; ++src) v[src] = src < C ? rxbuf[((size_t)src * Mt + m) * R + my_c] : T(0);
                     T sum = 0;
-                    for (int src = 0; src < C; ++src) sum += rxbuf[((size_t)src * Mt + m) * R + my_c];
+#pragma unroll
+                    for (int src = 0; src < 8; ++src)
+                        if (src < C) sum += v[src];
                     float f;
                     if constexpr (KIND == KIND_F8) {
                         f = sum * (act_scale[mat] * wrow[mat]);
@@ -538,8 +547,13 @@ __global__ void __launch_bounds__(kTcsqThreads, 2) gemm_tcsq_kernel(const __grid
             // the block's abs-max was written by the quantizer warps before their first arrival on a `full` barrier
             const float act_scale = div_mode_f32(fmaxf(sq.amax, 1e-12f), 448.f, a.div_mode);
             for (int m = my_m0; m < Mt; m += m_step) {
+                float v[8];
+#pragma unroll
+                for (int src = 0; src < 8; ++src) v[src] = src < C ? rxbuf[((size_t)src * Mt + m) * R + my_c] : 0.f;
                 float sum = 0.f;
-                for (int src = 0; src < C; ++src) sum += rxbuf[((size_t)src * Mt + m) * R + my_c];
+#pragma unroll
+                for (int src = 0; src < 8; ++src)
+                    if (src < C) sum += v[src];
                 float f = sum * (act_scale * wrow);
                 if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
                 a.out[0][(int64_t)m * a.ldo + my_row] = __float2half_rn(f);
