@@ -471,3 +471,40 @@ def test_cluster_one_launch_equals_two_launch_route(mods, dt, m, n, k):
     bits_equal(one, f._fp8_cluster_gemv(x2, w, w_ts), "run to run")
     assert rel_err(one, O.linear_fp8_fused(x, info, lib_div(abi))) <= 1e-2
     assert abi.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ GEMM + all-gather in one kernel
+@pytest.mark.parametrize("scheme", ["fp8", "int8", "nvfp4"])
+@pytest.mark.parametrize("m,n,k", [(300, 520, 1024), (96, 16384, 512)])
+def test_pushing_epilogue_on_one_gpu(mods, scheme, m, n, k):
+    """The GEMMs that carry a column-split projection's all-gather, exercised on ONE GPU: the "peers" are two more
+    buffers on the same device.  Every buffer receives this rank's column range bit-equal to the plain GEMM's result, the
+    columns of other ranks stay untouched, and both flag slots read the call's epoch; a second call (next epoch) works."""
+    import ctypes
+    import nvfp4_ops
+    abi, f, fp8_ops = mods
+    x = gen(500 + m, (m, k), 1.0).to(torch.bfloat16).cuda()
+    if scheme == "fp8":
+        info = dev(fp8_weight(501, n, k))
+    elif scheme == "int8":
+        q, s = O.q_int8_sym(gen(502, (n, k), 0.02, torch.float16))
+        info = dev({"weight": q, "tensor_scale": s, "qtype": "int8"})
+    else:
+        info = {kk: (v.cuda() if torch.is_tensor(v) else v) for kk, v in nvfp4_ops.quantize_to_nvfp4(gen(503, (n, k), (1.0 / k) ** 0.5).cuda()).items()}
+    assert nvfp4_ops.can_push(m, k) if scheme == "nvfp4" else f.can_push(m, n, k)
+    plain = fp8_ops.linear_quantized_fused(x, info)
+    n_total, col0 = 3 * n, n                                             # this "rank" owns the middle third of the columns
+    bufs = [torch.full((m, n_total), -7.0, dtype=torch.float16, device="cuda") for _ in range(3)]
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    arr = ctypes.c_void_p * 2
+    peer_out = arr(bufs[1].data_ptr() + col0 * 2, bufs[2].data_ptr() + col0 * 2)
+    for epoch in (5, 6):
+        peer_flag = arr(flags.data_ptr() + 4 * 1, flags.data_ptr() + 4 * 2)
+        with abi.output_into(bufs[0][:, col0:col0 + n]):
+            fp8_ops.linear_quantized_fused(x, info, torch.float16, push=(peer_out, peer_flag, 2, epoch))
+        torch.cuda.synchronize()
+        for b in bufs:
+            bits_equal(b[:, col0:col0 + n], plain, f"{scheme} pushed columns")
+            assert bool((b[:, :col0] == -7.0).all()) and bool((b[:, col0 + n:] == -7.0).all())
+        assert flags[1].item() == epoch and flags[2].item() == epoch and flags[0].item() == 0
+    assert abi.device_status() == 0
