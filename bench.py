@@ -658,6 +658,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    # stdout carries the result line(s) only: whatever libraries write to file descriptor 1 on the way (NCCL prints its
+    # version there) goes to stderr, and print() below reaches the original stdout through sys.stdout
+    sys.stdout.flush()
+    sys.stdout = os.fdopen(os.dup(1), "w", buffering=1)
+    os.dup2(2, 1)
     if args.case == "shape":
         if rank == 0:
             run_shape(args)
