@@ -145,6 +145,16 @@ int32_t rwkvq_gemv_fp8_preamax(const void* x, int32_t x_dtype, const uint8_t* w,
                                void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
                                uint32_t flags, void* ffn_scratch, void* stream);
 
+/* The pair on INT8 weights, up to 8 rows.  INT8 activations carry one scale per ROW, so rwkvq_gemv_int8_relu2 publishes
+ * max(h) per token row and rwkvq_gemv_int8_preamax quantizes every row of h with its own published maximum.
+ * ffn_scratch: 64 bytes (the FP8 pair uses the first 8 of the same block), 8-byte aligned, zeroed once; left zero. */
+int32_t rwkvq_gemv_int8_relu2(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale,
+                              void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                              uint32_t flags, void* ffn_scratch, void* stream);
+int32_t rwkvq_gemv_int8_preamax(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale,
+                                void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
+                                uint32_t flags, void* ffn_scratch, void* stream);
+
 /* The same pair for many rows (prefill): rwkvq_tc_gemm_fp8_relu2 is rwkvq_tc_gemm_fp8 (tiled form, M >= 17) with
  * relu_square and the amax accumulation in its epilogue; rwkvq_actq_fp8_given then makes the codes of h with the
  * published amax -- purely elementwise, no abs-max pass and no grid rendezvous -- writes its own copies amax_out[0]

@@ -466,6 +466,12 @@ def ffn_relu2_fp8(x, key_info, value_info, div=ieee_div):
     return linear_fp8_fused(hid, value_info, div), hid
 
 
+def ffn_relu2_int8(x, key_info, value_info, div=ieee_div):
+    """The same chain on INT8 weights: each projection quantizes its input per row (fused_fp8_gemm.py:785-818)."""
+    hid = relu_square(linear_int8_fused(x, key_info, div))
+    return linear_int8_fused(hid, value_info, div), hid
+
+
 def linear_fp8(x, weight_info, out_dtype=torch.float16):
     """fp8_ops.py:58-86 -- M > 512: fp16 -> bf16, prep_x_fp8, scaled matmul with a
     bf16 result, then the cast to fp16 (the result passes through bf16)."""

@@ -111,7 +111,7 @@ __device__ __forceinline__ void chunk_body(const uint8_t* st, const uint8_t* con
 // and n0+g+8 (values 2, 3) for the tokens 8i+2t and 8i+2t+1.
 template <int QT, int NT, bool RELU2, typename T>
 __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int g, int t, const T (&c)[NT][4], float act_scale,
-                                           const float* xs, float wscale, float& hmax) {
+                                           const float* xs, float wscale, float (&hmax)[2]) {
     // weight scale of this lane's two rows: one per matrix, or one per output row with RWKVQ_FLAG_WSCALE_PER_ROW
     float wlo = wscale, whi = wscale;
     if (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) {
@@ -140,7 +140,8 @@ __device__ __forceinline__ void store_tile(const W8Args& a, int mat, int n0, int
                 const float v = fmaxf(__half2float(y), 0.f);
                 y = __float2half_rn(v * v);
                 const float hv = __half2float(y);
-                hmax = fmaxf(hmax, (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? bf16_round(hv) : hv);
+                if constexpr (QT == QT_FP8) hmax[0] = fmaxf(hmax[0], (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) ? bf16_round(hv) : hv);
+                else hmax[j & 1] = fmaxf(hmax[j & 1], hv);          // INT8 scales its activations per row: tokens 2t and 2t + 1 (NT = 1)
             }
             a.out[mat][(int64_t)m * a.ldo + n] = y;
         }
@@ -272,7 +273,7 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
         }
         out_scale = div_mode_f32(amax, 448.f, a.div_mode);
     } else {
-        quantize_int8_to_smem<DT>(a, mat, xq, xs, sh);
+        quantize_int8_to_smem<DT, FFN == 2>(a, mat, xq, xs, sh);
     }
     __syncthreads();
     w8_mark(a, 3);
@@ -280,13 +281,17 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
         // every thread of this CTA has used the published amax; the last CTA to say so clears it for the next producer
         __threadfence();
         if (atomicAdd(a.ffn_count, 1) == (int)gridDim.x - 1) {
-            *a.ffn_amax = 0.f;
+            if constexpr (QT == QT_FP8) {
+                *a.ffn_amax = 0.f;
+            } else {
+                for (int r = 0; r < 8; ++r) a.ffn_amax[2 + r] = 0.f;
+            }
             __threadfence();
             *a.ffn_count = 0;
         }
     }
 
-    float hmax = 0.f;
+    float hmax[2] = {0.f, 0.f};
     int stage = 0;
     for (int r = 0; r < rounds; ++r) {
         T c[NT][4], c2[NT][4];
@@ -336,16 +341,37 @@ __global__ void __launch_bounds__(kThr, 2) gemv_w8a8_kernel(const W8Args a) {
         }
     }
     cp_async_wait<0>();
-    if constexpr (FFN == 1) {          // one atomic per CTA
-        hmax = warp_max(hmax);
+    if constexpr (FFN == 1 && QT == QT_FP8) {          // one atomic per CTA
+        const float hm = warp_max(hmax[0]);
         __syncthreads();
-        if (lane == 0) sh[warp] = hmax;
+        if (lane == 0) sh[warp] = hm;
         __syncthreads();
         if (threadIdx.x == 0) {
             float b = sh[0];
 #pragma unroll
             for (int i = 1; i < kWarps; ++i) b = fmaxf(b, sh[i]);
             atomic_max_nonneg(a.ffn_amax, b);
+        }
+    }
+    if constexpr (FFN == 1 && QT == QT_INT8) {         // one atomic per CTA and token row
+        float v0 = hmax[0], v1 = hmax[1];               // tokens 2t and 2t + 1: fold the lanes that share t (all g)
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, o));
+            v1 = fmaxf(v1, __shfl_xor_sync(0xffffffffu, v1, o));
+        }
+        __syncthreads();                                // the reduction buffer is free
+        float* rowmax = reinterpret_cast<float*>(red);  // [kWarps][8]
+        if (lane < 4) {
+            rowmax[warp * 8 + 2 * lane] = v0;
+            rowmax[warp * 8 + 2 * lane + 1] = v1;
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < a.M && threadIdx.x < 8) {
+            float b = rowmax[threadIdx.x];
+#pragma unroll
+            for (int i = 1; i < kWarps; ++i) b = fmaxf(b, rowmax[i * 8 + threadIdx.x]);
+            if (b > 0.f) atomic_max_nonneg(a.ffn_amax + 2 + threadIdx.x, b);
         }
     }
     w8_mark(a, 4);
@@ -429,7 +455,7 @@ static int32_t dispatch_s(const W8Args& a, cudaStream_t st) {
 
 template <int QT, int DT, bool PRE>
 static int32_t dispatch_mt(const W8Args& a, cudaStream_t st) {
-    if constexpr (QT == QT_FP8 && !PRE) {       // the FFN pair: up to 8 rows
+    if constexpr (!PRE) {                       // the FFN pair: up to 8 rows
         if (a.flags & (RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN)) {
             RWKVQ_REQUIRE(a.M <= 8 && a.nmat == 1, RWKVQ_E_SHAPE, "gemv_fp8 relu2 / preamax: at most 8 rows, got %d", a.M);
             return (a.flags & RWKVQ_FLAG_RELU2) ? dispatch_s<QT, DT, 1, PRE, 1>(a, st) : dispatch_s<QT, DT, 1, PRE, 2>(a, st);
@@ -563,6 +589,36 @@ int32_t rwkvq_gemv_int8(const void* x, int32_t x_dtype, const int8_t* w, int64_t
     a.div_mode = div_mode; a.flags = flags & ~(RWKVQ_FLAG_RELU2 | RWKVQ_FLAG_AMAX_GIVEN);
     RWKVQ_REQUIRE(acc_out == nullptr || ldacc >= N, RWKVQ_E_SHAPE, "gemv_int8: ldacc < N");
     return run_fused<QT_INT8>(a, x_dtype, (cudaStream_t)stream, "gemv_int8");
+}
+
+/* The FFN pair on INT8 weights (up to 8 rows).  INT8 activations carry one scale per ROW, so the key projection
+ * publishes the maximum of fp16(max(y, 0)^2) per token row and the value projection quantizes every row with its own
+ * published maximum.  ffn_scratch: 64 bytes owned by the caller (the FP8 pair uses the first 8 of the same block),
+ * zeroed once; the pair leaves it zero.  Results equal projection -> relu_square -> projection bit for bit. */
+int32_t rwkvq_gemv_int8_relu2(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale, void* out_f16,
+                              int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags,
+                              void* ffn_scratch, void* stream) {
+    RWKVQ_REQUIRE(ffn_scratch != nullptr && ((uintptr_t)ffn_scratch & 7) == 0, RWKVQ_E_BADARG, "gemv_int8_relu2: ffn_scratch must be 64 bytes, 8-byte aligned");
+    W8Args a{};
+    a.x[0] = x; a.w[0] = (const uint8_t*)w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
+    a.div_mode = div_mode; a.flags = (flags & ~RWKVQ_FLAG_AMAX_GIVEN) | RWKVQ_FLAG_RELU2;
+    a.ffn_amax = reinterpret_cast<float*>(ffn_scratch);
+    a.ffn_count = reinterpret_cast<int*>(ffn_scratch) + 1;
+    return run_fused<QT_INT8>(a, x_dtype, (cudaStream_t)stream, "gemv_int8_relu2");
+}
+
+int32_t rwkvq_gemv_int8_preamax(const void* x, int32_t x_dtype, const int8_t* w, int64_t ldw, const float* w_scale, void* out_f16,
+                                int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode, uint32_t flags,
+                                void* ffn_scratch, void* stream) {
+    RWKVQ_REQUIRE(ffn_scratch != nullptr && ((uintptr_t)ffn_scratch & 7) == 0, RWKVQ_E_BADARG, "gemv_int8_preamax: ffn_scratch must be 64 bytes, 8-byte aligned");
+    W8Args a{};
+    a.x[0] = x; a.w[0] = (const uint8_t*)w; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldw = ldw; a.ldo = ldo;
+    a.div_mode = div_mode; a.flags = (flags & ~RWKVQ_FLAG_RELU2) | RWKVQ_FLAG_AMAX_GIVEN;
+    a.ffn_amax = reinterpret_cast<float*>(ffn_scratch);
+    a.ffn_count = reinterpret_cast<int*>(ffn_scratch) + 1;
+    return run_fused<QT_INT8>(a, x_dtype, (cudaStream_t)stream, "gemv_int8_preamax");
 }
 
 int32_t rwkvq_gemv_int8_rkv(const void* xr, const void* xk, const void* xv, int32_t x_dtype, const int8_t* wr,

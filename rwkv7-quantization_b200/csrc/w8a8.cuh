@@ -309,10 +309,38 @@ __device__ __forceinline__ uint2 int8_vec_codes(const uint4& v, float s) {
                       pack_s8x4(__float2int_rz(f2.x * s), __float2int_rz(f2.y * s), __float2int_rz(f3.x * s), __float2int_rz(f3.y * s)));
 }
 
-template <int DT>
+// GIVEN: the rows' maxima come from a.ffn_amax[2 + r] (published by the kernel that produced x, the FFN key projection
+// with relu^2 in its epilogue): no abs-max pass; the CTA's threads walk all rows' vectors, eight loads in flight each.
+template <int DT, bool GIVEN = false>
 __device__ void quantize_int8_to_smem(const W8Args& a, int mat, uint8_t* xq, float* xs, float* sh) {
     const char* x = reinterpret_cast<const char*>(a.x[mat]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if constexpr (GIVEN) {
+        const int kv = a.K >> 3, nvec = a.M * kv;
+        const uint32_t inv_kv = 0xFFFFFFFFu / (uint32_t)kv + 1u;          // row of a flat vector index without a division
+        if ((int)threadIdx.x < a.M) {
+            const float m = fmaxf(__ldcg(a.ffn_amax + 2 + threadIdx.x), 1e-12f);
+            xs[threadIdx.x] = div_mode_f32(m, 127.f, a.div_mode);
+            sh[threadIdx.x] = div_mode_f32(127.f, m, a.div_mode);
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int i0 = threadIdx.x; i0 < nvec; i0 += 8 * kThr) {
+            uint4 v[8];
+            int rr[8], cc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int idx = min(i0 + j * kThr, nvec - 1);
+                rr[j] = (int)__umulhi((uint32_t)idx, inv_kv);
+                cc[j] = idx - rr[j] * kv;
+                v[j] = ldg_l2_16(x + ((int64_t)rr[j] * a.ldx + (int64_t)cc[j] * 8) * 2);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (i0 + j * kThr < nvec) *reinterpret_cast<uint2*>(xq + (size_t)rr[j] * a.pitch + (size_t)cc[j] * 8) = int8_vec_codes<DT>(v[j], sh[rr[j]]);
+        }
+        return;
+    }
     if (a.M <= 4 && a.K > 2 * kThr * 8 && a.K <= 8 * kThr * 8) {
         // long rows: the whole CTA works on one row at a time and keeps it in registers between amax and codes
         // (one read; measured quicker than two passes above K = 4096, slower below because of its code size)

@@ -490,11 +490,12 @@ _ffn_scratch: dict = {}
 
 
 def ffn_scratch(device) -> torch.Tensor:
-    """8 zeroed bytes per (device, stream) through which the key projection hands max|relu^2| to the value projection."""
+    """64 zeroed bytes per (device, stream) through which the key projection hands max|relu^2| (FP8: one value; INT8: one
+    per token row) to the value projection."""
     key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
     sc = _ffn_scratch.get(key)
     if sc is None:
-        sc = _ffn_scratch[key] = torch.zeros(2, dtype=torch.int32, device=device)
+        sc = _ffn_scratch[key] = torch.zeros(16, dtype=torch.int32, device=device)
     return sc
 
 
@@ -554,6 +555,35 @@ def ffn_relu2_fp8(x, key_info, value_info, out_dtype=torch.float16, return_hidde
         hid = linear_quantized_fused(x2, {"weight": wk, "tensor_scale": sk, "qtype": "fp8"})
         hid = (hid.float().clamp_(min=0.0) ** 2).to(torch.float16)       # relu_square: fp16(max(y, 0)^2), fp32 arithmetic
         out = linear_quantized_fused(hid, {"weight": wv, "tensor_scale": sv, "qtype": "fp8"})
+    out = _finish(out.reshape(m, n), x.shape[:-1], n, out_dtype)
+    return (out, hid.reshape(*x.shape[:-1], f_dim)) if return_hidden else out
+
+
+def ffn_relu2_int8(x, key_info, value_info, out_dtype=torch.float16, return_hidden=False):
+    """ffn_relu2_fp8 for INT8 weights.  Up to 8 rows: two launches, relu_square in the key projection's epilogue, which
+    publishes the maximum of its result per token row (INT8 activations are scaled per row), and a value projection
+    that quantizes with those maxima instead of reducing the hidden activations again.  More rows: the three steps.
+    Results equal the three-step chain bit for bit."""
+    wk, sk = key_info["weight"], key_info["tensor_scale"]
+    wv, sv = value_info["weight"], value_info["tensor_scale"]
+    x2 = _rows16(x)
+    m, k = x2.shape
+    f_dim, n = wk.shape[0], wv.shape[0]
+    if (ROUTE == "auto" and 0 < m <= 8 and _gemv_fits(m, k, fp8=False) and _gemv_fits(m, f_dim, fp8=False)
+            and not _codes_gemv_fits(m, k) and not _codes_gemv_fits(m, f_dim)):
+        hid = torch.empty((m, f_dim), dtype=torch.float16, device=x2.device)
+        out = abi.new_out(m, n, x2.device)
+        sc = ffn_scratch(x2.device)
+        st = abi.stream_ptr()
+        abi.call("rwkvq_gemv_int8_relu2", x2.data_ptr(), abi.dtype_code(x2), wk.data_ptr(), wk.stride(0), sk.data_ptr(),
+                 hid.data_ptr(), f_dim, m, f_dim, k, x2.stride(0) if m > 1 else k, abi.DEFAULT_DIV, 0, sc.data_ptr(), st)
+        abi.call("rwkvq_gemv_int8_preamax", hid.data_ptr(), abi.F16, wv.data_ptr(), wv.stride(0), sv.data_ptr(),
+                 out.data_ptr(), out.stride(0), m, n, f_dim, f_dim, abi.DEFAULT_DIV, 0, sc.data_ptr(), st)
+        abi.after_call()
+    else:
+        hid = linear_int8_fused(x2, key_info)
+        hid = (hid.float().clamp_(min=0.0) ** 2).to(torch.float16)       # relu_square: fp16(max(y, 0)^2), fp32 arithmetic
+        out = linear_int8_fused(hid, value_info)
     out = _finish(out.reshape(m, n), x.shape[:-1], n, out_dtype)
     return (out, hid.reshape(*x.shape[:-1], f_dim)) if return_hidden else out
 

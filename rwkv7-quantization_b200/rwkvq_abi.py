@@ -98,6 +98,8 @@ SIGNATURES = {
     "rwkvq_actq_fp8_given": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _i32, _u32, _p],
     "rwkvq_gemv_fp8_relu2": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],
     "rwkvq_gemv_fp8_preamax": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],
+    "rwkvq_gemv_int8_relu2": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],
+    "rwkvq_gemv_int8_preamax": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],
     "rwkvq_enable_peer_access": [_i32],
     "rwkvq_peer_alloc": [_i64, _p, _p],
     "rwkvq_peer_open": [_p, _p],

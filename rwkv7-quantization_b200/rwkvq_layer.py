@@ -112,16 +112,21 @@ class DecodeLayer:
         return self.outs[3][0]
 
     def ffn(self, x):
-        """value( relu_square( key(x) ) ) in two launches (FP8): relu_square runs in the key projection's epilogue, the
-        value projection quantizes with the amax that epilogue publishes.  Returns (ffn output, relu^2 hidden)."""
-        if self.int8:
-            raise NotImplementedError("the fused FFN pair is built for FP8 weights")
+        """value( relu_square( key(x) ) ) in two launches: relu_square runs in the key projection's epilogue, the value
+        projection quantizes with the maximum (FP8: of the block; INT8: per token row) that epilogue publishes.
+        Returns (ffn output, relu^2 hidden)."""
         dk, dv = self._descs[2], self._descs[3]
         self._bind(dk, 0, x, self._k[2])
         if self._ffn_scratch is None:
-            self._ffn_scratch = torch.zeros(2, dtype=torch.int32, device=self.device)
+            self._ffn_scratch = torch.zeros(16, dtype=torch.int32, device=self.device)
         st, sc = torch.cuda.current_stream().cuda_stream, self._ffn_scratch.data_ptr()
         hid, out = self.outs[2][0], self.outs[3][0]
+        if self.int8:
+            abi.call("rwkvq_gemv_int8_relu2", dk.x[0], dk.x_dtype, dk.w[0], dk.ldw, dk.w_scale[0], hid.data_ptr(), dk.ldo, dk.M, dk.N, dk.K,
+                     dk.ldx, dk.div_mode, dk.flags, sc, st)
+            abi.call("rwkvq_gemv_int8_preamax", hid.data_ptr(), abi.F16, dv.w[0], dv.ldw, dv.w_scale[0], out.data_ptr(), dv.ldo, dv.M, dv.N,
+                     dv.K, dv.ldx, dv.div_mode, dv.flags, sc, st)
+            return out, hid
         abi.call("rwkvq_gemv_fp8_relu2", dk.x[0], dk.x_dtype, dk.w[0], dk.ldw, dk.w_scale[0], hid.data_ptr(), dk.ldo, dk.M, dk.N, dk.K,
                  dk.ldx, dk.div_mode, dk.flags, sc, st)
         abi.call("rwkvq_gemv_fp8_preamax", hid.data_ptr(), abi.F16, dv.w[0], dv.ldw, dv.w_scale[0], out.data_ptr(), dv.ldo, dv.M, dv.N,

@@ -382,6 +382,56 @@ def test_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
         bits_equal(out2.reshape(out.shape), out, "DecodeLayer.ffn")
 
 
+@pytest.mark.parametrize("m,dt", [(1, torch.bfloat16), (2, torch.float16), (3, torch.bfloat16), (5, torch.float16), (8, torch.bfloat16),
+                                  (8, torch.float16), (20, torch.bfloat16)])
+def test_int8_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
+    """The pair on INT8 weights (per-row maxima published by the key projection): bit-equal to the three steps run
+    separately and to the oracle's chain; two launches up to 8 rows; the scratch is left clean; rows whose hidden
+    activations are all zero (negative key results only) keep the quantizer's floor."""
+    abi, f, _ = mods
+    c, ff = 768, 3072
+    qk, sk = O.q_int8_sym(gen(160, (ff, c), 0.02, torch.float16))
+    qv, sv = O.q_int8_sym(gen(161, (c, ff), 0.02, torch.float16))
+    key, val = {"weight": qk, "tensor_scale": sk, "qtype": "int8"}, {"weight": qv, "tensor_scale": sv, "qtype": "int8"}
+    dk, dv = dev(key), dev(val)
+    for rep in range(3):
+        x = gen(162 + m + rep, (m, c), 1.0 + rep).to(dt)
+        if rep == 2:
+            x[m // 2] = 0                                        # a row of zeros: relu^2 of it is zero, its published maximum stays 0
+        before = abi.launch_count()
+        out, hid = f.ffn_relu2_int8(x.cuda(), dk, dv, return_hidden=True)
+        launches = abi.launch_count() - before
+        y = f.linear_int8_fused(x.cuda(), dk)
+        h = (y.float().clamp(min=0) ** 2).half()
+        bits_equal(hid, h, "hidden")
+        bits_equal(out, f.linear_int8_fused(h, dv), "ffn output")
+        want, want_h = O.ffn_relu2_int8(x, key, val, lib_div(abi))
+        bits_equal(hid, want_h, "hidden against the oracle")
+        bits_equal(out, want, "ffn output against the oracle")
+        if m <= 8:
+            assert launches == 2
+            assert int(f.ffn_scratch("cuda").abs().sum().item()) == 0
+    if m <= 8:
+        from rwkvq_layer import DecodeLayer
+        qs, ss = O.q_int8_sym(gen(163, (c, c), 0.02, torch.float16))
+        sq = dev({"weight": qs, "tensor_scale": ss, "qtype": "int8"})
+        layer = DecodeLayer(sq, sq, sq, sq, dk, dv, rows=m, x_dtype=dt)
+        xg = x.cuda()
+        out2, hid2 = layer.ffn(xg)
+        bits_equal(out2.reshape(out.shape), out, "DecodeLayer.ffn")
+        graph = torch.cuda.CUDAGraph()                          # and under replay: the scratch returns to zero every time
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            layer.ffn(xg)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                out3, _ = layer.ffn(xg)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        bits_equal(out3.reshape(out.shape), out, "DecodeLayer.ffn under graph replay")
+
+
 # ------------------------------------------------------------------------------------------------ CTA-pair GEMM (tcgen05 cta_group::2)
 @pytest.mark.parametrize("scheme", ["fp8", "int8"])
 @pytest.mark.parametrize("m,n,k", [(4096, 2560, 256), (4100, 2600, 272)])
