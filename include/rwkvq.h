@@ -406,6 +406,9 @@ int32_t rwkvq_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, cons
 int64_t rwkvq_nvfp4_blocked_scale_bytes(int64_t rows, int64_t K);
 int32_t rwkvq_nvfp4_pack_scales(const uint8_t* block_scales, int64_t lds, int64_t rows, int64_t K, uint8_t* blocked,
                                 void* stream);
+/* 1 if rwkvq_tc_gemm_nvfp4 runs these sizes on the cluster split-K kernel (up to 256 tokens against few row tiles:
+ * weights as the 128-row operand, K split across a thread-block cluster), 0 for the tiled form */
+int32_t rwkvq_tc_gemm_nvfp4_cluster_route(int64_t M, int64_t N, int64_t K);
 int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts,
                             const uint8_t* w_codes, int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale,
                             void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,

@@ -56,6 +56,8 @@ struct TcArgs {
     unsigned long long* trace; // optional [grid][16] timestamps of role milestones (profiling aid), else null
     unsigned long long wait_ns; // wall-time limit of every mbarrier wait
     float* ffn_amax;            // RWKVQ_FLAG_RELU2 (GEMM mode, FP8): maximum of the relu^2 results, atomic max
+    const uint8_t* sfa;         // NVFP4 (cluster split-K kernel only): blocked scales of the activation codes ...
+    const uint8_t* sfw;         // ... and of the weight codes (rwkvq_nvfp4_pack_scales order)
     TcPush push;                // GEMM mode: also store the result into the peers' buffers and signal them (n = 0: off)
     int64_t ldx, ldo, ldacc;
     int M, N, K, nmat;
@@ -813,6 +815,34 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
     if (c.fused) return c.x_dtype == RWKVQ_F16 ? RWKVQ_TC(KIND_I8, true, true, RWKVQ_F16) : RWKVQ_TC(KIND_I8, true, true, RWKVQ_BF16);
     return swap ? RWKVQ_TC(KIND_I8, true, false, RWKVQ_BF16) : RWKVQ_TC(KIND_I8, false, false, RWKVQ_BF16);
 #undef RWKVQ_TC
+}
+
+// NVFP4 on the cluster split-K kernel.  The tiled NVFP4 GEMM (gemm_tc_nvfp4.cu) has no K split: with few tokens a
+// matrix gives it at most N / 128 tiles (32 for N = 4096), each streaming all of K through one SM.
+bool tcs_nvfp4_eligible(int64_t M, int64_t N, int64_t K) {
+    const char* env = std::getenv("RWKVQ_TCS_NF4_MIN_C");        // read per call: a test switches routes in one process
+    const int min_c = env ? std::atoi(env) : 0;
+    static const int on = std::getenv("RWKVQ_TCS") ? std::atoi(std::getenv("RWKVQ_TCS")) : 1;
+    if (!on || M < 1 || M > kTcsMaxM || K % 256 || K < 2048) return false;
+    // measured on the 7.2B shapes: with 128 row tiles (N = 16384) and a cluster of two the tiled form is as fast (16
+    // tokens) or faster (64); from 65 tokens on a cluster of two already wins (FFN value, 256 tokens: 57 -> 45 us)
+    return tcs_cluster_size(M, N, K / 2) >= (min_c > 0 ? min_c : (M <= 64 ? 4 : 2));
+}
+
+int32_t run_tcs_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts, const uint8_t* w_codes,
+                      int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale, __half* out, int64_t ldo, int64_t M, int64_t N,
+                      int64_t K, int* status, cudaStream_t st, const char* who) {
+    TcArgs a{};
+    a.a_scale[0] = a_pts; a.amax_is_amax = 0; a.ws[0] = w_tscale; a.out[0] = out;
+    a.sfa = a_scales_blocked; a.sfw = w_scales_blocked;
+    a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = 0;
+    a.kchunks = (int)(K / 256);               // ring stages of 128 bytes of codes = 256 values of k
+    a.trace = g_trace;
+    a.wait_ns = wait_limit_ns();
+    a.status = status;
+    TcCall c{};
+    c.kind = KIND_NF4; c.w[0] = w_codes; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda;
+    return run_tcs(a, c, st, who);
 }
 
 }  // namespace rwkvq

@@ -30,12 +30,9 @@ namespace rwkvq {
 using namespace tc;
 
 constexpr int kNfThreads = 192;
-constexpr int kNfTileM = 128;
 constexpr int kNfMaxStages = 8;
 constexpr uint32_t kNfRowBytes = 128;                       // packed codes of one row per stage (256 values of k)
 constexpr uint32_t kNfABytes = kNfTileM * kNfRowBytes;      // 16 KiB
-constexpr uint32_t kNfSfChunk = 512;                        // scales of 128 rows x 64 k
-constexpr uint32_t kNfSfStage = 4 * kNfSfChunk;             // scales of 128 rows x one stage
 constexpr uint32_t kNfSfCol = 256;                          // first tensor-memory column of the scale factors
 constexpr uint32_t kNfTmemCols = 512;
 constexpr size_t kNfSmemBudget = 225 * 1024;
@@ -68,29 +65,6 @@ struct NfShared {
 __device__ __forceinline__ void nf_abort(NfShared& s, const NfArgs& a) {
     s.abort_flag = 1;
     if (a.status) atomicExch(a.status, RWKVQ_E_TIMEOUT);
-}
-
-// K-major, no swizzle: 8-row x 16-byte core matrices, 128 bytes apart along the rows (32 rows x 16 bytes, dense)
-__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)(128 >> 4) << 32;       // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                // descriptor version (sm_100)
-    return d;
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_dst, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(desc) : "memory");
-}
-__device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t tsfa,
-                                             uint32_t tsfb, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb) : "memory");
-}
-// block-scaled instruction descriptor: A and B e2m1 (format 1), both K-major, e4m3 scale factors, M = 128
-__host__ __device__ inline uint32_t nvfp4_idesc(int n) {
-    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (0u << 23) | ((uint32_t)(kNfTileM >> 4) << 24);
 }
 
 template <int BN, bool PUSH = false>
@@ -133,6 +107,21 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
     if (warp == 0) {
         // ============================== producer ==============================
         if (lane == 0) {
+            // first pass over the ring: the weights and their scales do not depend on the kernels in front, so they are
+            // requested BEFORE the dependency wait of programmatic dependent launch
+            uint32_t npre = 0;
+            for (; npre < (uint32_t)a.stages; ++npre) {
+                const int t = blockIdx.x + (int)(npre / (uint32_t)a.kstages) * (int)gridDim.x, kc = (int)(npre % (uint32_t)a.kstages);
+                if (t >= tiles) break;
+                const int nt = t / a.mtiles;
+                uint8_t* dst = ring + (size_t)npre * kStage;
+                mbar_expect_tx(&s.full[npre], kStage);
+                tma_load_2d(dst + kNfABytes, &maps.w, kc * (int)kNfRowBytes, nt * BN, &s.full[npre]);
+                uint8_t* sf = dst + kNfABytes + kBBytes;
+#pragma unroll
+                for (int h = 0; h < NH; ++h)
+                    bulk_load_1d(sf + kNfSfStage * (1 + h), a.sfw + ((int64_t)(nt * NH + h) * k64 + kc * 4) * kNfSfChunk, kNfSfStage, &s.full[npre]);
+            }
             griddep_wait();                     // activation codes and scales come from the previous kernels
             uint32_t n = 0;
             bool ok = true;
@@ -140,17 +129,19 @@ __global__ void __launch_bounds__(kNfThreads, 1) gemm_tc_nvfp4_kernel(const __gr
                 const int mt = t % a.mtiles, nt = t / a.mtiles;
                 for (int kc = 0; kc < a.kstages; ++kc, ++n) {
                     const int st = n % a.stages;
-                    if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { nf_abort(s, a); ok = false; break; }
                     uint8_t* dst = ring + (size_t)st * kStage;
-                    mbar_expect_tx(&s.full[st], kStage);
-                    tma_load_2d(dst, &maps.a, kc * (int)kNfRowBytes, mt * kNfTileM, &s.full[st]);
-                    tma_load_2d(dst + kNfABytes, &maps.w, kc * (int)kNfRowBytes, nt * BN, &s.full[st]);
                     uint8_t* sf = dst + kNfABytes + kBBytes;
-                    bulk_load_1d(sf, a.sfa + ((int64_t)mt * k64 + kc * 4) * kNfSfChunk, kNfSfStage, &s.full[st]);
+                    if (n >= npre) {
+                        if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { nf_abort(s, a); ok = false; break; }
+                        mbar_expect_tx(&s.full[st], kStage);
+                        tma_load_2d(dst + kNfABytes, &maps.w, kc * (int)kNfRowBytes, nt * BN, &s.full[st]);
 #pragma unroll
-                    for (int h = 0; h < NH; ++h)
-                        bulk_load_1d(sf + kNfSfStage * (1 + h), a.sfw + ((int64_t)(nt * NH + h) * k64 + kc * 4) * kNfSfChunk,
-                                     kNfSfStage, &s.full[st]);
+                        for (int h = 0; h < NH; ++h)
+                            bulk_load_1d(sf + kNfSfStage * (1 + h), a.sfw + ((int64_t)(nt * NH + h) * k64 + kc * 4) * kNfSfChunk,
+                                         kNfSfStage, &s.full[st]);
+                    }
+                    tma_load_2d(dst, &maps.a, kc * (int)kNfRowBytes, mt * kNfTileM, &s.full[st]);
+                    bulk_load_1d(sf, a.sfa + ((int64_t)mt * k64 + kc * 4) * kNfSfChunk, kNfSfStage, &s.full[st]);
                 }
             }
             if (!ok) {   // give copies already in flight a bounded time to land before the CTA's memory is released
@@ -361,6 +352,9 @@ static int32_t run_tc_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* 
     RWKVQ_REQUIRE(M < (int64_t(1) << 30) && N < (int64_t(1) << 30) && K < (int64_t(1) << 30), RWKVQ_E_SHAPE, "%s: size too large", who);
     RWKVQ_REQUIRE(workspace == nullptr || (workspace_bytes >= kWsHeaderBytes && aligned16(workspace)), RWKVQ_E_WORKSPACE,
                   "%s: the workspace needs at least %lld bytes, 16-byte aligned", who, (long long)kWsHeaderBytes);
+    if (push == nullptr && tcs_nvfp4_eligible(M, N, K))         // few tokens: K split across a thread-block cluster
+        return run_tcs_nvfp4(a_codes, lda, a_scales_blocked, a_pts, w_codes, ldw, w_scales_blocked, w_tscale, (__half*)out_f16, ldo, M, N, K,
+                             workspace ? reinterpret_cast<int*>(workspace) + kWsCounterInts : nullptr, (cudaStream_t)stream, who);
     const char* bn_env = std::getenv("RWKVQ_NF4_BN");          // read per call: a test switches tiles in one process
     const int forced_bn = bn_env ? std::atoi(bn_env) : 0;
     // 256-row weight tiles halve the activation re-reads per flop but keep one accumulator; they pay once there are
@@ -388,6 +382,9 @@ static int32_t run_tc_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* 
         return bn == 128 ? launch_nvfp4<128, true>(maps, a, grid, (cudaStream_t)stream, who) : launch_nvfp4<256, true>(maps, a, grid, (cudaStream_t)stream, who);
     return bn == 128 ? launch_nvfp4<128>(maps, a, grid, (cudaStream_t)stream, who) : launch_nvfp4<256>(maps, a, grid, (cudaStream_t)stream, who);
 }
+
+/* 1 if rwkvq_tc_gemm_nvfp4 runs these sizes on the cluster split-K kernel (few tokens), 0 for the tiled form */
+int32_t rwkvq_tc_gemm_nvfp4_cluster_route(int64_t M, int64_t N, int64_t K) { return tcs_nvfp4_eligible(M, N, K) ? 1 : 0; }
 
 int32_t rwkvq_tc_gemm_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts,
                             const uint8_t* w_codes, int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale,

@@ -95,11 +95,14 @@ __device__ __forceinline__ void tcs_abort(TcsShared& s, const TcArgs& a) {
 // three-in-one launch and three single launches give the same bits.
 template <int KIND>
 __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_constant__ TcMaps maps, const TcArgs a) {
-    using T = typename Acc<KIND == KIND_F8 ? QT_FP8 : QT_INT8>::T;
+    using T = typename Acc<KIND == KIND_I8 ? QT_INT8 : QT_FP8>::T;
+    constexpr uint32_t kSfBytes = KIND == KIND_NF4 ? 2 * kNfSfStage : 0;     // NVFP4: block scales of both tiles ride in the stage
+    constexpr uint32_t kSfCol = 128;                                         // NVFP4: first tensor-memory column of the scale factors
     extern __shared__ uint8_t smem_raw[];
     __shared__ TcsShared s;
     uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t stage_bytes = kABytes + (uint32_t)a.NB * kChunk;
+    const uint32_t stage_bytes = kABytes + (uint32_t)a.NB * kChunk + kSfBytes;
+    const uint32_t sf_off = kABytes + (uint32_t)a.NB * kChunk;
     T* rxbuf = reinterpret_cast<T*>(ring + (size_t)a.stages * stage_bytes);        // [C][Mt][R]: partial sums per source CTA, token, row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int C = a.qtiles, R = kTileP / C;
@@ -109,7 +112,7 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
     const int m0 = (cid / a.ptiles) * a.NB, Mt = min(a.NB, a.M - m0);       // this cluster's tokens
     const int kc0 = a.kchunks * rank / C, kc1 = a.kchunks * (rank + 1) / C;
     const int nk = kc1 - kc0, total = a.nmat * nk;          // ring units of this CTA: matrix-major
-    const uint32_t need_cols = (uint32_t)(a.nmat * a.acc_stride);
+    const uint32_t need_cols = KIND == KIND_NF4 ? 256u : (uint32_t)(a.nmat * a.acc_stride);     // NVFP4: accumulator, then two sets of scale columns
     const uint32_t tmem_cols = need_cols <= 32 ? 32u : (need_cols <= 64 ? 64u : (need_cols <= 128 ? 128u : (need_cols <= 256 ? 256u : 512u)));
     const volatile int* abort_flag = &s.abort_flag;
 
@@ -143,10 +146,13 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
         // ============================== TMA producer ==============================
         if (lane == 0) {
             const int npre = min(total, a.stages);
+            const int64_t k64 = (int64_t)a.kchunks * 4;          // NVFP4: 512-byte scale chunks (128 rows x 64 k) per row tile
             for (int n = 0; n < npre; ++n) {           // weights first: they do not depend on the previous kernel
                 const int mat = n / nk, kc = kc0 + (n - mat * nk);
                 mbar_expect_tx(&s.full[n], stage_bytes);
                 tma_load_2d(ring + (size_t)n * stage_bytes, &maps.w[mat], kc * kChunk, prow, &s.full[n]);
+                if constexpr (KIND == KIND_NF4)
+                    bulk_load_1d(ring + (size_t)n * stage_bytes + sf_off, a.sfw + ((int64_t)(prow / kTileP) * k64 + kc * 4) * kNfSfChunk, kNfSfStage, &s.full[n]);
             }
             tc_mark(a, 2);
             griddep_wait();                            // the activation codes are written by the previous kernel
@@ -159,15 +165,19 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
                     if (!mbar_wait(&s.empty[st], ((n / a.stages) & 1) ^ 1, abort_flag, a.wait_ns)) { tcs_abort(s, a); break; }
                     mbar_expect_tx(&s.full[st], stage_bytes);
                     tma_load_2d(dst, &maps.w[mat], kc * kChunk, prow, &s.full[st]);
+                    if constexpr (KIND == KIND_NF4)
+                        bulk_load_1d(dst + sf_off, a.sfw + ((int64_t)(prow / kTileP) * k64 + kc * 4) * kNfSfChunk, kNfSfStage, &s.full[st]);
                 }
                 tma_load_2d(dst + kABytes, &maps.a[mat], kc * kChunk, m0, &s.full[st]);
+                if constexpr (KIND == KIND_NF4)
+                    bulk_load_1d(dst + sf_off + kNfSfStage, a.sfa + ((int64_t)(m0 / kNfTileM) * k64 + kc * 4) * kNfSfChunk, kNfSfStage, &s.full[st]);
             }
             tc_mark(a, 10);
         }
     } else if (warp == 1) {
         // ============================== MMA issuer ==============================
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(KIND, kTileP, a.NB);
+            const uint32_t idesc = KIND == KIND_NF4 ? nvfp4_idesc(a.NB) : umma_idesc(KIND, kTileP, a.NB);
             for (int n = 0; n < total; ++n) {
                 const int st = n % a.stages;
                 const int mat = n / nk, i = n - mat * nk;
@@ -176,9 +186,24 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
                 const uint32_t sa = smem_u32(ring + (size_t)st * stage_bytes);
                 const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sa + kABytes);
                 const uint32_t d = tmem_base + (uint32_t)(mat * a.acc_stride);
+                if constexpr (KIND == KIND_NF4) {
+                    // scale factors of this stage (weights = the 128-row operand, tokens the other): two alternating
+                    // column sets, so a copy never lands in columns the previous stage's MMAs may still be reading
+                    const uint32_t tsfa = tmem_base + kSfCol + (uint32_t)(n & 1) * 64, tsfb = tsfa + 16;
+                    const uint32_t ssf = sa + sf_off;
 #pragma unroll
-                for (int k = 0; k < kChunk / 32; ++k)
-                    tc_mma<KIND>(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k) {
+                        tc_cp_sf(tsfa + k * 4, sf_desc(ssf + k * kNfSfChunk));
+                        tc_cp_sf(tsfb + k * 4, sf_desc(ssf + kNfSfStage + k * kNfSfChunk));
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tc_mma_nvfp4(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, tsfa + k * 4, tsfb + k * 4, (i > 0 || k > 0) ? 1u : 0u);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < kChunk / 32; ++k)
+                        tc_mma<KIND>(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
                 tc_commit(&s.empty[st]);
                 if (i == nk - 1) tc_commit(&s.tfull[mat]);
                 if (n == 0) tc_mark(a, 5);
@@ -201,23 +226,26 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
         const uint32_t remote = tcs_mapa(smem_u32(rxbuf), owner) + (uint32_t)(((size_t)rank * Mt * R + lr) * 4);
         const uint32_t remote_rx = tcs_mapa(smem_u32(&s.rx), owner);
         // what the final pass needs from global memory is fetched now, not behind the exchange: a thread of the final
-        // pass keeps ONE weight row (R divides 128) and walks the tokens
-        const int my_c = et % R, my_m0 = et / R, m_step = 128 / R;
-        const int my_row = prow + rank * R + my_c;
+        // pass keeps EIGHT consecutive weight rows (R is a multiple of 16) and walks the tokens -- two 16-byte loads per
+        // contribution, one 16-byte store per token (one row per thread and 2-byte stores took 9.5 us at 256 tokens)
+        const int gpr = R >> 3, my_cg = et % gpr, my_m0 = et / gpr, m_step = 128 / gpr;
+        const int my_row = prow + rank * R + my_cg * 8;
         const bool per_row = (a.flags & RWKVQ_FLAG_WSCALE_PER_ROW) != 0;
-        float wrow[3], act_scale[3];
+        float act_scale[3];
         for (int i = 0; i < a.nmat; ++i) {
-            wrow[i] = __ldg(a.ws[i] + (per_row ? min(my_row, a.N - 1) : 0));
             act_scale[i] = 0.f;
-            if constexpr (KIND == KIND_F8) {
+            if constexpr (KIND != KIND_I8) {
                 const float v = __ldg(a.a_scale[i]);
                 act_scale[i] = a.amax_is_amax ? div_mode_f32(fmaxf(v, 1e-12f), 448.f, a.div_mode) : v;
             } else {
                 if (et < Mt) s.row_scale[i][et] = __ldg(a.a_scale[i] + m0 + et);      // read again only behind the named barrier below
             }
         }
-        if constexpr (KIND != KIND_F8) named_bar_sync(1, 128);
+        if constexpr (KIND == KIND_I8) named_bar_sync(1, 128);
         for (int mat = 0; mat < a.nmat; ++mat) {
+            float wrow[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wrow[j] = __ldg(a.ws[mat] + (per_row ? min(my_row + j, a.N - 1) : 0));
             bool have = mbar_wait(&s.tfull[mat], 0, abort_flag, a.wait_ns);
             if (!have) tcs_abort(s, a);
             have = __all_sync(0xffffffffu, have);       // the tensor-memory loads below are warp-wide
@@ -255,23 +283,53 @@ __global__ void __launch_bounds__(kTcsThreads, 2) gemm_tcs_kernel(const __grid_c
             if (!got) tcs_abort(s, a);
             if (et == 0 && mat == a.nmat - 1) tc_mark(a, 9);
             if (got && !*abort_flag && my_row < a.N) {
+                const bool vec = (a.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(a.out[mat]) & 15) == 0 && my_row + 8 <= a.N;
                 for (int m = my_m0; m < Mt; m += m_step) {
-                    T v[8];                                    // all contributions in flight, added in rank order
+                    T sum[8];
 #pragma unroll
-                    for (int src = 0; src < 8; ++src) v[src] = src < C ? rxbuf[((size_t)src * Mt + m) * R + my_c] : T(0);
-                    T sum = 0;
+                    for (int j = 0; j < 8; ++j) sum[j] = 0;
 #pragma unroll
-                    for (int src = 0; src < 8; ++src)
-                        if (src < C) sum += v[src];
-                    float f;
-                    if constexpr (KIND == KIND_F8) {
-                        f = sum * (act_scale[mat] * wrow[mat]);
-                    } else {
-                        if (a.acc[mat]) a.acc[mat][(int64_t)(m0 + m) * a.ldacc + my_row] = sum;
-                        f = (float)sum * (s.row_scale[mat][m] * wrow[mat]);
+                    for (int src = 0; src < 8; ++src)          // the contributions are added in rank order
+                        if (src < C) {
+                            const uint4* p = reinterpret_cast<const uint4*>(rxbuf + ((size_t)src * Mt + m) * R + my_cg * 8);
+                            const uint4 lo = p[0], hi = p[1];
+                            const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                if constexpr (KIND != KIND_I8) sum[j] += __uint_as_float(w[j]);
+                                else sum[j] += (int32_t)w[j];
+                            }
+                        }
+                    float tok_scale;
+                    if constexpr (KIND != KIND_I8) tok_scale = act_scale[mat];
+                    else tok_scale = s.row_scale[mat][m];
+                    if constexpr (KIND == KIND_I8) {
+                        if (a.acc[mat]) {
+                            int32_t* ap = a.acc[mat] + (int64_t)(m0 + m) * a.ldacc + my_row;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (my_row + j < a.N) ap[j] = sum[j];
+                        }
                     }
-                    if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) f = bf16_round(f);
-                    a.out[mat][(int64_t)(m0 + m) * a.ldo + my_row] = __float2half_rn(f);
+                    uint32_t h[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float f0 = (float)sum[2 * j] * (tok_scale * wrow[2 * j]), f1 = (float)sum[2 * j + 1] * (tok_scale * wrow[2 * j + 1]);
+                        if (a.flags & RWKVQ_FLAG_OUT_VIA_BF16) {
+                            f0 = bf16_round(f0);
+                            f1 = bf16_round(f1);
+                        }
+                        const __half2 hh = __floats2half2_rn(f0, f1);
+                        h[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                    }
+                    __half* o = a.out[mat] + (int64_t)(m0 + m) * a.ldo + my_row;
+                    if (vec) {
+                        *reinterpret_cast<uint4*>(o) = make_uint4(h[0], h[1], h[2], h[3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (my_row + j < a.N) o[j] = __ushort_as_half((unsigned short)((h[j >> 1] >> ((j & 1) * 16)) & 0xffff));
+                    }
                 }
             }
             if (mat + 1 < a.nmat) {                    // this CTA's buffer is empty: tell every sender of the cluster
@@ -600,14 +658,15 @@ static bool tcs_eligible(int64_t M, int64_t N, int64_t K, uint32_t flags, int nm
 }
 
 static int32_t run_tcs(TcArgs a, const TcCall& c, cudaStream_t st, const char* who) {
-    const int C = tcs_cluster_size(a.M, a.N, a.K);
+    const int64_t kbytes = c.kind == KIND_NF4 ? a.K / 2 : a.K;          // bytes of K per row: two e2m1 values per byte
+    const int C = tcs_cluster_size(a.M, a.N, kbytes);
     a.NB = tcs_token_tile(a.M);
     a.ptiles = (a.N + kTileP - 1) / kTileP;
     a.qtiles = C;
     a.max_slots = (a.M + a.NB - 1) / a.NB;                       // token tiles
     a.acc_stride = std::max(a.NB, 32);
     if (a.status == nullptr) a.status = c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : device_status_ptr();
-    const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk;
+    const size_t stage_bytes = kABytes + (size_t)a.NB * kChunk + (c.kind == KIND_NF4 ? 2 * kNfSfStage : 0);
     const size_t rx_bytes = (size_t)std::min(a.M, a.NB) * kTileP * 4;       // [C][tokens of a tile][128 / C] partial sums
     const size_t budget = a.NB <= 64 ? kTcSmemBudgetHalf : kTcSmemBudget;
     const int per_cta = (a.kchunks + C - 1) / C;
@@ -616,12 +675,12 @@ static int32_t run_tcs(TcArgs a, const TcCall& c, cudaStream_t st, const char* w
     a.stages = std::max(a.stages, 1);
     TcMaps maps;
     for (int i = 0; i < a.nmat; ++i) {
-        int32_t rc = make_map(&maps.w[i], c.w[i], a.N, a.K, c.ldw, kTileP, who);
+        int32_t rc = make_map(&maps.w[i], c.w[i], a.N, kbytes, c.ldw, kTileP, who);
         if (rc) return rc;
-        rc = make_map(&maps.a[i], c.codes[i], a.M, a.K, c.lda, a.NB, who);
+        rc = make_map(&maps.a[i], c.codes[i], a.M, kbytes, c.lda, a.NB, who);
         if (rc) return rc;
     }
-    auto kern = c.kind == KIND_F8 ? gemm_tcs_kernel<KIND_F8> : gemm_tcs_kernel<KIND_I8>;
+    auto kern = c.kind == KIND_F8 ? gemm_tcs_kernel<KIND_F8> : (c.kind == KIND_I8 ? gemm_tcs_kernel<KIND_I8> : gemm_tcs_kernel<KIND_NF4>);
     const int32_t rc = ensure_smem_optin(reinterpret_cast<const void*>(kern), (int)kTcSmemBudget, who);
     if (rc) return rc;
     cudaLaunchConfig_t cfg{};

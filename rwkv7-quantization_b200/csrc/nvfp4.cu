@@ -620,6 +620,112 @@ __global__ void __launch_bounds__(kNfQThreads, 2) actq_nvfp4_fused_kernel(const 
     }
 }
 
+// The same quantization as TWO plain launches chained by programmatic dependent launch, for blocks of up to 2^19
+// vectors (few tokens): a cooperative launch costs about 6 us more than a plain one and gives a 16-row block 16 CTAs;
+// here the abs-max pass and the code pass each spread the block over two CTAs per SM.  The maximum travels through a
+// scratch word (atomic max of the float's bits: the values are non-negative); the last CTA of the code pass clears
+// it, so the words are zero again before the next launch on the stream can reach them and a captured graph replays.
+// Words: flags[kNfQMaxCtas + 4] = maximum, [+ 7] = CTAs done (the FP8 two-launch quantizer uses the same words of the
+// same scratch in the same way).  Same arithmetic as the cooperative kernel: same bits.
+constexpr int kNfTwoThreads = 256;
+constexpr int64_t kNfTwoMaxVectors = 1 << 19;
+
+// grid rows * cpr: CTA b takes every cpr-th group of kNfTwoThreads vectors of row b / cpr and of every
+// (gridDim.x / cpr)-th row after it
+template <int DT>
+__global__ void __launch_bounds__(kNfTwoThreads) actq_nvfp4_two_amax_kernel(const NfQArgs a, int cpr) {
+    __shared__ float sh[kNfTwoThreads / 32];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int kv = a.K >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seg = (int)blockIdx.x % cpr, rstep = (int)gridDim.x / cpr, cstep = cpr * kNfTwoThreads;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float m = 0.f;
+    for (int r = (int)blockIdx.x / cpr; r < a.M; r += rstep) {
+        const char* row = reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
+        for (int c0 = seg * kNfTwoThreads + (int)threadIdx.x; c0 < kv; c0 += 4 * cstep) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j * cstep < kv) v[j] = *reinterpret_cast<const uint4*>(row + (int64_t)(c0 + j * cstep) * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (c0 + j * cstep < kv) m = fmaxf(m, packed_absmax8<DT>(v[j]));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) sh[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        m = warp_max(lane < kNfTwoThreads / 32 ? sh[lane] : 0.f);
+        if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(a.flags) + kNfQMaxCtas + 4, __float_as_int(m));
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kNfTwoThreads) actq_nvfp4_two_codes_kernel(const NfQArgs a, int cpr) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int kv = a.K >> 3;
+    const int seg = (int)blockIdx.x % cpr, rstep = (int)gridDim.x / cpr, cstep = cpr * kNfTwoThreads;
+    int* two = reinterpret_cast<int*>(a.flags) + kNfQMaxCtas + 4;
+    const int64_t k64 = a.K >> 6;
+    asm volatile("griddepcontrol.wait;" ::: "memory");              // the abs-max pass is complete and visible
+    const float amax = fmaxf(__int_as_float(__ldcg(two)), 1e-12f);
+    const float pts = __fdiv_rn(amax, 2688.f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.pts = pts;
+    const float inv_pts = __fdiv_rn(1.f, pts), k448 = __fdiv_rn(448.f, amax);
+    for (int r = (int)blockIdx.x / cpr; r < a.M; r += rstep) {
+        const char* row = reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
+        // whole warps walk together: kv is even and a 16-block is the vectors of lanes 2j and 2j + 1
+        for (int base = seg * kNfTwoThreads; base < kv; base += 2 * cstep) {
+            uint4 v[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int i = base + j * cstep + (int)threadIdx.x;
+                v[j] = i < kv ? *reinterpret_cast<const uint4*>(row + (int64_t)i * 16) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (base + j * cstep >= kv) continue;              // uniform over the CTA
+                const int i = base + j * cstep + (int)threadIdx.x;
+                const uint32_t wv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                float f[8], bm = 0.f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 p = cvt2<DT>(wv[q]);
+                    f[2 * q] = p.x;
+                    f[2 * q + 1] = p.y;
+                    bm = fmaxf(bm, fmaxf(fabsf(p.x), fabsf(p.y)));
+                }
+                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+                const float sb = fminf(fmaxf(bm * k448, 0.015625f), 448.f);
+                const uint32_t sc = e4m3x2(sb, 0.f) & 0xffu;
+                const float bs = e4m3_to_float(sc);
+                uint32_t out = 0;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) out |= e2m1x2(__fdiv_rn(f[2 * q] * inv_pts, bs), __fdiv_rn(f[2 * q + 1] * inv_pts, bs)) << (8 * q);
+                if (i < kv) {
+                    *reinterpret_cast<uint32_t*>(a.codes + (int64_t)r * a.ldc + (int64_t)i * 4) = out;
+                    if ((i & 1) == 0) {
+                        const int b = i >> 1;
+                        if (a.bs_rows) a.bs_rows[(int64_t)r * a.lds + b] = (uint8_t)sc;
+                        if (a.bs_blocked)
+                            a.bs_blocked[((int64_t)(r >> 7) * k64 + (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)] = (uint8_t)sc;
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();                                    // every thread of this CTA has read the maximum
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(two + 3, 1) == (int)gridDim.x - 1) {
+            two[0] = 0;
+            __threadfence();
+            two[3] = 0;
+        }
+    }
+}
+
 }  // namespace rwkvq
 
 using namespace rwkvq;
@@ -721,6 +827,34 @@ int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_
     a.slots = reinterpret_cast<float*>(scratch); a.flags = reinterpret_cast<uint32_t*>(scratch) + kNfQMaxCtas; a.status = status ? status : device_status_ptr();
     a.ldx = ldx; a.ldc = ldc; a.lds = lds; a.M = (int)M; a.K = (int)K;
     a.wait_ns = wait_limit_ns();
+    const char* two_env = std::getenv("RWKVQ_NVFP4_ACTQ_TWO_MAX");      // read per call: a test switches routes in one process
+    const int64_t two_max = two_env ? std::atoll(two_env) : kNfTwoMaxVectors;
+    if (M * (K / 8) <= two_max) {
+        const int kv = (int)(K / 8);
+        int cpr = 1;                                     // CTAs per row: about two CTAs per SM in all, 256+ vectors each
+        while ((int64_t)M * cpr < 2 * (int64_t)sm_count() && cpr * 2 * kNfTwoThreads <= kv) cpr <<= 1;
+        const int rows = (int)std::min<int64_t>(M, std::max<int64_t>(1, 4 * (int64_t)sm_count() / cpr));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)(rows * cpr));
+        cfg.blockDim = dim3(kNfTwoThreads);
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl() ? 1 : 0;
+        cudaError_t e = x_dtype == RWKVQ_F16 ? cudaLaunchKernelEx(&cfg, actq_nvfp4_two_amax_kernel<RWKVQ_F16>, a, cpr)
+                                             : cudaLaunchKernelEx(&cfg, actq_nvfp4_two_amax_kernel<RWKVQ_BF16>, a, cpr);
+        if (e == cudaSuccess)
+            e = x_dtype == RWKVQ_F16 ? cudaLaunchKernelEx(&cfg, actq_nvfp4_two_codes_kernel<RWKVQ_F16>, a, cpr)
+                                     : cudaLaunchKernelEx(&cfg, actq_nvfp4_two_codes_kernel<RWKVQ_BF16>, a, cpr);
+        if (e != cudaSuccess) {
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);         // two launches: check_launch counts the other one
+        return check_launch(who);
+    }
     const int grid = (int)std::min<int64_t>(M, std::min<int64_t>(512, 2 * (int64_t)sm_count()));
     void* args[] = {(void*)&a};
     const void* fn = x_dtype == RWKVQ_F16 ? (const void*)actq_nvfp4_fused_kernel<RWKVQ_F16> : (const void*)actq_nvfp4_fused_kernel<RWKVQ_BF16>;

@@ -97,7 +97,7 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-enum { KIND_F8 = 0, KIND_I8 = 1 };
+enum { KIND_F8 = 0, KIND_I8 = 1, KIND_NF4 = 2 };
 
 template <int KIND>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -131,6 +131,34 @@ __host__ __device__ inline uint32_t umma_idesc(int kind, int m, int n) {
     const uint32_t cfmt = kind == KIND_F8 ? 1u : 2u;
     const uint32_t fmt = kind == KIND_F8 ? 0u : 1u;
     return (cfmt << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- NVFP4: block-scaled MMA and its scale factors
+constexpr int kNfTileM = 128;                               // rows of the 128-row operand
+constexpr uint32_t kNfSfChunk = 512;                        // scales of 128 rows x 64 k
+constexpr uint32_t kNfSfStage = 4 * kNfSfChunk;             // scales of 128 rows x one ring stage (256 values of k)
+
+// K-major, no swizzle: 8-row x 16-byte core matrices, 128 bytes apart along the rows (32 rows x 16 bytes, dense)
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)(128 >> 4) << 32;       // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                // descriptor version (sm_100)
+    return d;
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_dst, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_dst), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t tsfa,
+                                             uint32_t tsfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb) : "memory");
+}
+// block-scaled instruction descriptor: A and B e2m1 (format 1), both K-major, e4m3 scale factors, M = 128
+__host__ __device__ inline uint32_t nvfp4_idesc(int n) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (0u << 23) | ((uint32_t)(kNfTileM >> 4) << 24);
 }
 
 // 32 lanes x 16 consecutive 32-bit columns: thread i of the warp gets lane (base lane + i)

@@ -126,4 +126,11 @@ int32_t run_tc2(int kind, const void* codes, int64_t lda, const float* a_scale, 
                 __half* out, int64_t ldo, int32_t* acc, int64_t ldacc, int M, int N, int K, int div_mode, uint32_t flags, float* ffn_amax,
                 int* status, cudaStream_t st, const char* who);
 
+// NVFP4 GEMM for few tokens (up to 256) on the cluster split-K kernel of gemm_tc.cu (gemm_tcs.cuh): weights = the
+// 128-row operand, K split across a thread-block cluster, partial sums through distributed shared memory.
+bool tcs_nvfp4_eligible(int64_t M, int64_t N, int64_t K);
+int32_t run_tcs_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts, const uint8_t* w_codes,
+                      int64_t ldw, const uint8_t* w_scales_blocked, const float* w_tscale, __half* out, int64_t ldo, int64_t M, int64_t N,
+                      int64_t K, int* status, cudaStream_t st, const char* who);
+
 }  // namespace rwkvq

@@ -153,11 +153,42 @@ def test_fused_decode_route(nf, monkeypatch, dt, m, n, k):
     assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
 
 
-@pytest.mark.parametrize("m,k", [(1, 512), (130, 1024), (300, 4096)])
-def test_fused_activation_quantizer_routes_agree(nf, monkeypatch, m, k):
-    """One-launch quantizer against the three-kernel route (codes, scales, tensor scale bit for bit), and its blocked
-    scales against pack_scales of the row-major ones on every valid row."""
+@pytest.mark.parametrize("m,n,k", [(16, 256, 4096), (9, 136, 16384), (64, 384, 8192), (200, 256, 16384), (256, 130, 16384), (33, 512, 2048)])
+def test_cluster_splitk_route(nf, monkeypatch, m, n, k):
+    """Few tokens against a long K: the weights become the 128-row operand and K is split across a thread-block cluster
+    (partial sums through distributed shared memory).  Against the oracle, and against the tiled GEMM on the same codes."""
+    import rwkvq_abi as abi
+    w = gen(n * 7 + k, (n, k), (1.0 / k) ** 0.5)
+    info = dev(nf.quantize_to_nvfp4(w))
+    x = gen(m + 13, (m, k), 1.0, torch.bfloat16)
+    x[m // 2].zero_()
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "tc")
+    assert abi.lib().rwkvq_tc_gemm_nvfp4_cluster_route(m, n, k) == 1
+    out = nf.linear_nvfp4(x.cuda(), info)
+    again = nf.linear_nvfp4(x.cuda(), info)
+    torch.cuda.synchronize()
+    assert abi.workspace_status(abi.workspace(1, 1, 1, 1, out.device)) == 0
+    assert torch.equal(out, again)                                      # rank-ordered sums: run-to-run identical
+    monkeypatch.setenv("RWKVQ_TCS_NF4_MIN_C", "99")                     # the tiled form
+    assert abi.lib().rwkvq_tc_gemm_nvfp4_cluster_route(m, n, k) == 0
+    tiled = nf.linear_nvfp4(x.cuda(), info)
+    assert rel_err(out, tiled) <= 2e-3
+    oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
+             "tensor_scale": info["tensor_scale"].cpu()}
+    assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
+
+
+@pytest.mark.parametrize("two_max", [None, "0"])
+@pytest.mark.parametrize("m,k", [(1, 512), (130, 1024), (300, 4096), (16, 16384)])
+def test_fused_activation_quantizer_routes_agree(nf, monkeypatch, m, k, two_max):
+    """Fused quantizer (two chained launches for blocks of up to 2^19 vectors, one cooperative launch above; the
+    second form is forced with a limit of 0) against the three-kernel route (codes, scales, tensor scale bit for bit),
+    and its blocked scales against pack_scales of the row-major ones on every valid row.  The two-launch form leaves
+    its scratch words zero."""
     import numpy as np
+    import rwkvq_abi as abi
+    if two_max is not None:
+        monkeypatch.setenv("RWKVQ_NVFP4_ACTQ_TWO_MAX", two_max)
     x = gen(m * 5 + k, (m, k), 1.0, torch.bfloat16).cuda()
     monkeypatch.setenv("RWKVQ_NVFP4_ACTQ", "split")
     c0, s0, p0 = nf.quantize_activations_nvfp4(x)
@@ -171,3 +202,4 @@ def test_fused_activation_quantizer_routes_agree(nf, monkeypatch, m, k):
     r = np.arange(m)[:, None]
     b = np.arange(k // 16)[None, :]
     assert (got[r // 128, b // 4, (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4] == src).all()
+    assert int(abi.actq_scratch(x.device)[1024 + 4:1024 + 8].abs().sum().item()) == 0
