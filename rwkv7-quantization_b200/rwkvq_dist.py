@@ -169,28 +169,35 @@ class ColumnSplitLinear:
     (rank-major) followed by one copy into the [M, N] layout; gather="peer": PeerGather above (GPU only, fp16 results;
     `max_rows` sizes its buffers); gather="push": the projection's GEMM stores its result tiles into every rank's buffer
     itself and the receivers only wait for a flag (FP8, INT8 and NVFP4 weights, row counts that run the tiled tensor-core
-    GEMM; other calls fall back to "peer").  The pushed FP8 result follows linear_quantized_fused's semantics."""
+    GEMM; other calls fall back to "peer").  The pushed FP8 result follows linear_quantized_fused's semantics.
+    gather="auto": "push" where it was measured faster than "peer" -- up to 4 ranks at every row count (4096 rows:
+    194 against 266 us on 2 GPUs, 232 against 279 us on 4), on more ranks up to PUSH_MAX_ROWS_WIDE rows (8 GPUs: 78
+    against 80 us at 256 rows, but 548 against 284 us at 4096, where every epilogue warp stores each tile to seven
+    peers) -- else "peer".  The choice depends on sizes only, so every rank makes the same one."""
+
+    PUSH_MAX_ROWS_WIDE = 512
 
     def __init__(self, weight_info: dict, linear_fn, group=None, already_sliced: bool = False, gather: str = "nccl", max_rows: int = 4096):
-        if gather not in ("nccl", "peer", "push"):
-            raise ValueError(f"gather must be 'nccl', 'peer' or 'push', got {gather!r}")
+        if gather not in ("nccl", "peer", "push", "auto"):
+            raise ValueError(f"gather must be 'nccl', 'peer', 'push' or 'auto', got {gather!r}")
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.local = weight_info if already_sliced else slice_weight_info(weight_info, self.rank, self.world)
         self.linear_fn = linear_fn
         self.n_local = self.local["weight" if "weight" in self.local else "packed"].shape[0]
-        self.peer = PeerGather(max_rows, self.n_local * self.world, group) if gather in ("peer", "push") else None
+        self.peer = PeerGather(max_rows, self.n_local * self.world, group) if gather in ("peer", "push", "auto") else None
+        self.auto = gather == "auto"
         # "push": the GEMM itself stores its tiles into every rank's buffer (one kernel computes and gathers); taken where
         # the projection runs the kernel that can do it (NVFP4 weights on the tensor-core route), else the pull form
-        self.push = gather == "push" and self.local.get("qtype", "fp8") in ("nvfp4", "fp8", "int8")
+        self.push = gather in ("push", "auto") and self.local.get("qtype", "fp8") in ("nvfp4", "fp8", "int8")
 
     def __call__(self, x: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
         if self.peer is not None:
             import rwkvq_abi as abi
             x2 = x.reshape(-1, x.shape[-1])
             pushing = False
-            if self.push:
+            if self.push and not (self.auto and self.world > 4 and x2.shape[0] > self.PUSH_MAX_ROWS_WIDE):
                 if self.local.get("qtype") == "nvfp4":
                     import nvfp4_ops
                     pushing = nvfp4_ops.can_push(x2.shape[0], x2.shape[1])

@@ -46,6 +46,8 @@ def main():
     for scheme, info in infos.items():
         lin = fp8_ops.linear_quantized_fused if scheme != "nvfp4" else fp8_ops.linear_quantized
         modes = ("nccl", "peer", "push")                          # push: the GEMM stores its tiles into the peers itself
+        if scheme == "nvfp4":
+            modes += ("auto",)                                    # push or peer by rank count and rows
         splits = {mode: D.ColumnSplitLinear(info, lin, gather=mode, max_rows=256) for mode in modes}
         for m in (1, 256):
             x = (torch.randn(m, k, generator=g)).to(torch.bfloat16).to(dev)

@@ -31,7 +31,7 @@ def test_column_split_ffn_key_two_gpus():
         line = [l for l in out.splitlines() if l.startswith(f"rank {r} ")]
         assert line, out[-3000:]
         verdicts = line[-1].split()[2:]
-        assert len(verdicts) == 18 and all(v.endswith("=True/True") for v in verdicts), line[-1]
+        assert len(verdicts) == 20 and all(v.endswith("=True/True") for v in verdicts), line[-1]
 
 
 def test_pull_gives_up_when_a_rank_never_signals():
