@@ -824,9 +824,10 @@ bool tcs_nvfp4_eligible(int64_t M, int64_t N, int64_t K) {
     const int min_c = env ? std::atoi(env) : 0;
     static const int on = std::getenv("RWKVQ_TCS") ? std::atoi(std::getenv("RWKVQ_TCS")) : 1;
     if (!on || M < 1 || M > kTcsMaxM || K % 256 || K < 2048) return false;
-    // measured on the 7.2B shapes: with 128 row tiles (N = 16384) and a cluster of two the tiled form is as fast (16
-    // tokens) or faster (64); from 65 tokens on a cluster of two already wins (FFN value, 256 tokens: 57 -> 45 us)
-    return tcs_cluster_size(M, N, K / 2) >= (min_c > 0 ? min_c : (M <= 64 ? 4 : 2));
+    // measured on the 7.2B shapes: with 128 row tiles (N = 16384) a cluster of two wins up to 32 tokens (16 tokens:
+    // 14.7 against 18.5 us) and loses at 64 (23.9 against 22.1 us); from 65 tokens on a cluster of two wins again (FFN
+    // value, 256 tokens: 57 -> 40 us)
+    return tcs_cluster_size(M, N, K / 2) >= (min_c > 0 ? min_c : (M > 32 && M <= 64 ? 4 : 2));
 }
 
 int32_t run_tcs_nvfp4(const uint8_t* a_codes, int64_t lda, const uint8_t* a_scales_blocked, const float* a_pts, const uint8_t* w_codes,

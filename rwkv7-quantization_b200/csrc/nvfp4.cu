@@ -13,6 +13,7 @@
 // from the streamed 16-byte loads (cvt.f16x2.e2m1x2 + one HMUL2 per pair) -- and multiplied with mma.sync.m16n8k16
 // with fp32 accumulation: every product is exact.  Same work split as the INT4 GEMV: 8 weight rows per CTA, the 8
 // warps on alternating 128-k units, register ring of loads across row tiles, fixed-order reduction.
+#include <cooperative_groups.h>
 #include <atomic>
 #include <cstdlib>
 
@@ -620,6 +621,98 @@ __global__ void __launch_bounds__(kNfQThreads, 2) actq_nvfp4_fused_kernel(const 
     }
 }
 
+// Few tokens (the kernel takes up to 16384 vectors; the dispatcher gives it up to 8192: 4 rows of K = 16384, 16 of
+// K = 4096): ONE plain launch of a CLUSTER of 1 to 8 CTAs
+// of 256 threads, like the small FP8 quantizer: every thread keeps up to 8 vectors in registers between the abs-max
+// and the codes (one read of the activations, all loads in flight together), the CTAs exchange their maxima through
+// distributed shared memory and one cluster barrier.  No scratch, no second launch for the projection behind it to
+// wait for.  CTAs of 256 threads (16 K registers) become resident next to the CTAs of the projection in front; with
+// 1024 threads (the whole register file) the cluster had to wait for free SMs and the call was slower than the two
+// chained launches below.  Same arithmetic as the other forms: same bits.
+constexpr int kNfSmallThreads = 256;
+constexpr int kNfSmallKeep = 8;
+
+template <int DT>
+__global__ void __launch_bounds__(kNfSmallThreads, 1) actq_nvfp4_small_kernel(const NfQArgs a) {
+    __shared__ float sh[kNfSmallThreads / 32];
+    __shared__ float s_part[8];           // maxima of the cluster's CTAs (each CTA writes its slot in every CTA)
+    __shared__ float s_amax;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    cooperative_groups::cluster_group cl = cooperative_groups::this_cluster();
+    const int C = (int)cl.num_blocks(), cr = (int)cl.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const char* x = reinterpret_cast<const char*>(a.x);
+    const int kv = a.K >> 3, nvec = a.M * kv;
+    const uint32_t inv_kv = 0xFFFFFFFFu / (uint32_t)kv + 1u;          // row of a flat vector index without a division
+    const int64_t k64 = a.K >> 6;
+    asm volatile("griddepcontrol.wait;" ::: "memory");                // the activations may come from the previous kernel
+    // the cluster's threads take the vectors round-robin; kv and the step are even, so the two vectors of a 16-block
+    // sit in neighbouring lanes at the same j
+    const int first = cr * kNfSmallThreads + (int)threadIdx.x, step = C * kNfSmallThreads;
+    uint4 v[kNfSmallKeep];
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < kNfSmallKeep; ++j) {
+        const int idx = first + j * step;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (idx < nvec) {
+            const int r = (int)__umulhi((uint32_t)idx, inv_kv), c = idx - r * kv;
+            v[j] = *reinterpret_cast<const uint4*>(x + ((int64_t)r * a.ldx + (int64_t)c * 8) * 2);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kNfSmallKeep; ++j) m = fmaxf(m, packed_absmax8<DT>(v[j]));
+    m = warp_max(m);
+    if (lane == 0) sh[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        const float b = warp_max(lane < kNfSmallThreads / 32 ? sh[lane] : 0.f);
+        if (lane < C) *cl.map_shared_rank(&s_part[cr], lane) = b;      // this CTA's maximum into slot cr of CTA `lane`
+    }
+    cl.sync();                                                          // all slots written (and visible) in every CTA
+    if (threadIdx.x == 0) {
+        float b = s_part[0];
+        for (int i = 1; i < C; ++i) b = fmaxf(b, s_part[i]);
+        s_amax = b;
+    }
+    __syncthreads();
+    const float amax = fmaxf(s_amax, 1e-12f);
+    const float pts = __fdiv_rn(amax, 2688.f);
+    if (cr == 0 && threadIdx.x == 0) *a.pts = pts;
+    const float inv_pts = __fdiv_rn(1.f, pts), k448 = __fdiv_rn(448.f, amax);
+#pragma unroll
+    for (int j = 0; j < kNfSmallKeep; ++j) {
+        const int idx = first + j * step;
+        if (j * step >= nvec) break;                                   // uniform over the cluster
+        const uint32_t wv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        float f[8], bm = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float2 p = cvt2<DT>(wv[q]);
+            f[2 * q] = p.x;
+            f[2 * q + 1] = p.y;
+            bm = fmaxf(bm, fmaxf(fabsf(p.x), fabsf(p.y)));
+        }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        const float sb = fminf(fmaxf(bm * k448, 0.015625f), 448.f);
+        const uint32_t sc = e4m3x2(sb, 0.f) & 0xffu;
+        const float bs = e4m3_to_float(sc);
+        uint32_t out = 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) out |= e2m1x2(__fdiv_rn(f[2 * q] * inv_pts, bs), __fdiv_rn(f[2 * q + 1] * inv_pts, bs)) << (8 * q);
+        if (idx < nvec) {
+            const int r = (int)__umulhi((uint32_t)idx, inv_kv), i = idx - r * kv;
+            *reinterpret_cast<uint32_t*>(a.codes + (int64_t)r * a.ldc + (int64_t)i * 4) = out;
+            if ((i & 1) == 0) {
+                const int b = i >> 1;
+                if (a.bs_rows) a.bs_rows[(int64_t)r * a.lds + b] = (uint8_t)sc;
+                if (a.bs_blocked)
+                    a.bs_blocked[((int64_t)(r >> 7) * k64 + (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)] = (uint8_t)sc;
+            }
+        }
+    }
+}
+
 // The same quantization as TWO plain launches chained by programmatic dependent launch, for blocks of up to 2^19
 // vectors (few tokens): a cooperative launch costs about 6 us more than a plain one and gives a 16-row block 16 CTAs;
 // here the abs-max pass and the code pass each spread the block over two CTAs per SM.  The maximum travels through a
@@ -676,15 +769,15 @@ __global__ void __launch_bounds__(kNfTwoThreads) actq_nvfp4_two_codes_kernel(con
     for (int r = (int)blockIdx.x / cpr; r < a.M; r += rstep) {
         const char* row = reinterpret_cast<const char*>(a.x) + (int64_t)r * a.ldx * 2;
         // whole warps walk together: kv is even and a 16-block is the vectors of lanes 2j and 2j + 1
-        for (int base = seg * kNfTwoThreads; base < kv; base += 2 * cstep) {
-            uint4 v[2];
+        for (int base = seg * kNfTwoThreads; base < kv; base += 4 * cstep) {
+            uint4 v[4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 const int i = base + j * cstep + (int)threadIdx.x;
                 v[j] = i < kv ? *reinterpret_cast<const uint4*>(row + (int64_t)i * 16) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 if (base + j * cstep >= kv) continue;              // uniform over the CTA
                 const int i = base + j * cstep + (int)threadIdx.x;
                 const uint32_t wv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
@@ -827,12 +920,41 @@ int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_
     a.slots = reinterpret_cast<float*>(scratch); a.flags = reinterpret_cast<uint32_t*>(scratch) + kNfQMaxCtas; a.status = status ? status : device_status_ptr();
     a.ldx = ldx; a.ldc = ldc; a.lds = lds; a.M = (int)M; a.K = (int)K;
     a.wait_ns = wait_limit_ns();
+    const char* small_env = std::getenv("RWKVQ_NVFP4_ACTQ_SMALL_MAX");  // read per call: a test switches routes in one process
+    // measured: up to 4 vectors per thread of the largest cluster the one launch wins (att, 16 rows: 9.5 against 10.2 us;
+    // FFN value, 4 rows: 14.0 against 18.6 us), at 8 per thread the two chained launches are as fast or faster
+    const int64_t small_max = small_env ? std::atoll(small_env) : (int64_t)8 * 4 * kNfSmallThreads;
+    if (M * (K / 8) <= std::min<int64_t>(small_max, (int64_t)8 * kNfSmallKeep * kNfSmallThreads) && K / 8 < 65536) {
+        int cluster = 1;                                 // about 4 vectors per thread
+        while (cluster < 8 && M * (K / 8) > (int64_t)cluster * 4 * kNfSmallThreads) cluster <<= 1;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3((unsigned)cluster);
+        cfg.blockDim = dim3(kNfSmallThreads);
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)cluster;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl() ? 2 : 1;
+        const cudaError_t e = x_dtype == RWKVQ_F16 ? cudaLaunchKernelEx(&cfg, actq_nvfp4_small_kernel<RWKVQ_F16>, a)
+                                                   : cudaLaunchKernelEx(&cfg, actq_nvfp4_small_kernel<RWKVQ_BF16>, a);
+        if (e != cudaSuccess) {
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+        }
+        return check_launch(who);
+    }
     const char* two_env = std::getenv("RWKVQ_NVFP4_ACTQ_TWO_MAX");      // read per call: a test switches routes in one process
     const int64_t two_max = two_env ? std::atoll(two_env) : kNfTwoMaxVectors;
     if (M * (K / 8) <= two_max) {
         const int kv = (int)(K / 8);
         int cpr = 1;                                     // CTAs per row: about two CTAs per SM in all, 256+ vectors each
         while ((int64_t)M * cpr < 2 * (int64_t)sm_count() && cpr * 2 * kNfTwoThreads <= kv) cpr <<= 1;
+        if (const char* e = std::getenv("RWKVQ_NVFP4_ACTQ_CPR")) cpr = std::max(1, std::atoi(e));
         const int rows = (int)std::min<int64_t>(M, std::max<int64_t>(1, 4 * (int64_t)sm_count() / cpr));
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3((unsigned)(rows * cpr));

@@ -23,6 +23,8 @@ import rwkvq_abi as abi
 E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 BLOCK = 16
 GEMV_ROWS = 16
+TC_LONG_K = int(os.environ.get("RWKVQ_NVFP4_TC_LONG_K", "8192"))   # rows this long go to the tensor-core route at every token count
+TC_WIDE_N = int(os.environ.get("RWKVQ_NVFP4_TC_WIDE_N", "8192"))   # this many weight rows: from 3 tokens on
 TC_MIN_M = int(os.environ.get("RWKVQ_NVFP4_TC_MIN_M", "8"))   # more tokens than this go to the tensor-core GEMM (measured: from 9 rows it is as fast or faster on the 7.2B shapes)
 
 
@@ -117,14 +119,21 @@ def _blocked_weight_scales(weight_info, k: int) -> torch.Tensor:
     return blk
 
 
-def _route(m: int, k: int) -> str:
+def _route(m: int, k: int, n: int = 0) -> str:
     """'fused' = one launch, activation quantization in the GEMV's prologue (up to TC_MIN_M tokens, K a multiple of 512);
     'tc' = block-scaled tensor-core GEMM (more tokens, K a multiple of 256); 'gemv' = quantization kernels + the
-    16-row GEMV (any K that is a multiple of 128)."""
+    16-row GEMV (any K that is a multiple of 128).
+    The fused GEMV quantizes the whole block in every CTA and converts every weight code in registers; the tensor-core
+    route quantizes once and streams the codes into block-scaled MMAs (K split across a cluster), so it takes over where
+    the prologue or the conversions weigh: measured at K = 16384 from one token on (13.2 against 16.3 us; 4 tokens 17.4
+    against 25.2), and at K = 4096 against many weight rows from 3 tokens on (N = 16384, 4 tokens: 13.9 against 16.0 us;
+    8 tokens: 14.3 against 19.7)."""
     forced = os.environ.get("RWKVQ_NVFP4_ROUTE", "auto")
     if forced == "gemv" or k % 256 != 0:
         return "gemv"
     if forced == "tc" or m > TC_MIN_M:
+        return "tc"
+    if forced == "auto" and (k >= TC_LONG_K or (m >= 3 and n >= TC_WIDE_N)) and abi.lib().rwkvq_tc_gemm_nvfp4_cluster_route(m, n, k):
         return "tc"
     # the tensor scale is per call: all rows must go into one launch
     if k % 512 == 0 and abi.lib().rwkvq_gemv_nvfp4_fused_smem_bytes(m, k) <= 224 * 1024:
@@ -149,7 +158,7 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16, push=None):
     from fused_fp8_gemm import _rows16
     x2 = _rows16(x).contiguous()
     m = x2.shape[0]
-    route = _route(m, k)
+    route = _route(m, k, n)
     if push is not None and route != "tc":
         raise RuntimeError("rwkvq: the pushed all-gather rides in the tensor-core GEMM only (see can_push)")
     if route == "fused" and wbs.stride(0) % 16 == 0 and wbs.data_ptr() % 16 == 0:

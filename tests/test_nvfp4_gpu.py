@@ -143,7 +143,9 @@ def test_fused_decode_route(nf, monkeypatch, dt, m, n, k):
         x[1].zero_()
     monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "auto")
     monkeypatch.setattr(nf, "TC_MIN_M", 16)            # the kernel takes up to 16 rows; the dispatcher hands over to the GEMM earlier
-    assert nf._route(m, k) == "fused"
+    monkeypatch.setattr(nf, "TC_LONG_K", 1 << 30)      # ... and so it does for long rows and wide matrices
+    monkeypatch.setattr(nf, "TC_WIDE_N", 1 << 30)
+    assert nf._route(m, k, n) == "fused"
     out = nf.linear_nvfp4(x.cuda(), info)
     monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "gemv")
     via_gemv = nf.linear_nvfp4(x.cuda(), info)
@@ -151,6 +153,24 @@ def test_fused_decode_route(nf, monkeypatch, dt, m, n, k):
     oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
              "tensor_scale": info["tensor_scale"].cpu()}
     assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
+
+
+def test_few_tokens_take_the_tensor_core_route_where_it_is_faster(nf, monkeypatch):
+    """Dispatcher: long rows (K >= 8192) at every token count, wide matrices (N >= 8192) from 3 tokens on; the rest of
+    the few-token calls stay on the one-launch GEMV."""
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "auto")
+    assert nf._route(1, 16384, 4096) == "tc" and nf._route(4, 16384, 4096) == "tc"
+    assert nf._route(1, 4096, 16384) == "fused" and nf._route(2, 4096, 16384) == "fused"
+    assert nf._route(3, 4096, 16384) == "tc" and nf._route(8, 4096, 16384) == "tc"
+    assert nf._route(1, 4096, 4096) == "fused" and nf._route(8, 4096, 4096) == "fused" and nf._route(9, 4096, 4096) == "tc"
+    w = gen(77, (256, 16384), 1.0 / 128)
+    info = dev(nf.quantize_to_nvfp4(w))
+    for m in (1, 2, 5):
+        x = gen(78 + m, (m, 16384), 1.0, torch.bfloat16)
+        out = nf.linear_nvfp4(x.cuda(), info)
+        oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
+                 "tensor_scale": info["tensor_scale"].cpu()}
+        assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
 
 
 @pytest.mark.parametrize("m,n,k", [(16, 256, 4096), (9, 136, 16384), (64, 384, 8192), (200, 256, 16384), (256, 130, 16384), (33, 512, 2048)])
@@ -178,17 +198,18 @@ def test_cluster_splitk_route(nf, monkeypatch, m, n, k):
     assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
 
 
-@pytest.mark.parametrize("two_max", [None, "0"])
-@pytest.mark.parametrize("m,k", [(1, 512), (130, 1024), (300, 4096), (16, 16384)])
-def test_fused_activation_quantizer_routes_agree(nf, monkeypatch, m, k, two_max):
-    """Fused quantizer (two chained launches for blocks of up to 2^19 vectors, one cooperative launch above; the
-    second form is forced with a limit of 0) against the three-kernel route (codes, scales, tensor scale bit for bit),
-    and its blocked scales against pack_scales of the row-major ones on every valid row.  The two-launch form leaves
-    its scratch words zero."""
+@pytest.mark.parametrize("form", ["auto", "two", "coop"])
+@pytest.mark.parametrize("m,k", [(1, 512), (130, 1024), (300, 4096), (16, 16384), (5, 4096), (64, 4096), (3, 16448)])
+def test_fused_activation_quantizer_routes_agree(nf, monkeypatch, m, k, form):
+    """Fused quantizer -- one cluster launch up to 65536 vectors, two chained launches up to 2^19, one cooperative
+    launch above ("two" and "coop" force the later forms with limits of 0) -- against the three-kernel route (codes,
+    scales, tensor scale bit for bit), and its blocked scales against pack_scales of the row-major ones on every valid
+    row.  The two-launch form leaves its scratch words zero."""
     import numpy as np
     import rwkvq_abi as abi
-    if two_max is not None:
-        monkeypatch.setenv("RWKVQ_NVFP4_ACTQ_TWO_MAX", two_max)
+    monkeypatch.setenv("RWKVQ_NVFP4_ACTQ_SMALL_MAX", "16384" if form == "auto" else "0")      # "auto": the cluster kernel up to its own limit
+    if form == "coop":
+        monkeypatch.setenv("RWKVQ_NVFP4_ACTQ_TWO_MAX", "0")
     x = gen(m * 5 + k, (m, k), 1.0, torch.bfloat16).cuda()
     monkeypatch.setenv("RWKVQ_NVFP4_ACTQ", "split")
     c0, s0, p0 = nf.quantize_activations_nvfp4(x)
