@@ -528,7 +528,11 @@ __global__ void __launch_bounds__(kFusedThreads, 2) actq_fp8_fused_kernel(const 
 // one cluster barrier; there is no grid rendezvous and no scratch, so the kernel can be launched with programmatic
 // dependent launch: it becomes resident while its predecessor drains, releases its own dependents at once (the
 // projection behind it starts prefetching weights) and waits for its input.
+// The CTA size is the launch's (blockDim.x): 256 threads for blocks of up to 16384 vectors -- such a CTA takes a quarter
+// of an SM's registers and becomes resident beside the CTAs of the projection in front, whereas a 1024-thread CTA takes
+// the whole register file and has to wait for a drained SM -- and 1024 threads for larger blocks.
 constexpr int kSmallThreads = 1024;
+constexpr int kSmallThreadsLight = 256;
 constexpr int kSmallKeep = 8;
 
 template <int DT>
@@ -545,7 +549,8 @@ __global__ void __launch_bounds__(kSmallThreads, 1) actq_fp8_small_kernel(const 
     const int kv = a.K >> 3, nvec = a.M * kv;
     const uint32_t inv_kv = 0xFFFFFFFFu / (uint32_t)kv + 1u;          // row of a flat vector index without a division
     const bool after_bf16 = a.after_bf16 != 0, from_bf16 = a.from_bf16 != 0;
-    const bool keep = nvec <= kSmallKeep * kSmallThreads * C;
+    const int nthr = (int)blockDim.x;
+    const bool keep = nvec <= kSmallKeep * nthr * C;
     asm volatile("griddepcontrol.wait;" ::: "memory");                // the activations may come from the previous kernel
     auto vec_ptr = [&](int idx) {
         const int r = (int)__umulhi((uint32_t)idx, inv_kv), c = idx - r * kv;
@@ -571,7 +576,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) actq_fp8_small_kernel(const 
         }
     };
     // the cluster's threads take the vectors round-robin: thread (cr, tid) vectors first, first + step, ...
-    const int first = cr * kSmallThreads + threadIdx.x, step = C * kSmallThreads;
+    const int first = cr * nthr + (int)threadIdx.x, step = C * nthr;
     uint4 v[kSmallKeep];
     float m = 0.f;
 #pragma unroll 1
@@ -587,7 +592,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1) actq_fp8_small_kernel(const 
     if (lane == 0) sh[warp] = m;
     __syncthreads();
     if (warp == 0) {
-        const float b = warp_max(sh[lane]);
+        const float b = warp_max(lane < (nthr >> 5) ? sh[lane] : 0.f);
         if (lane < C) *cl.map_shared_rank(&s_part[cr], lane) = b;      // this CTA's maximum into slot cr of CTA `lane`
     }
     cl.sync();                                                          // all slots written (and visible) in every CTA
@@ -987,11 +992,13 @@ static int32_t launch_actq_fused(ActqArgs a, int nt, int32_t x_dtype, int64_t M,
     if (M * (K / 8) <= 8 * 8 * kSmallThreads && K / 8 < 65536) {
         // decode-sized block: a cluster of CTAs per tensor (about 4 vectors per thread), no grid rendezvous, programmatic
         // dependent launch (the scratch is not touched)
+        static const int64_t light_max = std::getenv("RWKVQ_ACTQ_LIGHT_MAX") ? std::atoll(std::getenv("RWKVQ_ACTQ_LIGHT_MAX")) : 8 * 8 * kSmallThreadsLight;
+        const int threads = M * (K / 8) <= light_max ? kSmallThreadsLight : kSmallThreads;
         int cluster = 1;
-        while (cluster < 8 && M * (K / 8) > (int64_t)cluster * 4 * kSmallThreads) cluster <<= 1;
+        while (cluster < 8 && M * (K / 8) > (int64_t)cluster * 4 * threads) cluster <<= 1;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3((unsigned)(nt * cluster));
-        cfg.blockDim = dim3(kSmallThreads);
+        cfg.blockDim = dim3((unsigned)threads);
         cfg.stream = st;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
