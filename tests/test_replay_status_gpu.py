@@ -83,10 +83,20 @@ def test_captured_projection_replays_with_new_activations(mods):
             bits_equal(out, want, "replay")
 
 
+@pytest.mark.parametrize("form", ["auto", "two", "coop"])
 @pytest.mark.parametrize("which", ["fp8", "nvfp4"])
-def test_captured_quantizer_with_own_scratch_replays(mods, which):
-    """The raw one-launch quantizer with caller-owned scratch, captured alone: every replay must rendezvous afresh."""
+def test_captured_quantizer_with_own_scratch_replays(mods, monkeypatch, which, form):
+    """The raw fused quantizer with caller-owned scratch, captured alone and replayed with new inputs, in each of its
+    forms: the cluster launch this size takes by default, the two chained launches (their scratch words must be zero
+    again for every replay) and the cooperative launch (every replay must rendezvous afresh: nothing about the
+    rendezvous is fixed at capture time)."""
     abi, f, _ = mods
+    if form != "auto":
+        monkeypatch.setenv("RWKVQ_ACTQ_SMALL_MAX", "0")
+        monkeypatch.setenv("RWKVQ_NVFP4_ACTQ_SMALL_MAX", "0")
+    if form == "coop":
+        monkeypatch.setenv("RWKVQ_ACTQ_TWO_MAX", "0")
+        monkeypatch.setenv("RWKVQ_NVFP4_ACTQ_TWO_MAX", "0")
     L = abi.lib()
     m, k = 96, 2048
     xs = [gen(20 + i, (m, k), s).to(torch.bfloat16).cuda() for i, s in enumerate((40.0, 0.02, 2.0))]
