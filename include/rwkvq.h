@@ -155,6 +155,16 @@ int32_t rwkvq_gemv_int8_preamax(const void* x, int32_t x_dtype, const int8_t* w,
                                 void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, int64_t ldx, int32_t div_mode,
                                 uint32_t flags, void* ffn_scratch, void* stream);
 
+/* The INT8 pair for many rows: rwkvq_tc_gemm_int8_relu2 is rwkvq_tc_gemm_int8 (tiled form, no accumulator output) with
+ * relu_square in its epilogue; it folds the maximum of h per TOKEN ROW into row_max[M] (floats, zero before the call).
+ * rwkvq_actq_int8_given then makes the codes and row scales of h with those maxima (elementwise, no abs-max pass) and
+ * clears them, and rwkvq_tc_gemm_int8 finishes.  Same bits as projection -> relu_square -> projection. */
+int32_t rwkvq_tc_gemm_int8_relu2(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                                 const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                                 uint32_t flags, float* row_max, void* workspace, int64_t workspace_bytes, void* stream);
+int32_t rwkvq_actq_int8_given(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes,
+                              int64_t ldc, float* scales, float* row_max, int32_t div_mode, void* stream);
+
 /* The same pair for many rows (prefill): rwkvq_tc_gemm_fp8_relu2 is rwkvq_tc_gemm_fp8 (tiled form, M >= 17) with
  * relu_square and the amax accumulation in its epilogue; rwkvq_actq_fp8_given then makes the codes of h with the
  * published amax -- purely elementwise, no abs-max pass and no grid rendezvous -- writes its own copies amax_out[0]

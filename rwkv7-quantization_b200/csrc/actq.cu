@@ -806,6 +806,47 @@ __global__ void __launch_bounds__(kThreads) quant_fp8_given_kernel(const void* x
     }
 }
 
+// INT8 codes of h with row maxima that the PRODUCER of h published (the FFN key GEMM with relu^2 in its epilogue):
+// no abs-max pass; one CTA per row, four vectors in flight per thread; the CTA clears its row's maximum when every
+// thread has used it, so the array is zero again for the next producer (graph replay safe).
+template <int DT>
+__global__ void __launch_bounds__(kThreads) quant_int8_given_kernel(const void* x, int8_t* codes, float* scales, float* row_max, int64_t K,
+                                                                    int64_t ldx, int64_t ldc, int div_mode) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t row = blockIdx.x;
+    const char* xrow = reinterpret_cast<const char*>(x) + row * ldx * 2;
+    int8_t* crow = codes + row * ldc;
+    const float m = fmaxf(__ldcg(row_max + row), 1e-12f);
+    const float s = div_mode_f32(127.f, m, div_mode);
+    if (threadIdx.x == 0) scales[row] = div_mode_f32(m, 127.f, div_mode);
+    for (int64_t k0 = (int64_t)threadIdx.x * 8; k0 < K; k0 += (int64_t)kThreads * 8 * 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + (int64_t)j * kThreads * 8;
+            if (k < K) v[j] = *reinterpret_cast<const uint4*>(xrow + k * 2);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = k0 + (int64_t)j * kThreads * 8;
+            if (k >= K) continue;
+            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            uint32_t c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float2 f = cvt2<DT>(w[q]);
+                const uint32_t lo = (uint32_t)(__float2int_rz(fminf(fmaxf(f.x * s, -128.f), 127.f))) & 0xffu;
+                const uint32_t hi = (uint32_t)(__float2int_rz(fminf(fmaxf(f.y * s, -128.f), 127.f))) & 0xffu;
+                c[q] = lo | (hi << 8);
+            }
+            *reinterpret_cast<uint2*>(crow + k) = make_uint2(c[0] | (c[1] << 16), c[2] | (c[3] << 16));
+        }
+    }
+    __syncthreads();                                    // every thread of this CTA has used the maximum
+    if (threadIdx.x == 0) row_max[row] = 0.f;
+}
+
 // A kernel whose only job is to let a bounded wait run out: one CTA waits for an mbarrier phase that nothing
 // completes (mode 0) or for a flag value that nothing stores (mode 1), gives up after `limit_ns`, records
 // RWKVQ_E_TIMEOUT in *status and returns normally -- the path every kernel of this library takes when a producer
@@ -1106,6 +1147,35 @@ int32_t rwkvq_actq_fp8_given(const void* x, int32_t x_dtype, int64_t M, int64_t 
     const cudaError_t e = x_dtype == RWKVQ_F16
         ? cudaLaunchKernelEx(&cfg, quant_fp8_given_kernel<RWKVQ_F16>, x, codes, amax_out, scale_out, ffn, m, K, ldx, ldc, dm, fb)
         : cudaLaunchKernelEx(&cfg, quant_fp8_given_kernel<RWKVQ_BF16>, x, codes, amax_out, scale_out, ffn, m, K, ldx, ldc, dm, fb);
+    if (e != cudaSuccess) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));
+    }
+    return check_launch(who);
+}
+
+int32_t rwkvq_actq_int8_given(const void* x, int32_t x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* codes, int64_t ldc, float* scales,
+                              float* row_max, int32_t div_mode, void* stream) {
+    const char* who = "actq_int8_given";
+    RWKVQ_REQUIRE(x && codes && scales && row_max, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(div_mode == RWKVQ_DIV_IEEE || div_mode == RWKVQ_DIV_FULL, RWKVQ_E_BADARG, "%s: div_mode %d", who, div_mode);
+    RWKVQ_REQUIRE(M > 0 && K > 0 && K % 8 == 0 && M < (1 << 30), RWKVQ_E_SHAPE, "%s: M=%lld K=%lld (K must be a multiple of 8)", who, (long long)M, (long long)K);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K && ldc % 8 == 0 && ldc >= K && ((uintptr_t)codes & 7) == 0 && ((uintptr_t)row_max & 3) == 0,
+                  RWKVQ_E_ALIGN, "%s: rows must be 16-byte (x) / 8-byte (codes) aligned", who);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)M);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    const int dm = div_mode;
+    const cudaError_t e = x_dtype == RWKVQ_F16
+        ? cudaLaunchKernelEx(&cfg, quant_int8_given_kernel<RWKVQ_F16>, x, codes, scales, row_max, K, ldx, ldc, dm)
+        : cudaLaunchKernelEx(&cfg, quant_int8_given_kernel<RWKVQ_BF16>, x, codes, scales, row_max, K, ldx, ldc, dm);
     if (e != cudaSuccess) {
         g_launches.fetch_add(1, std::memory_order_relaxed);
         return fail(RWKVQ_E_LAUNCH, "%s: %s", who, cudaGetErrorString(e));

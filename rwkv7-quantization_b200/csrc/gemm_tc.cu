@@ -55,7 +55,7 @@ struct TcArgs {
     int* status;               // set to RWKVQ_E_TIMEOUT if a bounded wait gave up
     unsigned long long* trace; // optional [grid][16] timestamps of role milestones (profiling aid), else null
     unsigned long long wait_ns; // wall-time limit of every mbarrier wait
-    float* ffn_amax;            // RWKVQ_FLAG_RELU2 (GEMM mode, FP8): maximum of the relu^2 results, atomic max
+    float* ffn_amax;            // RWKVQ_FLAG_RELU2 (GEMM mode): maximum of the relu^2 results, atomic max -- FP8: one word; INT8: one per token row
     const uint8_t* sfa;         // NVFP4 (cluster split-K kernel only): blocked scales of the activation codes ...
     const uint8_t* sfw;         // ... and of the weight codes (rwkvq_nvfp4_pack_scales order)
     TcPush push;                // GEMM mode: also store the result into the peers' buffers and signal them (n = 0: off)
@@ -515,7 +515,7 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 }
                 const float rowscale = actscale * wsc;
                 const bool vec_ok = (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out[p.mat]) & 15) == 0);
-                const bool relu2 = KIND == KIND_F8 && (a.flags & RWKVQ_FLAG_RELU2) != 0;
+                const bool relu2 = (a.flags & RWKVQ_FLAG_RELU2) != 0;
                 const bool hmax_bf16 = (a.flags & RWKVQ_FLAG_AMAX_AFTER_BF16) != 0;
                 float hmax = 0.f;
                 // 16 accumulator columns of this thread's token row -> 8 fp16 pairs (scales, optional bf16 hop, relu^2)
@@ -601,9 +601,13 @@ __global__ void __launch_bounds__(kTcThreads, SWAP ? 2 : 1) gemm_tc_kernel(const
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.tempty[buf]);
-                if (relu2) {                                  // one atomic per warp and tile
-                    hmax = warp_max(hmax);
-                    if (lane == 0 && hmax > 0.f) atomic_max_nonneg(a.ffn_amax, hmax);
+                if (relu2) {
+                    if constexpr (KIND == KIND_F8) {          // one atomic per warp and tile
+                        hmax = warp_max(hmax);
+                        if (lane == 0 && hmax > 0.f) atomic_max_nonneg(a.ffn_amax, hmax);
+                    } else {                                  // INT8 activations are scaled per token row: a thread holds one
+                        if (m < a.M && hmax > 0.f) atomic_max_nonneg(a.ffn_amax + m, hmax);
+                    }
                 }
             }
             ++pc;
@@ -777,7 +781,7 @@ static int32_t run_tc(TcArgs a, const TcCall& c, cudaStream_t st, const char* wh
         a.status = a.counters + kWsCounterInts;
         a.scratch = reinterpret_cast<float*>(reinterpret_cast<char*>(c.workspace) + kWsHeaderBytes);
     } else {
-        if (!pushing && tc2_eligible(c.kind, a.M, a.N, a.K, a.nmat))      // many tokens: CTA pairs on 256 x 256 tiles (gemm_tc2.cu)
+        if (!pushing && tc2_eligible(c.kind, a.M, a.N, a.K, a.nmat) && !(c.kind == KIND_I8 && (a.flags & RWKVQ_FLAG_RELU2)))      // many tokens: CTA pairs on 256 x 256 tiles (gemm_tc2.cu)
             return run_tc2(c.kind, c.codes[0], c.lda, a.a_scale[0], a.amax_is_amax, c.w[0], c.ldw, a.ws[0], a.out[0], a.ldo, a.acc[0], a.ldacc,
                            a.M, a.N, a.K, a.div_mode, a.flags, a.ffn_amax,
                            c.workspace ? reinterpret_cast<int*>(c.workspace) + kWsCounterInts : device_status_ptr(), st, who);
@@ -1099,6 +1103,24 @@ int32_t rwkvq_tc_gemm_fp8_relu2(const uint8_t* a_codes, int64_t lda, const float
     TcCall c{};
     c.kind = KIND_F8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_fp8_relu2");
+}
+
+/* The same for INT8 weights: stores h = fp16(max(y, 0)^2) and folds the maximum of h per TOKEN ROW into row_max[M]
+ * (floats, zero before the call; rwkvq_actq_int8_given reads and clears them).  Tiled GEMM form only (M >= 17 and not
+ * the weight-streaming form); runs the single-CTA kernel at every row count. */
+int32_t rwkvq_tc_gemm_int8_relu2(const int8_t* a_codes, int64_t lda, const float* a_scales, const int8_t* w, int64_t ldw,
+                                 const float* w_scale, void* out_f16, int64_t ldo, int64_t M, int64_t N, int64_t K, uint32_t flags,
+                                 float* row_max, void* workspace, int64_t workspace_bytes, void* stream) {
+    RWKVQ_REQUIRE(row_max != nullptr && ((uintptr_t)row_max & 3) == 0, RWKVQ_E_BADARG, "tc_gemm_int8_relu2: row_max must be M floats");
+    RWKVQ_REQUIRE(!takes_swap_route(M, N, K, 1, false), RWKVQ_E_SHAPE, "tc_gemm_int8_relu2: M=%lld runs the weight-streaming form; use rwkvq_gemv_int8_relu2 for few rows",
+                  (long long)M);
+    TcArgs a{};
+    a.a_scale[0] = a_scales; a.ws[0] = w_scale; a.out[0] = (__half*)out_f16;
+    a.ffn_amax = row_max;
+    fill_common(a, 1, M, N, K, 0, ldo, RWKVQ_DIV_IEEE, flags | RWKVQ_FLAG_RELU2);
+    TcCall c{};
+    c.kind = KIND_I8; c.w[0] = w; c.ldw = ldw; c.codes[0] = a_codes; c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
+    return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8_relu2");
 }
 
 /* rwkvq_tc_gemm_fp8 without a caller workspace: the split-K partial sums, arrival counters and status word live in

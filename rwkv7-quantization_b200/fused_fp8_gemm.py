@@ -559,11 +559,26 @@ def ffn_relu2_fp8(x, key_info, value_info, out_dtype=torch.float16, return_hidde
     return (out, hid.reshape(*x.shape[:-1], f_dim)) if return_hidden else out
 
 
+_row_max = {}
+
+
+def _row_max_scratch(device, rows: int) -> torch.Tensor:
+    """Zeroed floats, one per token row, per (device, stream): the key GEMM of the INT8 FFN pair folds the rows' maxima
+    into them and the quantizer behind it clears them again."""
+    key = (torch.device(device).index or 0, torch.cuda.current_stream().cuda_stream)
+    buf = _row_max.get(key)
+    if buf is None or buf.numel() < rows:
+        buf = _row_max[key] = torch.zeros(max(rows, 4096), dtype=torch.float32, device=device)
+    return buf
+
+
 def ffn_relu2_int8(x, key_info, value_info, out_dtype=torch.float16, return_hidden=False):
     """ffn_relu2_fp8 for INT8 weights.  Up to 8 rows: two launches, relu_square in the key projection's epilogue, which
     publishes the maximum of its result per token row (INT8 activations are scaled per row), and a value projection
-    that quantizes with those maxima instead of reducing the hidden activations again.  More rows: the three steps.
-    Results equal the three-step chain bit for bit."""
+    that quantizes with those maxima instead of reducing the hidden activations again.  Row counts that run the tiled
+    tensor-core GEMM: four launches (quantizer, key GEMM with relu_square and the row maxima in its epilogue, an
+    elementwise given-maxima quantizer, value GEMM).  Other row counts: the three steps.  Results equal the three-step
+    chain bit for bit."""
     wk, sk = key_info["weight"], key_info["tensor_scale"]
     wv, sv = value_info["weight"], value_info["tensor_scale"]
     x2 = _rows16(x)
@@ -580,6 +595,25 @@ def ffn_relu2_int8(x, key_info, value_info, out_dtype=torch.float16, return_hidd
         abi.call("rwkvq_gemv_int8_preamax", hid.data_ptr(), abi.F16, wv.data_ptr(), wv.stride(0), sv.data_ptr(),
                  out.data_ptr(), out.stride(0), m, n, f_dim, f_dim, abi.DEFAULT_DIV, 0, sc.data_ptr(), st)
         abi.after_call()
+    elif ROUTE == "auto" and m > GEMV_M_MAX and k % 16 == 0 and f_dim % 16 == 0 and can_push(m, f_dim, k):
+        # many rows on the tiled GEMM (can_push: neither the weight-streaming nor the cluster form takes these sizes)
+        dev_, st = x2.device, abi.stream_ptr()
+        codes = torch.empty((m, k), dtype=torch.int8, device=dev_)
+        xs = torch.empty(m, dtype=torch.float32, device=dev_)
+        hid = torch.empty((m, f_dim), dtype=torch.float16, device=dev_)
+        hcodes = torch.empty((m, f_dim), dtype=torch.int8, device=dev_)
+        hs = torch.empty(m, dtype=torch.float32, device=dev_)
+        out = abi.new_out(m, n, dev_)
+        rowmax = _row_max_scratch(dev_, m)
+        abi.call("rwkvq_prep_x_int8", x2.data_ptr(), abi.dtype_code(x2), m, k, x2.stride(0), codes.data_ptr(), k, xs.data_ptr(), abi.DEFAULT_DIV, st)
+        ws = abi.workspace(min(m, 128), max(f_dim, n), max(k, f_dim), 1, dev_)
+        abi.call("rwkvq_tc_gemm_int8_relu2", codes.data_ptr(), k, xs.data_ptr(), wk.data_ptr(), wk.stride(0), sk.data_ptr(), hid.data_ptr(), f_dim,
+                 m, f_dim, k, 0, rowmax.data_ptr(), ws.data_ptr(), ws.numel(), st)
+        abi.call("rwkvq_actq_int8_given", hid.data_ptr(), abi.F16, m, f_dim, f_dim, hcodes.data_ptr(), f_dim, hs.data_ptr(), rowmax.data_ptr(),
+                 abi.DEFAULT_DIV, st)
+        abi.call("rwkvq_tc_gemm_int8", hcodes.data_ptr(), f_dim, hs.data_ptr(), wv.data_ptr(), wv.stride(0), sv.data_ptr(), out.data_ptr(),
+                 out.stride(0), None, 0, m, n, f_dim, 0, ws.data_ptr(), ws.numel(), st)
+        abi.after_call(ws)
     else:
         hid = linear_int8_fused(x2, key_info)
         hid = (hid.float().clamp_(min=0.0) ** 2).to(torch.float16)       # relu_square: fp16(max(y, 0)^2), fp32 arithmetic

@@ -97,6 +97,8 @@ SIGNATURES = {
     "rwkvq_gemv_batch": [_p, _i32, _p],
     "rwkvq_tc_gemm_fp8_relu2": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p, _i64, _p],
     "rwkvq_actq_fp8_given": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _i32, _u32, _p],
+    "rwkvq_actq_int8_given": [_p, _i32, _i64, _i64, _i64, _p, _i64, _p, _p, _i32, _p],
+    "rwkvq_tc_gemm_int8_relu2": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _u32, _p, _p, _i64, _p],
     "rwkvq_gemv_fp8_relu2": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],
     "rwkvq_gemv_fp8_preamax": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],
     "rwkvq_gemv_int8_relu2": [_p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i64, _i32, _u32, _p, _p],

@@ -393,10 +393,11 @@ def test_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
 
 
 @pytest.mark.parametrize("m,dt", [(1, torch.bfloat16), (2, torch.float16), (3, torch.bfloat16), (5, torch.float16), (8, torch.bfloat16),
-                                  (8, torch.float16), (20, torch.bfloat16)])
+                                  (8, torch.float16), (20, torch.bfloat16), (40, torch.bfloat16), (300, torch.float16), (600, torch.bfloat16)])
 def test_int8_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
     """The pair on INT8 weights (per-row maxima published by the key projection): bit-equal to the three steps run
-    separately and to the oracle's chain; two launches up to 8 rows; the scratch is left clean; rows whose hidden
+    separately and to the oracle's chain; two launches up to 8 rows, four on the tiled GEMM (quantizer, key GEMM with
+    relu_square and row maxima, given-maxima quantizer, value GEMM); the scratch is left clean; rows whose hidden
     activations are all zero (negative key results only) keep the quantizer's floor."""
     abi, f, _ = mods
     c, ff = 768, 3072
@@ -421,6 +422,9 @@ def test_int8_ffn_relu2_pair_equals_three_step_chain(mods, m, dt):
         if m <= 8:
             assert launches == 2
             assert int(f.ffn_scratch("cuda").abs().sum().item()) == 0
+        if m > 32:
+            assert launches == 4
+            assert float(f._row_max_scratch("cuda", m).abs().sum().item()) == 0.0
     if m <= 8:
         from rwkvq_layer import DecodeLayer
         qs, ss = O.q_int8_sym(gen(163, (c, c), 0.02, torch.float16))
