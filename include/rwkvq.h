@@ -416,6 +416,14 @@ int32_t rwkvq_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, cons
 int64_t rwkvq_nvfp4_blocked_scale_bytes(int64_t rows, int64_t K);
 int32_t rwkvq_nvfp4_pack_scales(const uint8_t* block_scales, int64_t lds, int64_t rows, int64_t K, uint8_t* blocked,
                                 void* stream);
+/* NVFP4 projection of one to four tokens in ONE launch: the cluster split-K kernel with the activation quantization
+ * inside (each CTA quantizes its K slice, the abs-max crosses the cluster through distributed shared memory).  Same
+ * bits as rwkvq_actq_nvfp4_fused followed by rwkvq_tc_gemm_nvfp4.  x: [M, ldx] fp16 / bf16, rows 16-byte aligned;
+ * weights as for rwkvq_tc_gemm_nvfp4 (packed codes, BLOCKED scales).  Sizes for which ..._route() returns 1. */
+int32_t rwkvq_tc_gemv_nvfp4_fused_route(int64_t M, int64_t N, int64_t K);
+int32_t rwkvq_tc_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, const uint8_t* w_codes, int64_t ldw,
+                                  const uint8_t* w_scales_blocked, const float* w_tscale, void* out_f16, int64_t ldo,
+                                  int64_t M, int64_t N, int64_t K, void* stream);
 /* 1 if rwkvq_tc_gemm_nvfp4 runs these sizes on the cluster split-K kernel (up to 256 tokens against few row tiles:
  * weights as the 128-row operand, K split across a thread-block cluster), 0 for the tiled form */
 int32_t rwkvq_tc_gemm_nvfp4_cluster_route(int64_t M, int64_t N, int64_t K);

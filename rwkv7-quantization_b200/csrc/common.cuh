@@ -92,6 +92,24 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_codes) {
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(c));
     return r;
 }
+
+// two floats -> one byte of two e2m1 codes (lo in the low nibble), round-to-nearest-even, saturating
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+    unsigned short r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t)r;
+}
+// one byte of two e2m1 codes -> f16 pair (low nibble in the low half), exact
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
+    uint32_t r;
+    const unsigned short b = (unsigned short)(byte & 0xffu);
+    asm("{ .reg .b8 t; cvt.u8.u16 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(r) : "h"(b));
+    return r;
+}
+__device__ __forceinline__ float e4m3_to_float(uint32_t code) {
+    const uint32_t h2 = e4m3x2_to_f16x2(code & 0xffu);
+    return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
+}
 __device__ __forceinline__ float clamp448(float v) { return fminf(fmaxf(v, -448.f), 448.f); }
 
 __device__ __forceinline__ float warp_max(float v) {

@@ -727,6 +727,7 @@ static unsigned long long* g_trace = nullptr;
 }  // namespace rwkvq
 
 #include "gemm_tcs.cuh"        // few tokens: K split across a thread-block cluster, partial sums through distributed shared memory
+#include "gemm_tcsn.cuh"       // NVFP4, one to four tokens: the same with the activation quantization inside (one launch)
 
 namespace rwkvq {
 
@@ -1085,6 +1086,28 @@ int32_t rwkvq_tc_gemm_int8_rkv(const int8_t* codes_r, const int8_t* codes_k, con
     c.kind = KIND_I8; c.w[0] = wr; c.w[1] = wk; c.w[2] = wv; c.ldw = ldw; c.codes[0] = codes_r; c.codes[1] = codes_k; c.codes[2] = codes_v;
     c.lda = lda; c.workspace = workspace; c.workspace_bytes = workspace_bytes;
     return run_tc(a, c, (cudaStream_t)stream, "tc_gemm_int8_rkv");
+}
+
+/* NVFP4 projection of one to four tokens in ONE launch (activation quantization inside the cluster split-K kernel);
+ * same bits as rwkvq_actq_nvfp4_fused followed by rwkvq_tc_gemm_nvfp4.  Sizes: rwkvq_tc_gemv_nvfp4_fused_route() == 1. */
+int32_t rwkvq_tc_gemv_nvfp4_fused_route(int64_t M, int64_t N, int64_t K) { return tcsn_eligible(M, N, K) ? 1 : 0; }
+
+int32_t rwkvq_tc_gemv_nvfp4_fused(const void* x, int32_t x_dtype, int64_t ldx, const uint8_t* w_codes, int64_t ldw,
+                                  const uint8_t* w_scales_blocked, const float* w_tscale, void* out_f16, int64_t ldo, int64_t M, int64_t N,
+                                  int64_t K, void* stream) {
+    const char* who = "tc_gemv_nvfp4_fused";
+    RWKVQ_REQUIRE(x && w_codes && w_scales_blocked && w_tscale && out_f16, RWKVQ_E_BADARG, "%s: null pointer", who);
+    RWKVQ_REQUIRE(x_dtype == RWKVQ_F16 || x_dtype == RWKVQ_BF16, RWKVQ_E_BADARG, "%s: x_dtype %d", who, x_dtype);
+    RWKVQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && ldo >= N, RWKVQ_E_SHAPE, "%s: negative size or ldo < N", who);
+    if (M == 0 || N == 0) return RWKVQ_OK;
+    RWKVQ_REQUIRE(tcsn_eligible(M, N, K), RWKVQ_E_SHAPE, "%s: M=%lld N=%lld K=%lld is not served by the one-launch kernel (see %s_route)", who,
+                  (long long)M, (long long)N, (long long)K, who);
+    RWKVQ_REQUIRE(aligned16(x) && ldx % 8 == 0 && ldx >= K, RWKVQ_E_ALIGN, "%s: activation rows must be 16-byte aligned", who);
+    RWKVQ_REQUIRE(aligned16(w_scales_blocked), RWKVQ_E_ALIGN, "%s: blocked scales must be 16-byte aligned", who);
+    TcArgs a{};
+    a.x[0] = x; a.ws[0] = w_tscale; a.out[0] = (__half*)out_f16; a.sfw = w_scales_blocked;
+    a.nmat = 1; a.M = (int)M; a.N = (int)N; a.K = (int)K; a.ldx = ldx; a.ldo = ldo; a.div_mode = RWKVQ_DIV_IEEE; a.flags = 0;
+    return run_tcsn(a, w_codes, ldw, x_dtype, (cudaStream_t)stream, who);
 }
 
 /* rwkvq_tc_gemm_fp8 (tiled GEMM form, M >= 17) with the engine's relu_square folded into the epilogue: stores

@@ -23,6 +23,7 @@ import rwkvq_abi as abi
 E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 BLOCK = 16
 GEMV_ROWS = 16
+ONE_LAUNCH = os.environ.get("RWKVQ_NVFP4_ONE_LAUNCH", "0") == "1"   # 1-4 tokens: quantization inside the cluster kernel (see linear_nvfp4)
 TC_LONG_K = int(os.environ.get("RWKVQ_NVFP4_TC_LONG_K", "8192"))   # rows this long go to the tensor-core route at every token count
 TC_WIDE_N = int(os.environ.get("RWKVQ_NVFP4_TC_WIDE_N", "8192"))   # this many weight rows: from 3 tokens on
 TC_MIN_M = int(os.environ.get("RWKVQ_NVFP4_TC_MIN_M", "8"))   # more tokens than this go to the tensor-core GEMM (measured: from 9 rows it is as fast or faster on the 7.2B shapes)
@@ -165,6 +166,18 @@ def linear_nvfp4(x, weight_info, out_dtype=torch.float16, push=None):
         out = abi.new_out(m, n, x2.device)
         abi.call("rwkvq_gemv_nvfp4_fused", x2.data_ptr(), abi.dtype_code(x2), k, w.data_ptr(), w.stride(0), wbs.data_ptr(),
                  wbs.stride(0), wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.stream_ptr())
+        out = out.reshape(*x.shape[:-1], n)
+        return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
+    if (ONE_LAUNCH and route == "tc" and push is None and 0 < m <= 4 and os.environ.get("RWKVQ_NVFP4_ROUTE", "auto") == "auto"
+            and abi.lib().rwkvq_tc_gemv_nvfp4_fused_route(m, n, k)):
+        # one to four tokens in ONE launch: the activation quantization runs inside the cluster split-K kernel (same bits as
+        # the quantizer launch followed by the GEMM).  Opt-in: measured as fast or slower than the two launches (FFN value,
+        # one token: 14.0 against 12.8 us; FFN key: 12.2 against 12.0) -- the quantizer launch already runs under the
+        # GEMM's weight prefetch, and inside the kernel the MMAs wait for the same abs-max exchange.
+        out = abi.new_out(m, n, x2.device)
+        w_blk = _blocked_weight_scales(weight_info, k)
+        abi.call("rwkvq_tc_gemv_nvfp4_fused", x2.data_ptr(), abi.dtype_code(x2), k, w.data_ptr(), w.stride(0), w_blk.data_ptr(),
+                 wts.data_ptr(), out.data_ptr(), out.stride(0), m, n, k, abi.stream_ptr())
         out = out.reshape(*x.shape[:-1], n)
         return out if out_dtype in (None, out.dtype) else out.to(out_dtype)
     codes, bs, pts = quantize_activations_nvfp4(x, blocked=(route == "tc"))

@@ -62,6 +62,8 @@ SIGNATURES = {
     "rwkvq_tc_gemm_int8_push": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _u32, _p, _i64, _p, _p, _i32, _u32, _p],
     "rwkvq_tc_cluster_gemv_route": [_i64, _i64, _i64],
     "rwkvq_tc_gemm_nvfp4_cluster_route": [_i64, _i64, _i64],
+    "rwkvq_tc_gemv_nvfp4_fused_route": [_i64, _i64, _i64],
+    "rwkvq_tc_gemv_nvfp4_fused": [_p, _i32, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _i64, _p],
     "rwkvq_tc_cluster_gemv_fp8": [_p, _i32, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p],
     "rwkvq_tc_gemm_fp8_push": [_p, _i64, _p, _i32, _p, _i64, _p, _p, _i64, _i64, _i64, _i64, _i32, _u32, _p, _i64, _p, _p, _i32, _u32, _p],
     "rwkvq_tc_gemm_int8": [_p, _i64, _p, _p, _i64, _p, _p, _i64, _p, _i64, _i64, _i64, _i64, _u32, _p, _i64, _p],

@@ -173,6 +173,38 @@ def test_few_tokens_take_the_tensor_core_route_where_it_is_faster(nf, monkeypatc
         assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 16384), (2, 136, 16384), (4, 384, 16384), (3, 16384, 4096), (4, 4096, 8192), (1, 130, 2048)])
+def test_one_launch_cluster_kernel_equals_quantizer_plus_gemm(nf, monkeypatch, dt, m, n, k):
+    """One to four tokens against long rows or many weight rows: the activation quantization runs INSIDE the cluster
+    split-K kernel (one launch).  Same bits as the quantizer launch followed by the cluster GEMM; within 1e-2 of the
+    oracle; a zero row and a second call in a row."""
+    import rwkvq_abi as abi
+    w = gen(n * 5 + k, (n, k), (1.0 / k) ** 0.5)
+    info = dev(nf.quantize_to_nvfp4(w))
+    x = gen(m + 17, (m, k), 1.0).to(dt)
+    if m > 1:
+        x[m - 1].zero_()
+    monkeypatch.setenv("RWKVQ_NVFP4_ROUTE", "auto")
+    monkeypatch.setattr(nf, "TC_LONG_K", 0)                      # every size of this test takes the tensor-core route
+    monkeypatch.setattr(nf, "ONE_LAUNCH", True)                  # opt-in form
+    assert abi.lib().rwkvq_tc_gemv_nvfp4_fused_route(m, n, k) == 1
+    out = nf.linear_nvfp4(x.cuda(), info)                        # the first call also packs the weight scales (cached)
+    before = abi.launch_count()
+    again = nf.linear_nvfp4(x.cuda(), info)
+    assert abi.launch_count() - before == 1
+    torch.cuda.synchronize()
+    assert abi.device_status() == 0
+    assert torch.equal(out, again)
+    monkeypatch.setenv("RWKVQ_TCSN", "0")                        # quantizer launch + cluster GEMM
+    assert abi.lib().rwkvq_tc_gemv_nvfp4_fused_route(m, n, k) == 0
+    two = nf.linear_nvfp4(x.cuda(), info)
+    assert torch.equal(out, two)
+    oinfo = {"weight": info["weight"].cpu(), "block_scale": info["block_scale"].cpu().view(torch.uint8),
+             "tensor_scale": info["tensor_scale"].cpu()}
+    assert rel_err(out, O.linear_nvfp4(x, oinfo)) <= 1e-2
+
+
 @pytest.mark.parametrize("m,n,k", [(16, 256, 4096), (9, 136, 16384), (64, 384, 8192), (200, 256, 16384), (256, 130, 16384), (33, 512, 2048)])
 def test_cluster_splitk_route(nf, monkeypatch, m, n, k):
     """Few tokens against a long K: the weights become the 128-row operand and K is split across a thread-block cluster
