@@ -11,6 +11,10 @@
 // shared memory that stays put (16 rows x 128 bytes + 2 KB of scales per step), while the TMA warp streams only the
 // weights and their scale chunks.  Amax, tensor scale, block scales, codes and the K split are those of
 // rwkvq_actq_nvfp4_fused followed by the cluster kernel, so the results are the same bits.
+// Measured as fast or SLOWER than those two launches (FFN value [4096, 16384], one token: 14.0 against 12.8 us; FFN key
+// [16384, 4096]: 12.2 against 12.0): the separate quantizer is one small cluster launch that already runs under the
+// GEMM's weight prefetch, and here the MMAs wait for the same abs-max exchange inside a heavier CTA.  Kept as an entry
+// point of its own (rwkvq_tc_gemv_nvfp4_fused); the Python dispatcher takes it only on request.
 //
 // Included by gemm_tc.cu after gemm_tcs.cuh (shares its argument structs, tensor maps and cluster helpers).
 #pragma once
