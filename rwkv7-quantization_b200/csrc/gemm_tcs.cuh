@@ -1,6 +1,6 @@
-// W8A8 GEMM for FEW tokens (decode batches, short prefill chunks: up to 256 rows) on pre-quantized codes: the weights
-// are the 128-row operand of tcgen05.mma, the tokens the other one (16 ... 128 per tile), and K is split across a
-// THREAD-BLOCK CLUSTER.
+// GEMM for FEW tokens (decode batches, short prefill chunks: up to 256 rows) on pre-quantized codes -- FP8 and INT8
+// (W8A8) and, with block-scaled MMAs, NVFP4 (W4A4): the weights are the 128-row operand of tcgen05.mma, the tokens the
+// other one (16 ... 128 per tile), and K is split across a THREAD-BLOCK CLUSTER.
 //
 // Why.  With few tokens the projection is a pure weight stream, and a matrix has far fewer 128-row tiles than the GPU
 // has SMs (N = 4096: 32), so every tile's K range has to be shared by several CTAs.  Sharing it through global memory
@@ -18,6 +18,11 @@
 // ring loads weights BEFORE the dependency wait of programmatic dependent launch: they do not depend on the
 // activation quantizer that runs in front.  Every wait is bounded; all CTAs of a cluster meet at a cluster barrier
 // before any of them exits, so no CTA's shared memory is written after it has gone.
+//
+// NVFP4 (KIND_NF4): a ring stage carries 256 values of k per row (128 bytes of packed e2m1 codes) plus the 2 KB chunk
+// of e4m3 block scales of the weight tile and of the token tile (the blocked order of rwkvq_nvfp4_pack_scales); the
+// MMA issuer copies the chunks to tensor memory with tcgen05.cp (two alternating column sets behind the accumulator)
+// and issues four tcgen05.mma.kind::mxf4nvf4.block_scale of K = 64 per stage.  Exchange and final pass are the same.
 //
 // Included by gemm_tc.cu (shares its argument structs and tensor maps).
 #pragma once

@@ -936,7 +936,6 @@ int32_t rwkvq_actq_nvfp4_fused(const void* x, int32_t x_dtype, int64_t M, int64_
         const int kv = (int)(K / 8);
         int cpr = 1;                                     // CTAs per row: about two CTAs per SM in all, 256+ vectors each
         while ((int64_t)M * cpr < 2 * (int64_t)sm_count() && cpr * 2 * kNfTwoThreads <= kv) cpr <<= 1;
-        if (const char* e = std::getenv("RWKVQ_NVFP4_ACTQ_CPR")) cpr = std::max(1, std::atoi(e));
         const int rows = (int)std::min<int64_t>(M, std::max<int64_t>(1, 4 * (int64_t)sm_count() / cpr));
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3((unsigned)(rows * cpr));
