@@ -177,6 +177,11 @@ class ColumnSplitLinear:
 
     PUSH_MAX_ROWS_WIDE = 512
 
+    @classmethod
+    def auto_pushes(cls, world: int, rows: int) -> bool:
+        """gather="auto": does a call of `rows` rows on `world` ranks push (True) or pull (False)?"""
+        return world <= 4 or rows <= cls.PUSH_MAX_ROWS_WIDE
+
     def __init__(self, weight_info: dict, linear_fn, group=None, already_sliced: bool = False, gather: str = "nccl", max_rows: int = 4096):
         if gather not in ("nccl", "peer", "push", "auto"):
             raise ValueError(f"gather must be 'nccl', 'peer', 'push' or 'auto', got {gather!r}")
@@ -197,7 +202,7 @@ class ColumnSplitLinear:
             import rwkvq_abi as abi
             x2 = x.reshape(-1, x.shape[-1])
             pushing = False
-            if self.push and not (self.auto and self.world > 4 and x2.shape[0] > self.PUSH_MAX_ROWS_WIDE):
+            if self.push and (not self.auto or self.auto_pushes(self.world, x2.shape[0])):
                 if self.local.get("qtype") == "nvfp4":
                     import nvfp4_ops
                     pushing = nvfp4_ops.can_push(x2.shape[0], x2.shape[1])

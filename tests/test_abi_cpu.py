@@ -144,6 +144,15 @@ def test_int4_k_split_plan_is_host_arithmetic():
     assert sl(17, 4096, 4096) == 0 and sl(4, 4096, 1000) == 0 and sl(0, 4096, 4096) == 0
 
 
+def test_column_split_auto_gather_rule():
+    """gather="auto": push up to 4 ranks at every row count, on more ranks only up to 512 rows (measured basis in the
+    class's docstring); the rule depends on sizes only, so all ranks agree."""
+    import rwkvq_dist as D
+    C = D.ColumnSplitLinear
+    assert C.auto_pushes(2, 1) and C.auto_pushes(2, 4096) and C.auto_pushes(4, 100000)
+    assert C.auto_pushes(8, 256) and C.auto_pushes(8, 512) and not C.auto_pushes(8, 513) and not C.auto_pushes(8, 4096)
+
+
 def test_column_split_rejects_unknown_gather():
     import rwkvq_dist as D
     with pytest.raises(ValueError):
