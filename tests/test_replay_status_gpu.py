@@ -572,3 +572,43 @@ def test_pushing_epilogue_on_one_gpu(mods, scheme, m, n, k):
             assert bool((b[:, :col0] == -7.0).all()) and bool((b[:, col0 + n:] == -7.0).all())
         assert flags[1].item() == epoch and flags[2].item() == epoch and flags[0].item() == 0
     assert abi.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------ results into a column range
+@pytest.mark.parametrize("scheme,m,n,k", [("fp8", 16, 256, 4096), ("fp8", 200, 384, 16384), ("int8", 40, 256, 4096),
+                                           ("nvfp4", 16, 256, 16384), ("nvfp4", 200, 384, 16384), ("nvfp4", 256, 2048, 4096),
+                                           ("nvfp4", 2, 256, 16384)])
+def test_cluster_kernels_write_into_a_column_range(mods, monkeypatch, scheme, m, n, k):
+    """What a column-split projection does on every rank: the projection writes its [M, N] result into a column range of
+    a wider buffer (leading dimension 3 N).  Sizes that run the cluster split-K kernels (and, for two tokens of NVFP4,
+    the one-launch form): the range equals the plain call bit for bit and the neighbouring columns stay untouched."""
+    import nvfp4_ops
+    abi, f, fp8_ops = mods
+    x = gen(600 + m, (m, k), 1.0).to(torch.bfloat16).cuda()
+
+    def takes_cluster_kernel(m, n, k):
+        # up to 32 rows the one-launch route query covers the same sizes; above 48 rows (no weight-streaming form) a
+        # tensor-core call that cannot carry a push is one the cluster kernel takes
+        L = abi.lib()
+        return L.rwkvq_tc_cluster_gemv_route(m, n, k) == 1 if m <= 32 else (m > 48 or k < 8192) and L.rwkvq_tc_gemm_can_push(m, n, k) == 0
+    if scheme == "fp8":
+        info = dev(fp8_weight(601, n, k))
+        assert takes_cluster_kernel(m, n, k)
+    elif scheme == "int8":
+        q, s = O.q_int8_sym(gen(602, (n, k), 0.02, torch.float16))
+        info = dev({"weight": q, "tensor_scale": s, "qtype": "int8"})
+        assert takes_cluster_kernel(m, n, k)
+    else:
+        info = {kk: (v.cuda() if torch.is_tensor(v) else v) for kk, v in nvfp4_ops.quantize_to_nvfp4(gen(603, (n, k), (1.0 / k) ** 0.5).cuda()).items()}
+        assert abi.lib().rwkvq_tc_gemm_nvfp4_cluster_route(m, n, k) == 1
+        if m <= 4:
+            monkeypatch.setattr(nvfp4_ops, "ONE_LAUNCH", True)
+    lin = fp8_ops.linear_quantized if scheme == "nvfp4" else fp8_ops.linear_quantized_fused
+    plain = lin(x, info)
+    buf = torch.full((m, 3 * n), -7.0, dtype=torch.float16, device="cuda")
+    with abi.output_into(buf[:, n:2 * n]):
+        lin(x, info)
+    torch.cuda.synchronize()
+    bits_equal(buf[:, n:2 * n], plain, f"{scheme} column range")
+    assert bool((buf[:, :n] == -7.0).all()) and bool((buf[:, 2 * n:] == -7.0).all())
+    assert abi.device_status() == 0
