@@ -49,12 +49,31 @@ _ACTQ_FUSED = os.environ.get("RWKVQ_ACTQ", "fused") == "fused"   # one cooperati
 CODES_M_MIN = int(os.environ.get("RWKVQ_CODES_M_MIN", "9"))      # rows from which the decode GEMV runs on pre-quantized codes
 TC_M_MIN = int(os.environ.get("RWKVQ_TC_M_MIN", "33"))          # rows from which the tensor-memory kernels take over from the decode GEMVs (never below 9)
 CODES_MK_MIN = 49152       # ... and already from 3 rows when the block is this large (long rows: K = 16384); measured
+# FP8, rows from which the cluster split-K tensor-core kernel takes over from the codes GEMV where it applies (matrices
+# with few 128-row tiles, e.g. N = 4096).  Measured on [4096, 4096]: 16 rows 8.7 (GEMV) against 9.2 us, 20 rows 10.4 against
+# 9.3, 28 rows 10.8 against 9.3; r/k/v: 16 rows 15.5 against 17.9, 20 rows 21.1 against 18.0, 28 rows 22.2 against 19.0
+# (from 17 rows the GEMV works on three token tiles).  With many row tiles (N = 16384) the GEMV stays ahead up to 32 rows.
+CLUSTER_FROM_M = int(os.environ.get("RWKVQ_CLUSTER_FROM_M", "17"))
 _decode_route_cache: dict = {}
+_tc_route_cache: dict = {}
 
 
-def _codes_gemv_fits(m: int, k: int) -> bool:
+def _takes_tc(m: int, k: int, n=None) -> bool:
+    """Do `m` rows go to the tensor-memory kernels instead of the decode GEMVs?  Always from TC_M_MIN rows; FP8 callers
+    that pass the matrix's row count `n` also from CLUSTER_FROM_M rows where the cluster split-K kernel applies."""
+    if m >= TC_M_MIN and m > 8:
+        return True
+    if n is None or m < max(CLUSTER_FROM_M, 9) or m > GEMV_M_MAX or ROUTE != "auto" or k % 16 or not _ACTQ_FUSED:
+        return False
+    hit = _tc_route_cache.get((m, n, k))
+    if hit is None:
+        hit = _tc_route_cache[(m, n, k)] = bool(abi.lib().rwkvq_tc_cluster_gemv_route(m, n, k))
+    return hit
+
+
+def _codes_gemv_fits(m: int, k: int, n=None) -> bool:
     """The decode GEMV on pre-quantized codes: CODES_M_MIN..32 rows whose 1-byte code tile fits shared memory."""
-    if not (m >= CODES_M_MIN or (m >= 3 and m * k >= CODES_MK_MIN and CODES_M_MIN <= GEMV_M_MAX)) or m > GEMV_M_MAX or (m >= TC_M_MIN and m > 8) or ROUTE != "auto" or k % 16:
+    if not (m >= CODES_M_MIN or (m >= 3 and m * k >= CODES_MK_MIN and CODES_M_MIN <= GEMV_M_MAX)) or m > GEMV_M_MAX or ROUTE != "auto" or k % 16 or _takes_tc(m, k, n):
         return False
     fits = _decode_route_cache.get((m, k))
     if fits is None:
@@ -81,10 +100,10 @@ def _unpack(weight_info_or_w, res_scale=None):
     return weight_info_or_w, res_scale
 
 
-def _gemv_fits(m: int, k: int, fp8: bool = True) -> bool:
+def _gemv_fits(m: int, k: int, fp8: bool = True, n=None) -> bool:
     """The fused mma.sync GEMV keeps the quantized activations in shared memory (FP8: 2 bytes each, INT8: 1)."""
     pitch = (2 * k + 127) // 128 * 128 + 16 if fp8 else (k + 127) // 128 * 128 + 64
-    if not (0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0) or (m >= TC_M_MIN and m > 8 and ROUTE == "auto"):
+    if not (0 < m <= GEMV_M_MAX and m * pitch <= _GEMV_SMEM_BUDGET and k % 16 == 0) or (ROUTE == "auto" and _takes_tc(m, k, n)):
         return False
     return ROUTE == "mma" or (ROUTE == "auto" and m <= GEMV_AUTO_M_MAX)
 
@@ -387,9 +406,9 @@ def linear_fp8_fused(x, weight_info_or_w, res_scale=None, out_dtype=torch.float1
     x2 = _rows16(x)
     if _CLUSTER_FIRST and _cluster_one_launch(m, w.shape[0], k):
         out = _fp8_cluster_gemv(x2, _u8(w), w_ts)
-    elif _codes_gemv_fits(m, k) and _ACTQ_FUSED and k % 8 == 0:
+    elif _codes_gemv_fits(m, k, w.shape[0]) and _ACTQ_FUSED and k % 8 == 0:
         out = _fp8_codes_gemv(x2, _u8(w), w_ts)
-    elif _tc_fused_fits(m, k) or _gemv_fits(m, k):
+    elif _tc_fused_fits(m, k) or _gemv_fits(m, k, n=w.shape[0]):
         out = _fp8_gemv(x2, _u8(w), w_ts, None, 0)
     elif _cluster_one_launch(m, w.shape[0], k):
         # where the two-launch route would run the cluster split-K kernel anyway: the same kernel with the activation
@@ -449,7 +468,8 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
     same_ld = len({w.stride(0) for w in ws_}) == 1 and all(w.shape == ws_[0].shape for w in ws_) and len(wflags) == 1
     wflag = next(iter(wflags)) if len(wflags) == 1 else 0
     f32 = lambda a: None if a is None else a.to(device=dev, dtype=torch.float32).contiguous()
-    if (_codes_gemv_fits(m, k) and _ACTQ_FUSED and same_ld and awq_r is None and awq_k is None and k % 8 == 0):
+    n_route = n if (awq_r is None and awq_k is None and same_ld) else None      # the cluster kernel runs on plain codes of like matrices
+    if (_codes_gemv_fits(m, k, n_route) and _ACTQ_FUSED and same_ld and awq_r is None and awq_k is None and k % 8 == 0):
         outs = _fp8_codes_gemv_rkv([t.contiguous() for t in xs], ws_, [i["tensor_scale"] for i in (wr_info, wk_info, wv_info)])
     elif _tc_fused_fits(m, k, 3) and same_ld:
         xs = [t.contiguous() for t in xs]
@@ -462,7 +482,7 @@ def linear_rkv_fused(xr, xk, xv, wr_info, wk_info, wv_info, out_dtype=torch.floa
                  wv_info["tensor_scale"].data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), n,
                  m, n, k, k, abi.DEFAULT_DIV, wflag, ws.data_ptr(), ws.numel(), abi.stream_ptr())
         abi.after_call(ws)
-    elif _gemv_fits(m, k) and same_ld:
+    elif _gemv_fits(m, k, n=n_route) and same_ld:
         xs = [t.contiguous() for t in xs]
         outs = [torch.empty((m, n), dtype=torch.float16, device=dev) for _ in range(3)]
         awq_r, awq_k = f32(awq_r), f32(awq_k)
