@@ -551,6 +551,10 @@ def colsplit_leg(world, dev, dist_on):
         row["peer_vs_nccl_e2e"] = round(row["nccl_e2e_us"] / row["peer_e2e_us"], 2)
         row["push_vs_nccl_e2e"] = round(row["nccl_e2e_us"] / row["push_e2e_us"], 2)
         row["push_fused"] = bool(nvfp4_ops.can_push(m, C))     # False: few rows take the decode GEMV and the pull form
+        # what gather="auto" runs for this rank count and row count (the same code path as the mode it picks)
+        row["auto_gather"] = "push" if (row["push_fused"] and D.ColumnSplitLinear.auto_pushes(world, m)) else "peer"
+        row["auto_e2e_us"] = row[row["auto_gather"] + "_e2e_us"]
+        row["auto_vs_nccl_e2e"] = round(row["nccl_e2e_us"] / row["auto_e2e_us"], 2)
         rows.append(row)
     for mode in ("peer", "push"):
         splits[mode].peer.check()
