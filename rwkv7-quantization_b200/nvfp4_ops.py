@@ -76,7 +76,8 @@ def load_nvfp4_weight(z, key, dev):
 
 
 def quantize_activations_nvfp4(x: torch.Tensor, blocked: bool = False):
-    """On-the-fly activation quantization on the device, one cooperative launch:
+    """On-the-fly activation quantization on the device (one cluster launch, two chained launches or one cooperative
+    launch by block size: rwkvq_actq_nvfp4_fused picks):
     (packed codes [M,K/2], block scales [M,K/16] e4m3, pts [1]); with blocked=True the scales come in the blocked
     order of the tensor-core GEMM (a flat uint8 buffer) instead of row-major."""
     from fused_fp8_gemm import _rows16
